@@ -1,0 +1,433 @@
+/*
+ * loom_b200 -- C ABI of the B200 (sm_100a) provider for the Loom Infer paged-decode path.
+ *
+ * The ABI mirrors, one to one, the Rust surface an engine uses for this path in the reference
+ * (paths below are relative to the reference project root):
+ *
+ *     validated spec -> immutable plan -> checked typed bindings -> one caller-owned
+ *     stream -> one completion fence            (docs/design/loom-infer-architecture.md)
+ *
+ * Conventions
+ *   - every function returns an lb_status (0 = LB_OK) and writes results through out-params;
+ *     nothing throws across the boundary;
+ *   - every non-zero status is a reference error variant, by name (lb_status_name);
+ *     the variant's payload is read with lb_last_error (thread-local);
+ *   - "moved" parameters are consumed by the call whether it succeeds or not, exactly where
+ *     the Rust API takes `self` / an owned value;
+ *   - no internal locking: one thread drives one queue; graph objects are thread-affine
+ *     (crates/loom-infer-cuda/src/graph/mod.rs:29,173,234);
+ *   - device buffers stay caller-allocated; a buffer bound read-write belongs to the binding
+ *     set until lb_completion_wait / lb_graph_exec_into_bindings hands the set back.
+ */
+#ifndef LOOM_B200_H
+#define LOOM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t lb_status;
+
+/* ---- status codes ------------------------------------------------------------------------ */
+enum {
+    LB_OK = 0,
+    /* ContractError, crates/loom-infer/src/error.rs:6-109 (same order) */
+    LB_ZERO_DIMENSION = 1,
+    LB_ELEMENT_COUNT_OVERFLOW,
+    LB_INVALID_EPSILON,
+    LB_UNSUPPORTED_HEAD_DIMENSION,       /* a=expected b=actual */
+    LB_UNSUPPORTED_PAGE_SIZE,            /* a=expected b=actual */
+    LB_INVALID_HEAD_MAPPING,             /* a=query_heads b=kv_heads */
+    LB_INVALID_PARTITION_COUNT,          /* a=partitions b=kv_len (pages for the paged split) */
+    LB_INVALID_INDPTR_START,
+    LB_NON_MONOTONIC_INDPTR,
+    LB_EMPTY_RAGGED_REQUEST,
+    LB_RAGGED_QUERY_LONGER_THAN_KV,
+    LB_INVALID_PAGE_INDPTR_START,        /* a=actual */
+    LB_NON_MONOTONIC_PAGE_INDPTR,        /* a=request b=start c=end */
+    LB_EMPTY_PAGED_REQUEST,              /* a=request */
+    LB_PAGE_INDEX_OUT_OF_RANGE,          /* a=position b=index c=max_num_pages */
+    LB_INVALID_LAST_PAGE_LENGTH,         /* a=request b=length c=page_size */
+    LB_INVALID_ROTARY_DIMENSION,
+    LB_INVALID_ROPE_SCALE,
+    LB_INVALID_ROPE_THETA,
+    LB_NEGATIVE_POSITION_ID,
+    LB_UNSUPPORTED_APPEND_TOKEN_COUNT,   /* a=maximum b=actual */
+    LB_APPEND_BATCH_INDEX_OUT_OF_RANGE,  /* a=token b=index c=batch_size */
+    LB_APPEND_POSITION_OUT_OF_RANGE,     /* a=token b=request c=position d=kv_len */
+    LB_DUPLICATE_PAGE_APPEND_SLOT,       /* a=first_request b=second_request c=page d=offset */
+    LB_DUPLICATE_PAGE_APPEND_TOKEN_SLOT, /* a=first_token b=second_token c=page d=offset */
+    LB_UNSUPPORTED_DTYPE,
+    LB_LENGTH_MISMATCH,                  /* operand=buffer a=expected b=actual */
+
+    /* CommandError, crates/loom-infer-cuda/src/command/mod.rs:66-107 */
+    LB_ZERO_COMMAND_CAPACITY = 100,
+    LB_ZERO_BINDING_CAPACITY,
+    LB_IDENTIFIER_SPACE_EXHAUSTED,
+    LB_BINDINGS_QUEUE_MISMATCH,
+    LB_QUEUE_POISONED,
+    LB_SCOPE_POISONED,
+    LB_BINDING_CAPACITY_EXCEEDED,        /* a=capacity */
+    LB_BUFFER_CONTEXT_MISMATCH,          /* a=buffer_device b=stream_device */
+    LB_BINDING_SET_MISMATCH,
+    LB_BINDING_SLOT_OUT_OF_RANGE,        /* a=slot b=bindings */
+    LB_BINDING_IS_READ_ONLY,             /* a=slot */
+    LB_BINDING_SLOT_VACANT,              /* a=slot */
+    LB_BINDING_TYPE_MISMATCH,            /* a=slot */
+    LB_DUPLICATE_BINDING_SLOT,
+    LB_COMMAND_CAPACITY_EXCEEDED,        /* a=capacity */
+    LB_EXTERNAL_COMMAND,
+    LB_DRIVER,                           /* a=CUDA error code */
+
+    /* {PagedBatchDecode,Rope}EnqueueError, crates/loom-infer-cuda/src/attention/decode.rs:1529-1551,
+     * crates/loom-infer-cuda/src/rope/mod.rs (RopeEnqueueError) */
+    LB_ENQUEUE_LENGTH_MISMATCH = 200,    /* operand a=expected b=actual */
+    LB_PAGE_INDICES_TOO_SHORT,           /* a=minimum b=actual */
+    LB_MISALIGNED_BUFFER,                /* operand a=address b=alignment */
+
+    /* {PagedBatchDecode,Rope}PlanError, decode.rs:1499-1505, rope/mod.rs (RopePlanError) */
+    LB_STATE_COUNT_OUT_OF_RANGE = 300,   /* a=states */
+    LB_STATE_COUNT_OVERFLOW,
+    LB_LAUNCH_CONTRACT,                  /* device or launch shape unusable; a=detail code */
+    LB_UNSUPPORTED_DEVICE,               /* a=compute capability major*10+minor */
+
+    /* GraphError, crates/loom-infer-cuda/src/graph/mod.rs:687-721; CaptureError :136-143 */
+    LB_GRAPH_DEFAULT_STREAM_UNSUPPORTED = 400,
+    LB_GRAPH_EMPTY_CAPTURE,
+    LB_GRAPH_CAPTURE_INVALIDATED,
+    LB_GRAPH_NULL_EXECUTABLE_HANDLE,
+    LB_GRAPH_EXECUTION_POISONED,
+    LB_GRAPH_REPLAY_IN_FLIGHT,
+    LB_GRAPH_LAUNCH_COUNT_EXHAUSTED,
+    LB_GRAPH_TIMING_EVENT_CONTEXT_MISMATCH,
+    LB_GRAPH_DRIVER,                     /* operand=operation a=CUDA error code */
+    LB_GRAPH_SETTLEMENT,                 /* operand=operation a=error b=synchronization error */
+    LB_GRAPH_CAPTURE_RECORD,             /* the record callback failed; a=its status */
+
+    /* misuse the Rust borrow checker rules out at compile time */
+    LB_INVALID_ARGUMENT = 500,           /* null pointer, dead object, not a device pointer */
+    LB_OBJECT_IN_USE                     /* queue already has a live scope / completion */
+};
+
+typedef struct lb_error_info {
+    lb_status status;
+    char name[48];    /* variant name, e.g. "LengthMismatch" */
+    char operand[32]; /* buffer / operand / operation name where the variant has one */
+    int64_t a, b, c, d;
+    char message[256]; /* the reference's Display text for the variant */
+} lb_error_info;
+
+const char *lb_status_name(lb_status status);
+/* Details of the last non-zero status returned on this thread. */
+void lb_last_error(lb_error_info *out);
+/* Library version and the compute architecture the kernels were built for. */
+const char *lb_build_info(void);
+
+/* ---- contract: specs and host-side metadata validation ------------------------------------ */
+
+/* Bf16PagedBatchDecodeSpec, crates/loom-infer/src/attention/paged_decode/mod.rs:17-149 */
+typedef struct lb_paged_spec {
+    size_t batch_size, max_num_pages, num_query_heads, num_kv_heads;
+    float softmax_scale; /* 1/sqrt(128) */
+} lb_paged_spec;
+
+#define LB_HEAD_DIM 128u
+#define LB_PAGE_SIZE 16u
+#define LB_PARTIAL_STATE_WIDTH 130u      /* single_decode/mod.rs:13 */
+#define LB_APPEND_MAX_TOKENS 64u         /* paged_append/mod.rs:12 */
+
+/* Bf16PagedBatchDecodeSpec::new, paged_decode/mod.rs:28-82 */
+lb_status lb_paged_spec_new(size_t batch_size, size_t max_num_pages, size_t num_query_heads,
+                            size_t num_kv_heads, size_t head_dim, size_t page_size,
+                            lb_paged_spec *out);
+/* numel accessors, paged_decode/mod.rs:112-149 */
+size_t lb_paged_spec_query_numel(const lb_paged_spec *spec);
+size_t lb_paged_spec_kv_pages_numel(const lb_paged_spec *spec);
+size_t lb_paged_spec_lse_numel(const lb_paged_spec *spec);
+size_t lb_paged_spec_gqa_group_size(const lb_paged_spec *spec);
+/* kv_head_for_query_head, :143-149; returns -1 for None */
+int64_t lb_paged_spec_kv_head_for_query_head(const lb_paged_spec *spec, size_t query_head);
+/* validate_page_table, :152-213 (host copies of the metadata) */
+lb_status lb_paged_spec_validate_page_table(const lb_paged_spec *spec, const int32_t *page_indptr,
+                                            size_t page_indptr_len, const int32_t *page_indices,
+                                            size_t page_indices_len, const int32_t *last_page_len,
+                                            size_t last_page_len_len);
+/* Bf16PagedBatchDecodePageTable::request_kv_len / physical_page_for_token, :252-278.
+ * The table must have passed validate_page_table.  Return 0 (None) or 1 (Some). */
+int lb_page_table_request_kv_len(const lb_paged_spec *spec, const int32_t *page_indptr,
+                                 const int32_t *last_page_len, size_t request, size_t *kv_len);
+int lb_page_table_physical_page_for_token(const lb_paged_spec *spec, const int32_t *page_indptr,
+                                          const int32_t *page_indices,
+                                          const int32_t *last_page_len, size_t request,
+                                          size_t logical_token, size_t *physical_page,
+                                          size_t *page_offset);
+
+/* Bf16RopePagedKvAppendSpec::validate_page_table (duplicate final slots),
+ * crates/loom-infer/src/attention/paged_append/mod.rs:95-131 */
+lb_status lb_append_spec_validate_page_table(const lb_paged_spec *spec, const int32_t *page_indptr,
+                                             size_t page_indptr_len, const int32_t *page_indices,
+                                             size_t page_indices_len,
+                                             const int32_t *last_page_len,
+                                             size_t last_page_len_len);
+
+/* Bf16RopePagedKvAppendTokensSpec, paged_append/mod.rs:136-241 */
+typedef struct lb_append_tokens_spec {
+    lb_paged_spec paged;
+    size_t tokens;
+    size_t max_tokens; /* LB_APPEND_MAX_TOKENS for the contract; 0 = extended (no total cap) */
+} lb_append_tokens_spec;
+
+/* Bf16RopePagedKvAppendTokensSpec::new, :144-177 */
+lb_status lb_append_tokens_spec_new(size_t tokens, size_t batch_size, size_t max_num_pages,
+                                    size_t num_query_heads, size_t num_kv_heads, size_t head_dim,
+                                    size_t page_size, lb_append_tokens_spec *out);
+/* Extension (no reference counterpart): the same contract without the 64-token total cap, up
+ * to lb_append_extended_max_tokens() tokens; one command, same all-or-nothing device guard. */
+lb_status lb_append_tokens_spec_new_extended(size_t tokens, size_t batch_size,
+                                             size_t max_num_pages, size_t num_query_heads,
+                                             size_t num_kv_heads, size_t head_dim,
+                                             size_t page_size, lb_append_tokens_spec *out);
+size_t lb_append_extended_max_tokens(void);
+/* validate_metadata, :244-317; slots_out (nullable) receives tokens x (page, offset) */
+lb_status lb_append_tokens_spec_validate_metadata(
+    const lb_append_tokens_spec *spec, const int32_t *batch_indices, size_t batch_indices_len,
+    const int32_t *positions, size_t positions_len, const int32_t *page_indptr,
+    size_t page_indptr_len, const int32_t *page_indices, size_t page_indices_len,
+    const int32_t *last_page_len, size_t last_page_len_len, int64_t *slots_out);
+
+/* Split-K contract pieces, crates/loom-infer/src/attention/single_decode/mod.rs:125-194,
+ * applied per request to the PAGE count (the reference has no paged split-K, so chunks are
+ * whole pages and the workspace gains a leading request dimension).
+ * partition_token_range :171-185 -> page range; returns 0 (None) / 1 (Some). */
+int lb_split_partition_range(size_t length, size_t partitions, size_t partition, size_t *start,
+                             size_t *end);
+/* workspace_numel :163-165 with a leading request dimension: batch*qh*partitions*130 */
+lb_status lb_paged_split_workspace_numel(const lb_paged_spec *spec, size_t partitions,
+                                         size_t *numel);
+/* partial_state_offset :187-193 with the request dimension; returns -1 for None */
+int64_t lb_paged_split_state_offset(const lb_paged_spec *spec, size_t partitions, size_t request,
+                                    size_t query_head, size_t partition);
+
+/* ---- command runtime ---------------------------------------------------------------------- */
+
+typedef struct lb_queue lb_queue;           /* CommandQueue,      command/submission.rs:18-117 */
+typedef struct lb_bindings lb_bindings;     /* CheckedBindings,   command/binding.rs:16-134 */
+typedef struct lb_scope lb_scope;           /* CommandScope,      command/submission.rs:119-329 */
+typedef struct lb_completion lb_completion; /* CommandCompletion, command/completion.rs:6-141 */
+
+/* BindingElement types, command/binding.rs:181-187 */
+enum { LB_F32 = 0, LB_F16 = 1, LB_BF16 = 2, LB_I32 = 3, LB_U8 = 4 };
+enum { LB_ACCESS_READ = 0, LB_ACCESS_WRITE = 1, LB_ACCESS_READ_WRITE = 2 };
+
+/* Read<T> / Write<T> / ReadWrite<T>, command/binding.rs:297-336.  Plain value; copyable. */
+typedef struct lb_handle {
+    uint64_t set_id;
+    uint32_t slot;
+    uint8_t dtype;
+    uint8_t access;
+    uint16_t reserved;
+} lb_handle;
+
+/* ReadWrite::read / ReadWrite::write, binding.rs:313-327 */
+lb_handle lb_handle_read(lb_handle read_write);
+lb_handle lb_handle_write(lb_handle read_write);
+
+/* CommandQueue::new, submission.rs:31-46.  `stream` is a cudaStream_t / CUstream owned by
+ * the caller; it must outlive the queue. */
+lb_status lb_queue_create(void *stream, size_t max_commands, lb_queue **out);
+/* Drop for CommandQueue, submission.rs:102-117 (synchronises retained work first). */
+void lb_queue_destroy(lb_queue *queue);
+void *lb_queue_stream(const lb_queue *queue);
+size_t lb_queue_max_commands(const lb_queue *queue);
+int lb_queue_is_poisoned(const lb_queue *queue);
+/* CommandQueue::bindings, submission.rs:58-70 */
+lb_status lb_queue_bindings(lb_queue *queue, size_t capacity, lb_bindings **out);
+/* CommandQueue::begin, submission.rs:73-99; `bindings` is moved. */
+lb_status lb_queue_begin(lb_queue *queue, lb_bindings *bindings, lb_scope **out);
+
+size_t lb_bindings_len(const lb_bindings *bindings);
+size_t lb_bindings_capacity(const lb_bindings *bindings);
+void lb_bindings_destroy(lb_bindings *bindings);
+/* bind_read / bind_read_write, binding.rs:38-87.  On failure the caller keeps the buffer. */
+lb_status lb_bind_read(lb_bindings *bindings, int dtype, const void *device_ptr, size_t numel,
+                       lb_handle *out);
+lb_status lb_bind_read_write(lb_bindings *bindings, int dtype, void *device_ptr, size_t numel,
+                             lb_handle *out);
+/* take_read_write, binding.rs:93-107; the slot becomes vacant. */
+lb_status lb_take_read_write(lb_bindings *bindings, lb_handle handle, void **device_ptr,
+                             size_t *numel);
+
+/* CommandScope::finish, submission.rs:131-151; `scope` is moved. */
+lb_status lb_scope_finish(lb_scope *scope, lb_completion **out);
+/* Drop of an unfinished CommandScope, submission.rs:296-329. */
+void lb_scope_abandon(lb_scope *scope);
+size_t lb_scope_submitted(const lb_scope *scope);
+
+/* CommandCompletion::{is_complete, submitted, wait}, completion.rs:38-88 */
+lb_status lb_completion_is_complete(lb_completion *completion, int *complete);
+size_t lb_completion_submitted(const lb_completion *completion);
+/* `completion` is moved; on success *out receives the reusable bindings. */
+lb_status lb_completion_wait(lb_completion *completion, lb_bindings **out);
+/* Drop for CommandCompletion, completion.rs:126-141 (settles, bindings are released). */
+void lb_completion_abandon(lb_completion *completion);
+
+/* ---- decode provider ----------------------------------------------------------------------- */
+
+typedef struct lb_decode_provider lb_decode_provider; /* DecodeProvider, decode.rs:1001-1104 */
+typedef struct lb_paged_decode_plan lb_paged_decode_plan; /* Bf16PagedBatchDecodePlan :1181-1297 */
+
+/* Bf16PagedBatchDecodeAlgorithm, decode.rs:1157-1161, for this provider */
+enum { LB_DECODE_DIRECT = 0, LB_DECODE_SPLIT_K = 1 };
+
+typedef struct lb_paged_decode_options {
+    uint32_t partitions;    /* 0 = plan-time heuristic, 1 = direct, N>1 = split-K with N chunks */
+    uint32_t heads_per_cta; /* 0 = heuristic; KV heads one CTA streams (1, 2, 4 or 8) */
+    uint32_t reserved[6];
+} lb_paged_decode_options;
+
+typedef struct lb_paged_decode_plan_info {
+    int32_t algorithm;       /* LB_DECODE_DIRECT / LB_DECODE_SPLIT_K */
+    uint32_t partitions;
+    uint32_t heads_per_cta;
+    uint32_t q_tiles;        /* 16-row MMA tiles per KV head group handled by one CTA */
+    uint32_t q_blocks;       /* CTAs per KV head needed to cover the GQA group */
+    uint32_t pages_per_stage;
+    uint32_t stages;
+    uint32_t grid, block, shared_bytes;
+    uint32_t merge_grid, merge_block;
+    uint32_t commands;       /* 1 direct, 2 split (partials + merge) */
+    size_t workspace_numel;  /* F32 elements the caller must bind (0 for direct) */
+    size_t workspace_bytes;
+} lb_paged_decode_plan_info;
+
+/* Bf16PagedBatchDecodeArgs, decode.rs:1451-1487, plus the split-K workspace
+ * (Bf16SingleDecodeSplitKArgs.workspace, :1420-1449).  workspace is ignored by direct plans. */
+typedef struct lb_paged_decode_args {
+    lb_handle query, key_pages, value_pages, page_indptr, page_indices, last_page_len; /* Read */
+    lb_handle output, lse;                                                              /* Write */
+    lb_handle workspace;                                                                /* ReadWrite<f32> */
+} lb_paged_decode_args;
+
+/* DecodeProvider::load, decode.rs:1009-1014 */
+lb_status lb_decode_provider_load(int device, lb_decode_provider **out);
+void lb_decode_provider_destroy(lb_decode_provider *provider);
+/* Reads (and clears) the provider's device status word: 0 = no kernel of this provider gave up
+ * on a bounded wait since the last read.  Synchronises the device.  No reference counterpart:
+ * the reference's kernels have no waits. */
+lb_status lb_decode_provider_device_status(const lb_decode_provider *provider, int32_t *status);
+/* DecodeProvider::plan_bf16_paged_batch, decode.rs:1067-1103; options may be NULL. */
+lb_status lb_paged_decode_plan_create(const lb_decode_provider *provider,
+                                      const lb_paged_spec *spec,
+                                      const lb_paged_decode_options *options,
+                                      lb_paged_decode_plan **out);
+void lb_paged_decode_plan_destroy(lb_paged_decode_plan *plan);
+/* Bf16PagedBatchDecodePlan::{spec, algorithm}, :1189-1196, and
+ * workspace_required_{numel,bytes}, :1313-1319 */
+lb_status lb_paged_decode_plan_info_get(const lb_paged_decode_plan *plan, lb_paged_spec *spec,
+                                        lb_paged_decode_plan_info *info);
+/* Bf16PagedBatchDecodePlan::enqueue_into, decode.rs:1199-1296 (direct) and the two-command
+ * shape of Bf16SingleDecodeSplitKPlan::enqueue_into, :1322-1389 (split-K). */
+lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *scope,
+                                  const lb_paged_decode_args *args);
+/* The plan-time split heuristic as a pure function (testable without a device). */
+lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
+                                 const lb_paged_decode_options *options,
+                                 lb_paged_decode_plan_info *info);
+
+/* ---- RoPE + paged KV append provider --------------------------------------------------------- */
+
+typedef struct lb_rope_provider lb_rope_provider;         /* RopeProvider, rope/mod.rs:579-683 */
+typedef struct lb_rope_append_plan lb_rope_append_plan;   /* Bf16RopePagedKvAppend{,Tokens}Plan */
+
+/* Bf16RopePagedKvAppendArgs / ...TokensArgs, rope/mod.rs:963-1077.  batch_indices and
+ * positions are ignored by the one-token-per-request plan. */
+typedef struct lb_rope_append_args {
+    lb_handle query, key, value, batch_indices, positions, page_indptr, page_indices,
+        last_page_len;                           /* Read */
+    lb_handle query_output, key_pages, value_pages; /* Write */
+} lb_rope_append_args;
+
+typedef struct lb_rope_append_plan_info {
+    int32_t explicit_tokens; /* 0: one token per request; 1: explicit token list */
+    uint32_t tokens;
+    uint32_t grid, block, shared_bytes;
+    uint32_t commands; /* always 1 */
+} lb_rope_append_plan_info;
+
+/* RopeProvider::load, rope/mod.rs:586-590 */
+lb_status lb_rope_provider_load(int device, lb_rope_provider **out);
+void lb_rope_provider_destroy(lb_rope_provider *provider);
+/* RopeProvider::plan_bf16_paged_append, rope/mod.rs:628-654 */
+lb_status lb_rope_append_plan_create(const lb_rope_provider *provider, const lb_paged_spec *spec,
+                                     lb_rope_append_plan **out);
+/* RopeProvider::plan_bf16_paged_append_tokens, rope/mod.rs:656-682 */
+lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
+                                            const lb_append_tokens_spec *spec,
+                                            lb_rope_append_plan **out);
+void lb_rope_append_plan_destroy(lb_rope_append_plan *plan);
+lb_status lb_rope_append_plan_info_get(const lb_rope_append_plan *plan,
+                                       lb_rope_append_plan_info *info);
+/* Bf16RopePagedKvAppend{,Tokens}Plan::enqueue_into, rope/mod.rs:758-830,846-933 */
+lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scope,
+                                 const lb_rope_append_args *args);
+
+/* ---- fixed-address CUDA Graph ------------------------------------------------------------------ */
+
+typedef struct lb_graph_queue lb_graph_queue;           /* GraphQueue, graph/mod.rs:27-71 */
+typedef struct lb_captured_graph lb_captured_graph;     /* CapturedGraph, :165-215 */
+typedef struct lb_graph_exec lb_graph_exec;             /* GraphExec, :217-382 */
+typedef struct lb_graph_completion lb_graph_completion; /* GraphLaunchCompletion, :384-463 */
+
+/* The closure given to GraphQueue::capture: enqueue plans into `scope`; return LB_OK or an
+ * error status (reported as LB_GRAPH_CAPTURE_RECORD). */
+typedef lb_status (*lb_record_fn)(lb_scope *scope, void *user);
+
+/* GraphQueue::new, graph/mod.rs:34-40 (private non-default stream on `device`) */
+lb_status lb_graph_queue_create(int device, size_t max_commands, lb_graph_queue **out);
+void lb_graph_queue_destroy(lb_graph_queue *queue);
+/* GraphQueue::bindings, :43-45 */
+lb_status lb_graph_queue_bindings(lb_graph_queue *queue, size_t capacity, lb_bindings **out);
+/* GraphQueue::capture, :54-70; `queue` and `bindings` are moved. */
+lb_status lb_graph_capture(lb_graph_queue *queue, lb_bindings *bindings, lb_record_fn record,
+                           void *user, lb_captured_graph **out);
+size_t lb_captured_graph_commands(const lb_captured_graph *graph);
+/* CapturedGraph::instantiate, :183-206; `graph` is moved. */
+lb_status lb_captured_graph_instantiate(lb_captured_graph *graph, lb_graph_exec **out);
+void lb_captured_graph_destroy(lb_captured_graph *graph);
+size_t lb_graph_exec_commands(const lb_graph_exec *exec);
+uint64_t lb_graph_exec_launches(const lb_graph_exec *exec);
+/* GraphExec::launch, :249-293 */
+lb_status lb_graph_exec_launch(lb_graph_exec *exec, lb_graph_completion **out);
+/* GraphExec::measure_launch_ms, :301-323: one replay plus its completion event between two
+ * timing events created and destroyed by the library on the capture stream. */
+lb_status lb_graph_exec_measure_launch_ms(lb_graph_exec *exec, float *milliseconds);
+/* GraphExec::into_bindings, :326-339; `exec` is moved. */
+lb_status lb_graph_exec_into_bindings(lb_graph_exec *exec, lb_bindings **out);
+void lb_graph_exec_destroy(lb_graph_exec *exec);
+uint64_t lb_graph_completion_launch_index(const lb_graph_completion *completion);
+lb_status lb_graph_completion_is_complete(lb_graph_completion *completion, int *complete);
+/* GraphLaunchCompletion::wait, :420-437; `completion` is moved. */
+lb_status lb_graph_completion_wait(lb_graph_completion *completion);
+void lb_graph_completion_abandon(lb_graph_completion *completion);
+
+/* ---- host-side fault injection (tests) ------------------------------------------------------------ */
+
+/* Replaces the CUDA driver layer under the runtime with an in-process fake: no device is
+ * touched, launches and event operations succeed unless a failure is armed.  The fake lets
+ * the ownership / poisoning state machine be exercised on a machine without a GPU.  Kernels
+ * never run under the fake; it cannot produce results. */
+void lb_test_use_fake_driver(int enable, int fake_sm_count);
+/* Arms the fake: the n-th next call of `what` ("launch", "event_record", "event_sync",
+ * "event_query", "stream_sync", "device_sync", "graph_launch", "capture_begin",
+ * "capture_end", "instantiate") returns `cuda_error`.  n = 1 fails the very next call. */
+void lb_test_fake_fail(const char *what, int n, int cuda_error);
+/* Number of kernel launches the fake (or the real driver layer) has accepted so far. */
+uint64_t lb_test_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOOM_B200_H */

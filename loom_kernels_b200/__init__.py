@@ -1,0 +1,9 @@
+"""B200-native provider for the Loom Infer paged-decode hot path.
+
+`api` mirrors the reference's operator interface over the C ABI (include/loom_b200.h);
+`build` compiles the CUDA library for sm_100a.  The package has no CPU implementation of the
+path: without the built library every entry point raises.
+"""
+from . import _abi  # noqa: F401
+from .api import *  # noqa: F401,F403
+from .api import DeviceSpan  # noqa: F401

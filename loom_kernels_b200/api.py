@@ -1,0 +1,779 @@
+"""Host-side mirror of the Loom Infer operator interface for the paged-decode path.
+
+Same names, argument meaning and error behaviour as the reference's Rust API
+(crates/loom-infer/src/attention/{paged_decode,paged_append}/mod.rs,
+crates/loom-infer-cuda/src/{command,graph,attention/decode.rs,rope/mod.rs}); every method is a
+thin call through the C ABI in include/loom_b200.h.  Nothing here computes on the CPU.
+
+Buffers are CUDA torch tensors (torch owns device memory; this layer only passes pointers) or
+`DeviceSpan` values (a raw device pointer with a length), which is what a non-torch engine binds.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from dataclasses import dataclass
+from typing import Callable, Optional, Sequence
+
+import numpy as np
+
+from . import _abi
+from ._abi import (ACCESS_READ, ACCESS_READ_WRITE, ACCESS_WRITE, BF16, F16, F32, HEAD_DIM, I32,
+                   PAGE_SIZE, PARTIAL_STATE_WIDTH, U8)
+
+# ---- errors --------------------------------------------------------------------------------------
+
+
+class LoomError(Exception):
+    """One reference error variant: `variant` is its name, `operand` and `payload` its fields."""
+
+    def __init__(self, info: _abi.ErrorInfo):
+        self.status = info.status
+        self.variant = info.name.decode()
+        self.operand = info.operand.decode()
+        self.payload = (info.a, info.b, info.c, info.d)
+        super().__init__(f"{self.variant}: {info.message.decode()}")
+
+
+class ContractError(LoomError):
+    pass
+
+
+class CommandError(LoomError):
+    pass
+
+
+class EnqueueError(LoomError):
+    """PagedBatchDecodeEnqueueError / RopeEnqueueError (own variants; Command(..) is CommandError)."""
+
+
+class PlanError(LoomError):
+    pass
+
+
+class GraphError(LoomError):
+    pass
+
+
+def _raise(status: int):
+    info = _abi.ErrorInfo()
+    _abi.load().lb_last_error(byref(info))
+    if status < 100:
+        raise ContractError(info)
+    if status < 200:
+        raise CommandError(info)
+    if status < 300:
+        raise EnqueueError(info)
+    if status < 400:
+        raise PlanError(info)
+    if status < 500:
+        raise GraphError(info)
+    raise LoomError(info)
+
+
+def _check(status: int):
+    if status != 0:
+        _raise(status)
+
+
+def _i32(values):
+    array = np.ascontiguousarray(values, dtype=np.int32)
+    return array, array.ctypes.data_as(ctypes.POINTER(c_int32)), c_size_t(array.size)
+
+
+# ---- contract --------------------------------------------------------------------------------------
+
+
+class Bf16PagedBatchDecodeSpec:
+    """crates/loom-infer/src/attention/paged_decode/mod.rs:17-214."""
+
+    def __init__(self, raw: _abi.PagedSpec):
+        self._raw = raw
+
+    @classmethod
+    def new(cls, batch_size, max_num_pages, num_query_heads, num_kv_heads, head_dim=HEAD_DIM,
+            page_size=PAGE_SIZE):
+        raw = _abi.PagedSpec()
+        _check(_abi.load().lb_paged_spec_new(batch_size, max_num_pages, num_query_heads,
+                                             num_kv_heads, head_dim, page_size, byref(raw)))
+        return cls(raw)
+
+    def __eq__(self, other):
+        return isinstance(other, Bf16PagedBatchDecodeSpec) and self.key() == other.key()
+
+    def key(self):
+        return (self.batch_size(), self.max_num_pages(), self.num_query_heads(),
+                self.num_kv_heads())
+
+    def batch_size(self): return self._raw.batch_size
+    def max_num_pages(self): return self._raw.max_num_pages
+    def num_query_heads(self): return self._raw.num_query_heads
+    def num_kv_heads(self): return self._raw.num_kv_heads
+    def head_dim(self): return HEAD_DIM
+    def page_size(self): return PAGE_SIZE
+    def softmax_scale(self): return self._raw.softmax_scale
+    def gqa_group_size(self): return _abi.load().lb_paged_spec_gqa_group_size(byref(self._raw))
+    def query_numel(self): return _abi.load().lb_paged_spec_query_numel(byref(self._raw))
+    def kv_pages_numel(self): return _abi.load().lb_paged_spec_kv_pages_numel(byref(self._raw))
+    def output_numel(self): return self.query_numel()
+    def lse_numel(self): return _abi.load().lb_paged_spec_lse_numel(byref(self._raw))
+    def page_indptr_numel(self): return self.batch_size() + 1
+    def last_page_len_numel(self): return self.batch_size()
+
+    def kv_head_for_query_head(self, query_head: int) -> Optional[int]:
+        head = _abi.load().lb_paged_spec_kv_head_for_query_head(byref(self._raw), query_head)
+        return None if head < 0 else head
+
+    def validate_page_table(self, page_indptr, page_indices, last_page_len):
+        ip, ipp, ipl = _i32(page_indptr)
+        ix, ixp, ixl = _i32(page_indices)
+        la, lap, lal = _i32(last_page_len)
+        _check(_abi.load().lb_paged_spec_validate_page_table(byref(self._raw), ipp, ipl, ixp, ixl,
+                                                             lap, lal))
+        return Bf16PagedBatchDecodePageTable(self, ip, ix, la)
+
+
+class Bf16PagedBatchDecodePageTable:
+    """Validated page-table view, paged_decode/mod.rs:216-279."""
+
+    def __init__(self, spec, indptr, indices, last):
+        self._spec, self._indptr, self._indices, self._last = spec, indptr, indices, last
+
+    def spec(self): return self._spec
+    def page_indptr(self): return self._indptr
+    def page_indices(self): return self._indices
+    def last_page_len(self): return self._last
+
+    def request_page_range(self, request):
+        if request >= self._spec.batch_size():
+            return None
+        return int(self._indptr[request]), int(self._indptr[request + 1])
+
+    def request_kv_len(self, request) -> Optional[int]:
+        out = c_size_t()
+        ok = _abi.load().lb_page_table_request_kv_len(
+            byref(self._spec._raw), self._indptr.ctypes.data_as(ctypes.POINTER(c_int32)),
+            self._last.ctypes.data_as(ctypes.POINTER(c_int32)), request, byref(out))
+        return out.value if ok else None
+
+    def physical_page_for_token(self, request, logical_token):
+        page, offset = c_size_t(), c_size_t()
+        ok = _abi.load().lb_page_table_physical_page_for_token(
+            byref(self._spec._raw), self._indptr.ctypes.data_as(ctypes.POINTER(c_int32)),
+            self._indices.ctypes.data_as(ctypes.POINTER(c_int32)),
+            self._last.ctypes.data_as(ctypes.POINTER(c_int32)), request, logical_token,
+            byref(page), byref(offset))
+        return (page.value, offset.value) if ok else None
+
+
+class Bf16RopePagedKvAppendSpec:
+    """crates/loom-infer/src/attention/paged_append/mod.rs:14-132."""
+
+    def __init__(self, paged: Bf16PagedBatchDecodeSpec):
+        self._paged = paged
+
+    @classmethod
+    def new(cls, batch_size, max_num_pages, num_query_heads, num_kv_heads, head_dim=HEAD_DIM,
+            page_size=PAGE_SIZE):
+        return cls(Bf16PagedBatchDecodeSpec.new(batch_size, max_num_pages, num_query_heads,
+                                                num_kv_heads, head_dim, page_size))
+
+    def paged(self): return self._paged
+    def batch_size(self): return self._paged.batch_size()
+    def max_num_pages(self): return self._paged.max_num_pages()
+    def num_query_heads(self): return self._paged.num_query_heads()
+    def num_kv_heads(self): return self._paged.num_kv_heads()
+    def query_numel(self): return self._paged.query_numel()
+    def key_numel(self): return self.batch_size() * self.num_kv_heads() * HEAD_DIM
+    def value_numel(self): return self.key_numel()
+    def query_output_numel(self): return self.query_numel()
+    def kv_pages_numel(self): return self._paged.kv_pages_numel()
+
+    def validate_page_table(self, page_indptr, page_indices, last_page_len):
+        ip, ipp, ipl = _i32(page_indptr)
+        ix, ixp, ixl = _i32(page_indices)
+        la, lap, lal = _i32(last_page_len)
+        _check(_abi.load().lb_append_spec_validate_page_table(byref(self._paged._raw), ipp, ipl,
+                                                              ixp, ixl, lap, lal))
+        return Bf16PagedBatchDecodePageTable(self._paged, ip, ix, la)
+
+
+class Bf16RopePagedKvAppendTokensSpec:
+    """paged_append/mod.rs:134-318.  `new_extended` lifts the 64-token total cap."""
+
+    def __init__(self, raw: _abi.AppendTokensSpec):
+        self._raw = raw
+        self._paged = Bf16PagedBatchDecodeSpec(raw.paged)
+
+    @classmethod
+    def new(cls, tokens, batch_size, max_num_pages, num_query_heads, num_kv_heads,
+            head_dim=HEAD_DIM, page_size=PAGE_SIZE):
+        raw = _abi.AppendTokensSpec()
+        _check(_abi.load().lb_append_tokens_spec_new(tokens, batch_size, max_num_pages,
+                                                     num_query_heads, num_kv_heads, head_dim,
+                                                     page_size, byref(raw)))
+        return cls(raw)
+
+    @classmethod
+    def new_extended(cls, tokens, batch_size, max_num_pages, num_query_heads, num_kv_heads,
+                     head_dim=HEAD_DIM, page_size=PAGE_SIZE):
+        raw = _abi.AppendTokensSpec()
+        _check(_abi.load().lb_append_tokens_spec_new_extended(
+            tokens, batch_size, max_num_pages, num_query_heads, num_kv_heads, head_dim, page_size,
+            byref(raw)))
+        return cls(raw)
+
+    def tokens(self): return self._raw.tokens
+    def paged(self): return self._paged
+    def batch_size(self): return self._paged.batch_size()
+    def max_num_pages(self): return self._paged.max_num_pages()
+    def num_query_heads(self): return self._paged.num_query_heads()
+    def num_kv_heads(self): return self._paged.num_kv_heads()
+    def query_numel(self): return self.tokens() * self.num_query_heads() * HEAD_DIM
+    def key_numel(self): return self.tokens() * self.num_kv_heads() * HEAD_DIM
+    def value_numel(self): return self.key_numel()
+    def query_output_numel(self): return self.query_numel()
+    def kv_pages_numel(self): return self._paged.kv_pages_numel()
+
+    def validate_metadata(self, batch_indices, positions, page_indptr, page_indices,
+                          last_page_len):
+        """Returns the physical (page, offset) slot of every token."""
+        _, bp, bl = _i32(batch_indices)
+        _, pp, pl = _i32(positions)
+        _, ipp, ipl = _i32(page_indptr)
+        _, ixp, ixl = _i32(page_indices)
+        _, lap, lal = _i32(last_page_len)
+        slots = np.zeros((self.tokens(), 2), dtype=np.int64)
+        _check(_abi.load().lb_append_tokens_spec_validate_metadata(
+            byref(self._raw), bp, bl, pp, pl, ipp, ipl, ixp, ixl, lap, lal,
+            slots.ctypes.data_as(ctypes.POINTER(c_int64))))
+        return [tuple(int(v) for v in row) for row in slots]
+
+
+def split_partition_range(length: int, partitions: int, partition: int):
+    """Bf16SingleDecodeSplitKSpec::partition_token_range (single_decode/mod.rs:171-185)."""
+    start, end = c_size_t(), c_size_t()
+    ok = _abi.load().lb_split_partition_range(length, partitions, partition, byref(start),
+                                              byref(end))
+    return (start.value, end.value) if ok else None
+
+
+def paged_split_workspace_numel(spec: Bf16PagedBatchDecodeSpec, partitions: int) -> int:
+    out = c_size_t()
+    _check(_abi.load().lb_paged_split_workspace_numel(byref(spec._raw), partitions, byref(out)))
+    return out.value
+
+
+def paged_split_state_offset(spec, partitions, request, query_head, partition):
+    offset = _abi.load().lb_paged_split_state_offset(byref(spec._raw), partitions, request,
+                                                     query_head, partition)
+    return None if offset < 0 else offset
+
+
+# ---- command runtime ---------------------------------------------------------------------------------
+
+
+@dataclass(frozen=True)
+class DeviceSpan:
+    """A caller-owned device allocation: pointer, element count, element type."""
+    ptr: int
+    numel: int
+    dtype: int
+
+
+def _describe(buffer):
+    if isinstance(buffer, DeviceSpan):
+        return buffer.dtype, buffer.ptr, buffer.numel
+    import torch
+    dtypes = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32,
+              torch.uint8: U8}
+    if buffer.dtype not in dtypes:
+        raise TypeError(f"unsupported element type {buffer.dtype}")
+    if not buffer.is_contiguous():
+        raise ValueError("bindings take contiguous device buffers")
+    return dtypes[buffer.dtype], buffer.data_ptr(), buffer.numel()
+
+
+class _Handle:
+    access = ACCESS_READ
+
+    def __init__(self, raw: _abi.Handle):
+        self._raw = raw
+
+    def slot(self): return self._raw.slot
+    def set_id(self): return self._raw.set_id
+
+
+class Read(_Handle):
+    access = ACCESS_READ
+
+
+class Write(_Handle):
+    access = ACCESS_WRITE
+
+
+class ReadWrite(_Handle):
+    """command/binding.rs:306-327."""
+    access = ACCESS_READ_WRITE
+
+    def read(self) -> Read:
+        return Read(_abi.load().lb_handle_read(self._raw))
+
+    def write(self) -> Write:
+        return Write(_abi.load().lb_handle_write(self._raw))
+
+
+def _null_handle():
+    return _abi.Handle()
+
+
+class CheckedBindings:
+    """command/binding.rs:16-134."""
+
+    def __init__(self, ptr):
+        self._ptr = ptr
+        self._buffers = {}
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_bindings_destroy(self._ptr)
+            self._ptr = None
+
+    def _release(self):
+        ptr, self._ptr = self._ptr, None
+        return ptr
+
+    def capacity(self): return _abi.load().lb_bindings_capacity(self._ptr)
+    def __len__(self): return _abi.load().lb_bindings_len(self._ptr)
+
+    def bind_read(self, buffer) -> Read:
+        dtype, ptr, numel = _describe(buffer)
+        raw = _abi.Handle()
+        _check(_abi.load().lb_bind_read(self._ptr, dtype, c_void_p(ptr), numel, byref(raw)))
+        self._buffers[raw.slot] = buffer
+        return Read(raw)
+
+    def bind_read_write(self, buffer) -> ReadWrite:
+        dtype, ptr, numel = _describe(buffer)
+        raw = _abi.Handle()
+        _check(_abi.load().lb_bind_read_write(self._ptr, dtype, c_void_p(ptr), numel, byref(raw)))
+        self._buffers[raw.slot] = buffer
+        return ReadWrite(raw)
+
+    def take_read_write(self, handle: ReadWrite):
+        ptr, numel = c_void_p(), c_size_t()
+        _check(_abi.load().lb_take_read_write(self._ptr, handle._raw, byref(ptr), byref(numel)))
+        return self._buffers.pop(handle._raw.slot)
+
+
+class CommandQueue:
+    """command/submission.rs:18-117.  `stream` is a torch.cuda.Stream or a raw stream handle."""
+
+    def __init__(self, stream, max_commands: int):
+        self._stream_owner = stream
+        handle = getattr(stream, "cuda_stream", stream)
+        out = c_void_p()
+        _check(_abi.load().lb_queue_create(c_void_p(handle), max_commands, byref(out)))
+        self._ptr = out.value
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_queue_destroy(self._ptr)
+            self._ptr = None
+
+    def stream(self): return self._stream_owner
+    def max_commands(self): return _abi.load().lb_queue_max_commands(self._ptr)
+    def is_poisoned(self): return bool(_abi.load().lb_queue_is_poisoned(self._ptr))
+
+    def bindings(self, capacity: int) -> CheckedBindings:
+        out = c_void_p()
+        _check(_abi.load().lb_queue_bindings(self._ptr, capacity, byref(out)))
+        return CheckedBindings(out.value)
+
+    def begin(self, bindings: CheckedBindings) -> "CommandScope":
+        buffers = bindings._buffers
+        out = c_void_p()
+        status = _abi.load().lb_queue_begin(self._ptr, bindings._ptr, byref(out))
+        if status != _abi_status("LB_OBJECT_IN_USE"):
+            bindings._release()  # moved, on success and on contract failures alike
+        _check(status)
+        return CommandScope(self, out.value, buffers)
+
+
+def _abi_status(name: str) -> int:
+    return {"LB_OBJECT_IN_USE": 501}[name]
+
+
+class CommandScope:
+    """command/submission.rs:119-329."""
+
+    def __init__(self, queue, ptr, buffers):
+        self._queue, self._ptr, self._buffers = queue, ptr, buffers
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_scope_abandon(self._ptr)
+            self._ptr = None
+
+    def submitted_commands(self): return _abi.load().lb_scope_submitted(self._ptr)
+
+    def finish(self) -> "CommandCompletion":
+        out = c_void_p()
+        ptr, self._ptr = self._ptr, None
+        _check(_abi.load().lb_scope_finish(ptr, byref(out)))
+        return CommandCompletion(self._queue, out.value, self._buffers)
+
+
+class CommandCompletion:
+    """command/completion.rs:6-141."""
+
+    def __init__(self, queue, ptr, buffers):
+        self._queue, self._ptr, self._buffers = queue, ptr, buffers
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_completion_abandon(self._ptr)
+            self._ptr = None
+
+    def submitted(self): return _abi.load().lb_completion_submitted(self._ptr)
+
+    def is_complete(self) -> bool:
+        done = c_int()
+        _check(_abi.load().lb_completion_is_complete(self._ptr, byref(done)))
+        return bool(done.value)
+
+    def wait(self) -> CheckedBindings:
+        out = c_void_p()
+        ptr, self._ptr = self._ptr, None
+        _check(_abi.load().lb_completion_wait(ptr, byref(out)))
+        bindings = CheckedBindings(out.value)
+        bindings._buffers = self._buffers
+        return bindings
+
+
+# ---- decode provider -----------------------------------------------------------------------------------
+
+
+class Bf16PagedBatchDecodeAlgorithm:
+    Direct = 0
+    SplitK = 1
+
+
+@dataclass
+class Bf16PagedBatchDecodeArgs:
+    """decode.rs:1451-1487 plus the split-K workspace operand (:1420-1449)."""
+    query: Read
+    key_pages: Read
+    value_pages: Read
+    page_indptr: Read
+    page_indices: Read
+    last_page_len: Read
+    output: Write
+    lse: Write
+    workspace: Optional[ReadWrite] = None
+
+
+class DecodeProvider:
+    """decode.rs:1001-1104."""
+
+    def __init__(self, ptr, device):
+        self._ptr, self._device = ptr, device
+
+    @classmethod
+    def load(cls, device: int = 0) -> "DecodeProvider":
+        out = c_void_p()
+        _check(_abi.load().lb_decode_provider_load(device, byref(out)))
+        return cls(out.value, device)
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_decode_provider_destroy(self._ptr)
+            self._ptr = None
+
+    def device_status(self) -> int:
+        out = c_int32()
+        _check(_abi.load().lb_decode_provider_device_status(self._ptr, byref(out)))
+        return out.value
+
+    def plan_bf16_paged_batch(self, spec: Bf16PagedBatchDecodeSpec, partitions: int = 0,
+                              heads_per_cta: int = 0) -> "Bf16PagedBatchDecodePlan":
+        options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta)
+        out = c_void_p()
+        _check(_abi.load().lb_paged_decode_plan_create(self._ptr, byref(spec._raw),
+                                                       byref(options), byref(out)))
+        return Bf16PagedBatchDecodePlan(out.value)
+
+
+def choose_paged_decode(spec, sm_count: int, partitions: int = 0, heads_per_cta: int = 0):
+    """The plan-time heuristic as a pure function (no device needed)."""
+    options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta)
+    info = _abi.DecodePlanInfo()
+    _check(_abi.load().lb_paged_decode_choose(byref(spec._raw), sm_count, byref(options),
+                                              byref(info)))
+    return info
+
+
+class Bf16PagedBatchDecodePlan:
+    """decode.rs:1181-1297; immutable."""
+
+    def __init__(self, ptr):
+        self._ptr = ptr
+        self._spec = _abi.PagedSpec()
+        self._info = _abi.DecodePlanInfo()
+        _check(_abi.load().lb_paged_decode_plan_info_get(ptr, byref(self._spec),
+                                                         byref(self._info)))
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_paged_decode_plan_destroy(self._ptr)
+            self._ptr = None
+
+    def spec(self): return Bf16PagedBatchDecodeSpec(self._spec)
+    def algorithm(self): return self._info.algorithm
+    def partitions(self): return self._info.partitions
+    def info(self): return self._info
+    def commands(self): return self._info.commands
+    def workspace_required_numel(self): return self._info.workspace_numel
+    def workspace_required_bytes(self): return self._info.workspace_bytes
+
+    def enqueue_into(self, scope: CommandScope, args: Bf16PagedBatchDecodeArgs):
+        raw = _abi.DecodeArgs(
+            query=args.query._raw, key_pages=args.key_pages._raw,
+            value_pages=args.value_pages._raw, page_indptr=args.page_indptr._raw,
+            page_indices=args.page_indices._raw, last_page_len=args.last_page_len._raw,
+            output=args.output._raw, lse=args.lse._raw,
+            workspace=args.workspace._raw if args.workspace is not None else _null_handle())
+        _check(_abi.load().lb_paged_decode_enqueue(self._ptr, scope._ptr, byref(raw)))
+
+
+# ---- RoPE + append provider -------------------------------------------------------------------------------
+
+
+@dataclass
+class Bf16RopePagedKvAppendArgs:
+    """rope/mod.rs:963-1010."""
+    query: Read
+    key: Read
+    value: Read
+    page_indptr: Read
+    page_indices: Read
+    last_page_len: Read
+    query_output: Write
+    key_pages: Write
+    value_pages: Write
+
+
+@dataclass
+class Bf16RopePagedKvAppendTokensArgs:
+    """rope/mod.rs:1012-1077."""
+    query: Read
+    key: Read
+    value: Read
+    batch_indices: Read
+    positions: Read
+    page_indptr: Read
+    page_indices: Read
+    last_page_len: Read
+    query_output: Write
+    key_pages: Write
+    value_pages: Write
+
+
+class RopeProvider:
+    """rope/mod.rs:579-683."""
+
+    def __init__(self, ptr):
+        self._ptr = ptr
+
+    @classmethod
+    def load(cls, device: int = 0) -> "RopeProvider":
+        out = c_void_p()
+        _check(_abi.load().lb_rope_provider_load(device, byref(out)))
+        return cls(out.value)
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_rope_provider_destroy(self._ptr)
+            self._ptr = None
+
+    def plan_bf16_paged_append(self, spec: Bf16RopePagedKvAppendSpec):
+        out = c_void_p()
+        _check(_abi.load().lb_rope_append_plan_create(self._ptr, byref(spec.paged()._raw),
+                                                      byref(out)))
+        return Bf16RopePagedKvAppendPlan(out.value, spec)
+
+    def plan_bf16_paged_append_tokens(self, spec: Bf16RopePagedKvAppendTokensSpec):
+        out = c_void_p()
+        _check(_abi.load().lb_rope_append_tokens_plan_create(self._ptr, byref(spec._raw),
+                                                             byref(out)))
+        return Bf16RopePagedKvAppendTokensPlan(out.value, spec)
+
+
+class _AppendPlan:
+    def __init__(self, ptr, spec):
+        self._ptr, self._spec = ptr, spec
+        self._info = _abi.AppendPlanInfo()
+        _check(_abi.load().lb_rope_append_plan_info_get(ptr, byref(self._info)))
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_rope_append_plan_destroy(self._ptr)
+            self._ptr = None
+
+    def spec(self): return self._spec
+    def info(self): return self._info
+
+
+class Bf16RopePagedKvAppendPlan(_AppendPlan):
+    """rope/mod.rs:745-831."""
+
+    def enqueue_into(self, scope: CommandScope, args: Bf16RopePagedKvAppendArgs):
+        raw = _abi.AppendArgs(
+            query=args.query._raw, key=args.key._raw, value=args.value._raw,
+            batch_indices=_null_handle(), positions=_null_handle(),
+            page_indptr=args.page_indptr._raw, page_indices=args.page_indices._raw,
+            last_page_len=args.last_page_len._raw, query_output=args.query_output._raw,
+            key_pages=args.key_pages._raw, value_pages=args.value_pages._raw)
+        _check(_abi.load().lb_rope_append_enqueue(self._ptr, scope._ptr, byref(raw)))
+
+
+class Bf16RopePagedKvAppendTokensPlan(_AppendPlan):
+    """rope/mod.rs:833-934."""
+
+    def enqueue_into(self, scope: CommandScope, args: Bf16RopePagedKvAppendTokensArgs):
+        raw = _abi.AppendArgs(
+            query=args.query._raw, key=args.key._raw, value=args.value._raw,
+            batch_indices=args.batch_indices._raw, positions=args.positions._raw,
+            page_indptr=args.page_indptr._raw, page_indices=args.page_indices._raw,
+            last_page_len=args.last_page_len._raw, query_output=args.query_output._raw,
+            key_pages=args.key_pages._raw, value_pages=args.value_pages._raw)
+        _check(_abi.load().lb_rope_append_enqueue(self._ptr, scope._ptr, byref(raw)))
+
+
+# ---- fixed-address CUDA Graph -------------------------------------------------------------------------------
+
+
+class GraphQueue:
+    """graph/mod.rs:27-71: capture-only queue with a private stream."""
+
+    def __init__(self, device: int, max_commands: int):
+        out = c_void_p()
+        _check(_abi.load().lb_graph_queue_create(device, max_commands, byref(out)))
+        self._ptr = out.value
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_graph_queue_destroy(self._ptr)
+            self._ptr = None
+
+    def bindings(self, capacity: int) -> CheckedBindings:
+        out = c_void_p()
+        _check(_abi.load().lb_graph_queue_bindings(self._ptr, capacity, byref(out)))
+        return CheckedBindings(out.value)
+
+    def capture(self, bindings: CheckedBindings,
+                record: Callable[[CommandScope], None]) -> "CapturedGraph":
+        """Consumes the queue and the bindings.  `record` enqueues plans into the scope; an
+        exception it raises aborts the capture and is re-raised."""
+        buffers = bindings._buffers
+        raised = []
+
+        def trampoline(scope_ptr, _user):
+            scope = CommandScope(None, scope_ptr, buffers)
+            try:
+                record(scope)
+                return 0
+            except LoomError as error:
+                raised.append(error)
+                return error.status
+            except Exception as error:  # noqa: BLE001 - reported to the caller below
+                raised.append(error)
+                return 500
+            finally:
+                scope._ptr = None  # the library owns the scope during capture
+
+        callback = _abi.RECORD_FN(trampoline)
+        out = c_void_p()
+        queue_ptr, self._ptr = self._ptr, None
+        status = _abi.load().lb_graph_capture(queue_ptr, bindings._release(), callback, None,
+                                              byref(out))
+        if raised:
+            raise raised[0]
+        _check(status)
+        return CapturedGraph(out.value, buffers)
+
+
+class CapturedGraph:
+    """graph/mod.rs:165-215."""
+
+    def __init__(self, ptr, buffers):
+        self._ptr, self._buffers = ptr, buffers
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_captured_graph_destroy(self._ptr)
+            self._ptr = None
+
+    def commands(self): return _abi.load().lb_captured_graph_commands(self._ptr)
+
+    def instantiate(self) -> "GraphExec":
+        out = c_void_p()
+        ptr, self._ptr = self._ptr, None
+        _check(_abi.load().lb_captured_graph_instantiate(ptr, byref(out)))
+        return GraphExec(out.value, self._buffers)
+
+
+class GraphExec:
+    """graph/mod.rs:217-382."""
+
+    def __init__(self, ptr, buffers):
+        self._ptr, self._buffers = ptr, buffers
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_graph_exec_destroy(self._ptr)
+            self._ptr = None
+
+    def commands(self): return _abi.load().lb_graph_exec_commands(self._ptr)
+    def launches(self): return _abi.load().lb_graph_exec_launches(self._ptr)
+
+    def launch(self) -> "GraphLaunchCompletion":
+        out = c_void_p()
+        _check(_abi.load().lb_graph_exec_launch(self._ptr, byref(out)))
+        return GraphLaunchCompletion(out.value, self)
+
+    def measure_launch_ms(self) -> float:
+        ms = c_float()
+        _check(_abi.load().lb_graph_exec_measure_launch_ms(self._ptr, byref(ms)))
+        return ms.value
+
+    def into_bindings(self) -> CheckedBindings:
+        out = c_void_p()
+        ptr, self._ptr = self._ptr, None
+        _check(_abi.load().lb_graph_exec_into_bindings(ptr, byref(out)))
+        bindings = CheckedBindings(out.value)
+        bindings._buffers = self._buffers
+        return bindings
+
+
+class GraphLaunchCompletion:
+    """graph/mod.rs:384-463."""
+
+    def __init__(self, ptr, exec_):
+        self._ptr, self._exec = ptr, exec_
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            _abi.load().lb_graph_completion_abandon(self._ptr)
+            self._ptr = None
+
+    def launch_index(self): return _abi.load().lb_graph_completion_launch_index(self._ptr)
+
+    def is_complete(self) -> bool:
+        done = c_int()
+        _check(_abi.load().lb_graph_completion_is_complete(self._ptr, byref(done)))
+        return bool(done.value)
+
+    def wait(self):
+        ptr, self._ptr = self._ptr, None
+        _check(_abi.load().lb_graph_completion_wait(ptr))

@@ -1,0 +1,63 @@
+"""Builds libloom_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU)."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libloom_b200.so")
+SOURCES = ["errors.cpp", "contract.cpp", "driver.cpp", "command.cpp", "graph.cpp",
+           "providers.cpp", "decode_kernels.cu", "append_kernels.cu", "static_scratch.cu"]
+HEADERS = ["runtime.hpp", "kernels.hpp", os.path.join(ROOT, "include", "loom_b200.h")]
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+         "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-x", "cu",
+         "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+
+
+def sources():
+    return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    built = os.path.getmtime(LIB)
+    deps = [os.path.join(CSRC, s) for s in sources()] + [
+        h if os.path.isabs(h) else os.path.join(CSRC, h) for h in HEADERS]
+    return any(os.path.getmtime(d) > built for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not is_stale():
+        return LIB
+    obj_dir = os.path.join(HERE, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    objects = []
+    procs = []
+    for source in sources():
+        obj = os.path.join(obj_dir, os.path.splitext(source)[0] + ".o")
+        objects.append(obj)
+        cmd = [NVCC, *FLAGS, "-c", os.path.join(CSRC, source), "-o", obj]
+        if verbose and source.endswith(".cu"):
+            cmd.insert(1, "-Xptxas=-v")
+        procs.append((source, subprocess.Popen(cmd, stdout=subprocess.PIPE,
+                                               stderr=subprocess.STDOUT, text=True)))
+    failed = False
+    for source, proc in procs:
+        output, _ = proc.communicate()
+        if proc.returncode != 0 or verbose:
+            sys.stderr.write(f"--- {source}\n{output}\n")
+        failed |= proc.returncode != 0
+    if failed:
+        raise RuntimeError("nvcc failed")
+    subprocess.run([NVCC, "-shared", "-o", LIB, *objects, "-gencode",
+                    "arch=compute_100a,code=sm_100a"], check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,392 @@
+// Host-side contract: validated specs, page-table and append metadata validation, split-K
+// partition rule, and the plan-time launch heuristic.  Pure functions; no CUDA.
+//
+// Follows crates/loom-infer/src/attention/paged_decode/mod.rs:26-279,
+// crates/loom-infer/src/attention/paged_append/mod.rs:95-131,144-177,244-317 and
+// crates/loom-infer/src/attention/single_decode/mod.rs:131-194 of the reference.
+#include <cmath>
+#include <vector>
+
+#include "runtime.hpp"
+
+namespace lb {
+namespace {
+
+bool mul_overflow(size_t a, size_t b, size_t *out) { return __builtin_mul_overflow(a, b, out); }
+
+lb_status require_len(const char *buffer, size_t actual, size_t expected) {
+    if (actual == expected) return LB_OK;
+    return fail(LB_LENGTH_MISMATCH, buffer, (int64_t)expected, (int64_t)actual);
+}
+
+size_t kv_len_of(const int32_t *indptr, const int32_t *last, size_t request) {
+    const size_t pages = (size_t)(indptr[request + 1] - indptr[request]);
+    return (pages - 1) * LB_PAGE_SIZE + (size_t)last[request];
+}
+
+uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+} // namespace
+
+// Plan-time choice of the decode launch shape.  Inputs are the spec and the device only; the
+// page table is not known when a plan is made.
+//
+//   q_tiles (MT)      16-row MMA tiles that cover the GQA group, a power of two <= warps
+//   q_blocks          CTAs per KV head when the group exceeds 16*MT rows
+//   units             warps / MT (page, KV head) tiles one pipeline stage holds
+//   heads_per_cta     KV heads one CTA streams (divides kv_heads and units)
+//   pages_per_stage   units / heads_per_cta
+//   partitions        1 = direct; otherwise page-balanced chunks merged by LSE
+lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t smem_optin,
+                        const lb_paged_decode_options *options, DecodeChoice *out) {
+    const uint32_t warps = 8;
+    const size_t group = spec.num_query_heads / spec.num_kv_heads;
+    size_t states;
+    if (mul_overflow(spec.batch_size, spec.num_query_heads, &states))
+        return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, INT64_MAX);
+    if (states > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)states);
+
+    uint32_t q_tiles = 1;
+    while (q_tiles < warps && (size_t)q_tiles * 16 < group) q_tiles *= 2;
+    const uint32_t q_blocks = (uint32_t)((group + (size_t)q_tiles * 16 - 1) / ((size_t)q_tiles * 16));
+    const uint32_t units = warps / q_tiles;
+
+    // candidate heads per CTA: powers of two dividing both kv_heads and units
+    auto valid_hc = [&](uint32_t hc) {
+        return hc >= 1 && hc <= units && units % hc == 0 && spec.num_kv_heads % hc == 0;
+    };
+    const uint32_t target_ctas = 2 * (sm_count ? sm_count : 148);
+
+    uint32_t partitions = options ? options->partitions : 0;
+    uint32_t hc = options ? options->heads_per_cta : 0;
+    if (hc != 0 && !valid_hc(hc)) return fail(LB_LAUNCH_CONTRACT, "heads_per_cta", hc);
+
+    auto items_for = [&](uint32_t h, uint32_t p) -> size_t {
+        return spec.batch_size * (spec.num_kv_heads / h) * q_blocks * (size_t)p;
+    };
+
+    if (hc == 0) {
+        // the widest CTA that still yields enough CTAs to fill the device twice
+        const uint32_t p = partitions ? partitions : 1;
+        hc = 1;
+        for (uint32_t candidate = units; candidate >= 1; candidate /= 2) {
+            if (!valid_hc(candidate)) continue;
+            if (items_for(candidate, p) >= target_ctas) {
+                hc = candidate;
+                break;
+            }
+        }
+    }
+    if (partitions == 0) {
+        // split only when one-CTA-per-(request, head block) cannot fill the device; keep
+        // every chunk at >= 8 pages of the per-request page capacity
+        const size_t items = items_for(hc, 1);
+        partitions = 1;
+        if (items < (sm_count ? sm_count : 148)) {
+            const size_t want = (target_ctas + items - 1) / items;
+            const size_t pages_per_request = spec.max_num_pages / spec.batch_size;
+            size_t cap = pages_per_request / 8;
+            if (cap < 1) cap = 1;
+            if (cap > 64) cap = 64;
+            partitions = (uint32_t)(want < cap ? want : cap);
+            if (partitions < 1) partitions = 1;
+        }
+    }
+    if (partitions > spec.max_num_pages)
+        return fail(LB_INVALID_PARTITION_COUNT, nullptr, partitions, (int64_t)spec.max_num_pages);
+
+    const size_t items = items_for(hc, partitions);
+    if (items > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)items);
+    size_t workspace = 0;
+    if (partitions > 1) {
+        if (mul_overflow(states, partitions, &workspace) ||
+            mul_overflow(workspace, LB_PARTIAL_STATE_WIDTH, &workspace) ||
+            workspace > SIZE_MAX / sizeof(float))
+            return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    }
+
+    const uint32_t stage_bytes = units * 8192u;
+    const size_t budget = (smem_optin ? smem_optin : 232448) - 2048; // barriers, flags
+    uint32_t stages = (uint32_t)(budget / stage_bytes);
+    if (stages > 6) stages = 6;
+    // the cross-warp state merge at the end of a CTA reuses the ring: 8 warps x 68 x 32 floats
+    if (stages < 2 || (units / hc > 1 && (size_t)stages * stage_bytes < 8u * 68u * 32u * 4u))
+        return fail(LB_LAUNCH_CONTRACT, "shared_memory", (int64_t)smem_optin);
+
+    out->partitions = partitions;
+    out->heads_per_cta = hc;
+    out->q_tiles = q_tiles;
+    out->q_blocks = q_blocks;
+    out->pages_per_stage = units / hc;
+    out->stages = stages;
+    out->warps = warps;
+    out->grid = (uint32_t)items;
+    out->block = (warps + 1) * 32;
+    out->shared_bytes = stages * stage_bytes + 1024 /* alignment slack */ + 1024 /* barriers */;
+    out->merge_block = 128;
+    out->merge_grid = partitions > 1 ? ceil_div((uint32_t)states, 4) : 0;
+    out->workspace_numel = workspace;
+    return LB_OK;
+}
+
+} // namespace lb
+
+using namespace lb;
+
+extern "C" {
+
+lb_status lb_paged_spec_new(size_t batch, size_t max_pages, size_t qh, size_t kvh, size_t head_dim,
+                            size_t page_size, lb_paged_spec *out) {
+    if (!out) return fail(LB_INVALID_ARGUMENT, "out");
+    if (batch == 0 || max_pages == 0 || qh == 0 || kvh == 0 || head_dim == 0 || page_size == 0)
+        return fail(LB_ZERO_DIMENSION);
+    if (head_dim != LB_HEAD_DIM)
+        return fail(LB_UNSUPPORTED_HEAD_DIMENSION, nullptr, LB_HEAD_DIM, (int64_t)head_dim);
+    if (page_size != LB_PAGE_SIZE)
+        return fail(LB_UNSUPPORTED_PAGE_SIZE, nullptr, LB_PAGE_SIZE, (int64_t)page_size);
+    if (qh % kvh != 0) return fail(LB_INVALID_HEAD_MAPPING, nullptr, (int64_t)qh, (int64_t)kvh);
+    size_t t;
+    if (batch + 1 < batch || mul_overflow(batch, qh, &t) || mul_overflow(t, head_dim, &t))
+        return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    if (mul_overflow(max_pages, page_size, &t) || mul_overflow(t, kvh, &t) ||
+        mul_overflow(t, head_dim, &t))
+        return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    out->batch_size = batch;
+    out->max_num_pages = max_pages;
+    out->num_query_heads = qh;
+    out->num_kv_heads = kvh;
+    out->softmax_scale = 1.0f / std::sqrt((float)head_dim);
+    return LB_OK;
+}
+
+size_t lb_paged_spec_query_numel(const lb_paged_spec *s) {
+    return s->batch_size * s->num_query_heads * LB_HEAD_DIM;
+}
+size_t lb_paged_spec_kv_pages_numel(const lb_paged_spec *s) {
+    return s->max_num_pages * LB_PAGE_SIZE * s->num_kv_heads * LB_HEAD_DIM;
+}
+size_t lb_paged_spec_lse_numel(const lb_paged_spec *s) {
+    return s->batch_size * s->num_query_heads;
+}
+size_t lb_paged_spec_gqa_group_size(const lb_paged_spec *s) {
+    return s->num_query_heads / s->num_kv_heads;
+}
+int64_t lb_paged_spec_kv_head_for_query_head(const lb_paged_spec *s, size_t query_head) {
+    if (query_head >= s->num_query_heads) return -1;
+    return (int64_t)(query_head / lb_paged_spec_gqa_group_size(s));
+}
+
+lb_status lb_paged_spec_validate_page_table(const lb_paged_spec *spec, const int32_t *indptr,
+                                            size_t indptr_len, const int32_t *indices,
+                                            size_t indices_len, const int32_t *last,
+                                            size_t last_len) {
+    if (!spec) return fail(LB_INVALID_ARGUMENT, "spec");
+    lb_status rc;
+    if ((rc = require_len("page_indptr", indptr_len, spec->batch_size + 1))) return rc;
+    if ((rc = require_len("last_page_len", last_len, spec->batch_size))) return rc;
+    if (!indptr || !last) return fail(LB_INVALID_ARGUMENT, "page table");
+    if (indptr[0] != 0) return fail(LB_INVALID_PAGE_INDPTR_START, nullptr, indptr[0]);
+    for (size_t request = 0; request < spec->batch_size; ++request) {
+        const int32_t start = indptr[request], end = indptr[request + 1];
+        if (end < start)
+            return fail(LB_NON_MONOTONIC_PAGE_INDPTR, nullptr, (int64_t)request, start, end);
+        if (end == start) return fail(LB_EMPTY_PAGED_REQUEST, nullptr, (int64_t)request);
+        const int32_t length = last[request];
+        if (length < 1 || length > (int32_t)LB_PAGE_SIZE)
+            return fail(LB_INVALID_LAST_PAGE_LENGTH, nullptr, (int64_t)request, length,
+                        LB_PAGE_SIZE);
+    }
+    if (indptr[spec->batch_size] < 0) return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    if ((rc = require_len("page_indices", indices_len, (size_t)indptr[spec->batch_size])))
+        return rc;
+    for (size_t position = 0; position < indices_len; ++position) {
+        const int32_t index = indices[position];
+        if (index < 0 || (size_t)index >= spec->max_num_pages)
+            return fail(LB_PAGE_INDEX_OUT_OF_RANGE, nullptr, (int64_t)position, index,
+                        (int64_t)spec->max_num_pages);
+    }
+    return LB_OK;
+}
+
+int lb_page_table_request_kv_len(const lb_paged_spec *spec, const int32_t *indptr,
+                                 const int32_t *last, size_t request, size_t *kv_len) {
+    if (request >= spec->batch_size) return 0;
+    *kv_len = kv_len_of(indptr, last, request);
+    return 1;
+}
+
+int lb_page_table_physical_page_for_token(const lb_paged_spec *spec, const int32_t *indptr,
+                                          const int32_t *indices, const int32_t *last,
+                                          size_t request, size_t token, size_t *page,
+                                          size_t *offset) {
+    if (request >= spec->batch_size) return 0;
+    if (token >= kv_len_of(indptr, last, request)) return 0;
+    *page = (size_t)indices[(size_t)indptr[request] + token / LB_PAGE_SIZE];
+    *offset = token % LB_PAGE_SIZE;
+    return 1;
+}
+
+lb_status lb_append_spec_validate_page_table(const lb_paged_spec *spec, const int32_t *indptr,
+                                             size_t indptr_len, const int32_t *indices,
+                                             size_t indices_len, const int32_t *last,
+                                             size_t last_len) {
+    lb_status rc = lb_paged_spec_validate_page_table(spec, indptr, indptr_len, indices,
+                                                     indices_len, last, last_len);
+    if (rc) return rc;
+    std::vector<int64_t> slots(spec->batch_size);
+    for (size_t request = 0; request < spec->batch_size; ++request) {
+        size_t page, offset;
+        lb_page_table_physical_page_for_token(spec, indptr, indices, last, request,
+                                              kv_len_of(indptr, last, request) - 1, &page,
+                                              &offset);
+        slots[request] = (int64_t)(page * LB_PAGE_SIZE + offset);
+    }
+    // report the lexicographically first (first_request, second_request) pair, as the
+    // reference's nested loops do
+    for (size_t first = 0; first < spec->batch_size; ++first)
+        for (size_t second = first + 1; second < spec->batch_size; ++second)
+            if (slots[first] == slots[second])
+                return fail(LB_DUPLICATE_PAGE_APPEND_SLOT, nullptr, (int64_t)first,
+                            (int64_t)second, slots[first] / LB_PAGE_SIZE,
+                            slots[first] % LB_PAGE_SIZE);
+    return LB_OK;
+}
+
+size_t lb_append_extended_max_tokens(void) { return 16384; }
+
+static lb_status tokens_spec(size_t tokens, size_t max_tokens, size_t batch, size_t max_pages,
+                             size_t qh, size_t kvh, size_t head_dim, size_t page_size,
+                             lb_append_tokens_spec *out) {
+    if (!out) return fail(LB_INVALID_ARGUMENT, "out");
+    if (tokens == 0) return fail(LB_ZERO_DIMENSION);
+    if (tokens > max_tokens)
+        return fail(LB_UNSUPPORTED_APPEND_TOKEN_COUNT, nullptr, (int64_t)max_tokens,
+                    (int64_t)tokens);
+    lb_status rc = lb_paged_spec_new(batch, max_pages, qh, kvh, head_dim, page_size, &out->paged);
+    if (rc) return rc;
+    size_t t;
+    if (mul_overflow(tokens, qh, &t) || mul_overflow(t, head_dim, &t) ||
+        mul_overflow(tokens, kvh, &t) || mul_overflow(t, head_dim, &t))
+        return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    out->tokens = tokens;
+    return LB_OK;
+}
+
+lb_status lb_append_tokens_spec_new(size_t tokens, size_t batch, size_t max_pages, size_t qh,
+                                    size_t kvh, size_t head_dim, size_t page_size,
+                                    lb_append_tokens_spec *out) {
+    lb_status rc = tokens_spec(tokens, LB_APPEND_MAX_TOKENS, batch, max_pages, qh, kvh, head_dim,
+                               page_size, out);
+    if (rc == LB_OK) out->max_tokens = LB_APPEND_MAX_TOKENS;
+    return rc;
+}
+
+lb_status lb_append_tokens_spec_new_extended(size_t tokens, size_t batch, size_t max_pages,
+                                             size_t qh, size_t kvh, size_t head_dim,
+                                             size_t page_size, lb_append_tokens_spec *out) {
+    lb_status rc = tokens_spec(tokens, lb_append_extended_max_tokens(), batch, max_pages, qh, kvh,
+                               head_dim, page_size, out);
+    if (rc == LB_OK) out->max_tokens = 0;
+    return rc;
+}
+
+lb_status lb_append_tokens_spec_validate_metadata(
+    const lb_append_tokens_spec *spec, const int32_t *batch_indices, size_t batch_indices_len,
+    const int32_t *positions, size_t positions_len, const int32_t *indptr, size_t indptr_len,
+    const int32_t *indices, size_t indices_len, const int32_t *last, size_t last_len,
+    int64_t *slots_out) {
+    if (!spec) return fail(LB_INVALID_ARGUMENT, "spec");
+    lb_status rc;
+    if ((rc = require_len("batch_indices", batch_indices_len, spec->tokens))) return rc;
+    if ((rc = require_len("positions", positions_len, spec->tokens))) return rc;
+    if ((rc = lb_paged_spec_validate_page_table(&spec->paged, indptr, indptr_len, indices,
+                                                indices_len, last, last_len)))
+        return rc;
+    std::vector<int64_t> slots(spec->tokens);
+    for (size_t token = 0; token < spec->tokens; ++token) {
+        const int32_t index = batch_indices[token];
+        if (index < 0 || (size_t)index >= spec->paged.batch_size)
+            return fail(LB_APPEND_BATCH_INDEX_OUT_OF_RANGE, nullptr, (int64_t)token, index,
+                        (int64_t)spec->paged.batch_size);
+        const size_t request = (size_t)index;
+        const size_t kv_len = kv_len_of(indptr, last, request);
+        const int32_t position = positions[token];
+        if (position < 0 || (size_t)position >= kv_len)
+            return fail(LB_APPEND_POSITION_OUT_OF_RANGE, nullptr, (int64_t)token, (int64_t)request,
+                        position, (int64_t)kv_len);
+        const size_t page = (size_t)indices[(size_t)indptr[request] + (size_t)position / LB_PAGE_SIZE];
+        const int64_t slot = (int64_t)(page * LB_PAGE_SIZE + (size_t)position % LB_PAGE_SIZE);
+        for (size_t first = 0; first < token; ++first)
+            if (slots[first] == slot)
+                return fail(LB_DUPLICATE_PAGE_APPEND_TOKEN_SLOT, nullptr, (int64_t)first,
+                            (int64_t)token, slot / LB_PAGE_SIZE, slot % LB_PAGE_SIZE);
+        slots[token] = slot;
+    }
+    if (slots_out)
+        for (size_t token = 0; token < spec->tokens; ++token) {
+            slots_out[token * 2] = slots[token] / LB_PAGE_SIZE;
+            slots_out[token * 2 + 1] = slots[token] % LB_PAGE_SIZE;
+        }
+    return LB_OK;
+}
+
+int lb_split_partition_range(size_t length, size_t partitions, size_t partition, size_t *start,
+                             size_t *end) {
+    if (partitions == 0 || partition >= partitions) return 0;
+    const size_t base = length / partitions, remainder = length % partitions;
+    const size_t extra_before = partition < remainder ? partition : remainder;
+    *start = partition * base + extra_before;
+    *end = *start + base + (partition < remainder ? 1 : 0);
+    return 1;
+}
+
+lb_status lb_paged_split_workspace_numel(const lb_paged_spec *spec, size_t partitions,
+                                         size_t *numel) {
+    if (!spec || !numel) return fail(LB_INVALID_ARGUMENT, "spec");
+    if (partitions == 0 || partitions > spec->max_num_pages)
+        return fail(LB_INVALID_PARTITION_COUNT, nullptr, (int64_t)partitions,
+                    (int64_t)spec->max_num_pages);
+    size_t t;
+    if (mul_overflow(spec->batch_size, spec->num_query_heads, &t) ||
+        mul_overflow(t, partitions, &t) || mul_overflow(t, LB_PARTIAL_STATE_WIDTH, &t) ||
+        t > SIZE_MAX / sizeof(float))
+        return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    *numel = t;
+    return LB_OK;
+}
+
+int64_t lb_paged_split_state_offset(const lb_paged_spec *spec, size_t partitions, size_t request,
+                                    size_t query_head, size_t partition) {
+    if (request >= spec->batch_size || query_head >= spec->num_query_heads ||
+        partition >= partitions)
+        return -1;
+    return (int64_t)(((request * spec->num_query_heads + query_head) * partitions + partition) *
+                     LB_PARTIAL_STATE_WIDTH);
+}
+
+lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
+                                 const lb_paged_decode_options *options,
+                                 lb_paged_decode_plan_info *info) {
+    if (!spec || !info) return fail(LB_INVALID_ARGUMENT, "spec");
+    DecodeChoice choice;
+    lb_status rc = choose_decode(*spec, sm_count, 0, options, &choice);
+    if (rc) return rc;
+    info->algorithm = choice.partitions > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+    info->partitions = choice.partitions;
+    info->heads_per_cta = choice.heads_per_cta;
+    info->q_tiles = choice.q_tiles;
+    info->q_blocks = choice.q_blocks;
+    info->pages_per_stage = choice.pages_per_stage;
+    info->stages = choice.stages;
+    info->grid = choice.grid;
+    info->block = choice.block;
+    info->shared_bytes = choice.shared_bytes;
+    info->merge_grid = choice.merge_grid;
+    info->merge_block = choice.merge_block;
+    info->commands = choice.partitions > 1 ? 2 : 1;
+    info->workspace_numel = choice.workspace_numel;
+    info->workspace_bytes = choice.workspace_numel * sizeof(float);
+    return LB_OK;
+}
+
+}

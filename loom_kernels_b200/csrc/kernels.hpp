@@ -1,0 +1,55 @@
+// Launch descriptors shared between the providers (host) and the kernel translation units.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+namespace lb {
+
+// One paged-decode launch.  Every pointer is a device pointer of the queue's device.
+struct DecodeLaunch {
+    alignas(64) unsigned char k_map[128]; // CUtensorMap over K pages, see decode_kernels.cu
+    alignas(64) unsigned char v_map[128]; // CUtensorMap over V pages
+    const void *query;       // bf16 [batch, qh, 128]
+    const int32_t *indptr;   // [batch + 1]
+    const int32_t *indices;  // [indices_len]
+    const int32_t *last;     // [batch]
+    void *output;            // bf16 [batch, qh, 128]
+    float *lse;              // [batch, qh]
+    float *workspace;        // [batch, qh, partitions, 130] when partitions > 1
+    int32_t *status;         // optional device status word (0 = ok)
+    int32_t batch, max_pages, qh, kvh, indices_len;
+    int32_t heads_per_cta, pages_per_stage, q_tiles, q_blocks, partitions, stages;
+    float scale_log2;
+    uint32_t grid, block, shared_bytes;
+};
+
+struct MergeLaunch {
+    const float *workspace;
+    void *output;
+    float *lse;
+    const int32_t *indptr;
+    const int32_t *last;
+    int32_t batch, qh, partitions, indices_len;
+    uint32_t grid, block;
+};
+
+// One fused RoPE + paged append launch.
+struct AppendLaunch {
+    const void *query, *key, *value;          // bf16 [tokens, qh|kvh, 128]
+    const int32_t *batch_indices, *positions; // [tokens]; null for one-token-per-request
+    const int32_t *indptr, *indices, *last;
+    void *query_output, *key_pages, *value_pages;
+    int32_t tokens, batch, max_pages, qh, kvh, indices_len;
+    int32_t hash_slots; // power of two >= 2 * tokens
+    uint32_t grid, block, shared_bytes;
+};
+
+// Each returns a CUDA error code (0 = success).
+int configure_decode_kernels(size_t max_dynamic_shared);
+int launch_paged_decode(const DecodeLaunch &launch, void *stream);
+int launch_split_merge(const MergeLaunch &launch, void *stream);
+int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency);
+int launch_rope_append(const AppendLaunch &launch, void *stream);
+
+} // namespace lb

@@ -1,0 +1,481 @@
+// Decode and RoPE-append providers: immutable plans and checked enqueue.
+//
+// Mirrors DecodeProvider / Bf16PagedBatchDecodePlan
+// (crates/loom-infer-cuda/src/attention/decode.rs:1001-1104,1181-1297), the two-command
+// split-K enqueue shape (:1322-1389) and RopeProvider / Bf16RopePagedKvAppend{,Tokens}Plan
+// (crates/loom-infer-cuda/src/rope/mod.rs:579-683,745-934) of the reference.  A plan fixes the
+// algorithm, split count, launch shape and workspace size before any enqueue; enqueue performs
+// no re-dispatch and has no fallback.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+
+#include "kernels.hpp"
+#include "runtime.hpp"
+
+using namespace lb;
+
+struct lb_decode_provider {
+    int device = 0, sm_count = 0;
+    size_t smem_optin = 0;
+    int32_t *status = nullptr; // device word written by a kernel that gave up on a wait
+};
+
+struct lb_paged_decode_plan {
+    lb_paged_spec spec;
+    DecodeChoice choice;
+    int device = 0;
+    int32_t *status = nullptr;
+};
+
+struct lb_rope_provider {
+    int device = 0, sm_count = 0;
+    size_t smem_optin = 0;
+};
+
+struct lb_rope_append_plan {
+    lb_paged_spec spec;
+    bool explicit_tokens = false;
+    size_t tokens = 0;
+    int device = 0;
+    uint32_t grid = 0, block = 256, shared_bytes = 0, hash_slots = 0;
+};
+
+namespace {
+
+const float kLog2E = 1.44269504088896340736f;
+
+lb_status require_exact_len(const char *operand, size_t actual, size_t expected) {
+    if (actual == expected) return LB_OK;
+    return fail(LB_ENQUEUE_LENGTH_MISMATCH, operand, (int64_t)expected, (int64_t)actual);
+}
+
+// The reference requires 4-byte bases (decode.rs:1585-1599); the 16-byte vector and TMA
+// accesses of these kernels need 16.
+lb_status require_alignment(const char *operand, const void *ptr, uint64_t alignment) {
+    const uint64_t address = (uint64_t)(uintptr_t)ptr;
+    if (address % alignment == 0) return LB_OK;
+    return fail(LB_MISALIGNED_BUFFER, operand, (int64_t)address, (int64_t)alignment);
+}
+
+lb_status load_device(int device, int *sm_count, size_t *smem_optin) {
+    int count = 0;
+    int rc = driver().device_count(&count);
+    if (rc) return fail(LB_DRIVER, "device_count", rc);
+    if (device < 0 || device >= count) return fail(LB_INVALID_ARGUMENT, "device", device);
+    int major = 0, minor = 0;
+    size_t l2 = 0;
+    if ((rc = driver().device_props(device, sm_count, &major, &minor, smem_optin, &l2)))
+        return fail(LB_DRIVER, "device_props", rc);
+    if (major != 10) return fail(LB_UNSUPPORTED_DEVICE, nullptr, major * 10 + minor);
+    return LB_OK;
+}
+
+void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
+    info->algorithm = c.partitions > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+    info->partitions = c.partitions;
+    info->heads_per_cta = c.heads_per_cta;
+    info->q_tiles = c.q_tiles;
+    info->q_blocks = c.q_blocks;
+    info->pages_per_stage = c.pages_per_stage;
+    info->stages = c.stages;
+    info->grid = c.grid;
+    info->block = c.block;
+    info->shared_bytes = c.shared_bytes;
+    info->merge_grid = c.merge_grid;
+    info->merge_block = c.merge_block;
+    info->commands = c.partitions > 1 ? 2 : 1;
+    info->workspace_numel = c.workspace_numel;
+    info->workspace_bytes = c.workspace_numel * sizeof(float);
+}
+
+} // namespace
+
+extern "C" {
+
+// ---- decode ----------------------------------------------------------------------------------
+
+lb_status lb_decode_provider_load(int device, lb_decode_provider **out) {
+    if (!out) return fail(LB_INVALID_ARGUMENT, "out");
+    *out = nullptr;
+    int sm_count = 0;
+    size_t smem = 0;
+    lb_status rc = load_device(device, &sm_count, &smem);
+    if (rc) return rc;
+    int32_t *status = nullptr;
+    const int error = driver().configure(device, [&]() -> int {
+        int e = configure_decode_kernels(smem);
+        if (e) return e;
+        if ((e = cudaMalloc((void **)&status, 64))) return e;
+        return cudaMemset(status, 0, 64);
+    });
+    if (error) return fail(LB_DRIVER, "provider_load", error);
+    lb_decode_provider *provider = new lb_decode_provider();
+    provider->device = device;
+    provider->sm_count = sm_count;
+    provider->smem_optin = smem;
+    provider->status = status;
+    *out = provider;
+    return LB_OK;
+}
+
+void lb_decode_provider_destroy(lb_decode_provider *provider) {
+    if (!provider) return;
+    if (provider->status) {
+        int32_t *status = provider->status;
+        driver().configure(provider->device, [&]() -> int { return cudaFree(status); });
+    }
+    delete provider;
+}
+
+lb_status lb_decode_provider_device_status(const lb_decode_provider *provider, int32_t *status) {
+    if (!provider || !status) return fail(LB_INVALID_ARGUMENT, "provider");
+    *status = 0;
+    if (!provider->status) return LB_OK;
+    const int error = driver().configure(provider->device, [&]() -> int {
+        int e = cudaMemcpy(status, provider->status, sizeof(int32_t), cudaMemcpyDeviceToHost);
+        if (e) return e;
+        return cudaMemset(provider->status, 0, sizeof(int32_t));
+    });
+    if (error) return fail(LB_DRIVER, "device_status", error);
+    return LB_OK;
+}
+
+lb_status lb_paged_decode_plan_create(const lb_decode_provider *provider, const lb_paged_spec *spec,
+                                      const lb_paged_decode_options *options,
+                                      lb_paged_decode_plan **out) {
+    if (!provider || !spec || !out) return fail(LB_INVALID_ARGUMENT, "provider");
+    *out = nullptr;
+    // a spec not made by lb_paged_spec_new is re-validated
+    lb_paged_spec checked;
+    lb_status rc = lb_paged_spec_new(spec->batch_size, spec->max_num_pages, spec->num_query_heads,
+                                     spec->num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE, &checked);
+    if (rc) return rc;
+    if (spec->max_num_pages > (size_t)0x7fffffff / LB_PAGE_SIZE ||
+        spec->num_kv_heads > 0x7fffffffu / LB_HEAD_DIM)
+        return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)spec->max_num_pages);
+    DecodeChoice choice;
+    if ((rc = choose_decode(checked, (uint32_t)provider->sm_count, provider->smem_optin, options,
+                            &choice)))
+        return rc;
+    lb_paged_decode_plan *plan = new lb_paged_decode_plan();
+    plan->spec = checked;
+    plan->choice = choice;
+    plan->device = provider->device;
+    plan->status = provider->status;
+    *out = plan;
+    return LB_OK;
+}
+
+void lb_paged_decode_plan_destroy(lb_paged_decode_plan *plan) { delete plan; }
+
+lb_status lb_paged_decode_plan_info_get(const lb_paged_decode_plan *plan, lb_paged_spec *spec,
+                                        lb_paged_decode_plan_info *info) {
+    if (!plan) return fail(LB_INVALID_ARGUMENT, "plan");
+    if (spec) *spec = plan->spec;
+    if (info) fill_info(plan->choice, info);
+    return LB_OK;
+}
+
+lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *scope,
+                                  const lb_paged_decode_args *args) {
+    if (!plan || !scope || !args) return fail(LB_INVALID_ARGUMENT, "plan");
+    const lb_paged_spec &spec = plan->spec;
+    const DecodeChoice &c = plan->choice;
+    const bool split = c.partitions > 1;
+    if (scope->queue->device != plan->device)
+        return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
+    // both commands of a split plan must fit before anything is launched (decode.rs:1327)
+    lb_status rc = require_command_capacity(*scope, split ? 2 : 1);
+    if (rc) return rc;
+
+    OperandRequest requests[9] = {
+        {args->query, LB_BF16, false},       {args->key_pages, LB_BF16, false},
+        {args->value_pages, LB_BF16, false}, {args->page_indptr, LB_I32, false},
+        {args->page_indices, LB_I32, false}, {args->last_page_len, LB_I32, false},
+        {args->output, LB_BF16, true},       {args->lse, LB_F32, true},
+        {args->workspace, LB_F32, true},
+    };
+    Operand op[9];
+    if ((rc = resolve(*scope, requests, split ? 9 : 8, op))) return rc;
+    const size_t pool = lb_paged_spec_kv_pages_numel(&spec);
+    if ((rc = require_exact_len("Q", op[0].numel, lb_paged_spec_query_numel(&spec)))) return rc;
+    if ((rc = require_exact_len("K_pages", op[1].numel, pool))) return rc;
+    if ((rc = require_exact_len("V_pages", op[2].numel, pool))) return rc;
+    if ((rc = require_exact_len("page_indptr", op[3].numel, spec.batch_size + 1))) return rc;
+    if (op[4].numel < spec.batch_size)
+        return fail(LB_PAGE_INDICES_TOO_SHORT, nullptr, (int64_t)spec.batch_size,
+                    (int64_t)op[4].numel);
+    if (op[4].numel > 0x7fffffffu)
+        return fail(LB_ENQUEUE_LENGTH_MISMATCH, "page_indices", 0x7fffffff, (int64_t)op[4].numel);
+    if ((rc = require_exact_len("last_page_len", op[5].numel, spec.batch_size))) return rc;
+    if (split && (rc = require_exact_len("workspace", op[8].numel, c.workspace_numel))) return rc;
+    if ((rc = require_exact_len("O", op[6].numel, lb_paged_spec_query_numel(&spec)))) return rc;
+    if ((rc = require_exact_len("LSE", op[7].numel, lb_paged_spec_lse_numel(&spec)))) return rc;
+    if ((rc = require_alignment("Q", op[0].ptr, 16))) return rc;
+    if ((rc = require_alignment("K_pages", op[1].ptr, 16))) return rc;
+    if ((rc = require_alignment("V_pages", op[2].ptr, 16))) return rc;
+    if ((rc = require_alignment("O", op[6].ptr, 16))) return rc;
+    if (split && (rc = require_alignment("workspace", op[8].ptr, 8))) return rc;
+
+    DecodeLaunch launch;
+    memset(&launch, 0, sizeof(launch));
+    // K/V pools viewed as a 2-D tensor [max_pages*16 token rows][kv_heads*128 dims]; one box is
+    // 16 token rows of one page x 64 dims of one head half
+    const uint64_t row_elems = (uint64_t)spec.num_kv_heads * LB_HEAD_DIM;
+    const uint64_t rows = (uint64_t)spec.max_num_pages * LB_PAGE_SIZE;
+    int error = driver().encode_tensor_map_2d(plan->device, launch.k_map, op[1].ptr, row_elems,
+                                              rows, row_elems * 2, 64, 16);
+    if (!error)
+        error = driver().encode_tensor_map_2d(plan->device, launch.v_map, op[2].ptr, row_elems,
+                                              rows, row_elems * 2, 64, 16);
+    if (error) return fail(LB_LAUNCH_CONTRACT, "tensor_map", error);
+    launch.query = op[0].ptr;
+    launch.indptr = (const int32_t *)op[3].ptr;
+    launch.indices = (const int32_t *)op[4].ptr;
+    launch.last = (const int32_t *)op[5].ptr;
+    launch.output = op[6].ptr;
+    launch.lse = (float *)op[7].ptr;
+    launch.workspace = split ? (float *)op[8].ptr : nullptr;
+    launch.status = plan->status;
+    launch.batch = (int32_t)spec.batch_size;
+    launch.max_pages = (int32_t)spec.max_num_pages;
+    launch.qh = (int32_t)spec.num_query_heads;
+    launch.kvh = (int32_t)spec.num_kv_heads;
+    launch.indices_len = (int32_t)op[4].numel;
+    launch.heads_per_cta = (int32_t)c.heads_per_cta;
+    launch.pages_per_stage = (int32_t)c.pages_per_stage;
+    launch.q_tiles = (int32_t)c.q_tiles;
+    launch.q_blocks = (int32_t)c.q_blocks;
+    launch.partitions = (int32_t)c.partitions;
+    launch.stages = (int32_t)c.stages;
+    launch.scale_log2 = spec.softmax_scale * kLog2E;
+    launch.grid = c.grid;
+    launch.block = c.block;
+    launch.shared_bytes = c.shared_bytes;
+    void *stream = scope->queue->stream;
+    if ((rc = submit_launch(*scope, [&]() { return launch_paged_decode(launch, stream); })))
+        return rc;
+    if (!split) return LB_OK;
+
+    // second command: workspace is now a read operand (decode.rs:1374-1388)
+    OperandRequest merge_requests[3] = {
+        {lb_handle_read(args->workspace), LB_F32, false},
+        {args->output, LB_BF16, true},
+        {args->lse, LB_F32, true},
+    };
+    Operand merge_op[3];
+    if ((rc = require_command_capacity(*scope, 1))) return rc;
+    if ((rc = resolve(*scope, merge_requests, 3, merge_op))) return rc;
+    MergeLaunch merge;
+    merge.workspace = (const float *)merge_op[0].ptr;
+    merge.output = merge_op[1].ptr;
+    merge.lse = (float *)merge_op[2].ptr;
+    merge.indptr = launch.indptr;
+    merge.last = launch.last;
+    merge.batch = launch.batch;
+    merge.qh = launch.qh;
+    merge.partitions = launch.partitions;
+    merge.indices_len = launch.indices_len;
+    merge.grid = c.merge_grid;
+    merge.block = c.merge_block;
+    return submit_launch(*scope, [&]() { return launch_split_merge(merge, stream); });
+}
+
+// ---- RoPE + append ---------------------------------------------------------------------------------
+
+lb_status lb_rope_provider_load(int device, lb_rope_provider **out) {
+    if (!out) return fail(LB_INVALID_ARGUMENT, "out");
+    *out = nullptr;
+    int sm_count = 0;
+    size_t smem = 0;
+    lb_status rc = load_device(device, &sm_count, &smem);
+    if (rc) return rc;
+    // inverse frequencies exactly as the CPU reference computes them
+    // (crates/loom-infer/src/rope/mod.rs:148-149): powf(theta, -(2*pair/rotary_dim)) / scale
+    float inverse_frequency[64];
+    for (int pair = 0; pair < 64; ++pair) {
+        const float exponent = 2.0f * (float)pair / 128.0f;
+        inverse_frequency[pair] = powf(10000.0f, -exponent) / 1.0f;
+    }
+    const size_t hash_bytes = 2 * lb_append_extended_max_tokens() * sizeof(int);
+    const int error = driver().configure(device, [&]() -> int {
+        return configure_append_kernels(hash_bytes, inverse_frequency);
+    });
+    if (error) return fail(LB_DRIVER, "provider_load", error);
+    lb_rope_provider *provider = new lb_rope_provider();
+    provider->device = device;
+    provider->sm_count = sm_count;
+    provider->smem_optin = smem;
+    *out = provider;
+    return LB_OK;
+}
+
+void lb_rope_provider_destroy(lb_rope_provider *provider) { delete provider; }
+
+static lb_status make_append_plan(const lb_rope_provider *provider, const lb_paged_spec &spec,
+                                  bool explicit_tokens, size_t tokens,
+                                  lb_rope_append_plan **out) {
+    // state count checks of plan_bf16_paged_append{,_tokens}, rope/mod.rs:628-682
+    size_t heads, states;
+    if (__builtin_add_overflow(spec.num_query_heads, spec.num_kv_heads, &heads) ||
+        __builtin_mul_overflow(tokens, heads, &states))
+        return fail(LB_STATE_COUNT_OVERFLOW);
+    if (states > 0xffffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)states);
+    if (tokens > lb_append_extended_max_tokens())
+        return fail(LB_UNSUPPORTED_APPEND_TOKEN_COUNT, nullptr,
+                    (int64_t)lb_append_extended_max_tokens(), (int64_t)tokens);
+    if (spec.max_num_pages > (size_t)0x7fffffff / LB_PAGE_SIZE)
+        return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)spec.max_num_pages);
+    lb_rope_append_plan *plan = new lb_rope_append_plan();
+    plan->spec = spec;
+    plan->explicit_tokens = explicit_tokens;
+    plan->tokens = tokens;
+    plan->device = provider->device;
+    uint32_t hash_slots = 128;
+    while (hash_slots < 2 * tokens) hash_slots *= 2;
+    plan->hash_slots = hash_slots;
+    plan->shared_bytes = hash_slots * (uint32_t)sizeof(int);
+    const uint32_t cap = 4u * (uint32_t)(provider->sm_count ? provider->sm_count : 148);
+    plan->grid = tokens < cap ? (uint32_t)tokens : cap;
+    *out = plan;
+    return LB_OK;
+}
+
+lb_status lb_rope_append_plan_create(const lb_rope_provider *provider, const lb_paged_spec *spec,
+                                     lb_rope_append_plan **out) {
+    if (!provider || !spec || !out) return fail(LB_INVALID_ARGUMENT, "provider");
+    *out = nullptr;
+    lb_paged_spec checked;
+    lb_status rc = lb_paged_spec_new(spec->batch_size, spec->max_num_pages, spec->num_query_heads,
+                                     spec->num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE, &checked);
+    if (rc) return rc;
+    return make_append_plan(provider, checked, false, checked.batch_size, out);
+}
+
+lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
+                                            const lb_append_tokens_spec *spec,
+                                            lb_rope_append_plan **out) {
+    if (!provider || !spec || !out) return fail(LB_INVALID_ARGUMENT, "provider");
+    *out = nullptr;
+    lb_append_tokens_spec checked;
+    lb_status rc =
+        spec->max_tokens == 0
+            ? lb_append_tokens_spec_new_extended(spec->tokens, spec->paged.batch_size,
+                                                 spec->paged.max_num_pages,
+                                                 spec->paged.num_query_heads,
+                                                 spec->paged.num_kv_heads, LB_HEAD_DIM,
+                                                 LB_PAGE_SIZE, &checked)
+            : lb_append_tokens_spec_new(spec->tokens, spec->paged.batch_size,
+                                        spec->paged.max_num_pages, spec->paged.num_query_heads,
+                                        spec->paged.num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE,
+                                        &checked);
+    if (rc) return rc;
+    return make_append_plan(provider, checked.paged, true, checked.tokens, out);
+}
+
+void lb_rope_append_plan_destroy(lb_rope_append_plan *plan) { delete plan; }
+
+lb_status lb_rope_append_plan_info_get(const lb_rope_append_plan *plan,
+                                       lb_rope_append_plan_info *info) {
+    if (!plan || !info) return fail(LB_INVALID_ARGUMENT, "plan");
+    info->explicit_tokens = plan->explicit_tokens ? 1 : 0;
+    info->tokens = (uint32_t)plan->tokens;
+    info->grid = plan->grid;
+    info->block = plan->block;
+    info->shared_bytes = plan->shared_bytes;
+    info->commands = 1;
+    return LB_OK;
+}
+
+lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scope,
+                                 const lb_rope_append_args *args) {
+    if (!plan || !scope || !args) return fail(LB_INVALID_ARGUMENT, "plan");
+    const lb_paged_spec &spec = plan->spec;
+    if (scope->queue->device != plan->device)
+        return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
+    lb_status rc = require_command_capacity(*scope, 1);
+    if (rc) return rc;
+
+    Operand op[11];
+    const size_t tokens = plan->tokens;
+    const size_t q_numel = tokens * spec.num_query_heads * LB_HEAD_DIM;
+    const size_t kv_numel = tokens * spec.num_kv_heads * LB_HEAD_DIM;
+    const size_t pool = lb_paged_spec_kv_pages_numel(&spec);
+    int indptr_i, indices_i, last_i, qout_i;
+    if (plan->explicit_tokens) {
+        OperandRequest requests[11] = {
+            {args->query, LB_BF16, false},        {args->key, LB_BF16, false},
+            {args->value, LB_BF16, false},        {args->batch_indices, LB_I32, false},
+            {args->positions, LB_I32, false},     {args->page_indptr, LB_I32, false},
+            {args->page_indices, LB_I32, false},  {args->last_page_len, LB_I32, false},
+            {args->query_output, LB_BF16, true},  {args->key_pages, LB_BF16, true},
+            {args->value_pages, LB_BF16, true},
+        };
+        if ((rc = resolve(*scope, requests, 11, op))) return rc;
+        indptr_i = 5; indices_i = 6; last_i = 7; qout_i = 8;
+    } else {
+        OperandRequest requests[9] = {
+            {args->query, LB_BF16, false},        {args->key, LB_BF16, false},
+            {args->value, LB_BF16, false},        {args->page_indptr, LB_I32, false},
+            {args->page_indices, LB_I32, false},  {args->last_page_len, LB_I32, false},
+            {args->query_output, LB_BF16, true},  {args->key_pages, LB_BF16, true},
+            {args->value_pages, LB_BF16, true},
+        };
+        if ((rc = resolve(*scope, requests, 9, op))) return rc;
+        indptr_i = 3; indices_i = 4; last_i = 5; qout_i = 6;
+    }
+    if ((rc = require_exact_len("query", op[0].numel, q_numel))) return rc;
+    if ((rc = require_exact_len("key", op[1].numel, kv_numel))) return rc;
+    if ((rc = require_exact_len("value", op[2].numel, kv_numel))) return rc;
+    if (plan->explicit_tokens) {
+        if ((rc = require_exact_len("batch_indices", op[3].numel, tokens))) return rc;
+        if ((rc = require_exact_len("positions", op[4].numel, tokens))) return rc;
+    }
+    if ((rc = require_exact_len("page_indptr", op[indptr_i].numel, spec.batch_size + 1))) return rc;
+    if (op[indices_i].numel < spec.batch_size)
+        return fail(LB_PAGE_INDICES_TOO_SHORT, nullptr, (int64_t)spec.batch_size,
+                    (int64_t)op[indices_i].numel);
+    if (op[indices_i].numel > 0x7fffffffu)
+        return fail(LB_ENQUEUE_LENGTH_MISMATCH, "page_indices", 0x7fffffff,
+                    (int64_t)op[indices_i].numel);
+    if ((rc = require_exact_len("last_page_len", op[last_i].numel, spec.batch_size))) return rc;
+    if ((rc = require_exact_len("query_output", op[qout_i].numel, q_numel))) return rc;
+    if ((rc = require_exact_len("key_pages", op[qout_i + 1].numel, pool))) return rc;
+    if ((rc = require_exact_len("value_pages", op[qout_i + 2].numel, pool))) return rc;
+    if ((rc = require_alignment("query", op[0].ptr, 16))) return rc;
+    if ((rc = require_alignment("key", op[1].ptr, 16))) return rc;
+    if ((rc = require_alignment("value", op[2].ptr, 16))) return rc;
+    if ((rc = require_alignment("query_output", op[qout_i].ptr, 16))) return rc;
+    if ((rc = require_alignment("key_pages", op[qout_i + 1].ptr, 16))) return rc;
+    if ((rc = require_alignment("value_pages", op[qout_i + 2].ptr, 16))) return rc;
+
+    AppendLaunch launch;
+    memset(&launch, 0, sizeof(launch));
+    launch.query = op[0].ptr;
+    launch.key = op[1].ptr;
+    launch.value = op[2].ptr;
+    launch.batch_indices = plan->explicit_tokens ? (const int32_t *)op[3].ptr : nullptr;
+    launch.positions = plan->explicit_tokens ? (const int32_t *)op[4].ptr : nullptr;
+    launch.indptr = (const int32_t *)op[indptr_i].ptr;
+    launch.indices = (const int32_t *)op[indices_i].ptr;
+    launch.last = (const int32_t *)op[last_i].ptr;
+    launch.query_output = op[qout_i].ptr;
+    launch.key_pages = op[qout_i + 1].ptr;
+    launch.value_pages = op[qout_i + 2].ptr;
+    launch.tokens = (int32_t)tokens;
+    launch.batch = (int32_t)spec.batch_size;
+    launch.max_pages = (int32_t)spec.max_num_pages;
+    launch.qh = (int32_t)spec.num_query_heads;
+    launch.kvh = (int32_t)spec.num_kv_heads;
+    launch.indices_len = (int32_t)op[indices_i].numel;
+    launch.hash_slots = (int32_t)plan->hash_slots;
+    launch.grid = plan->grid;
+    launch.block = plan->block;
+    launch.shared_bytes = plan->shared_bytes;
+    void *stream = scope->queue->stream;
+    return submit_launch(*scope, [&]() { return launch_rope_append(launch, stream); });
+}
+
+}

@@ -1,0 +1,125 @@
+"""Shared helpers for the GPU parity tests: seeded inputs, device runs through the public API,
+and the tolerances the parity gates use."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import loom_kernels_b200 as lk
+
+# Reference gate limits (crates/loom-infer-validation/src/gates/paged_batch_decode.rs:18-19,
+# gates/rope.rs:20) and the tolerances stated for this build's decode path.
+GATE_OUTPUT_MAX_ABS = 0.015625
+GATE_LSE_MAX_ABS = 0.01
+DECODE_MAX_ABS = 2e-2
+DECODE_REL = 1e-2
+SPLIT_LSE_MAX_ABS = 1e-3
+
+
+def bf16_bits(values: np.ndarray) -> np.ndarray:
+    """F32 -> bf16 bit patterns, round-to-nearest-even (torch's conversion)."""
+    t = torch.from_numpy(np.ascontiguousarray(values, dtype=np.float32)).to(torch.bfloat16)
+    return t.view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def normal_bf16(rng: np.random.Generator, size: int) -> np.ndarray:
+    return bf16_bits(rng.standard_normal(size, dtype=np.float32))
+
+
+def dev_bf16(bits: np.ndarray, device="cuda:0") -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16).copy()).to(device).view(torch.bfloat16)
+
+
+def dev_i32(values, device="cuda:0") -> torch.Tensor:
+    return torch.tensor(np.asarray(values, dtype=np.int32), dtype=torch.int32, device=device)
+
+
+def host_bits(t: torch.Tensor) -> np.ndarray:
+    return t.detach().cpu().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def make_page_table(rng, kv_lens, pool_pages, allow_reuse=False):
+    """Scattered pages: a random draw without replacement from the pool."""
+    pages = [(int(n) + 15) // 16 for n in kv_lens]
+    total = sum(pages)
+    ids = rng.permutation(pool_pages)[:total] if not allow_reuse else rng.integers(0, pool_pages, total)
+    indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
+    last = np.array([(int(n) - 1) % 16 + 1 for n in kv_lens], dtype=np.int32)
+    return indptr, ids.astype(np.int32), last
+
+
+class DecodeRun:
+    """One paged decode through the public API: spec -> plan -> bindings -> scope -> fence."""
+
+    def __init__(self, spec, q_bits, k_bits, v_bits, indptr, indices, last, partitions=0,
+                 heads_per_cta=0, device="cuda:0", provider=None, max_commands=2):
+        self.spec = spec
+        self.device = torch.device(device)
+        self.provider = provider or lk.DecodeProvider.load(self.device.index or 0)
+        self.plan = self.provider.plan_bf16_paged_batch(spec, partitions, heads_per_cta)
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.queue = lk.CommandQueue(self.stream, max_commands)
+        self.q = dev_bf16(q_bits, device)
+        self.k = dev_bf16(k_bits, device)
+        self.v = dev_bf16(v_bits, device)
+        self.indptr = dev_i32(indptr, device)
+        self.indices = dev_i32(indices, device)
+        self.last = dev_i32(last, device)
+        self.out = torch.full((spec.output_numel(),), float("nan"), dtype=torch.bfloat16,
+                              device=device)
+        self.lse = torch.full((spec.lse_numel(),), float("nan"), dtype=torch.float32,
+                              device=device)
+        numel = self.plan.workspace_required_numel()
+        self.workspace = (torch.full((numel,), float("nan"), dtype=torch.float32, device=device)
+                          if numel else None)
+        torch.cuda.synchronize(self.device)
+
+    def bind(self):
+        b = self.queue.bindings(9)
+        self.h = dict(
+            query=b.bind_read(self.q), key_pages=b.bind_read(self.k),
+            value_pages=b.bind_read(self.v), page_indptr=b.bind_read(self.indptr),
+            page_indices=b.bind_read(self.indices), last_page_len=b.bind_read(self.last))
+        self.h_out = b.bind_read_write(self.out)
+        self.h_lse = b.bind_read_write(self.lse)
+        self.h_ws = b.bind_read_write(self.workspace) if self.workspace is not None else None
+        return b
+
+    def args(self):
+        return lk.Bf16PagedBatchDecodeArgs(output=self.h_out.write(), lse=self.h_lse.write(),
+                                           workspace=self.h_ws, **self.h)
+
+    def run(self):
+        scope = self.queue.begin(self.bind())
+        self.plan.enqueue_into(scope, self.args())
+        completion = scope.finish()
+        self.submitted = completion.submitted()
+        bindings = completion.wait()
+        out = bindings.take_read_write(self.h_out)
+        lse = bindings.take_read_write(self.h_lse)
+        assert self.provider.device_status() == 0, "a kernel gave up on a bounded wait"
+        return host_bits(out), lse.cpu().numpy().copy()
+
+
+def check_decode(actual_bits, actual_lse, expected_bits, expected_lse, lse_limit=GATE_LSE_MAX_ABS,
+                 gate=False):
+    a, e = bits_to_f32(actual_bits), bits_to_f32(expected_bits)
+    assert np.all(np.isfinite(a)), "non-finite output"
+    assert np.all(np.isfinite(actual_lse)), "non-finite LSE"
+    err = np.abs(a - e)
+    max_abs = float(err.max()) if err.size else 0.0
+    assert max_abs <= DECODE_MAX_ABS, f"output max-abs {max_abs}"
+    if gate:
+        assert max_abs <= GATE_OUTPUT_MAX_ABS, f"output max-abs {max_abs} over the gate limit"
+    # rel 1e-2: per (request, head) row, ||actual - expected|| <= 1e-2 * ||expected||
+    rows_a, rows_e = a.reshape(-1, 128).astype(np.float64), e.reshape(-1, 128).astype(np.float64)
+    norm_e = np.linalg.norm(rows_e, axis=1)
+    rel = np.linalg.norm(rows_a - rows_e, axis=1) / np.maximum(norm_e, 1e-6)
+    assert float(rel.max()) <= DECODE_REL, f"row-relative error {float(rel.max())}"
+    lse_err = float(np.abs(actual_lse - expected_lse).max())
+    assert lse_err <= lse_limit, f"LSE max-abs {lse_err} (limit {lse_limit})"
+    return max_abs, lse_err
