@@ -11,7 +11,7 @@ from ctypes import (POINTER, c_char, c_char_p, c_float, c_int, c_int32, c_int64,
                     c_uint8, c_uint16, c_uint32, c_uint64, c_void_p)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libloom_b200.so")
+LIB_PATH = os.environ.get("LOOM_B200_LIBRARY", os.path.join(HERE, "libloom_b200.so"))
 
 HEAD_DIM = 128
 PAGE_SIZE = 16

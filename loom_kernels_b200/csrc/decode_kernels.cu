@@ -6,10 +6,11 @@
 //
 // Shape of the kernel
 //   work item  = (request, block of HC KV heads, query block, page chunk); one CTA each.
-//   data path  = one warp issues TMA tile loads (cp.async.bulk.tensor.2d, 128-byte swizzle)
-//                of [16 tokens x 64 dims] boxes into a ring of shared-memory stages; each
-//                (page, KV head) "unit" is 4 boxes (K lo/hi half, V lo/hi half, 8 KB) with its
-//                own full/empty mbarrier pair, so consumer warps drift independently.
+//   data path  = one warp issues TMA tile loads (cp.async.bulk.tensor.3d, 128-byte swizzle) into
+//                a ring of shared-memory stages: one box per (page, K|V) covering the CTA's HC
+//                heads, laid out [head half][16 tokens][64 dims] (up to 32 KB per instruction;
+//                small boxes cap an SM near 45 GB/s, 32 KB boxes reach 80+).  Every page slot
+//                of a stage has its own full/empty mbarrier pair.
 //   math       = each consumer warp owns one unit slot of every stage and the whole GQA group
 //                of that KV head as the M=16 rows of mma.sync.m16n8k16 (BF16 in, F32 out):
 //                S = Q K^T (16 MMAs), online softmax in registers (exp2 domain), O += P V
@@ -90,11 +91,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
-                                            uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-                 "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                 "l"(map), "r"(x), "r"(y), "r"(bar)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
                  : "memory");
 }
 
@@ -147,10 +148,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits 7..9
     uint8_t *ring = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const int slot_bytes = a.hc * kUnitBytes; // one page of the CTA's heads: K box then V box
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + a.stages * stage_bytes);
     const uint32_t full0 = smem_u32(bars);
-    const uint32_t empty0 = full0 + a.stages * units * 8;
-    volatile int *flags = reinterpret_cast<volatile int *>(bars + 2 * a.stages * units);
+    const uint32_t empty0 = full0 + a.stages * a.pps * 8;
+    volatile int *flags = reinterpret_cast<volatile int *>(bars + 2 * a.stages * a.pps);
     // flags[0] = an out-of-range page index was seen; flags[1] = a bounded wait ran out
 
     // ---- work item --------------------------------------------------------------------------
@@ -193,9 +195,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     }
 
     if (tid == 0) {
-        for (int i = 0; i < a.stages * units; ++i) {
+        for (int i = 0; i < a.stages * a.pps; ++i) {
             mbar_init(full0 + i * 8, 1);
-            mbar_init(empty0 + i * 8, a.mt);
+            mbar_init(empty0 + i * 8, a.hc * a.mt);
         }
         flags[0] = 0;
         flags[1] = 0;
@@ -217,13 +219,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
 
     if (warp == kComputeWarps) {
         // ================= producer warp: page-table walk + TMA issue =========================
-        const int my_unit = lane >> 2;
-        const int box = lane & 3; // 0: K dims 0-63, 1: K dims 64-127, 2: V lo, 3: V hi
-        const bool lane_active = my_unit < units;
-        const int my_slot = my_unit / a.hc;
-        const int my_head = hb * a.hc + my_unit % a.hc;
-        const int x = (my_head * 2 + (box & 1)) * 64;
-        const CUtensorMap *map = box < 2 ? &k_map : &v_map;
+        const int my_slot = lane >> 1;
+        const int which = lane & 1; // 0: K box, 1: V box
+        const bool lane_active = my_slot < a.pps;
+        const int z = hb * a.hc * 2;
+        const CUtensorMap *map = which == 0 ? &k_map : &v_map;
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&v_map) : "memory");
@@ -251,20 +251,24 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const int slot = first + my_slot;
             const int page_id = __shfl_sync(0xffffffffu, window, slot & 31);
             const bool has = lane_active && slot < cnt;
-            const uint32_t bar_full = full0 + (stage * units + my_unit) * 8;
-            const uint32_t bar_empty = empty0 + (stage * units + my_unit) * 8;
+            const uint32_t bar_full = full0 + (stage * a.pps + my_slot) * 8;
+            const uint32_t bar_empty = empty0 + (stage * a.pps + my_slot) * 8;
             bool ok = true;
             if (has && round > 0) ok = mbar_wait(bar_empty, (round - 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
                 break;
             }
-            if (has && box == 0) mbar_expect_tx(bar_full, kUnitBytes);
+#if defined(LB_PROBE) && LB_PROBE == 2
+            if (has && which == 0) mbar_arrive(bar_full); // probe: no loads, consumers run on stale tiles
+            continue;
+#endif
+            if (has && which == 0) mbar_expect_tx(bar_full, slot_bytes);
             __syncwarp();
             if (has)
-                tma_load_2d(smem_u32(ring + stage * stage_bytes + my_unit * kUnitBytes +
-                                     box * kBoxBytes),
-                            map, x, page_id * kPage, bar_full);
+                tma_load_3d(smem_u32(ring + stage * stage_bytes + my_slot * slot_bytes +
+                                     which * (slot_bytes / 2)),
+                            map, 0, page_id * kPage, z, bar_full);
         }
         if (__any_sync(0xffffffffu, bad_page) && lane == 0) flags[0] = 1;
     } else {
@@ -303,21 +307,21 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             if (slot >= cnt) continue;
             const int stage = it % a.stages;
             const int round = it / a.stages;
-            const uint32_t bar_full = full0 + (stage * units + unit) * 8;
-            const uint32_t bar_empty = empty0 + (stage * units + unit) * 8;
+            const uint32_t bar_full = full0 + (stage * a.pps + page_slot0) * 8;
+            const uint32_t bar_empty = empty0 + (stage * a.pps + page_slot0) * 8;
             const bool ok = mbar_wait(bar_full, round & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
                 break;
             }
-            uint8_t *tile = ring + stage * stage_bytes + unit * kUnitBytes;
-            const uint32_t k_tile = smem_u32(tile);
-            const uint32_t v_tile = k_tile + 2 * kBoxBytes;
+            uint8_t *slot_base = ring + stage * stage_bytes + page_slot0 * slot_bytes;
+            uint8_t *v_rows = slot_base + slot_bytes / 2 + head_in_cta * 2 * kBoxBytes;
+            const uint32_t k_tile = smem_u32(slot_base + head_in_cta * 2 * kBoxBytes);
+            const uint32_t v_tile = smem_u32(v_rows);
             const int valid_tokens = min(kPage, chunk_end_token - (pg0 + slot) * kPage);
             if (valid_tokens < kPage) {
                 // rows past the request's length hold whatever the pool holds; zero the V rows so
                 // that 0 * garbage cannot produce NaN (their scores are masked below)
-                uint8_t *v_rows = tile + 2 * kBoxBytes;
                 for (int i = lane; i < (kPage - valid_tokens) * 16; i += 32) {
                     const int row = valid_tokens + (i >> 4);
                     const int c = i & 15;
@@ -327,6 +331,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 __syncwarp();
             }
 
+#if defined(LB_PROBE) && LB_PROBE == 1
+            __syncwarp(); // probe: no math, the tile is released at once
+            if (lane == 0) mbar_arrive(bar_empty);
+            row_sum[0] = 1.0f; row_sum[1] = 1.0f; row_max[0] = 0.0f; row_max[1] = 0.0f;
+            continue;
+#endif
             // ---- S = Q K^T : 16 rows x 16 tokens ------------------------------------------------
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll

@@ -169,8 +169,8 @@ struct CudaDriver final : Driver {
         return cudaGraphExecDestroy((cudaGraphExec_t)exec);
     }
 
-    int encode_tensor_map_2d(int device, void *map, const void *base, uint64_t dim0, uint64_t dim1,
-                             uint64_t stride1_bytes, uint32_t box0, uint32_t box1) override {
+    int encode_tensor_map_3d(int device, void *map, const void *base, const uint64_t dims[3],
+                             const uint64_t strides_bytes[2], const uint32_t box[3]) override {
         DeviceGuard guard(device);
         if (!encode_tiled) {
             void *entry = nullptr;
@@ -181,13 +181,13 @@ struct CudaDriver final : Driver {
             if (query != cudaDriverEntryPointSuccess || !entry) return cudaErrorNotSupported;
             encode_tiled = (EncodeTiledFn)entry;
         }
-        const cuuint64_t dims[2] = {dim0, dim1};
-        const cuuint64_t strides[1] = {stride1_bytes};
-        const cuuint32_t box[2] = {box0, box1};
-        const cuuint32_t element_strides[2] = {1, 1};
+        const cuuint64_t global_dims[3] = {dims[0], dims[1], dims[2]};
+        const cuuint64_t global_strides[2] = {strides_bytes[0], strides_bytes[1]};
+        const cuuint32_t box_dims[3] = {box[0], box[1], box[2]};
+        const cuuint32_t element_strides[3] = {1, 1, 1};
         CUresult result = encode_tiled(
-            (CUtensorMap *)map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
-            strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            (CUtensorMap *)map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base),
+            global_dims, global_strides, box_dims, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         return result == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
@@ -277,8 +277,8 @@ struct FakeDriver final : Driver {
     int graph_launch(int, void *, void *) override { return hit("graph_launch"); }
     int graph_destroy(int, void *) override { return 0; }
     int graph_exec_destroy(int, void *) override { return 0; }
-    int encode_tensor_map_2d(int, void *map, const void *, uint64_t, uint64_t, uint64_t, uint32_t,
-                             uint32_t) override {
+    int encode_tensor_map_3d(int, void *map, const void *, const uint64_t *, const uint64_t *,
+                             const uint32_t *) override {
         memset(map, 0, 128);
         return hit("encode");
     }

@@ -221,15 +221,20 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
 
     DecodeLaunch launch;
     memset(&launch, 0, sizeof(launch));
-    // K/V pools viewed as a 2-D tensor [max_pages*16 token rows][kv_heads*128 dims]; one box is
-    // 16 token rows of one page x 64 dims of one head half
-    const uint64_t row_elems = (uint64_t)spec.num_kv_heads * LB_HEAD_DIM;
-    const uint64_t rows = (uint64_t)spec.max_num_pages * LB_PAGE_SIZE;
-    int error = driver().encode_tensor_map_2d(plan->device, launch.k_map, op[1].ptr, row_elems,
-                                              rows, row_elems * 2, 64, 16);
+    // K/V pools viewed as a rank-3 tensor [64 dims][token row][head half]: dimension 1 walks
+    // the max_pages*16 token rows (stride kv_heads*256 B), dimension 2 the 2*kv_heads 128-byte
+    // halves of a row (stride 128 B).  One box = 16 token rows of one page x the 2*HC halves of
+    // the CTA's heads; in shared memory a head half is 16 consecutive 128-byte rows, which is
+    // what makes the swizzled ldmatrix reads conflict-free.
+    const uint64_t dims[3] = {64, (uint64_t)spec.max_num_pages * LB_PAGE_SIZE,
+                              (uint64_t)spec.num_kv_heads * 2};
+    const uint64_t strides[2] = {(uint64_t)spec.num_kv_heads * LB_HEAD_DIM * 2, 128};
+    const uint32_t box[3] = {64, 16, c.heads_per_cta * 2};
+    int error = driver().encode_tensor_map_3d(plan->device, launch.k_map, op[1].ptr, dims, strides,
+                                              box);
     if (!error)
-        error = driver().encode_tensor_map_2d(plan->device, launch.v_map, op[2].ptr, row_elems,
-                                              rows, row_elems * 2, 64, 16);
+        error = driver().encode_tensor_map_3d(plan->device, launch.v_map, op[2].ptr, dims, strides,
+                                              box);
     if (error) return fail(LB_LAUNCH_CONTRACT, "tensor_map", error);
     launch.query = op[0].ptr;
     launch.indptr = (const int32_t *)op[3].ptr;

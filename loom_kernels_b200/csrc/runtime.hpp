@@ -103,10 +103,11 @@ struct Driver {
     virtual int graph_launch(int device, void *exec, void *stream) = 0;
     virtual int graph_destroy(int device, void *graph) = 0;
     virtual int graph_exec_destroy(int device, void *exec) = 0;
-    // Encodes a 2-D bf16 tiled tensor map with 128-byte swizzle into 128 bytes at `map`.
-    virtual int encode_tensor_map_2d(int device, void *map, const void *base, uint64_t dim0,
-                                     uint64_t dim1, uint64_t stride1_bytes, uint32_t box0,
-                                     uint32_t box1) = 0;
+    // Encodes a rank-3 bf16 tiled tensor map with 128-byte swizzle into 128 bytes at `map`.
+    // strides_bytes holds the strides of dimensions 1 and 2 (dimension 0 is contiguous).
+    virtual int encode_tensor_map_3d(int device, void *map, const void *base,
+                                     const uint64_t dims[3], const uint64_t strides_bytes[2],
+                                     const uint32_t box[3]) = 0;
     virtual bool is_fake() const = 0;
     virtual uint64_t launch_count() const = 0;
 };
