@@ -94,7 +94,7 @@ __device__ __forceinline__ void rotate_row(const uint4 *src, uint4 *dst, int j,
 
 __global__ void __launch_bounds__(kThreads) rope_append_kernel(const AppendArgs a) {
     extern __shared__ int hash_table[];
-    __shared__ float2 sincos[kPairs]; // (sin, cos) per rotation pair of the current token
+    __shared__ float2 sincos_table[kPairs]; // (sin, cos) per rotation pair of the current token
     const int tid = threadIdx.x;
 
     // ---- 1. whole-call validation (identical in every CTA) -----------------------------------
@@ -144,22 +144,24 @@ __global__ void __launch_bounds__(kThreads) rope_append_kernel(const AppendArgs 
         token_slot(a, token, position, slot);
         __syncthreads(); // the previous token's table is no longer read
         if (tid < kPairs) {
+            // The F32 angle is exactly the reference's; sin/cos are evaluated in double and
+            // rounded once, which reproduces the host libm's (near correctly rounded) sinf/cosf.
             const float angle = __fmul_rn((float)position, c_inverse_frequency[tid]);
-            float s, c;
-            sincosf(angle, &s, &c);
-            sincos[tid] = make_float2(s, c);
+            double s, c;
+            sincos((double)angle, &s, &c);
+            sincos_table[tid] = make_float2((float)s, (float)c);
         }
         __syncthreads();
         for (int task = tid; task < row_tasks; task += kThreads) {
             const int row = task >> 3, j = task & 7;
             if (row < a.qh) {
                 const size_t offset = ((size_t)token * a.qh + row) * (kHeadDim / 8);
-                rotate_row(a.query + offset, a.query_output + offset, j, sincos);
+                rotate_row(a.query + offset, a.query_output + offset, j, sincos_table);
             } else {
                 const int kv_head = row - a.qh;
                 const size_t src = ((size_t)token * a.kvh + kv_head) * (kHeadDim / 8);
                 const size_t dst = ((size_t)slot * a.kvh + kv_head) * (kHeadDim / 8);
-                rotate_row(a.key + src, a.key_pages + dst, j, sincos);
+                rotate_row(a.key + src, a.key_pages + dst, j, sincos_table);
             }
         }
         for (int task = tid; task < copy_tasks; task += kThreads) {

@@ -55,8 +55,7 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     auto valid_hc = [&](uint32_t hc) {
         return hc >= 1 && hc <= units && units % hc == 0 && spec.num_kv_heads % hc == 0;
     };
-    const uint32_t target_ctas = 2 * (sm_count ? sm_count : 148);
-
+    const uint32_t sms = sm_count ? sm_count : 148;
     uint32_t partitions = options ? options->partitions : 0;
     uint32_t hc = options ? options->heads_per_cta : 0;
     if (hc != 0 && !valid_hc(hc)) return fail(LB_LAUNCH_CONTRACT, "heads_per_cta", hc);
@@ -64,33 +63,46 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     auto items_for = [&](uint32_t h, uint32_t p) -> size_t {
         return spec.batch_size * (spec.num_kv_heads / h) * q_blocks * (size_t)p;
     };
+    // Relative cost of a (heads per CTA, partitions) candidate.  Measured on B200: the HBM
+    // ceiling for scattered pages is ~6.5 TB/s; one SM pulls ~80 GB/s through 32 KB TMA boxes
+    // (8 heads per CTA) but only ~45 GB/s through 4 KB boxes (1 head); the rates below
+    // are what the whole kernel sustains per CTA.  A launch therefore
+    // takes max(bytes / HBM, waves * bytes_per_cta / rate_per_cta); split plans pay for the
+    // workspace round trip and the merge launch.
+    auto cost_of = [&](uint32_t h, uint32_t p) -> double {
+        const double n = (double)items_for(h, p);
+        const double rate = h >= 8 ? 66.0 : h >= 4 ? 60.0 : h >= 2 ? 50.0 : 42.0; // GB/s per CTA
+        const double waves = std::ceil(n / sms);
+        const double hbm_time = 1.0 / 6500.0;
+        const double cta_time = waves / (n * rate);
+        double cost = hbm_time > cta_time ? hbm_time : cta_time;
+        cost *= 1.0 + 0.01 * (waves - 1.0); // each extra wave adds a fill/drain bubble
+        if (p > 1) cost *= 1.04;
+        return cost;
+    };
+    // every chunk keeps >= 8 pages of the per-request page capacity
+    size_t max_partitions = (spec.max_num_pages / spec.batch_size) / 8;
+    if (max_partitions < 1) max_partitions = 1;
+    if (max_partitions > 64) max_partitions = 64;
 
-    if (hc == 0) {
-        // the widest CTA that still yields enough CTAs to fill the device twice
-        const uint32_t p = partitions ? partitions : 1;
-        hc = 1;
-        for (uint32_t candidate = units; candidate >= 1; candidate /= 2) {
-            if (!valid_hc(candidate)) continue;
-            if (items_for(candidate, p) >= target_ctas) {
-                hc = candidate;
-                break;
+    if (hc == 0 || partitions == 0) {
+        double best = 0.0;
+        uint32_t best_hc = 0, best_p = 0;
+        for (uint32_t h = units; h >= 1; h /= 2) {
+            if (!valid_hc(h) || (hc != 0 && h != hc)) continue;
+            const uint32_t p_lo = partitions ? partitions : 1;
+            const uint32_t p_hi = partitions ? partitions : (uint32_t)max_partitions;
+            for (uint32_t p = p_lo; p <= p_hi; ++p) {
+                const double cost = cost_of(h, p);
+                if (best_hc == 0 || cost < best * 0.999) {
+                    best = cost;
+                    best_hc = h;
+                    best_p = p;
+                }
             }
         }
-    }
-    if (partitions == 0) {
-        // split only when one-CTA-per-(request, head block) cannot fill the device; keep
-        // every chunk at >= 8 pages of the per-request page capacity
-        const size_t items = items_for(hc, 1);
-        partitions = 1;
-        if (items < (sm_count ? sm_count : 148)) {
-            const size_t want = (target_ctas + items - 1) / items;
-            const size_t pages_per_request = spec.max_num_pages / spec.batch_size;
-            size_t cap = pages_per_request / 8;
-            if (cap < 1) cap = 1;
-            if (cap > 64) cap = 64;
-            partitions = (uint32_t)(want < cap ? want : cap);
-            if (partitions < 1) partitions = 1;
-        }
+        hc = best_hc;
+        partitions = best_p;
     }
     if (partitions > spec.max_num_pages)
         return fail(LB_INVALID_PARTITION_COUNT, nullptr, partitions, (int64_t)spec.max_num_pages);
