@@ -1,0 +1,117 @@
+"""Multi-GPU partitioning of the paged-decode path (host logic; one process per GPU).
+
+The reference is a single-GPU operator layer with no collective call site
+(crates/loom-infer-cuda/src/command/binding.rs:109-123 rejects cross-device buffers).  Attention
+over a paged KV cache has no exchange step: every (request, KV head) is independent.  So a batch
+is partitioned
+
+  * by request when batch >= GPUs: rank g owns a contiguous range of requests and the pages of
+    those requests in its own pool with local page ids; or
+  * by KV head when batch < GPUs and the GPU count divides kv_heads: rank g owns a contiguous
+    block of KV heads (and their query heads) of every request.
+
+Each rank builds its own spec, plan, queue and bindings; nothing is shared.  NCCL is used only by
+`gather_output_rows`, when the caller wants one contiguous result.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import numpy as np
+
+
+def request_range(batch: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous balanced split: the first batch % world ranks take one extra request."""
+    base, rem = divmod(batch, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def choose_partition(batch: int, kv_heads: int, world: int) -> str:
+    """'request', 'kv_head', or 'replicas' (nothing to split, e.g. one MQA request)."""
+    if world == 1 or batch >= world:
+        return "request"
+    if kv_heads % world == 0:
+        return "kv_head"
+    return "replicas"
+
+
+@dataclass
+class RequestShard:
+    """The part of a paged batch one rank owns, with pool-local page ids."""
+    lo: int
+    hi: int
+    indptr: np.ndarray        # [hi - lo + 1], starts at 0
+    indices: np.ndarray       # local page ids
+    last: np.ndarray
+    global_pages: np.ndarray  # local id -> page id in the caller's global pool
+
+
+def shard_by_request(indptr, indices, last, world: int, rank: int) -> RequestShard:
+    indptr = np.asarray(indptr, dtype=np.int64)
+    batch = len(indptr) - 1
+    lo, hi = request_range(batch, world, rank)
+    pages = np.asarray(indices)[indptr[lo]:indptr[hi]]
+    global_pages, local = np.unique(pages, return_inverse=True)
+    return RequestShard(lo, hi, (indptr[lo:hi + 1] - indptr[lo]).astype(np.int32),
+                        local.astype(np.int32), np.asarray(last)[lo:hi].astype(np.int32),
+                        global_pages.astype(np.int64))
+
+
+def kv_head_range(kv_heads: int, q_heads: int, world: int, rank: int):
+    """(kv_lo, kv_hi, q_lo, q_hi) of the head block rank owns; requires world | kv_heads."""
+    if kv_heads % world != 0:
+        raise ValueError(f"{world} GPUs do not divide {kv_heads} KV heads")
+    per = kv_heads // world
+    group = q_heads // kv_heads
+    return rank * per, (rank + 1) * per, rank * per * group, (rank + 1) * per * group
+
+
+def balanced_assignment(kv_lens, world: int) -> List[np.ndarray]:
+    """Longest-processing-time assignment of requests to ranks by KV bytes (ragged batches).
+
+    Returns, per rank, the request ids it owns in ascending order.  `unpermute_rows` restores
+    request order after a gather."""
+    kv_lens = np.asarray(kv_lens, dtype=np.int64)
+    order = np.argsort(-kv_lens, kind="stable")
+    loads = np.zeros(world, dtype=np.int64)
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for request in order:
+        rank = int(np.argmin(loads))
+        owned[rank].append(int(request))
+        loads[rank] += kv_lens[request]
+    return [np.array(sorted(ids), dtype=np.int64) for ids in owned]
+
+
+def unpermute_rows(gathered_rows, assignment: List[np.ndarray]):
+    """gathered_rows: per-rank row blocks concatenated in rank order -> rows in request order."""
+    order = np.concatenate(assignment)
+    inverse = np.empty_like(order)
+    inverse[order] = np.arange(len(order))
+    return gathered_rows[inverse]
+
+
+def gather_output_rows(local_rows, row_counts: Optional[List[int]] = None, group=None):
+    """All-gathers per-rank output rows `[rows_r, ...]` into `[sum rows, ...]` on every rank.
+
+    Runs on the current stream of the tensor's device (NCCL for CUDA tensors), so it orders
+    after the decode that produced `local_rows` when called under that stream.  Equal row counts
+    use one all_gather_into_tensor; unequal counts pad to the maximum."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    if row_counts is None:
+        row_counts = [local_rows.shape[0]] * world
+    if len(set(row_counts)) == 1:
+        out = local_rows.new_empty((world * row_counts[0],) + tuple(local_rows.shape[1:]))
+        dist.all_gather_into_tensor(out, local_rows.contiguous(), group=group)
+        return out
+    widest = max(row_counts)
+    padded = local_rows.new_zeros((widest,) + tuple(local_rows.shape[1:]))
+    padded[:local_rows.shape[0]] = local_rows
+    out = local_rows.new_empty((world * widest,) + tuple(local_rows.shape[1:]))
+    dist.all_gather_into_tensor(out, padded, group=group)
+    blocks = out.view((world, widest) + tuple(local_rows.shape[1:]))
+    return torch.cat([blocks[r, :row_counts[r]] for r in range(world)], dim=0)

@@ -1,0 +1,110 @@
+"""Multi-rank host logic on CPU (gloo, world size 2): request sharding with pool-local page ids,
+KV-head sharding, the ragged balanced assignment, and the all-gather of output rows.  The decode
+itself is stood in for by the CPU oracle (no GPU here); what is under test is the partitioning
+and the collective plumbing."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from loom_kernels_b200 import sharding
+
+
+def test_request_ranges_and_partition_choice():
+    assert [sharding.request_range(64, 8, r) for r in (0, 7)] == [(0, 8), (56, 64)]
+    assert [sharding.request_range(10, 4, r) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert sharding.choose_partition(512, 8, 8) == "request"
+    assert sharding.choose_partition(1, 32, 8) == "kv_head"
+    assert sharding.choose_partition(1, 1, 8) == "replicas"
+    assert sharding.kv_head_range(32, 32, 8, 3) == (12, 16, 12, 16)
+    assert sharding.kv_head_range(8, 32, 2, 1) == (4, 8, 16, 32)
+    with pytest.raises(ValueError):
+        sharding.kv_head_range(1, 32, 8, 0)
+
+
+def test_balanced_assignment_and_unpermute():
+    rng = np.random.default_rng(0xC5)
+    lens = np.floor(np.exp(rng.uniform(np.log(128), np.log(16384), 512))).astype(np.int64)
+    owned = sharding.balanced_assignment(lens, 8)
+    assert sorted(np.concatenate(owned).tolist()) == list(range(512))
+    loads = np.array([lens[ids].sum() for ids in owned])
+    assert loads.max() / loads.mean() < 1.01  # contiguous ranges would be off by far more
+    rows = np.arange(512)[np.concatenate(owned)]
+    assert np.array_equal(sharding.unpermute_rows(rows, owned), np.arange(512))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, mode, result_queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle
+        rng = np.random.default_rng(99)
+        batch, qh, kvh, pool = 5, 8, 2, 40
+        kv_lens = np.array([70, 16, 33, 120, 5])
+        pages = (kv_lens + 15) // 16
+        indices = rng.permutation(pool)[:pages.sum()].astype(np.int32)
+        indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
+        last = ((kv_lens - 1) % 16 + 1).astype(np.int32)
+        q = oracle.fixture_bf16(batch * qh * 128, 1)
+        k = oracle.fixture_bf16(pool * 16 * kvh * 128, 2)
+        v = oracle.fixture_bf16(pool * 16 * kvh * 128, 3)
+        full_o, full_lse = oracle.paged_decode(oracle.paged_spec(batch, pool, qh, kvh), q, k, v,
+                                               indptr, indices, last)
+        if mode == "request":
+            shard = sharding.shard_by_request(indptr, indices, last, world, rank)
+            n = shard.hi - shard.lo
+            # the rank's own pool holds only its pages, under local ids
+            kr = k.reshape(pool, -1)[shard.global_pages].ravel()
+            vr = v.reshape(pool, -1)[shard.global_pages].ravel()
+            o, lse = oracle.paged_decode(
+                oracle.paged_spec(n, len(shard.global_pages), qh, kvh),
+                q[shard.lo * qh * 128:shard.hi * qh * 128], kr, vr, shard.indptr, shard.indices,
+                shard.last)
+            counts = [hi - lo for lo, hi in (sharding.request_range(batch, world, r)
+                                             for r in range(world))]
+            rows = torch.from_numpy(o.view(np.uint8).reshape(n, qh * 256).copy())  # gloo has no int16
+            gathered = sharding.gather_output_rows(rows, counts)
+            got = gathered.numpy().view(np.uint16).ravel()
+            lse_all = sharding.gather_output_rows(torch.from_numpy(lse.reshape(n, qh).copy()), counts)
+            ok = np.array_equal(got, full_o) and np.array_equal(lse_all.numpy().ravel(), full_lse)
+        else:
+            kv_lo, kv_hi, q_lo, q_hi = sharding.kv_head_range(kvh, qh, world, rank)
+            heads = kv_hi - kv_lo
+            kr = k.reshape(pool * 16, kvh, 128)[:, kv_lo:kv_hi].ravel()
+            vr = v.reshape(pool * 16, kvh, 128)[:, kv_lo:kv_hi].ravel()
+            qr = q.reshape(batch, qh, 128)[:, q_lo:q_hi].ravel()
+            o, _ = oracle.paged_decode(oracle.paged_spec(batch, pool, q_hi - q_lo, heads), qr, kr,
+                                       vr, indptr, indices, last)
+            rows = torch.from_numpy(o.view(np.uint8).reshape(1, -1).copy())
+            gathered = sharding.gather_output_rows(rows)  # [world, batch*(qh/world)*128]
+            got = gathered.numpy().view(np.uint16).reshape(world, batch, (q_hi - q_lo) * 128)
+            got = np.transpose(got, (1, 0, 2)).ravel()
+            ok = np.array_equal(got, full_o)
+        result_queue.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["request", "kv_head"])
+def test_two_rank_sharding_reproduces_the_full_batch(mode, oracle):
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    got = dict(results.get(timeout=5) for _ in range(2))
+    assert got == {0: True, 1: True}
