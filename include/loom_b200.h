@@ -109,7 +109,8 @@ enum {
 
     /* misuse the Rust borrow checker rules out at compile time */
     LB_INVALID_ARGUMENT = 500,           /* null pointer, dead object, not a device pointer */
-    LB_OBJECT_IN_USE                     /* queue already has a live scope / completion */
+    LB_OBJECT_IN_USE,                    /* queue already has a live scope / completion */
+    LB_STATIC_SCRATCH_EXCEEDED           /* a=floats needed b=floats the static scratch holds */
 };
 
 typedef struct lb_error_info {
@@ -336,6 +337,29 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
 lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
                                  const lb_paged_decode_options *options,
                                  lb_paged_decode_plan_info *info);
+
+/* No counterpart in the reference.  Split-K paged decode for a caller that has no way to
+ * allocate device memory and so cannot bind the workspace a split plan requires: for example a
+ * plug-in whose engine owns every device byte and forbids cudaMalloc, or a loop that must stay out
+ * of the allocator.  The partial states go to a fixed array inside the library (on every GPU that
+ * loads it, for the life of the process) instead; inputs and outputs are still the caller's raw
+ * device pointers, with the lengths and 16-byte alignment lb_paged_decode_enqueue checks.
+ * Same kernels, same results as a split plan with `partitions` chunks (>= 2).
+ *   - limit: batch * query_heads * partitions <= lb_paged_decode_split_noalloc_max_states()
+ *     (16384 states = 8.1 MiB); beyond it the call fails with LB_STATIC_SCRATCH_EXCEEDED and
+ *     launches nothing;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - the first call on each GPU looks up the array's device address and sets kernel attributes;
+ *     make that first call before any stream capture;
+ *   - every call shares the one array and finds the previous call's states in it; nothing has to
+ *     start at zero (each state a call merges is written by that call first), but two calls that
+ *     overlap on the GPU -- different streams, or replays in flight together -- race on it. */
+size_t lb_paged_decode_split_noalloc_max_states(void);
+lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t partitions,
+                                        void *stream, const void *query, const void *key_pages,
+                                        const void *value_pages, const int32_t *page_indptr,
+                                        const int32_t *page_indices, size_t page_indices_len,
+                                        const int32_t *last_page_len, void *output, float *lse);
 
 /* ---- RoPE + paged KV append provider --------------------------------------------------------- */
 

@@ -143,6 +143,10 @@ SIGNATURES = {
     "lb_paged_decode_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(DecodeArgs)]),
     "lb_paged_decode_choose": (c_int32, [POINTER(PagedSpec), c_uint32, POINTER(DecodeOptions),
                                          POINTER(DecodePlanInfo)]),
+    "lb_paged_decode_split_noalloc_max_states": (c_size_t, []),
+    "lb_paged_decode_split_noalloc": (c_int32, [POINTER(PagedSpec), c_uint32, c_void_p, c_void_p,
+                                                c_void_p, c_void_p, _I32P, _I32P, c_size_t, _I32P,
+                                                c_void_p, c_void_p]),
     "lb_rope_provider_load": (c_int32, [c_int, POINTER(c_void_p)]),
     "lb_rope_provider_destroy": (None, [c_void_p]),
     "lb_rope_append_plan_create": (c_int32, [c_void_p, POINTER(PagedSpec), POINTER(c_void_p)]),

@@ -546,6 +546,32 @@ class Bf16PagedBatchDecodePlan:
         _check(_abi.load().lb_paged_decode_enqueue(self._ptr, scope._ptr, byref(raw)))
 
 
+def paged_decode_split_noalloc(spec: Bf16PagedBatchDecodeSpec, partitions: int, stream, query,
+                               key_pages, value_pages, page_indptr, page_indices, last_page_len,
+                               output, lse):
+    """Split-K paged decode without a caller workspace (lb_paged_decode_split_noalloc).
+
+    For hosts that cannot allocate device memory: the partial states live in a fixed array inside
+    the library (at most `paged_decode_split_noalloc_max_states()` states).  Arguments are CUDA
+    tensors (or DeviceSpan) used as raw pointers; the call enqueues on `stream` and returns.
+    Calls that overlap on the GPU race on the shared array."""
+    def pointer(buffer):
+        return c_void_p(_describe(buffer)[1])
+
+    handle = getattr(stream, "cuda_stream", stream)
+    indices_ptr = ctypes.cast(pointer(page_indices), ctypes.POINTER(c_int32))
+    _check(_abi.load().lb_paged_decode_split_noalloc(
+        byref(spec._raw), partitions, c_void_p(handle), pointer(query), pointer(key_pages),
+        pointer(value_pages), ctypes.cast(pointer(page_indptr), ctypes.POINTER(c_int32)),
+        indices_ptr, _describe(page_indices)[2],
+        ctypes.cast(pointer(last_page_len), ctypes.POINTER(c_int32)), pointer(output),
+        pointer(lse)))
+
+
+def paged_decode_split_noalloc_max_states() -> int:
+    return _abi.load().lb_paged_decode_split_noalloc_max_states()
+
+
 # ---- RoPE + append provider -------------------------------------------------------------------------------
 
 

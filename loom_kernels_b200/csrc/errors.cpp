@@ -83,6 +83,7 @@ const Entry kNames[] = {
     {LB_GRAPH_CAPTURE_RECORD, "CaptureRecord"},
     {LB_INVALID_ARGUMENT, "InvalidArgument"},
     {LB_OBJECT_IN_USE, "ObjectInUse"},
+    {LB_STATIC_SCRATCH_EXCEEDED, "StaticScratchExceeded"},
 };
 
 void format_message(lb_error_info &e) {
@@ -248,6 +249,12 @@ void format_message(lb_error_info &e) {
     case LB_INVALID_ARGUMENT: snprintf(m, n, "invalid argument: %s", e.operand); break;
     case LB_OBJECT_IN_USE:
         snprintf(m, n, "the command queue already has a live scope or completion");
+        break;
+    case LB_STATIC_SCRATCH_EXCEEDED:
+        snprintf(m, n,
+                 "split-K states need %lld floats but the library's static device scratch holds "
+                 "%lld; use a split plan with a caller-owned workspace",
+                 a, b);
         break;
     default: snprintf(m, n, "%s", e.name); break;
     }
