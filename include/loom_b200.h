@@ -281,12 +281,20 @@ typedef struct lb_decode_provider lb_decode_provider; /* DecodeProvider, decode.
 typedef struct lb_paged_decode_plan lb_paged_decode_plan; /* Bf16PagedBatchDecodePlan :1181-1297 */
 
 /* Bf16PagedBatchDecodeAlgorithm, decode.rs:1157-1161, for this provider */
-enum { LB_DECODE_DIRECT = 0, LB_DECODE_SPLIT_K = 1 };
+enum {
+    LB_DECODE_DIRECT = 0,   /* one CTA per (request, head block); one command, no workspace */
+    LB_DECODE_SPLIT_K = 1,  /* `partitions` page-balanced chunks per request + LSE merge */
+    LB_DECODE_BALANCED = 2  /* the batch's pages cut evenly over the SMs + LSE merge; the choice
+                               for ragged batches and for batches smaller than the device */
+};
 
 typedef struct lb_paged_decode_options {
     uint32_t partitions;    /* 0 = plan-time heuristic, 1 = direct, N>1 = split-K with N chunks */
     uint32_t heads_per_cta; /* 0 = heuristic; KV heads one CTA streams (1, 2, 4 or 8) */
-    uint32_t reserved[6];
+    uint32_t balanced;      /* with partitions == 0: 0 = heuristic, 1 = force the balanced
+                               algorithm, 2 = never use it */
+    uint32_t balanced_ctas; /* CTAs of the balanced algorithm; 0 = heuristic (<= one per SM) */
+    uint32_t reserved[4];
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
@@ -299,7 +307,7 @@ typedef struct lb_paged_decode_plan_info {
     uint32_t stages;
     uint32_t grid, block, shared_bytes;
     uint32_t merge_grid, merge_block;
-    uint32_t commands;       /* 1 direct, 2 split (partials + merge) */
+    uint32_t commands;       /* 1 direct, 2 split or balanced (partials + merge) */
     size_t workspace_numel;  /* F32 elements the caller must bind (0 for direct) */
     size_t workspace_bytes;
 } lb_paged_decode_plan_info;

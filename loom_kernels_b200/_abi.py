@@ -44,8 +44,8 @@ class Handle(ctypes.Structure):
 
 
 class DecodeOptions(ctypes.Structure):
-    _fields_ = [("partitions", c_uint32), ("heads_per_cta", c_uint32),
-                ("reserved", c_uint32 * 6)]
+    _fields_ = [("partitions", c_uint32), ("heads_per_cta", c_uint32), ("balanced", c_uint32),
+                ("balanced_ctas", c_uint32), ("reserved", c_uint32 * 4)]
 
 
 class DecodePlanInfo(ctypes.Structure):

@@ -457,6 +457,7 @@ class CommandCompletion:
 class Bf16PagedBatchDecodeAlgorithm:
     Direct = 0
     SplitK = 1
+    Balanced = 2
 
 
 @dataclass
@@ -496,17 +497,23 @@ class DecodeProvider:
         return out.value
 
     def plan_bf16_paged_batch(self, spec: Bf16PagedBatchDecodeSpec, partitions: int = 0,
-                              heads_per_cta: int = 0) -> "Bf16PagedBatchDecodePlan":
-        options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta)
+                              heads_per_cta: int = 0, balanced: int = 0,
+                              balanced_ctas: int = 0) -> "Bf16PagedBatchDecodePlan":
+        """partitions: 0 heuristic, 1 direct, N split-K; balanced (with partitions 0): 0
+        heuristic, 1 force the balanced algorithm, 2 never use it."""
+        options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta,
+                                     balanced=balanced, balanced_ctas=balanced_ctas)
         out = c_void_p()
         _check(_abi.load().lb_paged_decode_plan_create(self._ptr, byref(spec._raw),
                                                        byref(options), byref(out)))
         return Bf16PagedBatchDecodePlan(out.value)
 
 
-def choose_paged_decode(spec, sm_count: int, partitions: int = 0, heads_per_cta: int = 0):
+def choose_paged_decode(spec, sm_count: int, partitions: int = 0, heads_per_cta: int = 0,
+                        balanced: int = 0):
     """The plan-time heuristic as a pure function (no device needed)."""
-    options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta)
+    options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta,
+                                 balanced=balanced)
     info = _abi.DecodePlanInfo()
     _check(_abi.load().lb_paged_decode_choose(byref(spec._raw), sm_count, byref(options),
                                               byref(info)))

@@ -28,18 +28,21 @@ uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 
 } // namespace
 
-// Plan-time choice of the decode launch shape.  Inputs are the spec and the device only; the
-// page table is not known when a plan is made.
+// Plan-time choice of the decode algorithm and launch shape.  Inputs are the spec and the device
+// only; the page table is not known when a plan is made.
 //
 //   q_tiles (MT)      16-row MMA tiles that cover the GQA group, a power of two <= warps
 //   q_blocks          CTAs per KV head when the group exceeds 16*MT rows
 //   units             warps / MT (page, KV head) tiles one pipeline stage holds
 //   heads_per_cta     KV heads one CTA streams (divides kv_heads and units)
 //   pages_per_stage   units / heads_per_cta
-//   partitions        1 = direct; otherwise page-balanced chunks merged by LSE
+//   algorithm         direct (1 chunk, 1 command) | split-K (caller-pinned chunks per request)
+//                     | balanced (the batch's pages cut evenly over one CTA per SM)
 lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t smem_optin,
                         const lb_paged_decode_options *options, DecodeChoice *out) {
     const uint32_t warps = 8;
+    const uint32_t sms = sm_count ? sm_count : 148;
+    const size_t smem = smem_optin ? smem_optin : 232448;
     const size_t group = spec.num_query_heads / spec.num_kv_heads;
     size_t states;
     if (mul_overflow(spec.batch_size, spec.num_query_heads, &states))
@@ -50,25 +53,25 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     while (q_tiles < warps && (size_t)q_tiles * 16 < group) q_tiles *= 2;
     const uint32_t q_blocks = (uint32_t)((group + (size_t)q_tiles * 16 - 1) / ((size_t)q_tiles * 16));
     const uint32_t units = warps / q_tiles;
+    const uint32_t stage_bytes = units * 8192u;
 
-    // candidate heads per CTA: powers of two dividing both kv_heads and units
+    // heads per CTA: powers of two dividing both kv_heads and units
     auto valid_hc = [&](uint32_t hc) {
         return hc >= 1 && hc <= units && units % hc == 0 && spec.num_kv_heads % hc == 0;
     };
-    const uint32_t sms = sm_count ? sm_count : 148;
     uint32_t partitions = options ? options->partitions : 0;
     uint32_t hc = options ? options->heads_per_cta : 0;
+    const uint32_t balanced_option = options ? options->balanced : 0;
     if (hc != 0 && !valid_hc(hc)) return fail(LB_LAUNCH_CONTRACT, "heads_per_cta", hc);
+    if (balanced_option > 2) return fail(LB_LAUNCH_CONTRACT, "balanced", balanced_option);
 
     auto items_for = [&](uint32_t h, uint32_t p) -> size_t {
         return spec.batch_size * (spec.num_kv_heads / h) * q_blocks * (size_t)p;
     };
-    // Relative cost of a (heads per CTA, partitions) candidate.  Measured on B200: the HBM
-    // ceiling for scattered pages is ~6.5 TB/s; one SM pulls ~80 GB/s through 32 KB TMA boxes
-    // (8 heads per CTA) but only ~45 GB/s through 4 KB boxes (1 head); the rates below
-    // are what the whole kernel sustains per CTA.  A launch therefore
-    // takes max(bytes / HBM, waves * bytes_per_cta / rate_per_cta); split plans pay for the
-    // workspace round trip and the merge launch.
+    // Relative cost of a direct / split candidate.  Measured on B200: the HBM ceiling for
+    // scattered pages is ~6.5 TB/s; one SM pulls ~80 GB/s through 32 KB TMA boxes (8 heads per
+    // CTA) but only ~45 GB/s through 4 KB boxes (1 head); the rates below are what the whole
+    // kernel sustains per CTA.  A launch takes max(bytes / HBM, waves * bytes_per_cta / rate).
     auto cost_of = [&](uint32_t h, uint32_t p) -> double {
         const double n = (double)items_for(h, p);
         const double rate = h >= 8 ? 66.0 : h >= 4 ? 60.0 : h >= 2 ? 50.0 : 42.0; // GB/s per CTA
@@ -77,66 +80,121 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         const double cta_time = waves / (n * rate);
         double cost = hbm_time > cta_time ? hbm_time : cta_time;
         cost *= 1.0 + 0.01 * (waves - 1.0); // each extra wave adds a fill/drain bubble
-        if (p > 1) cost *= 1.04;
+        if (p > 1) cost *= 1.04;            // workspace round trip + merge launch
         return cost;
     };
-    // every chunk keeps >= 8 pages of the per-request page capacity
-    size_t max_partitions = (spec.max_num_pages / spec.batch_size) / 8;
-    if (max_partitions < 1) max_partitions = 1;
-    if (max_partitions > 64) max_partitions = 64;
 
-    if (hc == 0 || partitions == 0) {
-        double best = 0.0;
-        uint32_t best_hc = 0, best_p = 0;
-        for (uint32_t h = units; h >= 1; h /= 2) {
-            if (!valid_hc(h) || (hc != 0 && h != hc)) continue;
-            const uint32_t p_lo = partitions ? partitions : 1;
-            const uint32_t p_hi = partitions ? partitions : (uint32_t)max_partitions;
-            for (uint32_t p = p_lo; p <= p_hi; ++p) {
-                const double cost = cost_of(h, p);
-                if (best_hc == 0 || cost < best * 0.999) {
-                    best = cost;
-                    best_hc = h;
-                    best_p = p;
+    // The balanced algorithm keeps the page prefix of every request in shared memory and packs
+    // (page id, head block) pairs, which bounds what it accepts.
+    const uint32_t widest_hc = [&] {
+        for (uint32_t h = units; h >= 1; h /= 2)
+            if (valid_hc(h)) return h;
+        return 1u;
+    }();
+    const uint32_t balanced_hc = hc ? hc : widest_hc;
+    const size_t balanced_extra = (3 * spec.batch_size + 2) * sizeof(int32_t);
+    const bool balanced_possible =
+        spec.batch_size <= 1024 && spec.max_num_pages < (1u << 23) &&
+        (spec.num_kv_heads / balanced_hc) * q_blocks <= 4096 &&
+        2 * stage_bytes + 3072 + balanced_extra <= smem;
+
+    uint32_t algorithm;
+    if (partitions == 1) {
+        algorithm = LB_DECODE_DIRECT;
+    } else if (partitions > 1) {
+        algorithm = LB_DECODE_SPLIT_K;
+    } else if (balanced_option == 1) {
+        if (!balanced_possible) return fail(LB_LAUNCH_CONTRACT, "balanced", 1);
+        algorithm = LB_DECODE_BALANCED;
+    } else {
+        // Direct wins when whole (request, head block) items already tile the device: no merge
+        // launch, no workspace.  That needs many more items than SMs, because requests of one
+        // batch differ in length.  Otherwise cut by pages.
+        // A pool of at most 64 pages (1024 tokens in all) has nothing to balance either: such
+        // calls are launch-latency bound and a second launch would only add to it.
+        const size_t direct_items = items_for(widest_hc, 1);
+        const bool plenty = direct_items >= 8 * (size_t)sms || spec.max_num_pages <= 64;
+        if (plenty) algorithm = LB_DECODE_DIRECT;
+        else if (balanced_possible && balanced_option != 2) algorithm = LB_DECODE_BALANCED;
+        else algorithm = LB_DECODE_SPLIT_K; // best static split below (may come out as 1 chunk)
+    }
+
+    if (algorithm == LB_DECODE_BALANCED) {
+        hc = balanced_hc;
+        partitions = 1;
+    } else {
+        size_t max_partitions = (spec.max_num_pages / spec.batch_size) / 8; // >= 8 pages a chunk
+        if (max_partitions < 1) max_partitions = 1;
+        if (max_partitions > 64) max_partitions = 64;
+        const bool choose_p = partitions == 0;
+        if (algorithm == LB_DECODE_DIRECT && choose_p) partitions = 1;
+        const bool sweep_p = choose_p && algorithm == LB_DECODE_SPLIT_K;
+        if (hc == 0 || sweep_p) {
+            double best = 0.0;
+            uint32_t best_hc = 0, best_p = 0;
+            for (uint32_t h = units; h >= 1; h /= 2) {
+                if (!valid_hc(h) || (hc != 0 && h != hc)) continue;
+                const uint32_t p_lo = sweep_p ? 1 : partitions;
+                const uint32_t p_hi = sweep_p ? (uint32_t)max_partitions : partitions;
+                for (uint32_t p = p_lo; p <= p_hi; ++p) {
+                    const double cost = cost_of(h, p);
+                    if (best_hc == 0 || cost < best * 0.999) {
+                        best = cost;
+                        best_hc = h;
+                        best_p = p;
+                    }
                 }
             }
+            hc = best_hc;
+            partitions = best_p;
         }
-        hc = best_hc;
-        partitions = best_p;
-    }
-    if (partitions > spec.max_num_pages)
-        return fail(LB_INVALID_PARTITION_COUNT, nullptr, partitions, (int64_t)spec.max_num_pages);
-
-    const size_t items = items_for(hc, partitions);
-    if (items > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)items);
-    size_t workspace = 0;
-    if (partitions > 1) {
-        if (mul_overflow(states, partitions, &workspace) ||
-            mul_overflow(workspace, LB_PARTIAL_STATE_WIDTH, &workspace) ||
-            workspace > SIZE_MAX / sizeof(float))
-            return fail(LB_ELEMENT_COUNT_OVERFLOW);
+        algorithm = partitions > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+        if (partitions > spec.max_num_pages)
+            return fail(LB_INVALID_PARTITION_COUNT, nullptr, partitions,
+                        (int64_t)spec.max_num_pages);
     }
 
-    const uint32_t stage_bytes = units * 8192u;
-    const size_t budget = (smem_optin ? smem_optin : 232448) - 2048; // barriers, flags
-    uint32_t stages = (uint32_t)(budget / stage_bytes);
+    const uint32_t pps = units / hc;
+    size_t extra = 3072; // alignment slack, barriers, flags
+    if (algorithm == LB_DECODE_BALANCED) extra += balanced_extra;
+    uint32_t stages = (uint32_t)((smem - extra) / stage_bytes);
     if (stages > 6) stages = 6;
-    // the cross-warp state merge at the end of a CTA reuses the ring: 8 warps x 68 x 32 floats
-    if (stages < 2 || (units / hc > 1 && (size_t)stages * stage_bytes < 8u * 68u * 32u * 4u))
-        return fail(LB_LAUNCH_CONTRACT, "shared_memory", (int64_t)smem_optin);
+    // direct/split CTAs merge their warps' states in the ring: 8 warps x 68 x 32 floats
+    if (stages < 2 || (algorithm != LB_DECODE_BALANCED && pps > 1 &&
+                       (size_t)stages * stage_bytes < 8u * 68u * 32u * 4u))
+        return fail(LB_LAUNCH_CONTRACT, "shared_memory", (int64_t)smem);
 
+    size_t grid, workspace = 0;
+    if (algorithm == LB_DECODE_BALANCED) {
+        grid = options && options->balanced_ctas ? options->balanced_ctas : sms;
+        if (grid > sms) grid = sms; // workers share nothing, but one CTA per SM is the design
+        const size_t workers = grid * pps;
+        const size_t rows = group < 16u * q_tiles ? group : 16u * q_tiles;
+        workspace = workers * 2 * hc * rows * LB_PARTIAL_STATE_WIDTH + spec.batch_size + 2;
+    } else {
+        grid = items_for(hc, partitions);
+        if (grid > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)grid);
+        if (partitions > 1) {
+            if (mul_overflow(states, partitions, &workspace) ||
+                mul_overflow(workspace, LB_PARTIAL_STATE_WIDTH, &workspace) ||
+                workspace > SIZE_MAX / sizeof(float))
+                return fail(LB_ELEMENT_COUNT_OVERFLOW);
+        }
+    }
+
+    out->algorithm = algorithm;
     out->partitions = partitions;
     out->heads_per_cta = hc;
     out->q_tiles = q_tiles;
     out->q_blocks = q_blocks;
-    out->pages_per_stage = units / hc;
+    out->pages_per_stage = pps;
     out->stages = stages;
     out->warps = warps;
-    out->grid = (uint32_t)items;
+    out->grid = (uint32_t)grid;
     out->block = (warps + 1) * 32;
-    out->shared_bytes = stages * stage_bytes + 1024 /* alignment slack */ + 1024 /* barriers */;
+    out->shared_bytes = (uint32_t)(stages * stage_bytes + extra);
     out->merge_block = 128;
-    out->merge_grid = partitions > 1 ? ceil_div((uint32_t)states, 4) : 0;
+    out->merge_grid = algorithm == LB_DECODE_DIRECT ? 0 : ceil_div((uint32_t)states, 4);
     out->workspace_numel = workspace;
     return LB_OK;
 }
@@ -383,7 +441,7 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
     DecodeChoice choice;
     lb_status rc = choose_decode(*spec, sm_count, 0, options, &choice);
     if (rc) return rc;
-    info->algorithm = choice.partitions > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+    info->algorithm = (int32_t)choice.algorithm;
     info->partitions = choice.partitions;
     info->heads_per_cta = choice.heads_per_cta;
     info->q_tiles = choice.q_tiles;
@@ -395,7 +453,7 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
     info->shared_bytes = choice.shared_bytes;
     info->merge_grid = choice.merge_grid;
     info->merge_block = choice.merge_block;
-    info->commands = choice.partitions > 1 ? 2 : 1;
+    info->commands = choice.algorithm == LB_DECODE_DIRECT ? 1 : 2;
     info->workspace_numel = choice.workspace_numel;
     info->workspace_bytes = choice.workspace_numel * sizeof(float);
     return LB_OK;

@@ -1,0 +1,313 @@
+// Device-side building blocks shared by the paged-decode kernels: mbarrier / TMA / ldmatrix /
+// mma.sync wrappers, the per-request metadata guard, and the per-page attention step.
+//
+// Shared-memory tile layout (what one TMA box leaves behind): for each KV head of the CTA, a
+// K tile and a V tile of 4 KB each = two 2 KB halves (dims 0-63, dims 64-127); a half is 16 token
+// rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace lb {
+namespace dev {
+
+constexpr int kHeadDim = 128;
+constexpr int kPage = 16;
+constexpr int kStateWidth = 130;
+constexpr int kComputeWarps = 8;
+constexpr int kUnitBytes = 8192;  // K (16 x 256 B) + V (16 x 256 B) of one (page, KV head)
+constexpr int kBoxBytes = 2048;   // half a tile: 16 tokens x 64 dims x 2 B
+constexpr long long kWaitCycles = 4000000000ll; // ~2 s at 2 GHz; waits normally take microseconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+// Bounded wait: false after kWaitCycles without the phase completing.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 256; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - start > kWaitCycles) return false;
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1,
+                                            uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1,
+                                                  uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Per-request metadata guard of the reference's kernels
+// (crates/loom-infer-cuda/src/attention/decode.rs:234-248 / :426-437).
+__device__ __forceinline__ bool request_metadata_valid(const int32_t *indptr, const int32_t *last,
+                                                       int batch, int indices_len, int request,
+                                                       int &page_start, int &page_end, int &tail) {
+    const int global_end = indptr[batch];
+    page_start = indptr[request];
+    page_end = indptr[request + 1];
+    tail = last[request];
+    return indptr[0] == 0 && global_end >= 0 && global_end == indices_len && page_start >= 0 &&
+           page_end > page_start && page_end <= global_end && tail >= 1 && tail <= kPage;
+}
+
+// Online-softmax state of one warp: 16 query rows x 128 dims in MMA accumulator layout.  A lane
+// owns rows lane/4 and lane/4 + 8; row_sum is a per-lane partial until finish_rows().
+struct WarpState {
+    float acc[16][4];
+    float row_max[2];
+    float row_sum[2];
+    __device__ __forceinline__ void reset() {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        row_max[0] = row_max[1] = -INFINITY;
+        row_sum[0] = row_sum[1] = 0.0f;
+    }
+    __device__ __forceinline__ void finish_rows() {
+        row_sum[0] += __shfl_xor_sync(0xffffffffu, row_sum[0], 1);
+        row_sum[0] += __shfl_xor_sync(0xffffffffu, row_sum[0], 2);
+        row_sum[1] += __shfl_xor_sync(0xffffffffu, row_sum[1], 1);
+        row_sum[1] += __shfl_xor_sync(0xffffffffu, row_sum[1], 2);
+    }
+};
+
+// A-operand fragments of 16 query rows (rows >= `rows_valid` are zero): q points at row 0.
+__device__ __forceinline__ void load_query_fragments(const __nv_bfloat16 *q, int rows_valid,
+                                                     int lane, uint32_t (&qf)[8][4]) {
+    const int r0 = lane >> 2, c = lane & 3;
+    const bool valid0 = r0 < rows_valid, valid1 = r0 + 8 < rows_valid;
+    const uint32_t *q0 = reinterpret_cast<const uint32_t *>(q + (size_t)r0 * kHeadDim);
+    const uint32_t *q1 = q0 + 8 * kHeadDim / 2;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        qf[kk][0] = valid0 ? q0[kk * 8 + c] : 0u;
+        qf[kk][1] = valid1 ? q1[kk * 8 + c] : 0u;
+        qf[kk][2] = valid0 ? q0[kk * 8 + 4 + c] : 0u;
+        qf[kk][3] = valid1 ? q1[kk * 8 + 4 + c] : 0u;
+    }
+}
+
+// One page of one KV head: S = Q K^T (16 x 16), online softmax in the log2 domain, O += P V.
+// k_tile / v_tile are the 4 KB tiles in shared memory; tokens >= valid_tokens are masked and
+// their V rows zeroed first (pool rows past a request's length may hold anything, and
+// 0 * garbage must not produce NaN).  Returns true when shared memory was written by this warp
+// (the caller then fences before handing the tile back to the async proxy).
+__device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int valid_tokens,
+                                            const uint32_t (&qf)[8][4], float scale_log2,
+                                            int lane, WarpState &st) {
+    const uint32_t k_tile = smem_u32(k_ptr), v_tile = smem_u32(v_ptr);
+    const bool partial = valid_tokens < kPage;
+    if (partial) {
+        for (int i = lane; i < (kPage - valid_tokens) * 16; i += 32) {
+            const int row = valid_tokens + (i >> 4);
+            const int c = i & 15;
+            *reinterpret_cast<uint4 *>(v_ptr + (c >> 3) * kBoxBytes + row * 128 + (c & 7) * 16) =
+                make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+    }
+    // per-lane ldmatrix selectors: K matrices are (tokens 0-7 | 8-15) x (k chunk | k chunk + 1),
+    // V matrices (transposed on load) are (tokens 0-7 | 8-15) x (dim chunk | dim chunk + 1)
+    const int k_tok = ((lane >> 4) << 3) + (lane & 7);
+    const int k_hi = (lane >> 3) & 1;
+    const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
+    const int v_hi = lane >> 4;
+
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        const int chunk = ((kk & 3) << 1) + k_hi;
+        const uint32_t addr =
+            k_tile + (kk >> 2) * kBoxBytes + k_tok * 128 + ((chunk ^ (k_tok & 7)) << 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(addr, b0, b1, b2, b3);
+        mma_bf16(s0, qf[kk], b0, b1);
+        mma_bf16(s1, qf[kk], b2, b3);
+    }
+    const int t0 = (lane & 3) * 2;
+    float x00 = s0[0] * scale_log2, x01 = s0[1] * scale_log2;
+    float x02 = s0[2] * scale_log2, x03 = s0[3] * scale_log2;
+    float x10 = s1[0] * scale_log2, x11 = s1[1] * scale_log2;
+    float x12 = s1[2] * scale_log2, x13 = s1[3] * scale_log2;
+    if (partial) {
+        if (t0 >= valid_tokens) { x00 = -INFINITY; x02 = -INFINITY; }
+        if (t0 + 1 >= valid_tokens) { x01 = -INFINITY; x03 = -INFINITY; }
+        if (t0 + 8 >= valid_tokens) { x10 = -INFINITY; x12 = -INFINITY; }
+        if (t0 + 9 >= valid_tokens) { x11 = -INFINITY; x13 = -INFINITY; }
+    }
+    float m0 = fmaxf(fmaxf(x00, x01), fmaxf(x10, x11));
+    float m1 = fmaxf(fmaxf(x02, x03), fmaxf(x12, x13));
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+    // token 0 of a page is always valid, so the new maxima are finite
+    const float new0 = fmaxf(st.row_max[0], m0), new1 = fmaxf(st.row_max[1], m1);
+    const float alpha0 = exp2f(st.row_max[0] - new0), alpha1 = exp2f(st.row_max[1] - new1);
+    st.row_max[0] = new0;
+    st.row_max[1] = new1;
+    const float p00 = exp2f(x00 - new0), p01 = exp2f(x01 - new0);
+    const float p10 = exp2f(x10 - new0), p11 = exp2f(x11 - new0);
+    const float p02 = exp2f(x02 - new1), p03 = exp2f(x03 - new1);
+    const float p12 = exp2f(x12 - new1), p13 = exp2f(x13 - new1);
+    st.row_sum[0] = st.row_sum[0] * alpha0 + ((p00 + p01) + (p10 + p11));
+    st.row_sum[1] = st.row_sum[1] * alpha1 + ((p02 + p03) + (p12 + p13));
+    uint32_t pf[4];
+    pf[0] = pack_bf16(p00, p01);
+    pf[1] = pack_bf16(p02, p03);
+    pf[2] = pack_bf16(p10, p11);
+    pf[3] = pack_bf16(p12, p13);
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+        st.acc[nt][0] *= alpha0;
+        st.acc[nt][1] *= alpha0;
+        st.acc[nt][2] *= alpha1;
+        st.acc[nt][3] *= alpha1;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int chunk = ((2 * j) & 7) + v_hi;
+        const uint32_t addr =
+            v_tile + (j >> 2) * kBoxBytes + v_tok * 128 + ((chunk ^ (v_tok & 7)) << 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(addr, b0, b1, b2, b3);
+        mma_bf16(st.acc[2 * j], pf, b0, b1);
+        mma_bf16(st.acc[2 * j + 1], pf, b2, b3);
+    }
+    return partial;
+}
+
+// Writes the two rows a lane owns: BF16 O + log2 LSE (final) or the F32 state [m, n, wv[128]].
+__device__ __forceinline__ void write_final_row(__nv_bfloat16 *out_row, float *lse_slot, int lane,
+                                                int half, const WarpState &st) {
+    const float l = st.row_sum[half];
+    uint32_t *out = reinterpret_cast<uint32_t *>(out_row);
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+        out[nt * 4 + (lane & 3)] =
+            pack_bf16(st.acc[nt][half * 2] / l, st.acc[nt][half * 2 + 1] / l);
+    if ((lane & 3) == 0) *lse_slot = st.row_max[half] + log2f(l);
+}
+__device__ __forceinline__ void write_state_row(float *state, int lane, int half,
+                                                const WarpState &st, bool poisoned) {
+    if ((lane & 3) == 0) {
+        state[0] = st.row_max[half];
+        state[1] = poisoned ? -1.0f : st.row_sum[half]; // a negative normaliser poisons a merge
+    }
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+        *reinterpret_cast<float2 *>(state + 2 + nt * 8 + col) =
+            make_float2(st.acc[nt][half * 2], st.acc[nt][half * 2 + 1]);
+}
+
+// Merges n unnormalised states [max_log2, normaliser, wv[128]] of one (request, query head) and
+// writes BF16 O + log2 LSE.  state_of(i) returns the i-th state or nullptr for "no state";
+// states with a zero normaliser (chunks without pages) are skipped as in the reference's device
+// merge (crates/loom-infer-cuda/src/attention/decode.rs:635); a negative normaliser marks a chunk
+// that met an out-of-range page, and then nothing is published.  Same algebra as
+// single_decode_bf16_split_k_merge_reference (crates/loom-infer/src/attention/single_decode/
+// mod.rs:343-379), evaluated against the global maximum so that the state loads are independent
+// and pipeline instead of forming one dependent chain per state.
+template <typename StateOf>
+__device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane,
+                                             __nv_bfloat16 *out_row, float *lse_slot) {
+    float top = -INFINITY;
+    bool poisoned = false;
+    for (int i = lane; i < n; i += 32) {
+        const float *s = state_of(i);
+        if (s == nullptr) continue;
+        const float norm = __ldg(s + 1);
+        poisoned |= norm < 0.0f;
+        if (norm > 0.0f) top = fmaxf(top, __ldg(s));
+    }
+    if (__any_sync(0xffffffffu, poisoned)) return;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, d));
+    float norm = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int i = 0; i < n; ++i) {
+        const float *s = state_of(i);
+        if (s == nullptr) continue;
+        const float part_norm = __ldg(s + 1);
+        const float weight = part_norm > 0.0f ? exp2f(__ldg(s) - top) : 0.0f;
+        const float2 lo = __ldg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
+        const float2 hi = __ldg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+        norm += part_norm * weight;
+        acc.x += lo.x * weight;
+        acc.y += lo.y * weight;
+        acc.z += hi.x * weight;
+        acc.w += hi.y * weight;
+    }
+    uint2 packed;
+    packed.x = pack_bf16(acc.x / norm, acc.y / norm);
+    packed.y = pack_bf16(acc.z / norm, acc.w / norm);
+    *reinterpret_cast<uint2 *>(out_row + lane * 4) = packed;
+    if (lane == 0) *lse_slot = top + log2f(norm);
+}
+
+} // namespace dev
+} // namespace lb

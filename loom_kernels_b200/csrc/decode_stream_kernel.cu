@@ -1,0 +1,415 @@
+// Balanced paged decode for sm_100a: the same tile pipeline as paged_decode_kernel, but the work
+// is cut by PAGES, not by requests.
+//
+// The reference's paged decode gives one CTA to one (request, query head)
+// (crates/loom-infer-cuda/src/attention/decode.rs:225-233); with ragged batches or few requests
+// the longest request then decides the run time.  Here every (page, head block) unit of the
+// whole batch is laid on one line -- head block major, then request, then page -- and the line is
+// cut into `workers` equal pieces (within one page), so every SM streams the same number of bytes
+// whatever the request lengths are:
+//
+//     x = h * total_pages + prefix[r] + page          worker w owns [W*w/workers, W*(w+1)/workers)
+//
+// A worker = one page-slot lane of a CTA (HC*MT consumer warps + the shared producer warp).  Its
+// range decomposes into segments, each inside one (request, head block) item.  A segment that
+// covers its item completely is finished in place (BF16 O + log2 LSE); a cut segment leaves an
+// unnormalised F32 state [max_log2, normaliser, wv[128]] (crates/loom-infer/src/attention/
+// single_decode/mod.rs:10-13) in one of the worker's two workspace slots -- slot 0 if the
+// segment begins where the worker begins, else slot 1 -- and balanced_merge_kernel, which
+// recomputes the same cut, merges the states of an item in worker order with the arithmetic of
+// single_decode_bf16_split_k_merge_reference (:343-379).
+//
+// Device-resident metadata is never an error: an invalid request contributes no pages and keeps
+// its previous output; an out-of-range page index poisons its item.  All waits are bounded.
+#include <cstring>
+
+#include "decode_device.cuh"
+#include "kernels.hpp"
+
+namespace lb {
+namespace {
+
+using namespace dev;
+
+struct StreamArgs {
+    const __nv_bfloat16 *query;
+    const int32_t *indptr, *indices, *last;
+    __nv_bfloat16 *output;
+    float *lse;
+    float *workspace; // [workers][2][hc * rows][130] F32, then prefix[batch + 1] I32
+    int32_t *status;
+    int32_t batch, max_pages, qh, kvh, indices_len;
+    int32_t hc, pps, mt, qb, stages, workers;
+    int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
+    float scale_log2;
+};
+
+__device__ __forceinline__ size_t state_floats(const StreamArgs &a) {
+    return (size_t)a.workers * 2 * a.hc * a.rows * kStateWidth;
+}
+
+// first index i in [0, n] with prefix[i] > y, minus one: the request that owns page y
+__device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
+    int lo = 0, hi = n; // invariant: prefix[lo] <= y < prefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= y) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ long long worker_begin(long long total_units, int workers, int w) {
+    return total_units * w / workers;
+}
+
+__global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
+balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
+                       const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    const int units = kComputeWarps / a.mt;
+    const int stage_bytes = units * kUnitBytes;
+    const int slot_bytes = a.hc * kUnitBytes;
+    uint8_t *ring = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + a.stages * stage_bytes);
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + a.stages * a.pps * 8;
+    int *flags = reinterpret_cast<int *>(bars + 2 * a.stages * a.pps);
+    volatile int *timeout_flag = flags;             // a bounded wait ran out
+    volatile int *bad_slot = flags + 1;             // [stages * pps]: page id was out of range
+    int *prefix = flags + 1 + a.stages * a.pps;     // [batch + 1] cumulative valid pages
+    int *pstart = prefix + a.batch + 1;             // [batch] indptr[r]
+    int *ptail = pstart + a.batch;                  // [batch] last_page_len[r]
+
+    // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
+    const int global_end = a.indptr[a.batch];
+    const bool global_ok = a.indptr[0] == 0 && global_end >= 0 && global_end == a.indices_len;
+    for (int r = tid; r < a.batch; r += blockDim.x) {
+        const int s = a.indptr[r], e = a.indptr[r + 1], t = a.last[r];
+        const bool ok = global_ok && s >= 0 && e > s && e <= global_end && t >= 1 && t <= kPage;
+        pstart[r] = s;
+        ptail[r] = t;
+        prefix[r + 1] = ok ? e - s : 0;
+    }
+    if (tid == 0) {
+        prefix[0] = 0;
+        for (int i = 0; i < a.stages * a.pps; ++i) {
+            mbar_init(full0 + i * 8, 1);
+            mbar_init(empty0 + i * 8, a.hc * a.mt);
+            bad_slot[i] = 0;
+        }
+        *timeout_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // inclusive scan of prefix[1..batch] by one warp: per-lane chunks, then a warp scan
+        const int chunk = (a.batch + 31) / 32;
+        const int lo = 1 + lane * chunk, hi = min(a.batch + 1, lo + chunk);
+        int sum = 0;
+        for (int i = lo; i < hi; ++i) sum += prefix[i];
+        int offset = sum;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, offset, d);
+            if (lane >= d) offset += up;
+        }
+        int running = offset - sum;
+        for (int i = lo; i < hi; ++i) {
+            running += prefix[i];
+            prefix[i] = running;
+        }
+    }
+    __syncthreads();
+    const int total = prefix[a.batch];
+    const int group = a.qh / a.kvh;
+    const int head_blocks = a.kvh / a.hc;
+    const int items = head_blocks * a.qb;
+    const long long total_units = (long long)total * items;
+    if (blockIdx.x == 0) {
+        // the merge kernel reads the same prefix
+        int *out_prefix = reinterpret_cast<int *>(a.workspace + state_floats(a));
+        for (int i = tid; i <= a.batch; i += blockDim.x) out_prefix[i] = prefix[i];
+    }
+    if (total == 0) return;
+
+    const int rows_per_block = 16 * a.mt;
+
+    if (warp == kComputeWarps) {
+        // ================= producer warp ==========================================================
+        const int my_slot = lane >> 1;
+        const int which = lane & 1; // 0: K box, 1: V box
+        const bool lane_active = my_slot < a.pps;
+        const CUtensorMap *map = which == 0 ? &k_map : &v_map;
+        if (lane == 0) {
+            prefetch_tensormap(&k_map);
+            prefetch_tensormap(&v_map);
+        }
+        // per worker of this CTA: range, and a 32-page window of (page id, head block) pairs
+        long long begin[8], count[8];
+        int win_id[8], win_hb[8], next_id[8], next_hb[8];
+        int longest = 0;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            begin[s] = 0;
+            count[s] = 0;
+            if (s < a.pps) {
+                const int w = blockIdx.x * a.pps + s;
+                begin[s] = worker_begin(total_units, a.workers, w);
+                count[s] = worker_begin(total_units, a.workers, w + 1) - begin[s];
+                longest = max(longest, (int)count[s]);
+            }
+        }
+        auto load_window = [&](int s, int first, int &id_out, int &hb_out) {
+            id_out = 0;
+            hb_out = 0;
+            const long long j = (long long)first + lane;
+            if (j >= count[s]) return;
+            const long long x = begin[s] + j;
+            const int h = (int)(x / total);
+            const int y = (int)(x % total);
+            const int r = owner_of(prefix, a.batch, y);
+            const int id = a.indices[pstart[r] + (y - prefix[r])];
+            hb_out = h / a.qb;
+            id_out = (id < 0 || id >= a.max_pages) ? -1 : id;
+        };
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            if (s < a.pps) {
+                load_window(s, 0, win_id[s], win_hb[s]);
+                load_window(s, 32, next_id[s], next_hb[s]);
+            }
+        for (int j = 0; j < longest; ++j) {
+            if (j > 0 && (j & 31) == 0) {
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    if (s < a.pps) {
+                        win_id[s] = next_id[s];
+                        win_hb[s] = next_hb[s];
+                        load_window(s, j + 32, next_id[s], next_hb[s]);
+                    }
+            }
+            int page_id = 0, hb = 0;
+            long long my_count = 0;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                if (s < a.pps) {
+                    const int id = __shfl_sync(0xffffffffu, win_id[s], j & 31);
+                    const int h = __shfl_sync(0xffffffffu, win_hb[s], j & 31);
+                    if (my_slot == s) {
+                        page_id = id;
+                        hb = h;
+                        my_count = count[s];
+                    }
+                }
+            const int stage = j % a.stages;
+            const int round = j / a.stages;
+            const bool has = lane_active && j < my_count;
+            const uint32_t bar_full = full0 + (stage * a.pps + my_slot) * 8;
+            const uint32_t bar_empty = empty0 + (stage * a.pps + my_slot) * 8;
+            bool ok = true;
+            if (has && round > 0) ok = mbar_wait(bar_empty, (round - 1) & 1);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) *timeout_flag = 1;
+                break;
+            }
+            if (has && which == 0) {
+                bad_slot[stage * a.pps + my_slot] = page_id < 0;
+                mbar_expect_tx(bar_full, slot_bytes);
+            }
+            __syncwarp();
+            if (has)
+                tma_load_3d(smem_u32(ring + stage * stage_bytes + my_slot * slot_bytes +
+                                     which * (slot_bytes / 2)),
+                            map, 0, max(page_id, 0) * kPage, hb * a.hc * 2, bar_full);
+        }
+    } else {
+        // ================= consumer warps: one (worker, KV head, 16-row tile) each ==================
+        const int unit = warp / a.mt;
+        const int mtile = warp % a.mt;
+        const int my_slot = unit / a.hc;
+        const int head_in_cta = unit % a.hc;
+        const int w = blockIdx.x * a.pps + my_slot;
+        const long long x_begin = worker_begin(total_units, a.workers, w);
+        const long long x_end = worker_begin(total_units, a.workers, w + 1);
+        const size_t slot_rows = (size_t)a.hc * a.rows;
+        WarpState st;
+        uint32_t qf[8][4];
+        long long x = x_begin;
+        int j = 0; // pages this worker has consumed: stage = j % stages
+        bool live = true;
+        while (live && x < x_end) {
+            // ---- segment: the part of one (request, head block, query block) item in my range ---
+            const int h = (int)(x / total);
+            const int y = (int)(x % total);
+            const int r = owner_of(prefix, a.batch, y);
+            const int num_pages = prefix[r + 1] - prefix[r];
+            const int first_page = y - prefix[r];
+            const int seg_pages = (int)min((long long)(num_pages - first_page), x_end - x);
+            const int hb = h / a.qb, qb = h % a.qb;
+            const int kv_head = hb * a.hc + head_in_cta;
+            const int row0 = qb * rows_per_block + mtile * 16;
+            load_query_fragments(
+                a.query + ((size_t)r * a.qh + (size_t)kv_head * group + row0) * kHeadDim,
+                group - row0, lane, qf);
+            st.reset();
+            bool bad = false;
+            const int tail = ptail[r];
+            for (int p = 0; p < seg_pages; ++p, ++j) {
+                const int stage = j % a.stages;
+                const int round = j / a.stages;
+                const uint32_t bar_full = full0 + (stage * a.pps + my_slot) * 8;
+                const uint32_t bar_empty = empty0 + (stage * a.pps + my_slot) * 8;
+                const bool ok = mbar_wait(bar_full, round & 1);
+                if (__any_sync(0xffffffffu, !ok)) {
+                    if (lane == 0) *timeout_flag = 1;
+                    live = false;
+                    break;
+                }
+                bad |= bad_slot[stage * a.pps + my_slot] != 0;
+                uint8_t *slot_base = ring + stage * stage_bytes + my_slot * slot_bytes;
+                const int valid_tokens = first_page + p == num_pages - 1 ? tail : kPage;
+                const bool wrote =
+                    attend_page(slot_base + head_in_cta * 2 * kBoxBytes,
+                                slot_base + slot_bytes / 2 + head_in_cta * 2 * kBoxBytes,
+                                valid_tokens, qf, a.scale_log2, lane, st);
+                __syncwarp();
+                if (lane == 0) {
+                    if (wrote) fence_proxy_async();
+                    mbar_arrive(bar_empty);
+                }
+            }
+            if (!live) break;
+            st.finish_rows();
+            const bool complete = first_page == 0 && seg_pages == num_pages;
+            const int which = x == x_begin ? 0 : 1;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = mtile * 16 + (lane >> 2) + half * 8; // row within the query block
+                const int g = qb * rows_per_block + row;
+                if (g >= group) continue;
+                if (complete) {
+                    if (bad) continue; // the request keeps its previous output
+                    const size_t state = (size_t)r * a.qh + (size_t)kv_head * group + g;
+                    write_final_row(a.output + state * kHeadDim, a.lse + state, lane, half, st);
+                } else {
+                    float *slot = a.workspace +
+                                  (((size_t)w * 2 + which) * slot_rows +
+                                   (size_t)head_in_cta * a.rows + row) * kStateWidth;
+                    write_state_row(slot, lane, half, st, bad);
+                }
+            }
+            x += seg_pages;
+        }
+    }
+    __syncthreads();
+    if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);
+}
+
+// One warp per (request, query head): finds the workers whose ranges cut this head's item and
+// merges their states in worker order.  Items that one worker finished alone are skipped.
+__global__ void __launch_bounds__(128)
+balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
+                      int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
+                      int rows) {
+    const int lane = threadIdx.x & 31;
+    const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (state >= batch * qh) return;
+    const int request = state / qh, qhead = state % qh;
+    const size_t floats = (size_t)workers * 2 * hc * rows * kStateWidth;
+    const int *prefix = reinterpret_cast<const int *>(workspace + floats);
+    const int total = prefix[batch];
+    const int num_pages = prefix[request + 1] - prefix[request];
+    if (num_pages == 0) return; // invalid request: nothing was computed, nothing is published
+    const int group = qh / kvh;
+    const int kv_head = qhead / group, g = qhead % group;
+    const int rows_per_block = 16 * mt;
+    const int hb = kv_head / hc, head_in_cta = kv_head % hc;
+    const int qb = g / rows_per_block, row = g % rows_per_block;
+    const int items = (kvh / hc) * qblocks;
+    const long long total_units = (long long)total * items;
+    const long long start = (long long)(hb * qblocks + qb) * total + prefix[request];
+    const long long end = start + num_pages;
+    auto find = [&](long long x) {
+        int w = (int)(x * workers / total_units);
+        while (w + 1 < workers && worker_begin(total_units, workers, w + 1) <= x) ++w;
+        while (w > 0 && worker_begin(total_units, workers, w) > x) --w;
+        return w;
+    };
+    const int w0 = find(start), w1 = find(end - 1);
+    if (w0 == w1) return; // finished in place by the decode kernel
+    const size_t slot_rows = (size_t)hc * rows;
+    auto state_of = [&](int w) {
+        const int which = (w == w0 && worker_begin(total_units, workers, w0) != start) ? 1 : 0;
+        return workspace + (((size_t)w * 2 + which) * slot_rows +
+                            (size_t)head_in_cta * rows + row) * kStateWidth;
+    };
+    // workers between w0 and w1 whose range is empty (fewer units than workers) wrote nothing
+    merge_states(
+        [&](int i) -> const float * {
+            const int w = w0 + i;
+            if (worker_begin(total_units, workers, w) == worker_begin(total_units, workers, w + 1))
+                return nullptr;
+            return state_of(w);
+        },
+        w1 - w0 + 1, lane, output + (size_t)state * kHeadDim, lse + state);
+}
+
+int balanced_state_rows(const DecodeLaunch &launch) {
+    const int group = launch.qh / launch.kvh;
+    return group < 16 * launch.q_tiles ? group : 16 * launch.q_tiles;
+}
+
+} // namespace
+
+int configure_stream_kernels(size_t max_dynamic_shared) {
+    return cudaFuncSetAttribute(balanced_decode_kernel,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)max_dynamic_shared);
+}
+
+int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
+    StreamArgs args;
+    args.query = static_cast<const __nv_bfloat16 *>(launch.query);
+    args.indptr = launch.indptr;
+    args.indices = launch.indices;
+    args.last = launch.last;
+    args.output = static_cast<__nv_bfloat16 *>(launch.output);
+    args.lse = launch.lse;
+    args.workspace = launch.workspace;
+    args.status = launch.status;
+    args.batch = launch.batch;
+    args.max_pages = launch.max_pages;
+    args.qh = launch.qh;
+    args.kvh = launch.kvh;
+    args.indices_len = launch.indices_len;
+    args.hc = launch.heads_per_cta;
+    args.pps = launch.pages_per_stage;
+    args.mt = launch.q_tiles;
+    args.qb = launch.q_blocks;
+    args.stages = launch.stages;
+    args.workers = (int32_t)launch.grid * launch.pages_per_stage;
+    args.rows = balanced_state_rows(launch);
+    args.scale_log2 = launch.scale_log2;
+    CUtensorMap k_map, v_map;
+    memcpy(&k_map, launch.k_map, sizeof(k_map));
+    memcpy(&v_map, launch.v_map, sizeof(v_map));
+    balanced_decode_kernel<<<launch.grid, launch.block, launch.shared_bytes,
+                             static_cast<cudaStream_t>(stream)>>>(k_map, v_map, args);
+    return cudaGetLastError();
+}
+
+int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block,
+                          void *stream) {
+    balanced_merge_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        launch.workspace, static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.batch,
+        launch.qh, launch.kvh, launch.heads_per_cta, launch.q_tiles, launch.q_blocks,
+        (int)launch.grid * launch.pages_per_stage, balanced_state_rows(launch));
+    return cudaGetLastError();
+}
+
+} // namespace lb

@@ -47,6 +47,11 @@ struct AppendLaunch {
 
 // Each returns a CUDA error code (0 = success).
 int configure_decode_kernels(size_t max_dynamic_shared);
+int configure_stream_kernels(size_t max_dynamic_shared);
+// Balanced algorithm: launch.grid CTAs, launch.grid * pages_per_stage workers; launch.workspace
+// holds [workers][2][heads_per_cta * min(group, 16 * q_tiles)][130] floats, then batch + 1 ints.
+int launch_balanced_decode(const DecodeLaunch &launch, void *stream);
+int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block, void *stream);
 int launch_paged_decode(const DecodeLaunch &launch, void *stream);
 int launch_split_merge(const MergeLaunch &launch, void *stream);
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency);

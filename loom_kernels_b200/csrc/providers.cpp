@@ -73,7 +73,7 @@ lb_status load_device(int device, int *sm_count, size_t *smem_optin) {
 }
 
 void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
-    info->algorithm = c.partitions > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+    info->algorithm = (int32_t)c.algorithm;
     info->partitions = c.partitions;
     info->heads_per_cta = c.heads_per_cta;
     info->q_tiles = c.q_tiles;
@@ -85,7 +85,7 @@ void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
     info->shared_bytes = c.shared_bytes;
     info->merge_grid = c.merge_grid;
     info->merge_block = c.merge_block;
-    info->commands = c.partitions > 1 ? 2 : 1;
+    info->commands = c.algorithm == LB_DECODE_DIRECT ? 1 : 2;
     info->workspace_numel = c.workspace_numel;
     info->workspace_bytes = c.workspace_numel * sizeof(float);
 }
@@ -183,7 +183,8 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     if (!plan || !scope || !args) return fail(LB_INVALID_ARGUMENT, "plan");
     const lb_paged_spec &spec = plan->spec;
     const DecodeChoice &c = plan->choice;
-    const bool split = c.partitions > 1;
+    const bool balanced = c.algorithm == LB_DECODE_BALANCED;
+    const bool split = c.algorithm != LB_DECODE_DIRECT; // two commands and a workspace
     if (scope->queue->device != plan->device)
         return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
     // both commands of a split plan must fit before anything is launched (decode.rs:1327)
@@ -260,7 +261,10 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     launch.block = c.block;
     launch.shared_bytes = c.shared_bytes;
     void *stream = scope->queue->stream;
-    if ((rc = submit_launch(*scope, [&]() { return launch_paged_decode(launch, stream); })))
+    if ((rc = submit_launch(*scope, [&]() {
+             return balanced ? launch_balanced_decode(launch, stream)
+                             : launch_paged_decode(launch, stream);
+         })))
         return rc;
     if (!split) return LB_OK;
 
@@ -273,6 +277,10 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     Operand merge_op[3];
     if ((rc = require_command_capacity(*scope, 1))) return rc;
     if ((rc = resolve(*scope, merge_requests, 3, merge_op))) return rc;
+    if (balanced)
+        return submit_launch(*scope, [&]() {
+            return launch_balanced_merge(launch, c.merge_grid, c.merge_block, stream);
+        });
     MergeLaunch merge;
     merge.workspace = (const float *)merge_op[0].ptr;
     merge.output = merge_op[1].ptr;

@@ -44,6 +44,13 @@ def test_reference_gate_cases(oracle, provider, name, partitions):
                       partitions=partitions, provider=provider)
     out, lse = run.run()
     assert run.submitted == (1 if partitions == 1 else 2)
+    if partitions == 1:  # and once more through the heuristic's choice for this shape
+        auto = H.DecodeRun(spec, q, k, v, case["indptr"], case["indices"], case["last"],
+                           provider=provider)
+        out2, lse2 = auto.run()
+        eo2, el2 = oracle.paged_decode(oracle.paged_spec(batch, pages, qh, kvh), q, k, v,
+                                       case["indptr"], case["indices"], case["last"])
+        H.check_decode(out2, lse2, eo2, el2, lse_limit=H.SPLIT_LSE_MAX_ABS, gate=True)
     ospec = oracle.paged_spec(batch, pages, qh, kvh)
     eo, el = oracle.paged_decode(ospec, q, k, v, case["indptr"], case["indices"], case["last"])
     assert f"{oracle.digest_bf16(eo):016x}" == case["output"]  # the checker is the pinned one
@@ -112,6 +119,16 @@ SHAPES = [
 
 @pytest.mark.parametrize("batch,qh,kvh,hc,partitions", SHAPES)
 def test_random_ragged_batches(oracle, provider, batch, qh, kvh, hc, partitions):
+    ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced=2)
+
+
+@pytest.mark.parametrize("batch,qh,kvh,hc,partitions", SHAPES)
+def test_random_ragged_batches_balanced(oracle, provider, batch, qh, kvh, hc, partitions):
+    # the same batches through the page-balanced algorithm (pages cut evenly over the SMs)
+    ragged_case(oracle, provider, batch, qh, kvh, hc, 0, balanced=1)
+
+
+def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced):
     rng = np.random.default_rng(batch * 1000 + qh * 10 + kvh + hc + partitions)
     pool = 96
     kv_lens = rng.integers(1, 16 * 18, size=batch)
@@ -130,11 +147,41 @@ def test_random_ragged_batches(oracle, provider, batch, qh, kvh, hc, partitions)
         vr[page, last[r]:] = 0x7FC0
     q = H.normal_bf16(rng, spec.query_numel())
     run = H.DecodeRun(spec, q, k, v, indptr, indices, last, partitions=partitions,
-                      heads_per_cta=hc, provider=provider)
+                      heads_per_cta=hc, provider=provider, balanced=balanced)
+    if balanced == 1:
+        assert run.plan.algorithm() == lk.Bf16PagedBatchDecodeAlgorithm.Balanced
     out, lse = run.run()
+    assert run.submitted == run.plan.commands()
     ospec = oracle.paged_spec(batch, pool, qh, kvh)
     eo, el = oracle.paged_decode(ospec, q, k, v, indptr, indices, last, threads=4)
     H.check_decode(out, lse, eo, el, lse_limit=H.SPLIT_LSE_MAX_ABS)
+
+
+def test_balanced_guards_keep_sentinels(provider):
+    # the page-balanced algorithm keeps the reference's device guards: an out-of-range page or
+    # a bad last_page_len leaves that request (and only it) unwritten
+    spec = lk.Bf16PagedBatchDecodeSpec.new(2, 2, 4, 2)
+    zeros = np.zeros(spec.kv_pages_numel(), np.uint16)
+    run = H.DecodeRun(spec, np.zeros(spec.query_numel(), np.uint16), zeros, zeros, [0, 1, 2],
+                      [0, 2], [16, 16], provider=provider, balanced=1)
+    out, lse = run.run()
+    o = H.bits_to_f32(out).reshape(2, -1)
+    assert np.all(o[0] == 0.0) and np.all(lse[:4] == 4.0)
+    assert np.all(np.isnan(o[1])) and np.all(np.isnan(lse[4:]))
+    spec = lk.Bf16PagedBatchDecodeSpec.new(3, 64, 8, 2)
+    rng = np.random.default_rng(8)
+    k, v = H.normal_bf16(rng, spec.kv_pages_numel()), H.normal_bf16(rng, spec.kv_pages_numel())
+    q = H.normal_bf16(rng, spec.query_numel())
+    indptr, indices, last = H.make_page_table(rng, [300, 200, 150], 64)
+    indices = indices.copy()
+    indices[indptr[1] + 5] = 64  # request 1 names a page outside the pool, mid-way
+    last = last.copy()
+    last[2] = 17                 # request 2 has an impossible last page length
+    run = H.DecodeRun(spec, q, k, v, indptr, indices, last, provider=provider, balanced=1)
+    out, lse = run.run()
+    o = H.bits_to_f32(out).reshape(3, -1)
+    assert np.all(np.isfinite(o[0])) and np.all(np.isnan(o[1])) and np.all(np.isnan(o[2]))
+    assert np.all(np.isfinite(lse[:8])) and np.all(np.isnan(lse[8:]))
 
 
 def test_split_k_states_match_the_partial_state_contract(oracle, provider):
@@ -226,9 +273,9 @@ def test_large_logits_and_outlier_token(oracle, provider):
     q = H.normal_bf16(rng, spec.query_numel())
     ospec = oracle.paged_spec(batch, pool, qh, kvh)
     eo, el = oracle.paged_decode(ospec, q, k, v, indptr, indices, last, threads=8)
-    for partitions in (1, 16):
+    for partitions, balanced in ((1, 0), (16, 0), (0, 1)):
         run = H.DecodeRun(spec, q, k, v, indptr, indices, last, partitions=partitions,
-                          provider=provider)
+                          provider=provider, balanced=balanced)
         out, lse = run.run()
         H.check_decode(out, lse, eo, el, lse_limit=H.SPLIT_LSE_MAX_ABS)
 

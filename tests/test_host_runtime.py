@@ -130,14 +130,21 @@ def test_split_contract_pieces():
 
 
 def test_plan_heuristic_is_fixed_by_spec_and_device():
-    c3 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148)
+    c3 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148,
+                                partitions=1)
     assert (c3.partitions, c3.algorithm, c3.commands, c3.workspace_numel) == (1, 0, 1, 0)
     assert c3.grid == 64 * (8 // c3.heads_per_cta) and c3.block == 288
+    # left to itself the plan cuts a batch smaller than the device by pages, one CTA per SM
+    auto = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148)
+    assert (auto.algorithm, auto.commands, auto.grid, auto.heads_per_cta) == (2, 2, 148, 8)
+    assert auto.workspace_numel == 148 * 2 * 8 * 4 * 130 + 64 + 2
+    many = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(4096, 65536, 32, 8), 148)
+    assert (many.algorithm, many.commands) == (0, 1)  # thousands of requests tile the device
     c4 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(8, 20000, 64, 8), 148,
                                 partitions=16)
     assert (c4.partitions, c4.algorithm, c4.commands) == (16, 1, 2)
     assert c4.workspace_numel == 8 * 64 * 16 * 130 and c4.merge_grid == 8 * 64 // 4
-    c1 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(1, 256, 32, 32), 148)
+    c1 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(1, 256, 32, 32), 148, balanced=2)
     assert c1.partitions > 1 and c1.grid >= 64  # one request cannot fill 148 SMs unsplit
     mqa = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(256, 65536, 32, 1), 148)
     assert mqa.q_tiles == 2 and mqa.heads_per_cta == 1  # group 32 = two 16-row MMA tiles
@@ -147,7 +154,7 @@ def test_plan_heuristic_is_fixed_by_spec_and_device():
         lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(2, 64, 8, 2), 148, heads_per_cta=8)
     # same inputs, same plan
     again = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148)
-    assert (again.heads_per_cta, again.grid, again.stages) == (c3.heads_per_cta, c3.grid, c3.stages)
+    assert (again.heads_per_cta, again.grid, again.stages) == (auto.heads_per_cta, auto.grid, auto.stages)
 
 
 # ---- command runtime against the fake driver ---------------------------------------------------
@@ -200,7 +207,7 @@ def test_queue_and_binding_errors(fake):
 def test_decode_enqueue_preflight_and_resolution(fake):
     spec = lk.Bf16PagedBatchDecodeSpec.new(4, 8, 16, 4)
     provider = lk.DecodeProvider.load(0)
-    plan = provider.plan_bf16_paged_batch(spec)
+    plan = provider.plan_bf16_paged_batch(spec, partitions=1)
     queue = lk.CommandQueue(0x100, 2)
 
     def args(h, out, lse, **override):
