@@ -76,6 +76,16 @@ def _check(status: int):
         _raise(status)
 
 
+def _dispose(owner, symbol: str):
+    """Hand `owner._ptr` to the library's destroy/abandon entry point exactly once.  At interpreter
+    exit module globals are already cleared, and the process is about to release everything."""
+    ptr = getattr(owner, "_ptr", None)
+    owner._ptr = None
+    load = getattr(_abi, "load", None)
+    if ptr and load is not None:
+        getattr(load(), symbol)(ptr)
+
+
 def _i32(values):
     array = np.ascontiguousarray(values, dtype=np.int32)
     return array, array.ctypes.data_as(ctypes.POINTER(c_int32)), c_size_t(array.size)
@@ -335,9 +345,7 @@ class CheckedBindings:
         self._buffers = {}
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_bindings_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_bindings_destroy")
 
     def _release(self):
         ptr, self._ptr = self._ptr, None
@@ -377,9 +385,7 @@ class CommandQueue:
         self._ptr = out.value
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_queue_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_queue_destroy")
 
     def stream(self): return self._stream_owner
     def max_commands(self): return _abi.load().lb_queue_max_commands(self._ptr)
@@ -411,9 +417,7 @@ class CommandScope:
         self._queue, self._ptr, self._buffers = queue, ptr, buffers
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_scope_abandon(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_scope_abandon")
 
     def submitted_commands(self): return _abi.load().lb_scope_submitted(self._ptr)
 
@@ -431,9 +435,7 @@ class CommandCompletion:
         self._queue, self._ptr, self._buffers = queue, ptr, buffers
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_completion_abandon(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_completion_abandon")
 
     def submitted(self): return _abi.load().lb_completion_submitted(self._ptr)
 
@@ -487,9 +489,7 @@ class DecodeProvider:
         return cls(out.value, device)
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_decode_provider_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_decode_provider_destroy")
 
     def device_status(self) -> int:
         out = c_int32()
@@ -531,9 +531,7 @@ class Bf16PagedBatchDecodePlan:
                                                          byref(self._info)))
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_paged_decode_plan_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_paged_decode_plan_destroy")
 
     def spec(self): return Bf16PagedBatchDecodeSpec(self._spec)
     def algorithm(self): return self._info.algorithm
@@ -625,9 +623,7 @@ class RopeProvider:
         return cls(out.value)
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_rope_provider_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_rope_provider_destroy")
 
     def plan_bf16_paged_append(self, spec: Bf16RopePagedKvAppendSpec):
         out = c_void_p()
@@ -649,9 +645,7 @@ class _AppendPlan:
         _check(_abi.load().lb_rope_append_plan_info_get(ptr, byref(self._info)))
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_rope_append_plan_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_rope_append_plan_destroy")
 
     def spec(self): return self._spec
     def info(self): return self._info
@@ -695,9 +689,7 @@ class GraphQueue:
         self._ptr = out.value
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_graph_queue_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_graph_queue_destroy")
 
     def bindings(self, capacity: int) -> CheckedBindings:
         out = c_void_p()
@@ -743,9 +735,7 @@ class CapturedGraph:
         self._ptr, self._buffers = ptr, buffers
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_captured_graph_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_captured_graph_destroy")
 
     def commands(self): return _abi.load().lb_captured_graph_commands(self._ptr)
 
@@ -763,9 +753,7 @@ class GraphExec:
         self._ptr, self._buffers = ptr, buffers
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_graph_exec_destroy(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_graph_exec_destroy")
 
     def commands(self): return _abi.load().lb_graph_exec_commands(self._ptr)
     def launches(self): return _abi.load().lb_graph_exec_launches(self._ptr)
@@ -796,9 +784,7 @@ class GraphLaunchCompletion:
         self._ptr, self._exec = ptr, exec_
 
     def __del__(self):
-        if getattr(self, "_ptr", None):
-            _abi.load().lb_graph_completion_abandon(self._ptr)
-            self._ptr = None
+        _dispose(self, "lb_graph_completion_abandon")
 
     def launch_index(self): return _abi.load().lb_graph_completion_launch_index(self._ptr)
 

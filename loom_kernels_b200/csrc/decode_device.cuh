@@ -271,8 +271,11 @@ __device__ __forceinline__ void write_state_row(float *state, int lane, int half
 // single_decode_bf16_split_k_merge_reference (crates/loom-infer/src/attention/single_decode/
 // mod.rs:343-379), evaluated against the global maximum so that the state loads are independent
 // and pipeline instead of forming one dependent chain per state.
+// `publish` is consulted only after every load has been issued, so a caller can hand in a
+// predicate that itself depends on loads still in flight (the request guard) without putting a
+// second memory round trip in front of the state loads.
 template <typename StateOf>
-__device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane,
+__device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, bool publish,
                                              __nv_bfloat16 *out_row, float *lse_slot) {
     float top = -INFINITY;
     bool poisoned = false;
@@ -302,12 +305,39 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane,
         acc.z += hi.x * weight;
         acc.w += hi.y * weight;
     }
+    if (!publish) return;
     uint2 packed;
     packed.x = pack_bf16(acc.x / norm, acc.y / norm);
     packed.y = pack_bf16(acc.z / norm, acc.w / norm);
     *reinterpret_cast<uint2 *>(out_row + lane * 4) = packed;
     if (lane == 0) *lse_slot = top + log2f(norm);
 }
+
+// The even cut of `total` units over `workers` workers, evaluated without 64-bit division:
+// begin(w) = floor(total * w / workers) = q * w + floor(r * w / workers) with total = q *
+// workers + r.  Fewer workers than `max_workers` are used when there is little work, so that a
+// worker never gets less than kMinUnitsPerWorker pages (fewer states to merge).
+constexpr int kMinUnitsPerWorker = 4;
+struct EvenCut {
+    long long q;
+    int r, workers;
+    __device__ __forceinline__ EvenCut(long long total, int max_workers) {
+        const long long wanted = total / kMinUnitsPerWorker;
+        workers = wanted >= max_workers ? max_workers : (wanted < 1 ? 1 : (int)wanted);
+        q = total / workers;
+        r = (int)(total - q * workers);
+    }
+    __device__ __forceinline__ long long begin(int w) const {
+        return q * w + (long long)((unsigned)r * (unsigned)w / (unsigned)workers);
+    }
+    // the worker whose range [begin(w), begin(w + 1)) contains x
+    __device__ __forceinline__ int owner(long long x) const {
+        int w = (int)(x / q); // every worker holds at least q >= 1 units, so this is an upper bound
+        if (w >= workers) w = workers - 1;
+        while (begin(w) > x) --w;
+        return w;
+    }
+};
 
 } // namespace dev
 } // namespace lb

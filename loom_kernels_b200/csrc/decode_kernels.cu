@@ -291,12 +291,12 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
     const int request = state / qh;
+    // the guard's loads and the state loads travel together; the verdict is used at the end
     int page_start, page_end, tail;
-    if (!request_metadata_valid(indptr, last, batch, indices_len, request, page_start, page_end,
-                                tail))
-        return;
+    const bool valid = request_metadata_valid(indptr, last, batch, indices_len, request,
+                                              page_start, page_end, tail);
     const float *st = workspace + (size_t)state * partitions * kStateWidth;
-    merge_states([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane,
+    merge_states([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane, valid,
                  output + (size_t)state * kHeadDim, lse + state);
 }
 

@@ -44,8 +44,8 @@ struct StreamArgs {
     float scale_log2;
 };
 
-__device__ __forceinline__ size_t state_floats(const StreamArgs &a) {
-    return (size_t)a.workers * 2 * a.hc * a.rows * kStateWidth;
+__device__ __forceinline__ size_t state_floats(int workers, int hc, int rows) {
+    return (size_t)workers * 2 * hc * rows * kStateWidth;
 }
 
 // first index i in [0, n] with prefix[i] > y, minus one: the request that owns page y
@@ -57,10 +57,6 @@ __device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
         else hi = mid;
     }
     return lo;
-}
-
-__device__ __forceinline__ long long worker_begin(long long total_units, int workers, int w) {
-    return total_units * w / workers;
 }
 
 __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
@@ -129,13 +125,16 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
     const int items = head_blocks * a.qb;
-    const long long total_units = (long long)total * items;
     if (blockIdx.x == 0) {
         // the merge kernel reads the same prefix
-        int *out_prefix = reinterpret_cast<int *>(a.workspace + state_floats(a));
+        int *out_prefix =
+            reinterpret_cast<int *>(a.workspace + state_floats(a.workers, a.hc, a.rows));
         for (int i = tid; i <= a.batch; i += blockDim.x) out_prefix[i] = prefix[i];
     }
     if (total == 0) return;
+    // little work uses fewer workers; a CTA none of whose page slots is a worker leaves at once
+    const EvenCut cut((long long)total * items, a.workers);
+    if ((int)blockIdx.x * a.pps >= cut.workers) return;
 
     const int rows_per_block = 16 * a.mt;
 
@@ -150,28 +149,33 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             prefetch_tensormap(&v_map);
         }
         // per worker of this CTA: range, and a 32-page window of (page id, head block) pairs
-        long long begin[8], count[8];
+        // (the range starts at page y0 of item h0; one 64-bit division per worker, none per page)
+        int h0[8], y0[8], count[8];
         int win_id[8], win_hb[8], next_id[8], next_hb[8];
         int longest = 0;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            begin[s] = 0;
+            h0[s] = 0;
+            y0[s] = 0;
             count[s] = 0;
-            if (s < a.pps) {
-                const int w = blockIdx.x * a.pps + s;
-                begin[s] = worker_begin(total_units, a.workers, w);
-                count[s] = worker_begin(total_units, a.workers, w + 1) - begin[s];
-                longest = max(longest, (int)count[s]);
+            const int w = blockIdx.x * a.pps + s;
+            if (s < a.pps && w < cut.workers) {
+                const long long begin = cut.begin(w);
+                h0[s] = (int)(begin / total);
+                y0[s] = (int)(begin - (long long)h0[s] * total);
+                count[s] = (int)(cut.begin(w + 1) - begin);
+                longest = max(longest, count[s]);
             }
         }
         auto load_window = [&](int s, int first, int &id_out, int &hb_out) {
             id_out = 0;
             hb_out = 0;
-            const long long j = (long long)first + lane;
+            const int j = first + lane;
             if (j >= count[s]) return;
-            const long long x = begin[s] + j;
-            const int h = (int)(x / total);
-            const int y = (int)(x % total);
+            const unsigned pos = (unsigned)y0[s] + (unsigned)j; // < 2 * total: one wrap at most...
+            const int wraps = (int)(pos / (unsigned)total);     // ...unless the item line is short
+            const int h = h0[s] + wraps;
+            const int y = (int)(pos - (unsigned)wraps * (unsigned)total);
             const int r = owner_of(prefix, a.batch, y);
             const int id = a.indices[pstart[r] + (y - prefix[r])];
             hb_out = h / a.qb;
@@ -194,7 +198,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     }
             }
             int page_id = 0, hb = 0;
-            long long my_count = 0;
+            int my_count = 0;
 #pragma unroll
             for (int s = 0; s < 8; ++s)
                 if (s < a.pps) {
@@ -234,22 +238,25 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         const int my_slot = unit / a.hc;
         const int head_in_cta = unit % a.hc;
         const int w = blockIdx.x * a.pps + my_slot;
-        const long long x_begin = worker_begin(total_units, a.workers, w);
-        const long long x_end = worker_begin(total_units, a.workers, w + 1);
         const size_t slot_rows = (size_t)a.hc * a.rows;
         WarpState st;
         uint32_t qf[8][4];
-        long long x = x_begin;
+        int h = 0, y = 0, remaining = 0;
+        if (w < cut.workers) {
+            const long long begin = cut.begin(w);
+            h = (int)(begin / total);
+            y = (int)(begin - (long long)h * total);
+            remaining = (int)(cut.begin(w + 1) - begin);
+        }
+        bool first_segment = true;
         int j = 0; // pages this worker has consumed: stage = j % stages
         bool live = true;
-        while (live && x < x_end) {
+        while (live && remaining > 0) {
             // ---- segment: the part of one (request, head block, query block) item in my range ---
-            const int h = (int)(x / total);
-            const int y = (int)(x % total);
             const int r = owner_of(prefix, a.batch, y);
             const int num_pages = prefix[r + 1] - prefix[r];
             const int first_page = y - prefix[r];
-            const int seg_pages = (int)min((long long)(num_pages - first_page), x_end - x);
+            const int seg_pages = min(num_pages - first_page, remaining);
             const int hb = h / a.qb, qb = h % a.qb;
             const int kv_head = hb * a.hc + head_in_cta;
             const int row0 = qb * rows_per_block + mtile * 16;
@@ -286,7 +293,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             if (!live) break;
             st.finish_rows();
             const bool complete = first_page == 0 && seg_pages == num_pages;
-            const int which = x == x_begin ? 0 : 1;
+            const int which = first_segment ? 0 : 1;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = mtile * 16 + (lane >> 2) + half * 8; // row within the query block
@@ -303,7 +310,13 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     write_state_row(slot, lane, half, st, bad);
                 }
             }
-            x += seg_pages;
+            first_segment = false;
+            remaining -= seg_pages;
+            y += seg_pages;
+            if (y == total) { // the next head block starts again at the first request
+                y = 0;
+                ++h;
+            }
         }
     }
     __syncthreads();
@@ -320,10 +333,11 @@ balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
     const int request = state / qh, qhead = state % qh;
-    const size_t floats = (size_t)workers * 2 * hc * rows * kStateWidth;
-    const int *prefix = reinterpret_cast<const int *>(workspace + floats);
-    const int total = prefix[batch];
-    const int num_pages = prefix[request + 1] - prefix[request];
+    const int *prefix =
+        reinterpret_cast<const int *>(workspace + state_floats(workers, hc, rows));
+    const int total = __ldg(prefix + batch); // three independent loads, issued together
+    const int page0 = __ldg(prefix + request);
+    const int num_pages = __ldg(prefix + request + 1) - page0;
     if (num_pages == 0) return; // invalid request: nothing was computed, nothing is published
     const int group = qh / kvh;
     const int kv_head = qhead / group, g = qhead % group;
@@ -331,32 +345,21 @@ balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output
     const int hb = kv_head / hc, head_in_cta = kv_head % hc;
     const int qb = g / rows_per_block, row = g % rows_per_block;
     const int items = (kvh / hc) * qblocks;
-    const long long total_units = (long long)total * items;
-    const long long start = (long long)(hb * qblocks + qb) * total + prefix[request];
-    const long long end = start + num_pages;
-    auto find = [&](long long x) {
-        int w = (int)(x * workers / total_units);
-        while (w + 1 < workers && worker_begin(total_units, workers, w + 1) <= x) ++w;
-        while (w > 0 && worker_begin(total_units, workers, w) > x) --w;
-        return w;
-    };
-    const int w0 = find(start), w1 = find(end - 1);
+    const EvenCut cut((long long)total * items, workers);
+    const long long start = (long long)(hb * qblocks + qb) * total + page0;
+    const int w0 = cut.owner(start), w1 = cut.owner(start + num_pages - 1);
     if (w0 == w1) return; // finished in place by the decode kernel
-    const size_t slot_rows = (size_t)hc * rows;
-    auto state_of = [&](int w) {
-        const int which = (w == w0 && worker_begin(total_units, workers, w0) != start) ? 1 : 0;
-        return workspace + (((size_t)w * 2 + which) * slot_rows +
-                            (size_t)head_in_cta * rows + row) * kStateWidth;
-    };
-    // workers between w0 and w1 whose range is empty (fewer units than workers) wrote nothing
+    // every worker in [w0, w1] holds pages of this item (a worker is never empty); all but the
+    // first begin inside the item and used slot 0
+    const int first_slot = cut.begin(w0) != start ? 1 : 0;
+    const size_t slot_stride = (size_t)hc * rows * kStateWidth;
+    const float *base = workspace + (size_t)w0 * 2 * slot_stride +
+                        ((size_t)head_in_cta * rows + row) * kStateWidth;
     merge_states(
         [&](int i) -> const float * {
-            const int w = w0 + i;
-            if (worker_begin(total_units, workers, w) == worker_begin(total_units, workers, w + 1))
-                return nullptr;
-            return state_of(w);
+            return base + ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
         },
-        w1 - w0 + 1, lane, output + (size_t)state * kHeadDim, lse + state);
+        w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim, lse + state);
 }
 
 int balanced_state_rows(const DecodeLaunch &launch) {
