@@ -1,14 +1,16 @@
 #!/usr/bin/env python
 """Benchmark of the paged-decode hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c3|c1|c4|c5]
 
 One step = one paged decode call over one batch of seeded synthetic input.  At N=1 the workload is
 batch-64 GQA4 32/8-head decode at context 4096 with pages scattered in a 20000-page pool, direct
 (non-split) path -- the configuration the headline target is quoted on.  With N GPUs every rank
 owns its own shard of requests and of the paged KV cache (same per-GPU shape, weak scaling); the
 decode path has no exchange step, so the timed region contains no collective.  The optional
-all-gather of output rows is timed separately and reported under "allgather".
+all-gather of output rows is timed separately and reported under "allgather".  `--workload c5`
+is the strong-scaling case instead: one ragged 512-request MQA + GQA4 batch split over the ranks.
 
 `value` is aggregate algorithmic bytes per second with inputs resident in HBM; `e2e` is the same
 metric through the public API with host buffers (pinned host -> device copy of the step's Q and
@@ -319,7 +321,8 @@ def ours(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w.name, "per_gpu_batch": w.batch, "global_batch": w.batch * world,
                        "partitioning": "by request, one KV shard per GPU, no collective",
-                       "algorithm": "direct" if info.partitions == 1 else f"split-K x{info.partitions}",
+                       "algorithm": {0: "direct", 1: f"split-K x{info.partitions}",
+                                     2: "balanced"}.get(info.algorithm, str(info.algorithm)),
                        "heads_per_cta": info.heads_per_cta, "grid": info.grid,
                        "l2": f"inputs ({w.algorithmic_bytes() / 2**20:.0f} MiB per GPU per step) "
                              "exceed the 126 MB L2; no flush needed"},
@@ -347,13 +350,209 @@ def ours(args):
         dist.destroy_process_group()
 
 
+class RaggedJob:
+    """One KV-head family of the ragged mixed batch on one rank: workload, plan and device buffers."""
+
+    def __init__(self, lk, torch, provider, label, qh, kvh, kv_lens, seed, device):
+        from loom_kernels_b200 import workloads
+        self.label = label
+        self.w = w = workloads.decode_workload(f"C5 {label}", len(kv_lens), qh, kvh, kv_lens, 65536,
+                                               seed, with_values=False)
+        w.query = workloads.normal_bf16(np.random.default_rng(seed + 1), w.batch * qh * 128)
+        self.spec = lk.Bf16PagedBatchDecodeSpec.new(w.batch, w.max_pages, qh, kvh)
+        self.plan = provider.plan_bf16_paged_batch(self.spec)
+        self.info = self.plan.info()
+        generator = torch.Generator(device=device).manual_seed(seed)
+        pool = w.max_pages * 16 * kvh * 128
+        self.k = torch.randn(pool, dtype=torch.bfloat16, device=device, generator=generator)
+        self.v = torch.randn(pool, dtype=torch.bfloat16, device=device, generator=generator)
+        self.host = {"q": torch.from_numpy(w.query.view(np.int16)).pin_memory(),
+                     "indptr": torch.from_numpy(w.indptr).pin_memory(),
+                     "indices": torch.from_numpy(w.indices).pin_memory(),
+                     "last": torch.from_numpy(w.last).pin_memory()}
+        self.dev = {name: t.to(device) for name, t in self.host.items()}
+        self.out = torch.zeros(self.spec.output_numel(), dtype=torch.bfloat16, device=device)
+        self.lse = torch.zeros(self.spec.lse_numel(), dtype=torch.float32, device=device)
+        numel = self.plan.workspace_required_numel()
+        self.workspace = torch.zeros(numel, dtype=torch.float32, device=device) if numel else None
+        self.out_host = torch.empty(self.out.numel(), dtype=torch.bfloat16).pin_memory()
+        self.lse_host = torch.empty(self.lse.numel(), dtype=torch.float32).pin_memory()
+        self.args = None
+
+    def bind(self, lk, torch, bindings):
+        reads = [bindings.bind_read(t) for t in
+                 (self.dev["q"].view(torch.bfloat16), self.k, self.v, self.dev["indptr"],
+                  self.dev["indices"], self.dev["last"])]
+        out, lse = bindings.bind_read_write(self.out), bindings.bind_read_write(self.lse)
+        ws = bindings.bind_read_write(self.workspace) if self.workspace is not None else None
+        self.args = lk.Bf16PagedBatchDecodeArgs(*reads, out.write(), lse.write(), ws)
+
+    def algorithm(self):
+        names = {0: "direct", 1: f"split-K x{self.info.partitions}", 2: "balanced"}
+        return (f"{names.get(self.info.algorithm, self.info.algorithm)} hc{self.info.heads_per_cta} "
+                f"grid{self.info.grid}")
+
+    def h2d(self):
+        for name, host in self.host.items():
+            self.dev[name].copy_(host, non_blocking=True)
+
+    def d2h(self):
+        self.out_host.copy_(self.out, non_blocking=True)
+        self.lse_host.copy_(self.lse, non_blocking=True)
+
+    def io_bytes(self):
+        h2d = sum(t.numel() * t.element_size() for t in self.host.values())
+        return h2d, self.out_host.numel() * 2 + self.lse_host.numel() * 4
+
+
+def ragged_c5(args):
+    """Strong scaling on the ragged mixed batch: 512 requests with log-uniform contexts 128..16384,
+    256 MQA (32/1) + 256 GQA4 (32/8), assigned to the ranks by KV bytes; every rank runs its MQA
+    shard and its GQA4 shard as two decode calls on one stream.  No collective in the step."""
+    import torch
+    import torch.distributed as dist
+
+    import loom_kernels_b200 as lk
+    from loom_kernels_b200 import sharding, workloads
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    provider = lk.DecodeProvider.load(local_rank)
+    lens = workloads.c5_lengths(512)
+    jobs = []
+    for index, (label, qh, kvh, family) in enumerate((("MQA 32/1", 32, 1, lens[:256]),
+                                                      ("GQA4 32/8", 32, 8, lens[256:]))):
+        owned = sharding.balanced_assignment(family, world)[rank]
+        jobs.append(RaggedJob(lk, torch, provider, label, qh, kvh, family[owned],
+                              0xC5 + 64 * index + rank, device))
+    commands = sum(job.plan.commands() for job in jobs)
+    stream = torch.cuda.Stream(device=device)
+    queue = lk.CommandQueue(stream, max(8, commands * max(args.steps, args.warmup)))
+    bindings = queue.bindings(9 * len(jobs))
+    for job in jobs:
+        job.bind(lk, torch, bindings)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def timed(selected, steps, bindings):
+        """`steps` back-to-back steps of the selected jobs in one scope; ms on the device."""
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            start.record(stream)
+            scope = queue.begin(bindings)
+            for _ in range(steps):
+                for job in selected:
+                    job.plan.enqueue_into(scope, job.args)
+            end.record(stream)
+            bindings = scope.finish().wait()
+        torch.cuda.synchronize(device)
+        return start.elapsed_time(end), bindings
+
+    _, bindings = timed(jobs, args.warmup, bindings)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    step_ms, bindings = timed(jobs, args.steps, bindings)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    family_ms = []
+    for job in jobs:
+        ms, bindings = timed([job], args.steps, bindings)
+        family_ms.append(ms / args.steps)
+    if provider.device_status() != 0:
+        raise SystemExit("a decode kernel gave up on a bounded wait; the numbers are invalid")
+
+    def e2e_step(bindings):
+        with torch.cuda.stream(stream):
+            for job in jobs:
+                job.h2d()
+            scope = queue.begin(bindings)
+            for job in jobs:
+                job.plan.enqueue_into(scope, job.args)
+            bindings = scope.finish().wait()
+            for job in jobs:
+                job.d2h()
+            stream.synchronize()
+        return bindings
+
+    for _ in range(3):
+        bindings = e2e_step(bindings)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+    for _ in range(args.steps):
+        bindings = e2e_step(bindings)
+    with torch.cuda.stream(stream):
+        e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    rank_bytes = [job.w.algorithmic_bytes() for job in jobs]
+    times = torch.tensor([step_ms, e2e_ms] + family_ms, dtype=torch.float64, device=device)
+    totals = torch.tensor([float(sum(rank_bytes))] + [float(b) for b in rank_bytes],
+                          dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    times, totals = times.tolist(), totals.tolist()
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        step_s = times[0] / 1e3 / args.steps
+        gqa = jobs[1]
+        gqa_s = family_ms[1] / 1e3
+        achieved = rank_bytes[1] / gqa_s / 1e9
+        h2d, d2h = (sum(x) for x in zip(*(job.io_bytes() for job in jobs)))
+        line = {
+            "metric": METRIC, "value": totals[0] / step_s / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "C5 ragged mixed decode: 256 MQA 32/1 + 256 GQA4 32/8 requests, "
+                                   "contexts log-uniform 128..16384, 65536-page pool per GPU and family",
+                       "partitioning": "by request, longest-first by KV bytes; no collective",
+                       "requests_on_rank0": [job.w.batch for job in jobs],
+                       "algorithms_on_rank0": [job.algorithm() for job in jobs],
+                       "family_us_max_over_ranks": [1e3 * t for t in times[2:]],
+                       "family_GBs_whole_job": [totals[1 + i] / (times[2 + i] / 1e3) / 1e9
+                                                for i in range(len(jobs))],
+                       "l2": "each family's pages exceed the 126 MB L2 at every N measured; no flush"},
+            "us_per_call": step_s * 1e6, "tokens_per_s": 512 / step_s,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
+                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "algorithmic_bytes_per_launch": rank_bytes[1],
+                         "kernel": f"rank 0 GQA4 shard, all commands of the call ({gqa.algorithm()})"},
+            "e2e": {"value": totals[0] / (times[1] / 1e3 / args.steps) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "us_per_call": times[1] * 1e3 / args.steps},
+            "gpu_launches": args.steps * commands, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="c3", choices=["c1", "c3", "c4"])
+    parser.add_argument("--workload", default="c3", choices=["c1", "c3", "c4", "c5"])
     parser.add_argument("--reference-requests", type=int, default=16)
     parser.add_argument("--batch", type=int, default=64,
                         help="requests per GPU for the c3 workload (64 = the headline shape; "
@@ -363,6 +562,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         reference_arm(args)
+    elif args.workload == "c5":
+        ragged_c5(args)
     else:
         ours(args)
 

@@ -12,6 +12,12 @@
 
 #include <cstdint>
 
+// A profiling build may define LB_STAMP(slot) before this header to record a per-warp timeline
+// of the kernels; in the product it expands to nothing.
+#ifndef LB_STAMP
+#define LB_STAMP(slot)
+#endif
+
 namespace lb {
 namespace dev {
 
@@ -92,6 +98,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x on the special-function unit (relative error 2^-22; 2^0 = 1 and 2^-inf = 0 exactly)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -175,16 +187,26 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
     const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
     const int v_hi = lane >> 4;
 
+    // four accumulation chains of four MMAs each (dims 0-63 and 64-127 of tokens 0-7 and 8-15):
+    // the dependent chain is what a warp waits on, so it is kept short and summed afterwards
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    float u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-        const int chunk = ((kk & 3) << 1) + k_hi;
-        const uint32_t addr =
-            k_tile + (kk >> 2) * kBoxBytes + k_tok * 128 + ((chunk ^ (k_tok & 7)) << 4);
-        uint32_t b0, b1, b2, b3;
+    for (int kk = 0; kk < 4; ++kk) {
+        const int chunk = (kk << 1) + k_hi;
+        const uint32_t addr = k_tile + k_tok * 128 + ((chunk ^ (k_tok & 7)) << 4);
+        uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
         ldmatrix_x4(addr, b0, b1, b2, b3);
+        ldmatrix_x4(addr + kBoxBytes, c0, c1, c2, c3);
         mma_bf16(s0, qf[kk], b0, b1);
         mma_bf16(s1, qf[kk], b2, b3);
+        mma_bf16(u0, qf[kk + 4], c0, c1);
+        mma_bf16(u1, qf[kk + 4], c2, c3);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s0[i] += u0[i];
+        s1[i] += u1[i];
     }
     const int t0 = (lane & 3) * 2;
     float x00 = s0[0] * scale_log2, x01 = s0[1] * scale_log2;
@@ -205,13 +227,13 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
     // token 0 of a page is always valid, so the new maxima are finite
     const float new0 = fmaxf(st.row_max[0], m0), new1 = fmaxf(st.row_max[1], m1);
-    const float alpha0 = exp2f(st.row_max[0] - new0), alpha1 = exp2f(st.row_max[1] - new1);
+    const float alpha0 = fast_exp2(st.row_max[0] - new0), alpha1 = fast_exp2(st.row_max[1] - new1);
     st.row_max[0] = new0;
     st.row_max[1] = new1;
-    const float p00 = exp2f(x00 - new0), p01 = exp2f(x01 - new0);
-    const float p10 = exp2f(x10 - new0), p11 = exp2f(x11 - new0);
-    const float p02 = exp2f(x02 - new1), p03 = exp2f(x03 - new1);
-    const float p12 = exp2f(x12 - new1), p13 = exp2f(x13 - new1);
+    const float p00 = fast_exp2(x00 - new0), p01 = fast_exp2(x01 - new0);
+    const float p10 = fast_exp2(x10 - new0), p11 = fast_exp2(x11 - new0);
+    const float p02 = fast_exp2(x02 - new1), p03 = fast_exp2(x03 - new1);
+    const float p12 = fast_exp2(x12 - new1), p13 = fast_exp2(x13 - new1);
     st.row_sum[0] = st.row_sum[0] * alpha0 + ((p00 + p01) + (p10 + p11));
     st.row_sum[1] = st.row_sum[1] * alpha1 + ((p02 + p03) + (p12 + p13));
     uint32_t pf[4];
@@ -219,12 +241,15 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
     pf[1] = pack_bf16(p02, p03);
     pf[2] = pack_bf16(p10, p11);
     pf[3] = pack_bf16(p12, p13);
+    // the running maxima settle after the first pages; then every alpha is exactly 1
+    if (__any_sync(0xffffffffu, alpha0 != 1.0f || alpha1 != 1.0f)) {
 #pragma unroll
-    for (int nt = 0; nt < 16; ++nt) {
-        st.acc[nt][0] *= alpha0;
-        st.acc[nt][1] *= alpha0;
-        st.acc[nt][2] *= alpha1;
-        st.acc[nt][3] *= alpha1;
+        for (int nt = 0; nt < 16; ++nt) {
+            st.acc[nt][0] *= alpha0;
+            st.acc[nt][1] *= alpha0;
+            st.acc[nt][2] *= alpha1;
+            st.acc[nt][3] *= alpha1;
+        }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -243,11 +268,13 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
 __device__ __forceinline__ void write_final_row(__nv_bfloat16 *out_row, float *lse_slot, int lane,
                                                 int half, const WarpState &st) {
     const float l = st.row_sum[half];
+    // one reciprocal instead of 32 divisions: the extra F32 rounding is far below a BF16 ulp
+    const float inv = 1.0f / l;
     uint32_t *out = reinterpret_cast<uint32_t *>(out_row);
 #pragma unroll
     for (int nt = 0; nt < 16; ++nt)
         out[nt * 4 + (lane & 3)] =
-            pack_bf16(st.acc[nt][half * 2] / l, st.acc[nt][half * 2 + 1] / l);
+            pack_bf16(st.acc[nt][half * 2] * inv, st.acc[nt][half * 2 + 1] * inv);
     if ((lane & 3) == 0) *lse_slot = st.row_max[half] + log2f(l);
 }
 __device__ __forceinline__ void write_state_row(float *state, int lane, int half,

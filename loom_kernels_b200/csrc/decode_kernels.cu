@@ -69,6 +69,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     // flags[0] = an out-of-range page index was seen; flags[1] = a bounded wait ran out
 
     // ---- work item --------------------------------------------------------------------------
+    LB_STAMP(0);
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
     int item = blockIdx.x;
@@ -78,10 +79,22 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     const int request = item / a.partitions;
     if (request >= a.batch) return;
 
+    // the guard's loads are issued first; the barriers are initialised (one thread each) while
+    // they are in flight, and the verdict is consumed afterwards
     int page_start, page_end, tail;
-    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_len, request, page_start,
-                                page_end, tail))
-        return;
+    const bool metadata_ok = request_metadata_valid(a.indptr, a.last, a.batch, a.indices_len,
+                                                    request, page_start, page_end, tail);
+    if (tid < a.stages * a.pps) {
+        mbar_init(full0 + tid * 8, 1);
+        mbar_init(empty0 + tid * 8, a.hc * a.mt);
+        fence_barrier_init();
+    }
+    if (tid == 0) {
+        flags[0] = 0;
+        flags[1] = 0;
+    }
+    if (!metadata_ok) return;
+    LB_STAMP(1);
     const int num_pages = page_end - page_start;
     const int kv_len = (num_pages - 1) * kPage + tail;
     // balanced page partition (single_decode/mod.rs:171-185 applied to pages)
@@ -107,16 +120,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         return;
     }
 
-    if (tid == 0) {
-        for (int i = 0; i < a.stages * a.pps; ++i) {
-            mbar_init(full0 + i * 8, 1);
-            mbar_init(empty0 + i * 8, a.hc * a.mt);
-        }
-        flags[0] = 0;
-        flags[1] = 0;
-        fence_barrier_init();
-    }
     __syncthreads();
+    LB_STAMP(2);
 
     const int n_iter = (cnt + a.pps - 1) / a.pps;
 
@@ -150,31 +155,38 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         };
         int window = load_page(lane);
         int window_next = load_page(32 + lane);
+        LB_STAMP(3);
+        const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
+        const uint32_t my_tile =
+            smem_u32(ring + my_slot * slot_bytes + which * (slot_bytes / 2));
+        int stage = 0;
+        uint32_t phase = 0;    // parity of the ring round being filled
+        bool recycled = false; // the ring has wrapped: a slot must be handed back before reuse
         for (int it = 0; it < n_iter; ++it) {
             const int first = it * a.pps;
             if (it > 0 && (first & 31) == 0) {
                 window = window_next;
                 window_next = load_page(first + 32 + lane);
             }
-            const int stage = it % a.stages;
-            const int round = it / a.stages;
             const int slot = first + my_slot;
             const int page_id = __shfl_sync(0xffffffffu, window, slot & 31);
             const bool has = lane_active && slot < cnt;
-            const uint32_t bar_full = full0 + (stage * a.pps + my_slot) * 8;
-            const uint32_t bar_empty = empty0 + (stage * a.pps + my_slot) * 8;
+            const uint32_t bar_full = my_full + stage * a.pps * 8;
             bool ok = true;
-            if (has && round > 0) ok = mbar_wait(bar_empty, (round - 1) & 1);
+            if (has && recycled) ok = mbar_wait(my_empty + stage * a.pps * 8, phase ^ 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
                 break;
             }
             if (has && which == 0) mbar_expect_tx(bar_full, slot_bytes);
             __syncwarp();
-            if (has)
-                tma_load_3d(smem_u32(ring + stage * stage_bytes + my_slot * slot_bytes +
-                                     which * (slot_bytes / 2)),
-                            map, 0, page_id * kPage, z, bar_full);
+            if (has) tma_load_3d(my_tile + stage * stage_bytes, map, 0, page_id * kPage, z, bar_full);
+            if (it == 0) LB_STAMP(4);
+            if (++stage == a.stages) {
+                stage = 0;
+                phase ^= 1;
+                recycled = true;
+            }
         }
         if (__any_sync(0xffffffffu, bad_page) && lane == 0) flags[0] = 1;
     } else {
@@ -186,35 +198,44 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         load_query_fragments(
             a.query + ((size_t)request * a.qh + (size_t)kv_head * group + row0) * kHeadDim,
             group - row0, lane, qf);
+        LB_STAMP(5);
 
-        for (int it = 0; it < n_iter; ++it) {
-            const int slot = it * a.pps + page_slot0;
-            if (slot >= cnt) continue;
-            const int stage = it % a.stages;
-            const int round = it / a.stages;
-            const uint32_t bar_full = full0 + (stage * a.pps + page_slot0) * 8;
-            const uint32_t bar_empty = empty0 + (stage * a.pps + page_slot0) * 8;
-            const bool ok = mbar_wait(bar_full, round & 1);
+        // my pages are page_slot0, page_slot0 + pps, ... of the chunk; stage and phase are
+        // carried as counters (no division in the loop)
+        const int my_pages = cnt > page_slot0 ? (cnt - page_slot0 + a.pps - 1) / a.pps : 0;
+        int tokens_left = chunk_end_token - (pg0 + page_slot0) * kPage;
+        const int tile_offset = page_slot0 * slot_bytes + head_in_cta * 2 * kBoxBytes;
+        const uint32_t my_full = full0 + page_slot0 * 8, my_empty = empty0 + page_slot0 * 8;
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int it = 0; it < my_pages; ++it) {
+            const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
                 break;
             }
-            uint8_t *slot_base = ring + stage * stage_bytes + page_slot0 * slot_bytes;
-            const int valid_tokens = min(kPage, chunk_end_token - (pg0 + slot) * kPage);
-            const bool wrote = attend_page(slot_base + head_in_cta * 2 * kBoxBytes,
-                                           slot_base + slot_bytes / 2 + head_in_cta * 2 * kBoxBytes,
-                                           valid_tokens, qf, a.scale_log2, lane, st);
+            if (it == 0) LB_STAMP(6);
+            uint8_t *k_tile = ring + stage * stage_bytes + tile_offset;
+            const bool wrote = attend_page(k_tile, k_tile + slot_bytes / 2, min(kPage, tokens_left),
+                                           qf, a.scale_log2, lane, st);
             __syncwarp();
             if (lane == 0) {
                 if (wrote) fence_proxy_async();
-                mbar_arrive(bar_empty);
+                mbar_arrive(my_empty + stage * a.pps * 8);
+            }
+            tokens_left -= a.pps * kPage;
+            if (++stage == a.stages) {
+                stage = 0;
+                phase ^= 1;
             }
         }
         st.finish_rows();
+        LB_STAMP(7);
     }
 
     // ---- join: every TMA write has been consumed or abandoned; the ring becomes scratch ---------
     __syncthreads();
+    LB_STAMP(8);
     const bool timed_out = flags[1] != 0;
     const bool invalid_page = flags[0] != 0;
     if (timed_out) {
@@ -222,10 +243,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         return;
     }
 
-    if (a.pps > 1) {
+    // page slots that streamed pages of this chunk: slot s has pages iff s < cnt
+    const int populated = min(a.pps, cnt);
+    if (populated > 1) {
         // warps that streamed different pages of the same KV head merge their states
         float *scratch = reinterpret_cast<float *>(ring);
-        if (warp < kComputeWarps) {
+        if (warp < kComputeWarps && page_slot0 > 0 && page_slot0 < populated) {
             float *mine = scratch + warp * kMergeFloatsPerWarp;
 #pragma unroll
             for (int nt = 0; nt < 16; ++nt)
@@ -238,7 +261,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         __syncthreads();
         if (warp < kComputeWarps && page_slot0 == 0) {
-            for (int k = 1; k < a.pps; ++k) {
+            for (int k = 1; k < populated; ++k) {
                 const float *other = scratch + (warp + k * a.hc * a.mt) * kMergeFloatsPerWarp;
                 const float om0 = other[64 * 32 + lane], om1 = other[65 * 32 + lane];
                 const float ol0 = other[66 * 32 + lane], ol1 = other[67 * 32 + lane];
@@ -262,6 +285,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
     }
 
+    LB_STAMP(9);
     if (warp >= kComputeWarps || page_slot0 != 0) return;
 
     // ---- epilogue ---------------------------------------------------------------------------------
@@ -280,6 +304,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                             st, invalid_page);
         }
     }
+    LB_STAMP(10);
 }
 
 // Merges the split-K states of one (request, query head) per warp (merge_states).

@@ -92,15 +92,15 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         ptail[r] = t;
         prefix[r + 1] = ok ? e - s : 0;
     }
+    if (tid < a.stages * a.pps) {
+        mbar_init(full0 + tid * 8, 1);
+        mbar_init(empty0 + tid * 8, a.hc * a.mt);
+        bad_slot[tid] = 0;
+        fence_barrier_init();
+    }
     if (tid == 0) {
         prefix[0] = 0;
-        for (int i = 0; i < a.stages * a.pps; ++i) {
-            mbar_init(full0 + i * 8, 1);
-            mbar_init(empty0 + i * 8, a.hc * a.mt);
-            bad_slot[i] = 0;
-        }
         *timeout_flag = 0;
-        fence_barrier_init();
     }
     __syncthreads();
     if (warp == 0) {
@@ -187,6 +187,12 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 load_window(s, 0, win_id[s], win_hb[s]);
                 load_window(s, 32, next_id[s], next_hb[s]);
             }
+        const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
+        const uint32_t my_tile =
+            smem_u32(ring + my_slot * slot_bytes + which * (slot_bytes / 2));
+        int stage = 0;
+        uint32_t phase = 0;    // parity of the ring round being filled
+        bool recycled = false; // the ring has wrapped: a slot must be handed back before reuse
         for (int j = 0; j < longest; ++j) {
             if (j > 0 && (j & 31) == 0) {
 #pragma unroll
@@ -210,13 +216,10 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                         my_count = count[s];
                     }
                 }
-            const int stage = j % a.stages;
-            const int round = j / a.stages;
             const bool has = lane_active && j < my_count;
-            const uint32_t bar_full = full0 + (stage * a.pps + my_slot) * 8;
-            const uint32_t bar_empty = empty0 + (stage * a.pps + my_slot) * 8;
+            const uint32_t bar_full = my_full + stage * a.pps * 8;
             bool ok = true;
-            if (has && round > 0) ok = mbar_wait(bar_empty, (round - 1) & 1);
+            if (has && recycled) ok = mbar_wait(my_empty + stage * a.pps * 8, phase ^ 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) *timeout_flag = 1;
                 break;
@@ -227,9 +230,13 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             }
             __syncwarp();
             if (has)
-                tma_load_3d(smem_u32(ring + stage * stage_bytes + my_slot * slot_bytes +
-                                     which * (slot_bytes / 2)),
-                            map, 0, max(page_id, 0) * kPage, hb * a.hc * 2, bar_full);
+                tma_load_3d(my_tile + stage * stage_bytes, map, 0, max(page_id, 0) * kPage,
+                            hb * a.hc * 2, bar_full);
+            if (++stage == a.stages) {
+                stage = 0;
+                phase ^= 1;
+                recycled = true;
+            }
         }
     } else {
         // ================= consumer warps: one (worker, KV head, 16-row tile) each ==================
@@ -249,7 +256,11 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             remaining = (int)(cut.begin(w + 1) - begin);
         }
         bool first_segment = true;
-        int j = 0; // pages this worker has consumed: stage = j % stages
+        // ring position of the next page this worker consumes (counters, no division per page)
+        const int tile_offset = my_slot * slot_bytes + head_in_cta * 2 * kBoxBytes;
+        const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
+        int stage = 0;
+        uint32_t phase = 0;
         bool live = true;
         while (live && remaining > 0) {
             // ---- segment: the part of one (request, head block, query block) item in my range ---
@@ -266,28 +277,27 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             st.reset();
             bool bad = false;
             const int tail = ptail[r];
-            for (int p = 0; p < seg_pages; ++p, ++j) {
-                const int stage = j % a.stages;
-                const int round = j / a.stages;
-                const uint32_t bar_full = full0 + (stage * a.pps + my_slot) * 8;
-                const uint32_t bar_empty = empty0 + (stage * a.pps + my_slot) * 8;
-                const bool ok = mbar_wait(bar_full, round & 1);
+            const int last_in_segment = num_pages - 1 - first_page; // p of the request's last page
+            for (int p = 0; p < seg_pages; ++p) {
+                const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase);
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) *timeout_flag = 1;
                     live = false;
                     break;
                 }
                 bad |= bad_slot[stage * a.pps + my_slot] != 0;
-                uint8_t *slot_base = ring + stage * stage_bytes + my_slot * slot_bytes;
-                const int valid_tokens = first_page + p == num_pages - 1 ? tail : kPage;
+                uint8_t *k_tile = ring + stage * stage_bytes + tile_offset;
                 const bool wrote =
-                    attend_page(slot_base + head_in_cta * 2 * kBoxBytes,
-                                slot_base + slot_bytes / 2 + head_in_cta * 2 * kBoxBytes,
-                                valid_tokens, qf, a.scale_log2, lane, st);
+                    attend_page(k_tile, k_tile + slot_bytes / 2, p == last_in_segment ? tail : kPage,
+                                qf, a.scale_log2, lane, st);
                 __syncwarp();
                 if (lane == 0) {
                     if (wrote) fence_proxy_async();
-                    mbar_arrive(bar_empty);
+                    mbar_arrive(my_empty + stage * a.pps * 8);
+                }
+                if (++stage == a.stages) {
+                    stage = 0;
+                    phase ^= 1;
                 }
             }
             if (!live) break;
