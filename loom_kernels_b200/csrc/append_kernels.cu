@@ -6,13 +6,19 @@
 // one-token-per-request contract, the explicit <=64-token contract and the extended
 // any-total variant:
 //
+//   0. a CTA starts on its tokens at once: the first token's Q/K/V rows are fetched into
+//      registers and the sin/cos tables of its first eight tokens are computed, 64 threads per
+//      token (from in-bounds loads only), while
 //   1. every CTA validates the whole call against device-resident metadata (page table, token
 //      mapping, physical-slot uniqueness via a shared-memory hash set) and returns without
 //      writing when anything is invalid, so a call is all-or-nothing exactly like the
-//      reference's guards (rope/mod.rs:140-182,290-343);
-//   2. a CTA then walks its tokens: 64 threads compute the token's sin/cos table once, and
-//      8 lanes per head row rotate Q and K with 16-byte loads/stores (a rotation pair
-//      (i, i+64) lives in one thread), scatter K and copy V rows to the token's page slot.
+//      reference's guards (rope/mod.rs:140-182,290-343).  The validation is laid out for
+//      memory-level parallelism: four independent loads per thread per step, and the in-bounds
+//      levels of the token -> request -> page chain are issued before the page-table verdict;
+//   2. the CTA then walks its tokens (token, token + grid, ...): 8 lanes per head row rotate Q
+//      and K with 16-byte loads/stores (a rotation pair (i, i+64) lives in one thread), scatter
+//      K and copy V rows to the token's page slot, while the next token's rows are already on
+//      their way into a second register set.
 //
 // Angles use the host-computed inverse frequencies powf(10000, -2i/128) (constant memory), so
 // they are bit-identical to the CPU reference (crates/loom-infer/src/rope/mod.rs:148-150);
@@ -24,13 +30,19 @@
 
 #include "kernels.hpp"
 
+#ifndef LB_STAMP
+#define LB_STAMP(slot)
+#endif
+
 namespace lb {
 namespace {
 
 constexpr int kHeadDim = 128;
 constexpr int kPairs = 64;
 constexpr int kPage = 16;
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
+constexpr int kTables = kThreads / kPairs;        // sin/cos tables computed in one go
+constexpr int kMaxTokensPerCta = 128;            // the plan sizes the grid so that no CTA gets more
 
 __constant__ float c_inverse_frequency[kPairs];
 
@@ -41,26 +53,39 @@ struct AppendArgs {
     int32_t tokens, batch, max_pages, qh, kvh, indices_len, hash_slots;
 };
 
-// (request, position) of a token; one-token-per-request plans derive both from the page table.
-__device__ __forceinline__ bool token_slot(const AppendArgs &a, int token, int &position,
-                                           int &slot) {
-    int request, pos;
-    if (a.batch_indices) {
-        request = a.batch_indices[token];
-        pos = a.positions[token];
-        if (request < 0 || request >= a.batch || pos < 0) return false;
-    } else {
-        request = token;
-        pos = -1;
-    }
-    const int start = a.indptr[request];
+// Levels 1-2 of the token -> request -> page chain, from in-bounds loads only: an out-of-range
+// request reads request 0 instead.  `position` and `start` mean something only if the page table
+// is valid; the verdict on the token is the return value (to be combined with the table's).
+// One-token-per-request plans derive request and position from the page table.
+__device__ __forceinline__ bool token_request(const AppendArgs &a, int token, int &position,
+                                              int &start) {
+    const bool explicit_tokens = a.batch_indices != nullptr;
+    const int request_raw = explicit_tokens ? a.batch_indices[token] : token;
+    const int position_raw = explicit_tokens ? a.positions[token] : 0;
+    const bool ok = request_raw >= 0 && request_raw < a.batch && position_raw >= 0;
+    const int request = ok ? request_raw : 0;
+    start = a.indptr[request];
     const int pages = a.indptr[request + 1] - start;
     const int kv_len = (pages - 1) * kPage + a.last[request];
-    if (pos < 0) pos = kv_len - 1;
-    if (pos >= kv_len) return false;
-    position = pos;
-    slot = a.indices[start + pos / kPage] * kPage + pos % kPage;
-    return true;
+    position = explicit_tokens ? position_raw : kv_len - 1;
+    return ok && position < kv_len;
+}
+
+// The position the rotation of `token` uses, from in-bounds loads only (it may be garbage when
+// the call is invalid; nothing is written in that case).
+__device__ __forceinline__ int speculative_position(const AppendArgs &a, int token) {
+    if (a.batch_indices) return a.positions[token];
+    return (a.indptr[token + 1] - a.indptr[token] - 1) * kPage + a.last[token] - 1;
+}
+
+// (sin, cos) of rotation pair `pair` at `position`.  The F32 angle is exactly the reference's;
+// sin/cos are evaluated in double and rounded once, which reproduces the host libm's (near
+// correctly rounded) sinf/cosf.
+__device__ __forceinline__ float2 pair_sincos(int position, int pair) {
+    const float angle = __fmul_rn((float)position, c_inverse_frequency[pair]);
+    double s, c;
+    sincos((double)angle, &s, &c);
+    return make_float2((float)s, (float)c);
 }
 
 __device__ __forceinline__ uint32_t rotate_pack(uint32_t lo_bits, uint32_t hi_bits, float2 sc0,
@@ -78,24 +103,97 @@ __device__ __forceinline__ uint32_t rotate_pack(uint32_t lo_bits, uint32_t hi_bi
     return *reinterpret_cast<uint32_t *>(&lo);
 }
 
-__device__ __forceinline__ void rotate_row(const uint4 *src, uint4 *dst, int j,
+// lane j of 8 owns dims [8j, 8j+8) (lo) and [64+8j, 64+8j+8) (hi) of the 128-wide row
+__device__ __forceinline__ void rotate_row(uint4 lo, uint4 hi, uint4 *dst, int j,
                                            const float2 *sincos) {
-    // lane j of 8 owns dims [8j, 8j+8) and [64+8j, 64+8j+8) of the 128-wide row
-    const uint4 lo = src[j], hi = src[8 + j];
-    const float2 *sc = sincos + 8 * j;
+    const float4 *sc = reinterpret_cast<const float4 *>(sincos + 8 * j);
+    const float4 t0 = sc[0], t1 = sc[1], t2 = sc[2], t3 = sc[3];
     uint4 out_lo, out_hi;
-    out_lo.x = rotate_pack(lo.x, hi.x, sc[0], sc[1], out_hi.x);
-    out_lo.y = rotate_pack(lo.y, hi.y, sc[2], sc[3], out_hi.y);
-    out_lo.z = rotate_pack(lo.z, hi.z, sc[4], sc[5], out_hi.z);
-    out_lo.w = rotate_pack(lo.w, hi.w, sc[6], sc[7], out_hi.w);
+    out_lo.x = rotate_pack(lo.x, hi.x, make_float2(t0.x, t0.y), make_float2(t0.z, t0.w), out_hi.x);
+    out_lo.y = rotate_pack(lo.y, hi.y, make_float2(t1.x, t1.y), make_float2(t1.z, t1.w), out_hi.y);
+    out_lo.z = rotate_pack(lo.z, hi.z, make_float2(t2.x, t2.y), make_float2(t2.z, t2.w), out_hi.z);
+    out_lo.w = rotate_pack(lo.w, hi.w, make_float2(t3.x, t3.y), make_float2(t3.z, t3.w), out_hi.w);
     dst[j] = out_lo;
     dst[8 + j] = out_hi;
 }
 
-__global__ void __launch_bounds__(kThreads) rope_append_kernel(const AppendArgs a) {
+// The rows of one token a thread works on, fetched ahead of their use: row task tid (8 tasks
+// per Q/K row) and V chunk tid.  Tokens with more rows than that take the remainder straight
+// from memory.
+struct TokenRows {
+    uint4 lo, hi, v;
+};
+
+__device__ __forceinline__ const uint4 *row_source(const AppendArgs &a, int token, int row) {
+    return row < a.qh ? a.query + ((size_t)token * a.qh + row) * (kHeadDim / 8)
+                      : a.key + ((size_t)token * a.kvh + (row - a.qh)) * (kHeadDim / 8);
+}
+__device__ __forceinline__ uint4 *row_destination(const AppendArgs &a, int token, int slot,
+                                                  int row) {
+    return row < a.qh ? a.query_output + ((size_t)token * a.qh + row) * (kHeadDim / 8)
+                      : a.key_pages + ((size_t)slot * a.kvh + (row - a.qh)) * (kHeadDim / 8);
+}
+
+__device__ __forceinline__ void fetch_token(const AppendArgs &a, int token, int tid,
+                                            TokenRows &rows) {
+    if (tid < (a.qh + a.kvh) * 8) {
+        const uint4 *src = row_source(a, token, tid >> 3);
+        rows.lo = src[tid & 7];
+        rows.hi = src[8 + (tid & 7)];
+    }
+    if (tid < a.kvh * 16) rows.v = a.value[(size_t)token * a.kvh * 16 + tid];
+}
+
+__device__ __forceinline__ void store_token(const AppendArgs &a, int token, int slot, int tid,
+                                            const TokenRows &rows, const float2 *sincos) {
+    const int row_tasks = (a.qh + a.kvh) * 8; // 8 lanes per 128-wide row
+    const int copy_tasks = a.kvh * 16;        // V rows: 16 x 16-byte chunks per KV head
+    if (tid < row_tasks)
+        rotate_row(rows.lo, rows.hi, row_destination(a, token, slot, tid >> 3), tid & 7, sincos);
+    for (int task = tid + kThreads; task < row_tasks; task += kThreads) {
+        const uint4 *src = row_source(a, token, task >> 3);
+        rotate_row(src[task & 7], src[8 + (task & 7)], row_destination(a, token, slot, task >> 3),
+                   task & 7, sincos);
+    }
+    if (tid < copy_tasks) a.value_pages[(size_t)slot * copy_tasks + tid] = rows.v;
+    for (int task = tid + kThreads; task < copy_tasks; task += kThreads)
+        a.value_pages[(size_t)slot * copy_tasks + task] =
+            a.value[(size_t)token * copy_tasks + task];
+}
+
+__global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendArgs a) {
     extern __shared__ int hash_table[];
-    __shared__ float2 sincos_table[kPairs]; // (sin, cos) per rotation pair of the current token
+    __shared__ __align__(16) float2 sincos_table[kTables][kPairs]; // (sin, cos) per pair and token
+    __shared__ int2 mine[kMaxTokensPerCta];                  // (position, slot) of my tokens
     const int tid = threadIdx.x;
+    const int grid = (int)gridDim.x;
+    LB_STAMP(0);
+
+    // ---- 0. start on this CTA's first token while the call is being validated ---------------
+    const int first_token = blockIdx.x;
+    const int count = first_token < a.tokens ? (a.tokens - first_token + grid - 1) / grid : 0;
+    TokenRows rows;
+    if (count > 0) fetch_token(a, first_token, tid, rows);
+    // The sin/cos tables of my first kTables tokens, 64 threads per token, taken from the top of
+    // the CTA (the low threads carry the token mapping of small calls).  Double-precision
+    // sin/cos is the slowest single step of a small call, so it starts first and runs beside
+    // the validation; positions come from in-bounds loads and are confirmed by the validation.
+    {
+        const int r = kThreads - 1 - tid;
+        if (r / kPairs < min(count, kTables))
+            sincos_table[r / kPairs][r % kPairs] =
+                pair_sincos(speculative_position(a, first_token + (r / kPairs) * grid), r % kPairs);
+    }
+    // levels 1-2 of the first four tokens of this thread (in-bounds whatever the metadata holds)
+    int position[4], start[4];
+    bool ok[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int token = u * kThreads + tid;
+        position[u] = start[u] = 0;
+        ok[u] = token < a.tokens ? token_request(a, token, position[u], start[u]) : true;
+    }
+    LB_STAMP(1);
 
     // ---- 1. whole-call validation (identical in every CTA) -----------------------------------
     for (int i = tid; i < a.hash_slots; i += kThreads) hash_table[i] = -1;
@@ -105,71 +203,86 @@ __global__ void __launch_bounds__(kThreads) rope_append_kernel(const AppendArgs 
         invalid = a.indptr[0] != 0 || final_indptr < 0 || final_indptr != a.indices_len;
     }
     for (int request = tid; request < a.batch; request += kThreads) {
-        const int start = a.indptr[request], end = a.indptr[request + 1], tail = a.last[request];
-        if (start < 0 || end <= start || end > a.indices_len || tail < 1 || tail > kPage)
+        const int begin = a.indptr[request], end = a.indptr[request + 1], tail = a.last[request];
+        if (begin < 0 || end <= begin || end > a.indices_len || tail < 1 || tail > kPage)
             invalid = true;
     }
-    for (int page = tid; page < a.indices_len; page += kThreads) {
-        const int id = a.indices[page];
-        if (id < 0 || id >= a.max_pages) invalid = true;
+    for (int base = 0; base < a.indices_len; base += 4 * kThreads) {
+        int id[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int page = base + u * kThreads + tid;
+            id[u] = page < a.indices_len ? a.indices[page] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
     }
     if (__syncthreads_or(invalid)) return;
+    LB_STAMP(2);
 
-    for (int token = tid; token < a.tokens; token += kThreads) {
-        int position, slot;
-        if (!token_slot(a, token, position, slot)) {
-            invalid = true;
-            continue;
+    // token mapping: the page lookups of four tokens per thread travel together, then the
+    // physical slots go into the hash set (meeting the same key = two tokens share a slot)
+    for (int base = 0; base < a.tokens; base += 4 * kThreads) {
+        int slot[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int token = base + u * kThreads + tid;
+            if (base > 0)
+                ok[u] = token < a.tokens ? token_request(a, token, position[u], start[u]) : true;
+            const bool live = token < a.tokens && ok[u];
+            const int page = live ? start[u] + position[u] / kPage : 0;
+            slot[u] = a.indices[page] * kPage + position[u] % kPage;
         }
-        // open-addressing insert; meeting the same key means two tokens share a physical slot
-        unsigned h = ((unsigned)slot * 2654435761u) & (unsigned)(a.hash_slots - 1);
-        for (int probe = 0; probe < a.hash_slots; ++probe) {
-            const int seen = atomicCAS(&hash_table[h], -1, slot);
-            if (seen == -1) break;
-            if (seen == slot) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int token = base + u * kThreads + tid;
+            if (token >= a.tokens) continue;
+            if (!ok[u]) {
                 invalid = true;
-                break;
+                continue;
             }
-            h = (h + 1) & (unsigned)(a.hash_slots - 1);
+            if (token >= first_token && (token - first_token) % grid == 0)
+                mine[(token - first_token) / grid] = make_int2(position[u], slot[u]);
+            unsigned h = ((unsigned)slot[u] * 2654435761u) & (unsigned)(a.hash_slots - 1);
+            for (int probe = 0; probe < a.hash_slots; ++probe) {
+                const int seen = atomicCAS(&hash_table[h], -1, slot[u]);
+                if (seen == -1) break;
+                if (seen == slot[u]) {
+                    invalid = true;
+                    break;
+                }
+                h = (h + 1) & (unsigned)(a.hash_slots - 1);
+            }
         }
     }
+    LB_STAMP(3);
     if (__syncthreads_or(invalid)) return;
+    LB_STAMP(4);
+    if (first_token >= a.tokens) return;
 
-    // ---- 2. rotate + scatter -------------------------------------------------------------------
-    const int heads = a.qh + a.kvh;
-    const int row_tasks = heads * 8;   // 8 lanes per 128-wide row
-    const int copy_tasks = a.kvh * 16; // V rows: 16 x 16-byte chunks
-    for (int token = blockIdx.x; token < a.tokens; token += gridDim.x) {
-        int position = 0, slot = 0;
-        token_slot(a, token, position, slot);
-        __syncthreads(); // the previous token's table is no longer read
-        if (tid < kPairs) {
-            // The F32 angle is exactly the reference's; sin/cos are evaluated in double and
-            // rounded once, which reproduces the host libm's (near correctly rounded) sinf/cosf.
-            const float angle = __fmul_rn((float)position, c_inverse_frequency[tid]);
-            double s, c;
-            sincos((double)angle, &s, &c);
-            sincos_table[tid] = make_float2((float)s, (float)c);
+    // ---- 2. rotate + scatter: token k's rows are in registers and its table in shared memory
+    //         when its turn comes; token k + 1 is fetched while token k is rotated ------------------
+    for (int k = 0; k < count; ++k) {
+        const int token = first_token + k * grid;
+        if (k > 0 && k % kTables == 0) {
+            // the next kTables tables (only calls with more than kTables tokens per CTA get here)
+            __syncthreads();
+            const int r = kThreads - 1 - tid;
+            if (k + r / kPairs < count)
+                sincos_table[r / kPairs][r % kPairs] = pair_sincos(mine[k + r / kPairs].x, r % kPairs);
+            __syncthreads();
         }
-        __syncthreads();
-        for (int task = tid; task < row_tasks; task += kThreads) {
-            const int row = task >> 3, j = task & 7;
-            if (row < a.qh) {
-                const size_t offset = ((size_t)token * a.qh + row) * (kHeadDim / 8);
-                rotate_row(a.query + offset, a.query_output + offset, j, sincos_table);
-            } else {
-                const int kv_head = row - a.qh;
-                const size_t src = ((size_t)token * a.kvh + kv_head) * (kHeadDim / 8);
-                const size_t dst = ((size_t)slot * a.kvh + kv_head) * (kHeadDim / 8);
-                rotate_row(a.key + src, a.key_pages + dst, j, sincos_table);
-            }
-        }
-        for (int task = tid; task < copy_tasks; task += kThreads) {
-            const int kv_head = task >> 4, c = task & 15;
-            a.value_pages[((size_t)slot * a.kvh + kv_head) * 16 + c] =
-                a.value[((size_t)token * a.kvh + kv_head) * 16 + c];
-        }
+        // two tokens per round with two register sets, so that a fetched row is never moved (a
+        // register move would wait for the load it copies)
+        TokenRows other;
+        if (k + 1 < count) fetch_token(a, token + grid, tid, other);
+        store_token(a, token, mine[k].y, tid, rows, sincos_table[k % kTables]);
+        if (k == 0) LB_STAMP(5);
+        if (++k == count) break; // k is odd now: never a table boundary (kTables is even)
+        if (k + 1 < count) fetch_token(a, token + 2 * grid, tid, rows);
+        store_token(a, token + grid, mine[k].y, tid, other, sincos_table[k % kTables]);
     }
+    LB_STAMP(6);
 }
 
 } // namespace
@@ -180,6 +293,9 @@ int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_fre
     return cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)max_dynamic_shared);
 }
+
+int append_block_threads() { return kThreads; }
+int append_max_tokens_per_cta() { return kMaxTokensPerCta; }
 
 int launch_rope_append(const AppendLaunch &launch, void *stream) {
     AppendArgs args;

@@ -56,5 +56,7 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream);
 int launch_split_merge(const MergeLaunch &launch, void *stream);
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency);
 int launch_rope_append(const AppendLaunch &launch, void *stream);
+int append_block_threads();       // threads per CTA the append kernel is built for
+int append_max_tokens_per_cta();  // tokens one CTA can own (grid floor = tokens / this)
 
 } // namespace lb

@@ -350,8 +350,14 @@ static lb_status make_append_plan(const lb_rope_provider *provider, const lb_pag
     while (hash_slots < 2 * tokens) hash_slots *= 2;
     plan->hash_slots = hash_slots;
     plan->shared_bytes = hash_slots * (uint32_t)sizeof(int);
-    const uint32_t cap = 4u * (uint32_t)(provider->sm_count ? provider->sm_count : 148);
-    plan->grid = tokens < cap ? (uint32_t)tokens : cap;
+    // one CTA per token up to two CTAs per SM: every CTA validates the whole call, so more CTAs
+    // buy parallel rotation at the price of repeated validation; a CTA never owns more tokens
+    // than the kernel's per-CTA token list holds
+    plan->block = (uint32_t)append_block_threads();
+    const uint32_t cap = 2u * (uint32_t)(provider->sm_count ? provider->sm_count : 148);
+    const uint32_t per_cta = (uint32_t)append_max_tokens_per_cta();
+    const uint32_t floor = (uint32_t)((tokens + per_cta - 1) / per_cta);
+    plan->grid = tokens < cap ? (uint32_t)tokens : (cap > floor ? cap : floor);
     *out = plan;
     return LB_OK;
 }

@@ -249,6 +249,15 @@ def main():
                                                [7, 2, 6, 5, 1, 7, 0, 4], [3, 16, 1, 9]))]:
             w = gate_workload("gate " + name, *shape, seed=1)
             measure(DecodeCase(decode, w, device), w.name, 100, args.samples, 200, device)
+        # the append shapes the reference published H20 numbers for (3.989 us for one token per
+        # request at batch 4; 5.510 us eager / 8.288 us Graph for 6 explicit tokens at batch 3)
+        for name, new_tokens, prior in (("append b4 16/4 one token per request", [1, 1, 1, 1],
+                                         [0, 15, 16, 40]),
+                                        ("append b3 16/4 six explicit tokens", [1, 2, 3],
+                                         [3, 16, 30])):
+            w = workloads.append_small("gate " + name, new_tokens, prior, 16, 4, 16)
+            measure(AppendCase(rope, w, device, chunked=True), w.name, 100, args.samples, 200,
+                    device)
     if "c1" in cases:
         w = workloads.c1()
         measure(DecodeCase(decode, w, device), w.name + " warm", 100, args.samples, 200, device)

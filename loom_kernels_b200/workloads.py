@@ -170,3 +170,24 @@ def c2(with_values=True, seed=0xC2):
         w.key_pages = normal_bf16(rng, pool)
         w.value_pages = normal_bf16(rng, pool)
     return w
+
+
+def append_small(name, new, prior, qh, kvh, pool_pages, seed=0xA9):
+    """A small explicit-token append call: request r appends new[r] tokens after prior[r]."""
+    rng = np.random.default_rng(seed)
+    new, prior = np.asarray(new, dtype=np.int64), np.asarray(prior, dtype=np.int64)
+    batch = len(new)
+    indptr, indices, last = page_table(rng, prior + new, pool_pages)
+    batch_indices = np.repeat(np.arange(batch), new).astype(np.int32)
+    positions = np.concatenate([prior[r] + np.arange(new[r]) for r in range(batch)]).astype(
+        np.int32)
+    tokens = int(new.sum())
+    w = AppendWorkload(name, batch, pool_pages, qh, kvh, tokens, batch_indices, positions, indptr,
+                       indices, last)
+    pool = pool_pages * PAGE_SIZE * kvh * HEAD_DIM
+    w.query = normal_bf16(rng, tokens * qh * HEAD_DIM)
+    w.key = normal_bf16(rng, tokens * kvh * HEAD_DIM)
+    w.value = normal_bf16(rng, tokens * kvh * HEAD_DIM)
+    w.key_pages = normal_bf16(rng, pool)
+    w.value_pages = normal_bf16(rng, pool)
+    return w
