@@ -59,5 +59,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+NATIVE_BENCH = os.path.join(HERE, "loom_native_bench")
+
+
+def build_native_bench(force: bool = False) -> str:
+    """The C++ latency harness over the C ABI (csrc/native_bench.cpp), linked to the library."""
+    source = os.path.join(CSRC, "native_bench.cpp")
+    lib = build()
+    if (not force and os.path.exists(NATIVE_BENCH)
+            and os.path.getmtime(NATIVE_BENCH) > max(os.path.getmtime(source),
+                                                     os.path.getmtime(lib))):
+        return NATIVE_BENCH
+    subprocess.run([NVCC, "-std=c++17", "-O2", "-I", os.path.join(ROOT, "include"), source,
+                    "-o", NATIVE_BENCH, "-L", HERE, "-lloom_b200",
+                    "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"], check=True)
+    return NATIVE_BENCH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--native-bench" in sys.argv:
+        print(build_native_bench(force="--force" in sys.argv))

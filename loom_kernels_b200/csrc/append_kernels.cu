@@ -28,6 +28,7 @@
 
 #include <cstdint>
 
+#include "dependent_launch.cuh"
 #include "kernels.hpp"
 
 #ifndef LB_STAMP
@@ -165,8 +166,11 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
     extern __shared__ int hash_table[];
     __shared__ __align__(16) float2 sincos_table[kTables][kPairs]; // (sin, cos) per pair and token
     __shared__ int2 mine[kMaxTokensPerCta];                  // (position, slot) of my tokens
+    dev::dependent_launch_release();
     const int tid = threadIdx.x;
     const int grid = (int)gridDim.x;
+    for (int i = tid; i < a.hash_slots; i += kThreads) hash_table[i] = -1;
+    dev::dependent_launch_wait(); // global memory is touched from here on
     LB_STAMP(0);
 
     // ---- 0. start on this CTA's first token while the call is being validated ---------------
@@ -196,7 +200,6 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
     LB_STAMP(1);
 
     // ---- 1. whole-call validation (identical in every CTA) -----------------------------------
-    for (int i = tid; i < a.hash_slots; i += kThreads) hash_table[i] = -1;
     bool invalid = false;
     if (tid == 0) {
         const int final_indptr = a.indptr[a.batch];
@@ -317,9 +320,8 @@ int launch_rope_append(const AppendLaunch &launch, void *stream) {
     args.kvh = launch.kvh;
     args.indices_len = launch.indices_len;
     args.hash_slots = launch.hash_slots;
-    rope_append_kernel<<<launch.grid, launch.block, launch.shared_bytes,
-                         static_cast<cudaStream_t>(stream)>>>(args);
-    return cudaGetLastError();
+    return launch_dependent(rope_append_kernel, launch.grid, launch.block, launch.shared_bytes,
+                            stream, args);
 }
 
 } // namespace lb

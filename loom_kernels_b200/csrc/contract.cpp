@@ -114,8 +114,29 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         // calls are launch-latency bound and a second launch would only add to it.
         const size_t direct_items = items_for(widest_hc, 1);
         const bool plenty = direct_items >= 8 * (size_t)sms || spec.max_num_pages <= 64;
-        if (plenty) algorithm = LB_DECODE_DIRECT;
-        else if (balanced_possible && balanced_option != 2) algorithm = LB_DECODE_BALANCED;
+        if (plenty) {
+            algorithm = LB_DECODE_DIRECT;
+        } else if (spec.batch_size == 1 &&
+                   spec.max_num_pages * spec.num_kv_heads <= 64 * (size_t)sms) {
+            // One short request (at most 64 page-heads per SM even if it fills the pool) has
+            // nothing ragged to balance, and such calls are latency-bound: a
+            // static split into about half a wave of CTAs (fewer, longer chunks beat more states
+            // to merge; measured on MHA 32/32 at context 1024: 8 chunks x 8 head blocks 12.5 us,
+            // 16 chunks 14.9 us, balanced 21.7 us), two page slots per CTA where the heads allow.
+            uint32_t h = hc;
+            if (h == 0) {
+                h = units >= 2 ? units / 2 : 1;
+                while (h > 1 && !valid_hc(h)) h /= 2;
+            }
+            size_t limit = spec.max_num_pages / 8; // >= 8 pages a chunk if the pool is one request
+            if (limit > 64) limit = 64;
+            size_t p = (sms / 2) / items_for(h, 1);
+            if (p > limit) p = limit;
+            if (p < 1) p = 1;
+            hc = h;
+            partitions = (uint32_t)p;
+            algorithm = p > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+        } else if (balanced_possible && balanced_option != 2) algorithm = LB_DECODE_BALANCED;
         else algorithm = LB_DECODE_SPLIT_K; // best static split below (may come out as 1 chunk)
     }
 

@@ -12,6 +12,8 @@
 
 #include <cstdint>
 
+#include "dependent_launch.cuh"
+
 // A profiling build may define LB_STAMP(slot) before this header to record a per-warp timeline
 // of the kernels; in the product it expands to nothing.
 #ifndef LB_STAMP
@@ -309,9 +311,9 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     for (int i = lane; i < n; i += 32) {
         const float *s = state_of(i);
         if (s == nullptr) continue;
-        const float norm = __ldg(s + 1);
+        const float norm = __ldcg(s + 1);
         poisoned |= norm < 0.0f;
-        if (norm > 0.0f) top = fmaxf(top, __ldg(s));
+        if (norm > 0.0f) top = fmaxf(top, __ldcg(s));
     }
     if (__any_sync(0xffffffffu, poisoned)) return;
 #pragma unroll
@@ -322,10 +324,10 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     for (int i = 0; i < n; ++i) {
         const float *s = state_of(i);
         if (s == nullptr) continue;
-        const float part_norm = __ldg(s + 1);
-        const float weight = part_norm > 0.0f ? exp2f(__ldg(s) - top) : 0.0f;
-        const float2 lo = __ldg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
-        const float2 hi = __ldg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+        const float part_norm = __ldcg(s + 1);
+        const float weight = part_norm > 0.0f ? exp2f(__ldcg(s) - top) : 0.0f;
+        const float2 lo = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
+        const float2 hi = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
         norm += part_norm * weight;
         acc.x += lo.x * weight;
         acc.y += lo.y * weight;

@@ -52,6 +52,7 @@ __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const DecodeArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    dependent_launch_release();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
@@ -79,11 +80,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     const int request = item / a.partitions;
     if (request >= a.batch) return;
 
-    // the guard's loads are issued first; the barriers are initialised (one thread each) while
-    // they are in flight, and the verdict is consumed afterwards
-    int page_start, page_end, tail;
-    const bool metadata_ok = request_metadata_valid(a.indptr, a.last, a.batch, a.indices_len,
-                                                    request, page_start, page_end, tail);
+    // barriers: one thread each, before the first touch of global memory
     if (tid < a.stages * a.pps) {
         mbar_init(full0 + tid * 8, 1);
         mbar_init(empty0 + tid * 8, a.hc * a.mt);
@@ -93,7 +90,16 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         flags[0] = 0;
         flags[1] = 0;
     }
-    if (!metadata_ok) return;
+    if (warp == kComputeWarps && lane == 0) {
+        prefetch_tensormap(&k_map);
+        prefetch_tensormap(&v_map);
+    }
+    // everything above ran beside the previous command; global memory is touched from here on
+    dependent_launch_wait();
+    int page_start, page_end, tail;
+    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_len, request, page_start,
+                                page_end, tail))
+        return;
     LB_STAMP(1);
     const int num_pages = page_end - page_start;
     const int kv_len = (num_pages - 1) * kPage + tail;
@@ -139,10 +145,6 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         const bool lane_active = my_slot < a.pps;
         const int z = hb * a.hc * 2;
         const CUtensorMap *map = which == 0 ? &k_map : &v_map;
-        if (lane == 0) {
-            prefetch_tensormap(&k_map);
-            prefetch_tensormap(&v_map);
-        }
         bool bad_page = false;
         auto load_page = [&](int j) -> int {
             if (j >= cnt) return 0;
@@ -312,10 +314,12 @@ __global__ void __launch_bounds__(128)
 split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                    const int32_t *indptr, const int32_t *last, int batch, int qh, int partitions,
                    int indices_len) {
+    dependent_launch_release();
     const int lane = threadIdx.x & 31;
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
     const int request = state / qh;
+    dependent_launch_wait(); // the partial states are complete and visible
     // the guard's loads and the state loads travel together; the verdict is used at the end
     int page_start, page_end, tail;
     const bool valid = request_metadata_valid(indptr, last, batch, indices_len, request,
@@ -360,16 +364,15 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    paged_decode_kernel<<<launch.grid, launch.block, launch.shared_bytes,
-                          static_cast<cudaStream_t>(stream)>>>(k_map, v_map, args);
-    return cudaGetLastError();
+    return launch_dependent(paged_decode_kernel, launch.grid, launch.block, launch.shared_bytes,
+                            stream, k_map, v_map, args);
 }
 
 int launch_split_merge(const MergeLaunch &launch, void *stream) {
-    split_merge_kernel<<<launch.grid, launch.block, 0, static_cast<cudaStream_t>(stream)>>>(
-        launch.workspace, static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.indptr,
-        launch.last, launch.batch, launch.qh, launch.partitions, launch.indices_len);
-    return cudaGetLastError();
+    return launch_dependent(split_merge_kernel, launch.grid, launch.block, 0, stream,
+                            launch.workspace, static_cast<__nv_bfloat16 *>(launch.output),
+                            launch.lse, launch.indptr, launch.last, launch.batch, launch.qh,
+                            launch.partitions, launch.indices_len);
 }
 
 } // namespace lb

@@ -63,6 +63,7 @@ __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    dependent_launch_release();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
@@ -82,16 +83,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     int *pstart = prefix + a.batch + 1;             // [batch] indptr[r]
     int *ptail = pstart + a.batch;                  // [batch] last_page_len[r]
 
-    // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
-    const int global_end = a.indptr[a.batch];
-    const bool global_ok = a.indptr[0] == 0 && global_end >= 0 && global_end == a.indices_len;
-    for (int r = tid; r < a.batch; r += blockDim.x) {
-        const int s = a.indptr[r], e = a.indptr[r + 1], t = a.last[r];
-        const bool ok = global_ok && s >= 0 && e > s && e <= global_end && t >= 1 && t <= kPage;
-        pstart[r] = s;
-        ptail[r] = t;
-        prefix[r + 1] = ok ? e - s : 0;
-    }
     if (tid < a.stages * a.pps) {
         mbar_init(full0 + tid * 8, 1);
         mbar_init(empty0 + tid * 8, a.hc * a.mt);
@@ -101,6 +92,23 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if (tid == 0) {
         prefix[0] = 0;
         *timeout_flag = 0;
+    }
+    if (warp == kComputeWarps && lane == 0) {
+        prefetch_tensormap(&k_map);
+        prefetch_tensormap(&v_map);
+    }
+    // everything above ran beside the previous command; global memory is touched from here on
+    dependent_launch_wait();
+
+    // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
+    const int global_end = a.indptr[a.batch];
+    const bool global_ok = a.indptr[0] == 0 && global_end >= 0 && global_end == a.indices_len;
+    for (int r = tid; r < a.batch; r += blockDim.x) {
+        const int s = a.indptr[r], e = a.indptr[r + 1], t = a.last[r];
+        const bool ok = global_ok && s >= 0 && e > s && e <= global_end && t >= 1 && t <= kPage;
+        pstart[r] = s;
+        ptail[r] = t;
+        prefix[r + 1] = ok ? e - s : 0;
     }
     __syncthreads();
     if (warp == 0) {
@@ -144,10 +152,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         const int which = lane & 1; // 0: K box, 1: V box
         const bool lane_active = my_slot < a.pps;
         const CUtensorMap *map = which == 0 ? &k_map : &v_map;
-        if (lane == 0) {
-            prefetch_tensormap(&k_map);
-            prefetch_tensormap(&v_map);
-        }
         // per worker of this CTA: range, and a 32-page window of (page id, head block) pairs
         // (the range starts at page y0 of item h0; one 64-bit division per worker, none per page)
         int h0[8], y0[8], count[8];
@@ -339,15 +343,17 @@ __global__ void __launch_bounds__(128)
 balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
                       int rows) {
+    dependent_launch_release();
     const int lane = threadIdx.x & 31;
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
     const int request = state / qh, qhead = state % qh;
+    dependent_launch_wait(); // the states and the prefix are complete and visible
     const int *prefix =
         reinterpret_cast<const int *>(workspace + state_floats(workers, hc, rows));
-    const int total = __ldg(prefix + batch); // three independent loads, issued together
-    const int page0 = __ldg(prefix + request);
-    const int num_pages = __ldg(prefix + request + 1) - page0;
+    const int total = __ldcg(prefix + batch); // three independent loads, issued together
+    const int page0 = __ldcg(prefix + request);
+    const int num_pages = __ldcg(prefix + request + 1) - page0;
     if (num_pages == 0) return; // invalid request: nothing was computed, nothing is published
     const int group = qh / kvh;
     const int kv_head = qhead / group, g = qhead % group;
@@ -411,18 +417,18 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    balanced_decode_kernel<<<launch.grid, launch.block, launch.shared_bytes,
-                             static_cast<cudaStream_t>(stream)>>>(k_map, v_map, args);
-    return cudaGetLastError();
+    return launch_dependent(balanced_decode_kernel, launch.grid, launch.block, launch.shared_bytes,
+                            stream, k_map, v_map, args);
 }
 
 int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block,
                           void *stream) {
-    balanced_merge_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
-        launch.workspace, static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.batch,
-        launch.qh, launch.kvh, launch.heads_per_cta, launch.q_tiles, launch.q_blocks,
-        (int)launch.grid * launch.pages_per_stage, balanced_state_rows(launch));
-    return cudaGetLastError();
+    return launch_dependent(balanced_merge_kernel, grid, block, 0, stream,
+                            (const float *)launch.workspace,
+                            static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.batch,
+                            launch.qh, launch.kvh, launch.heads_per_cta, launch.q_tiles,
+                            launch.q_blocks, (int)launch.grid * launch.pages_per_stage,
+                            balanced_state_rows(launch));
 }
 
 } // namespace lb
