@@ -429,7 +429,11 @@ def ragged_c5(args):
     jobs = []
     for index, (label, qh, kvh, family) in enumerate((("MQA 32/1", 32, 1, lens[:256]),
                                                       ("GQA4 32/8", 32, 8, lens[256:]))):
-        owned = sharding.balanced_assignment(family, world)[rank]
+        if args.shard:  # one rank's share of an N-way split, on this GPU alone (no scaling claim)
+            of, which = (int(x) for x in args.shard.split(":"))
+            owned = sharding.balanced_assignment(family, of)[which]
+        else:
+            owned = sharding.balanced_assignment(family, world)[rank]
         jobs.append(RaggedJob(lk, torch, provider, label, qh, kvh, family[owned],
                               0xC5 + 64 * index + rank, device))
     commands = sum(job.plan.commands() for job in jobs)
@@ -554,6 +558,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="c3", choices=["c1", "c3", "c4", "c5"])
     parser.add_argument("--reference-requests", type=int, default=16)
+    parser.add_argument("--shard", default="",
+                        help="c5 only, 'N:r': time rank r's share of an N-way split on one GPU")
     parser.add_argument("--batch", type=int, default=64,
                         help="requests per GPU for the c3 workload (64 = the headline shape; "
                              "smaller values are for profiler captures)")

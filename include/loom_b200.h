@@ -93,6 +93,7 @@ enum {
     LB_STATE_COUNT_OVERFLOW,
     LB_LAUNCH_CONTRACT,                  /* device or launch shape unusable; a=detail code */
     LB_UNSUPPORTED_DEVICE,               /* a=compute capability major*10+minor */
+    LB_UNSUPPORTED_ROTARY_DIMENSION,     /* RopePlanError; a=expected b=actual */
 
     /* GraphError, crates/loom-infer-cuda/src/graph/mod.rs:687-721; CaptureError :136-143 */
     LB_GRAPH_DEFAULT_STREAM_UNSUPPORTED = 400,
@@ -405,6 +406,40 @@ lb_status lb_rope_append_plan_info_get(const lb_rope_append_plan *plan,
 /* Bf16RopePagedKvAppend{,Tokens}Plan::enqueue_into, rope/mod.rs:758-830,846-933 */
 lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scope,
                                  const lb_rope_append_args *args);
+
+/* ---- stand-alone NeoX RoPE over contiguous NHD Q and K ----------------------------------------- */
+
+/* Bf16RopePosIdsSpec, crates/loom-infer/src/rope/mod.rs:9-108 */
+typedef struct lb_rope_pos_ids_spec {
+    size_t tokens, query_heads, key_heads, head_dim, rotary_dim;
+    float rope_scale, rope_theta;
+} lb_rope_pos_ids_spec;
+/* Bf16RopePosIdsSpec::new, rope/mod.rs:21-62: ZeroDimension, InvalidRotaryDimension (zero, odd
+ * or > head_dim), InvalidRopeScale (not finite or <= 0), InvalidRopeTheta (not finite or <= 1),
+ * ElementCountOverflow. */
+lb_status lb_rope_pos_ids_spec_new(size_t tokens, size_t query_heads, size_t key_heads,
+                                   size_t head_dim, size_t rotary_dim, float rope_scale,
+                                   float rope_theta, lb_rope_pos_ids_spec *out);
+size_t lb_rope_pos_ids_spec_query_numel(const lb_rope_pos_ids_spec *spec);
+size_t lb_rope_pos_ids_spec_key_numel(const lb_rope_pos_ids_spec *spec);
+
+typedef struct lb_rope_pos_ids_plan lb_rope_pos_ids_plan; /* Bf16RopePosIdsPlan */
+/* Bf16RopePosIdsArgs, crates/loom-infer-cuda/src/rope/mod.rs (resolve_rrrww at :705-711) */
+typedef struct lb_rope_pos_ids_args {
+    lb_handle query, key, position_ids; /* Read: BF16, BF16, I32 */
+    lb_handle query_output, key_output; /* Write: BF16 */
+} lb_rope_pos_ids_args;
+/* RopeProvider::plan_bf16_pos_ids, rope/mod.rs:592-626: UnsupportedHeadDimension and
+ * UnsupportedRotaryDimension unless both are 128; StateCountOverflow / StateCountOutOfRange. */
+lb_status lb_rope_pos_ids_plan_create(const lb_rope_provider *provider,
+                                      const lb_rope_pos_ids_spec *spec,
+                                      lb_rope_pos_ids_plan **out);
+void lb_rope_pos_ids_plan_destroy(lb_rope_pos_ids_plan *plan);
+/* Bf16RopePosIdsPlan::enqueue_into, rope/mod.rs:698-742.  One command.  A token whose position
+ * id is negative is left unwritten by the device guard (rope/mod.rs:64-67); the other tokens of
+ * the call are rotated. */
+lb_status lb_rope_pos_ids_enqueue(const lb_rope_pos_ids_plan *plan, lb_scope *scope,
+                                  const lb_rope_pos_ids_args *args);
 
 /* ---- fixed-address CUDA Graph ------------------------------------------------------------------ */
 

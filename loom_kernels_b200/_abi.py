@@ -38,6 +38,12 @@ class AppendTokensSpec(ctypes.Structure):
     _fields_ = [("paged", PagedSpec), ("tokens", c_size_t), ("max_tokens", c_size_t)]
 
 
+class RopePosIdsSpec(ctypes.Structure):
+    _fields_ = [("tokens", c_size_t), ("query_heads", c_size_t), ("key_heads", c_size_t),
+                ("head_dim", c_size_t), ("rotary_dim", c_size_t), ("rope_scale", c_float),
+                ("rope_theta", c_float)]
+
+
 class Handle(ctypes.Structure):
     _fields_ = [("set_id", c_uint64), ("slot", c_uint32), ("dtype", c_uint8),
                 ("access", c_uint8), ("reserved", c_uint16)]
@@ -67,6 +73,11 @@ class AppendArgs(ctypes.Structure):
     _fields_ = [(name, Handle) for name in
                 ("query", "key", "value", "batch_indices", "positions", "page_indptr",
                  "page_indices", "last_page_len", "query_output", "key_pages", "value_pages")]
+
+
+class RopePosIdsArgs(ctypes.Structure):
+    _fields_ = [(name, Handle) for name in
+                ("query", "key", "position_ids", "query_output", "key_output")]
 
 
 class AppendPlanInfo(ctypes.Structure):
@@ -155,6 +166,14 @@ SIGNATURES = {
     "lb_rope_append_plan_destroy": (None, [c_void_p]),
     "lb_rope_append_plan_info_get": (c_int32, [c_void_p, POINTER(AppendPlanInfo)]),
     "lb_rope_append_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(AppendArgs)]),
+    "lb_rope_pos_ids_spec_new": (c_int32, [c_size_t] * 5 + [c_float, c_float,
+                                                            POINTER(RopePosIdsSpec)]),
+    "lb_rope_pos_ids_spec_query_numel": (c_size_t, [POINTER(RopePosIdsSpec)]),
+    "lb_rope_pos_ids_spec_key_numel": (c_size_t, [POINTER(RopePosIdsSpec)]),
+    "lb_rope_pos_ids_plan_create": (c_int32, [c_void_p, POINTER(RopePosIdsSpec),
+                                              POINTER(c_void_p)]),
+    "lb_rope_pos_ids_plan_destroy": (None, [c_void_p]),
+    "lb_rope_pos_ids_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(RopePosIdsArgs)]),
     "lb_graph_queue_create": (c_int32, [c_int, c_size_t, POINTER(c_void_p)]),
     "lb_graph_queue_destroy": (None, [c_void_p]),
     "lb_graph_queue_bindings": (c_int32, [c_void_p, c_size_t, POINTER(c_void_p)]),

@@ -610,11 +610,72 @@ class Bf16RopePagedKvAppendTokensArgs:
     value_pages: Write
 
 
+class Bf16RopePosIdsSpec:
+    """Standard NeoX split-half RoPE over contiguous NHD Q and K
+    (crates/loom-infer/src/rope/mod.rs:9-108)."""
+
+    def __init__(self, raw: _abi.RopePosIdsSpec):
+        self._raw = raw
+
+    @classmethod
+    def new(cls, tokens, query_heads, key_heads, head_dim=HEAD_DIM, rotary_dim=HEAD_DIM,
+            rope_scale=1.0, rope_theta=10000.0):
+        raw = _abi.RopePosIdsSpec()
+        _check(_abi.load().lb_rope_pos_ids_spec_new(tokens, query_heads, key_heads, head_dim,
+                                                    rotary_dim, rope_scale, rope_theta, byref(raw)))
+        return cls(raw)
+
+    def tokens(self): return self._raw.tokens
+    def query_heads(self): return self._raw.query_heads
+    def key_heads(self): return self._raw.key_heads
+    def head_dim(self): return self._raw.head_dim
+    def rotary_dim(self): return self._raw.rotary_dim
+    def rope_scale(self): return self._raw.rope_scale
+    def rope_theta(self): return self._raw.rope_theta
+    def query_numel(self): return _abi.load().lb_rope_pos_ids_spec_query_numel(byref(self._raw))
+    def key_numel(self): return _abi.load().lb_rope_pos_ids_spec_key_numel(byref(self._raw))
+    def position_numel(self): return self._raw.tokens
+
+
+@dataclass
+class Bf16RopePosIdsArgs:
+    """crates/loom-infer-cuda/src/rope/mod.rs (Bf16RopePosIdsArgs::new)."""
+    query: Read
+    key: Read
+    position_ids: Read
+    query_output: Write
+    key_output: Write
+
+
+class Bf16RopePosIdsPlan:
+    """rope/mod.rs:694-742."""
+
+    def __init__(self, ptr, spec):
+        self._ptr, self._spec = ptr, spec
+
+    def __del__(self):
+        _dispose(self, "lb_rope_pos_ids_plan_destroy")
+
+    def spec(self): return self._spec
+
+    def enqueue_into(self, scope: "CommandScope", args: Bf16RopePosIdsArgs):
+        raw = _abi.RopePosIdsArgs(query=args.query._raw, key=args.key._raw,
+                                  position_ids=args.position_ids._raw,
+                                  query_output=args.query_output._raw,
+                                  key_output=args.key_output._raw)
+        _check(_abi.load().lb_rope_pos_ids_enqueue(self._ptr, scope._ptr, byref(raw)))
+
+
 class RopeProvider:
     """rope/mod.rs:579-683."""
 
     def __init__(self, ptr):
         self._ptr = ptr
+
+    def plan_bf16_pos_ids(self, spec: Bf16RopePosIdsSpec) -> Bf16RopePosIdsPlan:
+        out = c_void_p()
+        _check(_abi.load().lb_rope_pos_ids_plan_create(self._ptr, byref(spec._raw), byref(out)))
+        return Bf16RopePosIdsPlan(out.value, spec)
 
     @classmethod
     def load(cls, device: int = 0) -> "RopeProvider":

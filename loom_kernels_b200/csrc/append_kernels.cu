@@ -288,7 +288,65 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
     LB_STAMP(6);
 }
 
+// Stand-alone NeoX RoPE over contiguous NHD Q and K (the reference's rope_pos_ids_bf16_neox_d128,
+// crates/loom-infer-cuda/src/rope/mod.rs:44-94): the same rotation as the append, output to
+// separate Q/K buffers.  A CTA walks tokens blockIdx.x, blockIdx.x + grid, ...; 64 threads build
+// the token's sin/cos table, 8 lanes per head row rotate.  A token with a negative position id is
+// left unwritten (the reference's device guard, :64-67); other tokens are not affected.
+constexpr int kRopeThreads = 256;
+
+struct RopeArgs {
+    const uint4 *query, *key;
+    const int32_t *position_ids;
+    uint4 *query_output, *key_output;
+    int32_t tokens, qh, kh;
+    float inverse_frequency[kPairs]; // powf(theta, -2i/128) / scale, computed on the host
+};
+
+__global__ void __launch_bounds__(kRopeThreads) rope_pos_ids_kernel(const RopeArgs a) {
+    __shared__ __align__(16) float2 table[kPairs];
+    dev::dependent_launch_release();
+    const int tid = threadIdx.x;
+    const int row_tasks = (a.qh + a.kh) * 8;
+    dev::dependent_launch_wait();
+    for (int token = blockIdx.x; token < a.tokens; token += gridDim.x) {
+        const int position = a.position_ids[token];
+        if (position < 0) continue; // uniform over the CTA
+        __syncthreads();            // the previous token's table is no longer read
+        if (tid < kPairs) {
+            const float angle = __fmul_rn((float)position, a.inverse_frequency[tid]);
+            double s, c;
+            sincos((double)angle, &s, &c);
+            table[tid] = make_float2((float)s, (float)c);
+        }
+        __syncthreads();
+        for (int task = tid; task < row_tasks; task += kRopeThreads) {
+            const int row = task >> 3, j = task & 7;
+            const bool is_query = row < a.qh;
+            const size_t offset = is_query ? ((size_t)token * a.qh + row) * (kHeadDim / 8)
+                                           : ((size_t)token * a.kh + (row - a.qh)) * (kHeadDim / 8);
+            const uint4 *src = (is_query ? a.query : a.key) + offset;
+            uint4 *dst = (is_query ? a.query_output : a.key_output) + offset;
+            rotate_row(src[j], src[8 + j], dst, j, table);
+        }
+    }
+}
+
 } // namespace
+
+int launch_rope_pos_ids(const RopeLaunch &launch, void *stream) {
+    RopeArgs args;
+    args.query = static_cast<const uint4 *>(launch.query);
+    args.key = static_cast<const uint4 *>(launch.key);
+    args.position_ids = launch.position_ids;
+    args.query_output = static_cast<uint4 *>(launch.query_output);
+    args.key_output = static_cast<uint4 *>(launch.key_output);
+    args.tokens = launch.tokens;
+    args.qh = launch.qh;
+    args.kh = launch.kh;
+    for (int i = 0; i < kPairs; ++i) args.inverse_frequency[i] = launch.inverse_frequency[i];
+    return launch_dependent(rope_pos_ids_kernel, launch.grid, kRopeThreads, 0, stream, args);
+}
 
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency) {
     int rc = cudaMemcpyToSymbol(c_inverse_frequency, inverse_frequency, sizeof(float) * kPairs);

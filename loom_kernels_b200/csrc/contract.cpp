@@ -480,4 +480,36 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
     return LB_OK;
 }
 
+// Bf16RopePosIdsSpec::new, crates/loom-infer/src/rope/mod.rs:21-62 (same order of checks)
+lb_status lb_rope_pos_ids_spec_new(size_t tokens, size_t query_heads, size_t key_heads,
+                                   size_t head_dim, size_t rotary_dim, float rope_scale,
+                                   float rope_theta, lb_rope_pos_ids_spec *out) {
+    if (!out) return fail(LB_INVALID_ARGUMENT, "out");
+    if (tokens == 0 || query_heads == 0 || key_heads == 0 || head_dim == 0)
+        return fail(LB_ZERO_DIMENSION);
+    if (rotary_dim == 0 || rotary_dim % 2 != 0 || rotary_dim > head_dim)
+        return fail(LB_INVALID_ROTARY_DIMENSION, nullptr, (int64_t)rotary_dim, (int64_t)head_dim);
+    if (!std::isfinite(rope_scale) || rope_scale <= 0.0f) return fail(LB_INVALID_ROPE_SCALE);
+    if (!std::isfinite(rope_theta) || rope_theta <= 1.0f) return fail(LB_INVALID_ROPE_THETA);
+    size_t t;
+    if (mul_overflow(tokens, query_heads, &t) || mul_overflow(t, head_dim, &t) ||
+        mul_overflow(tokens, key_heads, &t) || mul_overflow(t, head_dim, &t))
+        return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    out->tokens = tokens;
+    out->query_heads = query_heads;
+    out->key_heads = key_heads;
+    out->head_dim = head_dim;
+    out->rotary_dim = rotary_dim;
+    out->rope_scale = rope_scale;
+    out->rope_theta = rope_theta;
+    return LB_OK;
+}
+
+size_t lb_rope_pos_ids_spec_query_numel(const lb_rope_pos_ids_spec *spec) {
+    return spec ? spec->tokens * spec->query_heads * spec->head_dim : 0;
+}
+size_t lb_rope_pos_ids_spec_key_numel(const lb_rope_pos_ids_spec *spec) {
+    return spec ? spec->tokens * spec->key_heads * spec->head_dim : 0;
+}
+
 }

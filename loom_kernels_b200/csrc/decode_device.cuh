@@ -303,43 +303,82 @@ __device__ __forceinline__ void write_state_row(float *state, int lane, int half
 // `publish` is consulted only after every load has been issued, so a caller can hand in a
 // predicate that itself depends on loads still in flight (the request guard) without putting a
 // second memory round trip in front of the state loads.
+constexpr int kMergeBatch = 16; // states whose row loads are in flight together
+
+// The part of a merge one warp computes: the global maximum over all n states, then the weighted
+// sums over states first, first + stride, ... (per lane: four of the 128 dims; `norm` is complete
+// in every lane).  Returns false when a state is poisoned.
 template <typename StateOf>
-__device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, bool publish,
-                                             __nv_bfloat16 *out_row, float *lse_slot) {
-    float top = -INFINITY;
+__device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane, int first,
+                                              int stride, float &top, float &norm, float4 &acc) {
+    top = -INFINITY;
     bool poisoned = false;
     for (int i = lane; i < n; i += 32) {
         const float *s = state_of(i);
         if (s == nullptr) continue;
-        const float norm = __ldcg(s + 1);
-        poisoned |= norm < 0.0f;
-        if (norm > 0.0f) top = fmaxf(top, __ldcg(s));
+        const float part_norm = __ldcg(s + 1);
+        poisoned |= part_norm < 0.0f;
+        if (part_norm > 0.0f) top = fmaxf(top, __ldcg(s));
     }
-    if (__any_sync(0xffffffffu, poisoned)) return;
+    if (__any_sync(0xffffffffu, poisoned)) return false;
 #pragma unroll
     for (int d = 16; d >= 1; d >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, d));
-    float norm = 0.0f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int i = 0; i < n; ++i) {
-        const float *s = state_of(i);
-        if (s == nullptr) continue;
-        const float part_norm = __ldcg(s + 1);
-        const float weight = part_norm > 0.0f ? exp2f(__ldcg(s) - top) : 0.0f;
-        const float2 lo = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
-        const float2 hi = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
-        norm += part_norm * weight;
-        acc.x += lo.x * weight;
-        acc.y += lo.y * weight;
-        acc.z += hi.x * weight;
-        acc.w += hi.y * weight;
+    // 32 states per round: lane l computes the weight of its state once, then the rows are
+    // accumulated sixteen states at a time with all 32 loads of a batch in flight together
+    // (a long request is cut into a hundred states; one load latency per state would dominate)
+    norm = 0.0f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int mine_n = first < n ? (n - first + stride - 1) / stride : 0;
+    for (int base = 0; base < mine_n; base += 32) {
+        const float *mine = base + lane < mine_n ? state_of(first + (base + lane) * stride) : nullptr;
+        const float my_norm = mine ? __ldcg(mine + 1) : 0.0f;
+        const float my_weight = my_norm > 0.0f ? exp2f(__ldcg(mine) - top) : 0.0f;
+        norm += my_norm * my_weight;
+        const int count = min(32, mine_n - base);
+        for (int j = 0; j < count; j += kMergeBatch) {
+            float2 lo[kMergeBatch], hi[kMergeBatch];
+#pragma unroll
+            for (int u = 0; u < kMergeBatch; ++u) {
+                const float *s =
+                    j + u < count ? state_of(first + (base + j + u) * stride) : nullptr;
+                lo[u] = hi[u] = make_float2(0.f, 0.f);
+                if (s != nullptr) {
+                    lo[u] = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
+                    hi[u] = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kMergeBatch; ++u) {
+                const float weight = __shfl_sync(0xffffffffu, my_weight, (j + u) & 31);
+                acc.x += lo[u].x * weight;
+                acc.y += lo[u].y * weight;
+                acc.z += hi[u].x * weight;
+                acc.w += hi[u].y * weight;
+            }
+        }
     }
-    if (!publish) return;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) norm += __shfl_xor_sync(0xffffffffu, norm, d);
+    return true;
+}
+
+// BF16 O + log2 LSE of a merged row: lane l writes dims 4l .. 4l + 3.
+__device__ __forceinline__ void publish_merged(float top, float norm, float4 acc, int lane,
+                                               __nv_bfloat16 *out_row, float *lse_slot) {
     uint2 packed;
     packed.x = pack_bf16(acc.x / norm, acc.y / norm);
     packed.y = pack_bf16(acc.z / norm, acc.w / norm);
     *reinterpret_cast<uint2 *>(out_row + lane * 4) = packed;
     if (lane == 0) *lse_slot = top + log2f(norm);
+}
+
+template <typename StateOf>
+__device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, bool publish,
+                                             __nv_bfloat16 *out_row, float *lse_slot) {
+    float top, norm;
+    float4 acc;
+    if (!merge_partial(state_of, n, lane, 0, 1, top, norm, acc) || !publish) return;
+    publish_merged(top, norm, acc, lane, out_row, lse_slot);
 }
 
 // The even cut of `total` units over `workers` workers, evaluated without 64-bit division:

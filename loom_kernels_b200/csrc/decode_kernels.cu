@@ -146,17 +146,22 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         const int z = hb * a.hc * 2;
         const CUtensorMap *map = which == 0 ? &k_map : &v_map;
         bool bad_page = false;
-        auto load_page = [&](int j) -> int {
-            if (j >= cnt) return 0;
-            const int id = a.indices[page_start + pg0 + j];
+        auto fetch_page = [&](int j) -> int { // the raw id (0 past the chunk)
+            return j < cnt ? a.indices[page_start + pg0 + j] : 0;
+        };
+        auto check_page = [&](int id) -> int {
             if (id < 0 || id >= a.max_pages) {
                 bad_page = true;
                 return 0;
             }
             return id;
         };
-        int window = load_page(lane);
-        int window_next = load_page(32 + lane);
+        auto load_page = [&](int j) -> int { return check_page(fetch_page(j)); };
+        // the first two windows travel together
+        int window = fetch_page(lane);
+        int window_next = fetch_page(32 + lane);
+        window = check_page(window);
+        window_next = check_page(window_next);
         LB_STAMP(3);
         const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
         const uint32_t my_tile =

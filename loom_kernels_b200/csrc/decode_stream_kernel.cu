@@ -99,6 +99,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
+    LB_STAMP(0);
 
     // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
     const int global_end = a.indptr[a.batch];
@@ -110,6 +111,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         ptail[r] = t;
         prefix[r + 1] = ok ? e - s : 0;
     }
+    LB_STAMP(1);
     __syncthreads();
     if (warp == 0) {
         // inclusive scan of prefix[1..batch] by one warp: per-lane chunks, then a warp scan
@@ -129,6 +131,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
     }
     __syncthreads();
+    LB_STAMP(2);
     const int total = prefix[a.batch];
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
@@ -145,6 +148,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if ((int)blockIdx.x * a.pps >= cut.workers) return;
 
     const int rows_per_block = 16 * a.mt;
+    LB_STAMP(8);
 
     if (warp == kComputeWarps) {
         // ================= producer warp ==========================================================
@@ -152,45 +156,46 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         const int which = lane & 1; // 0: K box, 1: V box
         const bool lane_active = my_slot < a.pps;
         const CUtensorMap *map = which == 0 ? &k_map : &v_map;
-        // per worker of this CTA: range, and a 32-page window of (page id, head block) pairs
-        // (the range starts at page y0 of item h0; one 64-bit division per worker, none per page)
-        int h0[8], y0[8], count[8];
-        int win_id[8], win_hb[8], next_id[8], next_hb[8];
-        int longest = 0;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            h0[s] = 0;
-            y0[s] = 0;
-            count[s] = 0;
-            const int w = blockIdx.x * a.pps + s;
-            if (s < a.pps && w < cut.workers) {
+        // Page lookup is spread over the lanes: the warp's 32 lanes hold a window of 32 / pps pages
+        // for each of the CTA's pps workers; lane l looks after page (l % window) of worker
+        // (l / window).  So the range of a worker (it starts at page y0 of item h0; one 64-bit
+        // division) and every window refill cost one lane's work, whatever pps is.
+        const int window = 32 / a.pps;
+        const int look_slot = lane / window, look_j = lane & (window - 1);
+        int h0 = 0, y0 = 0, count = 0;
+        {
+            const int w = blockIdx.x * a.pps + look_slot;
+            if (w < cut.workers) {
                 const long long begin = cut.begin(w);
-                h0[s] = (int)(begin / total);
-                y0[s] = (int)(begin - (long long)h0[s] * total);
-                count[s] = (int)(cut.begin(w + 1) - begin);
-                longest = max(longest, count[s]);
+                h0 = (int)(begin / total);
+                y0 = (int)(begin - (long long)h0 * total);
+                count = (int)(cut.begin(w + 1) - begin);
             }
         }
-        auto load_window = [&](int s, int first, int &id_out, int &hb_out) {
-            id_out = 0;
-            hb_out = 0;
-            const int j = first + lane;
-            if (j >= count[s]) return;
-            const unsigned pos = (unsigned)y0[s] + (unsigned)j; // < 2 * total: one wrap at most...
-            const int wraps = (int)(pos / (unsigned)total);     // ...unless the item line is short
-            const int h = h0[s] + wraps;
+        int longest = count;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1)
+            longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, d));
+        // (page id or -1, head block) of page first + look_j of my worker's range
+        auto look_up = [&](int first, int &id, int &hb) {
+            id = 0;
+            hb = 0;
+            const int j = first + look_j;
+            if (j >= count) return;
+            const unsigned pos = (unsigned)y0 + (unsigned)j; // one wrap at most, unless the item
+            const int wraps = (int)(pos / (unsigned)total);  // line is short
             const int y = (int)(pos - (unsigned)wraps * (unsigned)total);
             const int r = owner_of(prefix, a.batch, y);
-            const int id = a.indices[pstart[r] + (y - prefix[r])];
-            hb_out = h / a.qb;
-            id_out = (id < 0 || id >= a.max_pages) ? -1 : id;
+            id = a.indices[pstart[r] + (y - prefix[r])];
+            if (id < 0 || id >= a.max_pages) id = -1;
+            hb = (h0 + wraps) / a.qb;
         };
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-            if (s < a.pps) {
-                load_window(s, 0, win_id[s], win_hb[s]);
-                load_window(s, 32, next_id[s], next_hb[s]);
-            }
+        int win_id, win_hb, next_id = 0, next_hb = 0;
+        LB_STAMP(9);
+        look_up(0, win_id, win_hb);
+        LB_STAMP(10);
+        const int my_source = (my_slot & (a.pps - 1)) * window; // first lane of my worker's window
+        const int my_count = __shfl_sync(0xffffffffu, count, my_source);
         const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
         const uint32_t my_tile =
             smem_u32(ring + my_slot * slot_bytes + which * (slot_bytes / 2));
@@ -198,28 +203,14 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         uint32_t phase = 0;    // parity of the ring round being filled
         bool recycled = false; // the ring has wrapped: a slot must be handed back before reuse
         for (int j = 0; j < longest; ++j) {
-            if (j > 0 && (j & 31) == 0) {
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    if (s < a.pps) {
-                        win_id[s] = next_id[s];
-                        win_hb[s] = next_hb[s];
-                        load_window(s, j + 32, next_id[s], next_hb[s]);
-                    }
+            if (j > 0 && (j & (window - 1)) == 0) {
+                win_id = next_id;
+                win_hb = next_hb;
+                if (j + window < longest) look_up(j + window, next_id, next_hb);
             }
-            int page_id = 0, hb = 0;
-            int my_count = 0;
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-                if (s < a.pps) {
-                    const int id = __shfl_sync(0xffffffffu, win_id[s], j & 31);
-                    const int h = __shfl_sync(0xffffffffu, win_hb[s], j & 31);
-                    if (my_slot == s) {
-                        page_id = id;
-                        hb = h;
-                        my_count = count[s];
-                    }
-                }
+            const int source = my_source + (j & (window - 1));
+            const int page_id = __shfl_sync(0xffffffffu, win_id, source);
+            const int hb = __shfl_sync(0xffffffffu, win_hb, source);
             const bool has = lane_active && j < my_count;
             const uint32_t bar_full = my_full + stage * a.pps * 8;
             bool ok = true;
@@ -236,6 +227,11 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             if (has)
                 tma_load_3d(my_tile + stage * stage_bytes, map, 0, max(page_id, 0) * kPage,
                             hb * a.hc * 2, bar_full);
+            if (j == 0) {
+                LB_STAMP(3);
+                // the second window is fetched once the first pages are on their way
+                if (window < longest) look_up(window, next_id, next_hb);
+            }
             if (++stage == a.stages) {
                 stage = 0;
                 phase ^= 1;
@@ -289,6 +285,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     live = false;
                     break;
                 }
+                if (p == 0 && first_segment) LB_STAMP(4);
                 bad |= bad_slot[stage * a.pps + my_slot] != 0;
                 uint8_t *k_tile = ring + stage * stage_bytes + tile_offset;
                 const bool wrote =
@@ -324,6 +321,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     write_state_row(slot, lane, half, st, bad);
                 }
             }
+            if (first_segment) LB_STAMP(5);
             first_segment = false;
             remaining -= seg_pages;
             y += seg_pages;
@@ -333,12 +331,14 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             }
         }
     }
+    LB_STAMP(6);
     __syncthreads();
+    LB_STAMP(7);
     if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);
 }
 
 // One warp per (request, query head): finds the workers whose ranges cut this head's item and
-// merges their states in worker order.  Items that one worker finished alone are skipped.
+// merges their states.  Items that one worker finished alone are skipped.
 __global__ void __launch_bounds__(128)
 balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,

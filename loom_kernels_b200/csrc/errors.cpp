@@ -70,6 +70,7 @@ const Entry kNames[] = {
     {LB_STATE_COUNT_OVERFLOW, "StateCountOverflow"},
     {LB_LAUNCH_CONTRACT, "Launch"},
     {LB_UNSUPPORTED_DEVICE, "UnsupportedDevice"},
+    {LB_UNSUPPORTED_ROTARY_DIMENSION, "UnsupportedRotaryDimension"},
     {LB_GRAPH_DEFAULT_STREAM_UNSUPPORTED, "DefaultStreamUnsupported"},
     {LB_GRAPH_EMPTY_CAPTURE, "EmptyCapture"},
     {LB_GRAPH_CAPTURE_INVALIDATED, "CaptureInvalidated"},
@@ -211,6 +212,9 @@ void format_message(lb_error_info &e) {
     case LB_UNSUPPORTED_DEVICE:
         snprintf(m, n, "kernels are built for sm_100a; device reports compute capability %lld.%lld",
                  a / 10, a % 10);
+        break;
+    case LB_UNSUPPORTED_ROTARY_DIMENSION:
+        snprintf(m, n, "RoPE provider supports rotary dimension %lld, got %lld", a, b);
         break;
     case LB_GRAPH_DEFAULT_STREAM_UNSUPPORTED:
         snprintf(m, n, "CUDA Graph capture requires a non-default stream");

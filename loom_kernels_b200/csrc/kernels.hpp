@@ -56,6 +56,16 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream);
 int launch_split_merge(const MergeLaunch &launch, void *stream);
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency);
 int launch_rope_append(const AppendLaunch &launch, void *stream);
+// One stand-alone RoPE launch over contiguous NHD Q and K.
+struct RopeLaunch {
+    const void *query, *key;   // bf16 [tokens, heads, 128]
+    const int32_t *position_ids;
+    void *query_output, *key_output;
+    int32_t tokens, qh, kh;
+    float inverse_frequency[64];
+    uint32_t grid;
+};
+int launch_rope_pos_ids(const RopeLaunch &launch, void *stream);
 int append_block_threads();       // threads per CTA the append kernel is built for
 int append_max_tokens_per_cta();  // tokens one CTA can own (grid floor = tokens / this)
 

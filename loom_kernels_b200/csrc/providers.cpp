@@ -42,6 +42,13 @@ struct lb_rope_append_plan {
     uint32_t grid = 0, block = 256, shared_bytes = 0, hash_slots = 0;
 };
 
+struct lb_rope_pos_ids_plan {
+    lb_rope_pos_ids_spec spec;
+    int device = 0;
+    uint32_t grid = 0;
+    float inverse_frequency[64];
+};
+
 namespace {
 
 const float kLog2E = 1.44269504088896340736f;
@@ -495,6 +502,87 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     launch.shared_bytes = plan->shared_bytes;
     void *stream = scope->queue->stream;
     return submit_launch(*scope, [&]() { return launch_rope_append(launch, stream); });
+}
+
+// ---- stand-alone RoPE ------------------------------------------------------------------------------
+
+lb_status lb_rope_pos_ids_plan_create(const lb_rope_provider *provider,
+                                      const lb_rope_pos_ids_spec *spec,
+                                      lb_rope_pos_ids_plan **out) {
+    if (!provider || !spec || !out) return fail(LB_INVALID_ARGUMENT, "provider");
+    *out = nullptr;
+    lb_rope_pos_ids_spec checked;
+    lb_status rc = lb_rope_pos_ids_spec_new(spec->tokens, spec->query_heads, spec->key_heads,
+                                            spec->head_dim, spec->rotary_dim, spec->rope_scale,
+                                            spec->rope_theta, &checked);
+    if (rc) return rc;
+    // plan_bf16_pos_ids, crates/loom-infer-cuda/src/rope/mod.rs:592-626
+    if (checked.head_dim != LB_HEAD_DIM)
+        return fail(LB_UNSUPPORTED_HEAD_DIMENSION, nullptr, LB_HEAD_DIM, (int64_t)checked.head_dim);
+    if (checked.rotary_dim != LB_HEAD_DIM)
+        return fail(LB_UNSUPPORTED_ROTARY_DIMENSION, nullptr, LB_HEAD_DIM,
+                    (int64_t)checked.rotary_dim);
+    size_t heads, states;
+    if (__builtin_add_overflow(checked.query_heads, checked.key_heads, &heads) ||
+        __builtin_mul_overflow(checked.tokens, heads, &states))
+        return fail(LB_STATE_COUNT_OVERFLOW);
+    if (states > 0xffffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)states);
+    lb_rope_pos_ids_plan *plan = new lb_rope_pos_ids_plan();
+    plan->spec = checked;
+    plan->device = provider->device;
+    const size_t cap = 8u * (size_t)(provider->sm_count ? provider->sm_count : 148);
+    plan->grid = (uint32_t)(checked.tokens < cap ? checked.tokens : cap);
+    // the CPU reference's expression (crates/loom-infer/src/rope/mod.rs:148-149), evaluated in
+    // F32 on the host so that the device angle is bit-identical to the reference's
+    for (int pair = 0; pair < 64; ++pair) {
+        const float exponent = 2.0f * (float)pair / (float)checked.rotary_dim;
+        plan->inverse_frequency[pair] = powf(checked.rope_theta, -exponent) / checked.rope_scale;
+    }
+    *out = plan;
+    return LB_OK;
+}
+
+void lb_rope_pos_ids_plan_destroy(lb_rope_pos_ids_plan *plan) { delete plan; }
+
+lb_status lb_rope_pos_ids_enqueue(const lb_rope_pos_ids_plan *plan, lb_scope *scope,
+                                  const lb_rope_pos_ids_args *args) {
+    if (!plan || !scope || !args) return fail(LB_INVALID_ARGUMENT, "plan");
+    const lb_rope_pos_ids_spec &spec = plan->spec;
+    if (scope->queue->device != plan->device)
+        return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
+    lb_status rc = require_command_capacity(*scope, 1);
+    if (rc) return rc;
+    OperandRequest requests[5] = {
+        {args->query, LB_BF16, false},       {args->key, LB_BF16, false},
+        {args->position_ids, LB_I32, false}, {args->query_output, LB_BF16, true},
+        {args->key_output, LB_BF16, true},
+    };
+    Operand op[5];
+    if ((rc = resolve(*scope, requests, 5, op))) return rc;
+    const size_t q_numel = lb_rope_pos_ids_spec_query_numel(&spec);
+    const size_t k_numel = lb_rope_pos_ids_spec_key_numel(&spec);
+    if ((rc = require_exact_len("query", op[0].numel, q_numel))) return rc;
+    if ((rc = require_exact_len("key", op[1].numel, k_numel))) return rc;
+    if ((rc = require_exact_len("position_ids", op[2].numel, spec.tokens))) return rc;
+    if ((rc = require_exact_len("query_output", op[3].numel, q_numel))) return rc;
+    if ((rc = require_exact_len("key_output", op[4].numel, k_numel))) return rc;
+    if ((rc = require_alignment("query", op[0].ptr, 16))) return rc;
+    if ((rc = require_alignment("key", op[1].ptr, 16))) return rc;
+    if ((rc = require_alignment("query_output", op[3].ptr, 16))) return rc;
+    if ((rc = require_alignment("key_output", op[4].ptr, 16))) return rc;
+    RopeLaunch launch;
+    launch.query = op[0].ptr;
+    launch.key = op[1].ptr;
+    launch.position_ids = (const int32_t *)op[2].ptr;
+    launch.query_output = op[3].ptr;
+    launch.key_output = op[4].ptr;
+    launch.tokens = (int32_t)spec.tokens;
+    launch.qh = (int32_t)spec.query_heads;
+    launch.kh = (int32_t)spec.key_heads;
+    memcpy(launch.inverse_frequency, plan->inverse_frequency, sizeof(launch.inverse_frequency));
+    launch.grid = plan->grid;
+    void *stream = scope->queue->stream;
+    return submit_launch(*scope, [&]() { return launch_rope_pos_ids(launch, stream); });
 }
 
 }

@@ -405,6 +405,57 @@ def test_rope_append_enqueue_preflight(fake):
         provider.plan_bf16_paged_append_tokens(lk.Bf16RopePagedKvAppendTokensSpec.new(65, 1, 4, 1, 1))
 
 
+def test_rope_pos_ids_contract_and_preflight(fake):
+    """Bf16RopePosIdsSpec::new (crates/loom-infer/src/rope/mod.rs:21-62), plan_bf16_pos_ids
+    (crates/loom-infer-cuda/src/rope/mod.rs:592-626) and the enqueue preflight (:698-742)."""
+    for args, variant in [((0, 16, 4), "ZeroDimension"), ((5, 0, 4), "ZeroDimension"),
+                          ((5, 16, 4, 128, 0), "InvalidRotaryDimension"),
+                          ((5, 16, 4, 128, 63), "InvalidRotaryDimension"),
+                          ((5, 16, 4, 128, 130), "InvalidRotaryDimension"),
+                          ((5, 16, 4, 128, 128, 0.0), "InvalidRopeScale"),
+                          ((5, 16, 4, 128, 128, float("inf")), "InvalidRopeScale"),
+                          ((5, 16, 4, 128, 128, 1.0, 1.0), "InvalidRopeTheta"),
+                          ((5, 16, 4, 128, 128, 1.0, float("nan")), "InvalidRopeTheta"),
+                          ((2 ** 62, 16, 4), "ElementCountOverflow")]:
+        with pytest.raises(lk.ContractError) as e:
+            lk.Bf16RopePosIdsSpec.new(*args)
+        assert e.value.variant == variant, args
+    spec = lk.Bf16RopePosIdsSpec.new(5, 16, 4, 128, 128, 1.0, 10000.0)
+    assert (spec.query_numel(), spec.key_numel(), spec.position_numel()) == (10240, 2560, 5)
+    provider = lk.RopeProvider.load(0)
+    with pytest.raises(lk.LoomError) as e:  # partial rotary dimension: rejected before submission
+        provider.plan_bf16_pos_ids(lk.Bf16RopePosIdsSpec.new(5, 16, 4, 128, 64))
+    assert (e.value.variant, e.value.payload[:2]) == ("UnsupportedRotaryDimension", (128, 64))
+    with pytest.raises(lk.LoomError) as e:
+        provider.plan_bf16_pos_ids(lk.Bf16RopePosIdsSpec.new(5, 16, 4, 64, 64))
+    assert (e.value.variant, e.value.payload[:2]) == ("UnsupportedHeadDimension", (128, 64))
+    plan = provider.plan_bf16_pos_ids(spec)
+    queue = lk.CommandQueue(0x100, 1)
+    names = ["query", "key", "position_ids", "query_output", "key_output"]
+    sizes = [10240, 2560, 5, 10240, 2560]
+
+    def setup(short=None):
+        b = queue.bindings(5)
+        h = []
+        for i, (name, numel) in enumerate(zip(names, sizes)):
+            span = D(0x30000000 + i * 0x1000000, numel - (name == short),
+                     _abi.I32 if name == "position_ids" else _abi.BF16)
+            h.append(b.bind_read(span) if i < 3 else b.bind_read_write(span).write())
+        return b, lk.Bf16RopePosIdsArgs(*h)
+
+    for short in names:
+        b, a = setup(short)
+        scope = queue.begin(b)
+        with pytest.raises(lk.EnqueueError) as e:
+            plan.enqueue_into(scope, a)
+        assert (e.value.variant, e.value.operand) == ("LengthMismatch", short)
+        assert scope.finish().submitted() == 0
+    b, a = setup()
+    scope = queue.begin(b)
+    plan.enqueue_into(scope, a)
+    assert scope.finish().submitted() == 1
+
+
 # ---- graph state machine against the fake driver --------------------------------------------------
 
 
