@@ -441,6 +441,31 @@ void lb_rope_pos_ids_plan_destroy(lb_rope_pos_ids_plan *plan);
 lb_status lb_rope_pos_ids_enqueue(const lb_rope_pos_ids_plan *plan, lb_scope *scope,
                                   const lb_rope_pos_ids_args *args);
 
+/* ---- state merge ------------------------------------------------------------------------------- */
+
+/* Merges caller-provided attention states: the split-K merge kernel as an operator of its own.
+ * No reference counterpart yet: the reference lists merge_state(s) as planned
+ * (docs/flashinfer-parity.md:38); the arithmetic is its contiguous split-K merge
+ * (single_decode_bf16_split_k_merge_reference, crates/loom-infer/src/attention/single_decode/
+ * mod.rs:343-379).  states is F32 [rows, partitions, 130] with [max_log2, normaliser, wv[128]]
+ * per state (single_decode/mod.rs:10-13); output BF16 [rows, 128]; lse F32 [rows], base 2.  A state
+ * with a zero normaliser is skipped; a row whose states are all empty is left unwritten.  An
+ * engine that splits one request's KV over several GPUs gathers the per-GPU states and merges
+ * them with this. */
+typedef struct lb_state_merge_plan lb_state_merge_plan;
+typedef struct lb_state_merge_args {
+    lb_handle states; /* Read<f32> */
+    lb_handle output; /* Write<bf16> */
+    lb_handle lse;    /* Write<f32> */
+} lb_state_merge_args;
+/* ZeroDimension (rows or partitions zero), InvalidPartitionCount (> 65535),
+ * StateCountOutOfRange, ElementCountOverflow. */
+lb_status lb_state_merge_plan_create(const lb_decode_provider *provider, size_t rows,
+                                     size_t partitions, lb_state_merge_plan **out);
+void lb_state_merge_plan_destroy(lb_state_merge_plan *plan);
+lb_status lb_state_merge_enqueue(const lb_state_merge_plan *plan, lb_scope *scope,
+                                 const lb_state_merge_args *args);
+
 /* ---- fixed-address CUDA Graph ------------------------------------------------------------------ */
 
 typedef struct lb_graph_queue lb_graph_queue;           /* GraphQueue, graph/mod.rs:27-71 */

@@ -75,6 +75,10 @@ class AppendArgs(ctypes.Structure):
                  "page_indices", "last_page_len", "query_output", "key_pages", "value_pages")]
 
 
+class StateMergeArgs(ctypes.Structure):
+    _fields_ = [("states", Handle), ("output", Handle), ("lse", Handle)]
+
+
 class RopePosIdsArgs(ctypes.Structure):
     _fields_ = [(name, Handle) for name in
                 ("query", "key", "position_ids", "query_output", "key_output")]
@@ -166,6 +170,9 @@ SIGNATURES = {
     "lb_rope_append_plan_destroy": (None, [c_void_p]),
     "lb_rope_append_plan_info_get": (c_int32, [c_void_p, POINTER(AppendPlanInfo)]),
     "lb_rope_append_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(AppendArgs)]),
+    "lb_state_merge_plan_create": (c_int32, [c_void_p, c_size_t, c_size_t, POINTER(c_void_p)]),
+    "lb_state_merge_plan_destroy": (None, [c_void_p]),
+    "lb_state_merge_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(StateMergeArgs)]),
     "lb_rope_pos_ids_spec_new": (c_int32, [c_size_t] * 5 + [c_float, c_float,
                                                             POINTER(RopePosIdsSpec)]),
     "lb_rope_pos_ids_spec_query_numel": (c_size_t, [POINTER(RopePosIdsSpec)]),

@@ -476,6 +476,31 @@ class Bf16PagedBatchDecodeArgs:
     workspace: Optional[ReadWrite] = None
 
 
+@dataclass
+class StateMergeArgs:
+    """states F32 [rows, partitions, 130]; output BF16 [rows, 128]; lse F32 [rows] (base 2)."""
+    states: Read
+    output: Write
+    lse: Write
+
+
+class StateMergePlan:
+    def __init__(self, ptr, rows, partitions):
+        self._ptr, self._rows, self._partitions = ptr, rows, partitions
+
+    def __del__(self):
+        _dispose(self, "lb_state_merge_plan_destroy")
+
+    def rows(self): return self._rows
+    def partitions(self): return self._partitions
+    def states_numel(self): return self._rows * self._partitions * PARTIAL_STATE_WIDTH
+
+    def enqueue_into(self, scope: "CommandScope", args: StateMergeArgs):
+        raw = _abi.StateMergeArgs(states=args.states._raw, output=args.output._raw,
+                                  lse=args.lse._raw)
+        _check(_abi.load().lb_state_merge_enqueue(self._ptr, scope._ptr, byref(raw)))
+
+
 class DecodeProvider:
     """decode.rs:1001-1104."""
 
@@ -495,6 +520,13 @@ class DecodeProvider:
         out = c_int32()
         _check(_abi.load().lb_decode_provider_device_status(self._ptr, byref(out)))
         return out.value
+
+    def plan_state_merge(self, rows: int, partitions: int) -> "StateMergePlan":
+        """The split-K merge as an operator over caller-provided states (no reference
+        counterpart; listed as planned in the reference's docs/flashinfer-parity.md:38)."""
+        out = c_void_p()
+        _check(_abi.load().lb_state_merge_plan_create(self._ptr, rows, partitions, byref(out)))
+        return StateMergePlan(out.value, rows, partitions)
 
     def plan_bf16_paged_batch(self, spec: Bf16PagedBatchDecodeSpec, partitions: int = 0,
                               heads_per_cta: int = 0, balanced: int = 0,

@@ -378,6 +378,7 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     float top, norm;
     float4 acc;
     if (!merge_partial(state_of, n, lane, 0, 1, top, norm, acc) || !publish) return;
+    if (!(norm > 0.0f)) return; // every state was empty: nothing to publish
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
 }
 

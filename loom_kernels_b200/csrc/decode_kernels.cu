@@ -327,7 +327,8 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
     dependent_launch_wait(); // the partial states are complete and visible
     // the guard's loads and the state loads travel together; the verdict is used at the end
     int page_start, page_end, tail;
-    const bool valid = request_metadata_valid(indptr, last, batch, indices_len, request,
+    const bool valid = indptr == nullptr || // a bare state merge has no request metadata
+                       request_metadata_valid(indptr, last, batch, indices_len, request,
                                               page_start, page_end, tail);
     const float *st = workspace + (size_t)state * partitions * kStateWidth;
     merge_states([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane, valid,

@@ -42,6 +42,11 @@ struct lb_rope_append_plan {
     uint32_t grid = 0, block = 256, shared_bytes = 0, hash_slots = 0;
 };
 
+struct lb_state_merge_plan {
+    size_t rows = 0, partitions = 0;
+    int device = 0;
+};
+
 struct lb_rope_pos_ids_plan {
     lb_rope_pos_ids_spec spec;
     int device = 0;
@@ -300,6 +305,65 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     merge.indices_len = launch.indices_len;
     merge.grid = c.merge_grid;
     merge.block = c.merge_block;
+    return submit_launch(*scope, [&]() { return launch_split_merge(merge, stream); });
+}
+
+// ---- state merge -----------------------------------------------------------------------------------
+
+lb_status lb_state_merge_plan_create(const lb_decode_provider *provider, size_t rows,
+                                     size_t partitions, lb_state_merge_plan **out) {
+    if (!provider || !out) return fail(LB_INVALID_ARGUMENT, "provider");
+    *out = nullptr;
+    if (rows == 0 || partitions == 0) return fail(LB_ZERO_DIMENSION);
+    if (partitions > 65535)
+        return fail(LB_INVALID_PARTITION_COUNT, nullptr, (int64_t)partitions, 65535);
+    if (rows > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)rows);
+    size_t numel;
+    if (__builtin_mul_overflow(rows, partitions, &numel) ||
+        __builtin_mul_overflow(numel, (size_t)LB_PARTIAL_STATE_WIDTH, &numel) ||
+        numel > SIZE_MAX / sizeof(float))
+        return fail(LB_ELEMENT_COUNT_OVERFLOW);
+    lb_state_merge_plan *plan = new lb_state_merge_plan();
+    plan->rows = rows;
+    plan->partitions = partitions;
+    plan->device = provider->device;
+    *out = plan;
+    return LB_OK;
+}
+
+void lb_state_merge_plan_destroy(lb_state_merge_plan *plan) { delete plan; }
+
+lb_status lb_state_merge_enqueue(const lb_state_merge_plan *plan, lb_scope *scope,
+                                 const lb_state_merge_args *args) {
+    if (!plan || !scope || !args) return fail(LB_INVALID_ARGUMENT, "plan");
+    if (scope->queue->device != plan->device)
+        return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
+    lb_status rc = require_command_capacity(*scope, 1);
+    if (rc) return rc;
+    OperandRequest requests[3] = {
+        {args->states, LB_F32, false}, {args->output, LB_BF16, true}, {args->lse, LB_F32, true}};
+    Operand op[3];
+    if ((rc = resolve(*scope, requests, 3, op))) return rc;
+    if ((rc = require_exact_len("states", op[0].numel,
+                                plan->rows * plan->partitions * LB_PARTIAL_STATE_WIDTH)))
+        return rc;
+    if ((rc = require_exact_len("O", op[1].numel, plan->rows * LB_HEAD_DIM))) return rc;
+    if ((rc = require_exact_len("LSE", op[2].numel, plan->rows))) return rc;
+    if ((rc = require_alignment("states", op[0].ptr, 8))) return rc;
+    if ((rc = require_alignment("O", op[1].ptr, 8))) return rc;
+    MergeLaunch merge;
+    merge.workspace = (const float *)op[0].ptr;
+    merge.output = op[1].ptr;
+    merge.lse = (float *)op[2].ptr;
+    merge.indptr = nullptr; // no request metadata: every row is merged
+    merge.last = nullptr;
+    merge.batch = (int32_t)plan->rows;
+    merge.qh = 1;
+    merge.partitions = (int32_t)plan->partitions;
+    merge.indices_len = 0;
+    merge.grid = (uint32_t)((plan->rows + 3) / 4);
+    merge.block = 128;
+    void *stream = scope->queue->stream;
     return submit_launch(*scope, [&]() { return launch_split_merge(merge, stream); });
 }
 

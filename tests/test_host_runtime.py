@@ -561,3 +561,33 @@ def test_unsupported_device_and_missing_gpu_fail_loudly():
         lk.DecodeProvider.load(0)
     with pytest.raises(lk.LoomError):
         lk.RopeProvider.load(0)
+
+
+def test_state_merge_plan_and_preflight(fake):
+    provider = lk.DecodeProvider.load(0)
+    for rows, partitions, variant in [(0, 4, "ZeroDimension"), (4, 0, "ZeroDimension"),
+                                      (4, 65536, "InvalidPartitionCount"),
+                                      (2 ** 31, 2, "StateCountOutOfRange")]:
+        with pytest.raises(lk.LoomError) as e:
+            provider.plan_state_merge(rows, partitions)
+        assert e.value.variant == variant, (rows, partitions)
+    plan = provider.plan_state_merge(6, 3)
+    assert plan.states_numel() == 6 * 3 * 130
+    queue = lk.CommandQueue(0x100, 1)
+    for short, operand in [("states", "states"), ("output", "O"), ("lse", "LSE")]:
+        b = queue.bindings(3)
+        states = b.bind_read(D(0x40000000, plan.states_numel() - (short == "states"), _abi.F32))
+        out = b.bind_read_write(D(0x41000000, 6 * 128 - (short == "output"), _abi.BF16))
+        lse = b.bind_read_write(D(0x42000000, 6 - (short == "lse"), _abi.F32))
+        scope = queue.begin(b)
+        with pytest.raises(lk.EnqueueError) as e:
+            plan.enqueue_into(scope, lk.StateMergeArgs(states, out.write(), lse.write()))
+        assert (e.value.variant, e.value.operand) == ("LengthMismatch", operand)
+        assert scope.finish().submitted() == 0
+    b = queue.bindings(3)
+    states = b.bind_read(D(0x40000000, plan.states_numel(), _abi.F32))
+    out = b.bind_read_write(D(0x41000000, 6 * 128, _abi.BF16))
+    lse = b.bind_read_write(D(0x42000000, 6, _abi.F32))
+    scope = queue.begin(b)
+    plan.enqueue_into(scope, lk.StateMergeArgs(states, out.write(), lse.write()))
+    assert scope.finish().submitted() == 1
