@@ -197,12 +197,33 @@ def ours(args):
         return torch.from_numpy(bits.view(np.int16)).to(device).view(torch.bfloat16)
 
     k_pages, v_pages = dev_bf16(w.key_pages), dev_bf16(w.value_pages)
-    q_dev = dev_bf16(w.query)
-    indptr_dev = torch.from_numpy(w.indptr).to(device)
-    indices_dev = torch.from_numpy(w.indices).to(device)
-    last_dev = torch.from_numpy(w.last).to(device)
-    out = torch.zeros(spec.output_numel(), dtype=torch.bfloat16, device=device)
-    lse = torch.zeros(spec.lse_numel(), dtype=torch.float32, device=device)
+    # The per-step inputs (Q + page table) live in ONE device allocation and the per-step outputs
+    # (O + LSE) in another, each mirrored by one pinned host buffer, so that the end-to-end step
+    # is one host->device copy, the decode, one device->host copy.
+    step_in = [("q", w.query.view(np.uint8)), ("indptr", w.indptr.view(np.uint8)),
+               ("indices", w.indices.view(np.uint8)), ("last", w.last.view(np.uint8))]
+    offsets, cursor = {}, 0
+    for name, array in step_in:
+        offsets[name] = (cursor, array.size)
+        cursor += (array.size + 255) // 256 * 256
+    host_in = torch.empty(cursor, dtype=torch.uint8).pin_memory()
+    for name, array in step_in:
+        start, size = offsets[name]
+        host_in[start:start + size] = torch.from_numpy(np.ascontiguousarray(array).reshape(-1))
+    dev_in = host_in.to(device)
+
+    def in_view(name, dtype):
+        start, size = offsets[name]
+        return dev_in[start:start + size].view(dtype)
+
+    q_dev = in_view("q", torch.bfloat16)
+    indptr_dev, indices_dev, last_dev = (in_view(n, torch.int32)
+                                         for n in ("indptr", "indices", "last"))
+    out_bytes = spec.output_numel() * 2
+    lse_offset = (out_bytes + 255) // 256 * 256
+    dev_out = torch.zeros(lse_offset + spec.lse_numel() * 4, dtype=torch.uint8, device=device)
+    out = dev_out[:out_bytes].view(torch.bfloat16)
+    lse = dev_out[lse_offset:].view(torch.float32)
     workspace = (torch.zeros(plan.workspace_required_numel(), dtype=torch.float32, device=device)
                  if plan.workspace_required_numel() else None)
     stream = torch.cuda.Stream(device=device)
@@ -251,25 +272,17 @@ def ours(args):
         raise SystemExit("a decode kernel gave up on a bounded wait; the numbers are invalid")
 
     # ---- end to end through the public API with host buffers ------------------------------------
-    pinned = {name: torch.from_numpy(array).pin_memory() for name, array in
-              (("q", w.query.view(np.int16)), ("indptr", w.indptr), ("indices", w.indices),
-               ("last", w.last))}
-    out_host = torch.empty(spec.output_numel(), dtype=torch.bfloat16).pin_memory()
-    lse_host = torch.empty(spec.lse_numel(), dtype=torch.float32).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in pinned.values())
-    d2h = out_host.numel() * 2 + lse_host.numel() * 4
+    host_out = torch.empty(dev_out.numel(), dtype=torch.uint8).pin_memory()
+    h2d = sum(size for _, size in offsets.values())  # bytes of Q + page table (padding excluded)
+    d2h = out_bytes + spec.lse_numel() * 4
 
     def e2e_step(bindings):
         with torch.cuda.stream(stream):
-            q_dev.view(torch.int16).copy_(pinned["q"], non_blocking=True)
-            indptr_dev.copy_(pinned["indptr"], non_blocking=True)
-            indices_dev.copy_(pinned["indices"], non_blocking=True)
-            last_dev.copy_(pinned["last"], non_blocking=True)
+            dev_in.copy_(host_in, non_blocking=True)
             scope = queue.begin(bindings)
             plan.enqueue_into(scope, decode_args)
-            bindings = scope.finish().wait()
-            out_host.copy_(out, non_blocking=True)
-            lse_host.copy_(lse, non_blocking=True)
+            bindings = scope.finish().wait()  # the completion fence hands O and LSE back
+            host_out.copy_(dev_out, non_blocking=True)
             stream.synchronize()
         return bindings
 
