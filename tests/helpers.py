@@ -63,9 +63,9 @@ class DecodeRun:
         self.plan = self.provider.plan_bf16_paged_batch(spec, partitions, heads_per_cta, balanced)
         self.stream = torch.cuda.Stream(device=self.device)
         self.queue = lk.CommandQueue(self.stream, max_commands)
-        self.q = dev_bf16(q_bits, device)
-        self.k = dev_bf16(k_bits, device)
-        self.v = dev_bf16(v_bits, device)
+        # BF16 bit arrays from the host, or tensors already on the device (full-size pools)
+        self.q, self.k, self.v = (t if isinstance(t, torch.Tensor) else dev_bf16(t, device)
+                                  for t in (q_bits, k_bits, v_bits))
         self.indptr = dev_i32(indptr, device)
         self.indices = dev_i32(indices, device)
         self.last = dev_i32(last, device)
@@ -106,13 +106,22 @@ class DecodeRun:
 
 
 def check_decode(actual_bits, actual_lse, expected_bits, expected_lse, lse_limit=GATE_LSE_MAX_ABS,
-                 gate=False):
+                 gate=False, large_outputs=False):
+    """O within max-abs 2e-2 and row-relative 1e-2 of the reference, LSE within `lse_limit`.
+
+    `large_outputs`: rows dominated by a x8 outlier token have |O| up to ~30, where one BF16 ulp
+    is 0.125; there the absolute bound is applied as |a - e| <= 2e-2 + 1e-2 |e| per element (the
+    row-relative bound is unchanged)."""
     a, e = bits_to_f32(actual_bits), bits_to_f32(expected_bits)
     assert np.all(np.isfinite(a)), "non-finite output"
     assert np.all(np.isfinite(actual_lse)), "non-finite LSE"
     err = np.abs(a - e)
     max_abs = float(err.max()) if err.size else 0.0
-    assert max_abs <= DECODE_MAX_ABS, f"output max-abs {max_abs}"
+    if large_outputs:
+        excess = float((err - DECODE_REL * np.abs(e)).max()) if err.size else 0.0
+        assert excess <= DECODE_MAX_ABS, f"output error {excess} beyond 2e-2 + 1e-2 |e|"
+    else:
+        assert max_abs <= DECODE_MAX_ABS, f"output max-abs {max_abs}"
     if gate:
         assert max_abs <= GATE_OUTPUT_MAX_ABS, f"output max-abs {max_abs} over the gate limit"
     # rel 1e-2: per (request, head) row, ||actual - expected|| <= 1e-2 * ||expected||

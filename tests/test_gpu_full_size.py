@@ -1,0 +1,132 @@
+"""Paged decode at the full sizes of the benchmark configurations, through the C ABI.
+
+The CPU oracle is too slow for whole batches of this size, so each case checks
+  * a sample of whole requests against the oracle (their pages are gathered into a compact pool
+    for the oracle; O max-abs 2e-2, row-relative 1e-2, LSE 1e-3 as in the small cases), and
+  * size-independent properties over EVERY row: the direct, split-K and page-balanced algorithms
+    agree within the same tolerances, and moving every page to another physical slot of the pool
+    (with the page table updated) leaves the direct output bit-identical (page indexing is exact).
+K/V pools are generated on the device (seeded); Q and the page table come from the host.
+"""
+import numpy as np
+import pytest
+import torch
+
+import loom_kernels_b200 as lk
+from loom_kernels_b200 import workloads
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def provider():
+    return lk.DecodeProvider.load(0)
+
+
+def device_pool(pool_pages, kvh, seed, outliers=None):
+    generator = torch.Generator(device="cuda:0").manual_seed(seed)
+    numel = pool_pages * 16 * kvh * 128
+    k = torch.randn(numel, dtype=torch.bfloat16, device="cuda:0", generator=generator)
+    v = torch.randn(numel, dtype=torch.bfloat16, device="cuda:0", generator=generator)
+    for page, offset in outliers or []:  # one x8 token per request stresses the softmax maximum
+        row = (page * 16 + offset) * kvh * 128
+        k[row:row + kvh * 128] *= 8.0
+        v[row:row + kvh * 128] *= 8.0
+    return k, v
+
+
+def oracle_rows(oracle, w, k, v, requests):
+    """Oracle O/LSE of whole requests: their pages are gathered into a compact pool."""
+    outs, lses = [], []
+    k4 = k.view(w.max_pages, 16 * w.kvh * 128)
+    v4 = v.view(w.max_pages, 16 * w.kvh * 128)
+    for r in requests:
+        pages = w.indices[w.indptr[r]:w.indptr[r + 1]].astype(np.int64)
+        ids = torch.from_numpy(pages).to("cuda:0")
+        k_sub = H.host_bits(k4[ids].reshape(-1))
+        v_sub = H.host_bits(v4[ids].reshape(-1))
+        spec = oracle.paged_spec(1, len(pages), w.qh, w.kvh)
+        q = w.query[r * w.qh * 128:(r + 1) * w.qh * 128]
+        out, lse = oracle.paged_decode(spec, q, k_sub, v_sub, np.array([0, len(pages)], np.int32),
+                                       np.arange(len(pages), dtype=np.int32),
+                                       w.last[r:r + 1], threads=16)
+        outs.append(out)
+        lses.append(lse)
+    return np.concatenate(outs), np.concatenate(lses)
+
+
+def rows_of(bits, lse, w, requests):
+    out = np.concatenate([bits[r * w.qh * 128:(r + 1) * w.qh * 128] for r in requests])
+    return out, np.concatenate([lse[r * w.qh:(r + 1) * w.qh] for r in requests])
+
+
+def run(provider, w, k, v, indices=None, **plan_options):
+    spec = lk.Bf16PagedBatchDecodeSpec.new(w.batch, w.max_pages, w.qh, w.kvh)
+    runner = H.DecodeRun(spec, w.query, k, v, w.indptr, w.indices if indices is None else indices,
+                         w.last, provider=provider, **plan_options)
+    return runner.run()
+
+
+def check_algorithms_agree(results, large_outputs=False):
+    (base_bits, base_lse), others = results[0], results[1:]
+    for bits, lse in others:
+        H.check_decode(bits, lse, base_bits, base_lse, lse_limit=1e-3, large_outputs=large_outputs)
+
+
+def moved_pool(w, k, v, seed):
+    """Every page moves to another physical slot; returns the new pools and page ids."""
+    rng = np.random.default_rng(seed)
+    destination = rng.permutation(w.max_pages).astype(np.int64)  # old page id -> new page id
+    dest = torch.from_numpy(destination).to("cuda:0")
+    row = 16 * w.kvh * 128
+    k2, v2 = torch.empty_like(k), torch.empty_like(v)
+    k2.view(w.max_pages, row)[dest] = k.view(w.max_pages, row)
+    v2.view(w.max_pages, row)[dest] = v.view(w.max_pages, row)
+    return k2, v2, destination[w.indices].astype(np.int32)
+
+
+def test_c3_batch64_gqa4_context4096(provider, oracle):
+    w = workloads.c3(with_values=False)
+    w.query = workloads.normal_bf16(np.random.default_rng(3), w.batch * w.qh * 128)
+    k, v = device_pool(w.max_pages, w.kvh, 0xC3)
+    direct = run(provider, w, k, v, partitions=1)
+    sample = [0, 31, 63]
+    expected = oracle_rows(oracle, w, k, v, sample)
+    H.check_decode(*rows_of(*direct, w, sample), *expected, lse_limit=1e-3)
+    check_algorithms_agree([direct, run(provider, w, k, v, partitions=4),
+                            run(provider, w, k, v, balanced=1)])
+    k2, v2, indices2 = moved_pool(w, k, v, 33)
+    moved = run(provider, w, k2, v2, indices=indices2, partitions=1)
+    assert np.array_equal(moved[0], direct[0]) and np.array_equal(moved[1], direct[1])
+
+
+def test_c4_batch8_gqa8_context32768_with_outliers(provider, oracle):
+    w = workloads.c4(with_values=False)
+    rng = np.random.default_rng(4)
+    w.query = workloads.normal_bf16(rng, w.batch * w.qh * 128)
+    outliers = []
+    for r in range(w.batch):
+        token = int(rng.integers(0, w.kv_lens[r]))
+        outliers.append((int(w.indices[w.indptr[r] + token // 16]), token % 16))
+    k, v = device_pool(w.max_pages, w.kvh, 0xC4, outliers)
+    split = run(provider, w, k, v, partitions=16)
+    expected = oracle_rows(oracle, w, k, v, [5])
+    H.check_decode(*rows_of(*split, w, [5]), *expected, lse_limit=1e-3, large_outputs=True)
+    check_algorithms_agree([split, run(provider, w, k, v, partitions=1),
+                            run(provider, w, k, v, balanced=1)], large_outputs=True)
+
+
+@pytest.mark.parametrize("label,qh,kvh,first", [("mqa", 32, 1, 0), ("gqa4", 32, 8, 256)])
+def test_c5_ragged_256_requests(provider, oracle, label, qh, kvh, first):
+    lens = workloads.c5_lengths(512)[first:first + 256]
+    w = workloads.decode_workload(f"C5 {label}", 256, qh, kvh, lens, 65536, 0xC5 + kvh,
+                                  with_values=False)
+    w.query = workloads.normal_bf16(np.random.default_rng(5), w.batch * w.qh * 128)
+    k, v = device_pool(w.max_pages, w.kvh, 0xC5 + kvh)
+    balanced = run(provider, w, k, v)  # what the plan chooses for this shape
+    shortest, longest = int(np.argmin(lens)), int(np.argmax(lens))
+    sample = sorted({shortest, longest, 17, 200})
+    expected = oracle_rows(oracle, w, k, v, sample)
+    H.check_decode(*rows_of(*balanced, w, sample), *expected, lse_limit=1e-3)
+    check_algorithms_agree([balanced, run(provider, w, k, v, partitions=1)])
