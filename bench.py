@@ -449,6 +449,7 @@ def ragged_c5(args):
             owned = sharding.balanced_assignment(family, world)[rank]
         jobs.append(RaggedJob(lk, torch, provider, label, qh, kvh, family[owned],
                               0xC5 + 64 * index + rank, device))
+        jobs[-1].row_counts = [len(ids) for ids in sharding.balanced_assignment(family, world)]
     commands = sum(job.plan.commands() for job in jobs)
     stream = torch.cuda.Stream(device=device)
     queue = lk.CommandQueue(stream, max(8, commands * max(args.steps, args.warmup)))
@@ -519,6 +520,24 @@ def ragged_c5(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1)
 
+    # ---- optional all-gather of the output rows of both families (host-checked: no rank enters
+    #      the collective unless every rank enqueued its shard), timed outside the step
+    gather_us = 0.0
+    if world > 1 and not args.shard:
+        def gather_all():
+            for job in jobs:
+                rows = job.out.view(job.w.batch, -1)
+                sharding.gather_output_rows_checked(rows, True, job.row_counts)
+        gather_all()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            gather_all()
+        g1.record()
+        barrier()
+        gather_us = g0.elapsed_time(g1) * 1e3 / 5
+
     rank_bytes = [job.w.algorithmic_bytes() for job in jobs]
     times = torch.tensor([step_ms, e2e_ms] + family_ms, dtype=torch.float64, device=device)
     totals = torch.tensor([float(sum(rank_bytes))] + [float(b) for b in rank_bytes],
@@ -558,6 +577,11 @@ def ragged_c5(args):
                     "us_per_call": times[1] * 1e3 / args.steps},
             "gpu_launches": args.steps * commands, "clocks": clocks,
         }
+        if gather_us:
+            line["allgather"] = {"us": gather_us,
+                                 "note": "NCCL all-gather of both families' output rows (padded "
+                                         "to the widest rank) with the host-side all-ranks-"
+                                         "enqueued check, timed outside the step"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -115,3 +115,44 @@ def gather_output_rows(local_rows, row_counts: Optional[List[int]] = None, group
     dist.all_gather_into_tensor(out, padded, group=group)
     blocks = out.view((world, widest) + tuple(local_rows.shape[1:]))
     return torch.cat([blocks[r, :row_counts[r]] for r in range(world)], dim=0)
+
+
+class ShardFailure(RuntimeError):
+    """A rank could not enqueue its shard; no rank entered the collective."""
+
+
+_HOST_GROUP = None
+
+
+def _host_group():
+    """A gloo group for host-side agreement (the default group when it is gloo already)."""
+    import torch.distributed as dist
+
+    global _HOST_GROUP
+    if dist.get_backend() == "gloo":
+        return None
+    if _HOST_GROUP is None:
+        _HOST_GROUP = dist.new_group(backend="gloo")  # collective: every rank calls it once
+    return _HOST_GROUP
+
+
+def all_ranks_ok(ok: bool) -> bool:
+    """Host-side agreement before a collective: True only if every rank passes ok=True.
+
+    A rank whose enqueue failed (contract error, poisoned queue, launch failure) reports False
+    instead of skipping the collective, so the others never wait for it on the GPU."""
+    import torch
+    import torch.distributed as dist
+
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=_host_group())
+    return bool(flag.item())
+
+
+def gather_output_rows_checked(local_rows, enqueued_ok: bool,
+                               row_counts: Optional[List[int]] = None, group=None):
+    """`gather_output_rows` guarded by `all_ranks_ok`: raises ShardFailure on EVERY rank when
+    any rank failed, before the all-gather is started."""
+    if not all_ranks_ok(enqueued_ok):
+        raise ShardFailure("a rank failed to enqueue its shard; the all-gather was not started")
+    return gather_output_rows(local_rows, row_counts, group)

@@ -2,6 +2,7 @@
 KV-head sharding, the ragged balanced assignment, and the all-gather of output rows.  The decode
 itself is stood in for by the CPU oracle (no GPU here); what is under test is the partitioning
 and the collective plumbing."""
+import datetime
 import os
 import socket
 
@@ -93,6 +94,64 @@ def _worker(rank, world, port, mode, result_queue):
         result_queue.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
+
+
+def _failing_worker(rank, world, port, result_queue):
+    """Rank 1's enqueue fails on the host (a launch failure injected through the fake driver);
+    it reports that instead of skipping the collective, and every rank gets ShardFailure."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=30))
+    try:
+        import loom_kernels_b200 as lk
+        from loom_kernels_b200 import _abi
+        lib = _abi.load()
+        lib.lb_test_use_fake_driver(1, 148)
+        spec = lk.Bf16PagedBatchDecodeSpec.new(2, 4, 4, 2)
+        plan = lk.DecodeProvider.load(0).plan_bf16_paged_batch(spec, partitions=1)
+        queue = lk.CommandQueue(0x100, 1)
+        b = queue.bindings(9)
+        sizes = [spec.query_numel(), spec.kv_pages_numel(), spec.kv_pages_numel(), 3, 4, 2]
+        reads = [b.bind_read(lk.DeviceSpan(0x10000000 + i * 0x1000000, n,
+                                           _abi.BF16 if i < 3 else _abi.I32))
+                 for i, n in enumerate(sizes)]
+        out = b.bind_read_write(lk.DeviceSpan(0x17000000, spec.output_numel(), _abi.BF16))
+        lse = b.bind_read_write(lk.DeviceSpan(0x18000000, spec.lse_numel(), _abi.F32))
+        if rank == 1:
+            lib.lb_test_fake_fail(b"launch", 1, 719)
+        scope = queue.begin(b)
+        enqueued = True
+        try:
+            plan.enqueue_into(scope, lk.Bf16PagedBatchDecodeArgs(*reads, out.write(), lse.write()))
+        except lk.LoomError:
+            enqueued = False
+        scope.finish()
+        try:
+            sharding.gather_output_rows_checked(torch.zeros(2, 8), enqueued)
+            outcome = "gathered"
+        except sharding.ShardFailure:
+            outcome = "shard failure"
+        result_queue.put((rank, enqueued, outcome))
+        del scope, queue, b, plan
+        import gc
+        gc.collect()
+        lib.lb_test_use_fake_driver(0, 0)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_failed_rank_stops_the_gather_on_every_rank():
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    got = sorted(results.get(timeout=5) for _ in range(2))
+    assert got == [(0, True, "shard failure"), (1, False, "shard failure")]
 
 
 @pytest.mark.parametrize("mode", ["request", "kv_head"])
