@@ -187,7 +187,9 @@ lb_status lb_append_tokens_spec_new(size_t tokens, size_t batch_size, size_t max
                                     size_t num_query_heads, size_t num_kv_heads, size_t head_dim,
                                     size_t page_size, lb_append_tokens_spec *out);
 /* Extension (no reference counterpart): the same contract without the 64-token total cap, up
- * to lb_append_extended_max_tokens() tokens; one command, same all-or-nothing device guard. */
+ * to lb_append_extended_max_tokens() tokens; same all-or-nothing device guard.  A plan made
+ * from such a spec is two commands (validate once, then rotate and scatter) and needs an I32
+ * workspace of lb_rope_append_plan_info.workspace_numel elements bound read-write. */
 lb_status lb_append_tokens_spec_new_extended(size_t tokens, size_t batch_size,
                                              size_t max_num_pages, size_t num_query_heads,
                                              size_t num_kv_heads, size_t head_dim,
@@ -381,13 +383,15 @@ typedef struct lb_rope_append_args {
     lb_handle query, key, value, batch_indices, positions, page_indptr, page_indices,
         last_page_len;                           /* Read */
     lb_handle query_output, key_pages, value_pages; /* Write */
+    lb_handle workspace; /* ReadWrite<i32>, extended plans only (workspace_numel elements) */
 } lb_rope_append_args;
 
 typedef struct lb_rope_append_plan_info {
     int32_t explicit_tokens; /* 0: one token per request; 1: explicit token list */
     uint32_t tokens;
     uint32_t grid, block, shared_bytes;
-    uint32_t commands; /* always 1 */
+    uint32_t commands;      /* 1; 2 for an extended plan (validate, then rotate and scatter) */
+    size_t workspace_numel; /* I32 elements the caller must bind; 0 unless the plan is extended */
 } lb_rope_append_plan_info;
 
 /* RopeProvider::load, rope/mod.rs:586-590 */

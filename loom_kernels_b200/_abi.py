@@ -72,7 +72,8 @@ class DecodeArgs(ctypes.Structure):
 class AppendArgs(ctypes.Structure):
     _fields_ = [(name, Handle) for name in
                 ("query", "key", "value", "batch_indices", "positions", "page_indptr",
-                 "page_indices", "last_page_len", "query_output", "key_pages", "value_pages")]
+                 "page_indices", "last_page_len", "query_output", "key_pages", "value_pages",
+                 "workspace")]
 
 
 class StateMergeArgs(ctypes.Structure):
@@ -86,7 +87,8 @@ class RopePosIdsArgs(ctypes.Structure):
 
 class AppendPlanInfo(ctypes.Structure):
     _fields_ = [("explicit_tokens", c_int32), ("tokens", c_uint32), ("grid", c_uint32),
-                ("block", c_uint32), ("shared_bytes", c_uint32), ("commands", c_uint32)]
+                ("block", c_uint32), ("shared_bytes", c_uint32), ("commands", c_uint32),
+                ("workspace_numel", c_size_t)]
 
 
 RECORD_FN = ctypes.CFUNCTYPE(c_int32, c_void_p, c_void_p)

@@ -640,6 +640,7 @@ class Bf16RopePagedKvAppendTokensArgs:
     query_output: Write
     key_pages: Write
     value_pages: Write
+    workspace: Optional[ReadWrite] = None  # I32, extended plans only
 
 
 class Bf16RopePosIdsSpec:
@@ -742,6 +743,8 @@ class _AppendPlan:
 
     def spec(self): return self._spec
     def info(self): return self._info
+    def commands(self): return self._info.commands
+    def workspace_required_numel(self): return self._info.workspace_numel
 
 
 class Bf16RopePagedKvAppendPlan(_AppendPlan):
@@ -766,7 +769,8 @@ class Bf16RopePagedKvAppendTokensPlan(_AppendPlan):
             batch_indices=args.batch_indices._raw, positions=args.positions._raw,
             page_indptr=args.page_indptr._raw, page_indices=args.page_indices._raw,
             last_page_len=args.last_page_len._raw, query_output=args.query_output._raw,
-            key_pages=args.key_pages._raw, value_pages=args.value_pages._raw)
+            key_pages=args.key_pages._raw, value_pages=args.value_pages._raw,
+            workspace=args.workspace._raw if args.workspace is not None else _null_handle())
         _check(_abi.load().lb_rope_append_enqueue(self._ptr, scope._ptr, byref(raw)))
 
 

@@ -2,9 +2,9 @@
 //
 // Replaces the reference's rope_paged_kv_append_bf16_neox_d128 and
 // rope_paged_kv_append_tokens_bf16_neox_d128 kernels
-// (crates/loom-infer-cuda/src/rope/mod.rs:119-230,259-405).  One kernel serves the
-// one-token-per-request contract, the explicit <=64-token contract and the extended
-// any-total variant:
+// (crates/loom-infer-cuda/src/rope/mod.rs:119-230,259-405).  rope_append_kernel serves the
+// one-token-per-request contract and the explicit <=64-token contract (the any-total extension
+// is the validate + scatter pair further down):
 //
 //   0. a CTA starts on its tokens at once: the first token's Q/K/V rows are fetched into
 //      registers and the sin/cos tables of its first eight tokens are computed, 64 threads per
@@ -79,14 +79,65 @@ __device__ __forceinline__ int speculative_position(const AppendArgs &a, int tok
     return (a.indptr[token + 1] - a.indptr[token] - 1) * kPage + a.last[token] - 1;
 }
 
-// (sin, cos) of rotation pair `pair` at `position`.  The F32 angle is exactly the reference's;
-// sin/cos are evaluated in double and rounded once, which reproduces the host libm's (near
-// correctly rounded) sinf/cosf.
-__device__ __forceinline__ float2 pair_sincos(int position, int pair) {
-    const float angle = __fmul_rn((float)position, c_inverse_frequency[pair]);
+// Outside the range of the reduction below (an angle of 2^32 or more, or a garbage position of a
+// call that will be rejected): the library routine, kept out of line.
+__device__ __noinline__ float2 sincos_any(double x) {
     double s, c;
-    sincos((double)angle, &s, &c);
+    sincos(x, &s, &c);
     return make_float2((float)s, (float)c);
+}
+
+// (sin, cos) of an F32 angle in [0, 2^32), evaluated in double and rounded once, which reproduces the host
+// libm's (near correctly rounded) sinf/cosf: absolute error below 2e-16 before the rounding.
+// The angle is reduced by k * pi/2 with pi/2 split into three 20-bit pieces (k * piece is exact
+// for k < 2^32) and a tail; both functions are then summed as Taylor series on [-pi/4, pi/4]
+// (degrees 17 and 18: the first omitted terms are below 1e-19).  A third of the instructions of
+// the general-purpose routine, no local memory, and short enough to leave registers for the rows.
+__device__ __forceinline__ float2 sincos_in_range(double x) { // 0 <= x < 2^32
+    const double k = rint(x * 0x1.45f306dc9c883p-1); // x * 2/pi
+    double r = fma(-k, 0x1.921fa00000000p+0, x);
+    r = fma(-k, 0x1.5444200000000p-20, r);
+    r = fma(-k, 0x1.a308c00000000p-41, r);
+    r = fma(-k, 0x1.313198a2e0370p-61, r);
+    const double r2 = r * r;
+    double s = 1.0 / 355687428096000.0;       //  1/17!
+    s = fma(s, r2, -1.0 / 1307674368000.0);   // -1/15!
+    s = fma(s, r2, 1.0 / 6227020800.0);       //  1/13!
+    s = fma(s, r2, -1.0 / 39916800.0);        // -1/11!
+    s = fma(s, r2, 1.0 / 362880.0);           //  1/9!
+    s = fma(s, r2, -1.0 / 5040.0);            // -1/7!
+    s = fma(s, r2, 1.0 / 120.0);              //  1/5!
+    s = fma(s, r2, -1.0 / 6.0);               // -1/3!
+    s = fma(s, r2, 1.0);
+    s *= r;
+    double c = -1.0 / 6402373705728000.0;     // -1/18!
+    c = fma(c, r2, 1.0 / 20922789888000.0);   //  1/16!
+    c = fma(c, r2, -1.0 / 87178291200.0);     // -1/14!
+    c = fma(c, r2, 1.0 / 479001600.0);        //  1/12!
+    c = fma(c, r2, -1.0 / 3628800.0);         // -1/10!
+    c = fma(c, r2, 1.0 / 40320.0);            //  1/8!
+    c = fma(c, r2, -1.0 / 720.0);             // -1/6!
+    c = fma(c, r2, 1.0 / 24.0);               //  1/4!
+    c = fma(c, r2, -0.5);
+    c = fma(c, r2, 1.0);
+    const int quadrant = (int)((long long)k & 3);
+    const double sine = (quadrant & 1) ? c : s, cosine = (quadrant & 1) ? s : c;
+    return make_float2((float)((quadrant & 2) ? -sine : sine),
+                       (float)(((quadrant + 1) & 2) ? -cosine : cosine));
+}
+
+// Any F32 angle: the stand-alone RoPE takes theta and scale from the caller.
+__device__ __forceinline__ float2 sincos_of_f32_angle(float angle) {
+    const double x = (double)angle;
+    return x >= 0.0 && x < 4294967296.0 ? sincos_in_range(x) : sincos_any(x);
+}
+
+// (sin, cos) of rotation pair `pair` at `position` for the append (theta 10000, scale 1); the
+// F32 angle is exactly the reference's.  Positions are below 2^31 and the inverse frequencies
+// at most 1, so the angle is always inside the reduction's range; the garbage position of a
+// call that is going to be rejected yields garbage that is never stored.
+__device__ __forceinline__ float2 pair_sincos(int position, int pair) {
+    return sincos_in_range((double)__fmul_rn((float)position, c_inverse_frequency[pair]));
 }
 
 __device__ __forceinline__ uint32_t rotate_pack(uint32_t lo_bits, uint32_t hi_bits, float2 sc0,
@@ -288,6 +339,149 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
     LB_STAMP(6);
 }
 
+// ---- the any-total append as two commands ----------------------------------------------------------
+//
+// Calls with hundreds or thousands of tokens pay too much for a validation that every CTA
+// repeats.  The extended plan therefore validates ONCE, in a kernel of its own, and leaves its
+// findings in a small caller-bound I32 workspace:
+//
+//     workspace[0 .. 32)                verdict of validation CTA i (0 = nothing wrong)
+//     workspace[32 + 2t], [33 + 2t]     (position, physical slot) of token t
+//
+// append_validate_kernel: CTA 0 maps the tokens (and checks slot uniqueness in a shared-memory
+// hash set), the other CTAs share the page-table and request checks.  It waits for the work
+// before it FIRST and only then releases its dependent, so that
+// append_scatter_kernel (one CTA per token) may read its inputs, build the sin/cos table and rotate
+// the rows in registers while the validation is still running; it waits for the verdict only
+// before it stores.  All-or-nothing as before: any non-zero verdict and nothing is written.
+constexpr int kVerdictSlots = 32;
+constexpr int kValidateThreads = 1024;
+constexpr int kScatterThreads = 256;
+
+__global__ void __launch_bounds__(kValidateThreads)
+append_validate_kernel(const AppendArgs a, int32_t *workspace) {
+    extern __shared__ int hash_table[];
+    dev::dependent_launch_wait();    // the inputs may come from the command before this one
+    dev::dependent_launch_release(); // from here on everything before this command is complete
+    const int tid = threadIdx.x;
+    bool invalid = false;
+    if (blockIdx.x > 0 || gridDim.x == 1) {
+        // page-table and request checks, sliced over the scanning CTAs
+        const int scanners = gridDim.x == 1 ? 1 : (int)gridDim.x - 1;
+        const int me = gridDim.x == 1 ? 0 : (int)blockIdx.x - 1;
+        if (me == 0 && tid == 0) {
+            const int final_indptr = a.indptr[a.batch];
+            invalid = a.indptr[0] != 0 || final_indptr < 0 || final_indptr != a.indices_len;
+        }
+        for (int request = me * kValidateThreads + tid; request < a.batch;
+             request += scanners * kValidateThreads) {
+            const int begin = a.indptr[request], end = a.indptr[request + 1];
+            const int tail = a.last[request];
+            if (begin < 0 || end <= begin || end > a.indices_len || tail < 1 || tail > kPage)
+                invalid = true;
+        }
+        for (int base = me * 4 * kValidateThreads; base < a.indices_len;
+             base += scanners * 4 * kValidateThreads) {
+            int id[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int page = base + u * kValidateThreads + tid;
+                id[u] = page < a.indices_len ? a.indices[page] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
+        }
+    }
+    if (blockIdx.x == 0) {
+        for (int i = tid; i < a.hash_slots; i += kValidateThreads) hash_table[i] = -1;
+        if (tid >= (int)gridDim.x && tid < kVerdictSlots) workspace[tid] = 0; // unused verdicts
+        __syncthreads();
+        for (int base = 0; base < a.tokens; base += 4 * kValidateThreads) {
+            int position[4], start[4], slot[4];
+            bool ok[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int token = base + u * kValidateThreads + tid;
+                position[u] = start[u] = 0;
+                ok[u] = token < a.tokens ? token_request(a, token, position[u], start[u]) : false;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                // the table itself is being checked elsewhere: stay inside page_indices
+                const long long page = (long long)start[u] + position[u] / kPage;
+                ok[u] = ok[u] && page >= 0 && page < a.indices_len;
+                slot[u] = a.indices[ok[u] ? (int)page : 0] * kPage + position[u] % kPage;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int token = base + u * kValidateThreads + tid;
+                if (token >= a.tokens) continue;
+                workspace[kVerdictSlots + 2 * token] = position[u];
+                workspace[kVerdictSlots + 2 * token + 1] = slot[u];
+                if (!ok[u]) {
+                    invalid = true;
+                    continue;
+                }
+                unsigned h = ((unsigned)slot[u] * 2654435761u) & (unsigned)(a.hash_slots - 1);
+                for (int probe = 0; probe < a.hash_slots; ++probe) {
+                    const int seen = atomicCAS(&hash_table[h], -1, slot[u]);
+                    if (seen == -1) break;
+                    if (seen == slot[u]) {
+                        invalid = true;
+                        break;
+                    }
+                    h = (h + 1) & (unsigned)(a.hash_slots - 1);
+                }
+            }
+        }
+    }
+    const int verdict = __syncthreads_or(invalid);
+    if (tid == 0) workspace[blockIdx.x] = verdict;
+}
+
+__global__ void __launch_bounds__(kScatterThreads, 8)
+append_scatter_kernel(const AppendArgs a, const int32_t *workspace) {
+    __shared__ __align__(16) float2 table[kPairs];
+    dev::dependent_launch_release();
+    const int tid = threadIdx.x;
+    const int token = blockIdx.x;
+    const int row_tasks = (a.qh + a.kvh) * 8, copy_tasks = a.kvh * 16;
+    // The validation kernel released this one only after everything before the call had
+    // completed, so the call's inputs are final: fetch, rotate and keep the result in registers.
+    uint4 lo[2], hi[2], v = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int task = tid + i * kScatterThreads;
+        lo[i] = hi[i] = make_uint4(0, 0, 0, 0);
+        if (task < row_tasks) {
+            const uint4 *src = row_source(a, token, task >> 3);
+            lo[i] = src[task & 7];
+            hi[i] = src[8 + (task & 7)];
+        }
+    }
+    if (tid < copy_tasks) v = a.value[(size_t)token * copy_tasks + tid];
+    if (tid < kPairs) table[tid] = pair_sincos(speculative_position(a, token), tid);
+    __syncthreads();
+    dev::dependent_launch_wait(); // the verdicts and this token's slot are final
+    const int verdict = __syncthreads_or(tid < kVerdictSlots ? __ldcg(workspace + tid) : 0);
+    if (verdict != 0) return;
+    const int slot = __ldcg(workspace + kVerdictSlots + 2 * token + 1);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int task = tid + i * kScatterThreads;
+        if (task < row_tasks)
+            rotate_row(lo[i], hi[i], row_destination(a, token, slot, task >> 3), task & 7, table);
+    }
+    for (int task = tid + 2 * kScatterThreads; task < row_tasks; task += kScatterThreads) {
+        const uint4 *src = row_source(a, token, task >> 3);
+        rotate_row(src[task & 7], src[8 + (task & 7)], row_destination(a, token, slot, task >> 3),
+                   task & 7, table);
+    }
+    if (tid < copy_tasks) a.value_pages[(size_t)slot * copy_tasks + tid] = v;
+    for (int task = tid + kScatterThreads; task < copy_tasks; task += kScatterThreads)
+        a.value_pages[(size_t)slot * copy_tasks + task] = a.value[(size_t)token * copy_tasks + task];
+}
+
 // Stand-alone NeoX RoPE over contiguous NHD Q and K (the reference's rope_pos_ids_bf16_neox_d128,
 // crates/loom-infer-cuda/src/rope/mod.rs:44-94): the same rotation as the append, output to
 // separate Q/K buffers.  A CTA walks tokens blockIdx.x, blockIdx.x + grid, ...; 64 threads build
@@ -314,10 +508,7 @@ __global__ void __launch_bounds__(kRopeThreads) rope_pos_ids_kernel(const RopeAr
         if (position < 0) continue; // uniform over the CTA
         __syncthreads();            // the previous token's table is no longer read
         if (tid < kPairs) {
-            const float angle = __fmul_rn((float)position, a.inverse_frequency[tid]);
-            double s, c;
-            sincos((double)angle, &s, &c);
-            table[tid] = make_float2((float)s, (float)c);
+            table[tid] = sincos_of_f32_angle(__fmul_rn((float)position, a.inverse_frequency[tid]));
         }
         __syncthreads();
         for (int task = tid; task < row_tasks; task += kRopeThreads) {
@@ -351,6 +542,9 @@ int launch_rope_pos_ids(const RopeLaunch &launch, void *stream) {
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency) {
     int rc = cudaMemcpyToSymbol(c_inverse_frequency, inverse_frequency, sizeof(float) * kPairs);
     if (rc) return rc;
+    rc = cudaFuncSetAttribute(append_validate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)max_dynamic_shared);
+    if (rc) return rc;
     return cudaFuncSetAttribute(rope_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)max_dynamic_shared);
 }
@@ -358,7 +552,7 @@ int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_fre
 int append_block_threads() { return kThreads; }
 int append_max_tokens_per_cta() { return kMaxTokensPerCta; }
 
-int launch_rope_append(const AppendLaunch &launch, void *stream) {
+static AppendArgs append_args(const AppendLaunch &launch) {
     AppendArgs args;
     args.query = static_cast<const uint4 *>(launch.query);
     args.key = static_cast<const uint4 *>(launch.key);
@@ -378,8 +572,25 @@ int launch_rope_append(const AppendLaunch &launch, void *stream) {
     args.kvh = launch.kvh;
     args.indices_len = launch.indices_len;
     args.hash_slots = launch.hash_slots;
+    return args;
+}
+
+int launch_rope_append(const AppendLaunch &launch, void *stream) {
     return launch_dependent(rope_append_kernel, launch.grid, launch.block, launch.shared_bytes,
-                            stream, args);
+                            stream, append_args(launch));
+}
+
+int append_workspace_numel(size_t tokens) { return (int)(kVerdictSlots + 2 * tokens); }
+
+int launch_append_validate(const AppendLaunch &launch, void *stream) {
+    return launch_dependent(append_validate_kernel, launch.validate_grid, kValidateThreads,
+                            launch.shared_bytes, stream, append_args(launch), launch.workspace);
+}
+
+int launch_append_scatter(const AppendLaunch &launch, void *stream) {
+    return launch_dependent(append_scatter_kernel, (unsigned)launch.tokens, kScatterThreads, 0,
+                            stream, append_args(launch),
+                            static_cast<const int32_t *>(launch.workspace));
 }
 
 } // namespace lb

@@ -43,6 +43,10 @@ struct AppendLaunch {
     int32_t tokens, batch, max_pages, qh, kvh, indices_len;
     int32_t hash_slots; // power of two >= 2 * tokens
     uint32_t grid, block, shared_bytes;
+    // two-command (extended) plans only: I32 workspace of append_workspace_numel(tokens) and
+    // the CTAs of the validation kernel (1, or 1 token CTA + page-table scanners)
+    int32_t *workspace;
+    uint32_t validate_grid;
 };
 
 // Each returns a CUDA error code (0 = success).
@@ -56,6 +60,9 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream);
 int launch_split_merge(const MergeLaunch &launch, void *stream);
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency);
 int launch_rope_append(const AppendLaunch &launch, void *stream);
+int append_workspace_numel(size_t tokens);
+int launch_append_validate(const AppendLaunch &launch, void *stream);
+int launch_append_scatter(const AppendLaunch &launch, void *stream);
 // One stand-alone RoPE launch over contiguous NHD Q and K.
 struct RopeLaunch {
     const void *query, *key;   // bf16 [tokens, heads, 128]

@@ -40,6 +40,10 @@ struct lb_rope_append_plan {
     size_t tokens = 0;
     int device = 0;
     uint32_t grid = 0, block = 256, shared_bytes = 0, hash_slots = 0;
+    // extended plans: validate + scatter as two commands over a caller-bound I32 workspace
+    bool extended = false;
+    uint32_t validate_grid = 0;
+    size_t workspace_numel = 0;
 };
 
 struct lb_state_merge_plan {
@@ -399,7 +403,7 @@ lb_status lb_rope_provider_load(int device, lb_rope_provider **out) {
 void lb_rope_provider_destroy(lb_rope_provider *provider) { delete provider; }
 
 static lb_status make_append_plan(const lb_rope_provider *provider, const lb_paged_spec &spec,
-                                  bool explicit_tokens, size_t tokens,
+                                  bool explicit_tokens, size_t tokens, bool extended,
                                   lb_rope_append_plan **out) {
     // state count checks of plan_bf16_paged_append{,_tokens}, rope/mod.rs:628-682
     size_t heads, states;
@@ -429,6 +433,13 @@ static lb_status make_append_plan(const lb_rope_provider *provider, const lb_pag
     const uint32_t per_cta = (uint32_t)append_max_tokens_per_cta();
     const uint32_t floor = (uint32_t)((tokens + per_cta - 1) / per_cta);
     plan->grid = tokens < cap ? (uint32_t)tokens : (cap > floor ? cap : floor);
+    if (extended) {
+        // one validation CTA for the tokens plus one scanner per 8192 pages of the pool
+        plan->extended = true;
+        const size_t scanners = (spec.max_num_pages + 8191) / 8192;
+        plan->validate_grid = (uint32_t)(1 + (scanners > 31 ? 31 : scanners));
+        plan->workspace_numel = (size_t)append_workspace_numel(tokens);
+    }
     *out = plan;
     return LB_OK;
 }
@@ -441,7 +452,7 @@ lb_status lb_rope_append_plan_create(const lb_rope_provider *provider, const lb_
     lb_status rc = lb_paged_spec_new(spec->batch_size, spec->max_num_pages, spec->num_query_heads,
                                      spec->num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE, &checked);
     if (rc) return rc;
-    return make_append_plan(provider, checked, false, checked.batch_size, out);
+    return make_append_plan(provider, checked, false, checked.batch_size, false, out);
 }
 
 lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
@@ -462,7 +473,8 @@ lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
                                         spec->paged.num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE,
                                         &checked);
     if (rc) return rc;
-    return make_append_plan(provider, checked.paged, true, checked.tokens, out);
+    return make_append_plan(provider, checked.paged, true, checked.tokens,
+                            checked.max_tokens == 0, out);
 }
 
 void lb_rope_append_plan_destroy(lb_rope_append_plan *plan) { delete plan; }
@@ -475,7 +487,8 @@ lb_status lb_rope_append_plan_info_get(const lb_rope_append_plan *plan,
     info->grid = plan->grid;
     info->block = plan->block;
     info->shared_bytes = plan->shared_bytes;
-    info->commands = 1;
+    info->commands = plan->extended ? 2 : 1;
+    info->workspace_numel = plan->workspace_numel;
     return LB_OK;
 }
 
@@ -485,7 +498,8 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     const lb_paged_spec &spec = plan->spec;
     if (scope->queue->device != plan->device)
         return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
-    lb_status rc = require_command_capacity(*scope, 1);
+    // both commands of an extended plan must fit before anything is launched
+    lb_status rc = require_command_capacity(*scope, plan->extended ? 2 : 1);
     if (rc) return rc;
 
     Operand op[11];
@@ -565,7 +579,21 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     launch.block = plan->block;
     launch.shared_bytes = plan->shared_bytes;
     void *stream = scope->queue->stream;
-    return submit_launch(*scope, [&]() { return launch_rope_append(launch, stream); });
+    if (!plan->extended)
+        return submit_launch(*scope, [&]() { return launch_rope_append(launch, stream); });
+
+    // extended: command 1 validates into the workspace, command 2 reads it (write, then read,
+    // like the split-K workspace)
+    OperandRequest ws_request[1] = {{args->workspace, LB_I32, true}};
+    Operand ws[1];
+    if ((rc = resolve(*scope, ws_request, 1, ws))) return rc;
+    if ((rc = require_exact_len("workspace", ws[0].numel, plan->workspace_numel))) return rc;
+    launch.workspace = (int32_t *)ws[0].ptr;
+    launch.validate_grid = plan->validate_grid;
+    if ((rc = submit_launch(*scope, [&]() { return launch_append_validate(launch, stream); })))
+        return rc;
+    if ((rc = require_command_capacity(*scope, 1))) return rc;
+    return submit_launch(*scope, [&]() { return launch_append_scatter(launch, stream); });
 }
 
 // ---- stand-alone RoPE ------------------------------------------------------------------------------

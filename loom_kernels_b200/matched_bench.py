@@ -109,10 +109,10 @@ class AppendCase:
         return self.w.tokens
 
     def commands(self):
-        return len(self.chunks)
+        return sum(plan.commands() for _, _, plan in self.chunks)
 
     def slots(self):
-        return 3 + 6 * len(self.chunks) + 2 * self.copies
+        return 3 + 7 * len(self.chunks) + 2 * self.copies
 
     def bind(self, bindings):
         w = self.w
@@ -126,8 +126,12 @@ class AppendCase:
                      self.batch_indices[start:stop], self.positions[start:stop])
             reads = [bindings.bind_read(t) for t in views]
             q_out = bindings.bind_read_write(self.q_out[start * w.qh * 128:stop * w.qh * 128])
+            ws = None
+            if plan.workspace_required_numel():  # extended plans validate into a workspace
+                ws = bindings.bind_read_write(torch.zeros(plan.workspace_required_numel(),
+                                                          dtype=torch.int32, device=self.device))
             per_pool = [lk.Bf16RopePagedKvAppendTokensArgs(*reads, *meta, q_out.write(), kp.write(),
-                                                           vp.write()) for kp, vp in pools]
+                                                           vp.write(), ws) for kp, vp in pools]
             self.args.append((plan, per_pool))
 
     def enqueue(self, scope, call):

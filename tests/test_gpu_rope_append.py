@@ -39,7 +39,10 @@ class AppendRun:
         self.plan = (provider.plan_bf16_paged_append_tokens(spec) if self.explicit
                      else provider.plan_bf16_paged_append(spec))
         self.stream = torch.cuda.Stream()
-        self.queue = lk.CommandQueue(self.stream, max_commands)
+        self.queue = lk.CommandQueue(self.stream, max(max_commands, self.plan.commands()))
+        numel = self.plan.workspace_required_numel()  # extended plans: validate, then scatter
+        self.workspace = (torch.full((numel,), -1, dtype=torch.int32, device="cuda:0")
+                          if numel else None)
         self.t = dict(query=H.dev_bf16(q), key=H.dev_bf16(k), value=H.dev_bf16(v),
                       page_indptr=H.dev_i32(indptr), page_indices=H.dev_i32(indices),
                       last_page_len=H.dev_i32(last))
@@ -52,7 +55,7 @@ class AppendRun:
         torch.cuda.synchronize()
 
     def bind(self, bindings=None):
-        b = bindings or self.queue.bindings(11)
+        b = bindings or self.queue.bindings(12)
         order = (["query", "key", "value", "batch_indices", "positions", "page_indptr",
                   "page_indices", "last_page_len"] if self.explicit else
                  ["query", "key", "value", "page_indptr", "page_indices", "last_page_len"])
@@ -60,12 +63,18 @@ class AppendRun:
         self.h_q = b.bind_read_write(self.q_out)
         self.h_k = b.bind_read_write(self.k_pages)
         self.h_v = b.bind_read_write(self.v_pages)
+        self.h_ws = b.bind_read_write(self.workspace) if self.workspace is not None else None
         return b
 
     def args(self):
-        cls = lk.Bf16RopePagedKvAppendTokensArgs if self.explicit else lk.Bf16RopePagedKvAppendArgs
-        return cls(query_output=self.h_q.write(), key_pages=self.h_k.write(),
-                   value_pages=self.h_v.write(), **self.h)
+        if not self.explicit:
+            return lk.Bf16RopePagedKvAppendArgs(query_output=self.h_q.write(),
+                                                key_pages=self.h_k.write(),
+                                                value_pages=self.h_v.write(), **self.h)
+        return lk.Bf16RopePagedKvAppendTokensArgs(query_output=self.h_q.write(),
+                                                  key_pages=self.h_k.write(),
+                                                  value_pages=self.h_v.write(),
+                                                  workspace=self.h_ws, **self.h)
 
     def run(self):
         scope = self.queue.begin(self.bind())
@@ -239,7 +248,7 @@ def test_extended_append_equals_chunked_reference(oracle, provider, shuffle):
     run = AppendRun(provider, spec, q, k, v, indptr, indices, last, kp0, vp0, batch_indices,
                     positions)
     actual = run.run()
-    assert run.submitted == 1
+    assert run.submitted == run.plan.commands() == 2
     ospec = oracle.paged_spec(batch, pool_pages, qh, kvh)
     kc, vc, qc = kp0, vp0, []
     for start in range(0, tokens, 64):
