@@ -69,6 +69,21 @@ def test_shapes_thetas_and_scales(provider, oracle, tokens, qh, kh, theta, scale
     assert within_one_ulp(aq, eq) and within_one_ulp(ak, ek)
 
 
+@pytest.mark.parametrize("scale", [1.0, 0.25])
+def test_largest_positions(provider, oracle, scale):
+    """Positions up to 2^31 - 1: angles up to 2.1e9 stay inside the in-kernel reduction (scale 1);
+    with scale 0.25 they reach 8.6e9 and take the library routine."""
+    positions = np.array([2147483647, 2147483646, 1073741824, 1999999999, 65536, 3],
+                         dtype=np.int32)
+    rng = np.random.default_rng(11)
+    spec = lk.Bf16RopePosIdsSpec.new(len(positions), 4, 2, 128, 128, scale, 10000.0)
+    q = H.normal_bf16(rng, spec.query_numel())
+    k = H.normal_bf16(rng, spec.key_numel())
+    eq, ek = oracle.rope(len(positions), 4, 2, q, k, positions, scale=scale)
+    aq, ak = run(provider, spec, q, k, positions)
+    assert within_one_ulp(aq, eq) and within_one_ulp(ak, ek)
+
+
 def test_negative_position_keeps_that_tokens_sentinels(provider, oracle):
     """rope.rs: negative_position_guard_preserves_output_sentinels.  The guard is per token
     (crates/loom-infer-cuda/src/rope/mod.rs:64-67): the other tokens are still rotated."""
