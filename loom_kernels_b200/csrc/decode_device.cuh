@@ -303,17 +303,46 @@ __device__ __forceinline__ void write_state_row(float *state, int lane, int half
 // `publish` is consulted only after every load has been issued, so a caller can hand in a
 // predicate that itself depends on loads still in flight (the request guard) without putting a
 // second memory round trip in front of the state loads.
-constexpr int kMergeBatch = 16; // states whose row loads are in flight together
+constexpr int kMergeBatch = 16;  // states whose row loads are in flight together
+constexpr int kMergeCached = 4;  // rounds of 32 states whose (max, normaliser) stay in registers
 
-// The part of a merge one warp computes: the global maximum over all n states, then the weighted
-// sums over states first, first + stride, ... (per lane: four of the 128 dims; `norm` is complete
-// in every lane).  Returns false when a state is poisoned.
+// The weighted sums of a merge, computed by one warp (per lane: four of the 128 dims; `norm` is
+// complete in every lane).  Returns false when a state is poisoned.  Everything that does not
+// depend on a value still in flight is issued first: the (max, normaliser) pairs of the first
+// 128 states and the rows of the first 16, so that a merge of up to 16 states -- the common
+// case -- costs one memory round trip, and a long request one more per 16 states.
 template <typename StateOf>
-__device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane, int first,
-                                              int stride, float &top, float &norm, float4 &acc) {
+__device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane, float &top,
+                                              float &norm, float4 &acc) {
+    float my_norm[kMergeCached], my_max[kMergeCached];
+#pragma unroll
+    for (int k = 0; k < kMergeCached; ++k) {
+        const float *s = k * 32 + lane < n ? state_of(k * 32 + lane) : nullptr;
+        my_norm[k] = s ? __ldcg(s + 1) : 0.0f;
+        my_max[k] = s ? __ldcg(s) : 0.0f;
+    }
+    float2 lo[kMergeBatch], hi[kMergeBatch];
+    auto fetch_rows = [&](int base) { // rows of states base .. base + 15 (zero past n)
+#pragma unroll
+        for (int u = 0; u < kMergeBatch; ++u) {
+            const float *s = base + u < n ? state_of(base + u) : nullptr;
+            lo[u] = hi[u] = make_float2(0.f, 0.f);
+            if (s != nullptr) {
+                lo[u] = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
+                hi[u] = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+            }
+        }
+    };
+    fetch_rows(0);
+
     top = -INFINITY;
     bool poisoned = false;
-    for (int i = lane; i < n; i += 32) {
+#pragma unroll
+    for (int k = 0; k < kMergeCached; ++k) {
+        poisoned |= my_norm[k] < 0.0f;
+        if (my_norm[k] > 0.0f) top = fmaxf(top, my_max[k]);
+    }
+    for (int i = kMergeCached * 32 + lane; i < n; i += 32) { // beyond the cached rounds
         const float *s = state_of(i);
         if (s == nullptr) continue;
         const float part_norm = __ldcg(s + 1);
@@ -323,33 +352,34 @@ __device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane,
     if (__any_sync(0xffffffffu, poisoned)) return false;
 #pragma unroll
     for (int d = 16; d >= 1; d >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, d));
-    // 32 states per round: lane l computes the weight of its state once, then the rows are
-    // accumulated sixteen states at a time with all 32 loads of a batch in flight together
-    // (a long request is cut into a hundred states; one load latency per state would dominate)
+
+    // 32 states per round: lane l holds the weight of state round * 32 + l
     norm = 0.0f;
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const int mine_n = first < n ? (n - first + stride - 1) / stride : 0;
-    for (int base = 0; base < mine_n; base += 32) {
-        const float *mine = base + lane < mine_n ? state_of(first + (base + lane) * stride) : nullptr;
-        const float my_norm = mine ? __ldcg(mine + 1) : 0.0f;
-        const float my_weight = my_norm > 0.0f ? exp2f(__ldcg(mine) - top) : 0.0f;
-        norm += my_norm * my_weight;
-        const int count = min(32, mine_n - base);
-        for (int j = 0; j < count; j += kMergeBatch) {
-            float2 lo[kMergeBatch], hi[kMergeBatch];
+    for (int round = 0; round * 32 < n; ++round) {
+        float part_norm = 0.0f, part_max = 0.0f;
+        if (round < kMergeCached) {
 #pragma unroll
-            for (int u = 0; u < kMergeBatch; ++u) {
-                const float *s =
-                    j + u < count ? state_of(first + (base + j + u) * stride) : nullptr;
-                lo[u] = hi[u] = make_float2(0.f, 0.f);
-                if (s != nullptr) {
-                    lo[u] = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
-                    hi[u] = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+            for (int k = 0; k < kMergeCached; ++k)
+                if (k == round) {
+                    part_norm = my_norm[k];
+                    part_max = my_max[k];
                 }
-            }
+        } else {
+            const float *s = round * 32 + lane < n ? state_of(round * 32 + lane) : nullptr;
+            part_norm = s ? __ldcg(s + 1) : 0.0f;
+            part_max = s ? __ldcg(s) : 0.0f;
+        }
+        const float my_weight = part_norm > 0.0f ? exp2f(part_max - top) : 0.0f;
+        norm += part_norm * my_weight;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int base = round * 32 + half * kMergeBatch;
+            if (base >= n) break;
+            if (base > 0) fetch_rows(base); // the first batch is already here
 #pragma unroll
             for (int u = 0; u < kMergeBatch; ++u) {
-                const float weight = __shfl_sync(0xffffffffu, my_weight, (j + u) & 31);
+                const float weight = __shfl_sync(0xffffffffu, my_weight, half * kMergeBatch + u);
                 acc.x += lo[u].x * weight;
                 acc.y += lo[u].y * weight;
                 acc.z += hi[u].x * weight;
@@ -377,7 +407,7 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
                                              __nv_bfloat16 *out_row, float *lse_slot) {
     float top, norm;
     float4 acc;
-    if (!merge_partial(state_of, n, lane, 0, 1, top, norm, acc) || !publish) return;
+    if (!merge_partial(state_of, n, lane, top, norm, acc) || !publish) return;
     if (!(norm > 0.0f)) return; // every state was empty: nothing to publish
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
 }
@@ -399,12 +429,11 @@ struct EvenCut {
     __device__ __forceinline__ long long begin(int w) const {
         return q * w + (long long)((unsigned)r * (unsigned)w / (unsigned)workers);
     }
-    // the worker whose range [begin(w), begin(w + 1)) contains x
+    // the worker whose range [begin(w), begin(w + 1)) contains x: begin(w) <= x means
+    // total * w / workers < x + 1, i.e. w <= ((x + 1) * workers - 1) / total
     __device__ __forceinline__ int owner(long long x) const {
-        int w = (int)(x / q); // every worker holds at least q >= 1 units, so this is an upper bound
-        if (w >= workers) w = workers - 1;
-        while (begin(w) > x) --w;
-        return w;
+        const long long total = q * workers + r;
+        return (int)(((x + 1) * workers - 1) / total);
     }
 };
 
