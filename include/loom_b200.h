@@ -297,7 +297,14 @@ typedef struct lb_paged_decode_options {
     uint32_t balanced;      /* with partitions == 0: 0 = heuristic, 1 = force the balanced
                                algorithm, 2 = never use it */
     uint32_t balanced_ctas; /* CTAs of the balanced algorithm; 0 = heuristic (<= one per SM) */
-    uint32_t reserved[4];
+    uint32_t indices_capacity; /* 0: the bound page_indices are exactly the table (the reference's
+                                  rule, page_indptr[batch] == page_indices.len());
+                                  1: page_indices may be bound LONGER than the table in use
+                                  (page_indptr[batch] <= len, the tail is never read), so that a
+                                  fixed-address Graph survives a change of the total page count.
+                                  No reference counterpart (the reference lists the mutable-
+                                  metadata Graph contract as open, docs/operator-catalog.md). */
+    uint32_t reserved[3];
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
@@ -397,13 +404,26 @@ typedef struct lb_rope_append_plan_info {
 /* RopeProvider::load, rope/mod.rs:586-590 */
 lb_status lb_rope_provider_load(int device, lb_rope_provider **out);
 void lb_rope_provider_destroy(lb_rope_provider *provider);
+/* Plan options of the append (NULL = all zero). */
+typedef struct lb_rope_append_options {
+    uint32_t indices_capacity; /* as lb_paged_decode_options.indices_capacity */
+    uint32_t reserved[3];
+} lb_rope_append_options;
 /* RopeProvider::plan_bf16_paged_append, rope/mod.rs:628-654 */
 lb_status lb_rope_append_plan_create(const lb_rope_provider *provider, const lb_paged_spec *spec,
                                      lb_rope_append_plan **out);
+lb_status lb_rope_append_plan_create_with(const lb_rope_provider *provider,
+                                          const lb_paged_spec *spec,
+                                          const lb_rope_append_options *options,
+                                          lb_rope_append_plan **out);
 /* RopeProvider::plan_bf16_paged_append_tokens, rope/mod.rs:656-682 */
 lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
                                             const lb_append_tokens_spec *spec,
                                             lb_rope_append_plan **out);
+lb_status lb_rope_append_tokens_plan_create_with(const lb_rope_provider *provider,
+                                                 const lb_append_tokens_spec *spec,
+                                                 const lb_rope_append_options *options,
+                                                 lb_rope_append_plan **out);
 void lb_rope_append_plan_destroy(lb_rope_append_plan *plan);
 lb_status lb_rope_append_plan_info_get(const lb_rope_append_plan *plan,
                                        lb_rope_append_plan_info *info);

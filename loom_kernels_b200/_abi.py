@@ -51,7 +51,12 @@ class Handle(ctypes.Structure):
 
 class DecodeOptions(ctypes.Structure):
     _fields_ = [("partitions", c_uint32), ("heads_per_cta", c_uint32), ("balanced", c_uint32),
-                ("balanced_ctas", c_uint32), ("reserved", c_uint32 * 4)]
+                ("balanced_ctas", c_uint32), ("indices_capacity", c_uint32),
+                ("reserved", c_uint32 * 3)]
+
+
+class AppendOptions(ctypes.Structure):
+    _fields_ = [("indices_capacity", c_uint32), ("reserved", c_uint32 * 3)]
 
 
 class DecodePlanInfo(ctypes.Structure):
@@ -169,6 +174,11 @@ SIGNATURES = {
     "lb_rope_append_plan_create": (c_int32, [c_void_p, POINTER(PagedSpec), POINTER(c_void_p)]),
     "lb_rope_append_tokens_plan_create": (c_int32, [c_void_p, POINTER(AppendTokensSpec),
                                                     POINTER(c_void_p)]),
+    "lb_rope_append_plan_create_with": (c_int32, [c_void_p, POINTER(PagedSpec),
+                                                  POINTER(AppendOptions), POINTER(c_void_p)]),
+    "lb_rope_append_tokens_plan_create_with": (c_int32, [c_void_p, POINTER(AppendTokensSpec),
+                                                         POINTER(AppendOptions),
+                                                         POINTER(c_void_p)]),
     "lb_rope_append_plan_destroy": (None, [c_void_p]),
     "lb_rope_append_plan_info_get": (c_int32, [c_void_p, POINTER(AppendPlanInfo)]),
     "lb_rope_append_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(AppendArgs)]),

@@ -530,11 +530,15 @@ class DecodeProvider:
 
     def plan_bf16_paged_batch(self, spec: Bf16PagedBatchDecodeSpec, partitions: int = 0,
                               heads_per_cta: int = 0, balanced: int = 0,
-                              balanced_ctas: int = 0) -> "Bf16PagedBatchDecodePlan":
+                              balanced_ctas: int = 0,
+                              indices_capacity: bool = False) -> "Bf16PagedBatchDecodePlan":
         """partitions: 0 heuristic, 1 direct, N split-K; balanced (with partitions 0): 0
-        heuristic, 1 force the balanced algorithm, 2 never use it."""
+        heuristic, 1 force the balanced algorithm, 2 never use it.  indices_capacity: the bound
+        page_indices may be longer than the table in use (page_indptr[batch] <= len), which
+        lets one fixed-address Graph serve steps with different total page counts."""
         options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta,
-                                     balanced=balanced, balanced_ctas=balanced_ctas)
+                                     balanced=balanced, balanced_ctas=balanced_ctas,
+                                     indices_capacity=1 if indices_capacity else 0)
         out = c_void_p()
         _check(_abi.load().lb_paged_decode_plan_create(self._ptr, byref(spec._raw),
                                                        byref(options), byref(out)))
@@ -719,16 +723,21 @@ class RopeProvider:
     def __del__(self):
         _dispose(self, "lb_rope_provider_destroy")
 
-    def plan_bf16_paged_append(self, spec: Bf16RopePagedKvAppendSpec):
+    def plan_bf16_paged_append(self, spec: Bf16RopePagedKvAppendSpec,
+                               indices_capacity: bool = False):
+        """indices_capacity: see DecodeProvider.plan_bf16_paged_batch."""
         out = c_void_p()
-        _check(_abi.load().lb_rope_append_plan_create(self._ptr, byref(spec.paged()._raw),
-                                                      byref(out)))
+        options = _abi.AppendOptions(indices_capacity=1 if indices_capacity else 0)
+        _check(_abi.load().lb_rope_append_plan_create_with(self._ptr, byref(spec.paged()._raw),
+                                                           byref(options), byref(out)))
         return Bf16RopePagedKvAppendPlan(out.value, spec)
 
-    def plan_bf16_paged_append_tokens(self, spec: Bf16RopePagedKvAppendTokensSpec):
+    def plan_bf16_paged_append_tokens(self, spec: Bf16RopePagedKvAppendTokensSpec,
+                                      indices_capacity: bool = False):
         out = c_void_p()
-        _check(_abi.load().lb_rope_append_tokens_plan_create(self._ptr, byref(spec._raw),
-                                                             byref(out)))
+        options = _abi.AppendOptions(indices_capacity=1 if indices_capacity else 0)
+        _check(_abi.load().lb_rope_append_tokens_plan_create_with(
+            self._ptr, byref(spec._raw), byref(options), byref(out)))
         return Bf16RopePagedKvAppendTokensPlan(out.value, spec)
 
 

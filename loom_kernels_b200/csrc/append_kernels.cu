@@ -51,7 +51,7 @@ struct AppendArgs {
     const uint4 *query, *key, *value;
     const int32_t *batch_indices, *positions, *indptr, *indices, *last;
     uint4 *query_output, *key_pages, *value_pages;
-    int32_t tokens, batch, max_pages, qh, kvh, indices_len, hash_slots;
+    int32_t tokens, batch, max_pages, qh, kvh, indices_len, indices_min, hash_slots;
 };
 
 // Levels 1-2 of the token -> request -> page chain, from in-bounds loads only: an out-of-range
@@ -251,22 +251,23 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
     LB_STAMP(1);
 
     // ---- 1. whole-call validation (identical in every CTA) -----------------------------------
-    bool invalid = false;
-    if (tid == 0) {
-        const int final_indptr = a.indptr[a.batch];
-        invalid = a.indptr[0] != 0 || final_indptr < 0 || final_indptr != a.indices_len;
-    }
+    // the table ends at page_indptr[batch], which must lie in [indices_min, indices_len] (equal
+    // bounds unless the plan was made with the capacity option); entries past it are not read
+    const int final_indptr = a.indptr[a.batch];
+    bool invalid = a.indptr[0] != 0 || final_indptr < a.indices_min || final_indptr > a.indices_len;
+    int table_end = a.indices_len; // known without a load unless the plan has the capacity option
+    if (a.indices_min != a.indices_len) table_end = min(max(final_indptr, 0), a.indices_len);
     for (int request = tid; request < a.batch; request += kThreads) {
         const int begin = a.indptr[request], end = a.indptr[request + 1], tail = a.last[request];
-        if (begin < 0 || end <= begin || end > a.indices_len || tail < 1 || tail > kPage)
+        if (begin < 0 || end <= begin || end > table_end || tail < 1 || tail > kPage)
             invalid = true;
     }
-    for (int base = 0; base < a.indices_len; base += 4 * kThreads) {
+    for (int base = 0; base < table_end; base += 4 * kThreads) {
         int id[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int page = base + u * kThreads + tid;
-            id[u] = page < a.indices_len ? a.indices[page] : 0;
+            id[u] = page < table_end ? a.indices[page] : 0;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
@@ -369,24 +370,24 @@ append_validate_kernel(const AppendArgs a, int32_t *workspace) {
         // page-table and request checks, sliced over the scanning CTAs
         const int scanners = gridDim.x == 1 ? 1 : (int)gridDim.x - 1;
         const int me = gridDim.x == 1 ? 0 : (int)blockIdx.x - 1;
-        if (me == 0 && tid == 0) {
-            const int final_indptr = a.indptr[a.batch];
-            invalid = a.indptr[0] != 0 || final_indptr < 0 || final_indptr != a.indices_len;
-        }
+        const int final_indptr = a.indptr[a.batch]; // must lie in [indices_min, indices_len]
+        invalid = a.indptr[0] != 0 || final_indptr < a.indices_min || final_indptr > a.indices_len;
+        int table_end = a.indices_len;
+        if (a.indices_min != a.indices_len) table_end = min(max(final_indptr, 0), a.indices_len);
         for (int request = me * kValidateThreads + tid; request < a.batch;
              request += scanners * kValidateThreads) {
             const int begin = a.indptr[request], end = a.indptr[request + 1];
             const int tail = a.last[request];
-            if (begin < 0 || end <= begin || end > a.indices_len || tail < 1 || tail > kPage)
+            if (begin < 0 || end <= begin || end > table_end || tail < 1 || tail > kPage)
                 invalid = true;
         }
-        for (int base = me * 4 * kValidateThreads; base < a.indices_len;
+        for (int base = me * 4 * kValidateThreads; base < table_end;
              base += scanners * 4 * kValidateThreads) {
             int id[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int page = base + u * kValidateThreads + tid;
-                id[u] = page < a.indices_len ? a.indices[page] : 0;
+                id[u] = page < table_end ? a.indices[page] : 0;
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
@@ -571,6 +572,7 @@ static AppendArgs append_args(const AppendLaunch &launch) {
     args.qh = launch.qh;
     args.kvh = launch.kvh;
     args.indices_len = launch.indices_len;
+    args.indices_min = launch.indices_min;
     args.hash_slots = launch.hash_slots;
     return args;
 }

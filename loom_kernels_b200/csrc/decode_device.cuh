@@ -113,15 +113,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Per-request metadata guard of the reference's kernels
-// (crates/loom-infer-cuda/src/attention/decode.rs:234-248 / :426-437).
+// (crates/loom-infer-cuda/src/attention/decode.rs:234-248 / :426-437).  The end of the table,
+// page_indptr[batch], must lie in [indices_min, indices_len]: the reference's rule is
+// indices_min == indices_len (the bound page_indices are exactly the table); a plan made with
+// the capacity option passes 0, so that page_indices may be bound longer than the table in use.
 __device__ __forceinline__ bool request_metadata_valid(const int32_t *indptr, const int32_t *last,
-                                                       int batch, int indices_len, int request,
-                                                       int &page_start, int &page_end, int &tail) {
+                                                       int batch, int indices_min, int indices_len,
+                                                       int request, int &page_start, int &page_end,
+                                                       int &tail) {
     const int global_end = indptr[batch];
     page_start = indptr[request];
     page_end = indptr[request + 1];
     tail = last[request];
-    return indptr[0] == 0 && global_end >= 0 && global_end == indices_len && page_start >= 0 &&
+    return indptr[0] == 0 && global_end >= indices_min && global_end <= indices_len &&
+           page_start >= 0 &&
            page_end > page_start && page_end <= global_end && tail >= 1 && tail <= kPage;
 }
 

@@ -43,7 +43,7 @@ struct DecodeArgs {
     float *lse;
     float *workspace;
     int32_t *status;
-    int32_t batch, max_pages, qh, kvh, indices_len;
+    int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, partitions, stages;
     float scale_log2;
 };
@@ -97,8 +97,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
     int page_start, page_end, tail;
-    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_len, request, page_start,
-                                page_end, tail))
+    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_min, a.indices_len, request,
+                                page_start, page_end, tail))
         return;
     LB_STAMP(1);
     const int num_pages = page_end - page_start;
@@ -318,7 +318,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
 __global__ void __launch_bounds__(128)
 split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                    const int32_t *indptr, const int32_t *last, int batch, int qh, int partitions,
-                   int indices_len) {
+                   int indices_min, int indices_len) {
     dependent_launch_release();
     const int lane = threadIdx.x & 31;
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -328,7 +328,7 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
     // the guard's loads and the state loads travel together; the verdict is used at the end
     int page_start, page_end, tail;
     const bool valid = indptr == nullptr || // a bare state merge has no request metadata
-                       request_metadata_valid(indptr, last, batch, indices_len, request,
+                       request_metadata_valid(indptr, last, batch, indices_min, indices_len, request,
                                               page_start, page_end, tail);
     const float *st = workspace + (size_t)state * partitions * kStateWidth;
     merge_states([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane, valid,
@@ -359,6 +359,7 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     args.qh = launch.qh;
     args.kvh = launch.kvh;
     args.indices_len = launch.indices_len;
+    args.indices_min = launch.indices_min;
     args.hc = launch.heads_per_cta;
     args.pps = launch.pages_per_stage;
     args.mt = launch.q_tiles;
@@ -378,7 +379,7 @@ int launch_split_merge(const MergeLaunch &launch, void *stream) {
     return launch_dependent(split_merge_kernel, launch.grid, launch.block, 0, stream,
                             launch.workspace, static_cast<__nv_bfloat16 *>(launch.output),
                             launch.lse, launch.indptr, launch.last, launch.batch, launch.qh,
-                            launch.partitions, launch.indices_len);
+                            launch.partitions, launch.indices_min, launch.indices_len);
 }
 
 } // namespace lb

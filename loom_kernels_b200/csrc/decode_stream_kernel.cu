@@ -38,7 +38,7 @@ struct StreamArgs {
     float *lse;
     float *workspace; // [workers][2][hc * rows][130] F32, then prefix[batch + 1] I32
     int32_t *status;
-    int32_t batch, max_pages, qh, kvh, indices_len;
+    int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, stages, workers;
     int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
     float scale_log2;
@@ -103,7 +103,8 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
 
     // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
     const int global_end = a.indptr[a.batch];
-    const bool global_ok = a.indptr[0] == 0 && global_end >= 0 && global_end == a.indices_len;
+    const bool global_ok =
+        a.indptr[0] == 0 && global_end >= a.indices_min && global_end <= a.indices_len;
     for (int r = tid; r < a.batch; r += blockDim.x) {
         const int s = a.indptr[r], e = a.indptr[r + 1], t = a.last[r];
         const bool ok = global_ok && s >= 0 && e > s && e <= global_end && t >= 1 && t <= kPage;
@@ -406,6 +407,7 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     args.qh = launch.qh;
     args.kvh = launch.kvh;
     args.indices_len = launch.indices_len;
+    args.indices_min = launch.indices_min;
     args.hc = launch.heads_per_cta;
     args.pps = launch.pages_per_stage;
     args.mt = launch.q_tiles;

@@ -19,6 +19,7 @@ struct DecodeLaunch {
     float *workspace;        // [batch, qh, partitions, 130] when partitions > 1
     int32_t *status;         // optional device status word (0 = ok)
     int32_t batch, max_pages, qh, kvh, indices_len;
+    int32_t indices_min; // page_indptr[batch] must lie in [indices_min, indices_len]
     int32_t heads_per_cta, pages_per_stage, q_tiles, q_blocks, partitions, stages;
     float scale_log2;
     uint32_t grid, block, shared_bytes;
@@ -30,7 +31,7 @@ struct MergeLaunch {
     float *lse;
     const int32_t *indptr;
     const int32_t *last;
-    int32_t batch, qh, partitions, indices_len;
+    int32_t batch, qh, partitions, indices_len, indices_min;
     uint32_t grid, block;
 };
 
@@ -40,7 +41,7 @@ struct AppendLaunch {
     const int32_t *batch_indices, *positions; // [tokens]; null for one-token-per-request
     const int32_t *indptr, *indices, *last;
     void *query_output, *key_pages, *value_pages;
-    int32_t tokens, batch, max_pages, qh, kvh, indices_len;
+    int32_t tokens, batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hash_slots; // power of two >= 2 * tokens
     uint32_t grid, block, shared_bytes;
     // two-command (extended) plans only: I32 workspace of append_workspace_numel(tokens) and

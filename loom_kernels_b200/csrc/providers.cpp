@@ -27,6 +27,7 @@ struct lb_paged_decode_plan {
     DecodeChoice choice;
     int device = 0;
     int32_t *status = nullptr;
+    bool indices_capacity = false; // page_indices may be bound longer than the table in use
 };
 
 struct lb_rope_provider {
@@ -44,6 +45,7 @@ struct lb_rope_append_plan {
     bool extended = false;
     uint32_t validate_grid = 0;
     size_t workspace_numel = 0;
+    bool indices_capacity = false; // page_indices may be bound longer than the table in use
 };
 
 struct lb_state_merge_plan {
@@ -175,7 +177,10 @@ lb_status lb_paged_decode_plan_create(const lb_decode_provider *provider, const 
     if ((rc = choose_decode(checked, (uint32_t)provider->sm_count, provider->smem_optin, options,
                             &choice)))
         return rc;
+    if (options && options->indices_capacity > 1)
+        return fail(LB_LAUNCH_CONTRACT, "indices_capacity", options->indices_capacity);
     lb_paged_decode_plan *plan = new lb_paged_decode_plan();
+    plan->indices_capacity = options && options->indices_capacity == 1;
     plan->spec = checked;
     plan->choice = choice;
     plan->device = provider->device;
@@ -266,6 +271,7 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     launch.qh = (int32_t)spec.num_query_heads;
     launch.kvh = (int32_t)spec.num_kv_heads;
     launch.indices_len = (int32_t)op[4].numel;
+    launch.indices_min = plan->indices_capacity ? 0 : launch.indices_len;
     launch.heads_per_cta = (int32_t)c.heads_per_cta;
     launch.pages_per_stage = (int32_t)c.pages_per_stage;
     launch.q_tiles = (int32_t)c.q_tiles;
@@ -307,6 +313,7 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     merge.qh = launch.qh;
     merge.partitions = launch.partitions;
     merge.indices_len = launch.indices_len;
+    merge.indices_min = launch.indices_min;
     merge.grid = c.merge_grid;
     merge.block = c.merge_block;
     return submit_launch(*scope, [&]() { return launch_split_merge(merge, stream); });
@@ -365,6 +372,7 @@ lb_status lb_state_merge_enqueue(const lb_state_merge_plan *plan, lb_scope *scop
     merge.qh = 1;
     merge.partitions = (int32_t)plan->partitions;
     merge.indices_len = 0;
+    merge.indices_min = 0;
     merge.grid = (uint32_t)((plan->rows + 3) / 4);
     merge.block = 128;
     void *stream = scope->queue->stream;
@@ -444,20 +452,48 @@ static lb_status make_append_plan(const lb_rope_provider *provider, const lb_pag
     return LB_OK;
 }
 
+static lb_status apply_append_options(const lb_rope_append_options *options,
+                                      lb_rope_append_plan **plan) {
+    if (!options) return LB_OK;
+    if (options->indices_capacity > 1) {
+        delete *plan;
+        *plan = nullptr;
+        return fail(LB_LAUNCH_CONTRACT, "indices_capacity", options->indices_capacity);
+    }
+    (*plan)->indices_capacity = options->indices_capacity == 1;
+    return LB_OK;
+}
+
 lb_status lb_rope_append_plan_create(const lb_rope_provider *provider, const lb_paged_spec *spec,
                                      lb_rope_append_plan **out) {
+    return lb_rope_append_plan_create_with(provider, spec, nullptr, out);
+}
+
+lb_status lb_rope_append_plan_create_with(const lb_rope_provider *provider,
+                                          const lb_paged_spec *spec,
+                                          const lb_rope_append_options *options,
+                                          lb_rope_append_plan **out) {
     if (!provider || !spec || !out) return fail(LB_INVALID_ARGUMENT, "provider");
     *out = nullptr;
     lb_paged_spec checked;
     lb_status rc = lb_paged_spec_new(spec->batch_size, spec->max_num_pages, spec->num_query_heads,
                                      spec->num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE, &checked);
     if (rc) return rc;
-    return make_append_plan(provider, checked, false, checked.batch_size, false, out);
+    if ((rc = make_append_plan(provider, checked, false, checked.batch_size, false, out)))
+        return rc;
+    return apply_append_options(options, out);
 }
 
 lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
                                             const lb_append_tokens_spec *spec,
                                             lb_rope_append_plan **out) {
+    return lb_rope_append_tokens_plan_create_with(provider, spec, nullptr, out);
+}
+
+lb_status lb_rope_append_tokens_plan_create_with(const lb_rope_provider *provider,
+                                                 const lb_append_tokens_spec *spec,
+                                                 const lb_rope_append_options *options,
+                                                 lb_rope_append_plan **out) {
     if (!provider || !spec || !out) return fail(LB_INVALID_ARGUMENT, "provider");
     *out = nullptr;
     lb_append_tokens_spec checked;
@@ -473,8 +509,10 @@ lb_status lb_rope_append_tokens_plan_create(const lb_rope_provider *provider,
                                         spec->paged.num_kv_heads, LB_HEAD_DIM, LB_PAGE_SIZE,
                                         &checked);
     if (rc) return rc;
-    return make_append_plan(provider, checked.paged, true, checked.tokens,
-                            checked.max_tokens == 0, out);
+    if ((rc = make_append_plan(provider, checked.paged, true, checked.tokens,
+                               checked.max_tokens == 0, out)))
+        return rc;
+    return apply_append_options(options, out);
 }
 
 void lb_rope_append_plan_destroy(lb_rope_append_plan *plan) { delete plan; }
@@ -574,6 +612,7 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     launch.qh = (int32_t)spec.num_query_heads;
     launch.kvh = (int32_t)spec.num_kv_heads;
     launch.indices_len = (int32_t)op[indices_i].numel;
+    launch.indices_min = plan->indices_capacity ? 0 : launch.indices_len;
     launch.hash_slots = (int32_t)plan->hash_slots;
     launch.grid = plan->grid;
     launch.block = plan->block;

@@ -130,6 +130,7 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     launch.qh = (int32_t)checked.num_query_heads;
     launch.kvh = (int32_t)checked.num_kv_heads;
     launch.indices_len = (int32_t)page_indices_len;
+    launch.indices_min = launch.indices_len;
     launch.heads_per_cta = (int32_t)c.heads_per_cta;
     launch.pages_per_stage = (int32_t)c.pages_per_stage;
     launch.q_tiles = (int32_t)c.q_tiles;
@@ -152,6 +153,7 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     merge.qh = launch.qh;
     merge.partitions = launch.partitions;
     merge.indices_len = launch.indices_len;
+    merge.indices_min = launch.indices_min;
     merge.grid = c.merge_grid;
     merge.block = c.merge_block;
     if ((error = driver().launch(device, [&]() { return launch_split_merge(merge, stream); })))

@@ -7,6 +7,7 @@ Cases follow crates/loom-infer/src/attention/paged_decode/tests.rs, .../paged_ap
 crates/loom-infer-cuda/src/command/resolve.rs:1095-1125 and the preflight parts of
 crates/loom-infer-validation/src/gates/{paged_batch_decode,single_decode,rope}.rs.
 """
+import ctypes
 import gc
 import os
 import re
@@ -591,3 +592,28 @@ def test_state_merge_plan_and_preflight(fake):
     scope = queue.begin(b)
     plan.enqueue_into(scope, lk.StateMergeArgs(states, out.write(), lse.write()))
     assert scope.finish().submitted() == 1
+
+
+def test_indices_capacity_option_is_a_plan_property(fake):
+    """The option only changes the device guard; plan shape and enqueue preflight are the same,
+    and a value other than 0 or 1 is refused at plan time."""
+    spec = lk.Bf16PagedBatchDecodeSpec.new(4, 96, 16, 4)
+    decode, rope = lk.DecodeProvider.load(0), lk.RopeProvider.load(0)
+    plain = decode.plan_bf16_paged_batch(spec, partitions=2)
+    relaxed = decode.plan_bf16_paged_batch(spec, partitions=2, indices_capacity=True)
+    assert (plain.commands(), plain.workspace_required_numel()) == \
+        (relaxed.commands(), relaxed.workspace_required_numel())
+    append_spec = lk.Bf16RopePagedKvAppendSpec.new(4, 96, 16, 4)
+    assert rope.plan_bf16_paged_append(append_spec, indices_capacity=True).commands() == 1
+    tokens_spec = lk.Bf16RopePagedKvAppendTokensSpec.new_extended(100, 4, 96, 16, 4)
+    extended = rope.plan_bf16_paged_append_tokens(tokens_spec, indices_capacity=True)
+    assert (extended.commands(), extended.workspace_required_numel()) == (2, 32 + 200)
+    lib = _abi.load()
+    options = _abi.DecodeOptions(indices_capacity=2)
+    out = ctypes.c_void_p()
+    assert lib.lb_paged_decode_plan_create(decode._ptr, ctypes.byref(spec._raw),
+                                           ctypes.byref(options), ctypes.byref(out)) != 0
+    append_options = _abi.AppendOptions(indices_capacity=7)
+    assert lib.lb_rope_append_plan_create_with(rope._ptr, ctypes.byref(spec._raw),
+                                               ctypes.byref(append_options),
+                                               ctypes.byref(out)) != 0
