@@ -42,10 +42,10 @@ enum {
     LB_UNSUPPORTED_PAGE_SIZE,            /* a=expected b=actual */
     LB_INVALID_HEAD_MAPPING,             /* a=query_heads b=kv_heads */
     LB_INVALID_PARTITION_COUNT,          /* a=partitions b=kv_len (pages for the paged split) */
-    LB_INVALID_INDPTR_START,
-    LB_NON_MONOTONIC_INDPTR,
-    LB_EMPTY_RAGGED_REQUEST,
-    LB_RAGGED_QUERY_LONGER_THAN_KV,
+    LB_INVALID_INDPTR_START,             /* operand=buffer a=actual */
+    LB_NON_MONOTONIC_INDPTR,             /* operand=buffer a=request b=start c=end */
+    LB_EMPTY_RAGGED_REQUEST,             /* operand=buffer a=request */
+    LB_RAGGED_QUERY_LONGER_THAN_KV,      /* a=request b=query_len c=kv_len */
     LB_INVALID_PAGE_INDPTR_START,        /* a=actual */
     LB_NON_MONOTONIC_PAGE_INDPTR,        /* a=request b=start c=end */
     LB_EMPTY_PAGED_REQUEST,              /* a=request */
@@ -489,6 +489,97 @@ lb_status lb_state_merge_plan_create(const lb_decode_provider *provider, size_t 
 void lb_state_merge_plan_destroy(lb_state_merge_plan *plan);
 lb_status lb_state_merge_enqueue(const lb_state_merge_plan *plan, lb_scope *scope,
                                  const lb_state_merge_args *args);
+
+/* ---- paged causal prefill ------------------------------------------------------------------------ */
+
+/* Bf16PagedPrefillSpec, crates/loom-infer/src/attention/paged_prefill/mod.rs:19-159.  Query and
+ * output are BF16 [nnz_qo, query_heads, 128], partitioned into requests by qo_indptr; the pools are
+ * the decode pools [max_num_pages, 16, kv_heads, 128]; LSE is F32 [nnz_qo, query_heads], base 2.
+ * Causal mask, bottom-right aligned: query i of a request sees kv_index <= kv_len - qo_len + i. */
+typedef struct lb_prefill_spec {
+    size_t batch_size, nnz_qo, max_num_pages, num_query_heads, num_kv_heads;
+    float softmax_scale; /* 1/sqrt(128) */
+} lb_prefill_spec;
+
+/* Bf16PagedPrefillSpec::new, paged_prefill/mod.rs:29-91 */
+lb_status lb_prefill_spec_new(size_t batch_size, size_t nnz_qo, size_t max_num_pages,
+                              size_t num_query_heads, size_t num_kv_heads, size_t head_dim,
+                              size_t page_size, lb_prefill_spec *out);
+/* numel accessors, paged_prefill/mod.rs:129-150 */
+size_t lb_prefill_spec_query_numel(const lb_prefill_spec *spec);
+size_t lb_prefill_spec_kv_pages_numel(const lb_prefill_spec *spec);
+size_t lb_prefill_spec_lse_numel(const lb_prefill_spec *spec);
+/* validate_metadata, paged_prefill/mod.rs:161-235 (host copies of the metadata) */
+lb_status lb_prefill_spec_validate_metadata(const lb_prefill_spec *spec, const int32_t *qo_indptr,
+                                            size_t qo_indptr_len, const int32_t *page_indptr,
+                                            size_t page_indptr_len, const int32_t *page_indices,
+                                            size_t page_indices_len,
+                                            const int32_t *last_page_len,
+                                            size_t last_page_len_len);
+/* Bf16PagedPrefillMetadata::causal_kv_end, :321-329.  The metadata must have passed
+ * validate_metadata.  Returns 0 (None) or 1 (Some). */
+int lb_prefill_metadata_causal_kv_end(const lb_prefill_spec *spec, const int32_t *qo_indptr,
+                                      const int32_t *page_indptr, const int32_t *last_page_len,
+                                      size_t request, size_t query_index, size_t *kv_end);
+
+typedef struct lb_prefill_provider lb_prefill_provider;     /* PrefillProvider, prefill.rs:2278-2330 */
+typedef struct lb_paged_prefill_plan lb_paged_prefill_plan; /* Bf16PagedPrefillPlan, :2440-2584 */
+
+/* Bf16PagedPrefillAlgorithm, prefill.rs:2411-2426, for this provider */
+enum {
+    LB_PREFILL_TOKEN_PARALLEL = 0 /* one CTA per (request, KV head, tile of packed query rows):
+                                     warps share the row tiles and the pages; one command */
+};
+
+typedef struct lb_paged_prefill_options {
+    uint32_t q_tiles;          /* 0 = plan-time heuristic; 16-row MMA tiles one CTA owns (1, 2, 4, 8):
+                                  8 / q_tiles warps then take different pages of the same rows */
+    uint32_t indices_capacity; /* as lb_paged_decode_options.indices_capacity */
+    uint32_t reserved[6];
+} lb_paged_prefill_options;
+
+typedef struct lb_paged_prefill_plan_info {
+    int32_t algorithm;
+    uint32_t q_tiles, pages_per_stage, stages;
+    uint32_t rows_per_cta;  /* packed (token, head-in-group) rows per CTA = 16 * q_tiles */
+    uint32_t tiles;         /* upper bound of row tiles per KV head the grid covers */
+    uint32_t grid, block, shared_bytes;
+    uint32_t commands;      /* 1 */
+} lb_paged_prefill_plan_info;
+
+/* Bf16PagedPrefillArgs, prefill.rs:2853-2891 */
+typedef struct lb_paged_prefill_args {
+    lb_handle query, key_pages, value_pages, qo_indptr, page_indptr, page_indices,
+        last_page_len;     /* Read */
+    lb_handle output, lse; /* Write */
+} lb_paged_prefill_args;
+
+/* PrefillProvider::load, prefill.rs:2283-2287 */
+lb_status lb_prefill_provider_load(int device, lb_prefill_provider **out);
+void lb_prefill_provider_destroy(lb_prefill_provider *provider);
+/* As lb_decode_provider_device_status. */
+lb_status lb_prefill_provider_device_status(const lb_prefill_provider *provider, int32_t *status);
+/* PrefillProvider::plan_bf16_paged, prefill.rs:2289-2329; options may be NULL.
+ * StateCountOutOfRange as PagedPrefillPlanError (:2934-2940). */
+lb_status lb_paged_prefill_plan_create(const lb_prefill_provider *provider,
+                                       const lb_prefill_spec *spec,
+                                       const lb_paged_prefill_options *options,
+                                       lb_paged_prefill_plan **out);
+void lb_paged_prefill_plan_destroy(lb_paged_prefill_plan *plan);
+lb_status lb_paged_prefill_plan_info_get(const lb_paged_prefill_plan *plan, lb_prefill_spec *spec,
+                                         lb_paged_prefill_plan_info *info);
+/* Bf16PagedPrefillPlan::enqueue_into, prefill.rs:2456-2583: one command.  Errors as
+ * PagedPrefillEnqueueError (:2942-2963): LengthMismatch (operands "Q", "K_pages", "V_pages",
+ * "qo_indptr", "page_indptr", "last_page_len", "O", "LSE"), PageIndicesTooShort, MisalignedBuffer
+ * (16 bytes here, 4 in the reference), Command errors.  Device-resident metadata is never an
+ * error: a query row whose request fails the kernel's guard keeps its previous output
+ * (prefill.rs:289-347). */
+lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *scope,
+                                   const lb_paged_prefill_args *args);
+/* The plan-time choice as a pure function of the spec and the device. */
+lb_status lb_paged_prefill_choose(const lb_prefill_spec *spec, uint32_t sm_count,
+                                  const lb_paged_prefill_options *options,
+                                  lb_paged_prefill_plan_info *info);
 
 /* ---- fixed-address CUDA Graph ------------------------------------------------------------------ */
 

@@ -96,6 +96,29 @@ class AppendPlanInfo(ctypes.Structure):
                 ("workspace_numel", c_size_t)]
 
 
+class PrefillSpec(ctypes.Structure):
+    _fields_ = [("batch_size", c_size_t), ("nnz_qo", c_size_t), ("max_num_pages", c_size_t),
+                ("num_query_heads", c_size_t), ("num_kv_heads", c_size_t),
+                ("softmax_scale", c_float)]
+
+
+class PrefillOptions(ctypes.Structure):
+    _fields_ = [("q_tiles", c_uint32), ("indices_capacity", c_uint32), ("reserved", c_uint32 * 6)]
+
+
+class PrefillPlanInfo(ctypes.Structure):
+    _fields_ = [("algorithm", c_int32), ("q_tiles", c_uint32), ("pages_per_stage", c_uint32),
+                ("stages", c_uint32), ("rows_per_cta", c_uint32), ("tiles", c_uint32),
+                ("grid", c_uint32), ("block", c_uint32), ("shared_bytes", c_uint32),
+                ("commands", c_uint32)]
+
+
+class PrefillArgs(ctypes.Structure):
+    _fields_ = [(name, Handle) for name in
+                ("query", "key_pages", "value_pages", "qo_indptr", "page_indptr", "page_indices",
+                 "last_page_len", "output", "lse")]
+
+
 RECORD_FN = ctypes.CFUNCTYPE(c_int32, c_void_p, c_void_p)
 
 _I32P = POINTER(c_int32)
@@ -193,6 +216,25 @@ SIGNATURES = {
                                               POINTER(c_void_p)]),
     "lb_rope_pos_ids_plan_destroy": (None, [c_void_p]),
     "lb_rope_pos_ids_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(RopePosIdsArgs)]),
+    "lb_prefill_spec_new": (c_int32, [c_size_t] * 7 + [POINTER(PrefillSpec)]),
+    "lb_prefill_spec_query_numel": (c_size_t, [POINTER(PrefillSpec)]),
+    "lb_prefill_spec_kv_pages_numel": (c_size_t, [POINTER(PrefillSpec)]),
+    "lb_prefill_spec_lse_numel": (c_size_t, [POINTER(PrefillSpec)]),
+    "lb_prefill_spec_validate_metadata": (c_int32, [POINTER(PrefillSpec), _I32P, c_size_t, _I32P,
+                                                    c_size_t, _I32P, c_size_t, _I32P, c_size_t]),
+    "lb_prefill_metadata_causal_kv_end": (c_int, [POINTER(PrefillSpec), _I32P, _I32P, _I32P,
+                                                  c_size_t, c_size_t, POINTER(c_size_t)]),
+    "lb_prefill_provider_load": (c_int32, [c_int, POINTER(c_void_p)]),
+    "lb_prefill_provider_destroy": (None, [c_void_p]),
+    "lb_prefill_provider_device_status": (c_int32, [c_void_p, POINTER(c_int32)]),
+    "lb_paged_prefill_plan_create": (c_int32, [c_void_p, POINTER(PrefillSpec),
+                                               POINTER(PrefillOptions), POINTER(c_void_p)]),
+    "lb_paged_prefill_plan_destroy": (None, [c_void_p]),
+    "lb_paged_prefill_plan_info_get": (c_int32, [c_void_p, POINTER(PrefillSpec),
+                                                 POINTER(PrefillPlanInfo)]),
+    "lb_paged_prefill_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(PrefillArgs)]),
+    "lb_paged_prefill_choose": (c_int32, [POINTER(PrefillSpec), c_uint32, POINTER(PrefillOptions),
+                                          POINTER(PrefillPlanInfo)]),
     "lb_graph_queue_create": (c_int32, [c_int, c_size_t, POINTER(c_void_p)]),
     "lb_graph_queue_destroy": (None, [c_void_p]),
     "lb_graph_queue_bindings": (c_int32, [c_void_p, c_size_t, POINTER(c_void_p)]),

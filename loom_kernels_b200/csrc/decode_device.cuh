@@ -173,9 +173,16 @@ __device__ __forceinline__ void load_query_fragments(const __nv_bfloat16 *q, int
 // their V rows zeroed first (pool rows past a request's length may hold anything, and
 // 0 * garbage must not produce NaN).  Returns true when shared memory was written by this warp
 // (the caller then fences before handing the tile back to the async proxy).
+//
+// kRowLimits (causal prefill): the two rows of a lane see only tokens below limit0 / limit1 of
+// this page (any value; <= 0 masks the whole page for that row).  A row may then meet pages in
+// which it sees nothing before it has seen any token, so its running maximum can still be
+// -inf: the exponent base falls back to 0 and every weight of the row comes out as exactly 0.
+template <bool kRowLimits = false>
 __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int valid_tokens,
                                             const uint32_t (&qf)[8][4], float scale_log2,
-                                            int lane, WarpState &st) {
+                                            int lane, WarpState &st, int limit0 = kPage,
+                                            int limit1 = kPage) {
     const uint32_t k_tile = smem_u32(k_ptr), v_tile = smem_u32(v_ptr);
     const bool partial = valid_tokens < kPage;
     if (partial) {
@@ -220,7 +227,17 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
     float x02 = s0[2] * scale_log2, x03 = s0[3] * scale_log2;
     float x10 = s1[0] * scale_log2, x11 = s1[1] * scale_log2;
     float x12 = s1[2] * scale_log2, x13 = s1[3] * scale_log2;
-    if (partial) {
+    if (kRowLimits) {
+        const int lim0 = min(limit0, valid_tokens), lim1 = min(limit1, valid_tokens);
+        if (t0 >= lim0) x00 = -INFINITY;
+        if (t0 + 1 >= lim0) x01 = -INFINITY;
+        if (t0 + 8 >= lim0) x10 = -INFINITY;
+        if (t0 + 9 >= lim0) x11 = -INFINITY;
+        if (t0 >= lim1) x02 = -INFINITY;
+        if (t0 + 1 >= lim1) x03 = -INFINITY;
+        if (t0 + 8 >= lim1) x12 = -INFINITY;
+        if (t0 + 9 >= lim1) x13 = -INFINITY;
+    } else if (partial) {
         if (t0 >= valid_tokens) { x00 = -INFINITY; x02 = -INFINITY; }
         if (t0 + 1 >= valid_tokens) { x01 = -INFINITY; x03 = -INFINITY; }
         if (t0 + 8 >= valid_tokens) { x10 = -INFINITY; x12 = -INFINITY; }
@@ -232,15 +249,17 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
     m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
-    // token 0 of a page is always valid, so the new maxima are finite
+    // without row limits token 0 of a page is always valid, so the new maxima are finite
     const float new0 = fmaxf(st.row_max[0], m0), new1 = fmaxf(st.row_max[1], m1);
-    const float alpha0 = fast_exp2(st.row_max[0] - new0), alpha1 = fast_exp2(st.row_max[1] - new1);
+    const float base0 = kRowLimits && new0 == -INFINITY ? 0.0f : new0;
+    const float base1 = kRowLimits && new1 == -INFINITY ? 0.0f : new1;
+    const float alpha0 = fast_exp2(st.row_max[0] - base0), alpha1 = fast_exp2(st.row_max[1] - base1);
     st.row_max[0] = new0;
     st.row_max[1] = new1;
-    const float p00 = fast_exp2(x00 - new0), p01 = fast_exp2(x01 - new0);
-    const float p10 = fast_exp2(x10 - new0), p11 = fast_exp2(x11 - new0);
-    const float p02 = fast_exp2(x02 - new1), p03 = fast_exp2(x03 - new1);
-    const float p12 = fast_exp2(x12 - new1), p13 = fast_exp2(x13 - new1);
+    const float p00 = fast_exp2(x00 - base0), p01 = fast_exp2(x01 - base0);
+    const float p10 = fast_exp2(x10 - base0), p11 = fast_exp2(x11 - base0);
+    const float p02 = fast_exp2(x02 - base1), p03 = fast_exp2(x03 - base1);
+    const float p12 = fast_exp2(x12 - base1), p13 = fast_exp2(x13 - base1);
     st.row_sum[0] = st.row_sum[0] * alpha0 + ((p00 + p01) + (p10 + p11));
     st.row_sum[1] = st.row_sum[1] * alpha1 + ((p02 + p03) + (p12 + p13));
     uint32_t pf[4];

@@ -106,6 +106,21 @@ void format_message(lb_error_info &e) {
     case LB_INVALID_PARTITION_COUNT:
         snprintf(m, n, "attention partition count must be in 1..=%lld, got %lld", b, a);
         break;
+    case LB_INVALID_INDPTR_START:
+        snprintf(m, n, "%s must start at zero, got %lld", e.operand, a);
+        break;
+    case LB_NON_MONOTONIC_INDPTR:
+        snprintf(m, n, "%s must be nondecreasing at request %lld, got %lld then %lld", e.operand,
+                 a, b, c);
+        break;
+    case LB_EMPTY_RAGGED_REQUEST:
+        snprintf(m, n, "%s request %lld has zero length", e.operand, a);
+        break;
+    case LB_RAGGED_QUERY_LONGER_THAN_KV:
+        snprintf(m, n,
+                 "ragged prefill request %lld has query length %lld greater than KV length %lld",
+                 a, b, c);
+        break;
     case LB_INVALID_PAGE_INDPTR_START:
         snprintf(m, n, "page indptr must start at zero, got %lld", a);
         break;

@@ -74,6 +74,25 @@ struct RopeLaunch {
     uint32_t grid;
 };
 int launch_rope_pos_ids(const RopeLaunch &launch, void *stream);
+// One paged causal prefill launch.
+struct PrefillLaunch {
+    alignas(64) unsigned char k_map[128]; // CUtensorMap over K pages, box = one page of one KV head
+    alignas(64) unsigned char v_map[128];
+    const void *query;          // bf16 [nnz_qo, qh, 128]
+    const int32_t *qo_indptr;   // [batch + 1]
+    const int32_t *indptr;      // [batch + 1]
+    const int32_t *indices;     // [indices_len]
+    const int32_t *last;        // [batch]
+    void *output;               // bf16 [nnz_qo, qh, 128]
+    float *lse;                 // [nnz_qo, qh]
+    int32_t *status;
+    int32_t batch, nnz_qo, max_pages, qh, kvh, indices_len, indices_min;
+    int32_t q_tiles, pages_per_stage, stages, tiles;
+    float scale_log2;
+    uint32_t grid, block, shared_bytes;
+};
+int configure_prefill_kernels(size_t max_dynamic_shared);
+int launch_paged_prefill(const PrefillLaunch &launch, void *stream);
 int append_block_threads();       // threads per CTA the append kernel is built for
 int append_max_tokens_per_cta();  // tokens one CTA can own (grid floor = tokens / this)
 

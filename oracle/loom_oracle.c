@@ -710,3 +710,196 @@ int lo_rope_append_tokens_ref(const lo_paged_spec *spec, size_t tokens, size_t m
     free(rotated);
     return rc;
 }
+
+/* ---- paged causal prefill --------------------------------------------------------------- */
+
+/* crates/loom-infer/src/attention/paged_prefill/mod.rs:29-91 */
+int lo_prefill_spec_new(size_t batch, size_t nnz_qo, size_t max_pages, size_t qh, size_t kvh,
+                        size_t head_dim, size_t page_size, lo_prefill_spec *spec, lo_error *err) {
+    if (batch == 0 || nnz_qo == 0 || max_pages == 0 || qh == 0 || kvh == 0 || head_dim == 0 ||
+        page_size == 0)
+        return fail(err, LO_ZERO_DIMENSION, NULL, 0, 0, 0, 0);
+    if (head_dim != HEAD_DIM)
+        return fail(err, LO_UNSUPPORTED_HEAD_DIMENSION, NULL, HEAD_DIM, (int64_t)head_dim, 0, 0);
+    if (page_size != PAGE_SIZE)
+        return fail(err, LO_UNSUPPORTED_PAGE_SIZE, NULL, PAGE_SIZE, (int64_t)page_size, 0, 0);
+    if (qh % kvh != 0)
+        return fail(err, LO_INVALID_HEAD_MAPPING, NULL, (int64_t)qh, (int64_t)kvh, 0, 0);
+    if (nnz_qo > (size_t)INT32_MAX) return fail(err, LO_ELEMENT_COUNT_OVERFLOW, NULL, 0, 0, 0, 0);
+    size_t t;
+    if (batch + 1 < batch || mul_overflow(nnz_qo, qh, &t) || mul_overflow(t, head_dim, &t))
+        return fail(err, LO_ELEMENT_COUNT_OVERFLOW, NULL, 0, 0, 0, 0);
+    if (mul_overflow(max_pages, page_size, &t) || mul_overflow(t, kvh, &t) ||
+        mul_overflow(t, head_dim, &t))
+        return fail(err, LO_ELEMENT_COUNT_OVERFLOW, NULL, 0, 0, 0, 0);
+    spec->batch_size = batch;
+    spec->nnz_qo = nnz_qo;
+    spec->max_num_pages = max_pages;
+    spec->num_query_heads = qh;
+    spec->num_kv_heads = kvh;
+    return LO_OK;
+}
+
+/* paged_prefill/mod.rs:238-266 */
+static int validate_query_indptr(const int32_t *indptr, size_t len, size_t expected_total,
+                                 lo_error *err) {
+    if (indptr[0] != 0) return fail(err, LO_INVALID_INDPTR_START, "qo_indptr", indptr[0], 0, 0, 0);
+    for (size_t request = 0; request + 1 < len; ++request) {
+        const int32_t start = indptr[request], end = indptr[request + 1];
+        if (end < start)
+            return fail(err, LO_NON_MONOTONIC_INDPTR, "qo_indptr", (int64_t)request, start, end, 0);
+        if (end == start)
+            return fail(err, LO_EMPTY_RAGGED_REQUEST, "qo_indptr", (int64_t)request, 0, 0, 0);
+    }
+    if (indptr[len - 1] < 0) return fail(err, LO_ELEMENT_COUNT_OVERFLOW, NULL, 0, 0, 0, 0);
+    return require_len(err, "qo_indptr", (size_t)indptr[len - 1], expected_total);
+}
+
+/* paged_prefill/mod.rs:161-235 */
+int lo_prefill_validate_metadata(const lo_prefill_spec *spec, const int32_t *qo_indptr,
+                                 size_t qo_indptr_len, const int32_t *page_indptr,
+                                 size_t page_indptr_len, const int32_t *indices,
+                                 size_t indices_len, const int32_t *last, size_t last_len,
+                                 lo_error *err) {
+    int rc;
+    const size_t batch = spec->batch_size;
+    if ((rc = require_len(err, "qo_indptr", qo_indptr_len, batch + 1))) return rc;
+    if ((rc = require_len(err, "page_indptr", page_indptr_len, batch + 1))) return rc;
+    if ((rc = require_len(err, "last_page_len", last_len, batch))) return rc;
+    if ((rc = validate_query_indptr(qo_indptr, qo_indptr_len, spec->nnz_qo, err))) return rc;
+    if (page_indptr[0] != 0)
+        return fail(err, LO_INVALID_PAGE_INDPTR_START, NULL, page_indptr[0], 0, 0, 0);
+    for (size_t request = 0; request < batch; ++request) {
+        const int32_t start = page_indptr[request], end = page_indptr[request + 1];
+        if (end < start)
+            return fail(err, LO_NON_MONOTONIC_PAGE_INDPTR, NULL, (int64_t)request, start, end, 0);
+        if (end == start) return fail(err, LO_EMPTY_PAGED_REQUEST, NULL, (int64_t)request, 0, 0, 0);
+        const int32_t tail = last[request];
+        if (tail < 1 || tail > (int32_t)PAGE_SIZE)
+            return fail(err, LO_INVALID_LAST_PAGE_LENGTH, NULL, (int64_t)request, tail, PAGE_SIZE,
+                        0);
+        const size_t qo_len = (size_t)(qo_indptr[request + 1] - qo_indptr[request]);
+        const size_t kv_len = (size_t)(end - start - 1) * PAGE_SIZE + (size_t)tail;
+        if (qo_len > kv_len)
+            return fail(err, LO_RAGGED_QUERY_LONGER_THAN_KV, NULL, (int64_t)request,
+                        (int64_t)qo_len, (int64_t)kv_len, 0);
+    }
+    if (page_indptr[batch] < 0) return fail(err, LO_ELEMENT_COUNT_OVERFLOW, NULL, 0, 0, 0, 0);
+    if ((rc = require_len(err, "page_indices", indices_len, (size_t)page_indptr[batch]))) return rc;
+    for (size_t position = 0; position < indices_len; ++position) {
+        const int32_t index = indices[position];
+        if (index < 0 || (size_t)index >= spec->max_num_pages)
+            return fail(err, LO_PAGE_INDEX_OUT_OF_RANGE, NULL, (int64_t)position, index,
+                        (int64_t)spec->max_num_pages, 0);
+    }
+    return LO_OK;
+}
+
+/* paged_prefill/mod.rs:383-443: one (query row, query head); the row sees the logical tokens
+ * [0, kv_len - qo_len + query_index] of its request (bottom-right aligned causal mask). */
+static void paged_prefill_one(const lo_prefill_spec *spec, const uint16_t *q,
+                              const uint16_t *k_pages, const uint16_t *v_pages,
+                              const int32_t *page_indptr, const int32_t *indices, size_t request,
+                              size_t causal_kv_end, size_t query_row, size_t query_head,
+                              uint16_t *out, float *lse) {
+    const size_t qh = spec->num_query_heads, kvh = spec->num_kv_heads;
+    const float scale = 1.0f / sqrtf((float)HEAD_DIM);
+    const size_t query_offset = (query_row * qh + query_head) * HEAD_DIM;
+    const size_t kv_head = query_head / (qh / kvh);
+    float query[HEAD_DIM], state[HEAD_DIM];
+    for (size_t c = 0; c < HEAD_DIM; ++c) query[c] = lo_bf16_to_f32(q[query_offset + c]);
+    memset(state, 0, sizeof(state));
+    float max_score = 0.0f, normalizer = 0.0f;
+    for (size_t token = 0; token < causal_kv_end; ++token) {
+        size_t page, offset;
+        physical_slot(page_indptr, indices, request, token, &page, &offset);
+        const size_t kv_offset = ((page * PAGE_SIZE + offset) * kvh + kv_head) * HEAD_DIM;
+        float dot = 0.0f;
+        for (size_t c = 0; c < HEAD_DIM; ++c)
+            dot = fmaf(query[c], lo_bf16_to_f32(k_pages[kv_offset + c]), dot);
+        const float score = dot * scale;
+        if (token == 0) {
+            max_score = score;
+            normalizer = 1.0f;
+            for (size_t c = 0; c < HEAD_DIM; ++c) state[c] = lo_bf16_to_f32(v_pages[kv_offset + c]);
+            continue;
+        }
+        const float next_max = fmaxf(max_score, score);
+        const float previous_weight = expf(max_score - next_max);
+        const float current_weight = expf(score - next_max);
+        normalizer = normalizer * previous_weight + current_weight;
+        for (size_t c = 0; c < HEAD_DIM; ++c)
+            state[c] = state[c] * previous_weight +
+                       lo_bf16_to_f32(v_pages[kv_offset + c]) * current_weight;
+        max_score = next_max;
+    }
+    for (size_t c = 0; c < HEAD_DIM; ++c)
+        out[query_offset + c] = lo_bf16_from_f32(state[c] / normalizer);
+    lse[query_row * qh + query_head] = (max_score + logf(normalizer)) * LOG2_E_F32;
+}
+
+struct prefill_job {
+    const lo_prefill_spec *spec;
+    const uint16_t *q, *k_pages, *v_pages;
+    const int32_t *qo_indptr, *page_indptr, *indices, *last;
+    uint16_t *out;
+    float *lse;
+    size_t rows;
+    size_t next; /* query rows, claimed with an atomic fetch-add */
+};
+
+static void *prefill_worker(void *arg) {
+    struct prefill_job *job = (struct prefill_job *)arg;
+    const size_t batch = job->spec->batch_size;
+    for (;;) {
+        const size_t row = __atomic_fetch_add(&job->next, 1, __ATOMIC_RELAXED);
+        if (row >= job->rows) break;
+        size_t request = 0;
+        while (request + 1 < batch && (size_t)job->qo_indptr[request + 1] <= row) ++request;
+        const size_t qo_start = (size_t)job->qo_indptr[request];
+        const size_t qo_len = (size_t)job->qo_indptr[request + 1] - qo_start;
+        const size_t kv_len = request_kv_len(job->page_indptr, job->last, request);
+        const size_t causal_kv_end = kv_len - qo_len + (row - qo_start) + 1; /* mod.rs:321-329 */
+        for (size_t head = 0; head < job->spec->num_query_heads; ++head)
+            paged_prefill_one(job->spec, job->q, job->k_pages, job->v_pages, job->page_indptr,
+                              job->indices, request, causal_kv_end, row, head, job->out, job->lse);
+    }
+    return NULL;
+}
+
+/* paged_prefill/mod.rs:361-446.  threads > 1 distributes query rows over POSIX threads; every
+ * (row, head) keeps the reference's arithmetic order, so results are identical. */
+int lo_paged_prefill_ref(const lo_prefill_spec *spec, const uint16_t *q, size_t q_len,
+                         const uint16_t *k_pages, size_t k_len, const uint16_t *v_pages,
+                         size_t v_len, const int32_t *qo_indptr, size_t qo_indptr_len,
+                         const int32_t *page_indptr, size_t page_indptr_len,
+                         const int32_t *indices, size_t indices_len, const int32_t *last,
+                         size_t last_len, uint16_t *out, size_t out_len, float *lse,
+                         size_t lse_len, int threads, lo_error *err) {
+    int rc;
+    const size_t q_numel = spec->nnz_qo * spec->num_query_heads * HEAD_DIM;
+    const size_t kv_numel = spec->max_num_pages * PAGE_SIZE * spec->num_kv_heads * HEAD_DIM;
+    if ((rc = require_len(err, "Q", q_len, q_numel))) return rc;
+    if ((rc = require_len(err, "K_pages", k_len, kv_numel))) return rc;
+    if ((rc = require_len(err, "V_pages", v_len, kv_numel))) return rc;
+    if ((rc = require_len(err, "O", out_len, q_numel))) return rc;
+    if ((rc = require_len(err, "LSE", lse_len, spec->nnz_qo * spec->num_query_heads))) return rc;
+    if ((rc = lo_prefill_validate_metadata(spec, qo_indptr, qo_indptr_len, page_indptr,
+                                           page_indptr_len, indices, indices_len, last, last_len,
+                                           err)))
+        return rc;
+    struct prefill_job job = {spec, q, k_pages, v_pages, qo_indptr, page_indptr, indices, last,
+                              out, lse, spec->nnz_qo, 0};
+    if (threads <= 1) {
+        prefill_worker(&job);
+        return LO_OK;
+    }
+    if (threads > 256) threads = 256;
+    pthread_t workers[256];
+    int started = 0;
+    for (int t = 0; t < threads - 1; ++t)
+        if (pthread_create(&workers[started], NULL, prefill_worker, &job) == 0) ++started;
+    prefill_worker(&job);
+    for (int t = 0; t < started; ++t) pthread_join(workers[t], NULL);
+    return LO_OK;
+}

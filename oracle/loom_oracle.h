@@ -134,6 +134,26 @@ int lo_rope_append_tokens_ref(const lo_paged_spec *spec, size_t tokens, size_t m
                               uint16_t *k_pages, size_t k_pages_len, uint16_t *v_pages,
                               size_t v_pages_len, lo_error *err);
 
+/* Paged causal prefill, crates/loom-infer/src/attention/paged_prefill/mod.rs:19-27. */
+typedef struct lo_prefill_spec {
+    size_t batch_size, nnz_qo, max_num_pages, num_query_heads, num_kv_heads;
+} lo_prefill_spec;
+
+int lo_prefill_spec_new(size_t batch, size_t nnz_qo, size_t max_pages, size_t qh, size_t kvh,
+                        size_t head_dim, size_t page_size, lo_prefill_spec *spec, lo_error *err);
+int lo_prefill_validate_metadata(const lo_prefill_spec *spec, const int32_t *qo_indptr,
+                                 size_t qo_indptr_len, const int32_t *page_indptr,
+                                 size_t page_indptr_len, const int32_t *indices,
+                                 size_t indices_len, const int32_t *last, size_t last_len,
+                                 lo_error *err);
+int lo_paged_prefill_ref(const lo_prefill_spec *spec, const uint16_t *q, size_t q_len,
+                         const uint16_t *k_pages, size_t k_len, const uint16_t *v_pages,
+                         size_t v_len, const int32_t *qo_indptr, size_t qo_indptr_len,
+                         const int32_t *page_indptr, size_t page_indptr_len,
+                         const int32_t *indices, size_t indices_len, const int32_t *last,
+                         size_t last_len, uint16_t *out, size_t out_len, float *lse,
+                         size_t lse_len, int threads, lo_error *err);
+
 #ifdef __cplusplus
 }
 #endif

@@ -342,3 +342,50 @@ def rope_append_tokens(spec, tokens, q, k, v, batch_indices, positions, indptr, 
                                            vpg.ctypes.data_as(POINTER(c_uint16)),
                                            c_size_t(vpg.size), ctypes.byref(err)), err)
     return q_out, kpg, vpg
+
+
+# ---- paged causal prefill --------------------------------------------------------------------
+
+class _PrefillSpec(ctypes.Structure):
+    _fields_ = [("batch_size", c_size_t), ("nnz_qo", c_size_t), ("max_num_pages", c_size_t),
+                ("num_query_heads", c_size_t), ("num_kv_heads", c_size_t)]
+
+
+def prefill_spec(batch, nnz_qo, max_pages, qh, kvh, head_dim=HEAD_DIM,
+                 page_size=PAGE_SIZE) -> _PrefillSpec:
+    """Bf16PagedPrefillSpec::new (paged_prefill/mod.rs:29-91)."""
+    spec, err = _PrefillSpec(), _Error()
+    _check(lib().lo_prefill_spec_new(c_size_t(batch), c_size_t(nnz_qo), c_size_t(max_pages),
+                                     c_size_t(qh), c_size_t(kvh), c_size_t(head_dim),
+                                     c_size_t(page_size), ctypes.byref(spec), ctypes.byref(err)),
+           err)
+    return spec
+
+
+def prefill_validate_metadata(spec, qo_indptr, page_indptr, indices, last):
+    err = _Error()
+    _, qp, ql = _i32(qo_indptr)
+    _, ip, il = _i32(page_indptr)
+    _, xp, xl = _i32(indices)
+    _, lp, ll = _i32(last)
+    _check(lib().lo_prefill_validate_metadata(ctypes.byref(spec), qp, ql, ip, il, xp, xl, lp, ll,
+                                              ctypes.byref(err)), err)
+
+
+def paged_prefill(spec, q, k_pages, v_pages, qo_indptr, page_indptr, indices, last, threads=1):
+    """paged_prefill_bf16_reference; returns (O bf16 bits, LSE f32 in the log2 domain)."""
+    err = _Error()
+    q, qp, ql = _u16(q)
+    k, kp, kl = _u16(k_pages)
+    v, vp, vl = _u16(v_pages)
+    _, op, ol = _i32(qo_indptr)
+    _, ip, il = _i32(page_indptr)
+    _, xp, xl = _i32(indices)
+    _, lp, ll = _i32(last)
+    out = np.full(spec.nnz_qo * spec.num_query_heads * HEAD_DIM, 0x7FC0, dtype=np.uint16)
+    lse = np.full(spec.nnz_qo * spec.num_query_heads, np.nan, dtype=np.float32)
+    _check(lib().lo_paged_prefill_ref(ctypes.byref(spec), qp, ql, kp, kl, vp, vl, op, ol, ip, il,
+                                      xp, xl, lp, ll, out.ctypes.data_as(POINTER(c_uint16)),
+                                      c_size_t(out.size), lse.ctypes.data_as(POINTER(c_float)),
+                                      c_size_t(lse.size), c_int(threads), ctypes.byref(err)), err)
+    return out, lse

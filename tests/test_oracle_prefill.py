@@ -1,0 +1,197 @@
+"""Pins the CPU oracle's paged causal prefill.
+
+The reference publishes no CPU-side digest for this operator (the digests in its prefill reports
+are of the device output, which differs from its CPU reference in a few elements), so the
+restatement is pinned by
+  - the known-answer cases of the reference's own unit tests
+    (crates/loom-infer/src/attention/paged_prefill/tests.rs:27-127),
+  - its metadata and spec error cases (tests.rs:129-267),
+  - the fixture digests its prefill reports publish for the page-reordered GQA4 case
+    (docs/results/h20-flashinfer-v0.6.16.post1-paged-prefill-graph-performance-20260807.json),
+  - bit-equality with the digest-pinned paged decode oracle where the two operators coincide
+    (one query token per request sees its whole KV), and
+  - an independent numpy evaluation of the same arithmetic.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_digests.json")))
+K_SALT, V_SALT = 0x4B455900, 0x56414C554500
+
+
+def hx(value):
+    return f"{value:016x}"
+
+
+def test_bottom_right_mask_over_physical_pages(oracle):
+    """tests.rs:27-68: two queries over four tokens in physical page 1; zero Q and K."""
+    spec = oracle.prefill_spec(1, 2, 2, 1, 1)
+    q = np.zeros(2 * 128, np.uint16)
+    k = np.zeros(2 * 16 * 128, np.uint16)
+    v = np.zeros(2 * 16 * 128, np.uint16)
+    for token, value in enumerate([1.0, 2.0, 3.0, 100.0]):
+        v[(16 + token) * 128:(16 + token + 1) * 128] = oracle.bf16_from_f32([value])[0]
+    out, lse = oracle.paged_prefill(spec, q, k, v, [0, 2], [0, 1], [1], [4])
+    assert np.all(out[:128] == oracle.bf16_from_f32([2.0])[0])
+    assert np.all(out[128:] == oracle.bf16_from_f32([26.5])[0])
+    assert np.array_equal(lse, np.log2(np.float32([3.0, 4.0])))
+
+
+def test_gqa_heads_and_reused_pages(oracle):
+    """tests.rs:70-127."""
+    spec = oracle.prefill_spec(2, 2, 2, 4, 2)
+    q = np.zeros(2 * 4 * 128, np.uint16)
+    k = np.zeros(2 * 16 * 2 * 128, np.uint16)
+    v = np.zeros(2 * 16 * 2 * 128, np.uint16)
+    for page in range(2):
+        for kv_head in range(2):
+            value = page + 1.0 if kv_head == 0 else -(page + 1.0)
+            start = (page * 16 * 2 + kv_head) * 128
+            v[start:start + 128] = oracle.bf16_from_f32([value])[0]
+    out, lse = oracle.paged_prefill(spec, q, k, v, [0, 1, 2], [0, 1, 2], [1, 0], [1, 1])
+    for request in range(2):
+        positive = oracle.bf16_from_f32([2.0 if request == 0 else 1.0])[0]
+        negative = positive | 0x8000
+        base = request * 4 * 128
+        assert np.all(out[base:base + 256] == positive)
+        assert np.all(out[base + 256:base + 512] == negative)
+    assert np.array_equal(lse, np.zeros(8, np.float32))
+
+
+def test_metadata_errors(oracle):
+    """tests.rs:129-201, same order."""
+    spec = oracle.prefill_spec(2, 3, 4, 4, 2)
+    cases = [
+        (([0, 3], [0, 1, 2], [0, 1], [16, 16]), "LengthMismatch", "qo_indptr", (3, 2)),
+        (([1, 2, 4], [0, 1, 2], [0, 1], [16, 16]), "InvalidIndptrStart", "qo_indptr", (1,)),
+        (([0, 2, 1], [0, 1, 2], [0, 1], [16, 16]), "NonMonotonicIndptr", "qo_indptr", (1, 2, 1)),
+        (([0, 2, 3], [1, 2, 3], [0, 1, 2], [16, 16]), "InvalidPageIndptrStart", "", (1,)),
+        (([0, 2, 3], [0, 2, 1], [0], [16, 16]), "NonMonotonicPageIndptr", "", (1, 2, 1)),
+        (([0, 2, 3], [0, 0, 1], [0], [16, 16]), "EmptyPagedRequest", "", (0,)),
+        (([0, 2, 3], [0, 1, 2], [0, 1], [16, 0]), "InvalidLastPageLength", "", (1, 0, 16)),
+        (([0, 2, 3], [0, 1, 2], [0, 4], [16, 16]), "PageIndexOutOfRange", "", (1, 4, 4)),
+        (([0, 2, 3], [0, 1, 2], [0, 1], [1, 16]), "RaggedQueryLongerThanKv", "", (0, 2, 1)),
+    ]
+    for args, variant, buffer, payload in cases:
+        with pytest.raises(oracle.OracleError) as e:
+            oracle.prefill_validate_metadata(spec, *args)
+        assert (e.value.variant, e.value.buffer, e.value.payload[:len(payload)]) == \
+            (variant, buffer, payload)
+    # an empty query range and a wrong total (mod.rs:253-265)
+    with pytest.raises(oracle.OracleError) as e:
+        oracle.prefill_validate_metadata(spec, [0, 0, 3], [0, 1, 2], [0, 1], [16, 16])
+    assert (e.value.variant, e.value.payload[0]) == ("EmptyRaggedRequest", 0)
+    with pytest.raises(oracle.OracleError) as e:
+        oracle.prefill_validate_metadata(spec, [0, 1, 2], [0, 1, 2], [0, 1], [16, 16])
+    assert (e.value.variant, e.value.buffer, e.value.payload[:2]) == \
+        ("LengthMismatch", "qo_indptr", (3, 2))
+
+
+def test_spec_errors(oracle):
+    """tests.rs:203-243."""
+    for shape in [(0, 1, 1, 1, 1, 128, 16), (1, 0, 1, 1, 1, 128, 16), (1, 1, 0, 1, 1, 128, 16),
+                  (1, 1, 1, 0, 1, 128, 16), (1, 1, 1, 1, 0, 128, 16), (1, 1, 1, 1, 1, 0, 16),
+                  (1, 1, 1, 1, 1, 128, 0)]:
+        with pytest.raises(oracle.OracleError) as e:
+            oracle.prefill_spec(*shape)
+        assert e.value.variant == "ZeroDimension"
+    for shape, variant, payload in [((1, 1, 1, 1, 1, 64, 16), "UnsupportedHeadDimension", (128, 64)),
+                                    ((1, 1, 1, 1, 1, 128, 8), "UnsupportedPageSize", (16, 8)),
+                                    ((1, 1, 1, 6, 4, 128, 16), "InvalidHeadMapping", (6, 4))]:
+        with pytest.raises(oracle.OracleError) as e:
+            oracle.prefill_spec(*shape)
+        assert (e.value.variant, e.value.payload[:2]) == (variant, payload)
+    for shape in [(1, 2 ** 31, 1, 1, 1, 128, 16), (1, 1, 2 ** 64 - 1, 1, 1, 128, 16)]:
+        with pytest.raises(oracle.OracleError) as e:
+            oracle.prefill_spec(*shape)
+        assert e.value.variant == "ElementCountOverflow"
+    spec = oracle.prefill_spec(1, 1, 1, 1, 1)
+    z = np.zeros(16 * 128, np.uint16)
+    with pytest.raises(oracle.OracleError) as e:
+        oracle.paged_prefill(spec, z[:127], z, z, [0, 1], [0, 1], [0], [1])
+    assert (e.value.variant, e.value.buffer, e.value.payload[:2]) == \
+        ("LengthMismatch", "Q", (128, 127))
+
+
+def test_published_fixture_digests_of_the_reordered_gqa4_case(oracle):
+    """The gate's gqa4_reordered_reuse inputs (gates/paged_prefill.rs:561-573) hash to the
+    fixture digests of the reference's Graph performance report."""
+    g = GOLDEN["paged_prefill"]["gqa4_reordered_reuse"]
+    batch, nnz, pages, qh, kvh = g["spec"]
+    salt = int(g["salt"], 16)
+    assert hx(oracle.digest_bf16(oracle.fixture_bf16(nnz * qh * 128, salt))) == g["query"]
+    assert hx(oracle.digest_bf16(oracle.fixture_bf16(pages * 16 * kvh * 128, salt ^ K_SALT))) == \
+        g["key_pages"]
+    assert hx(oracle.digest_bf16(oracle.fixture_bf16(pages * 16 * kvh * 128, salt ^ V_SALT))) == \
+        g["value_pages"]
+    for name in ("qo_indptr", "page_indptr", "page_indices", "last_page_len"):
+        assert hx(oracle.digest_i32(g[name + "_values"])) == g[name], name
+
+
+def test_one_query_token_per_request_is_the_pinned_paged_decode(oracle):
+    """With qo_len == 1 the causal limit is the whole KV, so prefill must reproduce, bit for bit,
+    the paged decode reference on the decode gate cases (whose output digests are published)."""
+    for name, case in GOLDEN["paged_decode"]["cases"].items():
+        batch, pages, qh, kvh = case["spec"]
+        salt = int(case["salt"], 16)
+        q = oracle.fixture_bf16(batch * qh * 128, salt)
+        k = oracle.fixture_bf16(pages * 16 * kvh * 128, salt ^ K_SALT)
+        v = oracle.fixture_bf16(pages * 16 * kvh * 128, salt ^ V_SALT)
+        spec = oracle.prefill_spec(batch, batch, pages, qh, kvh)
+        out, lse = oracle.paged_prefill(spec, q, k, v, np.arange(batch + 1), case["indptr"],
+                                        case["indices"], case["last"])
+        assert hx(oracle.digest_bf16(out)) == case["output"], name
+        d_out, d_lse = oracle.paged_decode(oracle.paged_spec(batch, pages, qh, kvh), q, k, v,
+                                           case["indptr"], case["indices"], case["last"])
+        assert np.array_equal(out, d_out) and np.array_equal(lse.view(np.uint32),
+                                                             d_lse.view(np.uint32)), name
+
+
+def numpy_prefill(oracle, qh, kvh, q, k, v, qo_indptr, indptr, indices, last):
+    """Independent two-pass softmax in float64 over the gathered rows."""
+    group = qh // kvh
+    qf = oracle.bf16_to_f32(q).reshape(-1, qh, 128).astype(np.float64)
+    kf = oracle.bf16_to_f32(k).reshape(-1, 16, kvh, 128).astype(np.float64)
+    vf = oracle.bf16_to_f32(v).reshape(-1, 16, kvh, 128).astype(np.float64)
+    out = np.zeros_like(qf)
+    lse = np.zeros(qf.shape[:2])
+    for r in range(len(last)):
+        pages = indices[indptr[r]:indptr[r + 1]]
+        kv_len = (len(pages) - 1) * 16 + last[r]
+        keys = kf[pages].reshape(-1, kvh, 128)[:kv_len]
+        values = vf[pages].reshape(-1, kvh, 128)[:kv_len]
+        qo_len = qo_indptr[r + 1] - qo_indptr[r]
+        for i in range(qo_len):
+            end = kv_len - qo_len + i + 1
+            row = qo_indptr[r] + i
+            for h in range(qh):
+                s = keys[:end, h // group] @ qf[row, h] * (1.0 / np.sqrt(128.0))
+                m = s.max()
+                p = np.exp(s - m)
+                out[row, h] = p @ values[:end, h // group] / p.sum()
+                lse[row, h] = (m + np.log(p.sum())) * np.log2(np.e)
+    return out.reshape(-1), lse.reshape(-1)
+
+
+def test_ragged_case_against_numpy(oracle):
+    rng = np.random.default_rng(17)
+    qh, kvh, pool = 8, 2, 24
+    qo_lens, kv_lens = [5, 1, 19], [37, 16, 19]
+    qo_indptr = np.concatenate([[0], np.cumsum(qo_lens)]).astype(np.int32)
+    pages = [(n + 15) // 16 for n in kv_lens]
+    indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
+    indices = rng.permutation(pool)[:sum(pages)].astype(np.int32)
+    last = np.array([(n - 1) % 16 + 1 for n in kv_lens], np.int32)
+    q = oracle.bf16_from_f32(rng.standard_normal(sum(qo_lens) * qh * 128).astype(np.float32))
+    k = oracle.bf16_from_f32(rng.standard_normal(pool * 16 * kvh * 128).astype(np.float32))
+    v = oracle.bf16_from_f32(rng.standard_normal(pool * 16 * kvh * 128).astype(np.float32))
+    spec = oracle.prefill_spec(3, sum(qo_lens), pool, qh, kvh)
+    out, lse = oracle.paged_prefill(spec, q, k, v, qo_indptr, indptr, indices, last)
+    out_mt, lse_mt = oracle.paged_prefill(spec, q, k, v, qo_indptr, indptr, indices, last, threads=4)
+    assert np.array_equal(out, out_mt) and np.array_equal(lse.view(np.uint32), lse_mt.view(np.uint32))
+    e_out, e_lse = numpy_prefill(oracle, qh, kvh, q, k, v, qo_indptr, indptr, indices, last)
+    assert np.abs(oracle.bf16_to_f32(out) - e_out).max() <= 2.0 ** -7  # half a BF16 ulp at |O| < 2
+    assert np.abs(lse - e_lse).max() <= 1e-5
