@@ -527,15 +527,21 @@ typedef struct lb_paged_prefill_plan lb_paged_prefill_plan; /* Bf16PagedPrefillP
 
 /* Bf16PagedPrefillAlgorithm, prefill.rs:2411-2426, for this provider */
 enum {
-    LB_PREFILL_TOKEN_PARALLEL = 0 /* one CTA per (request, KV head, tile of packed query rows):
-                                     warps share the row tiles and the pages; one command */
+    LB_PREFILL_TOKEN_PARALLEL = 0, /* one CTA per (request, KV head, tile of packed query rows):
+                                      warps share the row tiles and the pages (mma.sync); the
+                                      choice for short, latency-bound calls; one command */
+    LB_PREFILL_TILED = 1           /* one CTA per (request, KV head, 128 packed query rows) on the
+                                      tcgen05 tensor cores with the accumulators in TMEM; the
+                                      choice for long prompts; one command */
 };
 
 typedef struct lb_paged_prefill_options {
-    uint32_t q_tiles;          /* 0 = plan-time heuristic; 16-row MMA tiles one CTA owns (1, 2, 4, 8):
-                                  8 / q_tiles warps then take different pages of the same rows */
+    uint32_t q_tiles;          /* token-parallel only.  0 = plan-time heuristic; 16-row MMA tiles
+                                  one CTA owns (1, 2, 4, 8): 8 / q_tiles warps then take different
+                                  pages of the same rows */
     uint32_t indices_capacity; /* as lb_paged_decode_options.indices_capacity */
-    uint32_t reserved[6];
+    uint32_t algorithm;        /* 0 = plan-time heuristic, 1 = token-parallel, 2 = tiled */
+    uint32_t reserved[5];
 } lb_paged_prefill_options;
 
 typedef struct lb_paged_prefill_plan_info {

@@ -103,7 +103,8 @@ class PrefillSpec(ctypes.Structure):
 
 
 class PrefillOptions(ctypes.Structure):
-    _fields_ = [("q_tiles", c_uint32), ("indices_capacity", c_uint32), ("reserved", c_uint32 * 6)]
+    _fields_ = [("q_tiles", c_uint32), ("indices_capacity", c_uint32), ("algorithm", c_uint32),
+                ("reserved", c_uint32 * 5)]
 
 
 class PrefillPlanInfo(ctypes.Structure):

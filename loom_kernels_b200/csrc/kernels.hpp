@@ -93,6 +93,11 @@ struct PrefillLaunch {
 };
 int configure_prefill_kernels(size_t max_dynamic_shared);
 int launch_paged_prefill(const PrefillLaunch &launch, void *stream);
+// The tcgen05 kernel: 128-row tiles; launch.k_map must have the box {64 dims, 16 tokens, 1 half}
+// (the K rows of a block form one uniform operand), launch.v_map the box {64, 16, 2}.
+int configure_prefill_tiled_kernel(size_t max_dynamic_shared);
+int prefill_tiled_shared_bytes();
+int launch_paged_prefill_tiled(const PrefillLaunch &launch, void *stream);
 int append_block_threads();       // threads per CTA the append kernel is built for
 int append_max_tokens_per_cta();  // tokens one CTA can own (grid floor = tokens / this)
 

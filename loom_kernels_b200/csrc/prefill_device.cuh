@@ -1,0 +1,63 @@
+// Shared by the paged-prefill kernels: the launch arguments and the mapping from a row tile to
+// the request that owns it.
+#pragma once
+
+#include "decode_device.cuh"
+
+namespace lb {
+namespace dev {
+
+struct PrefillArgs {
+    const __nv_bfloat16 *query;
+    const int32_t *qo_indptr, *indptr, *indices, *last;
+    __nv_bfloat16 *output;
+    float *lse;
+    int32_t *status;
+    int32_t batch, nnz_qo, max_pages, qh, kvh, indices_len, indices_min;
+    int32_t mt, pps, stages, tiles;
+    float scale_log2;
+};
+
+// The request that owns row tile `tile` (tiles are numbered request by request; a request of
+// qo_len tokens has ceil(qo_len * group / rows) of them) and the tile's index inside it; false
+// when the tile is past the last one or a request up to and including the owner has an invalid
+// query range (crates/loom-infer-cuda/src/attention/prefill.rs:303-317).  Every lane of the
+// calling warp returns the same.
+__device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int rows, int tile,
+                                            int lane, int &request, int &tile_in_request) {
+    long long before = 0;
+    for (int r0 = 0; r0 < a.batch; r0 += 32) {
+        const int r = r0 + lane;
+        int start = 0, end = 0;
+        if (r < a.batch) {
+            start = a.qo_indptr[r];
+            end = a.qo_indptr[r + 1];
+        }
+        const bool valid = r >= a.batch || (start >= 0 && end > start && end <= a.nnz_qo);
+        const long long mine =
+            r < a.batch && valid ? ((long long)(end - start) * group + rows - 1) / rows : 0;
+        long long inclusive = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const long long up = __shfl_up_sync(0xffffffffu, inclusive, d);
+            if (lane >= d) inclusive += up;
+        }
+        const long long first = before + inclusive - mine;
+        const unsigned bad = __ballot_sync(0xffffffffu, !valid);
+        const unsigned hit =
+            __ballot_sync(0xffffffffu, mine > 0 && tile >= first && tile < first + mine);
+        if (hit) {
+            const int source = __ffs(hit) - 1;
+            if (bad && __ffs(bad) - 1 < source) return false;
+            request = r0 + source;
+            tile_in_request = tile - (int)__shfl_sync(0xffffffffu, first, source);
+            return true;
+        }
+        if (bad) return false;
+        before += __shfl_sync(0xffffffffu, inclusive, 31);
+    }
+    return false;
+}
+
+} // namespace dev
+} // namespace lb

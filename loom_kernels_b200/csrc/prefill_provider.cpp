@@ -95,6 +95,36 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         return fail(LB_LAUNCH_CONTRACT, "q_tiles", q_tiles);
     if (options && options->indices_capacity > 1)
         return fail(LB_LAUNCH_CONTRACT, "indices_capacity", options->indices_capacity);
+    const uint32_t algorithm_option = options ? options->algorithm : 0;
+    if (algorithm_option > 2) return fail(LB_LAUNCH_CONTRACT, "algorithm", algorithm_option);
+    // Tiled (tcgen05, 128-row tiles) when whole tiles fill the device at least once and the
+    // average request can hold a few blocks of KV: then the operator is bound by the tensor pipe.
+    // Short calls are latency-bound and take the token-parallel kernel.
+    const size_t full_tiles = (packed_rows / 128) * spec.num_kv_heads;
+    const size_t average_kv = spec.max_num_pages * LB_PAGE_SIZE / spec.batch_size;
+    const bool tiled = algorithm_option == 2 ||
+                       (algorithm_option == 0 && q_tiles == 0 && full_tiles >= sms &&
+                        average_kv >= 512);
+    if (tiled) {
+        const uint32_t shared = (uint32_t)prefill_tiled_shared_bytes();
+        if (shared > smem) return fail(LB_LAUNCH_CONTRACT, "shared_memory", shared);
+        const size_t tiles = packed_rows / 128 + spec.batch_size;
+        size_t grid;
+        if (mul_overflow(tiles, spec.num_kv_heads, &grid) || grid > 0x7fffffffu)
+            return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)states);
+        memset(out, 0, sizeof(*out));
+        out->algorithm = LB_PREFILL_TILED;
+        out->q_tiles = 8;
+        out->pages_per_stage = 8;
+        out->stages = 2;
+        out->rows_per_cta = 128;
+        out->tiles = (uint32_t)tiles;
+        out->grid = (uint32_t)grid;
+        out->block = 192;
+        out->shared_bytes = shared;
+        out->commands = 1;
+        return LB_OK;
+    }
     if (q_tiles == 0) {
         // the largest tile that still gives every SM two CTAs; short calls take the smallest
         q_tiles = 1;
@@ -252,6 +282,7 @@ lb_status lb_prefill_provider_load(int device, lb_prefill_provider **out) {
     const int error = driver().configure(device, [&]() -> int {
         int e = configure_prefill_kernels(smem);
         if (e) return e;
+        if ((e = configure_prefill_tiled_kernel(smem))) return e;
         if ((e = cudaMalloc((void **)&status, 64))) return e;
         return cudaMemset(status, 0, 64);
     });
@@ -383,8 +414,12 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
                               (uint64_t)spec.num_kv_heads * 2};
     const uint64_t strides[2] = {(uint64_t)spec.num_kv_heads * LB_HEAD_DIM * 2, 128};
     const uint32_t box[3] = {64, 16, 2};
+    // the tiled kernel loads K by 64-dim halves, so that the 128 token rows of a block lie 128
+    // bytes apart in shared memory and form one MMA operand
+    const bool tiled = c.algorithm == LB_PREFILL_TILED;
+    const uint32_t k_box[3] = {64, 16, tiled ? 1u : 2u};
     int error = driver().encode_tensor_map_3d(plan->device, launch.k_map, op[1].ptr, dims, strides,
-                                              box);
+                                              k_box);
     if (!error)
         error = driver().encode_tensor_map_3d(plan->device, launch.v_map, op[2].ptr, dims, strides,
                                               box);
@@ -413,7 +448,10 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
     launch.block = c.block;
     launch.shared_bytes = c.shared_bytes;
     void *stream = scope->queue->stream;
-    return submit_launch(*scope, [&]() { return launch_paged_prefill(launch, stream); });
+    return submit_launch(*scope, [&]() {
+        return tiled ? launch_paged_prefill_tiled(launch, stream)
+                     : launch_paged_prefill(launch, stream);
+    });
 }
 
 }

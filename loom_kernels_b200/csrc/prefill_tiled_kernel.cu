@@ -1,0 +1,520 @@
+// Paged causal prefill on the 5th-generation tensor cores (tcgen05 + TMEM), for prompts long
+// enough that the operator is bound by the tensor pipe rather than by latency.
+//
+// Same contract as paged_prefill_kernel (prefill_kernels.cu); replaces the same reference kernels
+// (crates/loom-infer-cuda/src/attention/prefill.rs:270-470,799-1170).
+//
+// Shape of the kernel
+//   work item  = (request, KV head, tile of 128 packed (token, head-in-group) rows); one CTA each,
+//                192 threads: warps 0-3 own one row per thread (row t = TMEM lane t), warp 4 issues
+//                the TMA loads, warp 5 allocates TMEM and issues the MMAs.
+//   per block  = 128 KV tokens (8 pages):
+//                  S = Q K^T      8 x tcgen05.mma 128x128x16 (A = Q, B = K block, both K-major in
+//                                 shared memory with the 128-byte swizzle), accumulator S in TMEM
+//                  softmax        each thread pulls its S row out of TMEM (tcgen05.ld), masks it
+//                                 with the row's causal limit, and writes P = 2^(S - m) as BF16
+//                                 into shared memory in the A-operand layout; the exponent base m
+//                                 follows the running maximum lazily (only a rise of more than 8
+//                                 rescales O and the normaliser, through tcgen05.ld/st)
+//                  O += P V       one tcgen05.mma 128x128x16 per page (A = P, B = the V page, which
+//                                 is MN-major: 64 dims contiguous per 128-byte row), O in TMEM
+//   pipelining = K and V blocks are double-buffered by TMA; the S MMAs of block j + 1 are issued
+//                before the P V MMAs of block j, so the tensor pipe computes the next scores while
+//                the softmax warps work; P is double-buffered.
+//   shared mem = Q 32 KB | K 2 x 32 KB | V 2 x 32 KB | P 2 x 32 KB | barriers  (about 225 KB)
+//   TMEM       = 256 columns: S (128 x F32) | O (128 x F32)
+//
+// Device-resident metadata is never an error (prefill.rs:289-347).  Every mbarrier wait is bounded;
+// after a timeout every role leaves its loop, the CTA frees its TMEM, records a status word and
+// writes nothing.
+#include <cstring>
+
+#include "kernels.hpp"
+#include "prefill_device.cuh"
+
+namespace lb {
+namespace {
+
+using namespace dev;
+
+constexpr int kTileRows = 128;   // packed query rows per CTA = TMEM lanes
+constexpr int kBlockTokens = 128; // KV tokens per block = 8 pages
+constexpr int kBlockPages = kBlockTokens / kPage;
+constexpr int kHalfBytes = kTileRows * 128; // one 64-element (128-byte) column half of a 128-row tile
+constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KB
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemColumns = 256;
+constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8
+
+// shared-memory map (offsets from the 1024-byte aligned base)
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kTileBytes;
+constexpr int kOffV = kOffK + kStages * kTileBytes;
+constexpr int kOffP = kOffV + kStages * kTileBytes;
+constexpr int kOffBars = kOffP + 2 * kTileBytes;
+// barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full[2] p_free[2] verdict
+constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
+              kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kNumBars = 15;
+constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
+constexpr int kSharedBytes = 1024 + kOffMisc + 32;
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]; one thread issues.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     bar)
+                 : "memory");
+}
+// 32 consecutive F32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};" ::"r"(
+            __float_as_uint(v[0])),
+        "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])),
+        "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])),
+        "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])),
+        "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])),
+        "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31])), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, tiles aligned to 1024 bytes.
+//   K-major operand (Q, K block, P): rows of 128 bytes, 8-row groups `sbo` bytes apart; a K step of
+//   16 elements is 32 bytes inside the row, reached by advancing the start address.
+//   MN-major operand (V page): rows of 128 bytes = 64 contiguous MN elements of one K index,
+//   8-row K groups `sbo` bytes apart, the next 64 MN elements `lbo` bytes away.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((address & 0x3ffffu) >> 4) | ((uint64_t)(lbo >> 4) << 16) |
+           ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: F32 accumulator, BF16 A and B, M = 128, N = 128; A K-major.
+constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) |
+                                ((128u >> 4) << 24);
+constexpr uint32_t kIdescQK = kIdescBase;             // B = K block, K-major
+constexpr uint32_t kIdescPV = kIdescBase | (1u << 16); // B = V page, MN-major
+
+// 16-byte chunk `chunk` (0..15) of 128-byte-swizzled row `row` of a 128-row K-major tile.
+__device__ __forceinline__ uint32_t tile_chunk_offset(int row, int chunk) {
+    return (chunk >> 3) * kHalfBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
+                           const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    dependent_launch_release();
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    uint8_t *base = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t base_u32 = smem_u32(base);
+    const uint32_t bars = base_u32 + kOffBars;
+    volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(base + kOffMisc);
+    // misc[0] = TMEM base address, misc[1] = an out-of-range page index was seen,
+    // misc[2] = a bounded wait ran out
+
+    const int group = a.qh / a.kvh;
+    const int kv_head = blockIdx.x % a.kvh;
+    const int tile = a.tiles - 1 - (int)(blockIdx.x / a.kvh); // late (long) tiles start first
+
+    if (tid == 0) {
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool by_warps = i == kBarSFree || i == kBarPFull || i == kBarPFull + 1;
+            mbar_init(bars + i * 8, by_warps ? 4 : 1);
+        }
+        fence_barrier_init();
+        misc[1] = 0;
+        misc[2] = 0;
+    }
+    if (warp == 4 && lane == 0) {
+        prefetch_tensormap(&k_half_map);
+        prefetch_tensormap(&v_map);
+    }
+    dependent_launch_wait();
+    // ---- guards: CTA-uniform, before any TMEM is held ---------------------------------------------
+    if (a.qo_indptr[0] != 0 || a.qo_indptr[a.batch] != a.nnz_qo) return; // prefill.rs:289-296
+    int request, tile_in_request;
+    if (!locate_tile(a, group, kTileRows, tile, lane, request, tile_in_request)) return;
+    int page_start, page_end, tail;
+    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_min, a.indices_len, request,
+                                page_start, page_end, tail))
+        return;
+    const int qo_start = a.qo_indptr[request];
+    const int qo_len = a.qo_indptr[request + 1] - qo_start;
+    const int num_pages = page_end - page_start;
+    const long long kv_len_wide = (long long)(num_pages - 1) * kPage + tail;
+    if (qo_len > kv_len_wide) return; // prefill.rs:343-347
+    const int kv_len = (int)kv_len_wide;
+    const int shift = kv_len - qo_len + 1; // the row of token t sees logical tokens [0, shift + t)
+    const long long rows_total = (long long)qo_len * group;
+    const long long row_lo = (long long)tile_in_request * kTileRows;
+    const long long row_hi = min(row_lo + kTileRows, rows_total);
+    const int cta_limit = shift + (int)((row_hi - 1) / group); // tokens the last row sees
+    const int cnt = (cta_limit + kPage - 1) / kPage;           // pages this CTA streams
+    const int blocks = (cnt + kBlockPages - 1) / kBlockPages;
+
+    // ---- TMEM, Q tile ---------------------------------------------------------------------------------
+    if (warp == 5) {
+        tmem_alloc(base_u32 + kOffMisc, kTmemColumns);
+        tmem_relinquish();
+    }
+    // this thread's packed row (warps 0-3)
+    const long long my_row = row_lo + tid;
+    const bool row_valid = tid < kTileRows && my_row < row_hi;
+    const int my_token = row_valid ? (int)(my_row / group) : 0;
+    const int my_head = kv_head * group + (row_valid ? (int)(my_row % group) : 0);
+    const size_t my_state = (size_t)(qo_start + my_token) * a.qh + my_head;
+    if (tid < kTileRows) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.query + my_state * kHeadDim);
+#pragma unroll
+        for (int chunk = 0; chunk < 16; ++chunk) {
+            const uint4 value = row_valid ? __ldg(src + chunk) : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(base + kOffQ + tile_chunk_offset(tid, chunk)) = value;
+        }
+        fence_proxy_async(); // the MMAs read Q through the async proxy
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = misc[0];
+    const uint32_t tmem_s = tmem_base;       // columns [0, 128): scores
+    const uint32_t tmem_o = tmem_base + 128; // columns [128, 256): output accumulator
+
+    if (warp == 4) {
+        // ================= producer: page-table walk + TMA ==========================================
+        // lanes 0-15: the two 64-dim halves of the K rows of page lane / 2 (2 KB boxes: the K block
+        // must be one uniform 128-token operand); lanes 16-23: the V page lane - 16 (4 KB box)
+        const bool is_k = lane < 16;
+        const int slot = is_k ? lane >> 1 : lane - 16;
+        const int half = lane & 1;
+        const bool lane_active = lane < 24;
+        bool bad_page = false;
+        for (int j = 0; j < blocks; ++j) {
+            const int stage = j & 1;
+            const uint32_t parity_prev = ((j >> 1) + 1) & 1; // parity of the previous use's release
+            const int page = j * kBlockPages + slot;
+            const bool has = lane_active && page < cnt;
+            int page_id = 0;
+            if (has) {
+                page_id = a.indices[page_start + page];
+                if (page_id < 0 || page_id >= a.max_pages) {
+                    bad_page = true;
+                    page_id = 0;
+                }
+            }
+            const int pages_here = min(kBlockPages, cnt - j * kBlockPages);
+            bool ok = true;
+            if (j >= kStages) {
+                ok = mbar_wait(bars + (kBarKEmpty + stage) * 8, parity_prev);
+                ok = mbar_wait(bars + (kBarVEmpty + stage) * 8, parity_prev) && ok;
+            }
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) misc[2] = 1;
+                break;
+            }
+            if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_here * 4096);
+            if (lane == 16) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
+            __syncwarp();
+            if (has && is_k)
+                tma_load_3d(base_u32 + kOffK + stage * kTileBytes + half * kHalfBytes + slot * 2048,
+                            &k_half_map, 0, page_id * kPage, kv_head * 2 + half,
+                            bars + (kBarKFull + stage) * 8);
+            if (has && !is_k)
+                tma_load_3d(base_u32 + kOffV + stage * kTileBytes + slot * 4096, &v_map, 0,
+                            page_id * kPage, kv_head * 2, bars + (kBarVFull + stage) * 8);
+        }
+        // the reference validates every page of the request, also those past the causal limit of
+        // a row (prefill.rs:333-340): the pages this CTA does not stream are range-checked
+        for (int j = cnt + lane; j < num_pages; j += 32) {
+            const int id = a.indices[page_start + j];
+            if (id < 0 || id >= a.max_pages) bad_page = true;
+        }
+        if (__any_sync(0xffffffffu, bad_page) && lane == 0) misc[1] = 1;
+        __syncwarp();
+        // the verdict on the request's pages is final: the epilogue warps wait for it
+        if (lane == 0) mbar_arrive(bars + kBarVerdict * 8);
+    } else if (warp == 5) {
+        // ================= MMA issue =================================================================
+        // order: S(0), S(1), PV(0), S(2), PV(1), ... so that the scores of the next block are ready
+        // when the softmax warps finish the current one
+        auto issue_pv = [&](int i) -> bool {
+            const int stage = i & 1, buffer = i & 1;
+            const uint32_t parity = (i >> 1) & 1;
+            bool ok = mbar_wait(bars + (kBarPFull + buffer) * 8, parity);
+            ok = mbar_wait(bars + (kBarVFull + stage) * 8, parity) && ok;
+            if (!ok) return false;
+            tc_fence_after();
+            if (lane == 0) {
+                const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
+                for (int p = 0; p < pages_here; ++p) {
+                    const uint64_t a_desc = smem_desc(
+                        base_u32 + kOffP + buffer * kTileBytes + (p >> 2) * kHalfBytes + (p & 3) * 32,
+                        16, 1024);
+                    const uint64_t b_desc =
+                        smem_desc(base_u32 + kOffV + stage * kTileBytes + p * 4096, 2048, 1024);
+                    umma_bf16(tmem_o, a_desc, b_desc, kIdescPV, (i > 0 || p > 0) ? 1u : 0u);
+                }
+                umma_commit(bars + (kBarPFree + buffer) * 8);
+                umma_commit(bars + (kBarVEmpty + stage) * 8);
+            }
+            __syncwarp();
+            return true;
+        };
+        bool ok = true;
+        for (int j = 0; j < blocks && ok; ++j) {
+            const int stage = j & 1;
+            ok = mbar_wait(bars + (kBarKFull + stage) * 8, (j >> 1) & 1);
+            if (ok && j > 0) ok = mbar_wait(bars + kBarSFree * 8, (j - 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t offset = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+                    const uint64_t a_desc = smem_desc(base_u32 + kOffQ + offset, 16, 1024);
+                    const uint64_t b_desc =
+                        smem_desc(base_u32 + kOffK + stage * kTileBytes + offset, 16, 1024);
+                    umma_bf16(tmem_s, a_desc, b_desc, kIdescQK, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(bars + kBarSFull * 8);
+                umma_commit(bars + (kBarKEmpty + stage) * 8);
+            }
+            __syncwarp();
+            if (j > 0) ok = issue_pv(j - 1);
+        }
+        if (ok) ok = issue_pv(blocks - 1);
+        if (!ok && lane == 0) misc[2] = 1;
+    } else {
+        // ================= softmax + epilogue: thread t owns packed row t ===========================
+        const int see = row_valid ? shift + my_token : 0; // logical tokens this row sees
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float m_used = -INFINITY; // exponent base of P, O and the normaliser
+        float l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < blocks; ++j) {
+            const int buffer = j & 1;
+            ok = mbar_wait(bars + kBarSFull * 8, j & 1);
+            if (__any_sync(0xffffffffu, !ok)) break;
+            tc_fence_after();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float part[32];
+                tmem_load32(tmem_s + lane_base + c * 32, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[c * 32 + i] = part[i];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + kBarSFree * 8); // S may be overwritten by block j + 1
+            // mask with the row's causal limit (stale or garbage columns included), row maximum
+            const int limit = see - j * kBlockTokens;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; ++i) {
+                s[i] = i < limit ? s[i] * a.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, s[i]);
+            }
+            // the exponent base follows the maximum lazily: P <= 2^8 keeps BF16 P and the F32
+            // normaliser exact enough, and most blocks skip the TMEM round trip of O
+            const bool rescale = mx > m_used + kRescaleThreshold ||
+                                 (m_used == -INFINITY && mx > -INFINITY);
+            const bool any_rescale = __any_sync(0xffffffffu, rescale);
+            if (any_rescale) {
+                const float m_new = rescale ? mx : m_used;
+                const float alpha = rescale ? fast_exp2(m_used - m_new) : 1.0f; // 0 from -inf
+                l *= alpha;
+                m_used = m_new;
+                if (j > 0) {
+                    // O holds blocks 0..j-1 once P V (j - 1) has completed
+                    ok = mbar_wait(bars + (kBarPFree + ((j - 1) & 1)) * 8, ((j - 1) >> 1) & 1);
+                    if (__any_sync(0xffffffffu, !ok)) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float part[32];
+                        tmem_load32(tmem_o + lane_base + c * 32, part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) part[i] *= alpha;
+                        tmem_store32(tmem_o + lane_base + c * 32, part);
+                    }
+                    tmem_store_wait();
+                }
+            }
+            const float base_m = m_used == -INFINITY ? 0.0f : m_used;
+            // P buffer `buffer` is free once P V (j - 2) has completed
+            if (j >= 2) {
+                ok = mbar_wait(bars + (kBarPFree + buffer) * 8, ((j - 2) >> 1) & 1);
+                if (__any_sync(0xffffffffu, !ok)) break;
+            }
+            uint8_t *p_tile = base + kOffP + buffer * kTileBytes;
+            float sum = 0.0f;
+#pragma unroll
+            for (int chunk = 0; chunk < 16; ++chunk) {
+                float p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    p[i] = fast_exp2(s[chunk * 8 + i] - base_m);
+                    sum += p[i];
+                }
+                *reinterpret_cast<uint4 *>(p_tile + tile_chunk_offset(tid, chunk)) =
+                    make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
+                               pack_bf16(p[6], p[7]));
+            }
+            l += sum;
+            // rows of the request's last page past its length may hold anything (0 * NaN): zero
+            // them in the V block before the MMA reads it
+            const int last_page = num_pages - 1;
+            if (tail < kPage && last_page / kBlockPages == j && last_page < cnt) {
+                ok = mbar_wait(bars + (kBarVFull + (j & 1)) * 8, (j >> 1) & 1);
+                if (__any_sync(0xffffffffu, !ok)) break;
+                uint8_t *v_page = base + kOffV + (j & 1) * kTileBytes + (last_page % kBlockPages) * 4096;
+                for (int i = tid; i < (kPage - tail) * 16; i += kTileRows) {
+                    const int row = tail + (i >> 4), c = i & 15;
+                    *reinterpret_cast<uint4 *>(v_page + (c >> 3) * 2048 + row * 128 + (c & 7) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            fence_proxy_async(); // P (and the zeroed V rows) become visible to the MMA
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + (kBarPFull + buffer) * 8);
+        }
+        if (__any_sync(0xffffffffu, !ok)) {
+            if (lane == 0) misc[2] = 1;
+        } else {
+            // every P V has completed once the last one has
+            ok = mbar_wait(bars + (kBarPFree + ((blocks - 1) & 1)) * 8, ((blocks - 1) >> 1) & 1);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) misc[2] = 1;
+            } else {
+                tc_fence_after();
+                const bool verdict = mbar_wait(bars + kBarVerdict * 8, 0); // the producer's page scan
+                const bool publish = verdict && row_valid && misc[1] == 0 && misc[2] == 0;
+                const float inv = 1.0f / l;
+                uint4 *dst = reinterpret_cast<uint4 *>(a.output + my_state * kHeadDim);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float part[32];
+                    tmem_load32(tmem_o + lane_base + c * 32, part);
+                    if (publish) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[c * 4 + i] = make_uint4(
+                                pack_bf16(part[i * 8] * inv, part[i * 8 + 1] * inv),
+                                pack_bf16(part[i * 8 + 2] * inv, part[i * 8 + 3] * inv),
+                                pack_bf16(part[i * 8 + 4] * inv, part[i * 8 + 5] * inv),
+                                pack_bf16(part[i * 8 + 6] * inv, part[i * 8 + 7] * inv));
+                    }
+                }
+                if (publish) a.lse[my_state] = m_used + log2f(l);
+            }
+        }
+    }
+
+    // ---- join: all tcgen05 work of this CTA has completed or been abandoned ------------------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 5) tmem_dealloc(tmem_base, kTmemColumns);
+    if (tid == 0 && misc[2] != 0 && a.status) atomicExch(a.status, 1);
+}
+
+} // namespace
+
+int configure_prefill_tiled_kernel(size_t max_dynamic_shared) {
+    if ((size_t)kSharedBytes > max_dynamic_shared) return cudaErrorInvalidValue;
+    return cudaFuncSetAttribute(paged_prefill_tiled_kernel,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedBytes);
+}
+
+int prefill_tiled_shared_bytes() { return kSharedBytes; }
+
+int launch_paged_prefill_tiled(const PrefillLaunch &launch, void *stream) {
+    PrefillArgs args;
+    args.query = static_cast<const __nv_bfloat16 *>(launch.query);
+    args.qo_indptr = launch.qo_indptr;
+    args.indptr = launch.indptr;
+    args.indices = launch.indices;
+    args.last = launch.last;
+    args.output = static_cast<__nv_bfloat16 *>(launch.output);
+    args.lse = launch.lse;
+    args.status = launch.status;
+    args.batch = launch.batch;
+    args.nnz_qo = launch.nnz_qo;
+    args.max_pages = launch.max_pages;
+    args.qh = launch.qh;
+    args.kvh = launch.kvh;
+    args.indices_len = launch.indices_len;
+    args.indices_min = launch.indices_min;
+    args.mt = 8;
+    args.pps = kBlockPages;
+    args.stages = kStages;
+    args.tiles = launch.tiles;
+    args.scale_log2 = launch.scale_log2;
+    CUtensorMap k_half_map, v_map;
+    memcpy(&k_half_map, launch.k_map, sizeof(k_half_map));
+    memcpy(&v_map, launch.v_map, sizeof(v_map));
+    return launch_dependent(paged_prefill_tiled_kernel, launch.grid, kThreads, kSharedBytes, stream,
+                            k_half_map, v_map, args);
+}
+
+} // namespace lb

@@ -119,6 +119,7 @@ class Bf16PagedPrefillMetadata:
 
 class Bf16PagedPrefillAlgorithm:
     TokenParallel = 0
+    Tiled = 1
 
 
 @dataclass
@@ -156,10 +157,12 @@ class PrefillProvider:
         return out.value
 
     def plan_bf16_paged(self, spec: Bf16PagedPrefillSpec, q_tiles: int = 0,
-                        indices_capacity: bool = False) -> "Bf16PagedPrefillPlan":
-        """q_tiles: 0 heuristic, else the 16-row tiles of packed query rows one CTA owns
-        (1, 2, 4 or 8).  indices_capacity as for the decode plan."""
-        options = _abi.PrefillOptions(q_tiles=q_tiles,
+                        indices_capacity: bool = False,
+                        algorithm: int = 0) -> "Bf16PagedPrefillPlan":
+        """algorithm: 0 heuristic, 1 token-parallel, 2 tiled (tcgen05).  q_tiles (token-parallel):
+        0 heuristic, else the 16-row tiles of packed query rows one CTA owns (1, 2, 4 or 8).
+        indices_capacity as for the decode plan."""
+        options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm,
                                       indices_capacity=1 if indices_capacity else 0)
         out = c_void_p()
         _check(_abi.load().lb_paged_prefill_plan_create(self._ptr, byref(spec._raw),
@@ -167,9 +170,10 @@ class PrefillProvider:
         return Bf16PagedPrefillPlan(out.value)
 
 
-def choose_paged_prefill(spec: Bf16PagedPrefillSpec, sm_count: int, q_tiles: int = 0):
+def choose_paged_prefill(spec: Bf16PagedPrefillSpec, sm_count: int, q_tiles: int = 0,
+                         algorithm: int = 0):
     """The plan-time launch shape as a pure function (no device needed)."""
-    options = _abi.PrefillOptions(q_tiles=q_tiles)
+    options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm)
     info = _abi.PrefillPlanInfo()
     _check(_abi.load().lb_paged_prefill_choose(byref(spec._raw), sm_count, byref(options),
                                                byref(info)))

@@ -42,9 +42,9 @@ class PrefillRun:
     """One paged prefill through the public API: spec -> plan -> bindings -> scope -> fence."""
 
     def __init__(self, provider, spec, q, k, v, qo_indptr, indptr, indices, last, q_tiles=0,
-                 sentinel=float("nan"), indices_capacity=False):
+                 sentinel=float("nan"), indices_capacity=False, algorithm=1):
         self.provider, self.spec = provider, spec
-        self.plan = provider.plan_bf16_paged(spec, q_tiles=q_tiles,
+        self.plan = provider.plan_bf16_paged(spec, q_tiles=q_tiles, algorithm=algorithm,
                                              indices_capacity=indices_capacity)
         self.queue = lk.CommandQueue(torch.cuda.Stream(), 1)
         self.tensors = [t if isinstance(t, torch.Tensor) else H.dev_bf16(t) for t in (q, k, v)]

@@ -94,12 +94,24 @@ def test_launch_shape_is_fixed_by_spec_and_device():
     short = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(2, 96, 96, 16, 4), 148)
     assert (short.q_tiles, short.pages_per_stage, short.rows_per_cta, short.commands) == (1, 8, 16, 1)
     assert short.tiles == 96 * 4 // 16 + 2 and short.grid == short.tiles * 4 and short.block == 288
-    # a long prompt: 128-row tiles, every loaded page used by 128 rows
-    long = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 8192, 600, 32, 8), 148)
+    # a long prompt: the tensor-core kernel, 128-row tiles and 128-token blocks
+    prompt = lk.Bf16PagedPrefillSpec.new(1, 8192, 600, 32, 8)
+    tiled = lk.choose_paged_prefill(prompt, 148)
+    assert tiled.algorithm == lk.Bf16PagedPrefillAlgorithm.Tiled
+    assert (tiled.rows_per_cta, tiled.pages_per_stage, tiled.block, tiled.commands) == (128, 8, 192, 1)
+    assert tiled.tiles == 8192 * 4 // 128 + 1 and tiled.grid == tiled.tiles * 8
+    assert 224 * 1024 <= tiled.shared_bytes <= 232448
+    # the same prompt forced onto the token-parallel kernel: every loaded page used by 128 rows
+    long = lk.choose_paged_prefill(prompt, 148, algorithm=1)
+    assert long.algorithm == lk.Bf16PagedPrefillAlgorithm.TokenParallel
     assert (long.q_tiles, long.pages_per_stage, long.rows_per_cta) == (8, 1, 128)
     assert long.tiles == 8192 * 4 // 128 + 1 and long.grid == long.tiles * 8
-    forced = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 8192, 600, 32, 8), 148, q_tiles=2)
-    assert (forced.q_tiles, forced.pages_per_stage) == (2, 4)
+    forced = lk.choose_paged_prefill(prompt, 148, q_tiles=2)
+    assert (forced.algorithm, forced.q_tiles, forced.pages_per_stage) == (0, 2, 4)
+    assert lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(2, 96, 96, 16, 4), 148,
+                                   algorithm=2).algorithm == 1  # the caller may force it
+    with pytest.raises(lk.PlanError):
+        lk.choose_paged_prefill(prompt, 148, algorithm=3)
     for info in (short, long, forced):
         # the ring holds whole stages and, with several page slots, the states they merge through
         ring = info.stages * info.pages_per_stage * 8192

@@ -116,10 +116,12 @@ def test_spec_errors(oracle):
         ("LengthMismatch", "Q", (128, 127))
 
 
-def test_published_fixture_digests_of_the_reordered_gqa4_case(oracle):
-    """The gate's gqa4_reordered_reuse inputs (gates/paged_prefill.rs:561-573) hash to the
-    fixture digests of the reference's Graph performance report."""
-    g = GOLDEN["paged_prefill"]["gqa4_reordered_reuse"]
+@pytest.mark.parametrize("name", ["gqa4_reordered_reuse", "mqa_token_parallel",
+                                  "gqa4_token_parallel"])
+def test_published_fixture_digests(oracle, name):
+    """The gate's inputs (gates/paged_prefill.rs:561-606) hash to the fixture digests of the
+    reference's Graph and long-context performance reports."""
+    g = GOLDEN["paged_prefill"][name]
     batch, nnz, pages, qh, kvh = g["spec"]
     salt = int(g["salt"], 16)
     assert hx(oracle.digest_bf16(oracle.fixture_bf16(nnz * qh * 128, salt))) == g["query"]
