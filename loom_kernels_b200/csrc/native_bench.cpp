@@ -324,6 +324,70 @@ struct AppendCase : Case {
     }
 };
 
+// Paged causal prefill: requests with qo_lens[r] query tokens over kv_lens[r] KV tokens, pages in
+// a fixed scattered order.
+struct PrefillCase : Case {
+    lb_prefill_spec spec{};
+    lb_paged_prefill_plan *plan = nullptr;
+    uint16_t *query, *key_pages, *value_pages, *output;
+    int32_t *qo_indptr, *indptr, *indices, *last;
+    float *lse;
+    size_t indices_len;
+    lb_paged_prefill_args args{};
+
+    PrefillCase(const char *label, lb_prefill_provider *provider, size_t qh, size_t kvh,
+                const std::vector<int> &qo_lens, const std::vector<int> &kv_lens) {
+        name = label;
+        const size_t batch = qo_lens.size();
+        std::vector<int32_t> qo{0}, page_indptr{0}, page_indices, last_page_len;
+        size_t total_pages = 0;
+        for (size_t r = 0; r < batch; ++r) total_pages += (size_t)(kv_lens[r] + 15) / 16;
+        const size_t pool = total_pages + 8;
+        size_t next = 0, stride = 37; // a stride coprime to the pool visits every page once
+        auto gcd = [](size_t x, size_t y) { while (y) { const size_t t = x % y; x = y; y = t; } return x; };
+        while (gcd(stride, pool) != 1) ++stride;
+        for (size_t r = 0; r < batch; ++r) {
+            qo.push_back(qo.back() + qo_lens[r]);
+            for (int p = 0; p < (kv_lens[r] + 15) / 16; ++p)
+                page_indices.push_back((int32_t)((next++ * stride + 11) % pool));
+            page_indptr.push_back((int32_t)page_indices.size());
+            last_page_len.push_back((kv_lens[r] - 1) % 16 + 1);
+        }
+        indices_len = page_indices.size();
+        LB(lb_prefill_spec_new(batch, (size_t)qo.back(), pool, qh, kvh, 128, 16, &spec));
+        LB(lb_paged_prefill_plan_create(provider, &spec, nullptr, &plan));
+        commands = 1;
+        query = upload_normal(lb_prefill_spec_query_numel(&spec), 7);
+        key_pages = upload_normal(lb_prefill_spec_kv_pages_numel(&spec), 8);
+        value_pages = upload_normal(lb_prefill_spec_kv_pages_numel(&spec), 9);
+        output = device_zeros<uint16_t>(lb_prefill_spec_query_numel(&spec));
+        lse = device_zeros<float>(lb_prefill_spec_lse_numel(&spec));
+        qo_indptr = upload(qo);
+        indptr = upload(page_indptr);
+        indices = upload(page_indices);
+        last = upload(last_page_len);
+        slots = 9;
+    }
+    void bind(lb_bindings *b) override {
+        lb_handle out{}, l{};
+        const size_t pool = lb_prefill_spec_kv_pages_numel(&spec);
+        LB(lb_bind_read(b, LB_BF16, query, lb_prefill_spec_query_numel(&spec), &args.query));
+        LB(lb_bind_read(b, LB_BF16, key_pages, pool, &args.key_pages));
+        LB(lb_bind_read(b, LB_BF16, value_pages, pool, &args.value_pages));
+        LB(lb_bind_read(b, LB_I32, qo_indptr, spec.batch_size + 1, &args.qo_indptr));
+        LB(lb_bind_read(b, LB_I32, indptr, spec.batch_size + 1, &args.page_indptr));
+        LB(lb_bind_read(b, LB_I32, indices, indices_len, &args.page_indices));
+        LB(lb_bind_read(b, LB_I32, last, spec.batch_size, &args.last_page_len));
+        LB(lb_bind_read_write(b, LB_BF16, output, lb_prefill_spec_query_numel(&spec), &out));
+        LB(lb_bind_read_write(b, LB_F32, lse, lb_prefill_spec_lse_numel(&spec), &l));
+        args.output = lb_handle_write(out);
+        args.lse = lb_handle_write(l);
+    }
+    lb_status enqueue(lb_scope *scope) override {
+        return lb_paged_prefill_enqueue(plan, scope, &args);
+    }
+};
+
 } // namespace
 
 int main(int argc, char **argv) {
@@ -336,8 +400,10 @@ int main(int argc, char **argv) {
     CU(cudaSetDevice(opt.device));
     lb_decode_provider *decode = nullptr;
     lb_rope_provider *rope = nullptr;
+    lb_prefill_provider *prefill = nullptr;
     LB(lb_decode_provider_load(opt.device, &decode));
     LB(lb_rope_provider_load(opt.device, &rope));
+    LB(lb_prefill_provider_load(opt.device, &prefill));
 
     // the three paged-decode shapes and the two append shapes with published reference numbers
     DecodeCase mha("gate mha_b1_l1", decode, 1, 2, 8, 8, {0, 1}, {1}, {1}, 1);
@@ -354,7 +420,17 @@ int main(int argc, char **argv) {
     for (int i = 0; i < 64; ++i) c1_pages[i] = (i * 37 + 11) % 256;
     DecodeCase c1("C1 paged decode MHA b1 32/32 ctx1024 pool256 (plan-chosen)", decode, 1, 256, 32,
                   32, {0, 64}, c1_pages, {16}, 0);
-    Case *cases[] = {&mha, &mqa, &gqa, &one, &six, &c1};
+    // the five paged-prefill shapes with published reference numbers
+    PrefillCase p_mha("gate prefill mha_b1_q4_kv4 8/8", prefill, 8, 8, {4}, {4});
+    PrefillCase p_mqa("gate prefill mqa_b3_q2_3_1_kv4_22_35 8/1", prefill, 8, 1, {2, 3, 1},
+                      {4, 22, 35});
+    PrefillCase p_gqa("gate prefill gqa4_b2_q4_2_kv23_18 16/4", prefill, 16, 4, {4, 2}, {23, 18});
+    PrefillCase p_mqa_long("gate prefill mqa_b3_q1_4_16_kv128_256_512 8/1", prefill, 8, 1,
+                           {1, 4, 16}, {128, 256, 512});
+    PrefillCase p_gqa_long("gate prefill gqa4_b2_q32_64_kv256_1024 16/4", prefill, 16, 4, {32, 64},
+                           {256, 1024});
+    Case *cases[] = {&mha, &mqa, &gqa, &one, &six, &c1, &p_mha, &p_mqa, &p_gqa, &p_mqa_long,
+                     &p_gqa_long};
     for (Case *c : cases) measure(*c, opt);
     return 0;
 }

@@ -115,7 +115,7 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         memset(out, 0, sizeof(*out));
         out->algorithm = LB_PREFILL_TILED;
         out->q_tiles = 8;
-        out->pages_per_stage = 8;
+        out->pages_per_stage = 4; // blocks of 64 KV tokens
         out->stages = 2;
         out->rows_per_cta = 128;
         out->tiles = (uint32_t)tiles;

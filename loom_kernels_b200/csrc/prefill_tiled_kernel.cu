@@ -7,22 +7,25 @@
 // Shape of the kernel
 //   work item  = (request, KV head, tile of 128 packed (token, head-in-group) rows); one CTA each,
 //                192 threads: warps 0-3 own one row per thread (row t = TMEM lane t), warp 4 issues
-//                the TMA loads, warp 5 allocates TMEM and issues the MMAs.
-//   per block  = 128 KV tokens (8 pages):
-//                  S = Q K^T      8 x tcgen05.mma 128x128x16 (A = Q, B = K block, both K-major in
+//                the TMA loads, warp 5 allocates TMEM and issues the MMAs.  Two CTAs share an SM
+//                (about 112 KB of shared memory and 256 TMEM columns each), so one CTA's MMAs run
+//                under the other's softmax and every scheduler has two softmax warps.
+//   per block  = 64 KV tokens (4 pages):
+//                  S = Q K^T      8 x tcgen05.mma 128x64x16 (A = Q, B = K block, both K-major in
 //                                 shared memory with the 128-byte swizzle), accumulator S in TMEM
 //                  softmax        each thread pulls its S row out of TMEM (tcgen05.ld), masks it
-//                                 with the row's causal limit, and writes P = 2^(S - m) as BF16
-//                                 into shared memory in the A-operand layout; the exponent base m
-//                                 follows the running maximum lazily (only a rise of more than 8
-//                                 rescales O and the normaliser, through tcgen05.ld/st)
+//                                 with the row's causal limit where the block crosses it, and
+//                                 writes P = 2^(S - m) as BF16 into shared memory in the A-operand
+//                                 layout; the exponent base m follows the running maximum lazily
+//                                 (only a rise of more than 8 rescales O and the normaliser,
+//                                 through tcgen05.ld/st)
 //                  O += P V       one tcgen05.mma 128x128x16 per page (A = P, B = the V page, which
 //                                 is MN-major: 64 dims contiguous per 128-byte row), O in TMEM
 //   pipelining = K and V blocks are double-buffered by TMA; the S MMAs of block j + 1 are issued
-//                before the P V MMAs of block j, so the tensor pipe computes the next scores while
-//                the softmax warps work; P is double-buffered.
-//   shared mem = Q 32 KB | K 2 x 32 KB | V 2 x 32 KB | P 2 x 32 KB | barriers  (about 225 KB)
-//   TMEM       = 256 columns: S (128 x F32) | O (128 x F32)
+//                before the P V MMAs of block j, so the next scores are ready when the softmax
+//                warps finish the current block.
+//   shared mem = Q 32 KB | K 2 x 16 KB | V 2 x 16 KB | P 16 KB | barriers
+//   TMEM       = 256 columns allocated: S (64 x F32) | O (128 x F32)
 //
 // Device-resident metadata is never an error (prefill.rs:289-347).  Every mbarrier wait is bounded;
 // after a timeout every role leaves its loop, the CTA frees its TMEM, records a status word and
@@ -38,26 +41,32 @@ namespace {
 using namespace dev;
 
 constexpr int kTileRows = 128;   // packed query rows per CTA = TMEM lanes
-constexpr int kBlockTokens = 128; // KV tokens per block = 8 pages
+constexpr int kBlockTokens = 64; // KV tokens per block = 4 pages
 constexpr int kBlockPages = kBlockTokens / kPage;
-constexpr int kHalfBytes = kTileRows * 128; // one 64-element (128-byte) column half of a 128-row tile
-constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KB
+constexpr int kQHalfBytes = kTileRows * 128;   // 64 dims (128 bytes) of the 128 query rows
+constexpr int kQBytes = 2 * kQHalfBytes;       // 32 KB
+constexpr int kKHalfBytes = kBlockTokens * 128; // 64 dims of the block's token rows
+constexpr int kKStageBytes = 2 * kKHalfBytes;  // 16 KB
+constexpr int kVStageBytes = kBlockPages * 4096; // 16 KB: per page [half][16 tokens][64 dims]
+constexpr int kPBytes = kTileRows * 128;       // 16 KB: 64 tokens (128 bytes) of the 128 rows
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemColumns = 256;
-constexpr float kRescaleThreshold = 8.0f; // log2 domain: P stays below 2^8
+constexpr uint32_t kTmemColumns = 256;         // a power of two >= 64 (S) + 128 (O)
+constexpr uint32_t kTmemS = 0, kTmemO = 64;
+constexpr float kRescaleThreshold = 8.0f;      // log2 domain: P stays below 2^8
 
-// shared-memory map (offsets from the 1024-byte aligned base)
+// shared-memory map (offsets from the 1024-byte aligned base of dynamic shared memory)
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kTileBytes;
-constexpr int kOffV = kOffK + kStages * kTileBytes;
-constexpr int kOffP = kOffV + kStages * kTileBytes;
-constexpr int kOffBars = kOffP + 2 * kTileBytes;
-// barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full[2] p_free[2] verdict
+constexpr int kOffK = kOffQ + kQBytes;
+constexpr int kOffV = kOffK + kStages * kKStageBytes;
+constexpr int kOffP = kOffV + kStages * kVStageBytes;
+constexpr int kOffBars = kOffP + kPBytes;
+// barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full p_free verdict
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
-              kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kNumBars = 15;
+              kBarSFree = 9, kBarPFull = 10, kBarPFree = 11, kBarVerdict = 12, kNumBars = 13;
 constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
-constexpr int kSharedBytes = 1024 + kOffMisc + 32;
+constexpr int kSharedBytes = kOffMisc + 24;
+static_assert(2 * (kSharedBytes + 1024) <= 233472, "two CTAs must fit one SM");
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------
 
@@ -144,27 +153,28 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t lbo, ui
     return (uint64_t)((address & 0x3ffffu) >> 4) | ((uint64_t)(lbo >> 4) << 16) |
            ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor: F32 accumulator, BF16 A and B, M = 128, N = 128; A K-major.
-constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) |
-                                ((128u >> 4) << 24);
-constexpr uint32_t kIdescQK = kIdescBase;             // B = K block, K-major
-constexpr uint32_t kIdescPV = kIdescBase | (1u << 16); // B = V page, MN-major
+// Instruction descriptor: F32 accumulator, BF16 A and B, M = 128, A K-major.
+constexpr uint32_t idesc(uint32_t n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? 1u << 16 : 0u) | ((n >> 3) << 17) |
+           ((128u >> 4) << 24);
+}
+constexpr uint32_t kIdescQK = idesc(kBlockTokens, false); // B = K block, K-major, N = 64 tokens
+constexpr uint32_t kIdescPV = idesc(kHeadDim, true);      // B = V page, MN-major, N = 128 dims
 
-// 16-byte chunk `chunk` (0..15) of 128-byte-swizzled row `row` of a 128-row K-major tile.
-__device__ __forceinline__ uint32_t tile_chunk_offset(int row, int chunk) {
-    return (chunk >> 3) * kHalfBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+// 16-byte chunk `chunk` of 128-byte-swizzled row `row` (one 128-byte column half of a tile).
+__device__ __forceinline__ uint32_t swizzled(int row, int chunk) {
+    return row * 128 + ((chunk ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                            const __grid_constant__ CUtensorMap v_map, const PrefillArgs a) {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     dependent_launch_release();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    uint8_t *base = reinterpret_cast<uint8_t *>(
-        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t *base = smem_raw;
     const uint32_t base_u32 = smem_u32(base);
     const uint32_t bars = base_u32 + kOffBars;
     volatile uint32_t *misc = reinterpret_cast<volatile uint32_t *>(base + kOffMisc);
@@ -176,10 +186,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     const int tile = a.tiles - 1 - (int)(blockIdx.x / a.kvh); // late (long) tiles start first
 
     if (tid == 0) {
-        for (int i = 0; i < kNumBars; ++i) {
-            const bool by_warps = i == kBarSFree || i == kBarPFull || i == kBarPFull + 1;
-            mbar_init(bars + i * 8, by_warps ? 4 : 1);
-        }
+        for (int i = 0; i < kNumBars; ++i)
+            mbar_init(bars + i * 8, i == kBarSFree || i == kBarPFull ? 4 : 1);
         fence_barrier_init();
         misc[1] = 0;
         misc[2] = 0;
@@ -190,6 +198,10 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     }
     dependent_launch_wait();
     // ---- guards: CTA-uniform, before any TMEM is held ---------------------------------------------
+    if ((base_u32 & 1023u) != 0) { // the swizzled tiles need the 1024-byte alignment asked for
+        if (tid == 0 && a.status) atomicExch(a.status, 2);
+        return;
+    }
     if (a.qo_indptr[0] != 0 || a.qo_indptr[a.batch] != a.nnz_qo) return; // prefill.rs:289-296
     int request, tile_in_request;
     if (!locate_tile(a, group, kTileRows, tile, lane, request, tile_in_request)) return;
@@ -227,7 +239,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
 #pragma unroll
         for (int chunk = 0; chunk < 16; ++chunk) {
             const uint4 value = row_valid ? __ldg(src + chunk) : make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4 *>(base + kOffQ + tile_chunk_offset(tid, chunk)) = value;
+            *reinterpret_cast<uint4 *>(base + kOffQ + (chunk >> 3) * kQHalfBytes +
+                                       swizzled(tid, chunk & 7)) = value;
         }
         fence_proxy_async(); // the MMAs read Q through the async proxy
     }
@@ -235,17 +248,17 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = misc[0];
-    const uint32_t tmem_s = tmem_base;       // columns [0, 128): scores
-    const uint32_t tmem_o = tmem_base + 128; // columns [128, 256): output accumulator
+    const uint32_t tmem_s = tmem_base + kTmemS; // scores of the block at hand
+    const uint32_t tmem_o = tmem_base + kTmemO; // output accumulator
 
     if (warp == 4) {
         // ================= producer: page-table walk + TMA ==========================================
-        // lanes 0-15: the two 64-dim halves of the K rows of page lane / 2 (2 KB boxes: the K block
-        // must be one uniform 128-token operand); lanes 16-23: the V page lane - 16 (4 KB box)
-        const bool is_k = lane < 16;
-        const int slot = is_k ? lane >> 1 : lane - 16;
+        // lanes 0-7: the two 64-dim halves of the K rows of page lane / 2 (2 KB boxes: the K block
+        // must be one uniform 64-token operand); lanes 8-11: the V page lane - 8 (4 KB box)
+        const bool is_k = lane < 8;
+        const int slot = is_k ? lane >> 1 : lane - 8;
         const int half = lane & 1;
-        const bool lane_active = lane < 24;
+        const bool lane_active = lane < 12;
         bool bad_page = false;
         for (int j = 0; j < blocks; ++j) {
             const int stage = j & 1;
@@ -271,14 +284,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 break;
             }
             if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_here * 4096);
-            if (lane == 16) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
+            if (lane == 8) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
             __syncwarp();
             if (has && is_k)
-                tma_load_3d(base_u32 + kOffK + stage * kTileBytes + half * kHalfBytes + slot * 2048,
+                tma_load_3d(base_u32 + kOffK + stage * kKStageBytes + half * kKHalfBytes + slot * 2048,
                             &k_half_map, 0, page_id * kPage, kv_head * 2 + half,
                             bars + (kBarKFull + stage) * 8);
             if (has && !is_k)
-                tma_load_3d(base_u32 + kOffV + stage * kTileBytes + slot * 4096, &v_map, 0,
+                tma_load_3d(base_u32 + kOffV + stage * kVStageBytes + slot * 4096, &v_map, 0,
                             page_id * kPage, kv_head * 2, bars + (kBarVFull + stage) * 8);
         }
         // the reference validates every page of the request, also those past the causal limit of
@@ -296,23 +309,20 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         // order: S(0), S(1), PV(0), S(2), PV(1), ... so that the scores of the next block are ready
         // when the softmax warps finish the current one
         auto issue_pv = [&](int i) -> bool {
-            const int stage = i & 1, buffer = i & 1;
-            const uint32_t parity = (i >> 1) & 1;
-            bool ok = mbar_wait(bars + (kBarPFull + buffer) * 8, parity);
-            ok = mbar_wait(bars + (kBarVFull + stage) * 8, parity) && ok;
+            const int stage = i & 1;
+            bool ok = mbar_wait(bars + kBarPFull * 8, i & 1);
+            ok = mbar_wait(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
             if (!ok) return false;
             tc_fence_after();
             if (lane == 0) {
                 const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
                 for (int p = 0; p < pages_here; ++p) {
-                    const uint64_t a_desc = smem_desc(
-                        base_u32 + kOffP + buffer * kTileBytes + (p >> 2) * kHalfBytes + (p & 3) * 32,
-                        16, 1024);
+                    const uint64_t a_desc = smem_desc(base_u32 + kOffP + p * 32, 16, 1024);
                     const uint64_t b_desc =
-                        smem_desc(base_u32 + kOffV + stage * kTileBytes + p * 4096, 2048, 1024);
+                        smem_desc(base_u32 + kOffV + stage * kVStageBytes + p * 4096, 2048, 1024);
                     umma_bf16(tmem_o, a_desc, b_desc, kIdescPV, (i > 0 || p > 0) ? 1u : 0u);
                 }
-                umma_commit(bars + (kBarPFree + buffer) * 8);
+                umma_commit(bars + kBarPFree * 8);
                 umma_commit(bars + (kBarVEmpty + stage) * 8);
             }
             __syncwarp();
@@ -328,10 +338,11 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (lane == 0) {
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t offset = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-                    const uint64_t a_desc = smem_desc(base_u32 + kOffQ + offset, 16, 1024);
-                    const uint64_t b_desc =
-                        smem_desc(base_u32 + kOffK + stage * kTileBytes + offset, 16, 1024);
+                    const uint64_t a_desc = smem_desc(
+                        base_u32 + kOffQ + (kk >> 2) * kQHalfBytes + (kk & 3) * 32, 16, 1024);
+                    const uint64_t b_desc = smem_desc(base_u32 + kOffK + stage * kKStageBytes +
+                                                          (kk >> 2) * kKHalfBytes + (kk & 3) * 32,
+                                                      16, 1024);
                     umma_bf16(tmem_s, a_desc, b_desc, kIdescQK, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(bars + kBarSFull * 8);
@@ -346,48 +357,57 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         // ================= softmax + epilogue: thread t owns packed row t ===========================
         const int see = row_valid ? shift + my_token : 0; // logical tokens this row sees
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float scale = a.scale_log2;
         float m_used = -INFINITY; // exponent base of P, O and the normaliser
         float l = 0.0f;
         bool ok = true;
         for (int j = 0; j < blocks; ++j) {
-            const int buffer = j & 1;
             ok = mbar_wait(bars + kBarSFull * 8, j & 1);
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
-            float s[128];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            float s[kBlockTokens]; // raw dot products
+            {
                 float part[32];
-                tmem_load32(tmem_s + lane_base + c * 32, part);
+                tmem_load32(tmem_s + lane_base, part);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c * 32 + i] = part[i];
+                for (int i = 0; i < 32; ++i) s[i] = part[i];
+                tmem_load32(tmem_s + lane_base + 32, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + kBarSFree * 8); // S may be overwritten by block j + 1
-            // mask with the row's causal limit (stale or garbage columns included), row maximum
+            // the row's causal limit inside this block; columns past it (which also covers stale
+            // or garbage key rows) are masked.  Most blocks lie wholly below the limit.
             const int limit = see - j * kBlockTokens;
-            float mx = -INFINITY;
+            if (!__all_sync(0xffffffffu, limit >= kBlockTokens)) {
 #pragma unroll
-            for (int i = 0; i < 128; ++i) {
-                s[i] = i < limit ? s[i] * a.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, s[i]);
+                for (int i = 0; i < kBlockTokens; ++i) s[i] = i < limit ? s[i] : -INFINITY;
+            }
+            float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+#pragma unroll
+            for (int i = 4; i < kBlockTokens; i += 2) {
+                mx0 = fmaxf(mx0, s[i]);
+                mx1 = fmaxf(mx1, s[i + 1]);
+            }
+            const float mx = fmaxf(mx0, mx1) * scale; // scale > 0; -inf stays -inf
+            // O holds blocks 0..j-1 and P is free once P V (j - 1) has completed
+            if (j > 0) {
+                ok = mbar_wait(bars + kBarPFree * 8, (j - 1) & 1);
+                if (__any_sync(0xffffffffu, !ok)) break;
+                tc_fence_after();
             }
             // the exponent base follows the maximum lazily: P <= 2^8 keeps BF16 P and the F32
             // normaliser exact enough, and most blocks skip the TMEM round trip of O
             const bool rescale = mx > m_used + kRescaleThreshold ||
                                  (m_used == -INFINITY && mx > -INFINITY);
-            const bool any_rescale = __any_sync(0xffffffffu, rescale);
-            if (any_rescale) {
+            if (__any_sync(0xffffffffu, rescale)) {
                 const float m_new = rescale ? mx : m_used;
                 const float alpha = rescale ? fast_exp2(m_used - m_new) : 1.0f; // 0 from -inf
                 l *= alpha;
                 m_used = m_new;
                 if (j > 0) {
-                    // O holds blocks 0..j-1 once P V (j - 1) has completed
-                    ok = mbar_wait(bars + (kBarPFree + ((j - 1) & 1)) * 8, ((j - 1) >> 1) & 1);
-                    if (__any_sync(0xffffffffu, !ok)) break;
-                    tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         float part[32];
@@ -399,34 +419,29 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                     tmem_store_wait();
                 }
             }
-            const float base_m = m_used == -INFINITY ? 0.0f : m_used;
-            // P buffer `buffer` is free once P V (j - 2) has completed
-            if (j >= 2) {
-                ok = mbar_wait(bars + (kBarPFree + buffer) * 8, ((j - 2) >> 1) & 1);
-                if (__any_sync(0xffffffffu, !ok)) break;
-            }
-            uint8_t *p_tile = base + kOffP + buffer * kTileBytes;
-            float sum = 0.0f;
+            const float neg_base = m_used == -INFINITY ? 0.0f : -m_used;
+            uint8_t *p_row = base + kOffP;
+            float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-            for (int chunk = 0; chunk < 16; ++chunk) {
+            for (int chunk = 0; chunk < kBlockTokens / 8; ++chunk) {
                 float p[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    p[i] = fast_exp2(s[chunk * 8 + i] - base_m);
-                    sum += p[i];
-                }
-                *reinterpret_cast<uint4 *>(p_tile + tile_chunk_offset(tid, chunk)) =
+                for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[chunk * 8 + i], scale, neg_base));
+                sum0 += (p[0] + p[1]) + (p[2] + p[3]);
+                sum1 += (p[4] + p[5]) + (p[6] + p[7]);
+                *reinterpret_cast<uint4 *>(p_row + swizzled(tid, chunk)) =
                     make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
                                pack_bf16(p[6], p[7]));
             }
-            l += sum;
+            l += sum0 + sum1;
             // rows of the request's last page past its length may hold anything (0 * NaN): zero
             // them in the V block before the MMA reads it
             const int last_page = num_pages - 1;
             if (tail < kPage && last_page / kBlockPages == j && last_page < cnt) {
                 ok = mbar_wait(bars + (kBarVFull + (j & 1)) * 8, (j >> 1) & 1);
                 if (__any_sync(0xffffffffu, !ok)) break;
-                uint8_t *v_page = base + kOffV + (j & 1) * kTileBytes + (last_page % kBlockPages) * 4096;
+                uint8_t *v_page =
+                    base + kOffV + (j & 1) * kVStageBytes + (last_page % kBlockPages) * 4096;
                 for (int i = tid; i < (kPage - tail) * 16; i += kTileRows) {
                     const int row = tail + (i >> 4), c = i & 15;
                     *reinterpret_cast<uint4 *>(v_page + (c >> 3) * 2048 + row * 128 + (c & 7) * 16) =
@@ -436,13 +451,13 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             fence_proxy_async(); // P (and the zeroed V rows) become visible to the MMA
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + (kBarPFull + buffer) * 8);
+            if (lane == 0) mbar_arrive(bars + kBarPFull * 8);
         }
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) misc[2] = 1;
         } else {
             // every P V has completed once the last one has
-            ok = mbar_wait(bars + (kBarPFree + ((blocks - 1) & 1)) * 8, ((blocks - 1) >> 1) & 1);
+            ok = mbar_wait(bars + kBarPFree * 8, (blocks - 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
             } else {
@@ -482,8 +497,13 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
 
 int configure_prefill_tiled_kernel(size_t max_dynamic_shared) {
     if ((size_t)kSharedBytes > max_dynamic_shared) return cudaErrorInvalidValue;
+    int rc = cudaFuncSetAttribute(paged_prefill_tiled_kernel,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedBytes);
+    if (rc) return rc;
+    // two CTAs per SM need the largest shared-memory carve-out
     return cudaFuncSetAttribute(paged_prefill_tiled_kernel,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedBytes);
+                                cudaFuncAttributePreferredSharedMemoryCarveout,
+                                cudaSharedmemCarveoutMaxShared);
 }
 
 int prefill_tiled_shared_bytes() { return kSharedBytes; }
