@@ -121,6 +121,31 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 64 consecutive F32 columns of this thread's TMEM lane: two loads in flight, one wait, all in one
+// statement so that no use of the destination registers can be scheduled before the wait.
+__device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]),
+          "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]),
+          "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+          "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]),
+          "=r"(r[63])
+        : "r"(taddr), "r"(taddr + 32)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_store32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
@@ -274,22 +299,27 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 }
             }
             const int pages_here = min(kBlockPages, cnt - j * kBlockPages);
-            bool ok = true;
-            if (j >= kStages) {
-                ok = mbar_wait(bars + (kBarKEmpty + stage) * 8, parity_prev);
-                ok = mbar_wait(bars + (kBarVEmpty + stage) * 8, parity_prev) && ok;
-            }
+            // The K stage is handed back when S(j - 2) has completed, the V stage only when
+            // P V (j - 2) has, a whole softmax later: K goes out first, so that the scores of
+            // block j never wait for their keys.
+            bool ok = j < kStages || mbar_wait(bars + (kBarKEmpty + stage) * 8, parity_prev);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
                 break;
             }
             if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_here * 4096);
-            if (lane == 8) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
             __syncwarp();
             if (has && is_k)
                 tma_load_3d(base_u32 + kOffK + stage * kKStageBytes + half * kKHalfBytes + slot * 2048,
                             &k_half_map, 0, page_id * kPage, kv_head * 2 + half,
                             bars + (kBarKFull + stage) * 8);
+            ok = j < kStages || mbar_wait(bars + (kBarVEmpty + stage) * 8, parity_prev);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) misc[2] = 1;
+                break;
+            }
+            if (lane == 8) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
+            __syncwarp();
             if (has && !is_k)
                 tma_load_3d(base_u32 + kOffV + stage * kVStageBytes + slot * 4096, &v_map, 0,
                             page_id * kPage, kv_head * 2, bars + (kBarVFull + stage) * 8);
@@ -366,15 +396,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
             float s[kBlockTokens]; // raw dot products
-            {
-                float part[32];
-                tmem_load32(tmem_s + lane_base, part);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[i] = part[i];
-                tmem_load32(tmem_s + lane_base + 32, part);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
-            }
+            tmem_load64(tmem_s + lane_base, s);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + kBarSFree * 8); // S may be overwritten by block j + 1
