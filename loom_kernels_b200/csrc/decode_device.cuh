@@ -18,6 +18,7 @@
 // of the kernels; in the product it expands to nothing.
 #ifndef LB_STAMP
 #define LB_STAMP(slot)
+#define LB_STAMPV(slot, value)
 #endif
 
 namespace lb {

@@ -48,19 +48,18 @@ constexpr int kQBytes = 2 * kQHalfBytes;       // 32 KB
 constexpr int kKHalfBytes = kBlockTokens * 128; // 64 dims of the block's token rows
 constexpr int kKStageBytes = 2 * kKHalfBytes;  // 16 KB
 constexpr int kVStageBytes = kBlockPages * 4096; // 16 KB: per page [half][16 tokens][64 dims]
-constexpr int kPBytes = kTileRows * 128;       // 16 KB: 64 tokens (128 bytes) of the 128 rows
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemColumns = 256;         // a power of two >= 64 (S) + 128 (O)
-constexpr uint32_t kTmemS = 0, kTmemO = 64;
+constexpr uint32_t kTmemColumns = 256;         // a power of two >= 64 (S) + 32 (P) + 128 (O)
+constexpr uint32_t kTmemS = 0, kTmemP = 64, kTmemO = 96;
 constexpr float kRescaleThreshold = 8.0f;      // log2 domain: P stays below 2^8
+constexpr int kProbeBlock = 20;                // the block a profiling build stamps (LB_STAMP)
 
 // shared-memory map (offsets from the 1024-byte aligned base of dynamic shared memory)
 constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKStageBytes;
-constexpr int kOffP = kOffV + kStages * kVStageBytes;
-constexpr int kOffBars = kOffP + kPBytes;
+constexpr int kOffBars = kOffV + kStages * kVStageBytes;
 // barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full p_free verdict
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
               kBarSFree = 9, kBarPFull = 10, kBarPFree = 11, kBarVerdict = 12, kNumBars = 13;
@@ -95,6 +94,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
                  "setp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
                  "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 16 BF16 (8 columns, two elements per column).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
 // The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
@@ -274,6 +282,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     tc_fence_after();
     const uint32_t tmem_base = misc[0];
     const uint32_t tmem_s = tmem_base + kTmemS; // scores of the block at hand
+    const uint32_t tmem_p = tmem_base + kTmemP; // BF16 weights of the block, two per column
     const uint32_t tmem_o = tmem_base + kTmemO; // output accumulator
 
     if (warp == 4) {
@@ -307,6 +316,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 if (lane == 0) misc[2] = 1;
                 break;
             }
+            if (j == kProbeBlock) LB_STAMP(8);
             if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_here * 4096);
             __syncwarp();
             if (has && is_k)
@@ -318,6 +328,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 if (lane == 0) misc[2] = 1;
                 break;
             }
+            if (j == kProbeBlock) LB_STAMP(9);
             if (lane == 8) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
             __syncwarp();
             if (has && !is_k)
@@ -344,13 +355,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             ok = mbar_wait(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
             if (!ok) return false;
             tc_fence_after();
+            if (i == kProbeBlock) LB_STAMP(7);
             if (lane == 0) {
                 const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
                 for (int p = 0; p < pages_here; ++p) {
-                    const uint64_t a_desc = smem_desc(base_u32 + kOffP + p * 32, 16, 1024);
                     const uint64_t b_desc =
                         smem_desc(base_u32 + kOffV + stage * kVStageBytes + p * 4096, 2048, 1024);
-                    umma_bf16(tmem_o, a_desc, b_desc, kIdescPV, (i > 0 || p > 0) ? 1u : 0u);
+                    umma_bf16_ts(tmem_o, tmem_p + p * 8, b_desc, kIdescPV,
+                                 (i > 0 || p > 0) ? 1u : 0u);
                 }
                 umma_commit(bars + kBarPFree * 8);
                 umma_commit(bars + (kBarVEmpty + stage) * 8);
@@ -365,6 +377,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (ok && j > 0) ok = mbar_wait(bars + kBarSFree * 8, (j - 1) & 1);
             if (!ok) break;
             tc_fence_after();
+            if (j == kProbeBlock) LB_STAMP(6);
+            if (j == kProbeBlock + 1) LB_STAMP(11);
             if (lane == 0) {
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
@@ -395,10 +409,13 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             ok = mbar_wait(bars + kBarSFull * 8, j & 1);
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
+            if (j == kProbeBlock) LB_STAMP(0);
+            if (j == kProbeBlock + 1) LB_STAMP(10);
             float s[kBlockTokens]; // raw dot products
             tmem_load64(tmem_s + lane_base, s);
             tc_fence_before();
             __syncwarp();
+            if (j == kProbeBlock) LB_STAMP(1);
             if (lane == 0) mbar_arrive(bars + kBarSFree * 8); // S may be overwritten by block j + 1
             // the row's causal limit inside this block; columns past it (which also covers stale
             // or garbage key rows) are masked.  Most blocks lie wholly below the limit.
@@ -414,12 +431,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 mx1 = fmaxf(mx1, s[i + 1]);
             }
             const float mx = fmaxf(mx0, mx1) * scale; // scale > 0; -inf stays -inf
+            if (j == kProbeBlock) LB_STAMPV(2, mx);
             // O holds blocks 0..j-1 and P is free once P V (j - 1) has completed
             if (j > 0) {
                 ok = mbar_wait(bars + kBarPFree * 8, (j - 1) & 1);
                 if (__any_sync(0xffffffffu, !ok)) break;
                 tc_fence_after();
             }
+            if (j == kProbeBlock) LB_STAMP(3);
             // the exponent base follows the maximum lazily: P <= 2^8 keeps BF16 P and the F32
             // normaliser exact enough, and most blocks skip the TMEM round trip of O
             const bool rescale = mx > m_used + kRescaleThreshold ||
@@ -442,8 +461,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 }
             }
             const float neg_base = m_used == -INFINITY ? 0.0f : -m_used;
-            uint8_t *p_row = base + kOffP;
             float sum0 = 0.0f, sum1 = 0.0f;
+            float packed[kBlockTokens / 2]; // BF16 pairs (token 2c in the low half), as raw bits
 #pragma unroll
             for (int chunk = 0; chunk < kBlockTokens / 8; ++chunk) {
                 float p[8];
@@ -451,15 +470,19 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[chunk * 8 + i], scale, neg_base));
                 sum0 += (p[0] + p[1]) + (p[2] + p[3]);
                 sum1 += (p[4] + p[5]) + (p[6] + p[7]);
-                *reinterpret_cast<uint4 *>(p_row + swizzled(tid, chunk)) =
-                    make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]),
-                               pack_bf16(p[6], p[7]));
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    packed[chunk * 4 + i] = __uint_as_float(pack_bf16(p[2 * i], p[2 * i + 1]));
             }
+            tmem_store32(tmem_p + lane_base, packed);
+            tmem_store_wait();
             l += sum0 + sum1;
+            if (j == kProbeBlock) LB_STAMPV(4, l);
             // rows of the request's last page past its length may hold anything (0 * NaN): zero
             // them in the V block before the MMA reads it
             const int last_page = num_pages - 1;
-            if (tail < kPage && last_page / kBlockPages == j && last_page < cnt) {
+            const bool zero_tail = tail < kPage && last_page / kBlockPages == j && last_page < cnt;
+            if (zero_tail) {
                 ok = mbar_wait(bars + (kBarVFull + (j & 1)) * 8, (j >> 1) & 1);
                 if (__any_sync(0xffffffffu, !ok)) break;
                 uint8_t *v_page =
@@ -470,10 +493,11 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                         make_uint4(0, 0, 0, 0);
                 }
             }
-            fence_proxy_async(); // P (and the zeroed V rows) become visible to the MMA
+            if (zero_tail) fence_proxy_async(); // the zeroed V rows become visible to the MMA
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + kBarPFull * 8);
+            if (j == kProbeBlock) LB_STAMP(5);
         }
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) misc[2] = 1;
