@@ -24,8 +24,8 @@
 //   pipelining = K and V blocks are double-buffered by TMA; the S MMAs of block j + 1 are issued
 //                before the P V MMAs of block j, so the next scores are ready when the softmax
 //                warps finish the current block.
-//   shared mem = Q 32 KB | K 2 x 16 KB | V 2 x 16 KB | P 16 KB | barriers
-//   TMEM       = 256 columns allocated: S (64 x F32) | O (128 x F32)
+//   shared mem = Q 32 KB | K 2 x 16 KB | V 2 x 16 KB | barriers
+//   TMEM       = 256 columns: S (64 x F32) | P (2 x 32 columns of BF16 pairs) | O (128 x F32)
 //
 // Device-resident metadata is never an error (prefill.rs:289-347).  Every mbarrier wait is bounded;
 // after a timeout every role leaves its loop, the CTA frees its TMEM, records a status word and
@@ -50,8 +50,8 @@ constexpr int kKStageBytes = 2 * kKHalfBytes;  // 16 KB
 constexpr int kVStageBytes = kBlockPages * 4096; // 16 KB: per page [half][16 tokens][64 dims]
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemColumns = 256;         // a power of two >= 64 (S) + 32 (P) + 128 (O)
-constexpr uint32_t kTmemS = 0, kTmemP = 64, kTmemO = 96;
+constexpr uint32_t kTmemColumns = 256;         // 64 (S) + 2 x 32 (P, double-buffered) + 128 (O)
+constexpr uint32_t kTmemS = 0, kTmemP = 64, kTmemO = 128;
 constexpr float kRescaleThreshold = 8.0f;      // log2 domain: P stays below 2^8
 constexpr int kProbeBlock = 20;                // the block a profiling build stamps (LB_STAMP)
 
@@ -60,12 +60,24 @@ constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKStageBytes;
 constexpr int kOffBars = kOffV + kStages * kVStageBytes;
-// barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full p_free verdict
+// barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full[2] p_free[2] verdict
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
-              kBarSFree = 9, kBarPFull = 10, kBarPFree = 11, kBarVerdict = 12, kNumBars = 13;
+              kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kNumBars = 15;
 constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
 constexpr int kSharedBytes = kOffMisc + 24;
 static_assert(2 * (kSharedBytes + 1024) <= 233472, "two CTAs must fit one SM");
+
+// True in exactly one lane of a converged warp.  Unlike a test of the lane id, elect.sync tells the
+// compiler that the guarded code runs in one thread of a converged warp, so the operands of the
+// MMA and TMA instructions issued there can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected = 0;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "elect.sync _|p, 0xffffffff;\n\t"
+                 "@p mov.u32 %0, 1;\n\t}"
+                 : "+r"(elected));
+    return elected != 0;
+}
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------
 
@@ -220,7 +232,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i)
-            mbar_init(bars + i * 8, i == kBarSFree || i == kBarPFull ? 4 : 1);
+            mbar_init(bars + i * 8,
+                      i == kBarSFree || i == kBarPFull || i == kBarPFull + 1 ? 4 : 1);
         fence_barrier_init();
         misc[1] = 0;
         misc[2] = 0;
@@ -294,46 +307,75 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         const int half = lane & 1;
         const bool lane_active = lane < 12;
         bool bad_page = false;
+        // Page ids travel in windows of 32 (one per lane): win0 holds the window of the block whose
+        // values are loaded next, win1 the one after it, fetched a whole window ahead, so that no
+        // load of the page table sits between a barrier and the TMA it releases.  An id out of
+        // range is replaced by page 0 when it is used and poisons the request.
+        auto load_window = [&](int w) -> int {
+            const int page = w * 32 + lane;
+            return page < cnt ? a.indices[page_start + page] : 0;
+        };
+        int first_window = 0;
+        int win0 = load_window(0), win1 = load_window(1);
+        auto id_of_page = [&](int page) -> int {
+            const int from0 = __shfl_sync(0xffffffffu, win0, page & 31);
+            const int from1 = __shfl_sync(0xffffffffu, win1, page & 31);
+            const int id = (page >> 5) == first_window ? from0 : from1;
+            if (id < 0 || id >= a.max_pages) {
+                bad_page = true;
+                return 0;
+            }
+            return id;
+        };
+        auto pages_in = [&](int block) { return min(kBlockPages, cnt - block * kBlockPages); };
+        auto load_k = [&](int block, int id) {
+            const int stage = block & 1;
+            if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_in(block) * 4096);
+            __syncwarp();
+            if (is_k && block * kBlockPages + slot < cnt)
+                tma_load_3d(base_u32 + kOffK + stage * kKStageBytes + half * kKHalfBytes + slot * 2048,
+                            &k_half_map, 0, id * kPage, kv_head * 2 + half,
+                            bars + (kBarKFull + stage) * 8);
+        };
+        auto load_v = [&](int block, int id) {
+            const int stage = block & 1;
+            if (lane == 8) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_in(block) * 4096);
+            __syncwarp();
+            if (lane_active && !is_k && block * kBlockPages + slot < cnt)
+                tma_load_3d(base_u32 + kOffV + stage * kVStageBytes + slot * 4096, &v_map, 0,
+                            id * kPage, kv_head * 2, bars + (kBarVFull + stage) * 8);
+        };
+        // Keys run two blocks ahead of the scores that consume them, values follow the P V MMAs:
+        // iteration j loads V(j) as soon as P V (j - 2) has freed its stage and K(j + 2) as soon
+        // as S(j) has -- the order in which the MMA warp completes them.
+        const int k_slot = lane >> 1, v_slot = lane - 8; // the page of a block this lane loads
+        load_k(0, id_of_page(k_slot));
+        if (blocks > 1) load_k(1, id_of_page(kBlockPages + k_slot));
         for (int j = 0; j < blocks; ++j) {
             const int stage = j & 1;
-            const uint32_t parity_prev = ((j >> 1) + 1) & 1; // parity of the previous use's release
-            const int page = j * kBlockPages + slot;
-            const bool has = lane_active && page < cnt;
-            int page_id = 0;
-            if (has) {
-                page_id = a.indices[page_start + page];
-                if (page_id < 0 || page_id >= a.max_pages) {
-                    bad_page = true;
-                    page_id = 0;
-                }
-            }
-            const int pages_here = min(kBlockPages, cnt - j * kBlockPages);
-            // The K stage is handed back when S(j - 2) has completed, the V stage only when
-            // P V (j - 2) has, a whole softmax later: K goes out first, so that the scores of
-            // block j never wait for their keys.
-            bool ok = j < kStages || mbar_wait(bars + (kBarKEmpty + stage) * 8, parity_prev);
-            if (__any_sync(0xffffffffu, !ok)) {
-                if (lane == 0) misc[2] = 1;
-                break;
-            }
-            if (j == kProbeBlock) LB_STAMP(8);
-            if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_here * 4096);
-            __syncwarp();
-            if (has && is_k)
-                tma_load_3d(base_u32 + kOffK + stage * kKStageBytes + half * kKHalfBytes + slot * 2048,
-                            &k_half_map, 0, page_id * kPage, kv_head * 2 + half,
-                            bars + (kBarKFull + stage) * 8);
-            ok = j < kStages || mbar_wait(bars + (kBarVEmpty + stage) * 8, parity_prev);
+            const int v_id = id_of_page(j * kBlockPages + v_slot);
+            const int k_id = id_of_page((j + 2) * kBlockPages + k_slot);
+            bool ok = j < kStages || mbar_wait(bars + (kBarVEmpty + stage) * 8, ((j >> 1) + 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
                 break;
             }
             if (j == kProbeBlock) LB_STAMP(9);
-            if (lane == 8) mbar_expect_tx(bars + (kBarVFull + stage) * 8, pages_here * 4096);
-            __syncwarp();
-            if (has && !is_k)
-                tma_load_3d(base_u32 + kOffV + stage * kVStageBytes + slot * 4096, &v_map, 0,
-                            page_id * kPage, kv_head * 2, bars + (kBarVFull + stage) * 8);
+            load_v(j, v_id);
+            if (j + 2 < blocks) {
+                ok = mbar_wait(bars + (kBarKEmpty + stage) * 8, (j >> 1) & 1); // S(j) has completed
+                if (__any_sync(0xffffffffu, !ok)) {
+                    if (lane == 0) misc[2] = 1;
+                    break;
+                }
+                if (j + 2 == kProbeBlock) LB_STAMP(8);
+                load_k(j + 2, k_id);
+            }
+            if ((((j + 1) * kBlockPages) >> 5) != first_window) { // the values enter the next window
+                ++first_window;
+                win0 = win1;
+                win1 = load_window(first_window + 1);
+            }
         }
         // the reference validates every page of the request, also those past the causal limit of
         // a row (prefill.rs:333-340): the pages this CTA does not stream are range-checked
@@ -349,22 +391,28 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         // ================= MMA issue =================================================================
         // order: S(0), S(1), PV(0), S(2), PV(1), ... so that the scores of the next block are ready
         // when the softmax warps finish the current one
+        // descriptors of the first tile of each operand; the others differ in the start address
+        // field only (bytes >> 4, no carry out of its 14 bits inside shared memory)
+        const uint64_t q_desc0 = smem_desc(base_u32 + kOffQ, 16, 1024);
+        const uint64_t k_desc0 = smem_desc(base_u32 + kOffK, 16, 1024);
+        const uint64_t v_desc0 = smem_desc(base_u32 + kOffV, 2048, 1024);
         auto issue_pv = [&](int i) -> bool {
-            const int stage = i & 1;
-            bool ok = mbar_wait(bars + kBarPFull * 8, i & 1);
+            const int stage = i & 1, buffer = i & 1;
+            bool ok = mbar_wait(bars + (kBarPFull + buffer) * 8, (i >> 1) & 1);
             ok = mbar_wait(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
             if (!ok) return false;
             tc_fence_after();
             if (i == kProbeBlock) LB_STAMP(7);
-            if (lane == 0) {
-                const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
-                for (int p = 0; p < pages_here; ++p) {
-                    const uint64_t b_desc =
-                        smem_desc(base_u32 + kOffV + stage * kVStageBytes + p * 4096, 2048, 1024);
-                    umma_bf16_ts(tmem_o, tmem_p + p * 8, b_desc, kIdescPV,
-                                 (i > 0 || p > 0) ? 1u : 0u);
+            const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
+            if (elect_one()) {
+#pragma unroll
+                for (int p = 0; p < kBlockPages; ++p) {
+                    if (p < pages_here)
+                        umma_bf16_ts(tmem_o, tmem_p + buffer * 32 + p * 8,
+                                     v_desc0 + (uint64_t)((stage * kVStageBytes + p * 4096) >> 4),
+                                     kIdescPV, (i > 0 || p > 0) ? 1u : 0u);
                 }
-                umma_commit(bars + kBarPFree * 8);
+                umma_commit(bars + (kBarPFree + buffer) * 8);
                 umma_commit(bars + (kBarVEmpty + stage) * 8);
             }
             __syncwarp();
@@ -379,16 +427,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             tc_fence_after();
             if (j == kProbeBlock) LB_STAMP(6);
             if (j == kProbeBlock + 1) LB_STAMP(11);
-            if (lane == 0) {
+            if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint64_t a_desc = smem_desc(
-                        base_u32 + kOffQ + (kk >> 2) * kQHalfBytes + (kk & 3) * 32, 16, 1024);
-                    const uint64_t b_desc = smem_desc(base_u32 + kOffK + stage * kKStageBytes +
-                                                          (kk >> 2) * kKHalfBytes + (kk & 3) * 32,
-                                                      16, 1024);
-                    umma_bf16(tmem_s, a_desc, b_desc, kIdescQK, kk > 0 ? 1u : 0u);
-                }
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_bf16(tmem_s,
+                              q_desc0 + (uint64_t)(((kk >> 2) * kQHalfBytes + (kk & 3) * 32) >> 4),
+                              k_desc0 + (uint64_t)((stage * kKStageBytes + (kk >> 2) * kKHalfBytes +
+                                                    (kk & 3) * 32) >> 4),
+                              kIdescQK, kk > 0 ? 1u : 0u);
                 umma_commit(bars + kBarSFull * 8);
                 umma_commit(bars + (kBarKEmpty + stage) * 8);
             }
@@ -432,12 +478,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             }
             const float mx = fmaxf(mx0, mx1) * scale; // scale > 0; -inf stays -inf
             if (j == kProbeBlock) LB_STAMPV(2, mx);
-            // O holds blocks 0..j-1 and P is free once P V (j - 1) has completed
-            if (j > 0) {
-                ok = mbar_wait(bars + kBarPFree * 8, (j - 1) & 1);
-                if (__any_sync(0xffffffffu, !ok)) break;
-                tc_fence_after();
-            }
             if (j == kProbeBlock) LB_STAMP(3);
             // the exponent base follows the maximum lazily: P <= 2^8 keeps BF16 P and the F32
             // normaliser exact enough, and most blocks skip the TMEM round trip of O
@@ -449,6 +489,10 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 l *= alpha;
                 m_used = m_new;
                 if (j > 0) {
+                    // O holds blocks 0..j-1 once P V (j - 1) has completed
+                    ok = mbar_wait(bars + (kBarPFree + ((j - 1) & 1)) * 8, ((j - 1) >> 1) & 1);
+                    if (__any_sync(0xffffffffu, !ok)) break;
+                    tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         float part[32];
@@ -461,6 +505,13 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 }
             }
             const float neg_base = m_used == -INFINITY ? 0.0f : -m_used;
+            // the weights are double-buffered: this buffer is free once P V (j - 2) has completed,
+            // which it has long before (the wait costs one look at the barrier)
+            if (j >= 2) {
+                ok = mbar_wait(bars + (kBarPFree + (j & 1)) * 8, ((j - 2) >> 1) & 1);
+                if (__any_sync(0xffffffffu, !ok)) break;
+                tc_fence_after();
+            }
             float sum0 = 0.0f, sum1 = 0.0f;
             float packed[kBlockTokens / 2]; // BF16 pairs (token 2c in the low half), as raw bits
 #pragma unroll
@@ -474,7 +525,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 for (int i = 0; i < 4; ++i)
                     packed[chunk * 4 + i] = __uint_as_float(pack_bf16(p[2 * i], p[2 * i + 1]));
             }
-            tmem_store32(tmem_p + lane_base, packed);
+            tmem_store32(tmem_p + (j & 1) * 32 + lane_base, packed);
             tmem_store_wait();
             l += sum0 + sum1;
             if (j == kProbeBlock) LB_STAMPV(4, l);
@@ -496,14 +547,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (zero_tail) fence_proxy_async(); // the zeroed V rows become visible to the MMA
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + kBarPFull * 8);
+            if (lane == 0) mbar_arrive(bars + (kBarPFull + (j & 1)) * 8);
             if (j == kProbeBlock) LB_STAMP(5);
         }
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) misc[2] = 1;
         } else {
             // every P V has completed once the last one has
-            ok = mbar_wait(bars + kBarPFree * 8, (blocks - 1) & 1);
+            ok = mbar_wait(bars + (kBarPFree + ((blocks - 1) & 1)) * 8, ((blocks - 1) >> 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
             } else {
