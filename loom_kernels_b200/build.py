@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libloom_b200.so")
 SOURCES = ["errors.cpp", "contract.cpp", "driver.cpp", "command.cpp", "graph.cpp",
            "providers.cpp", "prefill_provider.cpp", "prefill_kernels.cu", "prefill_tiled_kernel.cu", "decode_kernels.cu", "decode_stream_kernel.cu", "append_kernels.cu", "static_scratch.cu"]
-HEADERS = ["runtime.hpp", "kernels.hpp", "decode_device.cuh", "dependent_launch.cuh", "prefill_device.cuh", os.path.join(ROOT, "include", "loom_b200.h")]
+HEADERS = ["runtime.hpp", "kernels.hpp", "decode_device.cuh", "dependent_launch.cuh", "prefill_device.cuh", "tcgen05_device.cuh", os.path.join(ROOT, "include", "loom_b200.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-x", "cu",

@@ -34,6 +34,7 @@
 
 #include "kernels.hpp"
 #include "prefill_device.cuh"
+#include "tcgen05_device.cuh"
 
 namespace lb {
 namespace {
@@ -67,149 +68,8 @@ constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
 constexpr int kSharedBytes = kOffMisc + 24;
 static_assert(2 * (kSharedBytes + 1024) <= 233472, "two CTAs must fit one SM");
 
-// True in exactly one lane of a converged warp.  Unlike a test of the lane id, elect.sync tells the
-// compiler that the guarded code runs in one thread of a converged warp, so the operands of the
-// MMA and TMA instructions issued there can live in uniform registers.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t elected = 0;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "elect.sync _|p, 0xffffffff;\n\t"
-                 "@p mov.u32 %0, 1;\n\t}"
-                 : "+r"(elected));
-    return elected != 0;
-}
-
-// ---- tcgen05 wrappers ------------------------------------------------------------------------------
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
-                 "r"(columns)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]; one thread issues.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-                 : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 16 BF16 (8 columns, two elements per column).
-__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                             uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-                 : "memory");
-}
-// The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                     bar)
-                 : "memory");
-}
-// 32 consecutive F32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-// 64 consecutive F32 columns of this thread's TMEM lane: two loads in flight, one wait, all in one
-// statement so that no use of the destination registers can be scheduled before the wait.
-__device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
-    uint32_t r[64];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]),
-          "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]),
-          "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
-          "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
-          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]),
-          "=r"(r[63])
-        : "r"(taddr), "r"(taddr + 32)
-        : "memory");
-#pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_store32(uint32_t taddr, const float (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};" ::"r"(
-            __float_as_uint(v[0])),
-        "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
-        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])),
-        "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])),
-        "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
-        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])),
-        "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])),
-        "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
-        "r"(__float_as_uint(v[31])), "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_store_wait() {
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, tiles aligned to 1024 bytes.
-//   K-major operand (Q, K block, P): rows of 128 bytes, 8-row groups `sbo` bytes apart; a K step of
-//   16 elements is 32 bytes inside the row, reached by advancing the start address.
-//   MN-major operand (V page): rows of 128 bytes = 64 contiguous MN elements of one K index,
-//   8-row K groups `sbo` bytes apart, the next 64 MN elements `lbo` bytes away.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((address & 0x3ffffu) >> 4) | ((uint64_t)(lbo >> 4) << 16) |
-           ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: F32 accumulator, BF16 A and B, M = 128, A K-major.
-constexpr uint32_t idesc(uint32_t n, bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? 1u << 16 : 0u) | ((n >> 3) << 17) |
-           ((128u >> 4) << 24);
-}
 constexpr uint32_t kIdescQK = idesc(kBlockTokens, false); // B = K block, K-major, N = 64 tokens
 constexpr uint32_t kIdescPV = idesc(kHeadDim, true);      // B = V page, MN-major, N = 128 dims
-
-// 16-byte chunk `chunk` of 128-byte-swizzled row `row` (one 128-byte column half of a tile).
-__device__ __forceinline__ uint32_t swizzled(int row, int chunk) {
-    return row * 128 + ((chunk ^ (row & 7)) << 4);
-}
 
 __global__ void __launch_bounds__(kThreads, 2)
 paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
