@@ -155,3 +155,19 @@ def test_fixed_address_graph_replays(provider, oracle):
         check(H.host_bits(out), lse.cpu().numpy(), expected, expected_lse)
     assert provider.device_status() == 0
     exec_.into_bindings()
+
+
+def test_chunk_after_a_long_cache(provider, oracle):
+    """Chunked prefill at serving shape: a few hundred new queries over thousands of cached tokens
+    (many blocks per tile, page-id windows refilled several times, no block crosses the causal
+    limit until the last ones), against the oracle."""
+    rng = np.random.default_rng(51)
+    qo_lens, kv_lens = [130, 40], [5000, 2177]
+    qh, kvh, pool = 16, 4, 460
+    case = ragged_case(rng, qo_lens, kv_lens, qh, kvh, pool)
+    dims = (2, sum(qo_lens), pool, qh, kvh)
+    expected, expected_lse = oracle.paged_prefill(oracle.prefill_spec(*dims), *case, threads=16)
+    for algorithm in (TILED, 1):
+        actual, actual_lse = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(*dims), *case,
+                                        algorithm=algorithm).run()
+        check(actual, actual_lse, expected, expected_lse, gate=False)

@@ -94,7 +94,7 @@ def test_launch_shape_is_fixed_by_spec_and_device():
     short = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(2, 96, 96, 16, 4), 148)
     assert (short.q_tiles, short.pages_per_stage, short.rows_per_cta, short.commands) == (1, 8, 16, 1)
     assert short.tiles == 96 * 4 // 16 + 2 and short.grid == short.tiles * 4 and short.block == 288
-    # a long prompt: the tensor-core kernel, 128-row tiles and 128-token blocks
+    # a long prompt: the tensor-core kernel, 128-row tiles and 64-token blocks
     prompt = lk.Bf16PagedPrefillSpec.new(1, 8192, 600, 32, 8)
     tiled = lk.choose_paged_prefill(prompt, 148)
     assert tiled.algorithm == lk.Bf16PagedPrefillAlgorithm.Tiled
