@@ -2,7 +2,7 @@
 """Benchmark of the paged-decode hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c3|c1|c4|c5]
+                    [--workload c3|c1|c4|c5|prefill]
 
 One step = one paged decode call over one batch of seeded synthetic input.  At N=1 the workload is
 batch-64 GQA4 32/8-head decode at context 4096 with pages scattered in a 20000-page pool, direct
@@ -11,6 +11,8 @@ owns its own shard of requests and of the paged KV cache (same per-GPU shape, we
 decode path has no exchange step, so the timed region contains no collective.  The optional
 all-gather of output rows is timed separately and reported under "allgather".  `--workload c5`
 is the strong-scaling case instead: one ragged 512-request MQA + GQA4 batch split over the ranks.
+`--workload prefill` measures the step before decode (paged causal prefill of one 8192-token
+prompt per GPU) in TFLOP/s against the measured BF16 GEMM throughput.
 
 `value` is aggregate algorithmic bytes per second with inputs resident in HBM; `e2e` is the same
 metric through the public API with host buffers (pinned host -> device copy of the step's Q and
@@ -114,6 +116,9 @@ def reference_arm(args):
     from oracle import oracle
     oracle.build()
     threads = os.cpu_count() or 1
+    if args.workload == "prefill":
+        raise SystemExit("--impl reference covers the decode workloads; the prefill line carries "
+                         "its own cpu_baseline")
     w = build_workload(args.workload, 0, args.batch)
     # bounded sample: the first `sample` requests of the workload (whole requests, all heads)
     sample = min(w.batch, args.reference_requests)
@@ -587,13 +592,128 @@ def ragged_c5(args):
         dist.destroy_process_group()
 
 
+def prefill_workload(args):
+    """`--workload prefill`: the step before decode on the same pools (built after the decode
+    rows).  One step = paged causal prefill of one seeded 8192-token prompt (32 query / 8 KV heads)
+    per GPU; the metric is causal FLOPs (4 * 128 per visible (query, key) pair and query head) per
+    second against the measured BF16 GEMM throughput.  Same line format as the decode workloads."""
+    import torch
+    import torch.distributed as dist
+
+    import loom_kernels_b200 as lk
+    from loom_kernels_b200.prefill_bench import PrefillCase, tensor_peak_tflops
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    tokens, qh, kvh = 8192, 32, 8
+    provider = lk.PrefillProvider.load(local_rank)
+    case = PrefillCase(provider, "prompt", [tokens], [tokens], qh, kvh, device, seed=0xF3 + rank)
+    stream = torch.cuda.Stream(device=device)
+    queue = lk.CommandQueue(stream, 1)
+    host_q = case.q.cpu().pin_memory()
+    host_meta = [m.cpu().pin_memory() for m in case.meta]
+    host_out = torch.empty_like(case.out, device="cpu").pin_memory()
+
+    def step(copies: bool):
+        if copies:
+            with torch.cuda.stream(stream):
+                case.q.copy_(host_q, non_blocking=True)
+                for dst, src in zip(case.meta, host_meta):
+                    dst.copy_(src, non_blocking=True)
+        b = queue.bindings(9)
+        reads = [b.bind_read(t) for t in (case.q, case.k, case.v, *case.meta)]
+        out, lse = b.bind_read_write(case.out), b.bind_read_write(case.lse)
+        scope = queue.begin(b)
+        case.plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, out.write(), lse.write()))
+        scope.finish().wait()
+        if copies:
+            with torch.cuda.stream(stream):
+                host_out.copy_(case.out, non_blocking=True)
+            stream.synchronize()
+
+    def timed(copies: bool):
+        for _ in range(args.warmup):
+            step(copies)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(args.steps):
+            step(copies)
+        end.record(stream)
+        torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(end)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / args.steps
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed(False)
+    clocks = sampler.stop()
+    ms_e2e = timed(True)
+    status = provider.device_status()
+    flops = case.flops()
+    peak, peak_kind = tensor_peak_tflops()
+    if rank == 0:
+        # CPU leg: the oracle on the last 8 query tokens of the prompt (all heads, whole context)
+        from oracle import oracle
+        rows = 8
+        pages = (tokens + 15) // 16
+        q_bits = host_q.view(torch.int16).numpy().view(np.uint16)[-rows * qh * 128:]
+        k_bits = case.k.cpu().view(torch.int16).numpy().view(np.uint16)
+        v_bits = case.v.cpu().view(torch.int16).numpy().view(np.uint16)
+        meta = [m.numpy() for m in host_meta]
+        ospec = oracle.prefill_spec(1, rows, case.spec.max_num_pages(), qh, kvh)
+        cores = os.cpu_count() or 1
+        begin = time.perf_counter()
+        oracle.paged_prefill(ospec, q_bits, k_bits, v_bits, [0, rows], meta[1], meta[2], meta[3],
+                             threads=cores)
+        cpu_s = time.perf_counter() - begin
+        cpu_flops = 4.0 * 128 * qh * sum(tokens - rows + i + 1 for i in range(rows))
+        tflops = flops * world / (ms * 1e-3) / 1e12
+        line = {
+            "metric": "paged_prefill_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"paged causal prefill, one {tokens}-token prompt per GPU, "
+                                   f"{qh}/{kvh} heads, page size 16, scattered pages",
+                       "algorithm": ["token_parallel", "tiled_tcgen05"][case.plan.algorithm()],
+                       "l2": "K/V of a prompt (33 MB) stay in L2; the operator is tensor-bound"},
+            "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak,
+                         "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / 1e12 / peak,
+                         "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "kernel": "paged_prefill_tiled_kernel"},
+            "cpu_baseline": {"value": cpu_flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": cores,
+                             "kind": "port",
+                             "sample": f"last {rows} query tokens of the prompt, all heads "
+                                       f"({cpu_flops / 1e9:.2f} GFLOP, {cpu_s * 1e3:.0f} ms)"},
+            "e2e": {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": int(host_q.numel() * 2 + sum(m.numel() * 4 for m in host_meta)),
+                    "d2h_bytes_per_step": int(host_out.numel() * 2)},
+            "clocks": clocks, "gpu_launches": args.steps, "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="c3", choices=["c1", "c3", "c4", "c5"])
+    parser.add_argument("--workload", default="c3", choices=["c1", "c3", "c4", "c5", "prefill"])
     parser.add_argument("--reference-requests", type=int, default=16)
     parser.add_argument("--shard", default="",
                         help="c5 only, 'N:r': time rank r's share of an N-way split on one GPU")
@@ -607,6 +727,8 @@ def main():
         reference_arm(args)
     elif args.workload == "c5":
         ragged_c5(args)
+    elif args.workload == "prefill":
+        prefill_workload(args)
     else:
         ours(args)
 
