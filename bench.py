@@ -645,10 +645,24 @@ def prefill_workload(args):
             dist.barrier()
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
-        for _ in range(args.steps):
-            step(copies)
-        end.record(stream)
+        if copies:
+            start.record(stream)
+            for _ in range(args.steps):
+                step(True)
+            end.record(stream)
+        else:
+            # the reference's protocol: every step of the timed region enqueued in one scope
+            batch_queue = lk.CommandQueue(stream, args.steps)
+            b = batch_queue.bindings(9)
+            reads = [b.bind_read(t) for t in (case.q, case.k, case.v, *case.meta)]
+            out, lse = b.bind_read_write(case.out), b.bind_read_write(case.lse)
+            call = lk.Bf16PagedPrefillArgs(*reads, out.write(), lse.write())
+            scope = batch_queue.begin(b)
+            start.record(stream)
+            for _ in range(args.steps):
+                case.plan.enqueue_into(scope, call)
+            end.record(stream)
+            scope.finish().wait()
         torch.cuda.synchronize()
         ms = torch.tensor([start.elapsed_time(end)], device=device)
         if world > 1:
