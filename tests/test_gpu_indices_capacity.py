@@ -109,3 +109,41 @@ def test_the_reference_rule_still_holds_without_the_option():
                       partitions=1)
     out, lse = run.run()
     assert np.all(np.isnan(H.bits_to_f32(out))) and np.all(np.isnan(lse))
+
+
+@pytest.mark.parametrize("algorithm", [1, 2])
+def test_prefill_accepts_a_longer_page_indices_binding(oracle, algorithm):
+    """The same option on the prefill plans: the table in use may be shorter than the bound
+    page_indices (the tail is never read); without the option such a call writes nothing."""
+    rng = np.random.default_rng(12)
+    qo_lens, kv_lens = [37, 5, 70], [90, 200, 70]
+    qo_indptr = np.concatenate([[0], np.cumsum(qo_lens)]).astype(np.int32)
+    indptr, indices, last = table_for(rng, kv_lens, ())
+    padded = np.concatenate([indices, np.full(11, -1, np.int32)])
+    nnz = int(qo_indptr[-1])
+    spec = lk.Bf16PagedPrefillSpec.new(3, nnz, POOL, QH, KVH)
+    q = H.normal_bf16(rng, spec.query_numel())
+    k, v = (H.normal_bf16(rng, spec.kv_pages_numel()) for _ in range(2))
+    expected, expected_lse = oracle.paged_prefill(oracle.prefill_spec(3, nnz, POOL, QH, KVH), q, k, v,
+                                                  qo_indptr, indptr, indices, last, threads=4)
+    provider = lk.PrefillProvider.load(0)
+    for capacity in (True, False):
+        plan = provider.plan_bf16_paged(spec, algorithm=algorithm, indices_capacity=capacity)
+        out = torch.full((spec.output_numel(),), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+        lse = torch.full((spec.lse_numel(),), float("nan"), dtype=torch.float32, device="cuda:0")
+        tensors = [H.dev_bf16(q), H.dev_bf16(k), H.dev_bf16(v), H.dev_i32(qo_indptr),
+                   H.dev_i32(indptr), H.dev_i32(padded), H.dev_i32(last)]
+        torch.cuda.synchronize()
+        queue = lk.CommandQueue(torch.cuda.Stream(), 1)
+        b = queue.bindings(9)
+        reads = [b.bind_read(t) for t in tensors]
+        h_out, h_lse = b.bind_read_write(out), b.bind_read_write(lse)
+        scope = queue.begin(b)
+        plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, h_out.write(), h_lse.write()))
+        scope.finish().wait()
+        assert provider.device_status() == 0
+        if capacity:
+            H.check_decode(H.host_bits(out), lse.cpu().numpy(), expected, expected_lse,
+                           lse_limit=1e-3, large_outputs=True)
+        else:
+            assert np.all(np.isnan(lse.cpu().numpy()))
