@@ -61,33 +61,15 @@ constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKStageBytes;
 constexpr int kOffBars = kOffV + kStages * kVStageBytes;
-// barriers: k_full[2] v_full[2] s_full[2] s_free p_full[2] p_free[2] verdict.  s_full[b] and
-// p_free[b] (the commits after S(j) and P V (j), b = j & 1) also hand the K and the V stage of
-// block j back to the producer: a barrier that completes once per two blocks cannot run two
-// phases ahead of a waiter whose load the next completion depends on.
-constexpr int kBarKFull = 0, kBarVFull = 2, kBarSFull = 4, kBarSFree = 6, kBarPFull = 7,
-              kBarPFree = 9, kBarVerdict = 11, kNumBars = 12;
+// barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full[2] p_free[2] verdict
+constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
+              kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kNumBars = 15;
 constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
 constexpr int kSharedBytes = kOffMisc + 24;
 static_assert(2 * (kSharedBytes + 1024) <= 233472, "two CTAs must fit one SM");
 
 constexpr uint32_t kIdescQK = idesc(kBlockTokens, false); // B = K block, K-major, N = 64 tokens
 constexpr uint32_t kIdescPV = idesc(kHeadDim, true);      // B = V page, MN-major, N = 128 dims
-
-// 2^x on the FMA pipe, for x <= 8 (any x below -125, -inf included, gives ~2^-125, which rounds
-// to a BF16 zero): x is rounded to the nearest integer n by the 1.5 * 2^23 trick, 2^(x - n) on
-// [-0.5, 0.5] is a cubic (relative error 7.5e-5, a sixtieth of a BF16 ulp), and n goes into the
-// exponent by integer addition.  The special-function unit does 16 ex2 per cycle and SM, which is
-// what bounds the softmax warps; every second weight is computed here instead.
-__device__ __forceinline__ float poly_exp2(float x) {
-    x = fmaxf(x, -125.0f);
-    const float shifted = x + 12582912.0f;
-    const float f = x - (shifted - 12582912.0f);
-    float p = fmaf(f, 0x1.c3f5ecp-5f, 0x1.f0dd36p-3f);
-    p = fmaf(p, f, 0x1.62f31ap-1f);
-    p = fmaf(p, f, 0x1.fff696p-1f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
-}
 
 __global__ void __launch_bounds__(kThreads, 2)
 paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
@@ -233,8 +215,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             const int stage = j & 1;
             const int v_id = id_of_page(j * kBlockPages + v_slot);
             const int k_id = id_of_page((j + 2) * kBlockPages + k_slot);
-            // P V (j - 2) has completed: its V stage and its P buffer are free
-            bool ok = j < kStages || mbar_wait(bars + (kBarPFree + stage) * 8, ((j >> 1) + 1) & 1);
+            bool ok = j < kStages || mbar_wait(bars + (kBarVEmpty + stage) * 8, ((j >> 1) + 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
                 break;
@@ -242,7 +223,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (j == kProbeBlock) LB_STAMP(9);
             load_v(j, v_id);
             if (j + 2 < blocks) {
-                ok = mbar_wait(bars + (kBarSFull + stage) * 8, (j >> 1) & 1); // S(j) has completed
+                ok = mbar_wait(bars + (kBarKEmpty + stage) * 8, (j >> 1) & 1); // S(j) has completed
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) misc[2] = 1;
                     break;
@@ -277,8 +258,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         const uint64_t v_desc0 = smem_desc(base_u32 + kOffV, 2048, 1024);
         auto issue_pv = [&](int i) -> bool {
             const int stage = i & 1, buffer = i & 1;
-            // the warp that arrives last on p_full has seen V(i) land
-            const bool ok = mbar_wait(bars + (kBarPFull + buffer) * 8, (i >> 1) & 1);
+            bool ok = mbar_wait(bars + (kBarPFull + buffer) * 8, (i >> 1) & 1);
+            ok = mbar_wait(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
             if (!ok) return false;
             tc_fence_after();
             if (i == kProbeBlock) LB_STAMP(7);
@@ -292,6 +273,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                                      kIdescPV, (i > 0 || p > 0) ? 1u : 0u);
                 }
                 umma_commit(bars + (kBarPFree + buffer) * 8);
+                umma_commit(bars + (kBarVEmpty + stage) * 8);
             }
             __syncwarp();
             return true;
@@ -299,9 +281,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         bool ok = true;
         for (int j = 0; j < blocks && ok; ++j) {
             const int stage = j & 1;
-            // s_free(j - 1) also says that K(j) has landed (softmax warp 0 checked before arriving)
-            ok = j > 0 ? mbar_wait(bars + kBarSFree * 8, (j - 1) & 1)
-                       : mbar_wait(bars + kBarKFull * 8, 0);
+            ok = mbar_wait(bars + (kBarKFull + stage) * 8, (j >> 1) & 1);
+            if (ok && j > 0) ok = mbar_wait(bars + kBarSFree * 8, (j - 1) & 1);
             if (!ok) break;
             tc_fence_after();
             if (j == kProbeBlock) LB_STAMP(6);
@@ -314,7 +295,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                               k_desc0 + (uint64_t)((stage * kKStageBytes + (kk >> 2) * kKHalfBytes +
                                                     (kk & 3) * 32) >> 4),
                               kIdescQK, kk > 0 ? 1u : 0u);
-                umma_commit(bars + (kBarSFull + stage) * 8);
+                umma_commit(bars + kBarSFull * 8);
+                umma_commit(bars + (kBarKEmpty + stage) * 8);
             }
             __syncwarp();
             if (j > 0) ok = issue_pv(j - 1);
@@ -330,19 +312,13 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         float l = 0.0f;
         bool ok = true;
         for (int j = 0; j < blocks; ++j) {
-            ok = mbar_wait(bars + (kBarSFull + (j & 1)) * 8, (j >> 1) & 1);
+            ok = mbar_wait(bars + kBarSFull * 8, j & 1);
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
             if (j == kProbeBlock) LB_STAMP(0);
             if (j == kProbeBlock + 1) LB_STAMP(10);
             float s[kBlockTokens]; // raw dot products
             tmem_load64(tmem_s + lane_base, s);
-            // warp 0 vouches for the keys of the next block, so that the MMA warp, whose every
-            // wait is on the critical path, need not look at k_full itself
-            if (warp == 0 && j + 1 < blocks) {
-                ok = mbar_wait(bars + (kBarKFull + ((j + 1) & 1)) * 8, ((j + 1) >> 1) & 1);
-                if (__any_sync(0xffffffffu, !ok)) break;
-            }
             tc_fence_before();
             __syncwarp();
             if (j == kProbeBlock) LB_STAMP(1);
@@ -402,10 +378,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             for (int chunk = 0; chunk < kBlockTokens / 8; ++chunk) {
                 float p[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float x = fmaf(s[chunk * 8 + i], scale, neg_base);
-                    p[i] = (i & 1) ? poly_exp2(x) : fast_exp2(x);
-                }
+                for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[chunk * 8 + i], scale, neg_base));
                 sum0 += (p[0] + p[1]) + (p[2] + p[3]);
                 sum1 += (p[4] + p[5]) + (p[6] + p[7]);
 #pragma unroll
@@ -420,11 +393,9 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             // them in the V block before the MMA reads it
             const int last_page = num_pages - 1;
             const bool zero_tail = tail < kPage && last_page / kBlockPages == j && last_page < cnt;
-            if (zero_tail || warp == 1) { // warp 1 vouches for the values of this block (as above)
+            if (zero_tail) {
                 ok = mbar_wait(bars + (kBarVFull + (j & 1)) * 8, (j >> 1) & 1);
                 if (__any_sync(0xffffffffu, !ok)) break;
-            }
-            if (zero_tail) {
                 uint8_t *v_page =
                     base + kOffV + (j & 1) * kVStageBytes + (last_page % kBlockPages) * 4096;
                 for (int i = tid; i < (kPage - tail) * 16; i += kTileRows) {
