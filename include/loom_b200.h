@@ -532,7 +532,11 @@ enum {
                                       choice for short, latency-bound calls; one command */
     LB_PREFILL_TILED = 1           /* one CTA per (request, KV head, 128 packed query rows) on the
                                       tcgen05 tensor cores with the accumulators in TMEM; the
-                                      choice for long prompts; one command */
+                                      choice for long prompts; one command, or -- when the plan
+                                      cuts the KV range of every tile into `partitions` chunks so
+                                      that a short chunk over a long cache fills the device --
+                                      two: chunk states into a workspace, then the LSE merge of
+                                      the split-K contract (single_decode/mod.rs:343-379) */
 };
 
 typedef struct lb_paged_prefill_options {
@@ -541,7 +545,11 @@ typedef struct lb_paged_prefill_options {
                                   pages of the same rows */
     uint32_t indices_capacity; /* as lb_paged_decode_options.indices_capacity */
     uint32_t algorithm;        /* 0 = plan-time heuristic, 1 = token-parallel, 2 = tiled */
-    uint32_t reserved[5];
+    uint32_t partitions;       /* tiled only.  0 = plan-time heuristic, 1 = one CTA per tile, N > 1
+                                  (at most 64) = the 64-token KV blocks of every tile are shared
+                                  out to N CTAs by the balanced rule of the split-K contract
+                                  (single_decode/mod.rs:171-185) */
+    uint32_t reserved[4];
 } lb_paged_prefill_options;
 
 typedef struct lb_paged_prefill_plan_info {
@@ -550,14 +558,21 @@ typedef struct lb_paged_prefill_plan_info {
     uint32_t rows_per_cta;  /* packed (token, head-in-group) rows per CTA = 16 * q_tiles */
     uint32_t tiles;         /* upper bound of row tiles per KV head the grid covers */
     uint32_t grid, block, shared_bytes;
-    uint32_t commands;      /* 1 */
+    uint32_t commands;      /* 1, or 2 when partitions > 1 */
+    uint32_t partitions;    /* KV chunks per tile (1 unless tiled) */
+    uint32_t merge_grid, merge_block; /* second command of a split plan */
+    size_t workspace_numel; /* F32 elements the caller must bind: nnz_qo * qh * partitions * 130,
+                               0 when partitions == 1 */
 } lb_paged_prefill_plan_info;
 
-/* Bf16PagedPrefillArgs, prefill.rs:2853-2891 */
+/* Bf16PagedPrefillArgs, prefill.rs:2853-2891, plus the workspace of a split plan (as
+ * Bf16SingleDecodeSplitKArgs.workspace, decode.rs:1420-1449); workspace is ignored when the plan's
+ * partitions == 1. */
 typedef struct lb_paged_prefill_args {
     lb_handle query, key_pages, value_pages, qo_indptr, page_indptr, page_indices,
         last_page_len;     /* Read */
     lb_handle output, lse; /* Write */
+    lb_handle workspace;   /* ReadWrite<f32> */
 } lb_paged_prefill_args;
 
 /* PrefillProvider::load, prefill.rs:2283-2287 */
@@ -574,9 +589,11 @@ lb_status lb_paged_prefill_plan_create(const lb_prefill_provider *provider,
 void lb_paged_prefill_plan_destroy(lb_paged_prefill_plan *plan);
 lb_status lb_paged_prefill_plan_info_get(const lb_paged_prefill_plan *plan, lb_prefill_spec *spec,
                                          lb_paged_prefill_plan_info *info);
-/* Bf16PagedPrefillPlan::enqueue_into, prefill.rs:2456-2583: one command.  Errors as
+/* Bf16PagedPrefillPlan::enqueue_into, prefill.rs:2456-2583: one command (two for a split plan;
+ * both must fit the scope before anything is launched).  Errors as
  * PagedPrefillEnqueueError (:2942-2963): LengthMismatch (operands "Q", "K_pages", "V_pages",
- * "qo_indptr", "page_indptr", "last_page_len", "O", "LSE"), PageIndicesTooShort, MisalignedBuffer
+ * "qo_indptr", "page_indptr", "last_page_len", "O", "LSE", "workspace"), PageIndicesTooShort,
+ * MisalignedBuffer
  * (16 bytes here, 4 in the reference), Command errors.  Device-resident metadata is never an
  * error: a query row whose request fails the kernel's guard keeps its previous output
  * (prefill.rs:289-347). */

@@ -104,20 +104,21 @@ class PrefillSpec(ctypes.Structure):
 
 class PrefillOptions(ctypes.Structure):
     _fields_ = [("q_tiles", c_uint32), ("indices_capacity", c_uint32), ("algorithm", c_uint32),
-                ("reserved", c_uint32 * 5)]
+                ("partitions", c_uint32), ("reserved", c_uint32 * 4)]
 
 
 class PrefillPlanInfo(ctypes.Structure):
     _fields_ = [("algorithm", c_int32), ("q_tiles", c_uint32), ("pages_per_stage", c_uint32),
                 ("stages", c_uint32), ("rows_per_cta", c_uint32), ("tiles", c_uint32),
                 ("grid", c_uint32), ("block", c_uint32), ("shared_bytes", c_uint32),
-                ("commands", c_uint32)]
+                ("commands", c_uint32), ("partitions", c_uint32), ("merge_grid", c_uint32),
+                ("merge_block", c_uint32), ("workspace_numel", c_size_t)]
 
 
 class PrefillArgs(ctypes.Structure):
     _fields_ = [(name, Handle) for name in
                 ("query", "key_pages", "value_pages", "qo_indptr", "page_indptr", "page_indices",
-                 "last_page_len", "output", "lse")]
+                 "last_page_len", "output", "lse", "workspace")]
 
 
 RECORD_FN = ctypes.CFUNCTYPE(c_int32, c_void_p, c_void_p)

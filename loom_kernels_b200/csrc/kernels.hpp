@@ -90,6 +90,9 @@ struct PrefillLaunch {
     int32_t q_tiles, pages_per_stage, stages, tiles;
     float scale_log2;
     uint32_t grid, block, shared_bytes;
+    // tiled plans that cut a tile's KV range into chunks: F32 states [nnz_qo * qh][partitions][130]
+    float *workspace;
+    int32_t partitions;
 };
 int configure_prefill_kernels(size_t max_dynamic_shared);
 int launch_paged_prefill(const PrefillLaunch &launch, void *stream);
@@ -98,6 +101,7 @@ int launch_paged_prefill(const PrefillLaunch &launch, void *stream);
 int configure_prefill_tiled_kernel(size_t max_dynamic_shared);
 int prefill_tiled_shared_bytes();
 int launch_paged_prefill_tiled(const PrefillLaunch &launch, void *stream);
+int launch_prefill_merge(const PrefillLaunch &launch, void *stream); // second command of a split plan
 int append_block_threads();       // threads per CTA the append kernel is built for
 int append_max_tokens_per_cta();  // tokens one CTA can own (grid floor = tokens / this)
 

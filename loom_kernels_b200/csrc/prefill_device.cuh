@@ -16,6 +16,11 @@ struct PrefillArgs {
     int32_t batch, nnz_qo, max_pages, qh, kvh, indices_len, indices_min;
     int32_t mt, pps, stages, tiles;
     float scale_log2;
+    // tiled kernel with the KV range of a tile cut into chunks: F32 states
+    // [nnz_qo * qh][partitions][130] (the split-K state of the decode kernels); partitions == 1
+    // writes O and LSE directly
+    float *workspace;
+    int32_t partitions;
 };
 
 // The request that owns row tile `tile` (tiles are numbered request by request; a request of
@@ -55,6 +60,31 @@ __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int
         }
         if (bad) return false;
         before += __shfl_sync(0xffffffffu, inclusive, 31);
+    }
+    return false;
+}
+
+// The request that owns query row `row`; false when no request does or a request up to and
+// including the owner has an invalid query range (the guard of locate_tile, per row).
+__device__ __forceinline__ bool locate_row(const int32_t *qo_indptr, int batch, int nnz_qo, int row,
+                                           int lane, int &request) {
+    for (int r0 = 0; r0 < batch; r0 += 32) {
+        const int r = r0 + lane;
+        int start = 0, end = 0;
+        if (r < batch) {
+            start = qo_indptr[r];
+            end = qo_indptr[r + 1];
+        }
+        const bool valid = r >= batch || (start >= 0 && end > start && end <= nnz_qo);
+        const unsigned bad = __ballot_sync(0xffffffffu, !valid);
+        const unsigned hit = __ballot_sync(0xffffffffu, r < batch && valid && row >= start && row < end);
+        if (hit) {
+            const int source = __ffs(hit) - 1;
+            if (bad && __ffs(bad) - 1 < source) return false;
+            request = r0 + source;
+            return true;
+        }
+        if (bad) return false;
     }
     return false;
 }

@@ -97,20 +97,49 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         return fail(LB_LAUNCH_CONTRACT, "indices_capacity", options->indices_capacity);
     const uint32_t algorithm_option = options ? options->algorithm : 0;
     if (algorithm_option > 2) return fail(LB_LAUNCH_CONTRACT, "algorithm", algorithm_option);
-    // Tiled (tcgen05, 128-row tiles) when whole tiles fill the device at least once and the
-    // average request can hold a few blocks of KV: then the operator is bound by the tensor pipe.
-    // Short calls are latency-bound and take the token-parallel kernel.
+    uint32_t partitions = options ? options->partitions : 0;
+    if (partitions > 64) return fail(LB_INVALID_PARTITION_COUNT, nullptr, partitions, 64);
+    if (partitions > 1 && algorithm_option == 1)
+        return fail(LB_LAUNCH_CONTRACT, "partitions", partitions);
+    // Tiled (tcgen05, 128-row tiles) when the call has a whole tile per KV head and either 512
+    // packed rows (128 tokens of a 4-head group) with room for a few blocks of KV per request in
+    // the pool, or room for 4096 tokens per request (a short chunk over a long cache: the KV
+    // range is shared out below).  Shorter calls are latency-bound and take the token-parallel
+    // kernel.  (Measured back to back on B200, 32 query / 8 KV heads: 128 queries over 512
+    // tokens 13.9 us tiled against 20.3; 64 over 512 13.8 against 11.0; 32 over 8192 31.7
+    // against 65.7.)
     const size_t full_tiles = (packed_rows / 128) * spec.num_kv_heads;
     const size_t average_kv = spec.max_num_pages * LB_PAGE_SIZE / spec.batch_size;
-    const bool tiled = algorithm_option == 2 ||
-                       (algorithm_option == 0 && q_tiles == 0 && full_tiles >= sms &&
-                        average_kv >= 512);
+    const bool tiled =
+        algorithm_option == 2 ||
+        (algorithm_option == 0 && q_tiles == 0 &&
+         (partitions > 1 ||
+          (full_tiles >= 1 && ((packed_rows >= 512 && average_kv >= 256) || average_kv >= 4096))));
     if (tiled) {
         const uint32_t shared = (uint32_t)prefill_tiled_shared_bytes();
         if (shared > smem) return fail(LB_LAUNCH_CONTRACT, "shared_memory", shared);
         const size_t tiles = packed_rows / 128 + spec.batch_size;
-        size_t grid;
-        if (mul_overflow(tiles, spec.num_kv_heads, &grid) || grid > 0x7fffffffu)
+        if (partitions == 0) {
+            // Two CTAs run per SM.  When the tiles are fewer than half of those slots, the
+            // 64-token KV blocks of every tile are shared out to several CTAs -- as many as fit
+            // the slots in one wave, never fewer than sixteen blocks (1024 tokens of the average
+            // request's room in the pool) per CTA, at most sixteen CTAs -- and a second command
+            // merges their states.  Every request has at least one tile per KV head.
+            const size_t slots = 2 * (size_t)sms;
+            const size_t request_tiles = spec.batch_size * spec.num_kv_heads;
+            const size_t work = full_tiles > request_tiles ? full_tiles : request_tiles;
+            size_t wanted = slots / work;
+            const size_t room = average_kv / 1024;
+            if (wanted > room) wanted = room;
+            if (wanted > 16) wanted = 16;
+            partitions = wanted > 1 ? (uint32_t)wanted : 1;
+        }
+        size_t grid, workspace = 0;
+        if (mul_overflow(tiles, spec.num_kv_heads, &grid) || mul_overflow(grid, partitions, &grid) ||
+            grid > 0x7fffffffu)
+            return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)states);
+        if (partitions > 1 && (mul_overflow(states, (size_t)partitions * 130, &workspace) ||
+                               workspace > ((size_t)1 << 40)))
             return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)states);
         memset(out, 0, sizeof(*out));
         out->algorithm = LB_PREFILL_TILED;
@@ -122,7 +151,11 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         out->grid = (uint32_t)grid;
         out->block = 192;
         out->shared_bytes = shared;
-        out->commands = 1;
+        out->commands = partitions > 1 ? 2 : 1;
+        out->partitions = partitions;
+        out->merge_grid = partitions > 1 ? (uint32_t)((states + 3) / 4) : 0;
+        out->merge_block = partitions > 1 ? 128 : 0;
+        out->workspace_numel = workspace;
         return LB_OK;
     }
     if (q_tiles == 0) {
@@ -160,6 +193,7 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
     out->block = 288;
     out->shared_bytes = shared;
     out->commands = 1;
+    out->partitions = 1;
     return LB_OK;
 }
 
@@ -375,17 +409,18 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
     const lb_paged_prefill_plan_info &c = plan->info;
     if (scope->queue->device != plan->device)
         return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
-    lb_status rc = require_command_capacity(*scope, 1);
+    const bool split = c.partitions > 1; // two commands and a workspace
+    lb_status rc = require_command_capacity(*scope, split ? 2 : 1);
     if (rc) return rc;
-    OperandRequest requests[9] = {
+    OperandRequest requests[10] = {
         {args->query, LB_BF16, false},         {args->key_pages, LB_BF16, false},
         {args->value_pages, LB_BF16, false},   {args->qo_indptr, LB_I32, false},
         {args->page_indptr, LB_I32, false},    {args->page_indices, LB_I32, false},
         {args->last_page_len, LB_I32, false},  {args->output, LB_BF16, true},
-        {args->lse, LB_F32, true},
+        {args->lse, LB_F32, true},             {args->workspace, LB_F32, true},
     };
-    Operand op[9];
-    if ((rc = resolve(*scope, requests, 9, op))) return rc;
+    Operand op[10];
+    if ((rc = resolve(*scope, requests, split ? 10 : 9, op))) return rc;
     // the order of the reference's checks, prefill.rs:2475-2510
     const size_t pool = lb_prefill_spec_kv_pages_numel(&spec);
     if ((rc = require_exact_len("Q", op[0].numel, lb_prefill_spec_query_numel(&spec)))) return rc;
@@ -401,10 +436,12 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
     if ((rc = require_exact_len("last_page_len", op[6].numel, spec.batch_size))) return rc;
     if ((rc = require_exact_len("O", op[7].numel, lb_prefill_spec_query_numel(&spec)))) return rc;
     if ((rc = require_exact_len("LSE", op[8].numel, lb_prefill_spec_lse_numel(&spec)))) return rc;
+    if (split && (rc = require_exact_len("workspace", op[9].numel, c.workspace_numel))) return rc;
     if ((rc = require_alignment("Q", op[0].ptr, 16))) return rc;
     if ((rc = require_alignment("K_pages", op[1].ptr, 16))) return rc;
     if ((rc = require_alignment("V_pages", op[2].ptr, 16))) return rc;
     if ((rc = require_alignment("O", op[7].ptr, 16))) return rc;
+    if (split && (rc = require_alignment("workspace", op[9].ptr, 8))) return rc;
 
     PrefillLaunch launch;
     memset(&launch, 0, sizeof(launch));
@@ -447,11 +484,27 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
     launch.grid = c.grid;
     launch.block = c.block;
     launch.shared_bytes = c.shared_bytes;
+    launch.workspace = split ? (float *)op[9].ptr : nullptr;
+    launch.partitions = (int32_t)c.partitions;
     void *stream = scope->queue->stream;
-    return submit_launch(*scope, [&]() {
-        return tiled ? launch_paged_prefill_tiled(launch, stream)
-                     : launch_paged_prefill(launch, stream);
-    });
+    if ((rc = submit_launch(*scope, [&]() {
+             return tiled ? launch_paged_prefill_tiled(launch, stream)
+                          : launch_paged_prefill(launch, stream);
+         })))
+        return rc;
+    if (!split) return LB_OK;
+
+    // second command: the workspace is now a read operand, as in the split-K decode
+    // (decode.rs:1374-1388)
+    OperandRequest merge_requests[3] = {
+        {lb_handle_read(args->workspace), LB_F32, false},
+        {args->output, LB_BF16, true},
+        {args->lse, LB_F32, true},
+    };
+    Operand merge_op[3];
+    if ((rc = require_command_capacity(*scope, 1))) return rc;
+    if ((rc = resolve(*scope, merge_requests, 3, merge_op))) return rc;
+    return submit_launch(*scope, [&]() { return launch_prefill_merge(launch, stream); });
 }
 
 }

@@ -88,7 +88,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
 
     const int group = a.qh / a.kvh;
     const int kv_head = blockIdx.x % a.kvh;
-    const int tile = a.tiles - 1 - (int)(blockIdx.x / a.kvh); // late (long) tiles start first
+    // late (long) tiles start first; the chunks of a tile's KV range are neighbours in the grid
+    const int tile = a.tiles - 1 - (int)(blockIdx.x / a.kvh) / a.partitions;
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i)
@@ -117,8 +118,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         return;
     const int qo_start = a.qo_indptr[request];
     const int qo_len = a.qo_indptr[request + 1] - qo_start;
-    const int num_pages = page_end - page_start;
-    const long long kv_len_wide = (long long)(num_pages - 1) * kPage + tail;
+    const int request_pages = page_end - page_start;
+    const long long kv_len_wide = (long long)(request_pages - 1) * kPage + tail;
     if (qo_len > kv_len_wide) return; // prefill.rs:343-347
     const int kv_len = (int)kv_len_wide;
     const int shift = kv_len - qo_len + 1; // the row of token t sees logical tokens [0, shift + t)
@@ -126,20 +127,43 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     const long long row_lo = (long long)tile_in_request * kTileRows;
     const long long row_hi = min(row_lo + kTileRows, rows_total);
     const int cta_limit = shift + (int)((row_hi - 1) / group); // tokens the last row sees
-    const int cnt = (cta_limit + kPage - 1) / kPage;           // pages this CTA streams
-    const int blocks = (cnt + kBlockPages - 1) / kBlockPages;
+    // this CTA's share of the tile's 64-token blocks: the balanced rule of the split-K contract
+    // (crates/loom-infer/src/attention/single_decode/mod.rs:171-185)
+    const int chunk = (int)(blockIdx.x / a.kvh) % a.partitions;
+    const int tile_pages = (cta_limit + kPage - 1) / kPage; // pages the tile's last row sees
+    const int tile_blocks = (tile_pages + kBlockPages - 1) / kBlockPages;
+    const int block0 = chunk * (tile_blocks / a.partitions) + min(chunk, tile_blocks % a.partitions);
+    const int blocks = tile_blocks / a.partitions + (chunk < tile_blocks % a.partitions ? 1 : 0);
+    // from here on pages, blocks and tokens are counted from the start of the share
+    page_start += block0 * kBlockPages;
+    const int num_pages = request_pages - block0 * kBlockPages; // up to the request's last page
+    const int cnt = min(tile_pages - block0 * kBlockPages, blocks * kBlockPages); // pages streamed
+    const int shift_here = shift - block0 * kBlockTokens;
 
-    // ---- TMEM, Q tile ---------------------------------------------------------------------------------
-    if (warp == 5) {
-        tmem_alloc(base_u32 + kOffMisc, kTmemColumns);
-        tmem_relinquish();
-    }
     // this thread's packed row (warps 0-3)
     const long long my_row = row_lo + tid;
     const bool row_valid = tid < kTileRows && my_row < row_hi;
     const int my_token = row_valid ? (int)(my_row / group) : 0;
     const int my_head = kv_head * group + (row_valid ? (int)(my_row % group) : 0);
     const size_t my_state = (size_t)(qo_start + my_token) * a.qh + my_head;
+    // the state of this row and chunk in the workspace (plans with more than one chunk)
+    auto partial_state = [&]() -> float * {
+        const int chunk = (int)(blockIdx.x / a.kvh) % a.partitions;
+        return a.workspace + (my_state * a.partitions + chunk) * kStateWidth;
+    };
+    if (blocks == 0) { // more chunks than blocks: an empty state (the merge gives it weight 0)
+        if (row_valid) {
+            float2 *state = reinterpret_cast<float2 *>(partial_state());
+            for (int i = 0; i < kStateWidth / 2; ++i) state[i] = make_float2(0.0f, 0.0f);
+        }
+        return;
+    }
+
+    // ---- TMEM, Q tile ---------------------------------------------------------------------------------
+    if (warp == 5) {
+        tmem_alloc(base_u32 + kOffMisc, kTmemColumns);
+        tmem_relinquish();
+    }
     if (tid < kTileRows) {
         const uint4 *src = reinterpret_cast<const uint4 *>(a.query + my_state * kHeadDim);
 #pragma unroll
@@ -305,7 +329,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         if (!ok && lane == 0) misc[2] = 1;
     } else {
         // ================= softmax + epilogue: thread t owns packed row t ===========================
-        const int see = row_valid ? shift + my_token : 0; // logical tokens this row sees
+        // tokens of the share this row sees (none when negative)
+        const int see = row_valid ? shift_here + my_token : 0;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         const float scale = a.scale_log2;
         float m_used = -INFINITY; // exponent base of P, O and the normaliser
@@ -420,13 +445,27 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             } else {
                 tc_fence_after();
                 const bool verdict = mbar_wait(bars + kBarVerdict * 8, 0); // the producer's page scan
-                const bool publish = verdict && row_valid && misc[1] == 0 && misc[2] == 0;
+                const bool settled = verdict && row_valid && misc[2] == 0;
+                float *my_partial = a.partitions > 1 ? partial_state() : nullptr;
+                const bool publish = settled && misc[1] == 0 && my_partial == nullptr;
                 const float inv = 1.0f / l;
                 uint4 *dst = reinterpret_cast<uint4 *>(a.output + my_state * kHeadDim);
+                if (settled && my_partial != nullptr) {
+                    // the unnormalised state of this chunk: [maximum, normaliser, weighted values];
+                    // a row that saw nothing here is an empty state, a bad page id poisons it
+                    *reinterpret_cast<float2 *>(my_partial) =
+                        make_float2(l > 0.0f ? m_used : 0.0f, misc[1] != 0 ? -1.0f : l);
+                }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float part[32];
                     tmem_load32(tmem_o + lane_base + c * 32, part);
+                    if (settled && my_partial != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            *reinterpret_cast<float2 *>(my_partial + 2 + c * 32 + 2 * i) =
+                                make_float2(part[2 * i], part[2 * i + 1]);
+                    }
                     if (publish) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
@@ -448,6 +487,46 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     tc_fence_after();
     if (warp == 5) tmem_dealloc(tmem_base, kTmemColumns);
     if (tid == 0 && misc[2] != 0 && a.status) atomicExch(a.status, 1);
+    // a chunk that gave up on a wait poisons its states, so that the merge publishes nothing
+    if (misc[2] != 0 && a.partitions > 1 && row_valid) partial_state()[1] = -1.0f;
+}
+
+// Merges the chunk states of one (query row, query head) per warp and writes BF16 O + log2 LSE
+// (merge_states).  The row's request is checked again here -- the global checks, every query
+// range up to the owner, its page range and qo_len <= kv_len (prefill.rs:289-347) -- because a
+// CTA of the main kernel that rejects a request writes no state; a bad page id arrives as a
+// poisoned state.
+__global__ void __launch_bounds__(128, 5)
+prefill_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
+                     const int32_t *qo_indptr, const int32_t *indptr, const int32_t *last, int batch,
+                     int nnz_qo, int qh, int partitions, int indices_min, int indices_len) {
+    dependent_launch_release();
+    const int lane = threadIdx.x & 31;
+    const long long state = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (state >= (long long)nnz_qo * qh) return;
+    const int row = (int)(state / qh);
+    dependent_launch_wait(); // the chunk states are complete and visible
+    const bool global_ok = qo_indptr[0] == 0 && qo_indptr[batch] == nnz_qo;
+    int request = 0;
+    const bool located = locate_row(qo_indptr, batch, nnz_qo, row, lane, request);
+    // The owner's page range is loaded here and judged after the merge: its loads and those of
+    // the states are in flight together.
+    const int global_end = indptr[batch], first = indptr[0];
+    const int page_start = indptr[request], page_end = indptr[request + 1], tail = last[request];
+    const int qo_len = qo_indptr[request + 1] - qo_indptr[request];
+    const float *st = workspace + (size_t)state * partitions * kStateWidth;
+    float top, norm;
+    float4 acc;
+    if (!merge_partial([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane, top,
+                       norm, acc))
+        return; // a chunk met a page id out of range
+    // request_metadata_valid and qo_len <= kv_len, on the values loaded above
+    const bool valid = global_ok && located && first == 0 && global_end >= indices_min &&
+                       global_end <= indices_len && page_start >= 0 && page_end > page_start &&
+                       page_end <= global_end && tail >= 1 && tail <= kPage &&
+                       qo_len <= (long long)(page_end - page_start - 1) * kPage + tail;
+    if (!valid || !(norm > 0.0f)) return;
+    publish_merged(top, norm, acc, lane, output + (size_t)state * kHeadDim, lse + state);
 }
 
 } // namespace
@@ -487,11 +566,23 @@ int launch_paged_prefill_tiled(const PrefillLaunch &launch, void *stream) {
     args.stages = kStages;
     args.tiles = launch.tiles;
     args.scale_log2 = launch.scale_log2;
+    args.workspace = launch.workspace;
+    args.partitions = launch.partitions > 1 ? launch.partitions : 1;
     CUtensorMap k_half_map, v_map;
     memcpy(&k_half_map, launch.k_map, sizeof(k_half_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
     return launch_dependent(paged_prefill_tiled_kernel, launch.grid, kThreads, kSharedBytes, stream,
                             k_half_map, v_map, args);
+}
+
+int launch_prefill_merge(const PrefillLaunch &launch, void *stream) {
+    const long long states = (long long)launch.nnz_qo * launch.qh;
+    return launch_dependent(prefill_merge_kernel, (uint32_t)((states + 3) / 4), 128, 0, stream,
+                            (const float *)launch.workspace,
+                            static_cast<__nv_bfloat16 *>(launch.output), launch.lse,
+                            launch.qo_indptr, launch.indptr, launch.last, launch.batch,
+                            launch.nnz_qo, launch.qh, launch.partitions, launch.indices_min,
+                            launch.indices_len);
 }
 
 } // namespace lb

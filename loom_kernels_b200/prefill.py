@@ -15,7 +15,7 @@ from typing import Optional
 
 from . import _abi
 from ._abi import HEAD_DIM, PAGE_SIZE
-from .api import CommandScope, Read, Write, _check, _dispose, _i32
+from .api import CommandScope, Read, ReadWrite, Write, _check, _dispose, _i32
 
 _I32P = ctypes.POINTER(c_int32)
 
@@ -124,7 +124,8 @@ class Bf16PagedPrefillAlgorithm:
 
 @dataclass
 class Bf16PagedPrefillArgs:
-    """prefill.rs:2853-2891."""
+    """prefill.rs:2853-2891, plus the ReadWrite F32 workspace a plan with partitions > 1 needs
+    (plan.workspace_required_numel() elements; None otherwise)."""
     query: Read
     key_pages: Read
     value_pages: Read
@@ -134,6 +135,7 @@ class Bf16PagedPrefillArgs:
     last_page_len: Read
     output: Write
     lse: Write
+    workspace: Optional[ReadWrite] = None
 
 
 class PrefillProvider:
@@ -157,12 +159,14 @@ class PrefillProvider:
         return out.value
 
     def plan_bf16_paged(self, spec: Bf16PagedPrefillSpec, q_tiles: int = 0,
-                        indices_capacity: bool = False,
-                        algorithm: int = 0) -> "Bf16PagedPrefillPlan":
+                        indices_capacity: bool = False, algorithm: int = 0,
+                        partitions: int = 0) -> "Bf16PagedPrefillPlan":
         """algorithm: 0 heuristic, 1 token-parallel, 2 tiled (tcgen05).  q_tiles (token-parallel):
         0 heuristic, else the 16-row tiles of packed query rows one CTA owns (1, 2, 4 or 8).
+        partitions (tiled): 0 heuristic, 1 one CTA per tile, N > 1 the KV blocks of every tile
+        shared out to N CTAs whose states a second command merges (needs the workspace).
         indices_capacity as for the decode plan."""
-        options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm,
+        options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm, partitions=partitions,
                                       indices_capacity=1 if indices_capacity else 0)
         out = c_void_p()
         _check(_abi.load().lb_paged_prefill_plan_create(self._ptr, byref(spec._raw),
@@ -171,9 +175,9 @@ class PrefillProvider:
 
 
 def choose_paged_prefill(spec: Bf16PagedPrefillSpec, sm_count: int, q_tiles: int = 0,
-                         algorithm: int = 0):
+                         algorithm: int = 0, partitions: int = 0):
     """The plan-time launch shape as a pure function (no device needed)."""
-    options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm)
+    options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm, partitions=partitions)
     info = _abi.PrefillPlanInfo()
     _check(_abi.load().lb_paged_prefill_choose(byref(spec._raw), sm_count, byref(options),
                                                byref(info)))
@@ -197,6 +201,9 @@ class Bf16PagedPrefillPlan:
     def algorithm(self): return self._info.algorithm
     def info(self): return self._info
     def commands(self): return self._info.commands
+    def partitions(self): return self._info.partitions
+    def workspace_required_numel(self): return self._info.workspace_numel
+    def workspace_required_bytes(self): return self._info.workspace_numel * 4
 
     def enqueue_into(self, scope: CommandScope, args: Bf16PagedPrefillArgs):
         raw = _abi.PrefillArgs(
@@ -204,4 +211,6 @@ class Bf16PagedPrefillPlan:
             value_pages=args.value_pages._raw, qo_indptr=args.qo_indptr._raw,
             page_indptr=args.page_indptr._raw, page_indices=args.page_indices._raw,
             last_page_len=args.last_page_len._raw, output=args.output._raw, lse=args.lse._raw)
+        if args.workspace is not None:
+            raw.workspace = args.workspace._raw
         _check(_abi.load().lb_paged_prefill_enqueue(self._ptr, scope._ptr, byref(raw)))

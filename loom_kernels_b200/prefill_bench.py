@@ -65,7 +65,8 @@ class PrefillCase:
         pool = sum(pages) + 8
         rng = np.random.default_rng(seed)
         self.spec = lk.Bf16PagedPrefillSpec.new(len(qo_lens), sum(qo_lens), pool, qh, kvh)
-        self.plan = provider.plan_bf16_paged(self.spec, q_tiles=q_tiles)
+        self.device = device
+        self.use_plan(provider.plan_bf16_paged(self.spec, q_tiles=q_tiles))
         g = torch.Generator(device=device)
         g.manual_seed(seed)
         self.q = normal_bf16(g, self.spec.query_numel(), device)
@@ -76,6 +77,12 @@ class PrefillCase:
         self.meta = [torch.tensor(np.asarray(a, dtype=np.int32), device=device) for a in meta]
         self.out = torch.zeros(self.spec.output_numel(), dtype=torch.bfloat16, device=device)
         self.lse = torch.zeros(self.spec.lse_numel(), dtype=torch.float32, device=device)
+
+    def use_plan(self, plan):
+        """The plan to time, with the workspace a split plan needs."""
+        self.plan = plan
+        numel = plan.workspace_required_numel()
+        self.workspace = torch.zeros(numel, dtype=torch.float32, device=self.device) if numel else None
 
     def flops(self):
         """4 * 128 per visible (query, key) pair and query head: Q K^T and P V, 2 FLOPs per MAC."""
@@ -92,10 +99,11 @@ class PrefillCase:
         stream = queue.stream()
         times = []
         for sample in range(warmup + samples):
-            b = queue.bindings(9)
+            b = queue.bindings(10)
             reads = [b.bind_read(t) for t in (self.q, self.k, self.v, *self.meta)]
             out, lse = b.bind_read_write(self.out), b.bind_read_write(self.lse)
-            args = lk.Bf16PagedPrefillArgs(*reads, out.write(), lse.write())
+            ws = b.bind_read_write(self.workspace) if self.workspace is not None else None
+            args = lk.Bf16PagedPrefillArgs(*reads, out.write(), lse.write(), ws)
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             scope = queue.begin(b)
             start.record(stream)
@@ -130,7 +138,7 @@ def main():
         if args.only and args.only not in name:
             continue
         case = PrefillCase(provider, name, qo_lens, kv_lens, qh, kvh, device, q_tiles=args.q_tiles)
-        queue = lk.CommandQueue(torch.cuda.Stream(), calls)
+        queue = lk.CommandQueue(torch.cuda.Stream(), calls * case.plan.commands())
         times = case.time_us(queue, calls, args.samples)
         median = float(np.median(times))
         info = case.plan.info()

@@ -111,10 +111,11 @@ def test_the_reference_rule_still_holds_without_the_option():
     assert np.all(np.isnan(H.bits_to_f32(out))) and np.all(np.isnan(lse))
 
 
-@pytest.mark.parametrize("algorithm", [1, 2])
-def test_prefill_accepts_a_longer_page_indices_binding(oracle, algorithm):
-    """The same option on the prefill plans: the table in use may be shorter than the bound
-    page_indices (the tail is never read); without the option such a call writes nothing."""
+@pytest.mark.parametrize("algorithm,partitions", [(1, 1), (2, 1), (2, 3)])
+def test_prefill_accepts_a_longer_page_indices_binding(oracle, algorithm, partitions):
+    """The same option on the prefill plans (token-parallel, tiled, tiled with split KV): the table
+    in use may be shorter than the bound page_indices (the tail is never read); without the
+    option such a call writes nothing."""
     rng = np.random.default_rng(12)
     qo_lens, kv_lens = [37, 5, 70], [90, 200, 70]
     qo_indptr = np.concatenate([[0], np.cumsum(qo_lens)]).astype(np.int32)
@@ -128,18 +129,23 @@ def test_prefill_accepts_a_longer_page_indices_binding(oracle, algorithm):
                                                   qo_indptr, indptr, indices, last, threads=4)
     provider = lk.PrefillProvider.load(0)
     for capacity in (True, False):
-        plan = provider.plan_bf16_paged(spec, algorithm=algorithm, indices_capacity=capacity)
+        plan = provider.plan_bf16_paged(spec, algorithm=algorithm, indices_capacity=capacity,
+                                        partitions=partitions)
+        workspace = torch.zeros(plan.workspace_required_numel(), dtype=torch.float32,
+                                device="cuda:0") if plan.workspace_required_numel() else None
         out = torch.full((spec.output_numel(),), float("nan"), dtype=torch.bfloat16, device="cuda:0")
         lse = torch.full((spec.lse_numel(),), float("nan"), dtype=torch.float32, device="cuda:0")
         tensors = [H.dev_bf16(q), H.dev_bf16(k), H.dev_bf16(v), H.dev_i32(qo_indptr),
                    H.dev_i32(indptr), H.dev_i32(padded), H.dev_i32(last)]
         torch.cuda.synchronize()
-        queue = lk.CommandQueue(torch.cuda.Stream(), 1)
-        b = queue.bindings(9)
+        queue = lk.CommandQueue(torch.cuda.Stream(), 2)
+        b = queue.bindings(10)
         reads = [b.bind_read(t) for t in tensors]
         h_out, h_lse = b.bind_read_write(out), b.bind_read_write(lse)
+        h_ws = b.bind_read_write(workspace) if workspace is not None else None
         scope = queue.begin(b)
-        plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, h_out.write(), h_lse.write()))
+        plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, h_out.write(), h_lse.write(),
+                                                         h_ws))
         scope.finish().wait()
         assert provider.device_status() == 0
         if capacity:

@@ -42,11 +42,17 @@ class PrefillRun:
     """One paged prefill through the public API: spec -> plan -> bindings -> scope -> fence."""
 
     def __init__(self, provider, spec, q, k, v, qo_indptr, indptr, indices, last, q_tiles=0,
-                 sentinel=float("nan"), indices_capacity=False, algorithm=1):
+                 sentinel=float("nan"), indices_capacity=False, algorithm=1, partitions=1):
         self.provider, self.spec = provider, spec
         self.plan = provider.plan_bf16_paged(spec, q_tiles=q_tiles, algorithm=algorithm,
-                                             indices_capacity=indices_capacity)
-        self.queue = lk.CommandQueue(torch.cuda.Stream(), 1)
+                                             indices_capacity=indices_capacity,
+                                             partitions=partitions)
+        self.queue = lk.CommandQueue(torch.cuda.Stream(), 2)
+        # a split plan's chunk states; NaN so that a state the merge reads unwritten shows
+        self.workspace = None
+        if self.plan.workspace_required_numel():
+            self.workspace = torch.full((self.plan.workspace_required_numel(),), float("nan"),
+                                        dtype=torch.float32, device="cuda:0")
         self.tensors = [t if isinstance(t, torch.Tensor) else H.dev_bf16(t) for t in (q, k, v)]
         self.tensors += [H.dev_i32(a) for a in (qo_indptr, indptr, indices, last)]
         self.out = torch.full((spec.output_numel(),), sentinel, dtype=torch.bfloat16, device="cuda:0")
@@ -54,13 +60,15 @@ class PrefillRun:
         torch.cuda.synchronize()
 
     def run(self):
-        b = self.queue.bindings(9)
+        b = self.queue.bindings(10)
         reads = [b.bind_read(t) for t in self.tensors]
         h_out, h_lse = b.bind_read_write(self.out), b.bind_read_write(self.lse)
+        h_ws = b.bind_read_write(self.workspace) if self.workspace is not None else None
         scope = self.queue.begin(b)
-        self.plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, h_out.write(), h_lse.write()))
+        self.plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, h_out.write(), h_lse.write(),
+                                                              h_ws))
         completion = scope.finish()
-        assert completion.submitted() == 1
+        assert completion.submitted() == self.plan.commands()
         b = completion.wait()
         out, lse = b.take_read_write(h_out), b.take_read_write(h_lse)
         assert self.provider.device_status() == 0, "a kernel gave up on a bounded wait"

@@ -224,3 +224,84 @@ def test_plan_errors(fake):
     assert e.value.variant == "StateCountOutOfRange"
     with pytest.raises(lk.PlanError):
         provider.plan_bf16_paged(lk.Bf16PagedPrefillSpec.new(1, 8, 8, 4, 4), q_tiles=5)
+
+
+def test_split_plan_shape():
+    """A chunk of new tokens over a long cache has few 128-row tiles: the tiled plan shares the
+    64-token KV blocks of every tile out to several CTAs and adds a merge command."""
+    chunk = lk.Bf16PagedPrefillSpec.new(1, 128, 1024, 32, 8)  # 4 tiles x 8 KV heads, 16 K tokens
+    auto = lk.choose_paged_prefill(chunk, 148, algorithm=2)
+    assert auto.algorithm == lk.Bf16PagedPrefillAlgorithm.Tiled
+    # 32 whole tiles for 296 slots: nine chunks fill them in one wave
+    assert (auto.partitions, auto.commands) == (9, 2)
+    assert auto.grid == auto.tiles * 8 * 9 and auto.tiles == 128 * 4 // 128 + 1
+    assert auto.workspace_numel == 128 * 32 * 9 * 130
+    assert (auto.merge_grid, auto.merge_block) == (128 * 32 // 4, 128)
+    assert bytes(lk.choose_paged_prefill(chunk, 148)) == bytes(auto)  # also the plan-time choice
+    # eight whole tiles: at most sixteen chunks
+    assert lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 32, 1024, 32, 8),
+                                   148).partitions == 16
+    # little KV room in the pool: never fewer than 1024 tokens per chunk
+    small = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 128, 200, 32, 8), 148)
+    assert (small.algorithm, small.partitions, small.commands) == (1, 3, 2)
+    assert small.workspace_numel == 128 * 32 * 3 * 130
+    tiny = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 128, 40, 32, 8), 148,
+                                   algorithm=2)
+    assert (tiny.partitions, tiny.commands, tiny.workspace_numel, tiny.merge_grid) == (1, 1, 0, 0)
+    # many short requests: every request has a tile of its own, nothing to share out
+    assert lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(32, 512, 32 * 128, 32, 8),
+                                   148).partitions == 1
+    # by itself: the token-parallel kernel for few rows or next to no KV
+    for dims in ((1, 128, 12, 32, 8), (1, 64, 128, 32, 8), (2, 96, 130, 16, 4)):
+        assert lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(*dims), 148).algorithm == 0
+    assert lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 128, 40, 32, 8),
+                                   148).algorithm == 1
+    # 128 whole tiles: two chunks each
+    wide = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 512, 1024, 32, 8), 148)
+    assert (wide.algorithm, wide.partitions) == (1, 2)
+    # a long prompt fills the device by itself
+    prompt = lk.choose_paged_prefill(lk.Bf16PagedPrefillSpec.new(1, 8192, 600, 32, 8), 148)
+    assert (prompt.partitions, prompt.commands) == (1, 1)
+    # the caller's count wins, and implies the tiled kernel
+    forced = lk.choose_paged_prefill(chunk, 148, partitions=5)
+    assert (forced.algorithm, forced.partitions, forced.grid) == (1, 5, forced.tiles * 8 * 5)
+    assert lk.choose_paged_prefill(chunk, 148, algorithm=2, partitions=1).commands == 1
+    with pytest.raises(lk.ContractError) as e:
+        lk.choose_paged_prefill(chunk, 148, partitions=65)
+    assert e.value.variant == "InvalidPartitionCount"
+    with pytest.raises(lk.PlanError):
+        lk.choose_paged_prefill(chunk, 148, algorithm=1, partitions=2)
+    assert lk.choose_paged_prefill(chunk, 148, algorithm=1).partitions == 1
+
+
+def test_split_plan_reserves_both_commands_and_checks_workspace(fake):
+    spec = lk.Bf16PagedPrefillSpec.new(2, 2, 2, 4, 2)
+    plan = lk.PrefillProvider.load(0).plan_bf16_paged(spec, partitions=3)
+    numel = 2 * 4 * 3 * 130
+    assert plan.commands() == 2 and plan.partitions() == 3
+    assert plan.workspace_required_numel() == numel and plan.workspace_required_bytes() == numel * 4
+    for max_commands, workspace_numel, variant in [(1, numel, "CommandCapacityExceeded"),
+                                                   (2, numel - 1, "LengthMismatch")]:
+        queue = lk.CommandQueue(0x100, max_commands)
+        b, h, out, lse = prefill_setup(queue, spec, capacity=10)
+        ws = b.bind_read_write(D(0x40000000, workspace_numel, _abi.F32))
+        scope = queue.begin(b)
+        with pytest.raises(lk.LoomError) as e:
+            plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(output=out.write(), lse=lse.write(),
+                                                             workspace=ws, **h))
+        assert e.value.variant == variant
+        assert scope.finish().submitted() == 0
+    queue = lk.CommandQueue(0x100, 2)
+    b, h, out, lse = prefill_setup(queue, spec, capacity=10)
+    scope = queue.begin(b)
+    with pytest.raises(lk.LoomError):  # a split plan needs its workspace
+        plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(output=out.write(), lse=lse.write(), **h))
+    assert scope.finish().submitted() == 0
+    b, h, out, lse = prefill_setup(queue, spec, capacity=10)
+    ws = b.bind_read_write(D(0x40000000, numel, _abi.F32))
+    scope = queue.begin(b)
+    before = fake.lb_test_launch_count()
+    plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(output=out.write(), lse=lse.write(),
+                                                     workspace=ws, **h))
+    assert fake.lb_test_launch_count() - before == 2
+    assert scope.finish().submitted() == 2
