@@ -27,9 +27,10 @@ struct PrefillArgs {
 // qo_len tokens has ceil(qo_len * group / rows) of them) and the tile's index inside it; false
 // when the tile is past the last one or a request up to and including the owner has an invalid
 // query range (crates/loom-infer-cuda/src/attention/prefill.rs:303-317).  Every lane of the
-// calling warp returns the same.
+// calling warp returns the same.  qo_start / qo_end are the owner's query range.
 __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int rows, int tile,
-                                            int lane, int &request, int &tile_in_request) {
+                                            int lane, int &request, int &tile_in_request,
+                                            int &qo_start, int &qo_end) {
     long long before = 0;
     for (int r0 = 0; r0 < a.batch; r0 += 32) {
         const int r = r0 + lane;
@@ -56,12 +57,20 @@ __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int
             if (bad && __ffs(bad) - 1 < source) return false;
             request = r0 + source;
             tile_in_request = tile - (int)__shfl_sync(0xffffffffu, first, source);
+            qo_start = __shfl_sync(0xffffffffu, start, source);
+            qo_end = __shfl_sync(0xffffffffu, end, source);
             return true;
         }
         if (bad) return false;
         before += __shfl_sync(0xffffffffu, inclusive, 31);
     }
     return false;
+}
+
+__device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int rows, int tile,
+                                            int lane, int &request, int &tile_in_request) {
+    int qo_start, qo_end;
+    return locate_tile(a, group, rows, tile, lane, request, tile_in_request, qo_start, qo_end);
 }
 
 // The request that owns query row `row`; false when no request does or a request up to and

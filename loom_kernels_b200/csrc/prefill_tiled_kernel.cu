@@ -62,8 +62,10 @@ constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKStageBytes;
 constexpr int kOffBars = kOffV + kStages * kVStageBytes;
 // barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full s_free p_full[2] p_free[2] verdict
+// q_full (the Q tile is in shared memory and TMEM is allocated)
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
-              kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kNumBars = 15;
+              kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kBarQFull = 15,
+              kNumBars = 16;
 constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
 constexpr int kSharedBytes = kOffMisc + 24;
 static_assert(2 * (kSharedBytes + 1024) <= 233472, "two CTAs must fit one SM");
@@ -93,12 +95,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i)
-            mbar_init(bars + i * 8,
-                      i == kBarSFree || i == kBarPFull || i == kBarPFull + 1 ? 4 : 1);
+            mbar_init(bars + i * 8, i == kBarQFull ? 5
+                                    : i == kBarSFree || i == kBarPFull || i == kBarPFull + 1 ? 4
+                                                                                             : 1);
         fence_barrier_init();
         misc[1] = 0;
         misc[2] = 0;
     }
+    __syncthreads(); // the barriers exist for every warp, in particular for the producer's TMA
     if (warp == 4 && lane == 0) {
         prefetch_tensormap(&k_half_map);
         prefetch_tensormap(&v_map);
@@ -109,15 +113,22 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         if (tid == 0 && a.status) atomicExch(a.status, 2);
         return;
     }
-    if (a.qo_indptr[0] != 0 || a.qo_indptr[a.batch] != a.nnz_qo) return; // prefill.rs:289-296
-    int request, tile_in_request;
-    if (!locate_tile(a, group, kTileRows, tile, lane, request, tile_in_request)) return;
-    int page_start, page_end, tail;
-    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_min, a.indices_len, request,
-                                page_start, page_end, tail))
+    // Two dependent round trips to the metadata instead of one per check: everything that does
+    // not depend on the owner is loaded before the first value is looked at.
+    const int qo_first = a.qo_indptr[0], qo_total = a.qo_indptr[a.batch];
+    const int table_first = a.indptr[0], table_end = a.indptr[a.batch];
+    int request, tile_in_request, qo_start, qo_end;
+    const bool located =
+        locate_tile(a, group, kTileRows, tile, lane, request, tile_in_request, qo_start, qo_end);
+    if (qo_first != 0 || qo_total != a.nnz_qo || !located) return; // prefill.rs:289-317
+    int page_start = a.indptr[request];
+    const int page_end = a.indptr[request + 1], tail = a.last[request];
+    // request_metadata_valid on the values at hand
+    if (table_first != 0 || table_end < a.indices_min || table_end > a.indices_len ||
+        page_start < 0 || page_end <= page_start || page_end > table_end || tail < 1 ||
+        tail > kPage)
         return;
-    const int qo_start = a.qo_indptr[request];
-    const int qo_len = a.qo_indptr[request + 1] - qo_start;
+    const int qo_len = qo_end - qo_start;
     const int request_pages = page_end - page_start;
     const long long kv_len_wide = (long long)(request_pages - 1) * kPage + tail;
     if (qo_len > kv_len_wide) return; // prefill.rs:343-347
@@ -160,9 +171,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     }
 
     // ---- TMEM, Q tile ---------------------------------------------------------------------------------
+    // The producer warp does not wait for either: its first K/V boxes are in flight while the
+    // other warps are here.
     if (warp == 5) {
         tmem_alloc(base_u32 + kOffMisc, kTmemColumns);
         tmem_relinquish();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + kBarQFull * 8);
     }
     if (tid < kTileRows) {
         const uint4 *src = reinterpret_cast<const uint4 *>(a.query + my_state * kHeadDim);
@@ -173,11 +189,15 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                                        swizzled(tid, chunk & 7)) = value;
         }
         fence_proxy_async(); // the MMAs read Q through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + kBarQFull * 8);
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = misc[0];
+    bool q_ready = true;
+    if (warp != 4) {
+        q_ready = __all_sync(0xffffffffu, mbar_wait(bars + kBarQFull * 8, 0));
+        tc_fence_after();
+    }
+    const uint32_t tmem_base = misc[0]; // not used by the producer warp
     const uint32_t tmem_s = tmem_base + kTmemS; // scores of the block at hand
     const uint32_t tmem_p = tmem_base + kTmemP; // BF16 weights of the block, two per column
     const uint32_t tmem_o = tmem_base + kTmemO; // output accumulator
@@ -302,7 +322,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             __syncwarp();
             return true;
         };
-        bool ok = true;
+        bool ok = q_ready;
         for (int j = 0; j < blocks && ok; ++j) {
             const int stage = j & 1;
             ok = mbar_wait(bars + (kBarKFull + stage) * 8, (j >> 1) & 1);
@@ -335,8 +355,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         const float scale = a.scale_log2;
         float m_used = -INFINITY; // exponent base of P, O and the normaliser
         float l = 0.0f;
-        bool ok = true;
-        for (int j = 0; j < blocks; ++j) {
+        bool ok = q_ready;
+        for (int j = 0; q_ready && j < blocks; ++j) {
             ok = mbar_wait(bars + kBarSFull * 8, j & 1);
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
