@@ -1,8 +1,9 @@
 """Benchmark of paged causal prefill.
 
-    python -m loom_kernels_b200.prefill_bench [--cases gates,long] [--samples 10] [--q-tiles N]
+    python -m loom_kernels_b200.prefill_bench [--cases gates,long,chunked] [--samples 10]
+                                              [--q-tiles N] [--only NAME] [--plans ...]
 
-Two groups of cases:
+Three groups of cases:
   gates  the shapes the reference publishes prefill latencies for (H20, matched against FlashInfer,
          docs/results/h20-flashinfer-v0.6.16.post1-paged-prefill-{,long-}eager-performance-
          20260807.json), with its protocol (crates/loom-infer-validation/src/benchmarks/matched.rs:
@@ -10,6 +11,9 @@ Two groups of cases:
   long   prompts at serving sizes, where the operator is bound by the tensor pipe: causal FLOPs
          (4 * 128 per visible (query, key) pair and query head) over the CUDA-event time, against
          the measured BF16 GEMM throughput of this machine.
+  chunked  a chunk of new tokens behind cached ones (chunked prefill at serving shapes): per-call
+         device time of calls enqueued back to back over rotating copies of the pools, for the
+         plan's own choice, the token-parallel kernel and the tiled kernel with one CTA per tile.
 Prints one JSON object per case (JSONL).  Inputs are seeded synthetic data of the named shapes.
 """
 from __future__ import annotations
@@ -42,6 +46,26 @@ LONG_SHAPES = {
     "chunk_2048_after_14336_gqa4_32_8": ([2048], [16384], 32, 8),
     "ragged_prompts_gqa4_32_8": ([512, 3000, 64, 7000, 1500, 900, 4096, 33], None, 32, 8),
 }
+
+
+# Chunked prefill: a chunk of new tokens behind cached ones.  name -> (qo_lens, kv_lens, query
+# heads, KV heads).  Timed back to back over rotating copies of the pools (chunked_times).
+CHUNK_SHAPES = {
+    "chunk_128_of_16384": ([128], [16384], 32, 8),
+    "chunk_512_of_16384": ([512], [16384], 32, 8),
+    "chunk_1024_of_16384": ([1024], [16384], 32, 8),
+    "chunk_128_of_4096": ([128], [4096], 32, 8),
+    "chunk_32_of_8192": ([32], [8192], 32, 8),
+    "chunk_256_of_2048": ([256], [2048], 32, 8),
+    "chunk_64_of_2048": ([64], [2048], 32, 8),
+    "chunks_8x64_of_1024": ([64] * 8, [1024] * 8, 32, 8),
+    "chunks_32x16_of_2048": ([16] * 32, [2048] * 32, 32, 8),
+    "prompt_512": ([512], [512], 32, 8),
+    "chunk_128_of_512": ([128], [512], 32, 8),
+    "chunk_64_of_512": ([64], [512], 32, 8),
+}
+# plan variants of the chunked table: label -> (algorithm, partitions) options
+CHUNK_PLANS = {"plan": (0, 0), "token_parallel": (1, 0), "tiled_unsplit": (2, 1)}
 
 
 def tensor_peak_tflops():
@@ -116,9 +140,49 @@ class PrefillCase:
         return times
 
 
+def chunked_times(provider, shape, device, options, samples):
+    """Per-call device time (us) of calls enqueued back to back in one scope, rotating over
+    enough copies of the operands (2..8, at least 300 MB of K/V) that the pools do not stay in
+    L2 from one call to the next.  Returns (times, plan info of the first copy)."""
+    qo_lens, kv_lens, qh, kvh = shape
+    kv_bytes = sum(kv_lens) * kvh * 256 * 2
+    copies = max(2, min(8, int(300e6 / kv_bytes) + 1))
+    rounds = max(1, 24 // copies)
+    cases = [PrefillCase(provider, "copy", qo_lens, kv_lens, qh, kvh, device, seed=seed + 1)
+             for seed in range(copies)]
+    for case in cases:
+        case.use_plan(provider.plan_bf16_paged(case.spec, algorithm=options[0],
+                                               partitions=options[1]))
+    queue = lk.CommandQueue(torch.cuda.Stream(), 2 * copies * rounds)
+    stream = queue.stream()
+    times = []
+    for sample in range(2 + samples):
+        b = queue.bindings(10 * copies)
+        calls = []
+        for case in cases:
+            reads = [b.bind_read(t) for t in (case.q, case.k, case.v, *case.meta)]
+            out, lse = b.bind_read_write(case.out), b.bind_read_write(case.lse)
+            ws = b.bind_read_write(case.workspace) if case.workspace is not None else None
+            calls.append((case.plan, lk.Bf16PagedPrefillArgs(*reads, out.write(), lse.write(), ws)))
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        scope = queue.begin(b)
+        start.record(stream)
+        for _ in range(rounds):
+            for plan, call in calls:
+                plan.enqueue_into(scope, call)
+        end.record(stream)
+        scope.finish().wait()
+        if sample >= 2:
+            times.append(start.elapsed_time(end) * 1000.0 / (rounds * copies))
+    return times, cases[0].plan.info(), cases[0].flops()
+
+
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--cases", default="gates,long")
+    parser.add_argument("--cases", default="gates,long",
+                        help="comma list of gates, long, chunked")
+    parser.add_argument("--plans", default="plan,token_parallel,tiled_unsplit",
+                        help="chunked only: comma list of " + ", ".join(CHUNK_PLANS))
     parser.add_argument("--samples", type=int, default=10)
     parser.add_argument("--q-tiles", type=int, default=0)
     parser.add_argument("--only", default="", help="substring filter on case names")
@@ -129,6 +193,21 @@ def main():
     provider = lk.PrefillProvider.load(0)
     peak, peak_kind = tensor_peak_tflops()
     groups = args.cases.split(",")
+    if "chunked" in groups:
+        for name, shape in CHUNK_SHAPES.items():
+            if args.only and args.only not in name:
+                continue
+            line = {"case": name, "protocol": "back to back, rotating copies", "us_per_call": {}}
+            for label in args.plans.split(","):
+                times, info, flops = chunked_times(provider, shape, device, CHUNK_PLANS[label],
+                                                   args.samples)
+                median = float(np.median(times))
+                line["us_per_call"][label] = {
+                    "median": round(median, 1), "algorithm": info.algorithm,
+                    "partitions": info.partitions, "grid": info.grid,
+                    "tflops": round(flops / median / 1e6, 1)}
+            line["status"] = provider.device_status()
+            print(json.dumps(line), flush=True)
     cases = []
     if "gates" in groups:
         cases += [(name, shape[:4], 100, shape[4:]) for name, shape in GATE_SHAPES.items()]
