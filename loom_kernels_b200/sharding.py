@@ -11,7 +11,9 @@ is partitioned
     block of KV heads (and their query heads) of every request.
 
 Each rank builds its own spec, plan, queue and bindings; nothing is shared.  NCCL is used only by
-`gather_output_rows`, when the caller wants one contiguous result.
+`gather_output_rows`, when the caller wants one contiguous result.  A ragged prefill batch is
+partitioned the same way, by request, with the causal pair count as the weight
+(`prefill_assignment`, `shard_prefill`).
 """
 from __future__ import annotations
 
@@ -82,6 +84,57 @@ def balanced_assignment(kv_lens, world: int) -> List[np.ndarray]:
         owned[rank].append(int(request))
         loads[rank] += kv_lens[request]
     return [np.array(sorted(ids), dtype=np.int64) for ids in owned]
+
+
+def prefill_assignment(qo_lens, kv_lens, world: int) -> List[np.ndarray]:
+    """As balanced_assignment, for a ragged prefill batch: the weight of a request is its number
+    of visible (query, key) pairs under the bottom-right causal mask, qo * (kv - qo) +
+    qo * (qo + 1) / 2, which is what its attention costs."""
+    qo = np.asarray(qo_lens, dtype=np.int64)
+    kv = np.asarray(kv_lens, dtype=np.int64)
+    return balanced_assignment(qo * (kv - qo) + qo * (qo + 1) // 2, world)
+
+
+@dataclass
+class PrefillShard:
+    """The requests of a ragged prefill batch one rank owns, with pool-local page ids."""
+    requests: np.ndarray      # global request ids, ascending
+    qo_indptr: np.ndarray     # [n + 1], starts at 0
+    indptr: np.ndarray        # [n + 1], starts at 0
+    indices: np.ndarray       # local page ids
+    last: np.ndarray
+    global_pages: np.ndarray  # local id -> page id in the caller's global pool
+    query_rows: np.ndarray    # global query-token rows of the owned requests, in local order
+
+
+def shard_prefill(qo_indptr, indptr, indices, last, requests) -> PrefillShard:
+    """The sub-batch of `requests` (e.g. one entry of prefill_assignment): every request is
+    independent, so a rank needs only the query rows and the pages of its own requests."""
+    qo_indptr = np.asarray(qo_indptr, dtype=np.int64)
+    indptr = np.asarray(indptr, dtype=np.int64)
+    indices = np.asarray(indices)
+    requests = np.asarray(requests, dtype=np.int64)
+    qo_lens = qo_indptr[requests + 1] - qo_indptr[requests]
+    pages = indptr[requests + 1] - indptr[requests]
+    rows = (np.concatenate([np.arange(qo_indptr[r], qo_indptr[r + 1]) for r in requests])
+            if len(requests) else np.zeros(0, dtype=np.int64))
+    used = (np.concatenate([indices[indptr[r]:indptr[r + 1]] for r in requests])
+            if len(requests) else np.zeros(0, dtype=np.int64))
+    global_pages, local = np.unique(used, return_inverse=True)
+    return PrefillShard(requests,
+                        np.concatenate([[0], np.cumsum(qo_lens)]).astype(np.int32),
+                        np.concatenate([[0], np.cumsum(pages)]).astype(np.int32),
+                        local.astype(np.int32), np.asarray(last)[requests].astype(np.int32),
+                        global_pages.astype(np.int64), rows.astype(np.int64))
+
+
+def unpermute_query_rows(gathered_rows, shards_query_rows: List[np.ndarray]):
+    """gathered_rows: per-rank query-token rows concatenated in rank order -> rows in the order of
+    the unsharded batch.  shards_query_rows: PrefillShard.query_rows of every rank."""
+    order = np.concatenate(shards_query_rows)
+    inverse = np.empty_like(order)
+    inverse[order] = np.arange(len(order))
+    return gathered_rows[inverse]
 
 
 def unpermute_rows(gathered_rows, assignment: List[np.ndarray]):

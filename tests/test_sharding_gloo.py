@@ -96,6 +96,85 @@ def _worker(rank, world, port, mode, result_queue):
         dist.destroy_process_group()
 
 
+def _prefill_worker(rank, world, port, result_queue):
+    """A ragged prefill batch split by request over two ranks (weights: causal pairs): each rank
+    runs its sub-batch on its own pool with local page ids; the gathered query rows, put back in
+    batch order, equal the unsharded result bit for bit."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle
+        rng = np.random.default_rng(123)
+        qh, kvh, pool = 8, 2, 64
+        qo_lens = np.array([9, 1, 40, 3, 17])
+        kv_lens = np.array([70, 16, 40, 120, 33])
+        pages = (kv_lens + 15) // 16
+        indices = rng.permutation(pool)[:pages.sum()].astype(np.int32)
+        indptr = np.concatenate([[0], np.cumsum(pages)]).astype(np.int32)
+        qo_indptr = np.concatenate([[0], np.cumsum(qo_lens)]).astype(np.int32)
+        last = ((kv_lens - 1) % 16 + 1).astype(np.int32)
+        nnz = int(qo_indptr[-1])
+        q = oracle.fixture_bf16(nnz * qh * 128, 1)
+        k = oracle.fixture_bf16(pool * 16 * kvh * 128, 2)
+        v = oracle.fixture_bf16(pool * 16 * kvh * 128, 3)
+        full_o, full_lse = oracle.paged_prefill(oracle.prefill_spec(len(qo_lens), nnz, pool, qh, kvh),
+                                                q, k, v, qo_indptr, indptr, indices, last)
+        owned = sharding.prefill_assignment(qo_lens, kv_lens, world)
+        shards = [sharding.shard_prefill(qo_indptr, indptr, indices, last, ids) for ids in owned]
+        mine = shards[rank]
+        n, rows = len(mine.requests), len(mine.query_rows)
+        qr = q.reshape(nnz, qh * 128)[mine.query_rows].ravel()
+        kr = k.reshape(pool, -1)[mine.global_pages].ravel()
+        vr = v.reshape(pool, -1)[mine.global_pages].ravel()
+        o, lse = oracle.paged_prefill(
+            oracle.prefill_spec(n, rows, len(mine.global_pages), qh, kvh), qr, kr, vr,
+            mine.qo_indptr, mine.indptr, mine.indices, mine.last)
+        counts = [len(s.query_rows) for s in shards]
+        gathered = sharding.gather_output_rows(
+            torch.from_numpy(o.view(np.uint8).reshape(rows, qh * 256).copy()), counts)
+        got = sharding.unpermute_query_rows(gathered.numpy(), [s.query_rows for s in shards])
+        lse_all = sharding.gather_output_rows(torch.from_numpy(lse.reshape(rows, qh).copy()), counts)
+        got_lse = sharding.unpermute_query_rows(lse_all.numpy(), [s.query_rows for s in shards])
+        ok = (np.array_equal(got.view(np.uint16).ravel(), full_o)
+              and np.array_equal(got_lse.ravel(), full_lse)
+              and sorted(np.concatenate(owned).tolist()) == list(range(len(qo_lens))))
+        result_queue.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_prefill_assignment_balances_causal_pairs():
+    qo = np.array([8192, 512, 128, 2048, 64, 4096, 1024, 33])
+    kv = np.array([8192, 16384, 16384, 2048, 8192, 4096, 9000, 33])
+    owned = sharding.prefill_assignment(qo, kv, 4)
+    assert sorted(np.concatenate(owned).tolist()) == list(range(8))
+    pairs = qo * (kv - qo) + qo * (qo + 1) // 2
+    loads = np.array([pairs[ids].sum() for ids in owned])
+    assert loads.max() == pairs.max()  # the longest prompt has a rank to itself
+    shard = sharding.shard_prefill(np.concatenate([[0], np.cumsum(qo)]),
+                                   np.concatenate([[0], np.cumsum((kv + 15) // 16)]),
+                                   np.arange(((kv + 15) // 16).sum()), (kv - 1) % 16 + 1, owned[1])
+    assert shard.qo_indptr[-1] == qo[owned[1]].sum() == len(shard.query_rows)
+    assert shard.indptr[-1] == len(shard.indices) == len(shard.global_pages)
+    assert np.array_equal(shard.global_pages[shard.indices[:3]],
+                          np.arange(((kv + 15) // 16).sum())[
+                              np.concatenate([[0], np.cumsum((kv + 15) // 16)])[owned[1][0]]:][:3])
+
+
+def test_two_rank_prefill_sharding_reproduces_the_full_batch(oracle):
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_prefill_worker, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    got = dict(results.get(timeout=5) for _ in range(2))
+    assert got == {0: True, 1: True}
+
+
 def _failing_worker(rank, world, port, result_queue):
     """Rank 1's enqueue fails on the host (a launch failure injected through the fake driver);
     it reports that instead of skipping the collective, and every rank gets ShardFailure."""
