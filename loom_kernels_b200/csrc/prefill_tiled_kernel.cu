@@ -375,13 +375,17 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
 #pragma unroll
                 for (int i = 0; i < kBlockTokens; ++i) s[i] = i < limit ? s[i] : -INFINITY;
             }
-            float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+            // four chains of three-input maxima: 32 instructions, eight deep
+            float chain[4];
 #pragma unroll
-            for (int i = 4; i < kBlockTokens; i += 2) {
-                mx0 = fmaxf(mx0, s[i]);
-                mx1 = fmaxf(mx1, s[i + 1]);
+            for (int c = 0; c < 4; ++c) chain[c] = fmaxf(s[c * 16], s[c * 16 + 1]);
+#pragma unroll
+            for (int i = 2; i < 16; i += 2) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) chain[c] = max3(chain[c], s[c * 16 + i], s[c * 16 + i + 1]);
             }
-            const float mx = fmaxf(mx0, mx1) * scale; // scale > 0; -inf stays -inf
+            // scale > 0; -inf stays -inf
+            const float mx = fmaxf(fmaxf(chain[0], chain[1]), fmaxf(chain[2], chain[3])) * scale;
             if (j == kProbeBlock) LB_STAMPV(2, mx);
             if (j == kProbeBlock) LB_STAMP(3);
             // the exponent base follows the maximum lazily: P <= 2^8 keeps BF16 P and the F32
@@ -410,29 +414,26 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 }
             }
             const float neg_base = m_used == -INFINITY ? 0.0f : -m_used;
-            // the weights are double-buffered: this buffer is free once P V (j - 2) has completed,
-            // which it has long before (the wait costs one look at the barrier)
-            if (j >= 2) {
-                ok = mbar_wait(bars + (kBarPFree + (j & 1)) * 8, ((j - 2) >> 1) & 1);
-                if (__any_sync(0xffffffffu, !ok)) break;
-                tc_fence_after();
-            }
-            float sum0 = 0.0f, sum1 = 0.0f;
+            // The weights are double-buffered, and this buffer is free: P V (j - 2) was issued
+            // before S(j) by the same elected thread, and the commit behind s_full(j), which this
+            // warp has seen, covers every MMA that thread issued before it.
             float packed[kBlockTokens / 2]; // BF16 pairs (token 2c in the low half), as raw bits
+            // the scaling and the row sum on pairs (fma / add .f32x2: one instruction per two
+            // weights), the exponentials one by one
+            const float2 scale2 = make_float2(scale, scale), base2 = make_float2(neg_base, neg_base);
+            float2 sums[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
+                              make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int chunk = 0; chunk < kBlockTokens / 8; ++chunk) {
-                float p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[chunk * 8 + i], scale, neg_base));
-                sum0 += (p[0] + p[1]) + (p[2] + p[3]);
-                sum1 += (p[4] + p[5]) + (p[6] + p[7]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    packed[chunk * 4 + i] = __uint_as_float(pack_bf16(p[2 * i], p[2 * i + 1]));
+            for (int i = 0; i < kBlockTokens / 2; ++i) {
+                const float2 x = fma2(make_float2(s[2 * i], s[2 * i + 1]), scale2, base2);
+                const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                sums[i & 3] = add2(sums[i & 3], p);
+                packed[i] = __uint_as_float(pack_bf16(p.x, p.y));
             }
             tmem_store32(tmem_p + (j & 1) * 32 + lane_base, packed);
             tmem_store_wait();
-            l += sum0 + sum1;
+            const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
+            l += total.x + total.y;
             if (j == kProbeBlock) LB_STAMPV(4, l);
             // rows of the request's last page past its length may hold anything (0 * NaN): zero
             // them in the V block before the MMA reads it
