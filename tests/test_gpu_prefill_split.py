@@ -206,3 +206,62 @@ def test_fixed_address_graph_replays(provider, oracle):
         check(H.host_bits(out), lse.cpu().numpy(), expected, expected_lse, gate=False)
     assert provider.device_status() == 0
     exec_.into_bindings()
+
+
+def test_many_requests_span_several_scan_windows(provider, oracle):
+    """More than 32 requests: the main kernel finds the owner of a tile and the merge kernel the
+    owner of a row across prefix-scan windows; a malformed query range in the third window stops
+    every request from there on, and only those."""
+    rng = np.random.default_rng(79)
+    qo_lens = [int(n) for n in rng.integers(1, 40, size=75)]
+    kv_lens = [q + int(n) for q, n in zip(qo_lens, rng.integers(0, 300, size=75))]
+    pool = 900
+    case = ragged_case(rng, qo_lens, kv_lens, 16, 4, pool)
+    q, k, v, qo_indptr, indptr, indices, last = case
+    nnz = sum(qo_lens)
+    dims = (75, nnz, pool, 16, 4)
+    expected, expected_lse = oracle.paged_prefill(oracle.prefill_spec(*dims), *case, threads=8)
+    spec = lk.Bf16PagedPrefillSpec.new(*dims)
+    for partitions in (2, 3):
+        actual, actual_lse = PrefillRun(provider, spec, *case, algorithm=TILED,
+                                        partitions=partitions).run()
+        check(actual, actual_lse, expected, expected_lse, gate=False)
+    broken = np.asarray(qo_indptr).copy()
+    broken[70] = broken[69]  # request 69 is empty: it and every later request are rejected
+    out, lse = PrefillRun(provider, spec, q, k, v, broken, indptr, indices, last, algorithm=TILED,
+                          partitions=2).run()
+    written = np.isfinite(lse.reshape(nnz, 16)).all(axis=1)
+    assert written[:broken[69]].all() and not written[broken[69]:].any()
+    check(out[:broken[69] * 16 * 128], lse[:broken[69] * 16], expected[:broken[69] * 16 * 128],
+          expected_lse[:broken[69] * 16], gate=False)
+
+
+def test_split_and_unsplit_plans_agree_on_a_long_chunk(provider, oracle):
+    """Size-independent property at a serving size the CPU oracle cannot cover in a test: 256 new
+    tokens behind 12 000 cached ones give the same rows whether a tile has one CTA or nine, and
+    sampled rows agree with the oracle."""
+    rng = np.random.default_rng(83)
+    chunk, total, qh, kvh, pool = 256, 12256, 16, 4, 800
+    q, k, v, qo_indptr, indptr, indices, last = ragged_case(rng, [chunk], [total], qh, kvh, pool)
+    spec = lk.Bf16PagedPrefillSpec.new(1, chunk, pool, qh, kvh)
+    whole, whole_lse = PrefillRun(provider, spec, q, k, v, qo_indptr, indptr, indices, last,
+                                  algorithm=TILED, partitions=1).run()
+    auto = PrefillRun(provider, spec, q, k, v, qo_indptr, indptr, indices, last, algorithm=0,
+                      partitions=0)
+    assert auto.plan.algorithm() == lk.Bf16PagedPrefillAlgorithm.Tiled
+    assert auto.plan.partitions() == 9  # 32 whole tiles for 296 slots
+    shared, shared_lse = auto.run()
+    check(shared, shared_lse, whole, whole_lse, gate=False)
+    rows = [0, 1, 100, 255]
+    spec_rows = oracle.prefill_spec(len(rows), len(rows), pool, qh, kvh)
+    q_rows = np.concatenate([q[r * qh * 128:(r + 1) * qh * 128] for r in rows])
+    seen = [total - chunk + r + 1 for r in rows]
+    row_pages = [(n + 15) // 16 for n in seen]
+    expected, expected_lse = oracle.paged_prefill(
+        spec_rows, q_rows, k, v, np.arange(len(rows) + 1),
+        np.concatenate([[0], np.cumsum(row_pages)]).astype(np.int32),
+        np.concatenate([indices[:n] for n in row_pages]), [(n - 1) % 16 + 1 for n in seen],
+        threads=16)
+    sample = np.concatenate([shared[r * qh * 128:(r + 1) * qh * 128] for r in rows])
+    sample_lse = np.concatenate([shared_lse[r * qh:(r + 1) * qh] for r in rows])
+    check(sample, sample_lse, expected, expected_lse, gate=False)
