@@ -15,17 +15,22 @@
 //                                 shared memory with the 128-byte swizzle), accumulator S in TMEM
 //                  softmax        each thread pulls its S row out of TMEM (tcgen05.ld), masks it
 //                                 with the row's causal limit where the block crosses it, and
-//                                 writes P = 2^(S - m) as BF16 into shared memory in the A-operand
-//                                 layout; the exponent base m follows the running maximum lazily
-//                                 (only a rise of more than 8 rescales O and the normaliser,
-//                                 through tcgen05.ld/st)
-//                  O += P V       one tcgen05.mma 128x128x16 per page (A = P, B = the V page, which
-//                                 is MN-major: 64 dims contiguous per 128-byte row), O in TMEM
+//                                 writes P = 2^(S - m) as BF16 pairs back into TMEM
+//                                 (tcgen05.st, double-buffered); the exponent base m follows the
+//                                 running maximum lazily (only a rise of more than 8 rescales O
+//                                 and the normaliser, through tcgen05.ld/st)
+//                  O += P V       one tcgen05.mma 128x128x16 per page (A = P from TMEM, B = the V
+//                                 page, which is MN-major: 64 dims contiguous per 128-byte row),
+//                                 O in TMEM
 //   pipelining = K and V blocks are double-buffered by TMA; the S MMAs of block j + 1 are issued
 //                before the P V MMAs of block j, so the next scores are ready when the softmax
 //                warps finish the current block.
 //   shared mem = Q 32 KB | K 2 x 16 KB | V 2 x 16 KB | barriers
 //   TMEM       = 256 columns: S (64 x F32) | P (2 x 32 columns of BF16 pairs) | O (128 x F32)
+//   split KV   = a plan with partitions > 1 gives the 64-token blocks of a tile to that many CTAs
+//                (the balanced rule of the split-K contract); each writes the unnormalised state
+//                [max_log2, normaliser, weighted values] of its share into a workspace and
+//                prefill_merge_kernel, a second command, merges them per (query row, head).
 //
 // Device-resident metadata is never an error (prefill.rs:289-347).  Every mbarrier wait is bounded;
 // after a timeout every role leaves its loop, the CTA frees its TMEM, records a status word and
