@@ -63,6 +63,12 @@ CHUNK_SHAPES = {
     "prompt_512": ([512], [512], 32, 8),
     "chunk_128_of_512": ([128], [512], 32, 8),
     "chunk_64_of_512": ([64], [512], 32, 8),
+    # a few query tokens per request over a large batch (multi-token verification, the 1-64-token
+    # append followed by attention): HBM-bound like decode
+    "verify_8_b64_ctx4096": ([8] * 64, [4096] * 64, 32, 8),
+    "verify_4_b256_ctx1024": ([4] * 256, [1024] * 256, 32, 8),
+    "verify_8_b16_ctx8192": ([8] * 16, [8192] * 16, 32, 8),
+    "verify_8_b8_ctx32768_gqa8": ([8] * 8, [32768] * 8, 64, 8),
 }
 # plan variants of the chunked table: label -> (algorithm, partitions) options
 CHUNK_PLANS = {"plan": (0, 0), "token_parallel": (1, 0), "tiled_unsplit": (2, 1)}
@@ -202,10 +208,12 @@ def main():
                 times, info, flops = chunked_times(provider, shape, device, CHUNK_PLANS[label],
                                                    args.samples)
                 median = float(np.median(times))
+                kv_bytes = sum(shape[1]) * shape[3] * 128 * 2 * 2  # K and V of every request once
                 line["us_per_call"][label] = {
                     "median": round(median, 1), "algorithm": info.algorithm,
                     "partitions": info.partitions, "grid": info.grid,
-                    "tflops": round(flops / median / 1e6, 1)}
+                    "tflops": round(flops / median / 1e6, 1),
+                    "kv_gbs": round(kv_bytes / median / 1e3, 0)}
             line["status"] = provider.device_status()
             print(json.dumps(line), flush=True)
     cases = []
