@@ -115,6 +115,9 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         (algorithm_option == 0 && q_tiles == 0 &&
          (partitions > 1 ||
           (full_tiles >= 1 && ((packed_rows >= 512 && average_kv >= 256) || average_kv >= 4096))));
+    // chunks exist only in the tiled kernel: a count next to a token-parallel tile shape is a
+    // contradiction, not something to drop silently
+    if (!tiled && partitions > 1) return fail(LB_LAUNCH_CONTRACT, "partitions", partitions);
     if (tiled) {
         const uint32_t shared = (uint32_t)prefill_tiled_shared_bytes();
         if (shared > smem) return fail(LB_LAUNCH_CONTRACT, "shared_memory", shared);

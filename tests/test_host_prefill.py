@@ -271,6 +271,8 @@ def test_split_plan_shape():
     assert e.value.variant == "InvalidPartitionCount"
     with pytest.raises(lk.PlanError):
         lk.choose_paged_prefill(chunk, 148, algorithm=1, partitions=2)
+    with pytest.raises(lk.PlanError):  # a token-parallel tile shape and a chunk count
+        lk.choose_paged_prefill(chunk, 148, q_tiles=2, partitions=2)
     assert lk.choose_paged_prefill(chunk, 148, algorithm=1).partitions == 1
 
 
