@@ -171,3 +171,45 @@ def test_chunk_after_a_long_cache(provider, oracle):
         actual, actual_lse = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(*dims), *case,
                                         algorithm=algorithm).run()
         check(actual, actual_lse, expected, expected_lse, gate=False)
+
+
+def test_full_size_prompt_properties(provider, oracle):
+    """An 8192-token prompt at serving head counts (32 query / 8 KV heads), the size of the prefill
+    bench line, through size-independent properties over EVERY row: prefilling the prompt in two
+    chunks gives, bit for bit, the rows of the one-shot call (the mask is bottom-right aligned and
+    a row's arithmetic does not depend on its tile); a second run of the same plan repeats the
+    first bit for bit; the plan with the KV range shared out agrees within the parity limits; and
+    sampled rows agree with the CPU oracle."""
+    rng = np.random.default_rng(61)
+    total, first, qh, kvh, pool = 8192, 5000, 32, 8, 520
+    q, k, v, qo_indptr, indptr, indices, last = ragged_case(rng, [total], [total], qh, kvh, pool)
+    kd, vd = H.dev_bf16(k), H.dev_bf16(v)
+    whole = lk.Bf16PagedPrefillSpec.new(1, total, pool, qh, kvh)
+    run = PrefillRun(provider, whole, q, kd, vd, qo_indptr, indptr, indices, last, algorithm=TILED)
+    one_shot, one_lse = run.run()
+    again, again_lse = run.run()
+    assert np.array_equal(again, one_shot)
+    assert np.array_equal(again_lse.view(np.uint32), one_lse.view(np.uint32))
+    pages1 = (first + 15) // 16
+    out1, lse1 = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(1, first, pool, qh, kvh),
+                            q[:first * qh * 128], kd, vd, [0, first], [0, pages1],
+                            indices[:pages1], [(first - 1) % 16 + 1], algorithm=TILED).run()
+    out2, lse2 = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(1, total - first, pool, qh, kvh),
+                            q[first * qh * 128:], kd, vd, [0, total - first], indptr, indices,
+                            last, algorithm=TILED).run()
+    assert np.array_equal(np.concatenate([out1, out2]), one_shot)
+    assert np.array_equal(np.concatenate([lse1, lse2]).view(np.uint32), one_lse.view(np.uint32))
+    shared, shared_lse = PrefillRun(provider, whole, q, kd, vd, qo_indptr, indptr, indices, last,
+                                    algorithm=TILED, partitions=3).run()
+    check(shared, shared_lse, one_shot, one_lse, gate=False)
+    rows = [0, 63, 64, 4999, 5000, 8191]
+    spec_rows = oracle.prefill_spec(len(rows), len(rows), pool, qh, kvh)
+    q_rows = np.concatenate([q[r * qh * 128:(r + 1) * qh * 128] for r in rows])
+    row_pages = [(r + 16) // 16 for r in rows]
+    expected, expected_lse = oracle.paged_prefill(
+        spec_rows, q_rows, k, v, np.arange(len(rows) + 1),
+        np.concatenate([[0], np.cumsum(row_pages)]).astype(np.int32),
+        np.concatenate([indices[:n] for n in row_pages]), [r % 16 + 1 for r in rows], threads=16)
+    sample = np.concatenate([one_shot[r * qh * 128:(r + 1) * qh * 128] for r in rows])
+    sample_lse = np.concatenate([one_lse[r * qh:(r + 1) * qh] for r in rows])
+    check(sample, sample_lse, expected, expected_lse, gate=False)
