@@ -547,8 +547,8 @@ typedef struct lb_paged_prefill_options {
     uint32_t algorithm;        /* 0 = plan-time heuristic, 1 = token-parallel, 2 = tiled */
     uint32_t partitions;       /* tiled only.  0 = plan-time heuristic, 1 = one CTA per tile, N > 1
                                   (at most 64) = the 64-token KV blocks of every tile are shared
-                                  out to N CTAs by the balanced rule of the split-K contract
-                                  (single_decode/mod.rs:171-185) */
+                                  out to up to N CTAs by the balanced rule of the split-K contract
+                                  (single_decode/mod.rs:171-185); see min_chunk_blocks */
     uint32_t reserved[4];
 } lb_paged_prefill_options;
 
@@ -561,6 +561,11 @@ typedef struct lb_paged_prefill_plan_info {
     uint32_t commands;      /* 1, or 2 when partitions > 1 */
     uint32_t partitions;    /* KV chunks per tile (1 unless tiled) */
     uint32_t merge_grid, merge_block; /* second command of a split plan */
+    uint32_t min_chunk_blocks; /* on the device a tile of B 64-token blocks uses
+                                  min(partitions, max(1, B / min_chunk_blocks)) chunks, and a tile
+                                  of one chunk is finished by the first command: 16 when the plan
+                                  chose the count (the KV length is not known at plan time), 1
+                                  when the caller did */
     size_t workspace_numel; /* F32 elements the caller must bind: nnz_qo * qh * partitions * 130,
                                0 when partitions == 1 */
 } lb_paged_prefill_plan_info;

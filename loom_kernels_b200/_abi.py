@@ -112,7 +112,8 @@ class PrefillPlanInfo(ctypes.Structure):
                 ("stages", c_uint32), ("rows_per_cta", c_uint32), ("tiles", c_uint32),
                 ("grid", c_uint32), ("block", c_uint32), ("shared_bytes", c_uint32),
                 ("commands", c_uint32), ("partitions", c_uint32), ("merge_grid", c_uint32),
-                ("merge_block", c_uint32), ("workspace_numel", c_size_t)]
+                ("merge_block", c_uint32), ("min_chunk_blocks", c_uint32),
+                ("workspace_numel", c_size_t)]
 
 
 class PrefillArgs(ctypes.Structure):

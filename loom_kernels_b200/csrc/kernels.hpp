@@ -93,6 +93,7 @@ struct PrefillLaunch {
     // tiled plans that cut a tile's KV range into chunks: F32 states [nnz_qo * qh][partitions][130]
     float *workspace;
     int32_t partitions;
+    int32_t min_chunk_blocks; // a tile uses min(partitions, its blocks / min_chunk_blocks) chunks
 };
 int configure_prefill_kernels(size_t max_dynamic_shared);
 int launch_paged_prefill(const PrefillLaunch &launch, void *stream);

@@ -21,7 +21,17 @@ struct PrefillArgs {
     // writes O and LSE directly
     float *workspace;
     int32_t partitions;
+    // a tile uses min(partitions, blocks of the tile / min_chunk_blocks) chunks, at least one:
+    // the count follows the KV length actually met, which a plan cannot know
+    int32_t min_chunk_blocks;
 };
+
+// Chunks a tile of `tile_blocks` 64-token blocks is cut into.  One chunk means the CTA writes O and
+// LSE itself and the merge leaves the row alone.
+__device__ __forceinline__ int chunks_of_tile(int tile_blocks, int partitions, int min_chunk_blocks) {
+    const int wanted = tile_blocks / min_chunk_blocks;
+    return wanted < 1 ? 1 : (wanted < partitions ? wanted : partitions);
+}
 
 // The request that owns row tile `tile` (tiles are numbered request by request; a request of
 // qo_len tokens has ceil(qo_len * group / rows) of them) and the tile's index inside it; false
@@ -73,16 +83,26 @@ __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int
     return locate_tile(a, group, rows, tile, lane, request, tile_in_request, qo_start, qo_end);
 }
 
-// The request that owns query row `row`; false when no request does or a request up to and
-// including the owner has an invalid query range (the guard of locate_tile, per row).
-__device__ __forceinline__ bool locate_row(const int32_t *qo_indptr, int batch, int nnz_qo, int row,
-                                           int lane, int &request) {
+// The request that owns query row `row`, with its query range, page range and last-page length
+// (all loaded in the same round trip as the query ranges that are searched: lane l of a window
+// loads the metadata of request r0 + l, the owner's lane hands its values out); false when no
+// request does or a request up to and including the owner has an invalid query range (the guard
+// of locate_tile, per row).
+struct RowOwner {
+    int request, qo_start, qo_end, page_start, page_end, tail;
+};
+__device__ __forceinline__ bool locate_row(const int32_t *qo_indptr, const int32_t *indptr,
+                                           const int32_t *last, int batch, int nnz_qo, int row,
+                                           int lane, RowOwner &owner) {
     for (int r0 = 0; r0 < batch; r0 += 32) {
         const int r = r0 + lane;
-        int start = 0, end = 0;
+        int start = 0, end = 0, page_start = 0, page_end = 0, tail = 0;
         if (r < batch) {
             start = qo_indptr[r];
             end = qo_indptr[r + 1];
+            page_start = indptr[r];
+            page_end = indptr[r + 1];
+            tail = last[r];
         }
         const bool valid = r >= batch || (start >= 0 && end > start && end <= nnz_qo);
         const unsigned bad = __ballot_sync(0xffffffffu, !valid);
@@ -90,7 +110,12 @@ __device__ __forceinline__ bool locate_row(const int32_t *qo_indptr, int batch, 
         if (hit) {
             const int source = __ffs(hit) - 1;
             if (bad && __ffs(bad) - 1 < source) return false;
-            request = r0 + source;
+            owner.request = r0 + source;
+            owner.qo_start = __shfl_sync(0xffffffffu, start, source);
+            owner.qo_end = __shfl_sync(0xffffffffu, end, source);
+            owner.page_start = __shfl_sync(0xffffffffu, page_start, source);
+            owner.page_end = __shfl_sync(0xffffffffu, page_end, source);
+            owner.tail = __shfl_sync(0xffffffffu, tail, source);
             return true;
         }
         if (bad) return false;

@@ -318,6 +318,7 @@ int launch_paged_prefill(const PrefillLaunch &launch, void *stream) {
     args.scale_log2 = launch.scale_log2;
     args.workspace = nullptr;
     args.partitions = 1;
+    args.min_chunk_blocks = 1;
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));

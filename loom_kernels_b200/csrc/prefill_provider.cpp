@@ -122,12 +122,18 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         const uint32_t shared = (uint32_t)prefill_tiled_shared_bytes();
         if (shared > smem) return fail(LB_LAUNCH_CONTRACT, "shared_memory", shared);
         const size_t tiles = packed_rows / 128 + spec.batch_size;
+        uint32_t min_chunk_blocks = 1; // the caller's count is taken literally
         if (partitions == 0) {
+            min_chunk_blocks = 16;
             // Two CTAs run per SM.  When the tiles are fewer than half of those slots, the
             // 64-token KV blocks of every tile are shared out to several CTAs -- as many as fit
             // the slots in one wave, never fewer than sixteen blocks (1024 tokens of the average
             // request's room in the pool) per CTA, at most sixteen CTAs -- and a second command
-            // merges their states.  Every request has at least one tile per KV head.
+            // merges their states.  Every request has at least one tile per KV head.  The pool's
+            // room is an upper bound of the KV lengths a call will bring (an engine's pool is
+            // usually its whole cache), so the kernels apply the sixteen-block rule again to the
+            // length they meet: a tile too short for two chunks is finished by the first command
+            // alone (min_chunk_blocks).
             const size_t slots = 2 * (size_t)sms;
             const size_t request_tiles = spec.batch_size * spec.num_kv_heads;
             const size_t work = full_tiles > request_tiles ? full_tiles : request_tiles;
@@ -158,6 +164,7 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
         out->partitions = partitions;
         out->merge_grid = partitions > 1 ? (uint32_t)((states + 3) / 4) : 0;
         out->merge_block = partitions > 1 ? 128 : 0;
+        out->min_chunk_blocks = min_chunk_blocks;
         out->workspace_numel = workspace;
         return LB_OK;
     }
@@ -489,6 +496,7 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
     launch.shared_bytes = c.shared_bytes;
     launch.workspace = split ? (float *)op[9].ptr : nullptr;
     launch.partitions = (int32_t)c.partitions;
+    launch.min_chunk_blocks = (int32_t)c.min_chunk_blocks;
     void *stream = scope->queue->stream;
     if ((rc = submit_launch(*scope, [&]() {
              return tiled ? launch_paged_prefill_tiled(launch, stream)

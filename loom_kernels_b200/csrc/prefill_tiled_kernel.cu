@@ -148,8 +148,10 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     const int chunk = (int)(blockIdx.x / a.kvh) % a.partitions;
     const int tile_pages = (cta_limit + kPage - 1) / kPage; // pages the tile's last row sees
     const int tile_blocks = (tile_pages + kBlockPages - 1) / kBlockPages;
-    const int block0 = chunk * (tile_blocks / a.partitions) + min(chunk, tile_blocks % a.partitions);
-    const int blocks = tile_blocks / a.partitions + (chunk < tile_blocks % a.partitions ? 1 : 0);
+    const int chunks = chunks_of_tile(tile_blocks, a.partitions, a.min_chunk_blocks);
+    if (chunk >= chunks) return; // the tile is too short for this many chunks: nothing to do
+    const int block0 = chunk * (tile_blocks / chunks) + min(chunk, tile_blocks % chunks);
+    const int blocks = tile_blocks / chunks + (chunk < tile_blocks % chunks ? 1 : 0);
     // from here on pages, blocks and tokens are counted from the start of the share
     page_start += block0 * kBlockPages;
     const int num_pages = request_pages - block0 * kBlockPages; // up to the request's last page
@@ -167,13 +169,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         const int chunk = (int)(blockIdx.x / a.kvh) % a.partitions;
         return a.workspace + (my_state * a.partitions + chunk) * kStateWidth;
     };
-    if (blocks == 0) { // more chunks than blocks: an empty state (the merge gives it weight 0)
-        if (row_valid) {
-            float2 *state = reinterpret_cast<float2 *>(partial_state());
-            for (int i = 0; i < kStateWidth / 2; ++i) state[i] = make_float2(0.0f, 0.0f);
-        }
-        return;
-    }
 
     // ---- TMEM, Q tile ---------------------------------------------------------------------------------
     // The producer warp does not wait for either: its first K/V boxes are in flight while the
@@ -472,7 +467,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 tc_fence_after();
                 const bool verdict = mbar_wait(bars + kBarVerdict * 8, 0); // the producer's page scan
                 const bool settled = verdict && row_valid && misc[2] == 0;
-                float *my_partial = a.partitions > 1 ? partial_state() : nullptr;
+                float *my_partial = chunks > 1 ? partial_state() : nullptr;
                 const bool publish = settled && misc[1] == 0 && my_partial == nullptr;
                 const float inv = 1.0f / l;
                 uint4 *dst = reinterpret_cast<uint4 *>(a.output + my_state * kHeadDim);
@@ -514,44 +509,58 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     if (warp == 5) tmem_dealloc(tmem_base, kTmemColumns);
     if (tid == 0 && misc[2] != 0 && a.status) atomicExch(a.status, 1);
     // a chunk that gave up on a wait poisons its states, so that the merge publishes nothing
-    if (misc[2] != 0 && a.partitions > 1 && row_valid) partial_state()[1] = -1.0f;
+    if (misc[2] != 0 && chunks > 1 && row_valid) partial_state()[1] = -1.0f;
 }
 
 // Merges the chunk states of one (query row, query head) per warp and writes BF16 O + log2 LSE
-// (merge_states).  The row's request is checked again here -- the global checks, every query
-// range up to the owner, its page range and qo_len <= kv_len (prefill.rs:289-347) -- because a
-// CTA of the main kernel that rejects a request writes no state; a bad page id arrives as a
-// poisoned state.
+// (merge_partial, publish_merged).  The row's request is checked again here -- the global checks,
+// every query range up to the owner, its page range and qo_len <= kv_len (prefill.rs:289-347) --
+// because a CTA of the main kernel that rejects a request writes no state; a bad page id arrives
+// as a poisoned state.  The number of chunks of the row's tile is recomputed from the metadata
+// as the main kernel computed it; a tile of one chunk was finished there.
 __global__ void __launch_bounds__(128, 5)
 prefill_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                      const int32_t *qo_indptr, const int32_t *indptr, const int32_t *last, int batch,
-                     int nnz_qo, int qh, int partitions, int indices_min, int indices_len) {
+                     int nnz_qo, int qh, int kvh, int partitions, int min_chunk_blocks,
+                     int indices_min, int indices_len) {
     dependent_launch_release();
     const int lane = threadIdx.x & 31;
     const long long state = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= (long long)nnz_qo * qh) return;
     const int row = (int)(state / qh);
     dependent_launch_wait(); // the chunk states are complete and visible
-    const bool global_ok = qo_indptr[0] == 0 && qo_indptr[batch] == nnz_qo;
-    int request = 0;
-    const bool located = locate_row(qo_indptr, batch, nnz_qo, row, lane, request);
-    // The owner's page range is loaded here and judged after the merge: its loads and those of
-    // the states are in flight together.
+    // one round trip for the metadata, one for the states
+    const int qo_first = qo_indptr[0], qo_total = qo_indptr[batch];
     const int global_end = indptr[batch], first = indptr[0];
-    const int page_start = indptr[request], page_end = indptr[request + 1], tail = last[request];
-    const int qo_len = qo_indptr[request + 1] - qo_indptr[request];
+    RowOwner o;
+    const bool located = locate_row(qo_indptr, indptr, last, batch, nnz_qo, row, lane, o);
+    if (!located || qo_first != 0 || qo_total != nnz_qo) return;
+    // request_metadata_valid and qo_len <= kv_len
+    const int qo_len = o.qo_end - o.qo_start;
+    const long long kv_len = (long long)(o.page_end - o.page_start - 1) * kPage + o.tail;
+    if (first != 0 || global_end < indices_min || global_end > indices_len || o.page_start < 0 ||
+        o.page_end <= o.page_start || o.page_end > global_end || o.tail < 1 || o.tail > kPage ||
+        qo_len > kv_len)
+        return;
+    // the row's tile: 128 packed (token, head-in-group) rows of one KV head (32-bit arithmetic:
+    // a plan admits at most 2^32 states)
+    const unsigned group = (unsigned)(qh / kvh);
+    const unsigned packed = (unsigned)(row - o.qo_start) * group + ((unsigned)state % (unsigned)qh) % group;
+    const unsigned rows_total = (unsigned)qo_len * group;
+    const unsigned tile_end = (packed / kTileRows + 1) * kTileRows;
+    const unsigned row_hi = tile_end < rows_total ? tile_end : rows_total;
+    const int tile_limit = (int)(kv_len - qo_len + 1) + (int)((row_hi - 1) / group); // tokens seen
+    const int tile_pages = (tile_limit + kPage - 1) / kPage;
+    const int chunks = chunks_of_tile((tile_pages + kBlockPages - 1) / kBlockPages, partitions,
+                                      min_chunk_blocks);
+    if (chunks == 1) return; // written by the main kernel
     const float *st = workspace + (size_t)state * partitions * kStateWidth;
     float top, norm;
     float4 acc;
-    if (!merge_partial([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane, top,
-                       norm, acc))
+    if (!merge_partial([&](int p) { return st + (size_t)p * kStateWidth; }, chunks, lane, top, norm,
+                       acc))
         return; // a chunk met a page id out of range
-    // request_metadata_valid and qo_len <= kv_len, on the values loaded above
-    const bool valid = global_ok && located && first == 0 && global_end >= indices_min &&
-                       global_end <= indices_len && page_start >= 0 && page_end > page_start &&
-                       page_end <= global_end && tail >= 1 && tail <= kPage &&
-                       qo_len <= (long long)(page_end - page_start - 1) * kPage + tail;
-    if (!valid || !(norm > 0.0f)) return;
+    if (!(norm > 0.0f)) return;
     publish_merged(top, norm, acc, lane, output + (size_t)state * kHeadDim, lse + state);
 }
 
@@ -594,6 +603,7 @@ int launch_paged_prefill_tiled(const PrefillLaunch &launch, void *stream) {
     args.scale_log2 = launch.scale_log2;
     args.workspace = launch.workspace;
     args.partitions = launch.partitions > 1 ? launch.partitions : 1;
+    args.min_chunk_blocks = launch.min_chunk_blocks > 1 ? launch.min_chunk_blocks : 1;
     CUtensorMap k_half_map, v_map;
     memcpy(&k_half_map, launch.k_map, sizeof(k_half_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
@@ -607,8 +617,9 @@ int launch_prefill_merge(const PrefillLaunch &launch, void *stream) {
                             (const float *)launch.workspace,
                             static_cast<__nv_bfloat16 *>(launch.output), launch.lse,
                             launch.qo_indptr, launch.indptr, launch.last, launch.batch,
-                            launch.nnz_qo, launch.qh, launch.partitions, launch.indices_min,
-                            launch.indices_len);
+                            launch.nnz_qo, launch.qh, launch.kvh, launch.partitions,
+                            launch.min_chunk_blocks > 1 ? launch.min_chunk_blocks : 1,
+                            launch.indices_min, launch.indices_len);
 }
 
 } // namespace lb

@@ -80,7 +80,9 @@ def test_chunk_states_follow_the_split_k_contract(provider, oracle):
 
 
 def test_rows_before_a_chunk_publish_empty_states(provider, oracle):
-    """A whole prompt: early rows of a tile end before later chunks begin."""
+    """A whole prompt: early rows of a tile end before later chunks begin, and a tile with fewer
+    blocks than the plan has chunks uses as many chunks as it has blocks (the other CTAs leave
+    the workspace alone)."""
     rng = np.random.default_rng(78)
     qh, kvh, pool, partitions = 4, 4, 40, 4
     case = ragged_case(rng, [600], [600], qh, kvh, pool)
@@ -91,11 +93,14 @@ def test_rows_before_a_chunk_publish_empty_states(provider, oracle):
     actual, actual_lse = run.run()
     check(actual, actual_lse, expected, expected_lse, gate=False)
     states = run.workspace.cpu().numpy().reshape(600, qh, partitions, 130)
-    assert np.isfinite(states).all()
-    # token 0 sees one key: only the first chunk of its tile has a state
-    assert (states[0, :, 0, 1] > 0).all() and (states[0, :, 1:, :2] == 0).all()
-    # the last token of tile 0 (127) sees 128 keys = 2 blocks: chunks 0 and 1 hold one each
-    assert (states[127, :, :2, 1] > 0).all() and (states[127, :, 2:, :2] == 0).all()
+    # tile 0 (tokens 0..127, one head per KV head) sees at most 128 keys = 2 blocks = 2 chunks
+    assert np.isfinite(states[:128, :, :2]).all() and np.isnan(states[:128, :, 2:]).all()
+    # token 0 sees one key: only the first chunk has a state, the second is empty
+    assert (states[0, :, 0, 1] > 0).all() and (states[0, :, 1, :2] == 0).all()
+    # the last token of the tile sees 128 keys: chunks 0 and 1 hold one block each
+    assert (states[127, :, :2, 1] > 0).all()
+    # the last tile (tokens 512..599) sees 600 keys = 10 blocks: all four chunks
+    assert np.isfinite(states[512:]).all() and (states[599, :, :, 1] > 0).all()
 
 
 def test_long_rows_with_a_rising_maximum(provider, oracle):
@@ -265,3 +270,31 @@ def test_split_and_unsplit_plans_agree_on_a_long_chunk(provider, oracle):
     sample = np.concatenate([shared[r * qh * 128:(r + 1) * qh * 128] for r in rows])
     sample_lse = np.concatenate([shared_lse[r * qh:(r + 1) * qh] for r in rows])
     check(sample, sample_lse, expected, expected_lse, gate=False)
+
+
+def test_plan_chosen_chunks_follow_the_kv_length_met(provider, oracle):
+    """A plan cannot know the KV lengths (an engine's pool is its whole cache): the count it
+    chooses is an upper bound, and on the device a tile takes one chunk per sixteen 64-token
+    blocks it really has.  Short requests are finished by the first command alone -- their
+    states are never written -- long ones are shared out, in one call."""
+    rng = np.random.default_rng(91)
+    qh, kvh, pool = 16, 4, 4000
+    qo_lens, kv_lens = [64, 96, 32], [700, 3000, 64]
+    case = ragged_case(rng, qo_lens, kv_lens, qh, kvh, pool)
+    dims = (3, sum(qo_lens), pool, qh, kvh)
+    expected, expected_lse = oracle.paged_prefill(oracle.prefill_spec(*dims), *case, threads=16)
+    run = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(*dims), *case, algorithm=0, partitions=0)
+    info = run.plan.info()
+    assert run.plan.algorithm() == lk.Bf16PagedPrefillAlgorithm.Tiled
+    assert (info.partitions, info.min_chunk_blocks, info.commands) == (12, 16, 2)
+    actual, actual_lse = run.run()
+    check(actual, actual_lse, expected, expected_lse, gate=False)
+    states = run.workspace.cpu().numpy().reshape(sum(qo_lens), qh, 12, 130)
+    # 700 keys = 11 blocks and 64 keys = 1 block: one chunk, no state; 3000 keys = 47 blocks: 2
+    assert np.isnan(states[:64]).all() and np.isnan(states[160:]).all()
+    assert np.isfinite(states[64:160, :, :2]).all() and np.isnan(states[64:160, :, 2:]).all()
+    forced = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(*dims), *case, algorithm=TILED,
+                        partitions=16)
+    assert forced.plan.info().min_chunk_blocks == 1
+    actual, actual_lse = forced.run()
+    check(actual, actual_lse, expected, expected_lse, gate=False)

@@ -233,7 +233,7 @@ def test_split_plan_shape():
     auto = lk.choose_paged_prefill(chunk, 148, algorithm=2)
     assert auto.algorithm == lk.Bf16PagedPrefillAlgorithm.Tiled
     # 32 whole tiles for 296 slots: nine chunks fill them in one wave
-    assert (auto.partitions, auto.commands) == (9, 2)
+    assert (auto.partitions, auto.commands, auto.min_chunk_blocks) == (9, 2, 16)
     assert auto.grid == auto.tiles * 8 * 9 and auto.tiles == 128 * 4 // 128 + 1
     assert auto.workspace_numel == 128 * 32 * 9 * 130
     assert (auto.merge_grid, auto.merge_block) == (128 * 32 // 4, 128)
@@ -265,6 +265,7 @@ def test_split_plan_shape():
     # the caller's count wins, and implies the tiled kernel
     forced = lk.choose_paged_prefill(chunk, 148, partitions=5)
     assert (forced.algorithm, forced.partitions, forced.grid) == (1, 5, forced.tiles * 8 * 5)
+    assert forced.min_chunk_blocks == 1
     assert lk.choose_paged_prefill(chunk, 148, algorithm=2, partitions=1).commands == 1
     with pytest.raises(lk.ContractError) as e:
         lk.choose_paged_prefill(chunk, 148, partitions=65)
