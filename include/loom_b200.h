@@ -564,8 +564,8 @@ typedef struct lb_paged_prefill_plan_info {
     uint32_t min_chunk_blocks; /* on the device a tile of B 64-token blocks uses
                                   min(partitions, max(1, B / min_chunk_blocks)) chunks, and a tile
                                   of one chunk is finished by the first command: 16 when the plan
-                                  chose the count (the KV length is not known at plan time), 1
-                                  when the caller did */
+                                  chose the count (the KV length is not known at plan time; fewer
+                                  than three chunks then count as one), 1 when the caller did */
     size_t workspace_numel; /* F32 elements the caller must bind: nnz_qo * qh * partitions * 130,
                                0 when partitions == 1 */
 } lb_paged_prefill_plan_info;

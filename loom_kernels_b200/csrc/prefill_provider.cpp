@@ -141,7 +141,8 @@ lb_status choose_prefill(const lb_prefill_spec &spec, uint32_t sm_count, size_t 
             const size_t room = average_kv / 1024;
             if (wanted > room) wanted = room;
             if (wanted > 16) wanted = 16;
-            partitions = wanted > 1 ? (uint32_t)wanted : 1;
+            // a range of fewer than three times sixteen blocks does not pay for the merge
+            partitions = wanted > 1 && room >= 3 ? (uint32_t)wanted : 1;
         }
         size_t grid, workspace = 0;
         if (mul_overflow(tiles, spec.num_kv_heads, &grid) || mul_overflow(grid, partitions, &grid) ||

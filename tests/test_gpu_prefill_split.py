@@ -279,7 +279,7 @@ def test_plan_chosen_chunks_follow_the_kv_length_met(provider, oracle):
     states are never written -- long ones are shared out, in one call."""
     rng = np.random.default_rng(91)
     qh, kvh, pool = 16, 4, 4000
-    qo_lens, kv_lens = [64, 96, 32], [700, 3000, 64]
+    qo_lens, kv_lens = [64, 96, 32], [2500, 3900, 64]
     case = ragged_case(rng, qo_lens, kv_lens, qh, kvh, pool)
     dims = (3, sum(qo_lens), pool, qh, kvh)
     expected, expected_lse = oracle.paged_prefill(oracle.prefill_spec(*dims), *case, threads=16)
@@ -290,9 +290,10 @@ def test_plan_chosen_chunks_follow_the_kv_length_met(provider, oracle):
     actual, actual_lse = run.run()
     check(actual, actual_lse, expected, expected_lse, gate=False)
     states = run.workspace.cpu().numpy().reshape(sum(qo_lens), qh, 12, 130)
-    # 700 keys = 11 blocks and 64 keys = 1 block: one chunk, no state; 3000 keys = 47 blocks: 2
+    # 2500 keys = 40 blocks (two chunks of sixteen do not pay) and 64 keys = 1 block: one chunk,
+    # no state; 3900 keys = 61 blocks: 3
     assert np.isnan(states[:64]).all() and np.isnan(states[160:]).all()
-    assert np.isfinite(states[64:160, :, :2]).all() and np.isnan(states[64:160, :, 2:]).all()
+    assert np.isfinite(states[64:160, :, :3]).all() and np.isnan(states[64:160, :, 3:]).all()
     forced = PrefillRun(provider, lk.Bf16PagedPrefillSpec.new(*dims), *case, algorithm=TILED,
                         partitions=16)
     assert forced.plan.info().min_chunk_blocks == 1
