@@ -96,6 +96,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
+    // The first 32 page ids of the table travel with the request's metadata: when the pages this
+    // CTA starts with lie among them (small batches, short contexts) the producer has its ids
+    // one round trip earlier.
+    int head_of_table = 0;
+    if (warp == kComputeWarps && lane < a.indices_len) head_of_table = a.indices[lane];
     int page_start, page_end, tail;
     if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_min, a.indices_len, request,
                                 page_start, page_end, tail))
@@ -157,8 +162,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             return id;
         };
         auto load_page = [&](int j) -> int { return check_page(fetch_page(j)); };
-        // the first two windows travel together
-        int window = fetch_page(lane);
+        // the first two windows travel together; ids among the first 32 of the table are here
+        const int first_index = page_start + pg0 + lane;
+        int window = __shfl_sync(0xffffffffu, head_of_table, first_index & 31);
+        if (lane >= cnt) window = 0;
+        else if (first_index >= 32) window = a.indices[first_index];
         int window_next = fetch_page(32 + lane);
         window = check_page(window);
         window_next = check_page(window_next);
