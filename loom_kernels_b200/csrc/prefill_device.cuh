@@ -42,17 +42,24 @@ __device__ __forceinline__ int chunks_of_tile(int tile_blocks, int partitions, i
 // qo_len tokens has ceil(qo_len * group / rows) of them) and the tile's index inside it; false
 // when the tile is past the last one or a request up to and including the owner has an invalid
 // query range (crates/loom-infer-cuda/src/attention/prefill.rs:303-317).  Every lane of the
-// calling warp returns the same.  qo_start / qo_end are the owner's query range.
+// calling warp returns the same.  The owner's query range, page range and last-page length come
+// back with it: lane l of a window loads the metadata of request r0 + l in the same round trip
+// as the query ranges that are searched, and the owner's lane hands its values out.
+struct TileOwner {
+    int request, tile_in_request, qo_start, qo_end, page_start, page_end, tail;
+};
 __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int rows, int tile,
-                                            int lane, int &request, int &tile_in_request,
-                                            int &qo_start, int &qo_end) {
+                                            int lane, TileOwner &owner) {
     long long before = 0;
     for (int r0 = 0; r0 < a.batch; r0 += 32) {
         const int r = r0 + lane;
-        int start = 0, end = 0;
+        int start = 0, end = 0, page_start = 0, page_end = 0, tail = 0;
         if (r < a.batch) {
             start = a.qo_indptr[r];
             end = a.qo_indptr[r + 1];
+            page_start = a.indptr[r];
+            page_end = a.indptr[r + 1];
+            tail = a.last[r];
         }
         const bool valid = r >= a.batch || (start >= 0 && end > start && end <= a.nnz_qo);
         const long long mine =
@@ -70,10 +77,13 @@ __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int
         if (hit) {
             const int source = __ffs(hit) - 1;
             if (bad && __ffs(bad) - 1 < source) return false;
-            request = r0 + source;
-            tile_in_request = tile - (int)__shfl_sync(0xffffffffu, first, source);
-            qo_start = __shfl_sync(0xffffffffu, start, source);
-            qo_end = __shfl_sync(0xffffffffu, end, source);
+            owner.request = r0 + source;
+            owner.tile_in_request = tile - (int)__shfl_sync(0xffffffffu, first, source);
+            owner.qo_start = __shfl_sync(0xffffffffu, start, source);
+            owner.qo_end = __shfl_sync(0xffffffffu, end, source);
+            owner.page_start = __shfl_sync(0xffffffffu, page_start, source);
+            owner.page_end = __shfl_sync(0xffffffffu, page_end, source);
+            owner.tail = __shfl_sync(0xffffffffu, tail, source);
             return true;
         }
         if (bad) return false;
@@ -82,10 +92,26 @@ __device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int
     return false;
 }
 
-__device__ __forceinline__ bool locate_tile(const PrefillArgs &a, int group, int rows, int tile,
-                                            int lane, int &request, int &tile_in_request) {
-    int qo_start, qo_end;
-    return locate_tile(a, group, rows, tile, lane, request, tile_in_request, qo_start, qo_end);
+// The guard of the prefill kernels (prefill.rs:289-347) in one round trip to the metadata: the
+// global checks, every query range up to the owner of `tile`, the owner's page range and
+// qo_len <= kv_len.  Also fetches the first 32 page ids of the table (`head_of_table`, lane l holds
+// indices[l]) for the warp `want_head` names, so that a CTA whose first pages lie among them --
+// short calls -- has its ids without another trip.
+__device__ __forceinline__ bool prefill_guard(const PrefillArgs &a, int group, int rows, int tile,
+                                              int lane, bool want_head, TileOwner &owner,
+                                              int &head_of_table) {
+    const int qo_first = a.qo_indptr[0], qo_total = a.qo_indptr[a.batch];
+    const int table_first = a.indptr[0], table_end = a.indptr[a.batch];
+    head_of_table = want_head && lane < a.indices_len ? a.indices[lane] : 0;
+    const bool located = locate_tile(a, group, rows, tile, lane, owner);
+    if (qo_first != 0 || qo_total != a.nnz_qo || !located) return false;
+    // request_metadata_valid on the values at hand
+    if (table_first != 0 || table_end < a.indices_min || table_end > a.indices_len ||
+        owner.page_start < 0 || owner.page_end <= owner.page_start || owner.page_end > table_end ||
+        owner.tail < 1 || owner.tail > kPage)
+        return false;
+    const long long kv_len = (long long)(owner.page_end - owner.page_start - 1) * kPage + owner.tail;
+    return owner.qo_end - owner.qo_start <= kv_len;
 }
 
 // The request that owns query row `row`, with its query range, page range and last-page length

@@ -74,19 +74,17 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
-    if (a.qo_indptr[0] != 0 || a.qo_indptr[a.batch] != a.nnz_qo) return; // prefill.rs:289-296
-    int request, tile_in_request;
-    if (!locate_tile(a, group, rows_per_cta, tile, lane, request, tile_in_request)) return;
-    int page_start, page_end, tail;
-    if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_min, a.indices_len, request,
-                                page_start, page_end, tail))
-        return;
-    const int qo_start = a.qo_indptr[request];
-    const int qo_len = a.qo_indptr[request + 1] - qo_start;
-    const int num_pages = page_end - page_start;
-    const long long kv_len_wide = (long long)(num_pages - 1) * kPage + tail;
-    if (qo_len > kv_len_wide) return; // prefill.rs:343-347
-    const int kv_len = (int)kv_len_wide;
+    TileOwner owner;
+    int head_of_table;
+    if (!prefill_guard(a, group, rows_per_cta, tile, lane, warp == kComputeWarps, owner,
+                       head_of_table))
+        return; // prefill.rs:289-347
+    const int tile_in_request = owner.tile_in_request;
+    const int page_start = owner.page_start, tail = owner.tail;
+    const int qo_start = owner.qo_start;
+    const int qo_len = owner.qo_end - qo_start;
+    const int num_pages = owner.page_end - page_start;
+    const int kv_len = (num_pages - 1) * kPage + tail;
     const int shift = kv_len - qo_len + 1; // row of token t sees logical tokens [0, shift + t)
 
     const long long rows_total = (long long)qo_len * group;
@@ -117,7 +115,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
             }
             return id;
         };
-        int window = load_page(lane);
+        // the first window: ids among the first 32 of the table came with the guard
+        int window = __shfl_sync(0xffffffffu, head_of_table, (page_start + lane) & 31);
+        if (lane >= cnt) window = 0;
+        else if (page_start + lane >= 32) window = a.indices[page_start + lane];
+        if (window < 0 || window >= a.max_pages) {
+            bad_page = true;
+            window = 0;
+        }
         int window_next = load_page(32 + lane);
         const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
         const uint32_t my_tile = smem_u32(ring + my_slot * slot_bytes + which * (slot_bytes / 2));

@@ -118,21 +118,15 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         if (tid == 0 && a.status) atomicExch(a.status, 2);
         return;
     }
-    // Two dependent round trips to the metadata instead of one per check: everything that does
-    // not depend on the owner is loaded before the first value is looked at.
-    const int qo_first = a.qo_indptr[0], qo_total = a.qo_indptr[a.batch];
-    const int table_first = a.indptr[0], table_end = a.indptr[a.batch];
-    int request, tile_in_request, qo_start, qo_end;
-    const bool located =
-        locate_tile(a, group, kTileRows, tile, lane, request, tile_in_request, qo_start, qo_end);
-    if (qo_first != 0 || qo_total != a.nnz_qo || !located) return; // prefill.rs:289-317
-    int page_start = a.indptr[request];
-    const int page_end = a.indptr[request + 1], tail = a.last[request];
-    // request_metadata_valid on the values at hand
-    if (table_first != 0 || table_end < a.indices_min || table_end > a.indices_len ||
-        page_start < 0 || page_end <= page_start || page_end > table_end || tail < 1 ||
-        tail > kPage)
-        return;
+    // one round trip to the metadata (prefill.rs:289-347); the producer warp also gets the first 32
+    // page ids of the table
+    TileOwner owner;
+    int head_of_table;
+    if (!prefill_guard(a, group, kTileRows, tile, lane, warp == 4, owner, head_of_table)) return;
+    const int tile_in_request = owner.tile_in_request;
+    const int qo_start = owner.qo_start, qo_end = owner.qo_end;
+    int page_start = owner.page_start;
+    const int page_end = owner.page_end, tail = owner.tail;
     const int qo_len = qo_end - qo_start;
     const int request_pages = page_end - page_start;
     const long long kv_len_wide = (long long)(request_pages - 1) * kPage + tail;
@@ -220,7 +214,11 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             return page < cnt ? a.indices[page_start + page] : 0;
         };
         int first_window = 0;
-        int win0 = load_window(0), win1 = load_window(1);
+        // the first window: ids among the first 32 of the table came with the guard
+        int win0 = __shfl_sync(0xffffffffu, head_of_table, (page_start + lane) & 31);
+        if (lane >= cnt) win0 = 0;
+        else if (page_start + lane >= 32) win0 = a.indices[page_start + lane];
+        int win1 = load_window(1);
         auto id_of_page = [&](int page) -> int {
             const int from0 = __shfl_sync(0xffffffffu, win0, page & 31);
             const int from1 = __shfl_sync(0xffffffffu, win1, page & 31);
