@@ -94,6 +94,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         prefetch_tensormap(&k_map);
         prefetch_tensormap(&v_map);
     }
+    __syncthreads(); // the barriers exist for every warp
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
     // The first 32 page ids of the table travel with the request's metadata: when the pages this
@@ -131,7 +132,6 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         return;
     }
 
-    __syncthreads();
     LB_STAMP(2);
 
     const int n_iter = (cnt + a.pps - 1) / a.pps;

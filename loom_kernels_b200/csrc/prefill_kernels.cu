@@ -72,6 +72,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
         prefetch_tensormap(&k_map);
         prefetch_tensormap(&v_map);
     }
+    __syncthreads(); // the barriers exist for every warp
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
     TileOwner owner;
@@ -92,8 +93,6 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
     const long long row_hi = min(row_lo + rows_per_cta, rows_total); // > row_lo by construction
     const int cta_limit = shift + (int)((row_hi - 1) / group);       // tokens the last row sees
     const int cnt = (cta_limit + kPage - 1) / kPage;                 // pages this CTA streams
-
-    __syncthreads();
 
     WarpState st;
     const int unit = warp / a.mt;  // consumer: which page slot of each stage
