@@ -18,7 +18,9 @@ prompt per GPU) in TFLOP/s against the measured BF16 GEMM throughput.
 metric through the public API with host buffers (pinned host -> device copy of the step's Q and
 page table, device -> host read of O and LSE inside the timed region; the KV cache is device
 state, as in serving).  `--impl reference` times the CPU reference (the C restatement of the
-reference's own CPU path) on the host cores for the same workload and metric.
+reference's own CPU path) on the host cores for the same workload and metric, on a bounded sample
+per step (the first 16 requests of a decode workload; the last 8 query tokens of the prefill
+prompt).
 """
 from __future__ import annotations
 
@@ -117,8 +119,7 @@ def reference_arm(args):
     oracle.build()
     threads = os.cpu_count() or 1
     if args.workload == "prefill":
-        raise SystemExit("--impl reference covers the decode workloads; the prefill line carries "
-                         "its own cpu_baseline")
+        return reference_arm_prefill(args, oracle, threads)
     w = build_workload(args.workload, 0, args.batch)
     # bounded sample: the first `sample` requests of the workload (whole requests, all heads)
     sample = min(w.batch, args.reference_requests)
@@ -149,6 +150,50 @@ def reference_arm(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "us_per_call": seconds * 1e6 * w.batch / sample,
         "tokens_per_s": sample / seconds,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def reference_arm_prefill(args, oracle, threads):
+    """The prefill workload on the host cores: the oracle over the last `rows` query tokens of the
+    8192-token prompt (all heads, the whole context they see), the same sample as the
+    cpu_baseline of the device line.  Inputs are seeded synthetic data of the same shape."""
+    tokens, qh, kvh, rows = 8192, 32, 8, 8
+    pages = (tokens + 15) // 16
+    pool = pages + 8
+    rng = np.random.default_rng(0xF3)
+
+    def normal_bf16(count):
+        bits = rng.standard_normal(count, dtype=np.float32).view(np.uint32)
+        return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+    q = normal_bf16(rows * qh * 128)
+    k = normal_bf16(pool * 16 * kvh * 128)
+    v = normal_bf16(pool * 16 * kvh * 128)
+    indices = rng.permutation(pool)[:pages].astype(np.int32)
+    spec = oracle.prefill_spec(1, rows, pool, qh, kvh)
+    flops = 4.0 * 128 * qh * sum(tokens - rows + i + 1 for i in range(rows))
+    times = []
+    for step in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        oracle.paged_prefill(spec, q, k, v, [0, rows], [0, pages], indices, [(tokens - 1) % 16 + 1],
+                             threads=threads)
+        if step >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    seconds = float(np.mean(times))
+    value = flops / seconds / 1e12
+    line = {
+        "metric": "paged_prefill_tflops", "value": value, "unit": "TFLOP/s", "impl": "reference",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "paged causal prefill, one 8192-token prompt per GPU, 32/8 heads, "
+                               "page size 16, scattered pages", "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"last {rows} query tokens of the prompt per step, all heads "
+                                   f"({flops / 1e9:.2f} GFLOP)"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
