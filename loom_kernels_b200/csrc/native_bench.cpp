@@ -264,10 +264,14 @@ struct AppendCase : Case {
     uint16_t *query, *key, *value, *query_output, *key_pages, *value_pages;
     int32_t *batch_indices, *positions, *indptr, *indices, *last;
     lb_rope_append_args args{};
+    int32_t *workspace = nullptr; // extended plans: the validation's verdicts and slots
+    size_t workspace_numel = 0;
 
-    // request r appends new_tokens[r] tokens after prior[r] existing ones; pages in order
+    // request r appends new_tokens[r] tokens after prior[r] existing ones; pages in order.
+    // extended: no 64-token cap on the call (two commands: validate, then rotate and scatter)
     AppendCase(const char *label, lb_rope_provider *provider, size_t pool_pages, size_t qh,
-               size_t kvh, const std::vector<int> &new_tokens, const std::vector<int> &prior) {
+               size_t kvh, const std::vector<int> &new_tokens, const std::vector<int> &prior,
+               bool extended = false) {
         name = label;
         const size_t batch = new_tokens.size();
         std::vector<int32_t> page_indptr{0}, page_indices, last_page_len, owner, position;
@@ -285,9 +289,18 @@ struct AppendCase : Case {
         tokens = owner.size();
         indices_len = page_indices.size();
         lb_append_tokens_spec token_spec{};
-        LB(lb_append_tokens_spec_new(tokens, batch, pool_pages, qh, kvh, 128, 16, &token_spec));
+        if (extended)
+            LB(lb_append_tokens_spec_new_extended(tokens, batch, pool_pages, qh, kvh, 128, 16,
+                                                  &token_spec));
+        else
+            LB(lb_append_tokens_spec_new(tokens, batch, pool_pages, qh, kvh, 128, 16, &token_spec));
         LB(lb_paged_spec_new(batch, pool_pages, qh, kvh, 128, 16, &spec));
         LB(lb_rope_append_tokens_plan_create(provider, &token_spec, &plan));
+        lb_rope_append_plan_info info{};
+        LB(lb_rope_append_plan_info_get(plan, &info));
+        commands = (int)info.commands;
+        workspace_numel = info.workspace_numel;
+        if (workspace_numel) workspace = device_zeros<int32_t>(workspace_numel);
         query = upload_normal(tokens * qh * 128, 4);
         key = upload_normal(tokens * kvh * 128, 5);
         value = upload_normal(tokens * kvh * 128, 6);
@@ -299,11 +312,13 @@ struct AppendCase : Case {
         indptr = upload(page_indptr);
         indices = upload(page_indices);
         last = upload(last_page_len);
-        slots = 11;
+        slots = 12;
     }
     void bind(lb_bindings *b) override {
         const size_t qh = spec.num_query_heads, kvh = spec.num_kv_heads;
         lb_handle q_out{}, kp{}, vp{};
+        if (workspace_numel)
+            LB(lb_bind_read_write(b, LB_I32, workspace, workspace_numel, &args.workspace));
         LB(lb_bind_read(b, LB_BF16, query, tokens * qh * 128, &args.query));
         LB(lb_bind_read(b, LB_BF16, key, tokens * kvh * 128, &args.key));
         LB(lb_bind_read(b, LB_BF16, value, tokens * kvh * 128, &args.value));
@@ -415,6 +430,16 @@ int main(int argc, char **argv) {
                    {0, 15, 16, 40});
     AppendCase six("gate append b3 16/4 six explicit tokens", rope, 16, 16, 4, {1, 2, 3},
                    {3, 16, 30});
+    // C2 of the configuration list: 32 requests, 1-64 new tokens each after 0-2048 cached ones,
+    // 32/8 heads, one extended call (fixed pseudo-random lengths: 1081 tokens in all)
+    std::vector<int> c2_new(32), c2_prior(32);
+    for (int r = 0, total = 0; r < 32; ++r) {
+        c2_new[r] = r == 31 ? 1081 - total : (r + 17) % 64 + 1; // 18 .. 48, then 58
+        total += c2_new[r];
+        c2_prior[r] = (r * 613 + 101) % 2049;
+    }
+    AppendCase c2("C2 RoPE+append b32 32/8 tokens1081 pool8192 extended", rope, 8192, 32, 8, c2_new,
+                  c2_prior, true);
     // C1 of the configuration list: MHA batch 1, 32/32 heads, context 1024, plan-chosen split
     std::vector<int32_t> c1_pages(64);
     for (int i = 0; i < 64; ++i) c1_pages[i] = (i * 37 + 11) % 256;
@@ -429,7 +454,7 @@ int main(int argc, char **argv) {
                            {1, 4, 16}, {128, 256, 512});
     PrefillCase p_gqa_long("gate prefill gqa4_b2_q32_64_kv256_1024 16/4", prefill, 16, 4, {32, 64},
                            {256, 1024});
-    Case *cases[] = {&mha, &mqa, &gqa, &one, &six, &c1, &p_mha, &p_mqa, &p_gqa, &p_mqa_long,
+    Case *cases[] = {&mha, &mqa, &gqa, &one, &six, &c2, &c1, &p_mha, &p_mqa, &p_gqa, &p_mqa_long,
                      &p_gqa_long};
     for (Case *c : cases) measure(*c, opt);
     return 0;
