@@ -361,23 +361,33 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
  * plug-in whose engine owns every device byte and forbids cudaMalloc, or a loop that must stay out
  * of the allocator.  The partial states go to a fixed array inside the library (on every GPU that
  * loads it, for the life of the process) instead; inputs and outputs are still the caller's raw
- * device pointers, with the lengths and 16-byte alignment lb_paged_decode_enqueue checks.
- * Same kernels, same results as a split plan with `partitions` chunks (>= 2).
+ * device pointers.  Same kernels, same results as a split plan with `partitions` chunks (>= 2).
+ *   - what is checked: the spec, `partitions`, page_indices_len >= batch, that every pointer is
+ *     device memory of the stream's GPU (BufferContextMismatch otherwise) and that query, pools
+ *     and output are 16-byte aligned.  Raw pointers carry no length: the caller guarantees the
+ *     lengths lb_paged_decode_enqueue would check (Q and O batch*qh*128, the pools
+ *     max_pages*16*kvh*128, page_indptr batch+1, last_page_len batch, LSE batch*qh);
  *   - limit: batch * query_heads * partitions <= lb_paged_decode_split_noalloc_max_states()
  *     (16384 states = 8.1 MiB); beyond it the call fails with LB_STATIC_SCRATCH_EXCEEDED and
  *     launches nothing;
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
- *   - the first call on each GPU looks up the array's device address and sets kernel attributes;
- *     make that first call before any stream capture;
+ *   - the first call on each GPU looks up the array's device address and sets kernel attributes
+ *     (under a lock, so two threads may race to it); make that first call before any stream
+ *     capture;
  *   - every call shares the one array and finds the previous call's states in it; nothing has to
  *     start at zero (each state a call merges is written by that call first), but two calls that
- *     overlap on the GPU -- different streams, or replays in flight together -- race on it. */
+ *     overlap on the GPU -- different streams, or replays in flight together -- race on it;
+ *   - a CTA that gives up on a bounded wait leaves its rows unwritten and sets a status word
+ *     inside the library; lb_paged_decode_split_noalloc_status reads and clears it (it
+ *     synchronises the device and allocates nothing).  0 = every call since the last read ran to
+ *     completion. */
 size_t lb_paged_decode_split_noalloc_max_states(void);
 lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t partitions,
                                         void *stream, const void *query, const void *key_pages,
                                         const void *value_pages, const int32_t *page_indptr,
                                         const int32_t *page_indices, size_t page_indices_len,
                                         const int32_t *last_page_len, void *output, float *lse);
+lb_status lb_paged_decode_split_noalloc_status(int device, int32_t *status);
 
 /* ---- RoPE + paged KV append provider --------------------------------------------------------- */
 
@@ -661,6 +671,9 @@ void lb_test_use_fake_driver(int enable, int fake_sm_count);
 void lb_test_fake_fail(const char *what, int n, int cuda_error);
 /* Number of kernel launches the fake (or the real driver layer) has accepted so far. */
 uint64_t lb_test_launch_count(void);
+/* 1 once lb_paged_decode_split_noalloc has resolved its static array on `device` (never under the
+ * fake driver, which has no device to resolve it on). */
+int lb_test_noalloc_is_set_up(int device);
 
 #ifdef __cplusplus
 }

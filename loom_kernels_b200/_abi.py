@@ -195,6 +195,7 @@ SIGNATURES = {
     "lb_paged_decode_split_noalloc": (c_int32, [POINTER(PagedSpec), c_uint32, c_void_p, c_void_p,
                                                 c_void_p, c_void_p, _I32P, _I32P, c_size_t, _I32P,
                                                 c_void_p, c_void_p]),
+    "lb_paged_decode_split_noalloc_status": (c_int32, [c_int, POINTER(c_int32)]),
     "lb_rope_provider_load": (c_int32, [c_int, POINTER(c_void_p)]),
     "lb_rope_provider_destroy": (None, [c_void_p]),
     "lb_rope_append_plan_create": (c_int32, [c_void_p, POINTER(PagedSpec), POINTER(c_void_p)]),
@@ -258,6 +259,7 @@ SIGNATURES = {
     "lb_test_use_fake_driver": (None, [c_int, c_int]),
     "lb_test_fake_fail": (None, [c_char_p, c_int, c_int]),
     "lb_test_launch_count": (c_uint64, []),
+    "lb_test_noalloc_is_set_up": (c_int, [c_int]),
 }
 
 _lib = None

@@ -599,6 +599,32 @@ def paged_decode_split_noalloc(spec: Bf16PagedBatchDecodeSpec, partitions: int, 
     def pointer(buffer):
         return c_void_p(_describe(buffer)[1])
 
+    # raw pointers carry no length across the C ABI; this wrapper knows the tensors, so it makes
+    # the length and type checks lb_paged_decode_enqueue makes before anything is launched
+    batch = spec.batch_size()
+    expected = (("Q", query, BF16, spec.query_numel()),
+                ("K_pages", key_pages, BF16, spec.kv_pages_numel()),
+                ("V_pages", value_pages, BF16, spec.kv_pages_numel()),
+                ("page_indptr", page_indptr, I32, batch + 1),
+                ("last_page_len", last_page_len, I32, batch),
+                ("O", output, BF16, spec.output_numel()),
+                ("LSE", lse, F32, spec.lse_numel()))
+    limit = paged_decode_split_noalloc_max_states()
+    fits = partitions >= 2 and batch * spec.num_query_heads() * partitions <= limit
+    for operand, buffer, dtype, numel in expected:
+        actual_dtype, _, actual = _describe(buffer)
+        if actual_dtype != dtype:
+            raise TypeError(f"{operand}: element type {actual_dtype}, expected {dtype}")
+        # a request the static array cannot hold is refused by the library itself, whatever the
+        # buffers are
+        if fits and actual != numel:
+            info = _abi.ErrorInfo(status=200, name=b"LengthMismatch", operand=operand.encode(),
+                                  a=numel, b=actual,
+                                  message=f"{operand} length mismatch: expected {numel}, "
+                                          f"got {actual}".encode())
+            raise EnqueueError(info)
+    if _describe(page_indices)[0] != I32:
+        raise TypeError("page_indices: expected I32")
     handle = getattr(stream, "cuda_stream", stream)
     indices_ptr = ctypes.cast(pointer(page_indices), ctypes.POINTER(c_int32))
     _check(_abi.load().lb_paged_decode_split_noalloc(
@@ -607,6 +633,14 @@ def paged_decode_split_noalloc(spec: Bf16PagedBatchDecodeSpec, partitions: int, 
         indices_ptr, _describe(page_indices)[2],
         ctypes.cast(pointer(last_page_len), ctypes.POINTER(c_int32)), pointer(output),
         pointer(lse)))
+
+
+def paged_decode_split_noalloc_status(device: int = 0) -> int:
+    """Reads and clears the status word of the no-workspace entry point on `device`: non-zero when
+    a CTA of one of its calls gave up on a bounded wait since the last read."""
+    status = c_int32(0)
+    _check(_abi.load().lb_paged_decode_split_noalloc_status(device, byref(status)))
+    return status.value
 
 
 def paged_decode_split_noalloc_max_states() -> int:

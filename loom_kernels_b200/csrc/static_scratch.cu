@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <mutex>
 
 #include "kernels.hpp"
 #include "runtime.hpp"
@@ -21,15 +22,20 @@ namespace {
 constexpr size_t kMaxStates = 16384;
 constexpr size_t kScratchFloats = kMaxStates * LB_PARTIAL_STATE_WIDTH;
 static __device__ __align__(256) float g_split_scratch[kScratchFloats];
+// Set to 1 by a CTA of this entry point's kernels that gave up on a bounded wait (its rows are then
+// missing from the result); read and cleared by lb_paged_decode_split_noalloc_status.
+static __device__ int32_t g_split_status;
 
 constexpr int kMaxDevices = 64;
 struct DeviceSetup {
-    bool ready = false;
+    bool ready = false;       // set only by a set-up on a real device, never under the fake driver
     float *scratch = nullptr; // device address of g_split_scratch on this GPU
+    int32_t *status = nullptr; // device address of g_split_status on this GPU
     int sm_count = 0;
     size_t smem_optin = 0;
 };
 DeviceSetup g_setup[kMaxDevices];
+std::mutex g_setup_mutex; // the one-time set-up of a GPU may be raced by two host threads
 
 // In host code `g_split_scratch` names a host-side stand-in, not device memory: the device
 // address has to be asked for, once per GPU, with that GPU current.
@@ -38,12 +44,15 @@ int set_up_device(int device, DeviceSetup &setup) {
     int rc = cudaGetDevice(&previous);
     if (rc) return rc;
     if (previous != device && (rc = cudaSetDevice(device))) return rc;
-    void *address = nullptr;
+    void *address = nullptr, *status = nullptr;
     rc = cudaGetSymbolAddress(&address, g_split_scratch);
+    if (!rc) rc = cudaGetSymbolAddress(&status, g_split_status);
     if (!rc) rc = lb::configure_decode_kernels(setup.smem_optin);
     if (previous != device) cudaSetDevice(previous);
     if (rc) return rc;
+    if (address == nullptr || status == nullptr) return (int)cudaErrorInvalidSymbol;
     setup.scratch = static_cast<float *>(address);
+    setup.status = static_cast<int32_t *>(status);
     setup.ready = true;
     return 0;
 }
@@ -72,26 +81,44 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     if (page_indices_len < checked.batch_size)
         return fail(LB_PAGE_INDICES_TOO_SHORT, nullptr, (int64_t)checked.batch_size,
                     (int64_t)page_indices_len);
-    if (page_indices_len > 0x7fffffffu || checked.max_num_pages > (size_t)0x7fffffff / LB_PAGE_SIZE)
+    if (page_indices_len > 0x7fffffffu || checked.max_num_pages > (size_t)0x7fffffff / LB_PAGE_SIZE ||
+        checked.num_kv_heads > 0x7fffffffu / LB_HEAD_DIM)
         return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)page_indices_len);
 
     int device = 0;
     int error = driver().stream_device(stream, &device);
     if (error) return fail(LB_DRIVER, "stream_device", error);
     if (device < 0 || device >= kMaxDevices) return fail(LB_INVALID_ARGUMENT, "device", device);
-    DeviceSetup &setup = g_setup[device];
-    if (!setup.ready) {
-        int major = 0, minor = 0;
-        size_t l2 = 0;
-        if ((error = driver().device_props(device, &setup.sm_count, &major, &minor,
-                                           &setup.smem_optin, &l2)))
-            return fail(LB_DRIVER, "device_props", error);
-        if (major != 10) return fail(LB_UNSUPPORTED_DEVICE, nullptr, major * 10 + minor);
-        if (driver().is_fake()) {
-            setup.ready = true; // host-only tests: no device, no address
-        } else if ((error = set_up_device(device, setup))) {
-            return fail(LB_DRIVER, "cudaGetSymbolAddress", error);
+    // Under the fake driver (host-only tests) nothing is cached: there is no device and no
+    // address, and a later call on the real driver must still do its set-up.
+    DeviceSetup fake_setup;
+    const bool fake = driver().is_fake();
+    DeviceSetup &setup = fake ? fake_setup : g_setup[device];
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        if (!setup.ready) {
+            int major = 0, minor = 0;
+            size_t l2 = 0;
+            if ((error = driver().device_props(device, &setup.sm_count, &major, &minor,
+                                               &setup.smem_optin, &l2)))
+                return fail(LB_DRIVER, "device_props", error);
+            if (major != 10) return fail(LB_UNSUPPORTED_DEVICE, nullptr, major * 10 + minor);
+            if (!fake && (error = set_up_device(device, setup)))
+                return fail(LB_DRIVER, "cudaGetSymbolAddress", error);
         }
+    }
+    if (!fake && (setup.scratch == nullptr || setup.status == nullptr))
+        return fail(LB_DRIVER, "static scratch address", (int)cudaErrorInvalidSymbol);
+    // every operand must be device memory of the stream's GPU (BufferContextMismatch in the plan
+    // path, crates/loom-infer-cuda/src/command/binding.rs:109-123)
+    for (const void *p : {query, key_pages, value_pages, (const void *)page_indptr,
+                          (const void *)page_indices, (const void *)last_page_len,
+                          (const void *)output, (const void *)lse}) {
+        int owner = -1;
+        bool is_device = false;
+        if ((error = driver().pointer_device(p, &owner, &is_device)) || !is_device)
+            return fail(LB_INVALID_ARGUMENT, "not a device pointer", error);
+        if (owner != device) return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, owner, device);
     }
 
     lb_paged_decode_options options;
@@ -124,7 +151,7 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     launch.output = output;
     launch.lse = lse;
     launch.workspace = setup.scratch;
-    launch.status = nullptr;
+    launch.status = setup.status;
     launch.batch = (int32_t)checked.batch_size;
     launch.max_pages = (int32_t)checked.max_num_pages;
     launch.qh = (int32_t)checked.num_query_heads;
@@ -159,6 +186,32 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     if ((error = driver().launch(device, [&]() { return launch_split_merge(merge, stream); })))
         return fail(LB_DRIVER, "launch", error);
     return LB_OK;
+}
+
+lb_status lb_paged_decode_split_noalloc_status(int device, int32_t *status) {
+    using namespace lb;
+    if (!status || device < 0 || device >= kMaxDevices) return fail(LB_INVALID_ARGUMENT, "status");
+    *status = 0;
+    int32_t *word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        if (!g_setup[device].ready) return LB_OK; // no call has run on this GPU yet
+        word = g_setup[device].status;
+    }
+    if (driver().is_fake()) return LB_OK;
+    const int error = driver().configure(device, [&]() -> int {
+        int e = cudaMemcpy(status, word, sizeof(int32_t), cudaMemcpyDeviceToHost);
+        if (e) return e;
+        return cudaMemset(word, 0, sizeof(int32_t));
+    });
+    if (error) return fail(LB_DRIVER, "noalloc_status", error);
+    return LB_OK;
+}
+
+int lb_test_noalloc_is_set_up(int device) {
+    if (device < 0 || device >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    return g_setup[device].ready ? 1 : 0;
 }
 
 }

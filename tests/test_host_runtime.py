@@ -617,3 +617,41 @@ def test_indices_capacity_option_is_a_plan_property(fake):
     assert lib.lb_rope_append_plan_create_with(rope._ptr, ctypes.byref(spec._raw),
                                                ctypes.byref(append_options),
                                                ctypes.byref(out)) != 0
+
+
+def test_noalloc_entry_under_the_fake_driver_caches_nothing(fake):
+    """The no-workspace split-K entry resolves its static array once per GPU on the real driver.
+    Under the fake there is no device to resolve it on, so a call must leave the per-GPU set-up
+    untouched (a later real call still has to do it), while its checks and its two launches run as
+    on a device."""
+    lib = _abi.load()
+    spec = lk.Bf16PagedBatchDecodeSpec.new(2, 40, 16, 4)
+    stream = 0x1000  # fake stream of device 0
+    q = D(0x40000000, spec.query_numel(), _abi.BF16)
+    pool = spec.kv_pages_numel()
+    k, v = D(0x41000000, pool, _abi.BF16), D(0x42000000, pool, _abi.BF16)
+    indptr, indices, last = (D(0x43000000, 3, _abi.I32), D(0x43100000, 40, _abi.I32),
+                             D(0x43200000, 2, _abi.I32))
+    out, lse = D(0x44000000, spec.output_numel(), _abi.BF16), D(0x45000000, 32, _abi.F32)
+    before = lib.lb_test_launch_count()
+    lk.paged_decode_split_noalloc(spec, 4, stream, q, k, v, indptr, indices, last, out, lse)
+    assert lib.lb_test_launch_count() == before + 2  # partial states, then the merge
+    assert lib.lb_test_noalloc_is_set_up(0) == 0
+    assert lk.paged_decode_split_noalloc_status(0) == 0
+    # operand checks that need no device: lengths (in the wrapper), owner GPU, memory kind
+    with pytest.raises(lk.EnqueueError) as e:
+        lk.paged_decode_split_noalloc(spec, 4, stream, q, k, v, indptr, indices, last,
+                                      D(0x44000000, 16, _abi.BF16), lse)
+    assert (e.value.variant, e.value.operand, e.value.payload[:2]) == \
+        ("LengthMismatch", "O", (spec.output_numel(), 16))
+    other_gpu = D(0x41000000 | (1 << 40), pool, _abi.BF16)
+    with pytest.raises(lk.CommandError) as e:
+        lk.paged_decode_split_noalloc(spec, 4, stream, q, other_gpu, v, indptr, indices, last, out,
+                                      lse)
+    assert (e.value.variant, e.value.payload[:2]) == ("BufferContextMismatch", (1, 0))
+    host_memory = D(0x45000000 | (1 << 41), 32, _abi.F32)
+    with pytest.raises(lk.LoomError):
+        lk.paged_decode_split_noalloc(spec, 4, stream, q, k, v, indptr, indices, last, out,
+                                      host_memory)
+    assert lib.lb_test_launch_count() == before + 2
+    assert lib.lb_test_noalloc_is_set_up(0) == 0

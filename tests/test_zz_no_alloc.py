@@ -53,6 +53,8 @@ def test_noalloc_entry_matches_the_workspace_entry_on_two_calls_in_a_row(oracle)
     run_both(oracle, rng, 3, 32, 8, 80, [16 * 20 + 5, 16 * 2, 16 * 33], partitions=4)
     # second call right after it, another shape: it finds the first call's states in the array
     run_both(oracle, rng, 2, 64, 8, 96, [16 * 40, 16 * 37 + 9], partitions=8)
+    # no CTA of either call gave up on a bounded wait (the entry point's own status word)
+    assert lk.paged_decode_split_noalloc_status(0) == 0
 
 
 def test_noalloc_entry_refuses_what_the_static_array_cannot_hold():
@@ -73,3 +75,10 @@ def test_noalloc_entry_refuses_what_the_static_array_cannot_hold():
         lk.paged_decode_split_noalloc(spec, 1, torch.cuda.current_stream(), dummy, dummy, dummy,
                                       ints, ints, ints, dummy, lse)
     assert info.value.variant == "InvalidPartitionCount"
+    # a request that fits is checked operand by operand before anything is launched
+    small = lk.Bf16PagedBatchDecodeSpec.new(2, 8, 32, 8)
+    with pytest.raises(lk.EnqueueError) as info:
+        lk.paged_decode_split_noalloc(small, 2, torch.cuda.current_stream(), dummy, dummy, dummy,
+                                      ints, ints, ints, dummy, lse)
+    assert (info.value.variant, info.value.operand) == ("LengthMismatch", "Q")
+    assert _abi.load().lb_test_launch_count() == before
