@@ -1,13 +1,16 @@
 """Paged decode at the full sizes of the benchmark configurations, through the C ABI.
 
-The CPU oracle is too slow for whole batches of this size, so each case checks
-  * a sample of whole requests against the oracle (their pages are gathered into a compact pool
-    for the oracle; O max-abs 2e-2, row-relative 1e-2, LSE 1e-3 as in the small cases), and
-  * size-independent properties over EVERY row: the direct, split-K and page-balanced algorithms
+Each case checks
+  * EVERY request against the CPU oracle on all host cores (a request's pages are gathered into a
+    compact pool for the oracle; O max-abs 2e-2, row-relative 1e-2, LSE 1e-3 as in the small
+    cases), and
+  * size-independent properties over every row: the direct, split-K and page-balanced algorithms
     agree within the same tolerances, and moving every page to another physical slot of the pool
     (with the page table updated) leaves the direct output bit-identical (page indexing is exact).
 K/V pools are generated on the device (seeded); Q and the page table come from the host.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -50,7 +53,7 @@ def oracle_rows(oracle, w, k, v, requests):
         q = w.query[r * w.qh * 128:(r + 1) * w.qh * 128]
         out, lse = oracle.paged_decode(spec, q, k_sub, v_sub, np.array([0, len(pages)], np.int32),
                                        np.arange(len(pages), dtype=np.int32),
-                                       w.last[r:r + 1], threads=16)
+                                       w.last[r:r + 1], threads=os.cpu_count() or 1)
         outs.append(out)
         lses.append(lse)
     return np.concatenate(outs), np.concatenate(lses)
@@ -86,14 +89,38 @@ def moved_pool(w, k, v, seed):
     return k2, v2, destination[w.indices].astype(np.int32)
 
 
+def test_c1_mha_batch1_context1024(provider, oracle):
+    """MHA 32/32, one request of 1024 tokens on 64 of 256 pages: small enough for the oracle to
+    check every one of the 32 x 128 outputs and 32 LSEs, on the plan the heuristic picks for it and
+    on the direct, split-K and page-balanced plans a caller can pin."""
+    w = workloads.c1()
+    k, v = H.dev_bf16(w.key_pages), H.dev_bf16(w.value_pages)
+    ospec = oracle.paged_spec(w.batch, w.max_pages, w.qh, w.kvh)
+    expected = oracle.paged_decode(ospec, w.query, w.key_pages, w.value_pages, w.indptr, w.indices,
+                                   w.last, threads=os.cpu_count() or 1)
+    spec = lk.Bf16PagedBatchDecodeSpec.new(w.batch, w.max_pages, w.qh, w.kvh)
+    chosen = provider.plan_bf16_paged_batch(spec).info()
+    assert chosen.heads_per_cta * (w.kvh // chosen.heads_per_cta) == w.kvh
+    assert w.kvh // chosen.heads_per_cta > 1  # several head blocks: more KV heads than a CTA takes
+    results = []
+    for options in ({}, {"partitions": 1}, {"partitions": 9, "heads_per_cta": 4},
+                    {"partitions": 4, "heads_per_cta": 8}, {"balanced": 1}):
+        bits, lse = run(provider, w, k, v, **options)
+        H.check_decode(bits, lse, *expected, lse_limit=1e-3)
+        results.append((bits, lse))
+    moved_k, moved_v, moved_indices = moved_pool(w, k, v, 11)
+    moved = run(provider, w, moved_k, moved_v, indices=moved_indices, partitions=1)
+    assert np.array_equal(moved[0], results[1][0]) and np.array_equal(moved[1], results[1][1])
+
+
 def test_c3_batch64_gqa4_context4096(provider, oracle):
     w = workloads.c3(with_values=False)
     w.query = workloads.normal_bf16(np.random.default_rng(3), w.batch * w.qh * 128)
     k, v = device_pool(w.max_pages, w.kvh, 0xC3)
     direct = run(provider, w, k, v, partitions=1)
-    sample = [0, 31, 63]
-    expected = oracle_rows(oracle, w, k, v, sample)
-    H.check_decode(*rows_of(*direct, w, sample), *expected, lse_limit=1e-3)
+    everyone = list(range(w.batch))
+    expected = oracle_rows(oracle, w, k, v, everyone)
+    H.check_decode(*rows_of(*direct, w, everyone), *expected, lse_limit=1e-3)
     check_algorithms_agree([direct, run(provider, w, k, v, partitions=4),
                             run(provider, w, k, v, balanced=1)])
     k2, v2, indices2 = moved_pool(w, k, v, 33)
@@ -111,8 +138,9 @@ def test_c4_batch8_gqa8_context32768_with_outliers(provider, oracle):
         outliers.append((int(w.indices[w.indptr[r] + token // 16]), token % 16))
     k, v = device_pool(w.max_pages, w.kvh, 0xC4, outliers)
     split = run(provider, w, k, v, partitions=16)
-    expected = oracle_rows(oracle, w, k, v, [5])
-    H.check_decode(*rows_of(*split, w, [5]), *expected, lse_limit=1e-3, large_outputs=True)
+    everyone = list(range(w.batch))
+    expected = oracle_rows(oracle, w, k, v, everyone)
+    H.check_decode(*rows_of(*split, w, everyone), *expected, lse_limit=1e-3, large_outputs=True)
     check_algorithms_agree([split, run(provider, w, k, v, partitions=1),
                             run(provider, w, k, v, balanced=1)], large_outputs=True)
 
@@ -125,10 +153,9 @@ def test_c5_ragged_256_requests(provider, oracle, label, qh, kvh, first):
     w.query = workloads.normal_bf16(np.random.default_rng(5), w.batch * w.qh * 128)
     k, v = device_pool(w.max_pages, w.kvh, 0xC5 + kvh)
     balanced = run(provider, w, k, v)  # what the plan chooses for this shape
-    shortest, longest = int(np.argmin(lens)), int(np.argmax(lens))
-    sample = sorted({shortest, longest, 17, 200})
-    expected = oracle_rows(oracle, w, k, v, sample)
-    H.check_decode(*rows_of(*balanced, w, sample), *expected, lse_limit=1e-3)
+    everyone = list(range(w.batch))
+    expected = oracle_rows(oracle, w, k, v, everyone)
+    H.check_decode(*rows_of(*balanced, w, everyone), *expected, lse_limit=1e-3)
     check_algorithms_agree([balanced, run(provider, w, k, v, partitions=1)])
 
 

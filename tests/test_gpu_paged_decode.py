@@ -114,6 +114,9 @@ SHAPES = [
     (4, 32, 8, 8, 1), (4, 32, 8, 1, 1), (2, 64, 8, 4, 4), (2, 64, 8, 0, 16),
     (3, 32, 1, 0, 1), (3, 32, 1, 1, 5), (2, 12, 3, 0, 1), (2, 6, 6, 2, 2),
     (2, 40, 1, 0, 1), (1, 72, 1, 0, 2), (2, 160, 1, 0, 1), (1, 4, 2, 1, 1),
+    # more than 8 KV heads: several head blocks per request (MHA 32/32, 16/16, GQA4 64/16)
+    (1, 32, 32, 0, 0), (1, 32, 32, 4, 3), (2, 16, 16, 0, 1), (2, 16, 16, 2, 2), (3, 64, 16, 0, 1),
+    (3, 64, 16, 8, 4),
 ]
 
 
