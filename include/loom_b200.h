@@ -304,7 +304,14 @@ typedef struct lb_paged_decode_options {
                                   fixed-address Graph survives a change of the total page count.
                                   No reference counterpart (the reference lists the mutable-
                                   metadata Graph contract as open, docs/operator-catalog.md). */
-    uint32_t reserved[3];
+    uint32_t wait_limit_us; /* limit of every bounded wait of the plan's kernels (a copy that never
+                               arrives, a rank that never publishes), in microseconds; 0 = about
+                               two seconds.  When it runs out the kernel writes nothing more,
+                               records a status word (lb_decode_provider_device_status) and returns */
+    uint32_t test_skip_page; /* tests of that give-up path only: 1 + the index, within every CTA's
+                                page chunk, of a page whose copies the kernel leaves out; 0 = none.
+                                Direct and split-K plans */
+    uint32_t reserved[1];
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
@@ -388,6 +395,85 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
                                         const int32_t *page_indices, size_t page_indices_len,
                                         const int32_t *last_page_len, void *output, float *lse);
 lb_status lb_paged_decode_split_noalloc_status(int device, int32_t *status);
+
+/* ---- output rows across GPUs (no reference counterpart) ------------------------------------------- */
+
+/* The reference is a single-GPU operator layer.  Paged decode shards over the GPUs of a node by
+ * request (or by KV head) with no exchange step; only the finished output rows cross GPUs, when the
+ * caller wants one contiguous result.  One process per GPU; a peer group is the set of those
+ * processes.  Creating a group, a peer buffer, and enqueueing a gathering command are collective:
+ * every rank makes the same calls in the same order. */
+typedef struct lb_peer_group lb_peer_group;
+typedef struct lb_peer_buffer lb_peer_buffer;
+#define LB_PEER_ID_BYTES 128u
+#define LB_PEER_MAX_RANKS 32
+
+/* One rank makes the id (ncclGetUniqueId) and hands it to the others by any host channel. */
+lb_status lb_peer_group_unique_id(uint8_t *id /* [LB_PEER_ID_BYTES] */);
+/* Joins the group (ncclCommInitRank; the library is resolved with dlopen here, so a single-GPU
+ * host never loads it) and maps the group's signal block on every rank. */
+lb_status lb_peer_group_create(int device, int world, int rank, const uint8_t *id,
+                               lb_peer_group **out);
+/* Not collective.  Call it after every rank has finished using the group (a host barrier). */
+void lb_peer_group_destroy(lb_peer_group *group);
+int lb_peer_group_rank(const lb_peer_group *group);
+int lb_peer_group_world(const lb_peer_group *group);
+
+/* `bytes` of device memory on every rank (cudaMalloc, zeroed), each rank's copy mapped into every
+ * other rank's address space through CUDA IPC.  The local copy is bound like any caller buffer. */
+lb_status lb_peer_buffer_create(lb_peer_group *group, size_t bytes, lb_peer_buffer **out);
+void lb_peer_buffer_destroy(lb_peer_buffer *buffer); /* after a host barrier, as the group */
+void *lb_peer_buffer_local(const lb_peer_buffer *buffer);
+size_t lb_peer_buffer_bytes(const lb_peer_buffer *buffer);
+
+/* The all-gather of per-rank rows as ONE command of the scope: ncclAllGather (grouped
+ * ncclBroadcast when the ranks' row counts differ) on the queue's own stream, recorded like the
+ * reference's vendor-library commands (record_external_submission, crates/loom-infer-cuda/src/
+ * command/submission.rs:240-252; failure path :254-272): it counts in submitted(), completes under
+ * the scope's fence, can be captured, and a failure poisons scope and queue with
+ * LB_EXTERNAL_COMMAND (operand "nccl", a = the library's result code). */
+typedef struct lb_output_gather_plan lb_output_gather_plan;
+typedef struct lb_output_gather_args {
+    lb_handle local;    /* Read:  this rank's rows, rows_per_rank[rank] * row_numel elements */
+    lb_handle gathered; /* Write: every rank's rows in rank order, sum(rows) * row_numel elements */
+} lb_output_gather_args;
+lb_status lb_output_gather_plan_create(const lb_peer_group *group, int dtype,
+                                       const size_t *rows_per_rank /* [world] */, size_t row_numel,
+                                       lb_output_gather_plan **out);
+void lb_output_gather_plan_destroy(lb_output_gather_plan *plan);
+lb_status lb_output_gather_enqueue(const lb_output_gather_plan *plan, lb_scope *scope,
+                                   const lb_output_gather_args *args);
+
+/* Paged decode that leaves its result gathered on every rank, with no collective kernel and no
+ * extra launch: the plan's own kernels store every finished row straight into every rank's copy
+ * of `output` / `lse` (plain stores to peer-mapped memory over NVLink; never a TMA or multicast
+ * load from a peer), the last CTA of the command's last kernel publishes an epoch to every rank
+ * and waits, bounded by the plan's wait_limit_us, until every rank has published its own (when
+ * the wait runs out the provider's device status word reads 2 and the gathered result is
+ * incomplete on this GPU).  The command therefore completes under the scope's fence only when the
+ * gathered result is whole on this GPU.  Same plan, same command count, same checks as lb_paged_decode_enqueue; `output` and
+ * `lse` of the args are this rank's copies of the two peer buffers.
+ *   Row r of the local batch, local query head h is row
+ *       dest_rows[r] * gathered_query_heads + head_offset + h
+ *   of the gathered BF16 [total_requests * gathered_query_heads, 128] output and F32 LSE, so a
+ *   batch split by request (any assignment, no un-permute afterwards) and a batch split by KV
+ *   head are both one call.
+ *   Every rank must enqueue the same sequence of gathering commands on the group.  A rank must
+ *   not overwrite a gathered buffer its peers may still be reading: alternate two buffers step by
+ *   step (a rank that has completed step n+1 knows every rank has completed step n). */
+typedef struct lb_gather_layout {
+    size_t total_requests;       /* requests of the gathered result, over all ranks */
+    size_t gathered_query_heads; /* query heads per request of the gathered result */
+    size_t head_offset;          /* first gathered query head this rank's heads map to */
+} lb_gather_layout;
+typedef struct lb_paged_decode_gather_args {
+    lb_paged_decode_args decode; /* output / lse: bound local copies of the peer buffers below */
+    lb_handle dest_rows;         /* Read<i32> [batch]: gathered request index of each local request */
+} lb_paged_decode_gather_args;
+lb_status lb_paged_decode_enqueue_gathered(const lb_paged_decode_plan *plan, lb_scope *scope,
+                                           const lb_paged_decode_gather_args *args,
+                                           const lb_gather_layout *layout, lb_peer_group *group,
+                                           const lb_peer_buffer *output, const lb_peer_buffer *lse);
 
 /* ---- RoPE + paged KV append provider --------------------------------------------------------- */
 

@@ -52,7 +52,8 @@ class Handle(ctypes.Structure):
 class DecodeOptions(ctypes.Structure):
     _fields_ = [("partitions", c_uint32), ("heads_per_cta", c_uint32), ("balanced", c_uint32),
                 ("balanced_ctas", c_uint32), ("indices_capacity", c_uint32),
-                ("reserved", c_uint32 * 3)]
+                ("wait_limit_us", c_uint32), ("test_skip_page", c_uint32),
+                ("reserved", c_uint32 * 1)]
 
 
 class AppendOptions(ctypes.Structure):
@@ -72,6 +73,19 @@ class DecodeArgs(ctypes.Structure):
     _fields_ = [(name, Handle) for name in
                 ("query", "key_pages", "value_pages", "page_indptr", "page_indices",
                  "last_page_len", "output", "lse", "workspace")]
+
+
+class GatherLayout(ctypes.Structure):
+    _fields_ = [("total_requests", c_size_t), ("gathered_query_heads", c_size_t),
+                ("head_offset", c_size_t)]
+
+
+class DecodeGatherArgs(ctypes.Structure):
+    _fields_ = [("decode", DecodeArgs), ("dest_rows", Handle)]
+
+
+class OutputGatherArgs(ctypes.Structure):
+    _fields_ = [("local", Handle), ("gathered", Handle)]
 
 
 class AppendArgs(ctypes.Structure):
@@ -196,6 +210,23 @@ SIGNATURES = {
                                                 c_void_p, c_void_p, _I32P, _I32P, c_size_t, _I32P,
                                                 c_void_p, c_void_p]),
     "lb_paged_decode_split_noalloc_status": (c_int32, [c_int, POINTER(c_int32)]),
+    "lb_peer_group_unique_id": (c_int32, [POINTER(ctypes.c_uint8)]),
+    "lb_peer_group_create": (c_int32, [c_int, c_int, c_int, POINTER(ctypes.c_uint8),
+                                       POINTER(c_void_p)]),
+    "lb_peer_group_destroy": (None, [c_void_p]),
+    "lb_peer_group_rank": (c_int, [c_void_p]),
+    "lb_peer_group_world": (c_int, [c_void_p]),
+    "lb_peer_buffer_create": (c_int32, [c_void_p, c_size_t, POINTER(c_void_p)]),
+    "lb_peer_buffer_destroy": (None, [c_void_p]),
+    "lb_peer_buffer_local": (c_void_p, [c_void_p]),
+    "lb_peer_buffer_bytes": (c_size_t, [c_void_p]),
+    "lb_output_gather_plan_create": (c_int32, [c_void_p, c_int, POINTER(c_size_t), c_size_t,
+                                               POINTER(c_void_p)]),
+    "lb_output_gather_plan_destroy": (None, [c_void_p]),
+    "lb_output_gather_enqueue": (c_int32, [c_void_p, c_void_p, POINTER(OutputGatherArgs)]),
+    "lb_paged_decode_enqueue_gathered": (c_int32, [c_void_p, c_void_p, POINTER(DecodeGatherArgs),
+                                                   POINTER(GatherLayout), c_void_p, c_void_p,
+                                                   c_void_p]),
     "lb_rope_provider_load": (c_int32, [c_int, POINTER(c_void_p)]),
     "lb_rope_provider_destroy": (None, [c_void_p]),
     "lb_rope_append_plan_create": (c_int32, [c_void_p, POINTER(PagedSpec), POINTER(c_void_p)]),

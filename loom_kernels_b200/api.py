@@ -530,15 +530,19 @@ class DecodeProvider:
 
     def plan_bf16_paged_batch(self, spec: Bf16PagedBatchDecodeSpec, partitions: int = 0,
                               heads_per_cta: int = 0, balanced: int = 0,
-                              balanced_ctas: int = 0,
-                              indices_capacity: bool = False) -> "Bf16PagedBatchDecodePlan":
+                              balanced_ctas: int = 0, indices_capacity: bool = False,
+                              wait_limit_us: int = 0,
+                              test_skip_page: int = 0) -> "Bf16PagedBatchDecodePlan":
         """partitions: 0 heuristic, 1 direct, N split-K; balanced (with partitions 0): 0
         heuristic, 1 force the balanced algorithm, 2 never use it.  indices_capacity: the bound
         page_indices may be longer than the table in use (page_indptr[batch] <= len), which
-        lets one fixed-address Graph serve steps with different total page counts."""
+        lets one fixed-address Graph serve steps with different total page counts.
+        wait_limit_us: limit of the kernels' bounded waits (0 = about two seconds);
+        test_skip_page: tests of the give-up path only."""
         options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta,
                                      balanced=balanced, balanced_ctas=balanced_ctas,
-                                     indices_capacity=1 if indices_capacity else 0)
+                                     indices_capacity=1 if indices_capacity else 0,
+                                     wait_limit_us=wait_limit_us, test_skip_page=test_skip_page)
         out = c_void_p()
         _check(_abi.load().lb_paged_decode_plan_create(self._ptr, byref(spec._raw),
                                                        byref(options), byref(out)))
@@ -585,6 +589,132 @@ class Bf16PagedBatchDecodePlan:
             output=args.output._raw, lse=args.lse._raw,
             workspace=args.workspace._raw if args.workspace is not None else _null_handle())
         _check(_abi.load().lb_paged_decode_enqueue(self._ptr, scope._ptr, byref(raw)))
+
+    def enqueue_gathered_into(self, scope: CommandScope, args: Bf16PagedBatchDecodeArgs,
+                              dest_rows: Read, group: "PeerGroup", output: "PeerBuffer",
+                              lse: "PeerBuffer", total_requests: int,
+                              gathered_query_heads: int = 0, head_offset: int = 0):
+        """lb_paged_decode_enqueue_gathered: args.output / args.lse are the bound local copies of
+        the peer buffers `output` / `lse`; every finished row goes to every rank's copy."""
+        decode = _abi.DecodeArgs(
+            query=args.query._raw, key_pages=args.key_pages._raw,
+            value_pages=args.value_pages._raw, page_indptr=args.page_indptr._raw,
+            page_indices=args.page_indices._raw, last_page_len=args.last_page_len._raw,
+            output=args.output._raw, lse=args.lse._raw,
+            workspace=args.workspace._raw if args.workspace is not None else _null_handle())
+        raw = _abi.DecodeGatherArgs(decode=decode, dest_rows=dest_rows._raw)
+        layout = _abi.GatherLayout(
+            total_requests=total_requests,
+            gathered_query_heads=gathered_query_heads or self._spec.num_query_heads,
+            head_offset=head_offset)
+        _check(_abi.load().lb_paged_decode_enqueue_gathered(
+            self._ptr, scope._ptr, byref(raw), byref(layout), group._ptr, output._ptr, lse._ptr))
+
+
+# ---- output rows across GPUs ------------------------------------------------------------------------
+
+
+class PeerGroup:
+    """The ranks of one job, one process per GPU (lb_peer_group).  Creating a group, a peer buffer
+    and enqueueing a gathering command are collective."""
+
+    ID_BYTES = 128
+
+    @staticmethod
+    def unique_id() -> bytes:
+        raw = (ctypes.c_uint8 * PeerGroup.ID_BYTES)()
+        _check(_abi.load().lb_peer_group_unique_id(raw))
+        return bytes(raw)
+
+    def __init__(self, device: int, world: int, rank: int, unique_id: bytes):
+        raw = (ctypes.c_uint8 * PeerGroup.ID_BYTES).from_buffer_copy(unique_id)
+        out = c_void_p()
+        _check(_abi.load().lb_peer_group_create(device, world, rank, raw, byref(out)))
+        self._ptr = out.value
+        self._buffers = []
+
+    @classmethod
+    def from_torch_distributed(cls, device: int) -> "PeerGroup":
+        """Joins the ranks of the default torch.distributed group (the id travels by broadcast)."""
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(), dist.get_rank()
+        box = [cls.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return cls(device, world, rank, box[0])
+
+    def rank(self): return _abi.load().lb_peer_group_rank(self._ptr)
+    def world(self): return _abi.load().lb_peer_group_world(self._ptr)
+
+    def buffer(self, numel: int, dtype: int) -> "PeerBuffer":
+        return PeerBuffer(self, numel, dtype)
+
+    def close(self):
+        """After a host barrier: no rank may still store into this rank's buffers."""
+        for buffer in self._buffers:
+            buffer.close()
+        self._buffers = []
+        if self._ptr:
+            _abi.load().lb_peer_group_destroy(self._ptr)
+            self._ptr = None
+
+
+class PeerBuffer:
+    """Device memory of the same size on every rank, each copy mapped on every other rank
+    (lb_peer_buffer).  `span` binds the local copy; `tensor()` views it as a torch tensor."""
+
+    _ELEMENT_BYTES = {F32: 4, F16: 2, BF16: 2, I32: 4, U8: 1}
+
+    def __init__(self, group: PeerGroup, numel: int, dtype: int):
+        out = c_void_p()
+        _check(_abi.load().lb_peer_buffer_create(group._ptr, numel * self._ELEMENT_BYTES[dtype],
+                                                 byref(out)))
+        self._ptr = out.value
+        self.numel, self.dtype = numel, dtype
+        self.span = DeviceSpan(_abi.load().lb_peer_buffer_local(self._ptr), numel, dtype)
+        group._buffers.append(self)
+
+    def tensor(self, device):
+        """A torch view of the local copy (the library owns the memory; keep this object alive)."""
+        import torch
+        kinds = {F32: ("<f4", torch.float32), I32: ("<i4", torch.int32), U8: ("|u1", torch.uint8),
+                 BF16: ("<i2", torch.bfloat16), F16: ("<f2", torch.float16)}
+        typestr, dtype = kinds[self.dtype]
+
+        class _Holder:
+            __cuda_array_interface__ = {"shape": (self.numel,), "typestr": typestr,
+                                        "data": (self.span.ptr, False), "version": 3}
+        view = torch.as_tensor(_Holder(), device=device)
+        return view.view(dtype) if view.dtype != dtype else view
+
+    def close(self):
+        if self._ptr:
+            _abi.load().lb_peer_buffer_destroy(self._ptr)
+            self._ptr = None
+
+
+@dataclass
+class OutputGatherArgs:
+    local: Read
+    gathered: Write
+
+
+class OutputGatherPlan:
+    """The all-gather of per-rank rows as one command of the scope (lb_output_gather_*)."""
+
+    def __init__(self, group: PeerGroup, dtype: int, rows_per_rank: Sequence[int], row_numel: int):
+        rows = (c_size_t * len(rows_per_rank))(*rows_per_rank)
+        out = c_void_p()
+        _check(_abi.load().lb_output_gather_plan_create(group._ptr, dtype, rows, row_numel,
+                                                        byref(out)))
+        self._ptr = out.value
+        self._group = group
+
+    def __del__(self):
+        _dispose(self, "lb_output_gather_plan_destroy")
+
+    def enqueue_into(self, scope: CommandScope, args: OutputGatherArgs):
+        raw = _abi.OutputGatherArgs(local=args.local._raw, gathered=args.gathered._raw)
+        _check(_abi.load().lb_output_gather_enqueue(self._ptr, scope._ptr, byref(raw)))
 
 
 def paged_decode_split_noalloc(spec: Bf16PagedBatchDecodeSpec, partitions: int, stream, query,

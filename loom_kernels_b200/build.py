@@ -10,8 +10,8 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libloom_b200.so")
 SOURCES = ["errors.cpp", "contract.cpp", "driver.cpp", "command.cpp", "graph.cpp",
-           "providers.cpp", "prefill_provider.cpp", "prefill_kernels.cu", "prefill_tiled_kernel.cu", "decode_kernels.cu", "decode_stream_kernel.cu", "append_kernels.cu", "static_scratch.cu"]
-HEADERS = ["runtime.hpp", "kernels.hpp", "decode_device.cuh", "dependent_launch.cuh", "prefill_device.cuh", "tcgen05_device.cuh", os.path.join(ROOT, "include", "loom_b200.h")]
+           "providers.cpp", "peer_group.cpp", "prefill_provider.cpp", "prefill_kernels.cu", "prefill_tiled_kernel.cu", "decode_kernels.cu", "decode_stream_kernel.cu", "append_kernels.cu", "static_scratch.cu"]
+HEADERS = ["runtime.hpp", "kernels.hpp", "peer_group.hpp", "decode_device.cuh", "dependent_launch.cuh", "prefill_device.cuh", "tcgen05_device.cuh", os.path.join(ROOT, "include", "loom_b200.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-x", "cu",
@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     subprocess.run([NVCC, "-shared", "-o", LIB, *objects, "-gencode",
-                    "arch=compute_100a,code=sm_100a"], check=True)
+                    "arch=compute_100a,code=sm_100a", "-ldl"], check=True)
     return LIB
 
 

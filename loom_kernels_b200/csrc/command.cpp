@@ -85,6 +85,16 @@ lb_status submit_launch(Scope &scope, const std::function<int()> &launch) {
     return fail(LB_DRIVER, "launch", error);
 }
 
+lb_status submit_external(Scope &scope, const char *provider, const std::function<int()> &call) {
+    const int error = driver().external(scope.queue->device, call);
+    if (error == 0) {
+        record_submission(scope);
+        return LB_OK;
+    }
+    record_failed_submission(scope, error);
+    return fail(LB_EXTERNAL_COMMAND, provider, error);
+}
+
 namespace {
 
 bool valid_dtype(int dtype) { return dtype >= LB_F32 && dtype <= LB_U8; }

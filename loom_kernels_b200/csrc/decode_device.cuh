@@ -13,6 +13,7 @@
 #include <cstdint>
 
 #include "dependent_launch.cuh"
+#include "kernels.hpp"
 
 // A profiling build may define LB_STAMP(slot) before this header to record a per-warp timeline
 // of the kernels; in the product it expands to nothing.
@@ -55,15 +56,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "memory");
     return done != 0;
 }
-// Bounded wait: false after kWaitCycles without the phase completing.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: false after `limit` cycles without the phase completing.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
         for (int spin = 0; spin < 256; ++spin)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - start > kWaitCycles) return false;
+        if (clock64() - start > limit) return false;
     }
 }
 __device__ __forceinline__ void fence_barrier_init() {
@@ -317,6 +319,118 @@ __device__ __forceinline__ void write_state_row(float *state, int lane, int half
             make_float2(st.acc[nt][half * 2], st.acc[nt][half * 2 + 1]);
 }
 
+// ---- output rows across GPUs ------------------------------------------------------------------------
+//
+// A command whose plan gathers its output writes every finished row straight into every rank's
+// copy of one gathered result (peer-mapped device memory, plain stores over NVLink; this rank's
+// own copy is one of them), instead of into a local buffer that a collective would then move.
+// Row r of the local batch, local query head h lands at row
+//     dest_rows[r] * gathered_qh + head_offset + h
+// of the gathered [rows, 128] BF16 output and the gathered F32 LSE.
+//
+// The last kernel of a gathering command counts its CTAs; the last one to finish publishes a new
+// epoch in every rank's flag array and then waits (bounded) until every rank has published the
+// same epoch, so that the kernel -- and with it the command -- completes only when the gathered
+// result is whole on this GPU.  Ranks are other GPUs running the same command; they never share
+// a GPU with the waiter.
+using ::lb::PeerOut;    // kernels.hpp: where the finished rows go when a plan gathers its output
+using ::lb::PeerSignal; // kernels.hpp: the epoch the last kernel of such a command publishes
+
+__device__ __forceinline__ void store_release_system(uint32_t *address, uint32_t value) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_system(const uint32_t *address) {
+    uint32_t value;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+    return value;
+}
+
+// Called by every thread of every CTA of the kernel, after its last store.
+__device__ __forceinline__ void peer_signal_and_wait(const PeerSignal &s) {
+    if (s.world == 0) return;
+    dependent_launch_wait();  // a CTA that left early has not passed it yet
+    __threadfence_system();   // this thread's rows are performed before its CTA is counted
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    const int lane = threadIdx.x;
+    unsigned last = 0;
+    if (lane == 0) last = atomicAdd(s.done, 1u) == gridDim.x - 1 ? 1u : 0u;
+    if (!__shfl_sync(0xffffffffu, last, 0)) return;
+    __threadfence_system(); // every CTA fenced before it was counted: all rows precede the epoch
+    uint32_t epoch = 0;
+    if (lane == 0) {
+        *s.done = 0; // the next kernel counts from zero (it starts after this one has completed)
+        epoch = *s.epoch + 1;
+        *s.epoch = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    if (lane < s.world) store_release_system(s.flags[lane] + kPeerFlagsWord + s.rank, epoch);
+    bool arrived = true;
+    if (lane < s.world) {
+        const uint32_t *mine = s.flags[s.rank] + kPeerFlagsWord + lane;
+        arrived = (int32_t)(load_acquire_system(mine) - epoch) >= 0;
+        const long long start = clock64();
+        while (!arrived) {
+#pragma unroll 1
+            for (int spin = 0; spin < 64 && !arrived; ++spin)
+                arrived = (int32_t)(load_acquire_system(mine) - epoch) >= 0;
+            if (clock64() - start > s.wait_cycles) break;
+        }
+    }
+    if (__any_sync(0xffffffffu, !arrived) && lane == 0 && s.status) atomicExch(s.status, 2);
+}
+
+// 4 x 4 transpose of 32-bit words among the four lanes of a quad: afterwards lane c holds, in
+// r[k], what lane k held in r[c].
+__device__ __forceinline__ void quad_transpose(uint32_t (&r)[4], int lane) {
+    const bool odd = lane & 1, upper = lane & 2;
+#pragma unroll
+    for (int k = 0; k < 4; k += 2) {
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? r[k] : r[k + 1], 1);
+        if (odd) r[k] = other;
+        else r[k + 1] = other;
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, upper ? r[k] : r[k + 2], 2);
+        if (upper) r[k] = other;
+        else r[k + 2] = other;
+    }
+}
+
+// The two rows a lane owns (MMA accumulator layout), normalised, as BF16 into every rank's copy
+// of the gathered result.  The four lanes of a quad first exchange their 4-byte pieces so that a
+// lane owns whole 16-byte chunks: a row leaves as 16-byte stores, 64 contiguous bytes per quad.
+// Every lane of the warp must call (the exchange is warp-wide); rows[half] < 0 stores nothing.
+__device__ __forceinline__ void write_final_rows_to_peers(const PeerOut &peer, const long long (&rows)[2],
+                                                          int lane, const WarpState &st) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const float l = st.row_sum[half];
+        const float inv = 1.0f / l;
+        uint4 chunk[4]; // chunk[j] = bytes (4j + (lane & 3)) * 16 .. + 16 of the row
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t r[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                r[k] = pack_bf16(st.acc[4 * j + k][half * 2] * inv,
+                                 st.acc[4 * j + k][half * 2 + 1] * inv);
+            quad_transpose(r, lane);
+            chunk[j] = make_uint4(r[0], r[1], r[2], r[3]);
+        }
+        if (rows[half] < 0) continue;
+        const float lse = st.row_max[half] + log2f(l);
+        for (int p = 0; p < peer.world; ++p) {
+            uint4 *row = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(peer.out[p]) +
+                                                   rows[half] * kHeadDim);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) row[4 * j + (lane & 3)] = chunk[j];
+            if ((lane & 3) == 0) peer.lse[p][rows[half]] = lse;
+        }
+    }
+}
+
 // Merges n unnormalised states [max_log2, normaliser, wv[128]] of one (request, query head) and
 // writes BF16 O + log2 LSE.  state_of(i) returns the i-th state or nullptr for "no state";
 // states with a zero normaliser (chunks without pages) are skipped as in the reference's device
@@ -435,6 +549,21 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     if (!merge_partial(state_of, n, lane, top, norm, acc) || !publish) return;
     if (!(norm > 0.0f)) return; // every state was empty: nothing to publish
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
+}
+
+// As merge_states, into row `row` of every rank's copy of the gathered result.
+template <typename StateOf>
+__device__ __forceinline__ void merge_states_to_peers(StateOf state_of, int n, int lane,
+                                                      bool publish, const PeerOut &peer,
+                                                      long long row) {
+    float top, norm;
+    float4 acc;
+    if (!merge_partial(state_of, n, lane, top, norm, acc) || !publish) return;
+    if (!(norm > 0.0f)) return;
+    for (int p = 0; p < peer.world; ++p)
+        publish_merged(top, norm, acc, lane,
+                       static_cast<__nv_bfloat16 *>(peer.out[p]) + row * kHeadDim,
+                       peer.lse[p] + row);
 }
 
 // The even cut of `total` units over `workers` workers, evaluated without 64-bit division:

@@ -46,13 +46,17 @@ struct DecodeArgs {
     int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, partitions, stages;
     float scale_log2;
+    int32_t skip_page;     // tests of the give-up path: 1 + the page whose loads are left out
+    long long wait_cycles; // limit of every bounded wait
+    PeerOut peer;          // world == 0 unless the plan gathers its output
+    PeerSignal signal;     // world == 0 unless this kernel is the last of a gathering command
 };
 
-__global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
-paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const DecodeArgs a) {
+// The work of one CTA.  A thread that has nothing (more) to do returns from here; every thread
+// of the grid then meets again in the kernel below.
+__device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const CUtensorMap &v_map,
+                                                 const DecodeArgs &a) {
     extern __shared__ uint8_t smem_raw[];
-    dependent_launch_release();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
@@ -188,14 +192,18 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const bool has = lane_active && slot < cnt;
             const uint32_t bar_full = my_full + stage * a.pps * 8;
             bool ok = true;
-            if (has && recycled) ok = mbar_wait(my_empty + stage * a.pps * 8, phase ^ 1);
+            if (has && recycled)
+                ok = mbar_wait(my_empty + stage * a.pps * 8, phase ^ 1, a.wait_cycles);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
                 break;
             }
             if (has && which == 0) mbar_expect_tx(bar_full, slot_bytes);
             __syncwarp();
-            if (has) tma_load_3d(my_tile + stage * stage_bytes, map, 0, page_id * kPage, z, bar_full);
+            // (a test of the give-up path leaves one page's loads out: its consumers' wait for the
+            // expected bytes then runs out, which is all a lost copy would look like)
+            if (has && slot + 1 != a.skip_page)
+                tma_load_3d(my_tile + stage * stage_bytes, map, 0, page_id * kPage, z, bar_full);
             if (it == 0) LB_STAMP(4);
             if (++stage == a.stages) {
                 stage = 0;
@@ -224,7 +232,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         int stage = 0;
         uint32_t phase = 0;
         for (int it = 0; it < my_pages; ++it) {
-            const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase);
+            const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
                 break;
@@ -306,6 +314,16 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     // ---- epilogue ---------------------------------------------------------------------------------
     const int kv_head = hb * a.hc + head_in_cta;
     const int g0 = qb * rows_per_block + mtile * 16 + (lane >> 2);
+    if (a.partitions == 1 && a.peer.world != 0) {
+        // the finished rows go straight into every rank's copy of the gathered result
+        const long long row0 =
+            (long long)a.peer.dest_rows[request] * a.peer.gathered_qh + a.peer.head_offset +
+            (long long)kv_head * group;
+        const long long rows[2] = {g0 < group && !invalid_page ? row0 + g0 : -1,
+                                   g0 + 8 < group && !invalid_page ? row0 + g0 + 8 : -1};
+        write_final_rows_to_peers(a.peer, rows, lane, st);
+        return;
+    }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int g = g0 + half * 8;
@@ -322,12 +340,21 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     LB_STAMP(10);
 }
 
-// Merges the split-K states of one (request, query head) per warp (merge_states).
-__global__ void __launch_bounds__(128)
-split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
-                   const int32_t *indptr, const int32_t *last, int batch, int qh, int partitions,
-                   int indices_min, int indices_len) {
+__global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
+paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const DecodeArgs a) {
     dependent_launch_release();
+    paged_decode_cta(k_map, v_map, a);
+    peer_signal_and_wait(a.signal);
+}
+
+// Merges the split-K states of one (request, query head) per warp (merge_states).
+__device__ __forceinline__ void split_merge_warp(const float *__restrict__ workspace,
+                                                 __nv_bfloat16 *output, float *lse,
+                                                 const int32_t *indptr, const int32_t *last,
+                                                 int batch, int qh, int partitions,
+                                                 int indices_min, int indices_len,
+                                                 const PeerOut &peer) {
     const int lane = threadIdx.x & 31;
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
@@ -339,8 +366,24 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
                        request_metadata_valid(indptr, last, batch, indices_min, indices_len, request,
                                               page_start, page_end, tail);
     const float *st = workspace + (size_t)state * partitions * kStateWidth;
-    merge_states([&](int p) { return st + (size_t)p * kStateWidth; }, partitions, lane, valid,
-                 output + (size_t)state * kHeadDim, lse + state);
+    auto state_of = [&](int p) { return st + (size_t)p * kStateWidth; };
+    if (peer.world != 0) {
+        const long long row = (long long)peer.dest_rows[request] * peer.gathered_qh +
+                              peer.head_offset + (state - request * qh);
+        merge_states_to_peers(state_of, partitions, lane, valid, peer, row);
+        return;
+    }
+    merge_states(state_of, partitions, lane, valid, output + (size_t)state * kHeadDim, lse + state);
+}
+
+__global__ void __launch_bounds__(128)
+split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
+                   const int32_t *indptr, const int32_t *last, int batch, int qh, int partitions,
+                   int indices_min, int indices_len, const PeerOut peer, const PeerSignal signal) {
+    dependent_launch_release();
+    split_merge_warp(workspace, output, lse, indptr, last, batch, qh, partitions, indices_min,
+                     indices_len, peer);
+    peer_signal_and_wait(signal);
 }
 
 } // namespace
@@ -375,6 +418,10 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     args.partitions = launch.partitions;
     args.stages = launch.stages;
     args.scale_log2 = launch.scale_log2;
+    args.skip_page = launch.test_skip_page;
+    args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
+    args.peer = launch.peer;
+    args.signal = launch.signal;
     CUtensorMap k_map, v_map;
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
     memcpy(&k_map, launch.k_map, sizeof(k_map));
@@ -387,7 +434,10 @@ int launch_split_merge(const MergeLaunch &launch, void *stream) {
     return launch_dependent(split_merge_kernel, launch.grid, launch.block, 0, stream,
                             launch.workspace, static_cast<__nv_bfloat16 *>(launch.output),
                             launch.lse, launch.indptr, launch.last, launch.batch, launch.qh,
-                            launch.partitions, launch.indices_min, launch.indices_len);
+                            launch.partitions, launch.indices_min, launch.indices_len, launch.peer,
+                            launch.signal);
 }
+
+long long default_wait_cycles() { return kWaitCycles; }
 
 } // namespace lb

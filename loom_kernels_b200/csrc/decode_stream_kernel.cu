@@ -42,6 +42,8 @@ struct StreamArgs {
     int32_t hc, pps, mt, qb, stages, workers;
     int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
     float scale_log2;
+    long long wait_cycles; // limit of every bounded wait
+    PeerOut peer;          // world == 0 unless the plan gathers its output
 };
 
 __device__ __forceinline__ size_t state_floats(int workers, int hc, int rows) {
@@ -215,7 +217,8 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const bool has = lane_active && j < my_count;
             const uint32_t bar_full = my_full + stage * a.pps * 8;
             bool ok = true;
-            if (has && recycled) ok = mbar_wait(my_empty + stage * a.pps * 8, phase ^ 1);
+            if (has && recycled)
+                ok = mbar_wait(my_empty + stage * a.pps * 8, phase ^ 1, a.wait_cycles);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) *timeout_flag = 1;
                 break;
@@ -280,7 +283,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const int tail = ptail[r];
             const int last_in_segment = num_pages - 1 - first_page; // p of the request's last page
             for (int p = 0; p < seg_pages; ++p) {
-                const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase);
+                const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles);
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) *timeout_flag = 1;
                     live = false;
@@ -306,6 +309,15 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             st.finish_rows();
             const bool complete = first_page == 0 && seg_pages == num_pages;
             const int which = first_segment ? 0 : 1;
+            if (complete && a.peer.world != 0) {
+                // finished in place: straight into every rank's copy of the gathered result
+                const int g0 = qb * rows_per_block + mtile * 16 + (lane >> 2);
+                const long long row0 = (long long)a.peer.dest_rows[r] * a.peer.gathered_qh +
+                                       a.peer.head_offset + (long long)kv_head * group;
+                const long long rows[2] = {g0 < group && !bad ? row0 + g0 : -1,
+                                           g0 + 8 < group && !bad ? row0 + g0 + 8 : -1};
+                write_final_rows_to_peers(a.peer, rows, lane, st);
+            } else
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int row = mtile * 16 + (lane >> 2) + half * 8; // row within the query block
@@ -333,6 +345,9 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
     }
     LB_STAMP(6);
+    // rows this CTA stored into other GPUs' memory are performed before the grid counts as
+    // complete: the merge kernel, which follows, publishes the epoch that tells the peers so
+    if (a.peer.world != 0) __threadfence_system();
     __syncthreads();
     LB_STAMP(7);
     if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);
@@ -340,11 +355,10 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
 
 // One warp per (request, query head): finds the workers whose ranges cut this head's item and
 // merges their states.  Items that one worker finished alone are skipped.
-__global__ void __launch_bounds__(128)
-balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
-                      int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
-                      int rows) {
-    dependent_launch_release();
+__device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ workspace,
+                                                    __nv_bfloat16 *output, float *lse, int batch,
+                                                    int qh, int kvh, int hc, int mt, int qblocks,
+                                                    int workers, int rows, const PeerOut &peer) {
     const int lane = threadIdx.x & 31;
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
@@ -372,11 +386,26 @@ balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output
     const size_t slot_stride = (size_t)hc * rows * kStateWidth;
     const float *base = workspace + (size_t)w0 * 2 * slot_stride +
                         ((size_t)head_in_cta * rows + row) * kStateWidth;
-    merge_states(
-        [&](int i) -> const float * {
-            return base + ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
-        },
-        w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim, lse + state);
+    auto state_of = [&](int i) -> const float * {
+        return base + ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
+    };
+    if (peer.world != 0) {
+        const long long row =
+            (long long)peer.dest_rows[request] * peer.gathered_qh + peer.head_offset + qhead;
+        merge_states_to_peers(state_of, w1 - w0 + 1, lane, true, peer, row);
+        return;
+    }
+    merge_states(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim, lse + state);
+}
+
+__global__ void __launch_bounds__(128)
+balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
+                      int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
+                      int rows, const PeerOut peer, const PeerSignal signal) {
+    dependent_launch_release();
+    balanced_merge_warp(workspace, output, lse, batch, qh, kvh, hc, mt, qblocks, workers, rows,
+                        peer);
+    peer_signal_and_wait(signal);
 }
 
 int balanced_state_rows(const DecodeLaunch &launch) {
@@ -416,6 +445,8 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     args.workers = (int32_t)launch.grid * launch.pages_per_stage;
     args.rows = balanced_state_rows(launch);
     args.scale_log2 = launch.scale_log2;
+    args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
+    args.peer = launch.peer;
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
@@ -430,7 +461,7 @@ int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t bl
                             static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.batch,
                             launch.qh, launch.kvh, launch.heads_per_cta, launch.q_tiles,
                             launch.q_blocks, (int)launch.grid * launch.pages_per_stage,
-                            balanced_state_rows(launch));
+                            balanced_state_rows(launch), launch.peer, launch.signal);
 }
 
 } // namespace lb

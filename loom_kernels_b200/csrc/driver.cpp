@@ -132,6 +132,13 @@ struct CudaDriver final : Driver {
         if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
         return rc;
     }
+    int external(int device, const std::function<int()> &fn) override {
+        DeviceGuard guard(device);
+        return fn();
+    }
+    int device_clock_khz(int device, int *khz) override {
+        return cudaDeviceGetAttribute(khz, cudaDevAttrClockRate, device);
+    }
     int capture_begin(int device, void *stream) override {
         DeviceGuard guard(device);
         return cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal);
@@ -254,6 +261,8 @@ struct FakeDriver final : Driver {
         if (error == 0) ++launches;
         return error;
     }
+    int external(int, const std::function<int()> &) override { return hit("external"); }
+    int device_clock_khz(int, int *khz) override { *khz = 1965000; return 0; }
     int capture_begin(int, void *stream) override {
         const int error = hit("capture_begin");
         if (error == 0) capturing[stream] = true;

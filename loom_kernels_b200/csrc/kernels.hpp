@@ -6,6 +6,32 @@
 
 namespace lb {
 
+// Where finished rows go when a plan gathers its output over the ranks of a peer group: row r of
+// the local batch, local query head h is row dest_rows[r] * gathered_qh + head_offset + h of the
+// gathered [rows, 128] BF16 output and F32 LSE, in every rank's copy.  world == 0: no gather.
+struct PeerOut {
+    void *const *out;         // device array [world]: every rank's copy of the gathered O
+    float *const *lse;        // device array [world]: every rank's copy of the gathered LSE
+    const int32_t *dest_rows; // [batch]
+    int32_t world, gathered_qh, head_offset;
+};
+
+// A rank's signal block is an array of 32-bit words in peer-mapped memory: word 0 counts finished
+// CTAs, word 1 is the epoch, and the flags the other ranks write start at this word.
+constexpr int kPeerFlagsWord = 32;
+
+// What the last kernel of a gathering command needs to publish its epoch to every rank and to
+// wait for theirs.  world == 0: nothing to signal.
+struct PeerSignal {
+    uint32_t *done;         // this GPU: CTAs of the running kernel that have finished
+    uint32_t *epoch;        // this GPU: epochs published so far
+    uint32_t *const *flags; // device array [world]: every rank's signal block (flags at word
+                            // kPeerFlagsWord, one per sender)
+    int32_t *status;        // set to 2 when the wait for the other ranks ran out
+    int32_t rank, world;
+    long long wait_cycles;
+};
+
 // One paged-decode launch.  Every pointer is a device pointer of the queue's device.
 struct DecodeLaunch {
     alignas(64) unsigned char k_map[128]; // CUtensorMap over K pages, see decode_kernels.cu
@@ -23,6 +49,11 @@ struct DecodeLaunch {
     int32_t heads_per_cta, pages_per_stage, q_tiles, q_blocks, partitions, stages;
     float scale_log2;
     uint32_t grid, block, shared_bytes;
+    long long wait_cycles;  // limit of every bounded wait of the kernel, in SM clock cycles
+    int32_t test_skip_page; // tests of the give-up path: 1 + the page of a CTA's chunk whose
+                            // loads the producer leaves out (0 = none)
+    PeerOut peer;           // zeroed unless the plan gathers its output
+    PeerSignal signal;      // zeroed unless this launch is the last kernel of a gathering command
 };
 
 struct MergeLaunch {
@@ -33,6 +64,8 @@ struct MergeLaunch {
     const int32_t *last;
     int32_t batch, qh, partitions, indices_len, indices_min;
     uint32_t grid, block;
+    PeerOut peer;
+    PeerSignal signal;
 };
 
 // One fused RoPE + paged append launch.
@@ -57,6 +90,7 @@ int configure_stream_kernels(size_t max_dynamic_shared);
 // holds [workers][2][heads_per_cta * min(group, 16 * q_tiles)][130] floats, then batch + 1 ints.
 int launch_balanced_decode(const DecodeLaunch &launch, void *stream);
 int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block, void *stream);
+long long default_wait_cycles(); // ~2 s of SM clock
 int launch_paged_decode(const DecodeLaunch &launch, void *stream);
 int launch_split_merge(const MergeLaunch &launch, void *stream);
 int configure_append_kernels(size_t max_dynamic_shared, const float *inverse_frequency);

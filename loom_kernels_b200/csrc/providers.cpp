@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include "kernels.hpp"
+#include "peer_group.hpp"
 #include "runtime.hpp"
 
 using namespace lb;
@@ -19,6 +20,7 @@ using namespace lb;
 struct lb_decode_provider {
     int device = 0, sm_count = 0;
     size_t smem_optin = 0;
+    int clock_khz = 0;
     int32_t *status = nullptr; // device word written by a kernel that gave up on a wait
 };
 
@@ -28,6 +30,8 @@ struct lb_paged_decode_plan {
     int device = 0;
     int32_t *status = nullptr;
     bool indices_capacity = false; // page_indices may be bound longer than the table in use
+    long long wait_cycles = 0;     // 0 = the kernels' default (about two seconds)
+    int32_t test_skip_page = 0;
 };
 
 struct lb_rope_provider {
@@ -134,6 +138,7 @@ lb_status lb_decode_provider_load(int device, lb_decode_provider **out) {
     provider->sm_count = sm_count;
     provider->smem_optin = smem;
     provider->status = status;
+    driver().device_clock_khz(device, &provider->clock_khz);
     *out = provider;
     return LB_OK;
 }
@@ -179,8 +184,15 @@ lb_status lb_paged_decode_plan_create(const lb_decode_provider *provider, const 
         return rc;
     if (options && options->indices_capacity > 1)
         return fail(LB_LAUNCH_CONTRACT, "indices_capacity", options->indices_capacity);
+    if (options && options->test_skip_page && choice.algorithm == LB_DECODE_BALANCED)
+        return fail(LB_LAUNCH_CONTRACT, "test_skip_page", options->test_skip_page);
     lb_paged_decode_plan *plan = new lb_paged_decode_plan();
     plan->indices_capacity = options && options->indices_capacity == 1;
+    if (options && options->wait_limit_us) {
+        const long long khz = provider->clock_khz > 0 ? provider->clock_khz : 1965000;
+        plan->wait_cycles = (long long)options->wait_limit_us * khz / 1000;
+    }
+    plan->test_skip_page = options ? (int32_t)options->test_skip_page : 0;
     plan->spec = checked;
     plan->choice = choice;
     plan->device = provider->device;
@@ -199,9 +211,53 @@ lb_status lb_paged_decode_plan_info_get(const lb_paged_decode_plan *plan, lb_pag
     return LB_OK;
 }
 
+namespace {
+
+// Where a gathering enqueue sends its rows (lb_paged_decode_enqueue_gathered).
+struct GatherTarget {
+    const lb_gather_layout *layout;
+    lb_peer_group *group;
+    const lb_peer_buffer *output, *lse;
+    lb_handle dest_rows;
+};
+
+lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
+                         const lb_paged_decode_args *args, const GatherTarget *gather);
+
+} // namespace
+
 lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *scope,
                                   const lb_paged_decode_args *args) {
     if (!plan || !scope || !args) return fail(LB_INVALID_ARGUMENT, "plan");
+    return enqueue_decode(plan, scope, args, nullptr);
+}
+
+lb_status lb_paged_decode_enqueue_gathered(const lb_paged_decode_plan *plan, lb_scope *scope,
+                                           const lb_paged_decode_gather_args *args,
+                                           const lb_gather_layout *layout, lb_peer_group *group,
+                                           const lb_peer_buffer *output, const lb_peer_buffer *lse) {
+    if (!plan || !scope || !args || !layout || !group || !output || !lse)
+        return fail(LB_INVALID_ARGUMENT, "plan");
+    if (peer_group_device(group) != plan->device)
+        return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, peer_group_device(group), plan->device);
+    size_t heads_end, rows;
+    if (layout->total_requests == 0 || layout->gathered_query_heads == 0)
+        return fail(LB_ZERO_DIMENSION);
+    if (__builtin_add_overflow(layout->head_offset, plan->spec.num_query_heads, &heads_end) ||
+        heads_end > layout->gathered_query_heads)
+        return fail(LB_INVALID_HEAD_MAPPING, nullptr, (int64_t)layout->gathered_query_heads,
+                    (int64_t)layout->head_offset);
+    if (__builtin_mul_overflow(layout->total_requests, layout->gathered_query_heads, &rows) ||
+        rows > (size_t)0x7fffffff)
+        return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)rows);
+    const GatherTarget target = {layout, group, output, lse, args->dest_rows};
+    return enqueue_decode(plan, scope, &args->decode, &target);
+}
+
+namespace {
+
+lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
+                         const lb_paged_decode_args *args, const GatherTarget *gather) {
     const lb_paged_spec &spec = plan->spec;
     const DecodeChoice &c = plan->choice;
     const bool balanced = c.algorithm == LB_DECODE_BALANCED;
@@ -212,15 +268,22 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     lb_status rc = require_command_capacity(*scope, split ? 2 : 1);
     if (rc) return rc;
 
-    OperandRequest requests[9] = {
+    // operand 8 is the workspace of a split plan, else the row map of a gathering enqueue
+    OperandRequest requests[10] = {
         {args->query, LB_BF16, false},       {args->key_pages, LB_BF16, false},
         {args->value_pages, LB_BF16, false}, {args->page_indptr, LB_I32, false},
         {args->page_indices, LB_I32, false}, {args->last_page_len, LB_I32, false},
         {args->output, LB_BF16, true},       {args->lse, LB_F32, true},
         {args->workspace, LB_F32, true},
     };
-    Operand op[9];
-    if ((rc = resolve(*scope, requests, split ? 9 : 8, op))) return rc;
+    size_t count = split ? 9 : 8;
+    size_t rows_operand = 0;
+    if (gather) {
+        rows_operand = count;
+        requests[count++] = {gather->dest_rows, LB_I32, false};
+    }
+    Operand op[10];
+    if ((rc = resolve(*scope, requests, count, op))) return rc;
     const size_t pool = lb_paged_spec_kv_pages_numel(&spec);
     if ((rc = require_exact_len("Q", op[0].numel, lb_paged_spec_query_numel(&spec)))) return rc;
     if ((rc = require_exact_len("K_pages", op[1].numel, pool))) return rc;
@@ -233,8 +296,24 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
         return fail(LB_ENQUEUE_LENGTH_MISMATCH, "page_indices", 0x7fffffff, (int64_t)op[4].numel);
     if ((rc = require_exact_len("last_page_len", op[5].numel, spec.batch_size))) return rc;
     if (split && (rc = require_exact_len("workspace", op[8].numel, c.workspace_numel))) return rc;
-    if ((rc = require_exact_len("O", op[6].numel, lb_paged_spec_query_numel(&spec)))) return rc;
-    if ((rc = require_exact_len("LSE", op[7].numel, lb_paged_spec_lse_numel(&spec)))) return rc;
+    size_t out_numel = lb_paged_spec_query_numel(&spec), lse_numel = lb_paged_spec_lse_numel(&spec);
+    if (gather) {
+        lse_numel = gather->layout->total_requests * gather->layout->gathered_query_heads;
+        out_numel = lse_numel * LB_HEAD_DIM;
+    }
+    if ((rc = require_exact_len("O", op[6].numel, out_numel))) return rc;
+    if ((rc = require_exact_len("LSE", op[7].numel, lse_numel))) return rc;
+    if (gather) {
+        if ((rc = require_exact_len("dest_rows", op[rows_operand].numel, spec.batch_size)))
+            return rc;
+        // the bound output and LSE must be this rank's copies of the peer buffers
+        if (op[6].ptr != lb_peer_buffer_local(gather->output) ||
+            lb_peer_buffer_bytes(gather->output) < out_numel * 2)
+            return fail(LB_INVALID_ARGUMENT, "O is not the peer buffer");
+        if (op[7].ptr != lb_peer_buffer_local(gather->lse) ||
+            lb_peer_buffer_bytes(gather->lse) < lse_numel * 4)
+            return fail(LB_INVALID_ARGUMENT, "LSE is not the peer buffer");
+    }
     if ((rc = require_alignment("Q", op[0].ptr, 16))) return rc;
     if ((rc = require_alignment("K_pages", op[1].ptr, 16))) return rc;
     if ((rc = require_alignment("V_pages", op[2].ptr, 16))) return rc;
@@ -282,6 +361,26 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     launch.grid = c.grid;
     launch.block = c.block;
     launch.shared_bytes = c.shared_bytes;
+    launch.wait_cycles = plan->wait_cycles;
+    launch.test_skip_page = plan->test_skip_page;
+    PeerOut peer;
+    PeerSignal signal;
+    memset(&peer, 0, sizeof(peer));
+    memset(&signal, 0, sizeof(signal));
+    if (gather) {
+        peer.out = peer_buffer_table(gather->output);
+        peer.lse = reinterpret_cast<float *const *>(peer_buffer_table(gather->lse));
+        peer.dest_rows = (const int32_t *)op[rows_operand].ptr;
+        peer.world = lb_peer_group_world(gather->group);
+        peer.gathered_qh = (int32_t)gather->layout->gathered_query_heads;
+        peer.head_offset = (int32_t)gather->layout->head_offset;
+        signal = peer_signal_of(gather->group,
+                                plan->wait_cycles ? plan->wait_cycles : default_wait_cycles());
+        signal.status = plan->status; // reported by lb_decode_provider_device_status as 2
+    }
+    // rows leave from the kernel that finishes them; the command's last kernel signals
+    if (c.algorithm != LB_DECODE_SPLIT_K) launch.peer = peer;
+    if (!split) launch.signal = signal;
     void *stream = scope->queue->stream;
     if ((rc = submit_launch(*scope, [&]() {
              return balanced ? launch_balanced_decode(launch, stream)
@@ -299,11 +398,16 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     Operand merge_op[3];
     if ((rc = require_command_capacity(*scope, 1))) return rc;
     if ((rc = resolve(*scope, merge_requests, 3, merge_op))) return rc;
-    if (balanced)
+    if (balanced) {
+        launch.signal = signal;
         return submit_launch(*scope, [&]() {
             return launch_balanced_merge(launch, c.merge_grid, c.merge_block, stream);
         });
+    }
     MergeLaunch merge;
+    memset(&merge, 0, sizeof(merge));
+    merge.peer = peer;
+    merge.signal = signal;
     merge.workspace = (const float *)merge_op[0].ptr;
     merge.output = merge_op[1].ptr;
     merge.lse = (float *)merge_op[2].ptr;
@@ -318,6 +422,8 @@ lb_status lb_paged_decode_enqueue(const lb_paged_decode_plan *plan, lb_scope *sc
     merge.block = c.merge_block;
     return submit_launch(*scope, [&]() { return launch_split_merge(merge, stream); });
 }
+
+} // namespace
 
 // ---- state merge -----------------------------------------------------------------------------------
 
@@ -363,6 +469,7 @@ lb_status lb_state_merge_enqueue(const lb_state_merge_plan *plan, lb_scope *scop
     if ((rc = require_alignment("states", op[0].ptr, 8))) return rc;
     if ((rc = require_alignment("O", op[1].ptr, 8))) return rc;
     MergeLaunch merge;
+    memset(&merge, 0, sizeof(merge));
     merge.workspace = (const float *)op[0].ptr;
     merge.output = op[1].ptr;
     merge.lse = (float *)op[2].ptr;

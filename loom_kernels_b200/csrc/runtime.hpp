@@ -96,6 +96,11 @@ struct Driver {
     virtual int configure(int device, const std::function<int()> &setup) = 0;
     // Runs `launch` (a closure that calls one <<<>>> wrapper and returns its error code).
     virtual int launch(int device, const std::function<int()> &launch) = 0;
+    // Runs a library call that enqueues work on the command's stream (a collective of the
+    // communication library); the closure returns that library's own result code, 0 = success.
+    virtual int external(int device, const std::function<int()> &call) = 0;
+    // SM clock of the device in kHz (turns a wait limit in microseconds into cycles).
+    virtual int device_clock_khz(int device, int *khz) = 0;
     virtual int capture_begin(int device, void *stream) = 0;
     virtual int capture_end(int device, void *stream, void **graph) = 0;
     virtual int capture_status(void *stream, bool *capturing) = 0;
@@ -147,6 +152,10 @@ void record_submission(Scope &scope);
 void record_failed_submission(Scope &scope, int cuda_error);
 // Runs one kernel launch for a command that passed every preflight check and records it.
 lb_status submit_launch(Scope &scope, const std::function<int()> &launch);
+// record_external_submission / record_failed_external_submission, command/submission.rs:240-272:
+// a library call that enqueued work on the queue's stream counts as one command; its failure
+// poisons scope and queue (ExternalCommand, a = the library's result code).
+lb_status submit_external(Scope &scope, const char *provider, const std::function<int()> &call);
 
 uint64_t fresh_id();
 

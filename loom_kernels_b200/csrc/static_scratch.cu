@@ -171,6 +171,7 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     if ((error = driver().launch(device, [&]() { return launch_paged_decode(launch, stream); })))
         return fail(LB_DRIVER, "launch", error);
     MergeLaunch merge;
+    memset(&merge, 0, sizeof(merge));
     merge.workspace = setup.scratch;
     merge.output = output;
     merge.lse = lse;

@@ -89,6 +89,18 @@ class DecodeRun:
         self.h_ws = b.bind_read_write(self.workspace) if self.workspace is not None else None
         return b
 
+    def bind_extra(self, extra):
+        """As bind(), with room for `extra` more buffers (a gathered output, a row map)."""
+        b = self.queue.bindings(9 + extra)
+        self.h = dict(
+            query=b.bind_read(self.q), key_pages=b.bind_read(self.k),
+            value_pages=b.bind_read(self.v), page_indptr=b.bind_read(self.indptr),
+            page_indices=b.bind_read(self.indices), last_page_len=b.bind_read(self.last))
+        self.h_out = b.bind_read_write(self.out)
+        self.h_lse = b.bind_read_write(self.lse)
+        self.h_ws = b.bind_read_write(self.workspace) if self.workspace is not None else None
+        return b
+
     def args(self):
         return lk.Bf16PagedBatchDecodeArgs(output=self.h_out.write(), lse=self.h_lse.write(),
                                            workspace=self.h_ws, **self.h)

@@ -655,3 +655,75 @@ def test_noalloc_entry_under_the_fake_driver_caches_nothing(fake):
                                       host_memory)
     assert lib.lb_test_launch_count() == before + 2
     assert lib.lb_test_noalloc_is_set_up(0) == 0
+
+
+def test_gathering_commands_under_the_fake_driver(fake):
+    """Bookkeeping of the two ways to leave output rows gathered on every rank: the library
+    all-gather recorded as one external command (a failure poisons the queue, as the reference's
+    record_failed_external_submission), and the decode whose own kernels store the rows into the
+    peers' buffers (same command count as the plain enqueue, operands checked before any launch)."""
+    lib = _abi.load()
+    group = lk.PeerGroup(0, 2, 1, lk.PeerGroup.unique_id())
+    assert (group.rank(), group.world()) == (1, 2)
+    spec = lk.Bf16PagedBatchDecodeSpec.new(3, 40, 16, 4)
+    provider = lk.DecodeProvider.load(0)
+    queue = lk.CommandQueue(0x1000, 8)
+    total = 6  # requests of the gathered result
+    g_out, g_lse = group.buffer(total * 16 * 128, _abi.BF16), group.buffer(total * 16, _abi.F32)
+
+    def bind(b, plan):
+        reads = [b.bind_read(D(0x40000000 + i * 0x1000000, n, t)) for i, (n, t) in enumerate([
+            (spec.query_numel(), _abi.BF16), (spec.kv_pages_numel(), _abi.BF16),
+            (spec.kv_pages_numel(), _abi.BF16), (4, _abi.I32), (40, _abi.I32), (3, _abi.I32)])]
+        ws = (b.bind_read_write(D(0x48000000, plan.workspace_required_numel(), _abi.F32))
+              if plan.workspace_required_numel() else None)
+        return reads, ws
+
+    for options, commands in (({"partitions": 1}, 1), ({"partitions": 4}, 2), ({"balanced": 1}, 2)):
+        plan = provider.plan_bf16_paged_batch(spec, **options)
+        b = queue.bindings(12)
+        reads, ws = bind(b, plan)
+        out, lse = b.bind_read_write(g_out.span), b.bind_read_write(g_lse.span)
+        rows = b.bind_read(D(0x49000000, 3, _abi.I32))
+        short_rows = b.bind_read(D(0x49100000, 2, _abi.I32))
+        scope = queue.begin(b)
+        args = lk.Bf16PagedBatchDecodeArgs(*reads, out.write(), lse.write(), ws)
+        with pytest.raises(lk.EnqueueError) as e:
+            plan.enqueue_gathered_into(scope, args, short_rows, group, g_out, g_lse, total)
+        assert (e.value.variant, e.value.operand) == ("LengthMismatch", "dest_rows")
+        with pytest.raises(lk.EnqueueError) as e:  # the layout says 7 requests, the buffer holds 6
+            plan.enqueue_gathered_into(scope, args, rows, group, g_out, g_lse, total + 1)
+        assert (e.value.variant, e.value.operand) == ("LengthMismatch", "O")
+        with pytest.raises(lk.ContractError) as e:  # 16 heads at offset 8 of 16 gathered heads
+            plan.enqueue_gathered_into(scope, args, rows, group, g_out, g_lse, total, 16, 8)
+        assert e.value.variant == "InvalidHeadMapping"
+        with pytest.raises(lk.LoomError):  # the bound output is not the peer buffer's local copy
+            plan.enqueue_gathered_into(scope, args, rows, group, g_lse, g_lse, total)
+        assert scope.submitted_commands() == 0
+        plan.enqueue_gathered_into(scope, args, rows, group, g_out, g_lse, total)
+        assert scope.submitted_commands() == commands
+        scope.finish().wait()
+
+    # the all-gather as a command: rows differ per rank (2 and 4)
+    gather = lk.OutputGatherPlan(group, _abi.BF16, [2, 4], 16 * 128)
+    b = queue.bindings(3)
+    local = b.bind_read(D(0x4a000000, 4 * 16 * 128, _abi.BF16))
+    short = b.bind_read(D(0x4a800000, 2 * 16 * 128, _abi.BF16))
+    gathered = b.bind_read_write(D(0x4b000000, 6 * 16 * 128, _abi.BF16))
+    scope = queue.begin(b)
+    with pytest.raises(lk.EnqueueError) as e:
+        gather.enqueue_into(scope, lk.OutputGatherArgs(short, gathered.write()))
+    assert (e.value.variant, e.value.operand) == ("LengthMismatch", "local")
+    gather.enqueue_into(scope, lk.OutputGatherArgs(local, gathered.write()))
+    gather.enqueue_into(scope, lk.OutputGatherArgs(local, gathered.write()))
+    assert scope.submitted_commands() == 2
+    lib.lb_test_fake_fail(b"external", 1, 5)  # the library call fails: ncclInvalidUsage
+    with pytest.raises(lk.CommandError) as e:
+        gather.enqueue_into(scope, lk.OutputGatherArgs(local, gathered.write()))
+    assert (e.value.variant, e.value.operand, e.value.payload[0]) == ("External", "nccl", 5)
+    assert scope.submitted_commands() == 3 and queue.is_poisoned()
+    with pytest.raises(lk.CommandError) as e:
+        gather.enqueue_into(scope, lk.OutputGatherArgs(local, gathered.write()))
+    assert e.value.variant in ("ScopePoisoned", "QueuePoisoned")
+    del scope
+    group.close()
