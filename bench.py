@@ -382,11 +382,11 @@ class DecodeJob:
     def enqueue_plain(self, scope, plain):
         self.plan.enqueue_into(scope, plain)
 
-    def enqueue_gathered(self, scope, gathered):
+    def enqueue_gathered(self, scope, gathered, defer_wait=False):
         args, dest_rows, which = gathered
         self.plan.enqueue_gathered_into(scope, args, dest_rows, self.group, self.gathered_out[which],
                                         self.gathered_lse[which], self.total_requests,
-                                        self.gathered_qh, self.head_offset)
+                                        self.gathered_qh, self.head_offset, defer_wait)
 
     def gathered_tensors(self, which):
         return (self.gathered_out[which].tensor(self.device),
@@ -447,7 +447,7 @@ class PipelinedSteps:
             scope = self.queues[which].begin(self.bindings[which])
             for job, (plain, gathered) in zip(self.jobs, self.args[which]):
                 if self.gathered:
-                    job.enqueue_gathered(scope, gathered)
+                    job.enqueue_gathered(scope, gathered, defer_wait=job is not self.jobs[-1])
                 else:
                     job.enqueue_plain(scope, plain)
             self.completion[which] = scope.finish()
@@ -767,10 +767,13 @@ def c5_measure(args, lk, torch, dist, provider, group, rank, world, device, barr
         sets = [[job.bind(bindings, which) for job in jobs] for which in range(2)]
 
         def step_of(selected):
+            selected = list(selected)
+
             def step(scope, n):
                 for index in selected:
-                    if gathered:
-                        jobs[index].enqueue_gathered(scope, sets[n % 2][index][1])
+                    if gathered:  # only the step's last gathering command waits for the ranks
+                        jobs[index].enqueue_gathered(scope, sets[n % 2][index][1],
+                                                     defer_wait=index != selected[-1])
                     else:
                         jobs[index].enqueue_plain(scope, sets[n % 2][index][0])
             return step
@@ -815,7 +818,8 @@ def c5_measure(args, lk, torch, dist, provider, group, rank, world, device, barr
                                             lse.cpu().numpy(), fam.pools[0], fam.pools[1])
             ok &= good
         _, bindings = timed_scope(torch, queue, stream, bindings, 2, lambda scope, n: [
-            job.enqueue_gathered(scope, sets[n % 2][i][1]) for i, job in enumerate(jobs)])
+            job.enqueue_gathered(scope, sets[n % 2][i][1], defer_wait=i + 1 < len(jobs))
+            for i, job in enumerate(jobs)])
         for job, (out, lse) in zip(jobs, plain):
             for which in range(2):
                 ok &= verify_gathered(torch, dist, job, world, rank, out, lse, which)

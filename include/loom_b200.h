@@ -465,6 +465,12 @@ typedef struct lb_gather_layout {
     size_t total_requests;       /* requests of the gathered result, over all ranks */
     size_t gathered_query_heads; /* query heads per request of the gathered result */
     size_t head_offset;          /* first gathered query head this rank's heads map to */
+    uint32_t defer_wait;         /* 1: more gathering commands of the same step follow on this
+                                    queue; this one stores its rows but leaves the
+                                    epoch and the wait to the step's last gathering command, whose
+                                    completion then covers the rows of all of them.  Every rank
+                                    must make the same choice */
+    uint32_t reserved;
 } lb_gather_layout;
 typedef struct lb_paged_decode_gather_args {
     lb_paged_decode_args decode; /* output / lse: bound local copies of the peer buffers below */

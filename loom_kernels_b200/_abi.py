@@ -77,7 +77,7 @@ class DecodeArgs(ctypes.Structure):
 
 class GatherLayout(ctypes.Structure):
     _fields_ = [("total_requests", c_size_t), ("gathered_query_heads", c_size_t),
-                ("head_offset", c_size_t)]
+                ("head_offset", c_size_t), ("defer_wait", c_uint32), ("reserved", c_uint32)]
 
 
 class DecodeGatherArgs(ctypes.Structure):

@@ -593,9 +593,11 @@ class Bf16PagedBatchDecodePlan:
     def enqueue_gathered_into(self, scope: CommandScope, args: Bf16PagedBatchDecodeArgs,
                               dest_rows: Read, group: "PeerGroup", output: "PeerBuffer",
                               lse: "PeerBuffer", total_requests: int,
-                              gathered_query_heads: int = 0, head_offset: int = 0):
+                              gathered_query_heads: int = 0, head_offset: int = 0,
+                              defer_wait: bool = False):
         """lb_paged_decode_enqueue_gathered: args.output / args.lse are the bound local copies of
-        the peer buffers `output` / `lse`; every finished row goes to every rank's copy."""
+        the peer buffers `output` / `lse`; every finished row goes to every rank's copy.
+        defer_wait: a later gathering command of the same step publishes the epoch and waits."""
         decode = _abi.DecodeArgs(
             query=args.query._raw, key_pages=args.key_pages._raw,
             value_pages=args.value_pages._raw, page_indptr=args.page_indptr._raw,
@@ -606,7 +608,7 @@ class Bf16PagedBatchDecodePlan:
         layout = _abi.GatherLayout(
             total_requests=total_requests,
             gathered_query_heads=gathered_query_heads or self._spec.num_query_heads,
-            head_offset=head_offset)
+            head_offset=head_offset, defer_wait=1 if defer_wait else 0)
         _check(_abi.load().lb_paged_decode_enqueue_gathered(
             self._ptr, scope._ptr, byref(raw), byref(layout), group._ptr, output._ptr, lse._ptr))
 

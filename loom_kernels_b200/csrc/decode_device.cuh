@@ -336,47 +336,87 @@ __device__ __forceinline__ void write_state_row(float *state, int lane, int half
 using ::lb::PeerOut;    // kernels.hpp: where the finished rows go when a plan gathers its output
 using ::lb::PeerSignal; // kernels.hpp: the epoch the last kernel of such a command publishes
 
-__device__ __forceinline__ void store_release_system(uint32_t *address, uint32_t value) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+// acquire-release fence at system scope: orders this thread's earlier accesses -- and, through a
+// CTA or warp barrier before it, those of the threads that met at the barrier -- before its later
+// ones as seen from any GPU.  (Cheaper than the sequentially consistent membar.sys.)
+__device__ __forceinline__ void fence_system() {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
-__device__ __forceinline__ uint32_t load_acquire_system(const uint32_t *address) {
+__device__ __forceinline__ void store_relaxed_system(uint32_t *address, uint32_t value) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t load_relaxed_system(const uint32_t *address) {
     uint32_t value;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
     return value;
 }
 
-// Called by every thread of every CTA of the kernel, after its last store.
-__device__ __forceinline__ void peer_signal_and_wait(const PeerSignal &s) {
-    if (s.world == 0) return;
-    dependent_launch_wait();  // a CTA that left early has not passed it yet
-    __threadfence_system();   // this thread's rows are performed before its CTA is counted
-    __syncthreads();
-    if (threadIdx.x >= 32) return;
+// What a kernel fetches from the peer tables when it starts, so that its last instructions -- the
+// row stores and the epoch -- do not wait on chains of dependent loads: the tables are device
+// arrays of pointers, and the epoch and the row map are words in global memory.
+struct PeerLocal {
+    void *out[LB_PEER_MAX_RANKS];      // PeerOut::out
+    float *lse[LB_PEER_MAX_RANKS];     // PeerOut::lse
+    uint32_t *flags[LB_PEER_MAX_RANKS]; // PeerSignal::flags
+    uint32_t epoch;                    // *PeerSignal::epoch when the kernel started
+};
+
+// One warp fills `local` (in shared memory); the CTA synchronises before anyone reads it.
+__device__ __forceinline__ void peer_prefetch(const PeerOut &peer, const PeerSignal &signal,
+                                              int lane, PeerLocal &local) {
+    if (lane < peer.world) {
+        local.out[lane] = peer.out[lane];
+        local.lse[lane] = peer.lse[lane];
+    }
+    if (lane < signal.world) local.flags[lane] = signal.flags[lane];
+    if (lane == 0 && signal.world != 0) local.epoch = *signal.epoch;
+}
+
+// Called by warp 0 of every CTA of the kernel, after a CTA barrier that follows the CTA's last row
+// store.  Ordering, by the PTX memory model: the CTA barrier orders every thread's row stores
+// before lane 0's counting atomic, which is a release at GPU scope (a system-scope fence per CTA
+// costs about a microsecond each, and a kernel of a thousand small CTAs queues them up); the
+// last CTA's atomic is an acquire of all of them, and its system-scope fence then orders every
+// row of the grid -- and, through stream order, of the earlier kernels of the step -- before the
+// epoch it publishes.  `flag_of_lane` is s.flags[lane], `my_flags` is s.flags[s.rank] and `epoch`
+// is *s.epoch as the kernel found it (only this kernel's last CTA changes it), all fetched when
+// the kernel started.
+__device__ __forceinline__ void peer_signal_and_wait(const PeerSignal &s, uint32_t *flag_of_lane,
+                                                     const uint32_t *my_flags, uint32_t epoch) {
     const int lane = threadIdx.x;
     unsigned last = 0;
-    if (lane == 0) last = atomicAdd(s.done, 1u) == gridDim.x - 1 ? 1u : 0u;
-    if (!__shfl_sync(0xffffffffu, last, 0)) return;
-    __threadfence_system(); // every CTA fenced before it was counted: all rows precede the epoch
-    uint32_t epoch = 0;
     if (lane == 0) {
+        unsigned counted;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;"
+                     : "=r"(counted)
+                     : "l"(s.done)
+                     : "memory");
+        last = counted == gridDim.x - 1 ? 1u : 0u;
+    }
+    if (!__shfl_sync(0xffffffffu, last, 0)) return;
+    epoch += 1;
+    if (lane == 0) {
+        fence_system(); // every row of the step precedes the epoch, as seen from any GPU
         *s.done = 0; // the next kernel counts from zero (it starts after this one has completed)
-        epoch = *s.epoch + 1;
         *s.epoch = epoch;
     }
-    epoch = __shfl_sync(0xffffffffu, epoch, 0);
-    if (lane < s.world) store_release_system(s.flags[lane] + kPeerFlagsWord + s.rank, epoch);
+    __syncwarp(); // lane 0's fence precedes every lane's flag store
+    if (lane < s.world) store_relaxed_system(flag_of_lane + kPeerFlagsWord + s.rank, epoch);
     bool arrived = true;
     if (lane < s.world) {
-        const uint32_t *mine = s.flags[s.rank] + kPeerFlagsWord + lane;
-        arrived = (int32_t)(load_acquire_system(mine) - epoch) >= 0;
+        const uint32_t *mine = my_flags + kPeerFlagsWord + lane;
+        arrived = (int32_t)(load_relaxed_system(mine) - epoch) >= 0;
         const long long start = clock64();
         while (!arrived) {
 #pragma unroll 1
             for (int spin = 0; spin < 64 && !arrived; ++spin)
-                arrived = (int32_t)(load_acquire_system(mine) - epoch) >= 0;
+                arrived = (int32_t)(load_relaxed_system(mine) - epoch) >= 0;
             if (clock64() - start > s.wait_cycles) break;
         }
     }
+    // the flags were read relaxed: this fence makes the peers' rows, which precede their epochs,
+    // visible to everything that follows the kernel
+    fence_system();
     if (__any_sync(0xffffffffu, !arrived) && lane == 0 && s.status) atomicExch(s.status, 2);
 }
 
@@ -402,8 +442,9 @@ __device__ __forceinline__ void quad_transpose(uint32_t (&r)[4], int lane) {
 // of the gathered result.  The four lanes of a quad first exchange their 4-byte pieces so that a
 // lane owns whole 16-byte chunks: a row leaves as 16-byte stores, 64 contiguous bytes per quad.
 // Every lane of the warp must call (the exchange is warp-wide); rows[half] < 0 stores nothing.
-__device__ __forceinline__ void write_final_rows_to_peers(const PeerOut &peer, const long long (&rows)[2],
-                                                          int lane, const WarpState &st) {
+__device__ __forceinline__ void write_final_rows_to_peers(const PeerLocal &peer, int world,
+                                                          const long long (&rows)[2], int lane,
+                                                          const WarpState &st) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const float l = st.row_sum[half];
@@ -421,7 +462,7 @@ __device__ __forceinline__ void write_final_rows_to_peers(const PeerOut &peer, c
         }
         if (rows[half] < 0) continue;
         const float lse = st.row_max[half] + log2f(l);
-        for (int p = 0; p < peer.world; ++p) {
+        for (int p = 0; p < world; ++p) {
             uint4 *row = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(peer.out[p]) +
                                                    rows[half] * kHeadDim);
 #pragma unroll
@@ -551,20 +592,54 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
 }
 
-// As merge_states, into row `row` of every rank's copy of the gathered result.
+// As merge_states, into the row of `request`, query head `head` of every rank's copy of the
+// gathered result.  The row map and the peers' addresses (lane p holds rank p's) are fetched
+// before the states, so that the stores at the end wait for nothing.
 template <typename StateOf>
 __device__ __forceinline__ void merge_states_to_peers(StateOf state_of, int n, int lane,
                                                       bool publish, const PeerOut &peer,
-                                                      long long row) {
+                                                      int request, int head) {
+    const int dest = peer.dest_rows[request];
+    __nv_bfloat16 *out_of_lane =
+        lane < peer.world ? static_cast<__nv_bfloat16 *>(peer.out[lane]) : nullptr;
+    float *lse_of_lane = lane < peer.world ? peer.lse[lane] : nullptr;
     float top, norm;
     float4 acc;
-    if (!merge_partial(state_of, n, lane, top, norm, acc) || !publish) return;
-    if (!(norm > 0.0f)) return;
-    for (int p = 0; p < peer.world; ++p)
-        publish_merged(top, norm, acc, lane,
-                       static_cast<__nv_bfloat16 *>(peer.out[p]) + row * kHeadDim,
-                       peer.lse[p] + row);
+    const bool ok = merge_partial(state_of, n, lane, top, norm, acc) && publish && norm > 0.0f;
+    const long long row = (long long)dest * peer.gathered_qh + peer.head_offset + head;
+    for (int p = 0; p < peer.world; ++p) {
+        __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(
+            __shfl_sync(0xffffffffu, (unsigned long long)out_of_lane, p));
+        float *lse = reinterpret_cast<float *>(
+            __shfl_sync(0xffffffffu, (unsigned long long)lse_of_lane, p));
+        if (ok) publish_merged(top, norm, acc, lane, out + row * kHeadDim, lse + row);
+    }
 }
+
+// The epoch hand-shake of a merge kernel (CTAs of a few warps, no shared memory): warp 0 fetches
+// what the hand-shake needs before the merge, every thread calls this after it.
+struct MergeSignalPrefetch {
+    uint32_t *flag_of_lane;
+    const uint32_t *my_flags;
+    uint32_t epoch;
+    __device__ __forceinline__ void fetch(const PeerSignal &s) {
+        flag_of_lane = nullptr;
+        my_flags = nullptr;
+        epoch = 0;
+        if (s.world == 0 || threadIdx.x >= 32) return;
+        if ((int)threadIdx.x < s.world) flag_of_lane = s.flags[threadIdx.x];
+        my_flags = s.flags[s.rank];
+        epoch = *s.epoch;
+    }
+    __device__ __forceinline__ void finish(const PeerSignal &s) const {
+        // a command that leaves the epoch to a later command of the step has nothing to do: its
+        // rows are ordered before that command's kernels by the stream
+        if (s.world == 0 || s.defer) return;
+        __syncthreads();
+        if (threadIdx.x >= 32) return;
+        peer_signal_and_wait(s, flag_of_lane, my_flags, epoch);
+    }
+};
 
 // The even cut of `total` units over `workers` workers, evaluated without 64-bit division:
 // begin(w) = floor(total * w / workers) = q * w + floor(r * w / workers) with total = q *

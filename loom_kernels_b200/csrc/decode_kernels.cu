@@ -54,8 +54,9 @@ struct DecodeArgs {
 
 // The work of one CTA.  A thread that has nothing (more) to do returns from here; every thread
 // of the grid then meets again in the kernel below.
+template <bool kGather>
 __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const CUtensorMap &v_map,
-                                                 const DecodeArgs &a) {
+                                                 const DecodeArgs &a, PeerLocal &peer_local) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -82,7 +83,6 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     const int qb = item % a.qb; item /= a.qb;
     const int part = item % a.partitions;
     const int request = item / a.partitions;
-    if (request >= a.batch) return;
 
     // barriers: one thread each, before the first touch of global memory
     if (tid < a.stages * a.pps) {
@@ -101,6 +101,10 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     __syncthreads(); // the barriers exist for every warp
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
+    // a gathering plan: the peers' addresses and the epoch, fetched now for the kernel's last
+    // instructions (read after the join below, or after the barrier that ends the kernel)
+    if (kGather && warp == kComputeWarps - 1) peer_prefetch(a.peer, a.signal, lane, peer_local);
+    if (request >= a.batch) return;
     // The first 32 page ids of the table travel with the request's metadata: when the pages this
     // CTA starts with lie among them (small batches, short contexts) the producer has its ids
     // one round trip earlier.
@@ -142,6 +146,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
 
     // consumer identity (declared here so the epilogue after the join can use it)
     WarpState st;
+    int dest_request = 0; // gathering plans: the row of the gathered result this request owns
     const int unit = warp / a.mt;      // consumer: which (page slot, head) of each stage
     const int mtile = warp % a.mt;     // consumer: which 16-row tile of the group
     const int page_slot0 = unit / a.hc;
@@ -215,6 +220,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     } else {
         // ================= consumer warps ======================================================
         st.reset();
+        if (kGather && a.peer.world != 0) dest_request = a.peer.dest_rows[request];
         const int kv_head = hb * a.hc + head_in_cta;
         const int row0 = qb * rows_per_block + mtile * 16;
         uint32_t qf[8][4];
@@ -314,14 +320,13 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     // ---- epilogue ---------------------------------------------------------------------------------
     const int kv_head = hb * a.hc + head_in_cta;
     const int g0 = qb * rows_per_block + mtile * 16 + (lane >> 2);
-    if (a.partitions == 1 && a.peer.world != 0) {
+    if (kGather && a.partitions == 1 && a.peer.world != 0) {
         // the finished rows go straight into every rank's copy of the gathered result
-        const long long row0 =
-            (long long)a.peer.dest_rows[request] * a.peer.gathered_qh + a.peer.head_offset +
-            (long long)kv_head * group;
+        const long long row0 = (long long)dest_request * a.peer.gathered_qh + a.peer.head_offset +
+                               (long long)kv_head * group;
         const long long rows[2] = {g0 < group && !invalid_page ? row0 + g0 : -1,
                                    g0 + 8 < group && !invalid_page ? row0 + g0 + 8 : -1};
-        write_final_rows_to_peers(a.peer, rows, lane, st);
+        write_final_rows_to_peers(peer_local, a.peer.world, rows, lane, st);
         return;
     }
 #pragma unroll
@@ -340,12 +345,21 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     LB_STAMP(10);
 }
 
+// kGather: the instantiation for plans that gather their output (the other one carries none of
+// its registers or shared memory).
+template <bool kGather>
 __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const DecodeArgs a) {
+    __shared__ PeerLocal peer_local;
     dependent_launch_release();
-    paged_decode_cta(k_map, v_map, a);
-    peer_signal_and_wait(a.signal);
+    paged_decode_cta<kGather>(k_map, v_map, a, peer_local);
+    if (!kGather || a.signal.world == 0 || a.signal.defer) return;
+    __syncthreads(); // every row of this CTA has been stored; peer_local is complete
+    if (threadIdx.x >= 32) return;
+    peer_signal_and_wait(a.signal,
+                         (int)threadIdx.x < a.signal.world ? peer_local.flags[threadIdx.x] : nullptr,
+                         peer_local.flags[a.signal.rank], peer_local.epoch);
 }
 
 // Merges the split-K states of one (request, query head) per warp (merge_states).
@@ -368,9 +382,8 @@ __device__ __forceinline__ void split_merge_warp(const float *__restrict__ works
     const float *st = workspace + (size_t)state * partitions * kStateWidth;
     auto state_of = [&](int p) { return st + (size_t)p * kStateWidth; };
     if (peer.world != 0) {
-        const long long row = (long long)peer.dest_rows[request] * peer.gathered_qh +
-                              peer.head_offset + (state - request * qh);
-        merge_states_to_peers(state_of, partitions, lane, valid, peer, row);
+        merge_states_to_peers(state_of, partitions, lane, valid, peer, request,
+                              state - request * qh);
         return;
     }
     merge_states(state_of, partitions, lane, valid, output + (size_t)state * kHeadDim, lse + state);
@@ -381,16 +394,31 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
                    const int32_t *indptr, const int32_t *last, int batch, int qh, int partitions,
                    int indices_min, int indices_len, const PeerOut peer, const PeerSignal signal) {
     dependent_launch_release();
+    MergeSignalPrefetch handshake;
+    if (signal.world != 0) {
+        dependent_launch_wait();
+        handshake.fetch(signal);
+    }
     split_merge_warp(workspace, output, lse, indptr, last, batch, qh, partitions, indices_min,
                      indices_len, peer);
-    peer_signal_and_wait(signal);
+    handshake.finish(signal);
 }
 
 } // namespace
 
 int configure_decode_kernels(size_t max_dynamic_shared) {
-    int rc = cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)max_dynamic_shared);
+    // the opt-in limit covers static and dynamic shared memory together
+    cudaFuncAttributes attributes;
+    int rc = cudaFuncGetAttributes(&attributes, paged_decode_kernel<false>);
+    if (rc) return rc;
+    rc = cudaFuncSetAttribute(paged_decode_kernel<false>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)(max_dynamic_shared - attributes.sharedSizeBytes));
+    if (rc) return rc;
+    if ((rc = cudaFuncGetAttributes(&attributes, paged_decode_kernel<true>))) return rc;
+    rc = cudaFuncSetAttribute(paged_decode_kernel<true>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)(max_dynamic_shared - attributes.sharedSizeBytes));
     if (rc) return rc;
     return configure_stream_kernels(max_dynamic_shared);
 }
@@ -426,8 +454,11 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    return launch_dependent(paged_decode_kernel, launch.grid, launch.block, launch.shared_bytes,
-                            stream, k_map, v_map, args);
+    if (launch.peer.world != 0 || launch.signal.world != 0)
+        return launch_dependent(paged_decode_kernel<true>, launch.grid, launch.block,
+                                launch.shared_bytes, stream, k_map, v_map, args);
+    return launch_dependent(paged_decode_kernel<false>, launch.grid, launch.block,
+                            launch.shared_bytes, stream, k_map, v_map, args);
 }
 
 int launch_split_merge(const MergeLaunch &launch, void *stream) {

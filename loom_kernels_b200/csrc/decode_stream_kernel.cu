@@ -61,10 +61,14 @@ __device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
     return lo;
 }
 
+// kGather: the instantiation for plans that gather their output (the other one carries none of
+// its registers or shared memory).
+template <bool kGather>
 __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ PeerLocal peer_local;
     dependent_launch_release();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -102,6 +106,13 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
     LB_STAMP(0);
+    // a gathering plan: the peers' addresses, fetched now for the row stores (the barriers of the
+    // prefix computation below come before any of them)
+    if (kGather && warp == kComputeWarps - 1) {
+        PeerSignal none;
+        none.world = 0;
+        peer_prefetch(a.peer, none, lane, peer_local);
+    }
 
     // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
     const int global_end = a.indptr[a.batch];
@@ -275,6 +286,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const int hb = h / a.qb, qb = h % a.qb;
             const int kv_head = hb * a.hc + head_in_cta;
             const int row0 = qb * rows_per_block + mtile * 16;
+            const int dest_request = kGather && a.peer.world != 0 ? a.peer.dest_rows[r] : 0;
             load_query_fragments(
                 a.query + ((size_t)r * a.qh + (size_t)kv_head * group + row0) * kHeadDim,
                 group - row0, lane, qf);
@@ -309,14 +321,14 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             st.finish_rows();
             const bool complete = first_page == 0 && seg_pages == num_pages;
             const int which = first_segment ? 0 : 1;
-            if (complete && a.peer.world != 0) {
+            if (kGather && complete && a.peer.world != 0) {
                 // finished in place: straight into every rank's copy of the gathered result
                 const int g0 = qb * rows_per_block + mtile * 16 + (lane >> 2);
-                const long long row0 = (long long)a.peer.dest_rows[r] * a.peer.gathered_qh +
+                const long long row0 = (long long)dest_request * a.peer.gathered_qh +
                                        a.peer.head_offset + (long long)kv_head * group;
                 const long long rows[2] = {g0 < group && !bad ? row0 + g0 : -1,
                                            g0 + 8 < group && !bad ? row0 + g0 + 8 : -1};
-                write_final_rows_to_peers(a.peer, rows, lane, st);
+                write_final_rows_to_peers(peer_local, a.peer.world, rows, lane, st);
             } else
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -345,11 +357,10 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
     }
     LB_STAMP(6);
-    // rows this CTA stored into other GPUs' memory are performed before the grid counts as
-    // complete: the merge kernel, which follows, publishes the epoch that tells the peers so
-    if (a.peer.world != 0) __threadfence_system();
     __syncthreads();
     LB_STAMP(7);
+    // (rows this kernel stored into other GPUs' memory are ordered by the stream before the merge
+    // kernel, whose last CTA fences at system scope before it publishes the epoch)
     if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);
 }
 
@@ -390,9 +401,7 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
         return base + ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
     };
     if (peer.world != 0) {
-        const long long row =
-            (long long)peer.dest_rows[request] * peer.gathered_qh + peer.head_offset + qhead;
-        merge_states_to_peers(state_of, w1 - w0 + 1, lane, true, peer, row);
+        merge_states_to_peers(state_of, w1 - w0 + 1, lane, true, peer, request, qhead);
         return;
     }
     merge_states(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim, lse + state);
@@ -403,9 +412,14 @@ balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
                       int rows, const PeerOut peer, const PeerSignal signal) {
     dependent_launch_release();
+    MergeSignalPrefetch handshake;
+    if (signal.world != 0) {
+        dependent_launch_wait();
+        handshake.fetch(signal);
+    }
     balanced_merge_warp(workspace, output, lse, batch, qh, kvh, hc, mt, qblocks, workers, rows,
                         peer);
-    peer_signal_and_wait(signal);
+    handshake.finish(signal);
 }
 
 int balanced_state_rows(const DecodeLaunch &launch) {
@@ -416,9 +430,18 @@ int balanced_state_rows(const DecodeLaunch &launch) {
 } // namespace
 
 int configure_stream_kernels(size_t max_dynamic_shared) {
-    return cudaFuncSetAttribute(balanced_decode_kernel,
+    // the opt-in limit covers static and dynamic shared memory together
+    cudaFuncAttributes attributes;
+    int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<false>);
+    if (rc) return rc;
+    rc = cudaFuncSetAttribute(balanced_decode_kernel<false>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)(max_dynamic_shared - attributes.sharedSizeBytes));
+    if (rc) return rc;
+    if ((rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<true>))) return rc;
+    return cudaFuncSetAttribute(balanced_decode_kernel<true>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)max_dynamic_shared);
+                                (int)(max_dynamic_shared - attributes.sharedSizeBytes));
 }
 
 int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
@@ -450,8 +473,11 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    return launch_dependent(balanced_decode_kernel, launch.grid, launch.block, launch.shared_bytes,
-                            stream, k_map, v_map, args);
+    if (launch.peer.world != 0)
+        return launch_dependent(balanced_decode_kernel<true>, launch.grid, launch.block,
+                                launch.shared_bytes, stream, k_map, v_map, args);
+    return launch_dependent(balanced_decode_kernel<false>, launch.grid, launch.block,
+                            launch.shared_bytes, stream, k_map, v_map, args);
 }
 
 int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block,

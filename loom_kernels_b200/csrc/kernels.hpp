@@ -4,6 +4,8 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "loom_b200.h"
+
 namespace lb {
 
 // Where finished rows go when a plan gathers its output over the ranks of a peer group: row r of
@@ -29,6 +31,7 @@ struct PeerSignal {
                             // kPeerFlagsWord, one per sender)
     int32_t *status;        // set to 2 when the wait for the other ranks ran out
     int32_t rank, world;
+    int32_t defer;          // 1: store the rows only; a later command of the step publishes the epoch
     long long wait_cycles;
 };
 

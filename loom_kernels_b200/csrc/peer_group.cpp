@@ -354,8 +354,9 @@ lb_status lb_output_gather_plan_create(const lb_peer_group *g, int dtype,
     }
     size_t total;
     if (plan->total_rows == 0 || __builtin_mul_overflow(plan->total_rows, row_numel, &total)) {
+        const bool empty = plan->total_rows == 0;
         delete plan;
-        return fail(plan->total_rows == 0 ? LB_ZERO_DIMENSION : LB_ELEMENT_COUNT_OVERFLOW);
+        return fail(empty ? LB_ZERO_DIMENSION : LB_ELEMENT_COUNT_OVERFLOW);
     }
     *out = plan;
     return LB_OK;

@@ -243,6 +243,7 @@ lb_status lb_paged_decode_enqueue_gathered(const lb_paged_decode_plan *plan, lb_
     size_t heads_end, rows;
     if (layout->total_requests == 0 || layout->gathered_query_heads == 0)
         return fail(LB_ZERO_DIMENSION);
+    if (layout->defer_wait > 1) return fail(LB_LAUNCH_CONTRACT, "defer_wait", layout->defer_wait);
     if (__builtin_add_overflow(layout->head_offset, plan->spec.num_query_heads, &heads_end) ||
         heads_end > layout->gathered_query_heads)
         return fail(LB_INVALID_HEAD_MAPPING, nullptr, (int64_t)layout->gathered_query_heads,
@@ -377,6 +378,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
         signal = peer_signal_of(gather->group,
                                 plan->wait_cycles ? plan->wait_cycles : default_wait_cycles());
         signal.status = plan->status; // reported by lb_decode_provider_device_status as 2
+        signal.defer = gather->layout->defer_wait ? 1 : 0;
     }
     // rows leave from the kernel that finishes them; the command's last kernel signals
     if (c.algorithm != LB_DECODE_SPLIT_K) launch.peer = peer;

@@ -66,6 +66,33 @@ def main():
                 assert np.array_equal(got[ids].reshape(-1), out), (rank, options)
                 assert np.array_equal(got_lse[ids].reshape(-1).view(np.uint32), lse.view(np.uint32))
 
+    # two gathering commands in one step: the first only stores and fences its rows, the second
+    # publishes the epoch and waits, and its completion covers the rows of both
+    run = H.DecodeRun(spec, q, k, v, indptr, indices, last, device=device, provider=provider,
+                      max_commands=4, balanced=1)
+    plain_out, plain_lse = run.run()
+    for buffer in g_out:
+        buffer.tensor(device).zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    b = run.bind_extra(5)
+    handles = [(b.bind_read_write(g_out[i].span), b.bind_read_write(g_lse[i].span)) for i in (0, 1)]
+    rows = b.bind_read(H.dev_i32(owned.astype(np.int32), device))
+    scope = run.queue.begin(b)
+    for i, (h_out, h_lse) in enumerate(handles):
+        args = lk.Bf16PagedBatchDecodeArgs(output=h_out.write(), lse=h_lse.write(),
+                                           workspace=run.h_ws, **run.h)
+        run.plan.enqueue_gathered_into(scope, args, rows, group, g_out[i], g_lse[i], batch,
+                                       defer_wait=i == 0)
+    scope.finish().wait()
+    assert provider.device_status() == 0
+    everyone = [None] * world
+    dist.all_gather_object(everyone, (owned, plain_out))
+    for i in (0, 1):
+        got = H.host_bits(g_out[i].tensor(device)).reshape(batch, qh * 128)
+        for ids, out in everyone:
+            assert np.array_equal(got[ids].reshape(-1), out), (rank, "deferred", i)
+
     # one request split by KV head: every rank computes qh / world heads of the same request
     if kvh % world == 0:
         kv_lo, kv_hi, q_lo, q_hi = sharding.kv_head_range(kvh, qh, world, rank)
