@@ -311,7 +311,9 @@ typedef struct lb_paged_decode_options {
     uint32_t test_skip_page; /* tests of that give-up path only: 1 + the index, within every CTA's
                                 page chunk, of a page whose copies the kernel leaves out; 0 = none.
                                 Direct and split-K plans */
-    uint32_t reserved[1];
+    uint32_t pages_per_step; /* pages a consumer warp takes per step of its loop: 0 = plan-time
+                                heuristic, 1, or 2 (one joint softmax update over 32 tokens; the
+                                choice for query groups wider than 16 rows) */
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
@@ -327,6 +329,8 @@ typedef struct lb_paged_decode_plan_info {
     uint32_t commands;       /* 1 direct, 2 split or balanced (partials + merge) */
     size_t workspace_numel;  /* F32 elements the caller must bind (0 for direct) */
     size_t workspace_bytes;
+    uint32_t pages_per_step; /* 1 or 2, see lb_paged_decode_options */
+    uint32_t reserved;
 } lb_paged_decode_plan_info;
 
 /* Bf16PagedBatchDecodeArgs, decode.rs:1451-1487, plus the split-K workspace

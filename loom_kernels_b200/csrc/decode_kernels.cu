@@ -46,6 +46,7 @@ struct DecodeArgs {
     int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, partitions, stages;
     float scale_log2;
+    int32_t pair;          // 1: a consumer warp takes two pages of its slot per step
     int32_t skip_page;     // tests of the give-up path: 1 + the page whose loads are left out
     long long wait_cycles; // limit of every bounded wait
     PeerOut peer;          // world == 0 unless the plan gathers its output
@@ -237,7 +238,36 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         const uint32_t my_full = full0 + page_slot0 * 8, my_empty = empty0 + page_slot0 * 8;
         int stage = 0;
         uint32_t phase = 0;
-        for (int it = 0; it < my_pages; ++it) {
+        int it = 0;
+        if (a.pair) {
+            // two pages of this slot per step: they sit in two consecutive stages of the ring
+            for (; it + 1 < my_pages; it += 2) {
+                const int stage_b = stage + 1 == a.stages ? 0 : stage + 1;
+                const uint32_t phase_b = stage_b == 0 ? phase ^ 1 : phase;
+                const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles) &&
+                                mbar_wait(my_full + stage_b * a.pps * 8, phase_b, a.wait_cycles);
+                if (__any_sync(0xffffffffu, !ok)) {
+                    if (lane == 0) flags[1] = 1;
+                    break;
+                }
+                uint8_t *tile_a = ring + stage * stage_bytes + tile_offset;
+                uint8_t *tile_b = ring + stage_b * stage_bytes + tile_offset;
+                const bool wrote = attend_page_pair(
+                    tile_a, tile_a + slot_bytes / 2, tile_b, tile_b + slot_bytes / 2,
+                    min(kPage, tokens_left - a.pps * kPage), qf, a.scale_log2, lane, st);
+                __syncwarp();
+                if (lane == 0) {
+                    if (wrote) fence_proxy_async();
+                    mbar_arrive(my_empty + stage * a.pps * 8);
+                    mbar_arrive(my_empty + stage_b * a.pps * 8);
+                }
+                tokens_left -= 2 * a.pps * kPage;
+                stage = stage_b + 1 == a.stages ? 0 : stage_b + 1;
+                phase = stage == 0 ? phase_b ^ 1 : phase_b;
+            }
+            if (it + 1 < my_pages) it = my_pages; // a wait ran out: nothing more is consumed
+        }
+        for (; it < my_pages; ++it) {
             const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
@@ -446,6 +476,7 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     args.partitions = launch.partitions;
     args.stages = launch.stages;
     args.scale_log2 = launch.scale_log2;
+    args.pair = launch.pages_per_step == 2 ? 1 : 0;
     args.skip_page = launch.test_skip_page;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
     args.peer = launch.peer;

@@ -41,6 +41,7 @@ struct StreamArgs {
     int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, stages, workers;
     int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
+    int32_t pair; // 1: a consumer warp takes two pages of its range per step
     float scale_log2;
     long long wait_cycles; // limit of every bounded wait
     PeerOut peer;          // world == 0 unless the plan gathers its output
@@ -294,7 +295,38 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             bool bad = false;
             const int tail = ptail[r];
             const int last_in_segment = num_pages - 1 - first_page; // p of the request's last page
-            for (int p = 0; p < seg_pages; ++p) {
+            int p = 0;
+            if (a.pair) {
+                // two pages of the segment per step: consecutive stages of this worker's slot
+                for (; p + 1 < seg_pages; p += 2) {
+                    const int stage_b = stage + 1 == a.stages ? 0 : stage + 1;
+                    const uint32_t phase_b = stage_b == 0 ? phase ^ 1 : phase;
+                    const bool ok =
+                        mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles) &&
+                        mbar_wait(my_full + stage_b * a.pps * 8, phase_b, a.wait_cycles);
+                    if (__any_sync(0xffffffffu, !ok)) {
+                        if (lane == 0) *timeout_flag = 1;
+                        live = false;
+                        break;
+                    }
+                    bad |= bad_slot[stage * a.pps + my_slot] != 0 ||
+                           bad_slot[stage_b * a.pps + my_slot] != 0;
+                    uint8_t *tile_a = ring + stage * stage_bytes + tile_offset;
+                    uint8_t *tile_b = ring + stage_b * stage_bytes + tile_offset;
+                    const bool wrote = attend_page_pair(
+                        tile_a, tile_a + slot_bytes / 2, tile_b, tile_b + slot_bytes / 2,
+                        p + 1 == last_in_segment ? tail : kPage, qf, a.scale_log2, lane, st);
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (wrote) fence_proxy_async();
+                        mbar_arrive(my_empty + stage * a.pps * 8);
+                        mbar_arrive(my_empty + stage_b * a.pps * 8);
+                    }
+                    stage = stage_b + 1 == a.stages ? 0 : stage_b + 1;
+                    phase = stage == 0 ? phase_b ^ 1 : phase_b;
+                }
+            }
+            for (; live && p < seg_pages; ++p) {
                 const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles);
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) *timeout_flag = 1;
@@ -467,6 +499,7 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     args.stages = launch.stages;
     args.workers = (int32_t)launch.grid * launch.pages_per_stage;
     args.rows = balanced_state_rows(launch);
+    args.pair = launch.pages_per_step == 2 ? 1 : 0;
     args.scale_log2 = launch.scale_log2;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
     args.peer = launch.peer;

@@ -110,6 +110,8 @@ void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
     info->commands = c.algorithm == LB_DECODE_DIRECT ? 1 : 2;
     info->workspace_numel = c.workspace_numel;
     info->workspace_bytes = c.workspace_numel * sizeof(float);
+    info->pages_per_step = c.pages_per_step;
+    info->reserved = 0;
 }
 
 } // namespace
@@ -358,6 +360,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     launch.q_blocks = (int32_t)c.q_blocks;
     launch.partitions = (int32_t)c.partitions;
     launch.stages = (int32_t)c.stages;
+    launch.pages_per_step = (int32_t)c.pages_per_step;
     launch.scale_log2 = spec.softmax_scale * kLog2E;
     launch.grid = c.grid;
     launch.block = c.block;
