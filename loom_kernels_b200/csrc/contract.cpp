@@ -225,7 +225,12 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     out->block = (warps + 1) * 32;
     out->shared_bytes = (uint32_t)(stages * stage_bytes + extra);
     out->merge_block = 128;
-    out->merge_grid = algorithm == LB_DECODE_DIRECT ? 0 : ceil_div((uint32_t)states, 4);
+    // one warp per (request, query head); the balanced merge of a small batch -- where a long
+    // request is cut into many states -- gives every item a whole CTA of four warps
+    out->merge_grid = algorithm == LB_DECODE_DIRECT ? 0
+                      : algorithm == LB_DECODE_BALANCED && states <= 2048
+                          ? (uint32_t)states
+                          : ceil_div((uint32_t)states, 4);
     out->workspace_numel = workspace;
     return LB_OK;
 }

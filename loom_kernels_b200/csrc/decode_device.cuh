@@ -697,6 +697,50 @@ __device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane,
     return true;
 }
 
+// merge_partial shared out to the kWarps warps of a CTA that all work on ONE item: warp `part`
+// merges a contiguous share of the n states, the shares are combined through shared memory, and
+// warp 0 returns the result (the other warps return false).  A long request cut into ~90 states
+// costs one warp six dependent rounds of loads; four warps need two.  Every thread of the CTA
+// must call (CTA barrier inside).
+template <int kWarps, typename StateOf>
+__device__ __forceinline__ bool merge_partial_shared(StateOf state_of, int n, int lane, int part,
+                                                     float &top, float &norm, float4 &acc) {
+    __shared__ float4 share_acc[kWarps][32];
+    __shared__ float share_top[kWarps], share_norm[kWarps];
+    __shared__ int share_poisoned;
+    const int lo = (int)((long long)n * part / kWarps);
+    const int hi = (int)((long long)n * (part + 1) / kWarps);
+    if (part == 0 && lane == 0) share_poisoned = 0;
+    __syncthreads();
+    const bool ok =
+        merge_partial([&](int i) { return state_of(lo + i); }, hi - lo, lane, top, norm, acc);
+    share_acc[part][lane] = acc;
+    if (lane == 0) {
+        share_top[part] = top;
+        share_norm[part] = norm;
+        if (!ok) share_poisoned = 1;
+    }
+    __syncthreads();
+    if (part != 0 || share_poisoned) return false;
+    top = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kWarps; ++k)
+        if (share_norm[k] > 0.0f) top = fmaxf(top, share_top[k]);
+    norm = 0.0f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < kWarps; ++k) {
+        const float weight = share_norm[k] > 0.0f ? exp2f(share_top[k] - top) : 0.0f;
+        const float4 other = share_acc[k][lane];
+        norm += share_norm[k] * weight;
+        acc.x += other.x * weight;
+        acc.y += other.y * weight;
+        acc.z += other.z * weight;
+        acc.w += other.w * weight;
+    }
+    return true;
+}
+
 // BF16 O + log2 LSE of a merged row: lane l writes dims 4l .. 4l + 3.
 __device__ __forceinline__ void publish_merged(float top, float norm, float4 acc, int lane,
                                                __nv_bfloat16 *out_row, float *lse_slot) {
@@ -717,20 +761,34 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
 }
 
+// As merge_states, by the kWarps warps of a CTA for one item (every thread of the CTA calls).
+template <int kWarps, typename StateOf>
+__device__ __forceinline__ void merge_states_shared(StateOf state_of, int n, int lane, int part,
+                                                    __nv_bfloat16 *out_row, float *lse_slot) {
+    float top, norm;
+    float4 acc;
+    if (!merge_partial_shared<kWarps>(state_of, n, lane, part, top, norm, acc)) return;
+    if (!(norm > 0.0f)) return;
+    publish_merged(top, norm, acc, lane, out_row, lse_slot);
+}
+
 // As merge_states, into the row of `request`, query head `head` of every rank's copy of the
 // gathered result.  The row map and the peers' addresses (lane p holds rank p's) are fetched
 // before the states, so that the stores at the end wait for nothing.
-template <typename StateOf>
+template <int kWarps = 1, typename StateOf>
 __device__ __forceinline__ void merge_states_to_peers(StateOf state_of, int n, int lane,
                                                       bool publish, const PeerOut &peer,
-                                                      int request, int head) {
+                                                      int request, int head, int part = 0) {
     const int dest = peer.dest_rows[request];
     __nv_bfloat16 *out_of_lane =
         lane < peer.world ? static_cast<__nv_bfloat16 *>(peer.out[lane]) : nullptr;
     float *lse_of_lane = lane < peer.world ? peer.lse[lane] : nullptr;
     float top, norm;
     float4 acc;
-    const bool ok = merge_partial(state_of, n, lane, top, norm, acc) && publish && norm > 0.0f;
+    bool ok;
+    if (kWarps == 1) ok = merge_partial(state_of, n, lane, top, norm, acc);
+    else ok = merge_partial_shared<kWarps>(state_of, n, lane, part, top, norm, acc);
+    ok = ok && publish && norm > 0.0f;
     const long long row = (long long)dest * peer.gathered_qh + peer.head_offset + head;
     for (int p = 0; p < peer.world; ++p) {
         __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(

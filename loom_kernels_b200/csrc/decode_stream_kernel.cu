@@ -398,12 +398,16 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
 
 // One warp per (request, query head): finds the workers whose ranges cut this head's item and
 // merges their states.  Items that one worker finished alone are skipped.
+// kWarps = 1: one warp per item, four items per CTA.  kWarps = 4: the four warps of a CTA share
+// the states of one item (small batches, where a long request is cut into many states).
+template <int kWarps>
 __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ workspace,
                                                     __nv_bfloat16 *output, float *lse, int batch,
                                                     int qh, int kvh, int hc, int mt, int qblocks,
                                                     int workers, int rows, const PeerOut &peer) {
     const int lane = threadIdx.x & 31;
-    const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int part = kWarps == 1 ? 0 : (int)(threadIdx.x >> 5);
+    const int state = kWarps == 1 ? blockIdx.x * 4 + (threadIdx.x >> 5) : blockIdx.x;
     if (state >= batch * qh) return;
     const int request = state / qh, qhead = state % qh;
     dependent_launch_wait(); // the states and the prefix are complete and visible
@@ -433,12 +437,19 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
         return base + ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
     };
     if (peer.world != 0) {
-        merge_states_to_peers(state_of, w1 - w0 + 1, lane, true, peer, request, qhead);
+        merge_states_to_peers<kWarps>(state_of, w1 - w0 + 1, lane, true, peer, request, qhead,
+                                      part);
         return;
     }
-    merge_states(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim, lse + state);
+    if (kWarps == 1)
+        merge_states(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim,
+                     lse + state);
+    else
+        merge_states_shared<kWarps>(state_of, w1 - w0 + 1, lane, part,
+                                    output + (size_t)state * kHeadDim, lse + state);
 }
 
+template <int kWarps>
 __global__ void __launch_bounds__(128)
 balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
@@ -449,8 +460,8 @@ balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output
         dependent_launch_wait();
         handshake.fetch(signal);
     }
-    balanced_merge_warp(workspace, output, lse, batch, qh, kvh, hc, mt, qblocks, workers, rows,
-                        peer);
+    balanced_merge_warp<kWarps>(workspace, output, lse, batch, qh, kvh, hc, mt, qblocks, workers,
+                                rows, peer);
     handshake.finish(signal);
 }
 
@@ -515,7 +526,16 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
 
 int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block,
                           void *stream) {
-    return launch_dependent(balanced_merge_kernel, grid, block, 0, stream,
+    // a grid of one CTA per (request, query head) means four warps per item
+    if ((uint64_t)grid >= (uint64_t)launch.batch * (uint64_t)launch.qh)
+        return launch_dependent(balanced_merge_kernel<4>, grid, block, 0, stream,
+                                (const float *)launch.workspace,
+                                static_cast<__nv_bfloat16 *>(launch.output), launch.lse,
+                                launch.batch, launch.qh, launch.kvh, launch.heads_per_cta,
+                                launch.q_tiles, launch.q_blocks,
+                                (int)launch.grid * launch.pages_per_stage,
+                                balanced_state_rows(launch), launch.peer, launch.signal);
+    return launch_dependent(balanced_merge_kernel<1>, grid, block, 0, stream,
                             (const float *)launch.workspace,
                             static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.batch,
                             launch.qh, launch.kvh, launch.heads_per_cta, launch.q_tiles,
