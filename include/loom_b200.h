@@ -287,8 +287,12 @@ typedef struct lb_paged_decode_plan lb_paged_decode_plan; /* Bf16PagedBatchDecod
 enum {
     LB_DECODE_DIRECT = 0,   /* one CTA per (request, head block); one command, no workspace */
     LB_DECODE_SPLIT_K = 1,  /* `partitions` page-balanced chunks per request + LSE merge */
-    LB_DECODE_BALANCED = 2  /* the batch's pages cut evenly over the SMs + LSE merge; the choice
+    LB_DECODE_BALANCED = 2, /* the batch's pages cut evenly over the SMs + LSE merge; the choice
                                for ragged batches and for batches smaller than the device */
+    LB_DECODE_CLUSTER_SPLIT = 3 /* `partitions` (2..8) chunks per request whose CTAs form one
+                               thread-block cluster and merge their states through distributed
+                               shared memory: split-K as ONE command, without a workspace; the
+                               choice for a single short request (latency-bound) */
 };
 
 typedef struct lb_paged_decode_options {
@@ -314,10 +318,13 @@ typedef struct lb_paged_decode_options {
     uint32_t pages_per_step; /* pages a consumer warp takes per step of its loop: 0 = plan-time
                                 heuristic, 1, or 2 (one joint softmax update over 32 tokens; the
                                 choice for query groups wider than 16 rows) */
+    uint32_t cluster;        /* with partitions 2..8: 1 = LB_DECODE_CLUSTER_SPLIT instead of the
+                                two-command split-K */
+    uint32_t reserved[3];
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
-    int32_t algorithm;       /* LB_DECODE_DIRECT / LB_DECODE_SPLIT_K */
+    int32_t algorithm;       /* LB_DECODE_DIRECT / _SPLIT_K / _BALANCED / _CLUSTER_SPLIT */
     uint32_t partitions;
     uint32_t heads_per_cta;
     uint32_t q_tiles;        /* 16-row MMA tiles per KV head group handled by one CTA */
@@ -326,7 +333,7 @@ typedef struct lb_paged_decode_plan_info {
     uint32_t stages;
     uint32_t grid, block, shared_bytes;
     uint32_t merge_grid, merge_block;
-    uint32_t commands;       /* 1 direct, 2 split or balanced (partials + merge) */
+    uint32_t commands;       /* 1 direct or cluster split, 2 split or balanced (partials + merge) */
     size_t workspace_numel;  /* F32 elements the caller must bind (0 for direct) */
     size_t workspace_bytes;
     uint32_t pages_per_step; /* 1 or 2, see lb_paged_decode_options */

@@ -53,7 +53,7 @@ class DecodeOptions(ctypes.Structure):
     _fields_ = [("partitions", c_uint32), ("heads_per_cta", c_uint32), ("balanced", c_uint32),
                 ("balanced_ctas", c_uint32), ("indices_capacity", c_uint32),
                 ("wait_limit_us", c_uint32), ("test_skip_page", c_uint32),
-                ("pages_per_step", c_uint32)]
+                ("pages_per_step", c_uint32), ("cluster", c_uint32), ("reserved", c_uint32 * 3)]
 
 
 class AppendOptions(ctypes.Structure):

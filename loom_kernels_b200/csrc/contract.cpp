@@ -98,6 +98,11 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         (spec.num_kv_heads / balanced_hc) * q_blocks <= 4096 &&
         2 * stage_bytes + 3072 + balanced_extra <= smem;
 
+    const bool cluster_option = options && options->cluster == 1;
+    if (options && options->cluster > 1) return fail(LB_LAUNCH_CONTRACT, "cluster", options->cluster);
+    if (cluster_option && (partitions < 2 || partitions > 8))
+        return fail(LB_INVALID_PARTITION_COUNT, nullptr, partitions, 8);
+    bool cluster = cluster_option;
     uint32_t algorithm;
     if (partitions == 1) {
         algorithm = LB_DECODE_DIRECT;
@@ -133,9 +138,14 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
             size_t p = (sms / 2) / items_for(h, 1);
             if (p > limit) p = limit;
             if (p < 1) p = 1;
+            // up to eight chunks fit one thread-block cluster, which merges them through
+            // distributed shared memory: one command instead of two (C1: 8.2 -> see the
+            // measurement notes), so the count is capped there
+            if (p > 8) p = 8;
             hc = h;
             partitions = (uint32_t)p;
             algorithm = p > 1 ? LB_DECODE_SPLIT_K : LB_DECODE_DIRECT;
+            cluster = p > 1;
         } else if (balanced_possible && balanced_option != 2) algorithm = LB_DECODE_BALANCED;
         else algorithm = LB_DECODE_SPLIT_K; // best static split below (may come out as 1 chunk)
     }
@@ -185,6 +195,14 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
                        (size_t)stages * stage_bytes < 8u * 68u * 32u * 4u))
         return fail(LB_LAUNCH_CONTRACT, "shared_memory", (int64_t)smem);
 
+    if (cluster && algorithm == LB_DECODE_SPLIT_K) {
+        // the chunk states of a CTA sit in the ring beyond the scratch of its slot merge
+        const size_t rows = group < 16u * q_tiles ? group : 16u * q_tiles;
+        const size_t needed = 8u * 68u * 32u * 4u + (size_t)hc * 16u * q_tiles * 520u;
+        (void)rows;
+        if ((size_t)stages * stage_bytes >= needed) algorithm = LB_DECODE_CLUSTER_SPLIT;
+        else if (cluster_option) return fail(LB_LAUNCH_CONTRACT, "cluster", (int64_t)needed);
+    }
     size_t grid, workspace = 0;
     if (algorithm == LB_DECODE_BALANCED) {
         grid = options && options->balanced_ctas ? options->balanced_ctas : sms;
@@ -195,7 +213,7 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     } else {
         grid = items_for(hc, partitions);
         if (grid > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)grid);
-        if (partitions > 1) {
+        if (partitions > 1 && algorithm != LB_DECODE_CLUSTER_SPLIT) {
             if (mul_overflow(states, partitions, &workspace) ||
                 mul_overflow(workspace, LB_PARTIAL_STATE_WIDTH, &workspace) ||
                 workspace > SIZE_MAX / sizeof(float))
@@ -227,7 +245,7 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     out->merge_block = 128;
     // one warp per (request, query head); the balanced merge of a small batch -- where a long
     // request is cut into many states -- gives every item a whole CTA of four warps
-    out->merge_grid = algorithm == LB_DECODE_DIRECT ? 0
+    out->merge_grid = algorithm == LB_DECODE_DIRECT || algorithm == LB_DECODE_CLUSTER_SPLIT ? 0
                       : algorithm == LB_DECODE_BALANCED && states <= 2048
                           ? (uint32_t)states
                           : ceil_div((uint32_t)states, 4);
@@ -489,7 +507,10 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
     info->shared_bytes = choice.shared_bytes;
     info->merge_grid = choice.merge_grid;
     info->merge_block = choice.merge_block;
-    info->commands = choice.algorithm == LB_DECODE_DIRECT ? 1 : 2;
+    info->commands = choice.algorithm == LB_DECODE_DIRECT ||
+                             choice.algorithm == LB_DECODE_CLUSTER_SPLIT
+                         ? 1
+                         : 2;
     info->workspace_numel = choice.workspace_numel;
     info->workspace_bytes = choice.workspace_numel * sizeof(float);
     info->pages_per_step = choice.pages_per_step;

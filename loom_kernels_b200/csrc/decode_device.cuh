@@ -68,6 +68,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
         if (clock64() - start > limit) return false;
     }
 }
+// After a wait ran out: before the CTA leaves, the lane that armed the `full` barriers of one
+// page slot waits (bounded again) for the copies it issued last into every stage of the ring, so
+// that no copy is still on its way into shared memory the next CTA may own.  `issued` = pages of
+// this slot whose copies were issued, page k into stage k % stages in round k / stages.
+__device__ __forceinline__ void drain_issued_copies(uint32_t slot_full0, int stage_stride,
+                                                    int stages, int issued, long long limit) {
+    for (int k = issued > stages ? issued - stages : 0; k < issued; ++k)
+        (void)mbar_wait(slot_full0 + (k % stages) * stage_stride, (uint32_t)(k / stages) & 1u,
+                        limit);
+}
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -595,6 +605,69 @@ __device__ __forceinline__ void write_final_rows_to_peers(const PeerLocal &peer,
             if ((lane & 3) == 0) peer.lse[p][rows[half]] = lse;
         }
     }
+}
+
+// ---- thread-block clusters: the chunks of one request reduced through distributed shared memory ----
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The address, in the shared::cluster window, of `local` (a shared::cta address) in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_address(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float2 load_cluster_float2(uint32_t address) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];"
+                 : "=f"(v.x), "=f"(v.y)
+                 : "r"(address)
+                 : "memory");
+    return v;
+}
+
+// One warp merges the `parts` states [max_log2, normaliser, wv[128]] that the CTAs of its cluster
+// hold for one row at shared-memory address `row_state` (the same address in every CTA): the
+// algebra of merge_partial against the global maximum, the states read with plain
+// ld.shared::cluster (no multicast).  Returns false when a state is poisoned or all are empty.
+__device__ __forceinline__ bool merge_cluster_row(uint32_t row_state, int parts, int lane,
+                                                  float &top, float &norm, float4 &acc) {
+    constexpr int kMaxParts = 8;
+    float part_max[kMaxParts], part_norm[kMaxParts];
+    float2 lo[kMaxParts], hi[kMaxParts];
+#pragma unroll
+    for (int p = 0; p < kMaxParts; ++p) {
+        part_max[p] = part_norm[p] = 0.0f;
+        lo[p] = hi[p] = make_float2(0.f, 0.f);
+        if (p < parts) {
+            const uint32_t remote = cluster_address(row_state, (uint32_t)p);
+            const float2 head = load_cluster_float2(remote);
+            part_max[p] = head.x;
+            part_norm[p] = head.y;
+            lo[p] = load_cluster_float2(remote + 8 + lane * 16);
+            hi[p] = load_cluster_float2(remote + 16 + lane * 16);
+        }
+    }
+    top = -INFINITY;
+    bool poisoned = false;
+#pragma unroll
+    for (int p = 0; p < kMaxParts; ++p) {
+        poisoned |= part_norm[p] < 0.0f;
+        if (part_norm[p] > 0.0f) top = fmaxf(top, part_max[p]);
+    }
+    norm = 0.0f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < kMaxParts; ++p) {
+        const float weight = part_norm[p] > 0.0f ? exp2f(part_max[p] - top) : 0.0f;
+        norm += part_norm[p] * weight;
+        acc.x += lo[p].x * weight;
+        acc.y += lo[p].y * weight;
+        acc.z += hi[p].x * weight;
+        acc.w += hi[p].y * weight;
+    }
+    return !poisoned && norm > 0.0f;
 }
 
 // Merges n unnormalised states [max_log2, normaliser, wv[128]] of one (request, query head) and

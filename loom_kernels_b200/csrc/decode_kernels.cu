@@ -55,7 +55,10 @@ struct DecodeArgs {
 
 // The work of one CTA.  A thread that has nothing (more) to do returns from here; every thread
 // of the grid then meets again in the kernel below.
-template <bool kGather>
+// kCluster: the `partitions` CTAs of one (request, head block, query block) form a thread-block
+// cluster (the chunk is the CTA's rank in it) and their states are merged through distributed
+// shared memory by the cluster's first CTA: split-K as one command, without a workspace.
+template <bool kGather, bool kCluster>
 __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const CUtensorMap &v_map,
                                                  const DecodeArgs &a, PeerLocal &peer_local) {
     extern __shared__ uint8_t smem_raw[];
@@ -80,10 +83,18 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
     int item = blockIdx.x;
+    int part = 0;
+    if (kCluster) { // the CTAs of a cluster are consecutive blocks: the chunk varies fastest
+        part = item % a.partitions;
+        item /= a.partitions;
+    }
     const int hb = item % head_blocks; item /= head_blocks;
     const int qb = item % a.qb; item /= a.qb;
-    const int part = item % a.partitions;
-    const int request = item / a.partitions;
+    if (!kCluster) {
+        part = item % a.partitions;
+        item /= a.partitions;
+    }
+    const int request = item;
 
     // barriers: one thread each, before the first touch of global memory
     if (tid < a.stages * a.pps) {
@@ -125,7 +136,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     const int chunk_end_token = min((pg0 + cnt) * kPage, kv_len);
     const int rows_per_block = 16 * a.mt;
 
-    if (cnt == 0) {
+    if (!kCluster && cnt == 0) {
         // a chunk without pages: the empty state [0, 0, 0...] the merge skips
         const int row_lo = qb * rows_per_block;
         const int row_hi = min(group, row_lo + rows_per_block);
@@ -148,6 +159,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     // consumer identity (declared here so the epilogue after the join can use it)
     WarpState st;
     int dest_request = 0; // gathering plans: the row of the gathered result this request owns
+    int issued = 0;       // producer lanes: pages of my slot whose copies were issued
     const int unit = warp / a.mt;      // consumer: which (page slot, head) of each stage
     const int mtile = warp % a.mt;     // consumer: which 16-row tile of the group
     const int page_slot0 = unit / a.hc;
@@ -210,6 +222,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
             // expected bytes then runs out, which is all a lost copy would look like)
             if (has && slot + 1 != a.skip_page)
                 tma_load_3d(my_tile + stage * stage_bytes, map, 0, page_id * kPage, z, bar_full);
+            if (has) ++issued;
             if (it == 0) LB_STAMP(4);
             if (++stage == a.stages) {
                 stage = 0;
@@ -298,12 +311,18 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     const bool timed_out = flags[1] != 0;
     const bool invalid_page = flags[0] != 0;
     if (timed_out) {
+        // nothing is published; the copies already on their way are waited for (bounded), so
+        // that none lands in shared memory after this CTA has gone
+        if (warp == kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps)
+            drain_issued_copies(full0 + (lane >> 1) * 8, a.pps * 8, a.stages, issued,
+                                a.wait_cycles);
+        __syncthreads();
         if (tid == 0 && a.status) atomicExch(a.status, 1);
-        return;
+        if (!kCluster) return; // (a cluster's CTAs still meet at its barriers: a poisoned state)
     }
 
     // page slots that streamed pages of this chunk: slot s has pages iff s < cnt
-    const int populated = min(a.pps, cnt);
+    const int populated = timed_out ? 0 : min(a.pps, cnt);
     if (populated > 1) {
         // warps that streamed different pages of the same KV head merge their states
         float *scratch = reinterpret_cast<float *>(ring);
@@ -345,6 +364,51 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     }
 
     LB_STAMP(9);
+    if (kCluster) {
+        // every CTA leaves the state of its chunk in its own shared memory (beyond the scratch of
+        // the slot merge, which other warps may still be reading) ...
+        float *chunk_state = reinterpret_cast<float *>(ring) + kComputeWarps * kMergeFloatsPerWarp;
+        const int valid_rows = min(rows_per_block, group - qb * rows_per_block);
+        if (warp < kComputeWarps && page_slot0 == 0) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = mtile * 16 + (lane >> 2) + half * 8;
+                if (row < valid_rows)
+                    write_state_row(chunk_state +
+                                        (size_t)(head_in_cta * rows_per_block + row) * kStateWidth,
+                                    lane, half, st, invalid_page || timed_out);
+            }
+        }
+        cluster_barrier();
+        // ... and the cluster's first CTA merges them, one warp per row
+        if (part == 0 && warp < kComputeWarps) {
+            for (int r = warp; r < a.hc * valid_rows; r += kComputeWarps) {
+                const int h = r / valid_rows, row = r - h * valid_rows;
+                float top, norm;
+                float4 acc;
+                const bool ok = merge_cluster_row(
+                    smem_u32(chunk_state + (size_t)(h * rows_per_block + row) * kStateWidth),
+                    a.partitions, lane, top, norm, acc);
+                const long long head = (long long)(hb * a.hc + h) * group + qb * rows_per_block + row;
+                if (kGather && a.peer.world != 0) {
+                    const long long out_row =
+                        (long long)a.peer.dest_rows[request] * a.peer.gathered_qh +
+                        a.peer.head_offset + head;
+                    for (int p = 0; p < a.peer.world; ++p)
+                        if (ok)
+                            publish_merged(top, norm, acc, lane,
+                                           static_cast<__nv_bfloat16 *>(peer_local.out[p]) +
+                                               out_row * kHeadDim,
+                                           peer_local.lse[p] + out_row);
+                } else if (ok) {
+                    const long long state = (long long)request * a.qh + head;
+                    publish_merged(top, norm, acc, lane, a.output + state * kHeadDim, a.lse + state);
+                }
+            }
+        }
+        cluster_barrier(); // nobody leaves while the first CTA still reads its shared memory
+        return;
+    }
     if (warp >= kComputeWarps || page_slot0 != 0) return;
 
     // ---- epilogue ---------------------------------------------------------------------------------
@@ -377,13 +441,13 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
 
 // kGather: the instantiation for plans that gather their output (the other one carries none of
 // its registers or shared memory).
-template <bool kGather>
+template <bool kGather, bool kCluster>
 __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const DecodeArgs a) {
     __shared__ PeerLocal peer_local;
     dependent_launch_release();
-    paged_decode_cta<kGather>(k_map, v_map, a, peer_local);
+    paged_decode_cta<kGather, kCluster>(k_map, v_map, a, peer_local);
     if (!kGather || a.signal.world == 0 || a.signal.defer) return;
     __syncthreads(); // every row of this CTA has been stored; peer_local is complete
     if (threadIdx.x >= 32) return;
@@ -434,21 +498,24 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
     handshake.finish(signal);
 }
 
+template <bool kGather, bool kCluster>
+int configure_one(size_t max_dynamic_shared) {
+    // the opt-in limit covers static and dynamic shared memory together
+    cudaFuncAttributes attributes;
+    int rc = cudaFuncGetAttributes(&attributes, paged_decode_kernel<kGather, kCluster>);
+    if (rc) return rc;
+    return cudaFuncSetAttribute(paged_decode_kernel<kGather, kCluster>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)(max_dynamic_shared - attributes.sharedSizeBytes));
+}
+
 } // namespace
 
 int configure_decode_kernels(size_t max_dynamic_shared) {
-    // the opt-in limit covers static and dynamic shared memory together
-    cudaFuncAttributes attributes;
-    int rc = cudaFuncGetAttributes(&attributes, paged_decode_kernel<false>);
-    if (rc) return rc;
-    rc = cudaFuncSetAttribute(paged_decode_kernel<false>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)(max_dynamic_shared - attributes.sharedSizeBytes));
-    if (rc) return rc;
-    if ((rc = cudaFuncGetAttributes(&attributes, paged_decode_kernel<true>))) return rc;
-    rc = cudaFuncSetAttribute(paged_decode_kernel<true>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)(max_dynamic_shared - attributes.sharedSizeBytes));
+    int rc = configure_one<false, false>(max_dynamic_shared);
+    if (!rc) rc = configure_one<true, false>(max_dynamic_shared);
+    if (!rc) rc = configure_one<false, true>(max_dynamic_shared);
+    if (!rc) rc = configure_one<true, true>(max_dynamic_shared);
     if (rc) return rc;
     return configure_stream_kernels(max_dynamic_shared);
 }
@@ -485,10 +552,21 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    if (launch.peer.world != 0 || launch.signal.world != 0)
-        return launch_dependent(paged_decode_kernel<true>, launch.grid, launch.block,
+    const bool gather = launch.peer.world != 0 || launch.signal.world != 0;
+    if (launch.cluster) {
+        // the chunks of one item are one thread-block cluster (at most 8 CTAs: portable size)
+        const unsigned cluster = (unsigned)launch.partitions;
+        if (gather)
+            return launch_dependent_cluster(paged_decode_kernel<true, true>, launch.grid,
+                                            launch.block, launch.shared_bytes, cluster, stream,
+                                            k_map, v_map, args);
+        return launch_dependent_cluster(paged_decode_kernel<false, true>, launch.grid, launch.block,
+                                        launch.shared_bytes, cluster, stream, k_map, v_map, args);
+    }
+    if (gather)
+        return launch_dependent(paged_decode_kernel<true, false>, launch.grid, launch.block,
                                 launch.shared_bytes, stream, k_map, v_map, args);
-    return launch_dependent(paged_decode_kernel<false>, launch.grid, launch.block,
+    return launch_dependent(paged_decode_kernel<false, false>, launch.grid, launch.block,
                             launch.shared_bytes, stream, k_map, v_map, args);
 }
 

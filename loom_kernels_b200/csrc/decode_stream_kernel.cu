@@ -163,6 +163,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if ((int)blockIdx.x * a.pps >= cut.workers) return;
 
     const int rows_per_block = 16 * a.mt;
+    int issued = 0; // producer lanes: pages of my slot whose copies were issued
     LB_STAMP(8);
 
     if (warp == kComputeWarps) {
@@ -240,9 +241,11 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 mbar_expect_tx(bar_full, slot_bytes);
             }
             __syncwarp();
-            if (has)
+            if (has) {
                 tma_load_3d(my_tile + stage * stage_bytes, map, 0, max(page_id, 0) * kPage,
                             hb * a.hc * 2, bar_full);
+                ++issued;
+            }
             if (j == 0) {
                 LB_STAMP(3);
                 // the second window is fetched once the first pages are on their way
@@ -391,6 +394,14 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     LB_STAMP(6);
     __syncthreads();
     LB_STAMP(7);
+    if (*timeout_flag != 0) {
+        // a wait ran out: the copies already on their way are waited for (bounded), so that none
+        // lands in shared memory after this CTA has gone
+        if (warp == kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps)
+            drain_issued_copies(full0 + (lane >> 1) * 8, a.pps * 8, a.stages, issued,
+                                a.wait_cycles);
+        __syncthreads();
+    }
     // (rows this kernel stored into other GPUs' memory are ordered by the stream before the merge
     // kernel, whose last CTA fences at system scope before it publishes the epoch)
     if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);

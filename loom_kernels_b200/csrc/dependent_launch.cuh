@@ -45,4 +45,25 @@ int launch_dependent(void (*kernel)(KernelArgs...), unsigned grid, unsigned bloc
     return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
 }
 
+// As launch_dependent, with the grid cut into thread-block clusters of `cluster` consecutive CTAs.
+template <typename... KernelArgs, typename... Args>
+int launch_dependent_cluster(void (*kernel)(KernelArgs...), unsigned grid, unsigned block,
+                             size_t shared, unsigned cluster, void *stream, Args &&...args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(block);
+    config.dynamicSmemBytes = shared;
+    config.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = cluster;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 2;
+    return (int)cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 } // namespace lb

@@ -50,6 +50,7 @@ struct DecodeLaunch {
     int32_t batch, max_pages, qh, kvh, indices_len;
     int32_t indices_min; // page_indptr[batch] must lie in [indices_min, indices_len]
     int32_t heads_per_cta, pages_per_stage, q_tiles, q_blocks, partitions, stages;
+    int32_t cluster;        // 1: the chunks of an item are one thread-block cluster (one command)
     int32_t pages_per_step; // pages a consumer warp takes per step: 1, or 2 (one joint softmax update)
     float scale_log2;
     uint32_t grid, block, shared_bytes;

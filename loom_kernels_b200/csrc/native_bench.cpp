@@ -9,7 +9,7 @@
 // fixed-address Graph (device time per call without host launch cost), and a third one Graph of
 // a single call plus its completion event (crates/loom-infer-cuda/src/graph/mod.rs:301-323).
 //
-//     loom_native_bench [--samples 50] [--calls 100] [--device 0]
+//     loom_native_bench [--samples 50] [--calls 100] [--device 0] [--only <part of a case name>]
 //
 // Prints one JSON object per case.
 #include <cuda_runtime.h>
@@ -104,6 +104,7 @@ struct Case {
 
 struct Options {
     int samples = 50, calls = 100, device = 0;
+    std::string only; // run only the cases whose name contains this
 };
 
 lb_status record_calls(lb_scope *scope, void *user) {
@@ -210,11 +211,12 @@ struct DecodeCase : Case {
     DecodeCase(const char *label, lb_decode_provider *provider, size_t batch, size_t pages,
                size_t qh, size_t kvh, std::vector<int32_t> page_indptr,
                std::vector<int32_t> page_indices, std::vector<int32_t> last_page_len,
-               uint32_t partitions) {
+               uint32_t partitions, const lb_paged_decode_options *pinned = nullptr) {
         name = label;
         LB(lb_paged_spec_new(batch, pages, qh, kvh, 128, 16, &spec));
         lb_paged_decode_options options{};
         options.partitions = partitions;
+        if (pinned) options = *pinned;
         LB(lb_paged_decode_plan_create(provider, &spec, &options, &plan));
         lb_paged_decode_plan_info info{};
         LB(lb_paged_decode_plan_info_get(plan, nullptr, &info));
@@ -411,6 +413,7 @@ int main(int argc, char **argv) {
         if (!std::strcmp(argv[i], "--samples")) opt.samples = std::atoi(argv[i + 1]);
         else if (!std::strcmp(argv[i], "--calls")) opt.calls = std::atoi(argv[i + 1]);
         else if (!std::strcmp(argv[i], "--device")) opt.device = std::atoi(argv[i + 1]);
+        else if (!std::strcmp(argv[i], "--only")) opt.only = argv[i + 1];
     }
     CU(cudaSetDevice(opt.device));
     lb_decode_provider *decode = nullptr;
@@ -454,8 +457,31 @@ int main(int argc, char **argv) {
                            {1, 4, 16}, {128, 256, 512});
     PrefillCase p_gqa_long("gate prefill gqa4_b2_q32_64_kv256_1024 16/4", prefill, 16, 4, {32, 64},
                            {256, 1024});
-    Case *cases[] = {&mha, &mqa, &gqa, &one, &six, &c2, &c1, &p_mha, &p_mqa, &p_gqa, &p_mqa_long,
-                     &p_gqa_long};
-    for (Case *c : cases) measure(*c, opt);
+    // C1 with the plan's parameters pinned (heads per CTA, chunks, one- or two-command split, pages
+    // per consumer step): the measurements behind the plan-time rule for a single short request
+    std::vector<DecodeCase *> c1_variants;
+    if (!opt.only.empty() && opt.only.find("C1") == 0) {
+        const uint32_t grid[][4] = {{4, 8, 1, 1}, {4, 8, 1, 2}, {2, 8, 1, 1}, {2, 8, 1, 2},
+                                    {1, 4, 1, 1}, {1, 4, 1, 2}, {4, 8, 0, 1}, {4, 9, 0, 1},
+                                    {2, 4, 1, 2}, {4, 4, 1, 2}};
+        for (const auto &g : grid) {
+            lb_paged_decode_options o{};
+            o.heads_per_cta = g[0];
+            o.partitions = g[1];
+            o.cluster = g[2];
+            o.pages_per_step = g[3];
+            char label[160];
+            std::snprintf(label, sizeof(label),
+                          "C1 variant hc%u x %u chunks, %s, %u page(s) per step", g[0], g[1],
+                          g[2] ? "cluster (1 command)" : "workspace (2 commands)", g[3]);
+            c1_variants.push_back(new DecodeCase(label, decode, 1, 256, 32, 32, {0, 64}, c1_pages,
+                                                 {16}, 0, &o));
+        }
+    }
+    std::vector<Case *> cases = {&mha, &mqa, &gqa, &one, &six, &c2, &c1, &p_mha, &p_mqa, &p_gqa,
+                                 &p_mqa_long, &p_gqa_long};
+    for (DecodeCase *c : c1_variants) cases.push_back(c);
+    for (Case *c : cases)
+        if (opt.only.empty() || c->name.find(opt.only) != std::string::npos) measure(*c, opt);
     return 0;
 }

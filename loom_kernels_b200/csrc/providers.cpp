@@ -107,7 +107,8 @@ void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
     info->shared_bytes = c.shared_bytes;
     info->merge_grid = c.merge_grid;
     info->merge_block = c.merge_block;
-    info->commands = c.algorithm == LB_DECODE_DIRECT ? 1 : 2;
+    info->commands =
+        c.algorithm == LB_DECODE_DIRECT || c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 2;
     info->workspace_numel = c.workspace_numel;
     info->workspace_bytes = c.workspace_numel * sizeof(float);
     info->pages_per_step = c.pages_per_step;
@@ -264,7 +265,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     const lb_paged_spec &spec = plan->spec;
     const DecodeChoice &c = plan->choice;
     const bool balanced = c.algorithm == LB_DECODE_BALANCED;
-    const bool split = c.algorithm != LB_DECODE_DIRECT; // two commands and a workspace
+    const bool split = c.algorithm == LB_DECODE_SPLIT_K || balanced; // two commands, a workspace
     if (scope->queue->device != plan->device)
         return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
     // both commands of a split plan must fit before anything is launched (decode.rs:1327)
@@ -361,6 +362,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     launch.partitions = (int32_t)c.partitions;
     launch.stages = (int32_t)c.stages;
     launch.pages_per_step = (int32_t)c.pages_per_step;
+    launch.cluster = c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 0;
     launch.scale_log2 = spec.softmax_scale * kLog2E;
     launch.grid = c.grid;
     launch.block = c.block;

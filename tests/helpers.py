@@ -56,11 +56,13 @@ class DecodeRun:
     """One paged decode through the public API: spec -> plan -> bindings -> scope -> fence."""
 
     def __init__(self, spec, q_bits, k_bits, v_bits, indptr, indices, last, partitions=0,
-                 heads_per_cta=0, device="cuda:0", provider=None, max_commands=2, balanced=0):
+                 heads_per_cta=0, device="cuda:0", provider=None, max_commands=2, balanced=0,
+                 **plan_options):
         self.spec = spec
         self.device = torch.device(device)
         self.provider = provider or lk.DecodeProvider.load(self.device.index or 0)
-        self.plan = self.provider.plan_bf16_paged_batch(spec, partitions, heads_per_cta, balanced)
+        self.plan = self.provider.plan_bf16_paged_batch(spec, partitions, heads_per_cta, balanced,
+                                                        **plan_options)
         self.stream = torch.cuda.Stream(device=self.device)
         self.queue = lk.CommandQueue(self.stream, max_commands)
         # BF16 bit arrays from the host, or tensors already on the device (full-size pools)

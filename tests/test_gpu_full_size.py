@@ -103,6 +103,7 @@ def test_c1_mha_batch1_context1024(provider, oracle):
     assert chosen.heads_per_cta * (w.kvh // chosen.heads_per_cta) == w.kvh
     assert w.kvh // chosen.heads_per_cta > 1  # several head blocks: more KV heads than a CTA takes
     results = []
+    assert chosen.algorithm == lk.Bf16PagedBatchDecodeAlgorithm.ClusterSplit and chosen.commands == 1
     for options in ({}, {"partitions": 1}, {"partitions": 9, "heads_per_cta": 4},
                     {"partitions": 4, "heads_per_cta": 8}, {"balanced": 1}):
         bits, lse = run(provider, w, k, v, **options)

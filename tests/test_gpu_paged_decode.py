@@ -160,6 +160,47 @@ def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced):
     H.check_decode(out, lse, eo, el, lse_limit=H.SPLIT_LSE_MAX_ABS)
 
 
+CLUSTER_SHAPES = [
+    # (batch, qh, kvh, heads_per_cta, partitions): the chunks of a request form one cluster
+    (1, 32, 32, 4, 8), (1, 32, 32, 0, 0), (1, 8, 8, 0, 2), (2, 16, 4, 2, 3), (3, 32, 8, 4, 5),
+    (2, 32, 1, 0, 4), (1, 64, 2, 0, 8), (2, 24, 1, 0, 2), (4, 12, 3, 1, 7),
+]
+
+
+@pytest.mark.parametrize("batch,qh,kvh,hc,partitions", CLUSTER_SHAPES)
+def test_cluster_split_is_one_command(oracle, provider, batch, qh, kvh, hc, partitions):
+    """Split-K whose chunk states are merged inside a thread-block cluster: one command, no
+    workspace, the results of the two-command split (requests shorter than the chunk count leave
+    chunks without pages)."""
+    rng = np.random.default_rng(batch * 77 + qh + kvh + partitions)
+    pool = 256 if batch == 1 else 96
+    kv_lens = rng.integers(1, 16 * 18, size=batch)
+    kv_lens[0] = 16 * 64 if batch == 1 else 16 * 17 + 1
+    if batch > 1:
+        kv_lens[1] = 5  # one page: every chunk but the first is empty
+    indptr, indices, last = H.make_page_table(rng, kv_lens, pool)
+    spec = lk.Bf16PagedBatchDecodeSpec.new(batch, pool, qh, kvh)
+    q, k, v = (H.normal_bf16(rng, n) for n in (spec.query_numel(), spec.kv_pages_numel(),
+                                               spec.kv_pages_numel()))
+    options = dict(partitions=partitions, heads_per_cta=hc, cluster=True) if partitions else {}
+    run = H.DecodeRun(spec, q, k, v, indptr, indices, last, provider=provider, **options)
+    assert run.plan.algorithm() == lk.Bf16PagedBatchDecodeAlgorithm.ClusterSplit
+    assert run.plan.commands() == 1 and run.plan.workspace_required_numel() == 0
+    out, lse = run.run()
+    assert run.submitted == 1
+    eo, el = oracle.paged_decode(oracle.paged_spec(batch, pool, qh, kvh), q, k, v, indptr, indices,
+                                 last, threads=4)
+    H.check_decode(out, lse, eo, el, lse_limit=H.SPLIT_LSE_MAX_ABS)
+    # an out-of-range page in one chunk: that request keeps its sentinels, the others do not
+    if batch > 1:
+        broken = indices.copy()
+        broken[indptr[0] + 9] = pool
+        run = H.DecodeRun(spec, q, k, v, indptr, broken, last, provider=provider, **options)
+        out, lse = run.run()
+        rows = H.bits_to_f32(out).reshape(batch, -1)
+        assert np.all(np.isnan(rows[0])) and np.all(np.isfinite(rows[1:]))
+
+
 def test_balanced_guards_keep_sentinels(provider):
     # the page-balanced algorithm keeps the reference's device guards: an out-of-range page or
     # a bad last_page_len leaves that request (and only it) unwritten
