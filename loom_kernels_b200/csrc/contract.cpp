@@ -209,7 +209,8 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         if (grid > sms) grid = sms; // workers share nothing, but one CTA per SM is the design
         const size_t workers = grid * pps;
         const size_t rows = group < 16u * q_tiles ? group : 16u * q_tiles;
-        workspace = workers * 2 * hc * rows * LB_PARTIAL_STATE_WIDTH + spec.batch_size + 2;
+        // states, then the page prefix (batch + 1 ints) and the cut the merge kernel reuses
+        workspace = workers * 2 * hc * rows * LB_PARTIAL_STATE_WIDTH + spec.batch_size + 8;
     } else {
         grid = items_for(hc, partitions);
         if (grid > 0x7fffffffu) return fail(LB_STATE_COUNT_OUT_OF_RANGE, nullptr, (int64_t)grid);

@@ -689,9 +689,47 @@ constexpr int kMergeCached = 4;  // rounds of 32 states whose (max, normaliser) 
 // depend on a value still in flight is issued first: the (max, normaliser) pairs of the first
 // 128 states and the rows of the first 16, so that a merge of up to 16 states -- the common
 // case -- costs one memory round trip, and a long request one more per 16 states.
-template <typename StateOf>
+// kBatch: states whose row loads are in flight together (16, or 8 where registers are scarce).
+template <int kBatch = kMergeBatch, typename StateOf>
 __device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane, float &top,
                                               float &norm, float4 &acc) {
+    if (n <= 4) {
+        // the common case of a balanced plan (a request cut once or twice): a handful of
+        // instructions instead of the batched loops below, whose cost does not depend on n
+        float part_max[4], part_norm[4];
+        float2 lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float *s = i < n ? state_of(i) : nullptr;
+            part_max[i] = part_norm[i] = 0.0f;
+            lo[i] = hi[i] = make_float2(0.f, 0.f);
+            if (s != nullptr) {
+                part_max[i] = __ldcg(s);
+                part_norm[i] = __ldcg(s + 1);
+                lo[i] = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
+                hi[i] = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+            }
+        }
+        top = -INFINITY;
+        bool poisoned = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            poisoned |= part_norm[i] < 0.0f;
+            if (part_norm[i] > 0.0f) top = fmaxf(top, part_max[i]);
+        }
+        norm = 0.0f;
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float weight = part_norm[i] > 0.0f ? exp2f(part_max[i] - top) : 0.0f;
+            norm += part_norm[i] * weight;
+            acc.x += lo[i].x * weight;
+            acc.y += lo[i].y * weight;
+            acc.z += hi[i].x * weight;
+            acc.w += hi[i].y * weight;
+        }
+        return !poisoned;
+    }
     float my_norm[kMergeCached], my_max[kMergeCached];
 #pragma unroll
     for (int k = 0; k < kMergeCached; ++k) {
@@ -699,10 +737,10 @@ __device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane,
         my_norm[k] = s ? __ldcg(s + 1) : 0.0f;
         my_max[k] = s ? __ldcg(s) : 0.0f;
     }
-    float2 lo[kMergeBatch], hi[kMergeBatch];
+    float2 lo[kBatch], hi[kBatch];
     auto fetch_rows = [&](int base) { // rows of states base .. base + 15 (zero past n)
 #pragma unroll
-        for (int u = 0; u < kMergeBatch; ++u) {
+        for (int u = 0; u < kBatch; ++u) {
             const float *s = base + u < n ? state_of(base + u) : nullptr;
             lo[u] = hi[u] = make_float2(0.f, 0.f);
             if (s != nullptr) {
@@ -751,13 +789,13 @@ __device__ __forceinline__ bool merge_partial(StateOf state_of, int n, int lane,
         const float my_weight = part_norm > 0.0f ? exp2f(part_max - top) : 0.0f;
         norm += part_norm * my_weight;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int base = round * 32 + half * kMergeBatch;
+        for (int half = 0; half < 32 / kBatch; ++half) {
+            const int base = round * 32 + half * kBatch;
             if (base >= n) break;
             if (base > 0) fetch_rows(base); // the first batch is already here
 #pragma unroll
-            for (int u = 0; u < kMergeBatch; ++u) {
-                const float weight = __shfl_sync(0xffffffffu, my_weight, half * kMergeBatch + u);
+            for (int u = 0; u < kBatch; ++u) {
+                const float weight = __shfl_sync(0xffffffffu, my_weight, half * kBatch + u);
                 acc.x += lo[u].x * weight;
                 acc.y += lo[u].y * weight;
                 acc.z += hi[u].x * weight;
@@ -824,12 +862,12 @@ __device__ __forceinline__ void publish_merged(float top, float norm, float4 acc
     if (lane == 0) *lse_slot = top + log2f(norm);
 }
 
-template <typename StateOf>
+template <int kBatch = kMergeBatch, typename StateOf>
 __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, bool publish,
                                              __nv_bfloat16 *out_row, float *lse_slot) {
     float top, norm;
     float4 acc;
-    if (!merge_partial(state_of, n, lane, top, norm, acc) || !publish) return;
+    if (!merge_partial<kBatch>(state_of, n, lane, top, norm, acc) || !publish) return;
     if (!(norm > 0.0f)) return; // every state was empty: nothing to publish
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
 }
@@ -859,7 +897,7 @@ __device__ __forceinline__ void merge_states_to_peers(StateOf state_of, int n, i
     float top, norm;
     float4 acc;
     bool ok;
-    if (kWarps == 1) ok = merge_partial(state_of, n, lane, top, norm, acc);
+    if (kWarps == 1) ok = merge_partial<8>(state_of, n, lane, top, norm, acc);
     else ok = merge_partial_shared<kWarps>(state_of, n, lane, part, top, norm, acc);
     ok = ok && publish && norm > 0.0f;
     const long long row = (long long)dest * peer.gathered_qh + peer.head_offset + head;
@@ -911,6 +949,9 @@ struct EvenCut {
         q = total / workers;
         r = (int)(total - q * workers);
     }
+    // a cut computed earlier (the 64-bit division above costs a warp hundreds of instructions)
+    __device__ __forceinline__ EvenCut(long long q_, int r_, int workers_)
+        : q(q_), r(r_), workers(workers_) {}
     __device__ __forceinline__ long long begin(int w) const {
         return q * w + (long long)((unsigned)r * (unsigned)w / (unsigned)workers);
     }
@@ -919,6 +960,16 @@ struct EvenCut {
     __device__ __forceinline__ int owner(long long x) const {
         const long long total = q * workers + r;
         return (int)(((x + 1) * workers - 1) / total);
+    }
+    // the same without a 64-bit division: a double-precision estimate (exact to well below one
+    // worker for any total this library accepts), then at most a step either way
+    __device__ __forceinline__ int owner_fast(long long x) const {
+        const double total = (double)q * (double)workers + (double)r;
+        int w = (int)(((double)(x + 1) * (double)workers - 1.0) / total);
+        w = w < 0 ? 0 : (w >= workers ? workers - 1 : w);
+        while (w > 0 && begin(w) > x) --w;
+        while (w + 1 < workers && begin(w + 1) <= x) ++w;
+        return w;
     }
 };
 

@@ -151,15 +151,21 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
     const int items = head_blocks * a.qb;
+    // little work uses fewer workers; a CTA none of whose page slots is a worker leaves at once
+    const EvenCut cut((long long)(total > 0 ? total : 1) * items, a.workers);
     if (blockIdx.x == 0) {
-        // the merge kernel reads the same prefix
+        // the merge kernel reads the same prefix and the same cut
         int *out_prefix =
             reinterpret_cast<int *>(a.workspace + state_floats(a.workers, a.hc, a.rows));
         for (int i = tid; i <= a.batch; i += blockDim.x) out_prefix[i] = prefix[i];
+        if (tid == 0) {
+            out_prefix[a.batch + 1] = (int)(cut.q & 0xffffffffll);
+            out_prefix[a.batch + 2] = (int)(cut.q >> 32);
+            out_prefix[a.batch + 3] = cut.r;
+            out_prefix[a.batch + 4] = cut.workers;
+        }
     }
     if (total == 0) return;
-    // little work uses fewer workers; a CTA none of whose page slots is a worker leaves at once
-    const EvenCut cut((long long)total * items, a.workers);
     if ((int)blockIdx.x * a.pps >= cut.workers) return;
 
     const int rows_per_block = 16 * a.mt;
@@ -433,10 +439,12 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
     const int rows_per_block = 16 * mt;
     const int hb = kv_head / hc, head_in_cta = kv_head % hc;
     const int qb = g / rows_per_block, row = g % rows_per_block;
-    const int items = (kvh / hc) * qblocks;
-    const EvenCut cut((long long)total * items, workers);
+    // the cut the decode kernel made (four more words behind the prefix, loaded with it)
+    const EvenCut cut(((long long)__ldcg(prefix + batch + 2) << 32) |
+                          (long long)(unsigned)__ldcg(prefix + batch + 1),
+                      __ldcg(prefix + batch + 3), __ldcg(prefix + batch + 4));
     const long long start = (long long)(hb * qblocks + qb) * total + page0;
-    const int w0 = cut.owner(start), w1 = cut.owner(start + num_pages - 1);
+    const int w0 = cut.owner_fast(start), w1 = cut.owner_fast(start + num_pages - 1);
     if (w0 == w1) return; // finished in place by the decode kernel
     // every worker in [w0, w1] holds pages of this item (a worker is never empty); all but the
     // first begin inside the item and used slot 0
@@ -453,15 +461,17 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
         return;
     }
     if (kWarps == 1)
-        merge_states(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim,
-                     lse + state);
+        merge_states<8>(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim,
+                        lse + state);
     else
         merge_states_shared<kWarps>(state_of, w1 - w0 + 1, lane, part,
                                     output + (size_t)state * kHeadDim, lse + state);
 }
 
+// (one warp per item: the kernel is a few waves of latency-bound CTAs, so it is built for eight
+// CTAs per SM, 64 registers, rather than for the four that its long-request path would take)
 template <int kWarps>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, kWarps == 1 ? 8 : 1)
 balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
                       int rows, const PeerOut peer, const PeerSignal signal) {
