@@ -40,9 +40,10 @@ sys.path.insert(0, ROOT)
 METRIC = "paged_decode_achieved_hbm_bandwidth"
 UNIT = "GB/s"
 # DRAM traffic per launch / algorithmic bytes, from the ncu capture summarised in
-# profiles/paged_decode_kernel_gqa4_ctx4096.md (dram__bytes_read.sum + dram__bytes_write.sum of a
-# batch-16 launch, which scales with the units processed).
-TRAFFIC_RATIO = 1.017
+# profiles/paged_decode_kernel_gqa4_ctx4096.md: dram__bytes_read.sum + dram__bytes_write.sum =
+# 268.63 + 3.69 MB of a batch-16 launch of the timed plan (direct, 4 KV heads per CTA, 16 KB
+# boxes) over its 268.72 MB of algorithmic bytes; traffic scales with the pages read.
+TRAFFIC_RATIO = 1.0134
 
 
 def measured_peak_gbs():

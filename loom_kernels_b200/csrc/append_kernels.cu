@@ -464,9 +464,10 @@ append_scatter_kernel(const AppendArgs a, const int32_t *workspace) {
     if (tid < kPairs) table[tid] = pair_sincos(speculative_position(a, token), tid);
     __syncthreads();
     dev::dependent_launch_wait(); // the verdicts and this token's slot are final
+    // the slot travels with the verdicts (one round trip, not two); it is used only if they agree
+    const int slot = __ldcg(workspace + kVerdictSlots + 2 * token + 1);
     const int verdict = __syncthreads_or(tid < kVerdictSlots ? __ldcg(workspace + tid) : 0);
     if (verdict != 0) return;
-    const int slot = __ldcg(workspace + kVerdictSlots + 2 * token + 1);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int task = tid + i * kScatterThreads;
