@@ -242,7 +242,9 @@ lb_handle lb_handle_write(lb_handle read_write);
 /* CommandQueue::new, submission.rs:31-46.  `stream` is a cudaStream_t / CUstream owned by
  * the caller; it must outlive the queue. */
 lb_status lb_queue_create(void *stream, size_t max_commands, lb_queue **out);
-/* Drop for CommandQueue, submission.rs:102-117 (synchronises retained work first). */
+/* Drop for CommandQueue, submission.rs:102-117 (synchronises retained work first).  While a scope
+ * or completion of the queue is alive the destruction is deferred until it has settled (in Rust the
+ * borrow makes that order impossible). */
 void lb_queue_destroy(lb_queue *queue);
 void *lb_queue_stream(const lb_queue *queue);
 size_t lb_queue_max_commands(const lb_queue *queue);

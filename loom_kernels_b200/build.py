@@ -22,26 +22,44 @@ def sources():
     return [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
 
 
-def is_stale() -> bool:
-    if not os.path.exists(LIB):
+def is_stale(lib: str = LIB) -> bool:
+    if not os.path.exists(lib):
         return True
-    built = os.path.getmtime(LIB)
+    built = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, s) for s in sources()] + [
         h if os.path.isabs(h) else os.path.join(CSRC, h) for h in HEADERS]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not is_stale():
-        return LIB
-    obj_dir = os.path.join(HERE, "build")
+# Checked builds (libraries of their own beside the product; `python build.py --asan` ...):
+#   asan          host code with AddressSanitizer + UndefinedBehaviorSanitizer, for the host-side
+#                 tests under the fake driver (the stand-in for compute-sanitizer's host checks)
+#   debug-bounds  every computed global index of the decode and append kernels checked against the
+#                 length of the operand it indexes (LB_DEBUG_BOUNDS): a violation sets the status
+#                 word and skips the access, it never traps
+VARIANTS = {
+    "asan": ["-g", "-Xcompiler", "-fsanitize=address,-fsanitize=undefined,-fno-omit-frame-pointer"],
+    "debug-bounds": ["-DLB_DEBUG_BOUNDS=1"],
+}
+
+
+def variant_path(variant: str) -> str:
+    return os.path.join(HERE, f"libloom_b200_{variant.replace('-', '_')}.so")
+
+
+def build(force: bool = False, verbose: bool = False, variant: str = "") -> str:
+    lib = variant_path(variant) if variant else LIB
+    if not force and not is_stale(lib):
+        return lib
+    obj_dir = os.path.join(HERE, "build", variant) if variant else os.path.join(HERE, "build")
     os.makedirs(obj_dir, exist_ok=True)
+    extra = VARIANTS[variant] if variant else []
     objects = []
     procs = []
     for source in sources():
         obj = os.path.join(obj_dir, os.path.splitext(source)[0] + ".o")
         objects.append(obj)
-        cmd = [NVCC, *FLAGS, "-c", os.path.join(CSRC, source), "-o", obj]
+        cmd = [NVCC, *FLAGS, *extra, "-c", os.path.join(CSRC, source), "-o", obj]
         if verbose and source.endswith(".cu"):
             cmd.insert(1, "-Xptxas=-v")
         procs.append((source, subprocess.Popen(cmd, stdout=subprocess.PIPE,
@@ -54,9 +72,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= proc.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.run([NVCC, "-shared", "-o", LIB, *objects, "-gencode",
-                    "arch=compute_100a,code=sm_100a", "-ldl"], check=True)
-    return LIB
+    link_extra = ["-Xcompiler", "-fsanitize=address,-fsanitize=undefined"] if variant == "asan" else []
+    subprocess.run([NVCC, "-shared", "-o", lib, *objects, "-gencode",
+                    "arch=compute_100a,code=sm_100a", "-ldl", *link_extra], check=True)
+    return lib
 
 
 NATIVE_BENCH = os.path.join(HERE, "loom_native_bench")
@@ -77,6 +96,8 @@ def build_native_bench(force: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    chosen = [v for v in VARIANTS if f"--{v}" in sys.argv]
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv,
+                variant=chosen[0] if chosen else ""))
     if "--native-bench" in sys.argv:
         print(build_native_bench(force="--force" in sys.argv))

@@ -184,8 +184,24 @@ lb_status lb_queue_create(void *stream, size_t max_commands, lb_queue **out) {
     return LB_OK;
 }
 
+// The borrower (scope or completion) of a queue has settled: the queue is free again, or, if
+// its owner destroyed it meanwhile, goes now.
+static void release_queue(lb_queue *queue) {
+    queue->retained = 0;
+    queue->busy = false;
+    if (queue->orphaned) lb_queue_destroy(queue);
+}
+
 void lb_queue_destroy(lb_queue *queue) {
     if (!queue) return;
+    // Rust's borrow of the queue by its scope / completion makes this order impossible there; a
+    // C caller (or a garbage collector finalising a group of objects in no particular order) can
+    // get it wrong, and the borrower still holds a pointer to the queue: destruction is deferred
+    // until the borrower has settled.
+    if (queue->busy) {
+        queue->orphaned = true;
+        return;
+    }
     if (queue->retained != 0) {
         const int error = synchronize_stream_or_abort(queue->stream, queue->device);
         queue->retained = 0;
@@ -296,8 +312,7 @@ void lb_scope_abandon(lb_scope *scope) {
     } else if (scope->has_error) {
         queue->poisoned = true;
     }
-    queue->retained = 0;
-    queue->busy = false;
+    release_queue(queue);
 }
 
 lb_status lb_completion_is_complete(lb_completion *completion, int *complete) {
@@ -329,15 +344,15 @@ lb_status lb_completion_wait(lb_completion *completion, lb_bindings **out) {
     if (out) *out = nullptr;
     Queue *queue = completion->queue;
     const int failure = settle(*completion);
-    queue->retained = 0;
-    queue->busy = false;
     if (failure == 0) {
         lb_bindings *bindings = completion->bindings.release();
         if (out) *out = bindings;
         else delete bindings;
+        release_queue(queue);
         return LB_OK;
     }
     queue->poisoned = true; // bindings are dropped with the completion
+    release_queue(queue);
     return fail(LB_DRIVER, "completion", failure);
 }
 
@@ -346,8 +361,7 @@ void lb_completion_abandon(lb_completion *completion) {
     std::unique_ptr<lb_completion> owned(completion);
     Queue *queue = completion->queue;
     if (settle(*completion) != 0) queue->poisoned = true;
-    queue->retained = 0;
-    queue->busy = false;
+    release_queue(queue);
 }
 
 }

@@ -39,6 +39,7 @@ struct lb_queue { // CommandQueue
     size_t retained = 0; // retained_resources.len()
     bool poisoned = false;
     bool busy = false; // a scope or completion borrowed from this queue is alive
+    bool orphaned = false; // lb_queue_destroy came while busy: the borrower destroys the queue
     bool owns_stream = false;
 };
 

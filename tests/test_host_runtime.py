@@ -138,7 +138,7 @@ def test_plan_heuristic_is_fixed_by_spec_and_device():
     # left to itself the plan cuts a batch smaller than the device by pages, one CTA per SM
     auto = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148)
     assert (auto.algorithm, auto.commands, auto.grid, auto.heads_per_cta) == (2, 2, 148, 8)
-    assert auto.workspace_numel == 148 * 2 * 8 * 4 * 130 + 64 + 2
+    assert auto.workspace_numel == 148 * 2 * 8 * 4 * 130 + 64 + 8
     many = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(4096, 65536, 32, 8), 148)
     assert (many.algorithm, many.commands) == (0, 1)  # thousands of requests tile the device
     c4 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(8, 20000, 64, 8), 148,
@@ -727,3 +727,18 @@ def test_gathering_commands_under_the_fake_driver(fake):
     assert e.value.variant in ("ScopePoisoned", "QueuePoisoned")
     del scope
     group.close()
+
+
+def test_queue_destroyed_before_its_scope_is_deferred(fake):
+    """A queue destroyed while its scope (or completion) is alive goes only when that borrower has
+    settled: the borrower keeps a pointer to it.  (Found by the AddressSanitizer build when a
+    garbage collector finalised a queue before its scope.)"""
+    lib = _abi.load()
+    queue, bindings, scope, completion = (ctypes.c_void_p() for _ in range(4))
+    assert lib.lb_queue_create(ctypes.c_void_p(0x1000), 2, ctypes.byref(queue)) == 0
+    assert lib.lb_queue_bindings(queue, 1, ctypes.byref(bindings)) == 0
+    assert lib.lb_queue_begin(queue, bindings, ctypes.byref(scope)) == 0
+    lib.lb_queue_destroy(queue)          # deferred: the scope still points at the queue
+    assert lib.lb_scope_submitted(scope) == 0
+    assert lib.lb_scope_finish(scope, ctypes.byref(completion)) == 0
+    lib.lb_completion_abandon(completion)  # settles, and the queue goes with it
