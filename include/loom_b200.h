@@ -354,8 +354,10 @@ typedef struct lb_paged_decode_args {
 lb_status lb_decode_provider_load(int device, lb_decode_provider **out);
 void lb_decode_provider_destroy(lb_decode_provider *provider);
 /* Reads (and clears) the provider's device status word: 0 = no kernel of this provider gave up
- * on a bounded wait since the last read.  Synchronises the device.  No reference counterpart:
- * the reference's kernels have no waits. */
+ * on a bounded wait since the last read (1 = a wait inside a CTA, 2 = the wait of a gathering
+ * command for the other ranks; 0x1000 | site = the checked build of the library found a computed
+ * index outside its operand and skipped the access).  Synchronises the device.  No reference
+ * counterpart: the reference's kernels have no waits. */
 lb_status lb_decode_provider_device_status(const lb_decode_provider *provider, int32_t *status);
 /* DecodeProvider::plan_bf16_paged_batch, decode.rs:1067-1103; options may be NULL. */
 lb_status lb_paged_decode_plan_create(const lb_decode_provider *provider,
@@ -519,6 +521,10 @@ typedef struct lb_rope_append_plan_info {
 /* RopeProvider::load, rope/mod.rs:586-590 */
 lb_status lb_rope_provider_load(int device, lb_rope_provider **out);
 void lb_rope_provider_destroy(lb_rope_provider *provider);
+/* Reads (and clears) the provider's device status word.  The append kernels have no waits; only the
+ * checked build of the library (LB_DEBUG_BOUNDS: every computed index compared with its operand's
+ * length, a violation recorded as 0x1000 | site and the access skipped) ever writes it. */
+lb_status lb_rope_provider_device_status(const lb_rope_provider *provider, int32_t *status);
 /* Plan options of the append (NULL = all zero). */
 typedef struct lb_rope_append_options {
     uint32_t indices_capacity; /* as lb_paged_decode_options.indices_capacity */

@@ -230,6 +230,7 @@ SIGNATURES = {
                                                    c_void_p]),
     "lb_rope_provider_load": (c_int32, [c_int, POINTER(c_void_p)]),
     "lb_rope_provider_destroy": (None, [c_void_p]),
+    "lb_rope_provider_device_status": (c_int32, [c_void_p, POINTER(c_int32)]),
     "lb_rope_append_plan_create": (c_int32, [c_void_p, POINTER(PagedSpec), POINTER(c_void_p)]),
     "lb_rope_append_tokens_plan_create": (c_int32, [c_void_p, POINTER(AppendTokensSpec),
                                                     POINTER(c_void_p)]),

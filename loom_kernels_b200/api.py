@@ -878,6 +878,13 @@ class RopeProvider:
     def __init__(self, ptr):
         self._ptr = ptr
 
+    def device_status(self) -> int:
+        """Reads and clears the provider's device status word (written by the checked build of the
+        library only: 0x1000 | site when a computed index fell outside its operand)."""
+        status = c_int32(0)
+        _check(_abi.load().lb_rope_provider_device_status(self._ptr, byref(status)))
+        return status.value
+
     def plan_bf16_pos_ids(self, spec: Bf16RopePosIdsSpec) -> Bf16RopePosIdsPlan:
         out = c_void_p()
         _check(_abi.load().lb_rope_pos_ids_plan_create(self._ptr, byref(spec._raw), byref(out)))

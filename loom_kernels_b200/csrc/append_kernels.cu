@@ -28,15 +28,14 @@
 
 #include <cstdint>
 
+#include "bounds_check.cuh"
 #include "dependent_launch.cuh"
 #include "kernels.hpp"
 
-#ifndef LB_STAMP
-#define LB_STAMP(slot)
-#endif
-
 namespace lb {
 namespace {
+
+using dev::in_bounds;
 
 constexpr int kHeadDim = 128;
 constexpr int kPairs = 64;
@@ -52,6 +51,8 @@ struct AppendArgs {
     const int32_t *batch_indices, *positions, *indptr, *indices, *last;
     uint4 *query_output, *key_pages, *value_pages;
     int32_t tokens, batch, max_pages, qh, kvh, indices_len, indices_min, hash_slots;
+    int32_t *status;         // the checked build records an index outside its operand here
+    int32_t workspace_numel; // I32 elements bound as the workspace of an extended plan
 };
 
 // Levels 1-2 of the token -> request -> page chain, from in-bounds loads only: an out-of-range
@@ -188,6 +189,7 @@ __device__ __forceinline__ uint4 *row_destination(const AppendArgs &a, int token
 
 __device__ __forceinline__ void fetch_token(const AppendArgs &a, int token, int tid,
                                             TokenRows &rows) {
+    if (!in_bounds(token, a.tokens, a.status, dev::kSiteAppendToken)) return;
     if (tid < (a.qh + a.kvh) * 8) {
         const uint4 *src = row_source(a, token, tid >> 3);
         rows.lo = src[tid & 7];
@@ -200,6 +202,9 @@ __device__ __forceinline__ void store_token(const AppendArgs &a, int token, int 
                                             const TokenRows &rows, const float2 *sincos) {
     const int row_tasks = (a.qh + a.kvh) * 8; // 8 lanes per 128-wide row
     const int copy_tasks = a.kvh * 16;        // V rows: 16 x 16-byte chunks per KV head
+    if (!in_bounds(token, a.tokens, a.status, dev::kSiteAppendToken) ||
+        !in_bounds(slot, (long long)a.max_pages * kPage, a.status, dev::kSiteAppendPool))
+        return;
     if (tid < row_tasks)
         rotate_row(rows.lo, rows.hi, row_destination(a, token, slot, tid >> 3), tid & 7, sincos);
     for (int task = tid + kThreads; task < row_tasks; task += kThreads) {
@@ -222,7 +227,6 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
     const int grid = (int)gridDim.x;
     for (int i = tid; i < a.hash_slots; i += kThreads) hash_table[i] = -1;
     dev::dependent_launch_wait(); // global memory is touched from here on
-    LB_STAMP(0);
 
     // ---- 0. start on this CTA's first token while the call is being validated ---------------
     const int first_token = blockIdx.x;
@@ -248,7 +252,6 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
         position[u] = start[u] = 0;
         ok[u] = token < a.tokens ? token_request(a, token, position[u], start[u]) : true;
     }
-    LB_STAMP(1);
 
     // ---- 1. whole-call validation (identical in every CTA) -----------------------------------
     // the table ends at page_indptr[batch], which must lie in [indices_min, indices_len] (equal
@@ -273,7 +276,6 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
         for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
     }
     if (__syncthreads_or(invalid)) return;
-    LB_STAMP(2);
 
     // token mapping: the page lookups of four tokens per thread travel together, then the
     // physical slots go into the hash set (meeting the same key = two tokens share a slot)
@@ -286,7 +288,9 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
                 ok[u] = token < a.tokens ? token_request(a, token, position[u], start[u]) : true;
             const bool live = token < a.tokens && ok[u];
             const int page = live ? start[u] + position[u] / kPage : 0;
-            slot[u] = a.indices[page] * kPage + position[u] % kPage;
+            slot[u] = (in_bounds(page, a.indices_len, a.status, dev::kSiteIndices)
+                           ? a.indices[page]
+                           : 0) * kPage + position[u] % kPage;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -310,9 +314,7 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
             }
         }
     }
-    LB_STAMP(3);
     if (__syncthreads_or(invalid)) return;
-    LB_STAMP(4);
     if (first_token >= a.tokens) return;
 
     // ---- 2. rotate + scatter: token k's rows are in registers and its table in shared memory
@@ -332,12 +334,10 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
         TokenRows other;
         if (k + 1 < count) fetch_token(a, token + grid, tid, other);
         store_token(a, token, mine[k].y, tid, rows, sincos_table[k % kTables]);
-        if (k == 0) LB_STAMP(5);
         if (++k == count) break; // k is odd now: never a table boundary (kTables is even)
         if (k + 1 < count) fetch_token(a, token + 2 * grid, tid, rows);
         store_token(a, token + grid, mine[k].y, tid, other, sincos_table[k % kTables]);
     }
-    LB_STAMP(6);
 }
 
 // ---- the any-total append as two commands ----------------------------------------------------------
@@ -417,8 +417,11 @@ append_validate_kernel(const AppendArgs a, int32_t *workspace) {
             for (int u = 0; u < 4; ++u) {
                 const int token = base + u * kValidateThreads + tid;
                 if (token >= a.tokens) continue;
-                workspace[kVerdictSlots + 2 * token] = position[u];
-                workspace[kVerdictSlots + 2 * token + 1] = slot[u];
+                if (in_bounds(kVerdictSlots + 2 * token + 1, a.workspace_numel, a.status,
+                              dev::kSiteAppendWorkspace)) {
+                    workspace[kVerdictSlots + 2 * token] = position[u];
+                    workspace[kVerdictSlots + 2 * token + 1] = slot[u];
+                }
                 if (!ok[u]) {
                     invalid = true;
                     continue;
@@ -468,6 +471,7 @@ append_scatter_kernel(const AppendArgs a, const int32_t *workspace) {
     const int slot = __ldcg(workspace + kVerdictSlots + 2 * token + 1);
     const int verdict = __syncthreads_or(tid < kVerdictSlots ? __ldcg(workspace + tid) : 0);
     if (verdict != 0) return;
+    if (!in_bounds(slot, (long long)a.max_pages * kPage, a.status, dev::kSiteAppendPool)) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int task = tid + i * kScatterThreads;
@@ -575,6 +579,8 @@ static AppendArgs append_args(const AppendLaunch &launch) {
     args.indices_len = launch.indices_len;
     args.indices_min = launch.indices_min;
     args.hash_slots = launch.hash_slots;
+    args.status = launch.status;
+    args.workspace_numel = launch.workspace_numel;
     return args;
 }
 

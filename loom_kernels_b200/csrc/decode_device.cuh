@@ -12,15 +12,9 @@
 
 #include <cstdint>
 
+#include "bounds_check.cuh"
 #include "dependent_launch.cuh"
 #include "kernels.hpp"
-
-// A profiling build may define LB_STAMP(slot) before this header to record a per-warp timeline
-// of the kernels; in the product it expands to nothing.
-#ifndef LB_STAMP
-#define LB_STAMP(slot)
-#define LB_STAMPV(slot, value)
-#endif
 
 namespace lb {
 namespace dev {
@@ -133,7 +127,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ bool request_metadata_valid(const int32_t *indptr, const int32_t *last,
                                                        int batch, int indices_min, int indices_len,
                                                        int request, int &page_start, int &page_end,
-                                                       int &tail) {
+                                                       int &tail, int32_t *status = nullptr) {
+    if (!in_bounds(request, batch, status, kSiteIndptr)) return false; // indptr[request + 1], last
     const int global_end = indptr[batch];
     page_start = indptr[request];
     page_end = indptr[request + 1];

@@ -46,6 +46,7 @@ struct DecodeArgs {
     int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, partitions, stages;
     float scale_log2;
+    long long workspace_numel; // F32 elements bound as the workspace (checked builds)
     int32_t pair;          // 1: a consumer warp takes two pages of its slot per step
     int32_t skip_page;     // tests of the give-up path: 1 + the page whose loads are left out
     long long wait_cycles; // limit of every bounded wait
@@ -79,7 +80,6 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     // flags[0] = an out-of-range page index was seen; flags[1] = a bounded wait ran out
 
     // ---- work item --------------------------------------------------------------------------
-    LB_STAMP(0);
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
     int item = blockIdx.x;
@@ -124,9 +124,8 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     if (warp == kComputeWarps && lane < a.indices_len) head_of_table = a.indices[lane];
     int page_start, page_end, tail;
     if (!request_metadata_valid(a.indptr, a.last, a.batch, a.indices_min, a.indices_len, request,
-                                page_start, page_end, tail))
+                                page_start, page_end, tail, a.status))
         return;
-    LB_STAMP(1);
     const int num_pages = page_end - page_start;
     const int kv_len = (num_pages - 1) * kPage + tail;
     // balanced page partition (single_decode/mod.rs:171-185 applied to pages)
@@ -146,13 +145,14 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
             const int row = (i / kStateWidth) % rows;
             const int h = i / (kStateWidth * rows);
             const int qhead = (hb * a.hc + h) * group + row_lo + row;
-            a.workspace[((size_t)(request * a.qh + qhead) * a.partitions + part) * kStateWidth + e] =
-                0.0f;
+            const size_t at =
+                ((size_t)(request * a.qh + qhead) * a.partitions + part) * kStateWidth + e;
+            if (in_bounds((long long)at, a.workspace_numel, a.status, kSiteWorkspace))
+                a.workspace[at] = 0.0f;
         }
         return;
     }
 
-    LB_STAMP(2);
 
     const int n_iter = (cnt + a.pps - 1) / a.pps;
 
@@ -174,7 +174,9 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         const CUtensorMap *map = which == 0 ? &k_map : &v_map;
         bool bad_page = false;
         auto fetch_page = [&](int j) -> int { // the raw id (0 past the chunk)
-            return j < cnt ? a.indices[page_start + pg0 + j] : 0;
+            if (j >= cnt) return 0;
+            const int at = page_start + pg0 + j;
+            return in_bounds(at, a.indices_len, a.status, kSiteIndices) ? a.indices[at] : 0;
         };
         auto check_page = [&](int id) -> int {
             if (id < 0 || id >= a.max_pages) {
@@ -188,11 +190,12 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         const int first_index = page_start + pg0 + lane;
         int window = __shfl_sync(0xffffffffu, head_of_table, first_index & 31);
         if (lane >= cnt) window = 0;
-        else if (first_index >= 32) window = a.indices[first_index];
+        else if (first_index >= 32 &&
+                 in_bounds(first_index, a.indices_len, a.status, kSiteIndices))
+            window = a.indices[first_index];
         int window_next = fetch_page(32 + lane);
         window = check_page(window);
         window_next = check_page(window_next);
-        LB_STAMP(3);
         const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
         const uint32_t my_tile =
             smem_u32(ring + my_slot * slot_bytes + which * (slot_bytes / 2));
@@ -221,9 +224,11 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
             // (a test of the give-up path leaves one page's loads out: its consumers' wait for the
             // expected bytes then runs out, which is all a lost copy would look like)
             if (has && slot + 1 != a.skip_page)
-                tma_load_3d(my_tile + stage * stage_bytes, map, 0, page_id * kPage, z, bar_full);
+                tma_load_3d(my_tile + stage * stage_bytes, map, 0,
+                            in_bounds(page_id, a.max_pages, a.status, kSitePage) ? page_id * kPage
+                                                                                : 0,
+                            z, bar_full);
             if (has) ++issued;
-            if (it == 0) LB_STAMP(4);
             if (++stage == a.stages) {
                 stage = 0;
                 phase ^= 1;
@@ -238,10 +243,13 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         const int kv_head = hb * a.hc + head_in_cta;
         const int row0 = qb * rows_per_block + mtile * 16;
         uint32_t qf[8][4];
-        load_query_fragments(
-            a.query + ((size_t)request * a.qh + (size_t)kv_head * group + row0) * kHeadDim,
-            group - row0, lane, qf);
-        LB_STAMP(5);
+        // the rows this warp reads: [row0, min(group, row0 + 16)) of the head's group
+        const long long q_row = (long long)request * a.qh + (long long)kv_head * group + row0;
+        const int q_rows = in_bounds(q_row, (long long)a.batch * a.qh, a.status, kSiteQuery,
+                                     max(0, min(16, group - row0)))
+                               ? group - row0
+                               : 0;
+        load_query_fragments(a.query + (size_t)q_row * kHeadDim, q_rows, lane, qf);
 
         // my pages are page_slot0, page_slot0 + pps, ... of the chunk; stage and phase are
         // carried as counters (no division in the loop)
@@ -286,7 +294,6 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
                 if (lane == 0) flags[1] = 1;
                 break;
             }
-            if (it == 0) LB_STAMP(6);
             uint8_t *k_tile = ring + stage * stage_bytes + tile_offset;
             const bool wrote = attend_page(k_tile, k_tile + slot_bytes / 2, min(kPage, tokens_left),
                                            qf, a.scale_log2, lane, st);
@@ -302,12 +309,10 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
             }
         }
         st.finish_rows();
-        LB_STAMP(7);
     }
 
     // ---- join: every TMA write has been consumed or abandoned; the ring becomes scratch ---------
     __syncthreads();
-    LB_STAMP(8);
     const bool timed_out = flags[1] != 0;
     const bool invalid_page = flags[0] != 0;
     if (timed_out) {
@@ -363,7 +368,6 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         }
     }
 
-    LB_STAMP(9);
     if (kCluster) {
         // every CTA leaves the state of its chunk in its own shared memory (beyond the scratch of
         // the slot merge, which other warps may still be reading) ...
@@ -402,7 +406,9 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
                                            peer_local.lse[p] + out_row);
                 } else if (ok) {
                     const long long state = (long long)request * a.qh + head;
-                    publish_merged(top, norm, acc, lane, a.output + state * kHeadDim, a.lse + state);
+                    if (in_bounds(state, (long long)a.batch * a.qh, a.status, kSiteOutput))
+                        publish_merged(top, norm, acc, lane, a.output + state * kHeadDim,
+                                       a.lse + state);
                 }
             }
         }
@@ -430,13 +436,14 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         const size_t state = (size_t)request * a.qh + (size_t)kv_head * group + g;
         if (a.partitions == 1) {
             if (invalid_page) continue; // the request keeps its previous output
-            write_final_row(a.output + state * kHeadDim, a.lse + state, lane, half, st);
+            if (in_bounds((long long)state, (long long)a.batch * a.qh, a.status, kSiteOutput))
+                write_final_row(a.output + state * kHeadDim, a.lse + state, lane, half, st);
         } else {
-            write_state_row(a.workspace + (state * a.partitions + part) * kStateWidth, lane, half,
-                            st, invalid_page);
+            const size_t at = (state * a.partitions + part) * kStateWidth;
+            if (in_bounds((long long)at, a.workspace_numel, a.status, kSiteWorkspace, kStateWidth))
+                write_state_row(a.workspace + at, lane, half, st, invalid_page);
         }
     }
-    LB_STAMP(10);
 }
 
 // kGather: the instantiation for plans that gather their output (the other one carries none of
@@ -462,10 +469,14 @@ __device__ __forceinline__ void split_merge_warp(const float *__restrict__ works
                                                  const int32_t *indptr, const int32_t *last,
                                                  int batch, int qh, int partitions,
                                                  int indices_min, int indices_len,
-                                                 const PeerOut &peer) {
+                                                 const PeerOut &peer, long long workspace_numel,
+                                                 int32_t *status) {
     const int lane = threadIdx.x & 31;
     const int state = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (state >= batch * qh) return;
+    if (!in_bounds((long long)(state + 1) * partitions * kStateWidth - 1, workspace_numel, status,
+                   kSiteWorkspace))
+        return;
     const int request = state / qh;
     dependent_launch_wait(); // the partial states are complete and visible
     // the guard's loads and the state loads travel together; the verdict is used at the end
@@ -486,7 +497,8 @@ __device__ __forceinline__ void split_merge_warp(const float *__restrict__ works
 __global__ void __launch_bounds__(128)
 split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                    const int32_t *indptr, const int32_t *last, int batch, int qh, int partitions,
-                   int indices_min, int indices_len, const PeerOut peer, const PeerSignal signal) {
+                   int indices_min, int indices_len, const PeerOut peer, const PeerSignal signal,
+                   long long workspace_numel, int32_t *status) {
     dependent_launch_release();
     MergeSignalPrefetch handshake;
     if (signal.world != 0) {
@@ -494,7 +506,7 @@ split_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, f
         handshake.fetch(signal);
     }
     split_merge_warp(workspace, output, lse, indptr, last, batch, qh, partitions, indices_min,
-                     indices_len, peer);
+                     indices_len, peer, workspace_numel, status);
     handshake.finish(signal);
 }
 
@@ -543,6 +555,7 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     args.partitions = launch.partitions;
     args.stages = launch.stages;
     args.scale_log2 = launch.scale_log2;
+    args.workspace_numel = launch.workspace_numel;
     args.pair = launch.pages_per_step == 2 ? 1 : 0;
     args.skip_page = launch.test_skip_page;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
@@ -575,7 +588,7 @@ int launch_split_merge(const MergeLaunch &launch, void *stream) {
                             launch.workspace, static_cast<__nv_bfloat16 *>(launch.output),
                             launch.lse, launch.indptr, launch.last, launch.batch, launch.qh,
                             launch.partitions, launch.indices_min, launch.indices_len, launch.peer,
-                            launch.signal);
+                            launch.signal, launch.workspace_numel, launch.status);
 }
 
 long long default_wait_cycles() { return kWaitCycles; }

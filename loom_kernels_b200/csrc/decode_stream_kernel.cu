@@ -42,6 +42,7 @@ struct StreamArgs {
     int32_t hc, pps, mt, qb, stages, workers;
     int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
     int32_t pair; // 1: a consumer warp takes two pages of its range per step
+    long long workspace_numel; // F32 elements bound as the workspace (checked builds)
     float scale_log2;
     long long wait_cycles; // limit of every bounded wait
     PeerOut peer;          // world == 0 unless the plan gathers its output
@@ -106,7 +107,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     // everything above ran beside the previous command; global memory is touched from here on
     dependent_launch_wait();
-    LB_STAMP(0);
     // a gathering plan: the peers' addresses, fetched now for the row stores (the barriers of the
     // prefix computation below come before any of them)
     if (kGather && warp == kComputeWarps - 1) {
@@ -126,7 +126,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         ptail[r] = t;
         prefix[r + 1] = ok ? e - s : 0;
     }
-    LB_STAMP(1);
     __syncthreads();
     if (warp == 0) {
         // inclusive scan of prefix[1..batch] by one warp: per-lane chunks, then a warp scan
@@ -146,7 +145,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         }
     }
     __syncthreads();
-    LB_STAMP(2);
     const int total = prefix[a.batch];
     const int group = a.qh / a.kvh;
     const int head_blocks = a.kvh / a.hc;
@@ -157,8 +155,10 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         // the merge kernel reads the same prefix and the same cut
         int *out_prefix =
             reinterpret_cast<int *>(a.workspace + state_floats(a.workers, a.hc, a.rows));
-        for (int i = tid; i <= a.batch; i += blockDim.x) out_prefix[i] = prefix[i];
-        if (tid == 0) {
+        const bool room = in_bounds((long long)state_floats(a.workers, a.hc, a.rows) + a.batch + 5,
+                                    a.workspace_numel + 1, a.status, kSiteWorkspace);
+        for (int i = tid; room && i <= a.batch; i += blockDim.x) out_prefix[i] = prefix[i];
+        if (tid == 0 && room) {
             out_prefix[a.batch + 1] = (int)(cut.q & 0xffffffffll);
             out_prefix[a.batch + 2] = (int)(cut.q >> 32);
             out_prefix[a.batch + 3] = cut.r;
@@ -170,7 +170,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
 
     const int rows_per_block = 16 * a.mt;
     int issued = 0; // producer lanes: pages of my slot whose copies were issued
-    LB_STAMP(8);
 
     if (warp == kComputeWarps) {
         // ================= producer warp ==========================================================
@@ -208,14 +207,13 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const int wraps = (int)(pos / (unsigned)total);  // line is short
             const int y = (int)(pos - (unsigned)wraps * (unsigned)total);
             const int r = owner_of(prefix, a.batch, y);
-            id = a.indices[pstart[r] + (y - prefix[r])];
+            const int at = pstart[r] + (y - prefix[r]);
+            id = in_bounds(at, a.indices_len, a.status, kSiteIndices) ? a.indices[at] : -1;
             if (id < 0 || id >= a.max_pages) id = -1;
             hb = (h0 + wraps) / a.qb;
         };
         int win_id, win_hb, next_id = 0, next_hb = 0;
-        LB_STAMP(9);
         look_up(0, win_id, win_hb);
-        LB_STAMP(10);
         const int my_source = (my_slot & (a.pps - 1)) * window; // first lane of my worker's window
         const int my_count = __shfl_sync(0xffffffffu, count, my_source);
         const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
@@ -253,7 +251,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 ++issued;
             }
             if (j == 0) {
-                LB_STAMP(3);
                 // the second window is fetched once the first pages are on their way
                 if (window < longest) look_up(window, next_id, next_hb);
             }
@@ -297,9 +294,12 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const int kv_head = hb * a.hc + head_in_cta;
             const int row0 = qb * rows_per_block + mtile * 16;
             const int dest_request = kGather && a.peer.world != 0 ? a.peer.dest_rows[r] : 0;
-            load_query_fragments(
-                a.query + ((size_t)r * a.qh + (size_t)kv_head * group + row0) * kHeadDim,
-                group - row0, lane, qf);
+            const long long q_row = (long long)r * a.qh + (long long)kv_head * group + row0;
+            const int q_rows = in_bounds(q_row, (long long)a.batch * a.qh, a.status, kSiteQuery,
+                                         max(0, min(16, group - row0)))
+                                   ? group - row0
+                                   : 0;
+            load_query_fragments(a.query + (size_t)q_row * kHeadDim, q_rows, lane, qf);
             st.reset();
             bool bad = false;
             const int tail = ptail[r];
@@ -342,7 +342,6 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     live = false;
                     break;
                 }
-                if (p == 0 && first_segment) LB_STAMP(4);
                 bad |= bad_slot[stage * a.pps + my_slot] != 0;
                 uint8_t *k_tile = ring + stage * stage_bytes + tile_offset;
                 const bool wrote =
@@ -379,15 +378,18 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 if (complete) {
                     if (bad) continue; // the request keeps its previous output
                     const size_t state = (size_t)r * a.qh + (size_t)kv_head * group + g;
-                    write_final_row(a.output + state * kHeadDim, a.lse + state, lane, half, st);
+                    if (in_bounds((long long)state, (long long)a.batch * a.qh, a.status,
+                                  kSiteOutput))
+                        write_final_row(a.output + state * kHeadDim, a.lse + state, lane, half, st);
                 } else {
                     float *slot = a.workspace +
                                   (((size_t)w * 2 + which) * slot_rows +
                                    (size_t)head_in_cta * a.rows + row) * kStateWidth;
-                    write_state_row(slot, lane, half, st, bad);
+                    if (in_bounds(slot - a.workspace, a.workspace_numel, a.status, kSiteWorkspace,
+                                  kStateWidth))
+                        write_state_row(slot, lane, half, st, bad);
                 }
             }
-            if (first_segment) LB_STAMP(5);
             first_segment = false;
             remaining -= seg_pages;
             y += seg_pages;
@@ -397,9 +399,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             }
         }
     }
-    LB_STAMP(6);
     __syncthreads();
-    LB_STAMP(7);
     if (*timeout_flag != 0) {
         // a wait ran out: the copies already on their way are waited for (bounded), so that none
         // lands in shared memory after this CTA has gone
@@ -421,7 +421,8 @@ template <int kWarps>
 __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ workspace,
                                                     __nv_bfloat16 *output, float *lse, int batch,
                                                     int qh, int kvh, int hc, int mt, int qblocks,
-                                                    int workers, int rows, const PeerOut &peer) {
+                                                    int workers, int rows, const PeerOut &peer,
+                                                    long long workspace_numel, int32_t *status) {
     const int lane = threadIdx.x & 31;
     const int part = kWarps == 1 ? 0 : (int)(threadIdx.x >> 5);
     const int state = kWarps == 1 ? blockIdx.x * 4 + (threadIdx.x >> 5) : blockIdx.x;
@@ -452,6 +453,10 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
     const size_t slot_stride = (size_t)hc * rows * kStateWidth;
     const float *base = workspace + (size_t)w0 * 2 * slot_stride +
                         ((size_t)head_in_cta * rows + row) * kStateWidth;
+    // (the checked build: the last state this item reads lies inside the bound workspace)
+    if (!in_bounds((base - workspace) + (long long)((size_t)(w1 - w0) * 2 + 1) * slot_stride,
+                   workspace_numel, status, kSiteWorkspace, kStateWidth))
+        return;
     auto state_of = [&](int i) -> const float * {
         return base + ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
     };
@@ -474,7 +479,8 @@ template <int kWarps>
 __global__ void __launch_bounds__(128, kWarps == 1 ? 8 : 1)
 balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
-                      int rows, const PeerOut peer, const PeerSignal signal) {
+                      int rows, const PeerOut peer, const PeerSignal signal,
+                      long long workspace_numel, int32_t *status) {
     dependent_launch_release();
     MergeSignalPrefetch handshake;
     if (signal.world != 0) {
@@ -482,7 +488,7 @@ balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output
         handshake.fetch(signal);
     }
     balanced_merge_warp<kWarps>(workspace, output, lse, batch, qh, kvh, hc, mt, qblocks, workers,
-                                rows, peer);
+                                rows, peer, workspace_numel, status);
     handshake.finish(signal);
 }
 
@@ -532,6 +538,7 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     args.workers = (int32_t)launch.grid * launch.pages_per_stage;
     args.rows = balanced_state_rows(launch);
     args.pair = launch.pages_per_step == 2 ? 1 : 0;
+    args.workspace_numel = launch.workspace_numel;
     args.scale_log2 = launch.scale_log2;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
     args.peer = launch.peer;
@@ -555,13 +562,15 @@ int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t bl
                                 launch.batch, launch.qh, launch.kvh, launch.heads_per_cta,
                                 launch.q_tiles, launch.q_blocks,
                                 (int)launch.grid * launch.pages_per_stage,
-                                balanced_state_rows(launch), launch.peer, launch.signal);
+                                balanced_state_rows(launch), launch.peer, launch.signal,
+                                launch.workspace_numel, launch.status);
     return launch_dependent(balanced_merge_kernel<1>, grid, block, 0, stream,
                             (const float *)launch.workspace,
                             static_cast<__nv_bfloat16 *>(launch.output), launch.lse, launch.batch,
                             launch.qh, launch.kvh, launch.heads_per_cta, launch.q_tiles,
                             launch.q_blocks, (int)launch.grid * launch.pages_per_stage,
-                            balanced_state_rows(launch), launch.peer, launch.signal);
+                            balanced_state_rows(launch), launch.peer, launch.signal,
+                                launch.workspace_numel, launch.status);
 }
 
 } // namespace lb

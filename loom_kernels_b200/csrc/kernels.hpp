@@ -55,6 +55,7 @@ struct DecodeLaunch {
     float scale_log2;
     uint32_t grid, block, shared_bytes;
     long long wait_cycles;  // limit of every bounded wait of the kernel, in SM clock cycles
+    long long workspace_numel; // F32 elements bound as the workspace (the checked build's bound)
     int32_t test_skip_page; // tests of the give-up path: 1 + the page of a CTA's chunk whose
                             // loads the producer leaves out (0 = none)
     PeerOut peer;           // zeroed unless the plan gathers its output
@@ -71,6 +72,8 @@ struct MergeLaunch {
     uint32_t grid, block;
     PeerOut peer;
     PeerSignal signal;
+    long long workspace_numel; // F32 elements of `workspace` (the checked build's bound)
+    int32_t *status;           // optional device status word
 };
 
 // One fused RoPE + paged append launch.
@@ -86,6 +89,8 @@ struct AppendLaunch {
     // the CTAs of the validation kernel (1, or 1 token CTA + page-table scanners)
     int32_t *workspace;
     uint32_t validate_grid;
+    int32_t workspace_numel; // I32 elements of `workspace` (the checked build's bound)
+    int32_t *status;         // optional device status word (written by the checked build only)
 };
 
 // Each returns a CUDA error code (0 = success).

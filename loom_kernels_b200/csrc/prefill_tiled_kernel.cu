@@ -59,7 +59,6 @@ constexpr int kThreads = 192;
 constexpr uint32_t kTmemColumns = 256;         // 64 (S) + 2 x 32 (P, double-buffered) + 128 (O)
 constexpr uint32_t kTmemS = 0, kTmemP = 64, kTmemO = 128;
 constexpr float kRescaleThreshold = 8.0f;      // log2 domain: P stays below 2^8
-constexpr int kProbeBlock = 20;                // the block a profiling build stamps (LB_STAMP)
 
 // shared-memory map (offsets from the 1024-byte aligned base of dynamic shared memory)
 constexpr int kOffQ = 0;
@@ -262,7 +261,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 if (lane == 0) misc[2] = 1;
                 break;
             }
-            if (j == kProbeBlock) LB_STAMP(9);
             load_v(j, v_id);
             if (j + 2 < blocks) {
                 ok = mbar_wait(bars + (kBarKEmpty + stage) * 8, (j >> 1) & 1); // S(j) has completed
@@ -270,7 +268,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                     if (lane == 0) misc[2] = 1;
                     break;
                 }
-                if (j + 2 == kProbeBlock) LB_STAMP(8);
                 load_k(j + 2, k_id);
             }
             if ((((j + 1) * kBlockPages) >> 5) != first_window) { // the values enter the next window
@@ -304,7 +301,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             ok = mbar_wait(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
             if (!ok) return false;
             tc_fence_after();
-            if (i == kProbeBlock) LB_STAMP(7);
             const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
             if (elect_one()) {
 #pragma unroll
@@ -327,8 +323,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (ok && j > 0) ok = mbar_wait(bars + kBarSFree * 8, (j - 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            if (j == kProbeBlock) LB_STAMP(6);
-            if (j == kProbeBlock + 1) LB_STAMP(11);
             if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
@@ -358,13 +352,10 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             ok = mbar_wait(bars + kBarSFull * 8, j & 1);
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
-            if (j == kProbeBlock) LB_STAMP(0);
-            if (j == kProbeBlock + 1) LB_STAMP(10);
             float s[kBlockTokens]; // raw dot products
             tmem_load64(tmem_s + lane_base, s);
             tc_fence_before();
             __syncwarp();
-            if (j == kProbeBlock) LB_STAMP(1);
             if (lane == 0) mbar_arrive(bars + kBarSFree * 8); // S may be overwritten by block j + 1
             // the row's causal limit inside this block; columns past it (which also covers stale
             // or garbage key rows) are masked.  Most blocks lie wholly below the limit.
@@ -384,8 +375,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             }
             // scale > 0; -inf stays -inf
             const float mx = fmaxf(fmaxf(chain[0], chain[1]), fmaxf(chain[2], chain[3])) * scale;
-            if (j == kProbeBlock) LB_STAMPV(2, mx);
-            if (j == kProbeBlock) LB_STAMP(3);
             // the exponent base follows the maximum lazily: P <= 2^8 keeps BF16 P and the F32
             // normaliser exact enough, and most blocks skip the TMEM round trip of O
             const bool rescale = mx > m_used + kRescaleThreshold ||
@@ -432,7 +421,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             tmem_store_wait();
             const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
             l += total.x + total.y;
-            if (j == kProbeBlock) LB_STAMPV(4, l);
             // rows of the request's last page past its length may hold anything (0 * NaN): zero
             // them in the V block before the MMA reads it
             const int last_page = num_pages - 1;
@@ -452,7 +440,6 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bars + (kBarPFull + (j & 1)) * 8);
-            if (j == kProbeBlock) LB_STAMP(5);
         }
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) misc[2] = 1;

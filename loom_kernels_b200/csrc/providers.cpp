@@ -37,6 +37,7 @@ struct lb_paged_decode_plan {
 struct lb_rope_provider {
     int device = 0, sm_count = 0;
     size_t smem_optin = 0;
+    int32_t *status = nullptr; // device word; only the checked (bounds) build ever writes it
 };
 
 struct lb_rope_append_plan {
@@ -50,6 +51,7 @@ struct lb_rope_append_plan {
     uint32_t validate_grid = 0;
     size_t workspace_numel = 0;
     bool indices_capacity = false; // page_indices may be bound longer than the table in use
+    int32_t *status = nullptr;
 };
 
 struct lb_state_merge_plan {
@@ -368,6 +370,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     launch.block = c.block;
     launch.shared_bytes = c.shared_bytes;
     launch.wait_cycles = plan->wait_cycles;
+    launch.workspace_numel = split ? (long long)op[8].numel : 0;
     launch.test_skip_page = plan->test_skip_page;
     PeerOut peer;
     PeerSignal signal;
@@ -415,6 +418,8 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     memset(&merge, 0, sizeof(merge));
     merge.peer = peer;
     merge.signal = signal;
+    merge.workspace_numel = launch.workspace_numel;
+    merge.status = plan->status;
     merge.workspace = (const float *)merge_op[0].ptr;
     merge.output = merge_op[1].ptr;
     merge.lse = (float *)merge_op[2].ptr;
@@ -477,6 +482,7 @@ lb_status lb_state_merge_enqueue(const lb_state_merge_plan *plan, lb_scope *scop
     if ((rc = require_alignment("O", op[1].ptr, 8))) return rc;
     MergeLaunch merge;
     memset(&merge, 0, sizeof(merge));
+    merge.workspace_numel = (long long)op[0].numel;
     merge.workspace = (const float *)op[0].ptr;
     merge.output = op[1].ptr;
     merge.lse = (float *)op[2].ptr;
@@ -510,11 +516,16 @@ lb_status lb_rope_provider_load(int device, lb_rope_provider **out) {
         inverse_frequency[pair] = powf(10000.0f, -exponent) / 1.0f;
     }
     const size_t hash_bytes = 2 * lb_append_extended_max_tokens() * sizeof(int);
+    int32_t *status = nullptr;
     const int error = driver().configure(device, [&]() -> int {
-        return configure_append_kernels(hash_bytes, inverse_frequency);
+        int e = configure_append_kernels(hash_bytes, inverse_frequency);
+        if (e) return e;
+        if ((e = cudaMalloc((void **)&status, 64))) return e;
+        return cudaMemset(status, 0, 64);
     });
     if (error) return fail(LB_DRIVER, "provider_load", error);
     lb_rope_provider *provider = new lb_rope_provider();
+    provider->status = status;
     provider->device = device;
     provider->sm_count = sm_count;
     provider->smem_optin = smem;
@@ -522,7 +533,27 @@ lb_status lb_rope_provider_load(int device, lb_rope_provider **out) {
     return LB_OK;
 }
 
-void lb_rope_provider_destroy(lb_rope_provider *provider) { delete provider; }
+void lb_rope_provider_destroy(lb_rope_provider *provider) {
+    if (!provider) return;
+    if (provider->status) {
+        int32_t *status = provider->status;
+        driver().configure(provider->device, [&]() -> int { return cudaFree(status); });
+    }
+    delete provider;
+}
+
+lb_status lb_rope_provider_device_status(const lb_rope_provider *provider, int32_t *status) {
+    if (!provider || !status) return fail(LB_INVALID_ARGUMENT, "provider");
+    *status = 0;
+    if (!provider->status) return LB_OK;
+    const int error = driver().configure(provider->device, [&]() -> int {
+        int e = cudaMemcpy(status, provider->status, sizeof(int32_t), cudaMemcpyDeviceToHost);
+        if (e) return e;
+        return cudaMemset(provider->status, 0, sizeof(int32_t));
+    });
+    if (error) return fail(LB_DRIVER, "device_status", error);
+    return LB_OK;
+}
 
 static lb_status make_append_plan(const lb_rope_provider *provider, const lb_paged_spec &spec,
                                   bool explicit_tokens, size_t tokens, bool extended,
@@ -543,6 +574,7 @@ static lb_status make_append_plan(const lb_rope_provider *provider, const lb_pag
     plan->explicit_tokens = explicit_tokens;
     plan->tokens = tokens;
     plan->device = provider->device;
+    plan->status = provider->status;
     uint32_t hash_slots = 128;
     while (hash_slots < 2 * tokens) hash_slots *= 2;
     plan->hash_slots = hash_slots;
@@ -731,6 +763,7 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     launch.grid = plan->grid;
     launch.block = plan->block;
     launch.shared_bytes = plan->shared_bytes;
+    launch.status = plan->status;
     void *stream = scope->queue->stream;
     if (!plan->extended)
         return submit_launch(*scope, [&]() { return launch_rope_append(launch, stream); });
@@ -742,6 +775,7 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     if ((rc = resolve(*scope, ws_request, 1, ws))) return rc;
     if ((rc = require_exact_len("workspace", ws[0].numel, plan->workspace_numel))) return rc;
     launch.workspace = (int32_t *)ws[0].ptr;
+    launch.workspace_numel = (int32_t)ws[0].numel;
     launch.validate_grid = plan->validate_grid;
     if ((rc = submit_launch(*scope, [&]() { return launch_append_validate(launch, stream); })))
         return rc;

@@ -152,6 +152,7 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     launch.lse = lse;
     launch.workspace = setup.scratch;
     launch.status = setup.status;
+    launch.workspace_numel = (long long)c.workspace_numel;
     launch.batch = (int32_t)checked.batch_size;
     launch.max_pages = (int32_t)checked.max_num_pages;
     launch.qh = (int32_t)checked.num_query_heads;
@@ -174,6 +175,8 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     MergeLaunch merge;
     memset(&merge, 0, sizeof(merge));
     merge.workspace = setup.scratch;
+    merge.workspace_numel = (long long)c.workspace_numel;
+    merge.status = setup.status;
     merge.output = output;
     merge.lse = lse;
     merge.indptr = page_indptr;

@@ -12,6 +12,13 @@ fixed-address Graph replay including its completion event (graph/mod.rs:301-323)
 Working sets smaller than L2 (C1, C2, the gate shapes) are measured twice: "warm" re-runs one
 copy, "cold" rotates over enough copies of the pools to exceed the 126 MB L2.
 Prints one JSON object per case (JSONL), like crates/loom-infer-validation/src/support/benchmark.rs.
+
+The reference harness is configured through the environment
+(crates/loom-infer-validation/src/benchmarks/matched.rs:47-59,116-124,1245) and the same names
+work here: LOOM_BENCH_WARMUP (warm-up launches), LOOM_BENCH_LAUNCHES (launches per sample),
+LOOM_BENCH_SAMPLES, LOOM_BENCH_OPERATORS (comma-separated cases, as --cases), LOOM_BENCH_RUN_LABEL
+and LOOM_SOURCE_COMMIT (a full 40-character commit SHA; when unset the commit of the working tree
+is asked of git).  Every record carries provider_commit and run_label.
 """
 from __future__ import annotations
 
@@ -139,7 +146,31 @@ class AppendCase:
             plan.enqueue_into(scope, per_pool[call % self.copies])
 
 
+def env_int(name):
+    value = os.environ.get(name)
+    return int(value) if value else None
+
+
+def run_identity():
+    """provider_commit and run_label of BenchmarkRecord (support/benchmark.rs:5-32)."""
+    commit = os.environ.get("LOOM_SOURCE_COMMIT", "")
+    if commit and (len(commit) != 40 or any(c not in "0123456789abcdefABCDEF" for c in commit)):
+        raise SystemExit("LOOM_SOURCE_COMMIT must be a full 40-character Git commit SHA")
+    if not commit:
+        import subprocess
+        try:
+            commit = subprocess.run(["git", "rev-parse", "HEAD"], cwd=ROOT, capture_output=True,
+                                    text=True, timeout=10).stdout.strip() or "unknown"
+        except OSError:
+            commit = "unknown"
+    return commit, os.environ.get("LOOM_BENCH_RUN_LABEL", "unlabeled")
+
+
 def measure(case, name, calls, samples, warmup, device, extra=None):
+    # the reference's environment overrides, when set, apply to every case
+    calls = env_int("LOOM_BENCH_LAUNCHES") or calls
+    samples = env_int("LOOM_BENCH_SAMPLES") or samples
+    warmup = env_int("LOOM_BENCH_WARMUP") if env_int("LOOM_BENCH_WARMUP") is not None else warmup
     stream = torch.cuda.Stream(device=device)
     queue = lk.CommandQueue(stream, calls * case.commands() + 1)
     bindings = queue.bindings(case.slots())
@@ -201,8 +232,11 @@ def measure(case, name, calls, samples, warmup, device, extra=None):
         graph_batch_us = f"unavailable: {error.variant}"
 
     us = float(np.median(samples_us))
+    commit, label = run_identity()
     record = {
-        "provider": "loom_b200", "measurement": "eager_stream_batch_cuda_event", "case": name,
+        "schema_version": 1, "provider": "loom_b200", "provider_commit": commit,
+        "run_label": label, "measurement": "eager_stream_batch_cuda_event", "case": name,
+        "dtype": "bf16", "layout": "NHD",
         "warmup_launches": warmup, "launches_per_sample": calls, "commands_per_call": case.commands(),
         "us_per_call": round(us, 3), "p10_us": round(float(np.percentile(samples_us, 10)), 3),
         "p90_us": round(float(np.percentile(samples_us, 90)), 3), "graph_us": graph_us,
@@ -242,7 +276,7 @@ def main():
     torch.cuda.set_device(device)
     decode = lk.DecodeProvider.load(args.device)
     rope = lk.RopeProvider.load(args.device)
-    cases = set(args.cases.split(","))
+    cases = set((os.environ.get("LOOM_BENCH_OPERATORS") or args.cases).split(","))
 
     if "gates" in cases:
         # the three shapes the reference published H20 numbers for (3.100 / 5.798 / 5.854 us)

@@ -19,3 +19,4 @@ def oracle():
 
     o.build()
     return o
+

@@ -35,6 +35,7 @@ class AppendRun:
     def __init__(self, provider, spec, q, k, v, indptr, indices, last, k_pages, v_pages,
                  batch_indices=None, positions=None, max_commands=1):
         self.spec = spec
+        self.provider = provider
         self.explicit = batch_indices is not None
         self.plan = (provider.plan_bf16_paged_append_tokens(spec) if self.explicit
                      else provider.plan_bf16_paged_append(spec))
@@ -82,6 +83,8 @@ class AppendRun:
         completion = scope.finish()
         self.submitted = completion.submitted()
         b = completion.wait()
+        # (only the checked build of the library writes this word: an index outside its operand)
+        assert self.provider.device_status() == 0
         return (H.host_bits(b.take_read_write(self.h_q)), H.host_bits(b.take_read_write(self.h_k)),
                 H.host_bits(b.take_read_write(self.h_v)))
 
