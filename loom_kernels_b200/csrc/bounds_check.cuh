@@ -39,7 +39,8 @@ enum BoundsSite : int {
 __device__ __forceinline__ bool in_bounds(long long index, long long bound, int32_t *status,
                                           int site, long long count = 1) {
     if (!kCheckBounds) return true;
-    if (index >= 0 && count >= 0 && index + count <= bound) return true;
+    if (count == 0) return true; // nothing is accessed
+    if (index >= 0 && count > 0 && index + count <= bound) return true;
     if (status != nullptr) atomicExch(status, 0x1000 | site);
     return false;
 }

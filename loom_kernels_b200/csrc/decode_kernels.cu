@@ -242,14 +242,12 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         if (kGather && a.peer.world != 0) dest_request = a.peer.dest_rows[request];
         const int kv_head = hb * a.hc + head_in_cta;
         const int row0 = qb * rows_per_block + mtile * 16;
-        uint32_t qf[8][4];
         // the rows this warp reads: [row0, min(group, row0 + 16)) of the head's group
         const long long q_row = (long long)request * a.qh + (long long)kv_head * group + row0;
         const int q_rows = in_bounds(q_row, (long long)a.batch * a.qh, a.status, kSiteQuery,
                                      max(0, min(16, group - row0)))
                                ? group - row0
                                : 0;
-        load_query_fragments(a.query + (size_t)q_row * kHeadDim, q_rows, lane, qf);
 
         // my pages are page_slot0, page_slot0 + pps, ... of the chunk; stage and phase are
         // carried as counters (no division in the loop)
@@ -259,6 +257,8 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         const uint32_t my_full = full0 + page_slot0 * 8, my_empty = empty0 + page_slot0 * 8;
         int stage = 0;
         uint32_t phase = 0;
+        uint32_t qf[8][4];
+        load_query_fragments(a.query + (size_t)q_row * kHeadDim, q_rows, lane, qf);
         int it = 0;
         if (a.pair) {
             // two pages of this slot per step: they sit in two consecutive stages of the ring
