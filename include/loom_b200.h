@@ -317,9 +317,9 @@ typedef struct lb_paged_decode_options {
     uint32_t test_skip_page; /* tests of that give-up path only: 1 + the index, within every CTA's
                                 page chunk, of a page whose copies the kernel leaves out; 0 = none.
                                 Direct and split-K plans */
-    uint32_t pages_per_step; /* pages a consumer warp takes per step of its loop: 0 = plan-time
-                                heuristic, 1, or 2 (one joint softmax update over 32 tokens; the
-                                choice for query groups wider than 16 rows) */
+    uint32_t pages_per_step; /* pages a consumer warp takes per step of its loop: 0 or 1 = one,
+                                2 = two (one joint softmax update over 32 tokens, two stages
+                                of the ring at once); the plan never chooses 2 by itself */
     uint32_t cluster;        /* with partitions 2..8: 1 = LB_DECODE_CLUSTER_SPLIT instead of the
                                 two-command split-K */
     uint32_t reserved[3];

@@ -222,14 +222,13 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         }
     }
 
-    // Pages a consumer warp takes per step.  A query group wider than one 16-row MMA tile has two
-    // warps per page and, per page, a dependent chain (maximum, shuffles, exponentials) that the
-    // two warps per scheduler cannot hide: two pages per step halve the chain per token (ragged
-    // MQA 32/1: 0.69 -> see the measurement notes of the kernel).  Narrow groups stream at the HBM
-    // rate with one page per step and keep it.  Two pages occupy two stages of the ring at once.
+    // Pages a consumer warp takes per step: two halve the dependent chain (maximum, shuffles,
+    // exponentials) per token and occupy two stages of the ring at once.  The plan does not choose
+    // it: on the wide-group shape it was written for (ragged MQA 32/1) the producer's copies, not
+    // the consumers, bound the kernel, and it measured 117.6 against 114.4 us; a caller may pin it.
     uint32_t pages_per_step = options ? options->pages_per_step : 0;
     if (pages_per_step > 2) return fail(LB_LAUNCH_CONTRACT, "pages_per_step", pages_per_step);
-    if (pages_per_step == 0) pages_per_step = q_tiles >= 2 && stages >= 4 ? 2 : 1;
+    if (pages_per_step == 0) pages_per_step = 1;
     if (pages_per_step == 2 && stages < 3) pages_per_step = 1;
     out->pages_per_step = pages_per_step;
     out->algorithm = algorithm;

@@ -65,7 +65,8 @@ __device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
 
 // kGather: the instantiation for plans that gather their output (the other one carries none of
 // its registers or shared memory).
-template <bool kGather>
+// kPair: the instantiation whose consumer warps take two pages per step.
+template <bool kGather, bool kPair>
 __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
@@ -305,7 +306,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             const int tail = ptail[r];
             const int last_in_segment = num_pages - 1 - first_page; // p of the request's last page
             int p = 0;
-            if (a.pair) {
+            if (kPair) {
                 // two pages of the segment per step: consecutive stages of this worker's slot
                 for (; p + 1 < seg_pages; p += 2) {
                     const int stage_b = stage + 1 == a.stages ? 0 : stage + 1;
@@ -499,19 +500,23 @@ int balanced_state_rows(const DecodeLaunch &launch) {
 
 } // namespace
 
-int configure_stream_kernels(size_t max_dynamic_shared) {
+template <bool kGather, bool kPair>
+static int configure_balanced(size_t max_dynamic_shared) {
     // the opt-in limit covers static and dynamic shared memory together
     cudaFuncAttributes attributes;
-    int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<false>);
+    const int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<kGather, kPair>);
     if (rc) return rc;
-    rc = cudaFuncSetAttribute(balanced_decode_kernel<false>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              (int)(max_dynamic_shared - attributes.sharedSizeBytes));
-    if (rc) return rc;
-    if ((rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<true>))) return rc;
-    return cudaFuncSetAttribute(balanced_decode_kernel<true>,
+    return cudaFuncSetAttribute(balanced_decode_kernel<kGather, kPair>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)(max_dynamic_shared - attributes.sharedSizeBytes));
+}
+
+int configure_stream_kernels(size_t max_dynamic_shared) {
+    int rc = configure_balanced<false, false>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<false, true>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<true, false>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<true, true>(max_dynamic_shared);
+    return rc;
 }
 
 int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
@@ -545,11 +550,12 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    if (launch.peer.world != 0)
-        return launch_dependent(balanced_decode_kernel<true>, launch.grid, launch.block,
-                                launch.shared_bytes, stream, k_map, v_map, args);
-    return launch_dependent(balanced_decode_kernel<false>, launch.grid, launch.block,
-                            launch.shared_bytes, stream, k_map, v_map, args);
+    const bool gather = launch.peer.world != 0, pair = args.pair != 0;
+    auto kernel = gather ? (pair ? balanced_decode_kernel<true, true> : balanced_decode_kernel<true, false>)
+                         : (pair ? balanced_decode_kernel<false, true>
+                                 : balanced_decode_kernel<false, false>);
+    return launch_dependent(kernel, launch.grid, launch.block, launch.shared_bytes, stream, k_map,
+                            v_map, args);
 }
 
 int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block,
