@@ -315,14 +315,12 @@ typedef struct lb_paged_decode_options {
                                two seconds.  When it runs out the kernel writes nothing more,
                                records a status word (lb_decode_provider_device_status) and returns */
     uint32_t test_skip_page; /* tests of that give-up path only: 1 + the index, within every CTA's
-                                page chunk, of a page whose copies the kernel leaves out; 0 = none.
-                                Direct and split-K plans */
-    uint32_t pages_per_step; /* pages a consumer warp takes per step of its loop: 0 or 1 = one,
-                                2 = two (one joint softmax update over 32 tokens, two stages
-                                of the ring at once); the plan never chooses 2 by itself */
+                                page chunk, of a page whose barrier expects 16 bytes more than its
+                                copies deliver (the page never becomes ready); 0 = none.  Direct
+                                and split-K plans, a page of the ring's first round */
     uint32_t cluster;        /* with partitions 2..8: 1 = LB_DECODE_CLUSTER_SPLIT instead of the
                                 two-command split-K */
-    uint32_t reserved[3];
+    uint32_t reserved[4];    /* zero */
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
@@ -338,8 +336,7 @@ typedef struct lb_paged_decode_plan_info {
     uint32_t commands;       /* 1 direct or cluster split, 2 split or balanced (partials + merge) */
     size_t workspace_numel;  /* F32 elements the caller must bind (0 for direct) */
     size_t workspace_bytes;
-    uint32_t pages_per_step; /* 1 or 2, see lb_paged_decode_options */
-    uint32_t reserved;
+    uint32_t reserved[2];
 } lb_paged_decode_plan_info;
 
 /* Bf16PagedBatchDecodeArgs, decode.rs:1451-1487, plus the split-K workspace

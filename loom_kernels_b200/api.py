@@ -533,7 +533,6 @@ class DecodeProvider:
                               heads_per_cta: int = 0, balanced: int = 0,
                               balanced_ctas: int = 0, indices_capacity: bool = False,
                               wait_limit_us: int = 0, test_skip_page: int = 0,
-                              pages_per_step: int = 0,
                               cluster: bool = False) -> "Bf16PagedBatchDecodePlan":
         """partitions: 0 heuristic, 1 direct, N split-K; balanced (with partitions 0): 0
         heuristic, 1 force the balanced algorithm, 2 never use it.  indices_capacity: the bound
@@ -545,7 +544,7 @@ class DecodeProvider:
                                      balanced=balanced, balanced_ctas=balanced_ctas,
                                      indices_capacity=1 if indices_capacity else 0,
                                      wait_limit_us=wait_limit_us, test_skip_page=test_skip_page,
-                                     pages_per_step=pages_per_step, cluster=1 if cluster else 0)
+                                     cluster=1 if cluster else 0)
         out = c_void_p()
         _check(_abi.load().lb_paged_decode_plan_create(self._ptr, byref(spec._raw),
                                                        byref(options), byref(out)))

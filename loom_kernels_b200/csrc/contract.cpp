@@ -226,11 +226,6 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     // exponentials) per token and occupy two stages of the ring at once.  The plan does not choose
     // it: on the wide-group shape it was written for (ragged MQA 32/1) the producer's copies, not
     // the consumers, bound the kernel, and it measured 117.6 against 114.4 us; a caller may pin it.
-    uint32_t pages_per_step = options ? options->pages_per_step : 0;
-    if (pages_per_step > 2) return fail(LB_LAUNCH_CONTRACT, "pages_per_step", pages_per_step);
-    if (pages_per_step == 0) pages_per_step = 1;
-    if (pages_per_step == 2 && stages < 3) pages_per_step = 1;
-    out->pages_per_step = pages_per_step;
     out->algorithm = algorithm;
     out->partitions = partitions;
     out->heads_per_cta = hc;
@@ -513,8 +508,7 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
                          : 2;
     info->workspace_numel = choice.workspace_numel;
     info->workspace_bytes = choice.workspace_numel * sizeof(float);
-    info->pages_per_step = choice.pages_per_step;
-    info->reserved = 0;
+    info->reserved[0] = info->reserved[1] = 0;
     return LB_OK;
 }
 

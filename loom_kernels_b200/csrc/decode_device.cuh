@@ -37,6 +37,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// Raises the byte count the current phase waits for, without arriving.
+__device__ __forceinline__ void mbar_expect_more(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -294,131 +299,6 @@ __device__ __forceinline__ bool attend_page(uint8_t *k_ptr, uint8_t *v_ptr, int 
         ldmatrix_x4_trans(addr, b0, b1, b2, b3);
         mma_bf16(st.acc[2 * j], pf, b0, b1);
         mma_bf16(st.acc[2 * j + 1], pf, b2, b3);
-    }
-    return partial;
-}
-
-// Two pages of one KV head in one step: S = Q [K_a; K_b]^T (16 x 32), ONE online-softmax update
-// over the 32 tokens, O += P_a V_a + P_b V_b.  The dependent part of a step -- row maximum, two
-// shuffle rounds, exponentials, the rescale decision -- is paid once for twice the tokens, and the
-// two pages' MMAs interleave, which is what a wide query group (two 16-row tiles per page, two
-// consumer warps per scheduler) needs to keep up with the page stream.  Page a is full; page b has
-// valid_b tokens (rows past them are zeroed in V and masked in S as in attend_page).  Returns
-// true when shared memory was written.
-__device__ __forceinline__ bool attend_page_pair(uint8_t *ka_ptr, uint8_t *va_ptr, uint8_t *kb_ptr,
-                                                 uint8_t *vb_ptr, int valid_b,
-                                                 const uint32_t (&qf)[8][4], float scale_log2,
-                                                 int lane, WarpState &st) {
-    const uint32_t ka = smem_u32(ka_ptr), va = smem_u32(va_ptr);
-    const uint32_t kb = smem_u32(kb_ptr), vb = smem_u32(vb_ptr);
-    const bool partial = valid_b < kPage;
-    if (partial) {
-        for (int i = lane; i < (kPage - valid_b) * 16; i += 32) {
-            const int row = valid_b + (i >> 4);
-            const int c = i & 15;
-            *reinterpret_cast<uint4 *>(vb_ptr + (c >> 3) * kBoxBytes + row * 128 + (c & 7) * 16) =
-                make_uint4(0, 0, 0, 0);
-        }
-        __syncwarp();
-    }
-    const int k_tok = ((lane >> 4) << 3) + (lane & 7);
-    const int k_hi = (lane >> 3) & 1;
-    const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7);
-    const int v_hi = lane >> 4;
-
-    // four chains (tokens 0-7 and 8-15 of each page), eight MMAs each
-    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-    float b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-        const int chunk = (kk << 1) + k_hi;
-        const uint32_t offset = k_tok * 128 + ((chunk ^ (k_tok & 7)) << 4);
-        uint32_t p0, p1, p2, p3, c0, c1, c2, c3;
-        ldmatrix_x4(ka + offset, p0, p1, p2, p3);
-        ldmatrix_x4(ka + offset + kBoxBytes, c0, c1, c2, c3);
-        mma_bf16(a0, qf[kk], p0, p1);
-        mma_bf16(a1, qf[kk], p2, p3);
-        uint32_t r0, r1, r2, r3, d0, d1, d2, d3;
-        ldmatrix_x4(kb + offset, r0, r1, r2, r3);
-        ldmatrix_x4(kb + offset + kBoxBytes, d0, d1, d2, d3);
-        mma_bf16(b0, qf[kk], r0, r1);
-        mma_bf16(b1, qf[kk], r2, r3);
-        mma_bf16(a0, qf[kk + 4], c0, c1);
-        mma_bf16(a1, qf[kk + 4], c2, c3);
-        mma_bf16(b0, qf[kk + 4], d0, d1);
-        mma_bf16(b1, qf[kk + 4], d2, d3);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        a0[i] *= scale_log2;
-        a1[i] *= scale_log2;
-        b0[i] *= scale_log2;
-        b1[i] *= scale_log2;
-    }
-    if (partial) {
-        const int t0 = (lane & 3) * 2;
-        if (t0 >= valid_b) { b0[0] = -INFINITY; b0[2] = -INFINITY; }
-        if (t0 + 1 >= valid_b) { b0[1] = -INFINITY; b0[3] = -INFINITY; }
-        if (t0 + 8 >= valid_b) { b1[0] = -INFINITY; b1[2] = -INFINITY; }
-        if (t0 + 9 >= valid_b) { b1[1] = -INFINITY; b1[3] = -INFINITY; }
-    }
-    // elements 0, 1 of a fragment belong to the lane's first row, 2, 3 to its second
-    float m0 = fmaxf(fmaxf(fmaxf(a0[0], a0[1]), fmaxf(a1[0], a1[1])),
-                     fmaxf(fmaxf(b0[0], b0[1]), fmaxf(b1[0], b1[1])));
-    float m1 = fmaxf(fmaxf(fmaxf(a0[2], a0[3]), fmaxf(a1[2], a1[3])),
-                     fmaxf(fmaxf(b0[2], b0[3]), fmaxf(b1[2], b1[3])));
-    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
-    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
-    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
-    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
-    const float new0 = fmaxf(st.row_max[0], m0), new1 = fmaxf(st.row_max[1], m1); // finite
-    const float alpha0 = fast_exp2(st.row_max[0] - new0), alpha1 = fast_exp2(st.row_max[1] - new1);
-    st.row_max[0] = new0;
-    st.row_max[1] = new1;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        a0[i] = fast_exp2(a0[i] - new0);
-        a1[i] = fast_exp2(a1[i] - new0);
-        b0[i] = fast_exp2(b0[i] - new0);
-        b1[i] = fast_exp2(b1[i] - new0);
-        a0[i + 2] = fast_exp2(a0[i + 2] - new1);
-        a1[i + 2] = fast_exp2(a1[i + 2] - new1);
-        b0[i + 2] = fast_exp2(b0[i + 2] - new1);
-        b1[i + 2] = fast_exp2(b1[i + 2] - new1);
-    }
-    st.row_sum[0] = st.row_sum[0] * alpha0 +
-                    (((a0[0] + a0[1]) + (a1[0] + a1[1])) + ((b0[0] + b0[1]) + (b1[0] + b1[1])));
-    st.row_sum[1] = st.row_sum[1] * alpha1 +
-                    (((a0[2] + a0[3]) + (a1[2] + a1[3])) + ((b0[2] + b0[3]) + (b1[2] + b1[3])));
-    uint32_t pa[4], pb[4];
-    pa[0] = pack_bf16(a0[0], a0[1]);
-    pa[1] = pack_bf16(a0[2], a0[3]);
-    pa[2] = pack_bf16(a1[0], a1[1]);
-    pa[3] = pack_bf16(a1[2], a1[3]);
-    pb[0] = pack_bf16(b0[0], b0[1]);
-    pb[1] = pack_bf16(b0[2], b0[3]);
-    pb[2] = pack_bf16(b1[0], b1[1]);
-    pb[3] = pack_bf16(b1[2], b1[3]);
-    if (__any_sync(0xffffffffu, alpha0 != 1.0f || alpha1 != 1.0f)) {
-#pragma unroll
-        for (int nt = 0; nt < 16; ++nt) {
-            st.acc[nt][0] *= alpha0;
-            st.acc[nt][1] *= alpha0;
-            st.acc[nt][2] *= alpha1;
-            st.acc[nt][3] *= alpha1;
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int chunk = ((2 * j) & 7) + v_hi;
-        const uint32_t offset = (j >> 2) * kBoxBytes + v_tok * 128 + ((chunk ^ (v_tok & 7)) << 4);
-        uint32_t x0, x1, x2, x3, y0, y1, y2, y3;
-        ldmatrix_x4_trans(va + offset, x0, x1, x2, x3);
-        ldmatrix_x4_trans(vb + offset, y0, y1, y2, y3);
-        mma_bf16(st.acc[2 * j], pa, x0, x1);
-        mma_bf16(st.acc[2 * j + 1], pa, x2, x3);
-        mma_bf16(st.acc[2 * j], pb, y0, y1);
-        mma_bf16(st.acc[2 * j + 1], pb, y2, y3);
     }
     return partial;
 }

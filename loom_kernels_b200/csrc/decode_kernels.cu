@@ -47,8 +47,7 @@ struct DecodeArgs {
     int32_t hc, pps, mt, qb, partitions, stages;
     float scale_log2;
     long long workspace_numel; // F32 elements bound as the workspace (checked builds)
-    int32_t pair;          // 1: a consumer warp takes two pages of its slot per step
-    int32_t skip_page;     // tests of the give-up path: 1 + the page whose loads are left out
+    int32_t skip_page;     // tests of the give-up path: 1 + the page whose bytes never all arrive
     long long wait_cycles; // limit of every bounded wait
     PeerOut peer;          // world == 0 unless the plan gathers its output
     PeerSignal signal;     // world == 0 unless this kernel is the last of a gathering command
@@ -95,6 +94,9 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         item /= a.partitions;
     }
     const int request = item;
+    // (a CTA past the batch leaves at once, unless the plan gathers: there every CTA of the grid
+    // is counted at the kernel's end)
+    if (!kGather && request >= a.batch) return;
 
     // barriers: one thread each, before the first touch of global memory
     if (tid < a.stages * a.pps) {
@@ -116,7 +118,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     // a gathering plan: the peers' addresses and the epoch, fetched now for the kernel's last
     // instructions (read after the join below, or after the barrier that ends the kernel)
     if (kGather && warp == kComputeWarps - 1) peer_prefetch(a.peer, a.signal, lane, peer_local);
-    if (request >= a.batch) return;
+    if (kGather && request >= a.batch) return;
     // The first 32 page ids of the table travel with the request's metadata: when the pages this
     // CTA starts with lie among them (small batches, short contexts) the producer has its ids
     // one round trip earlier.
@@ -159,7 +161,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     // consumer identity (declared here so the epilogue after the join can use it)
     WarpState st;
     int dest_request = 0; // gathering plans: the row of the gathered result this request owns
-    int issued = 0;       // producer lanes: pages of my slot whose copies were issued
+    int producer_trips = 0; // producer lanes: iterations of the page loop that issued copies
     const int unit = warp / a.mt;      // consumer: which (page slot, head) of each stage
     const int mtile = warp % a.mt;     // consumer: which 16-row tile of the group
     const int page_slot0 = unit / a.hc;
@@ -202,7 +204,14 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         int stage = 0;
         uint32_t phase = 0;    // parity of the ring round being filled
         bool recycled = false; // the ring has wrapped: a slot must be handed back before reuse
-        for (int it = 0; it < n_iter; ++it) {
+        // A test of the give-up path: the barrier of one page (of the ring's first round) expects
+        // 16 bytes more than its copies deliver, which is all a lost copy would look like -- the
+        // page's consumers wait for bytes that never arrive.
+        if (a.skip_page != 0 && lane_active && which == 0 && a.skip_page - 1 < cnt &&
+            (a.skip_page - 1) % a.pps == my_slot && (a.skip_page - 1) / a.pps < a.stages)
+            mbar_expect_more(my_full + ((a.skip_page - 1) / a.pps) * a.pps * 8, 16);
+        int it = 0;
+        for (; it < n_iter; ++it) {
             const int first = it * a.pps;
             if (it > 0 && (first & 31) == 0) {
                 window = window_next;
@@ -221,20 +230,18 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
             }
             if (has && which == 0) mbar_expect_tx(bar_full, slot_bytes);
             __syncwarp();
-            // (a test of the give-up path leaves one page's loads out: its consumers' wait for the
-            // expected bytes then runs out, which is all a lost copy would look like)
-            if (has && slot + 1 != a.skip_page)
+            if (has)
                 tma_load_3d(my_tile + stage * stage_bytes, map, 0,
                             in_bounds(page_id, a.max_pages, a.status, kSitePage) ? page_id * kPage
                                                                                 : 0,
                             z, bar_full);
-            if (has) ++issued;
             if (++stage == a.stages) {
                 stage = 0;
                 phase ^= 1;
                 recycled = true;
             }
         }
+        producer_trips = it;
         if (__any_sync(0xffffffffu, bad_page) && lane == 0) flags[0] = 1;
     } else {
         // ================= consumer warps ======================================================
@@ -259,36 +266,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         uint32_t phase = 0;
         uint32_t qf[8][4];
         load_query_fragments(a.query + (size_t)q_row * kHeadDim, q_rows, lane, qf);
-        int it = 0;
-        if (a.pair) {
-            // two pages of this slot per step: they sit in two consecutive stages of the ring
-            for (; it + 1 < my_pages; it += 2) {
-                const int stage_b = stage + 1 == a.stages ? 0 : stage + 1;
-                const uint32_t phase_b = stage_b == 0 ? phase ^ 1 : phase;
-                const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles) &&
-                                mbar_wait(my_full + stage_b * a.pps * 8, phase_b, a.wait_cycles);
-                if (__any_sync(0xffffffffu, !ok)) {
-                    if (lane == 0) flags[1] = 1;
-                    break;
-                }
-                uint8_t *tile_a = ring + stage * stage_bytes + tile_offset;
-                uint8_t *tile_b = ring + stage_b * stage_bytes + tile_offset;
-                const bool wrote = attend_page_pair(
-                    tile_a, tile_a + slot_bytes / 2, tile_b, tile_b + slot_bytes / 2,
-                    min(kPage, tokens_left - a.pps * kPage), qf, a.scale_log2, lane, st);
-                __syncwarp();
-                if (lane == 0) {
-                    if (wrote) fence_proxy_async();
-                    mbar_arrive(my_empty + stage * a.pps * 8);
-                    mbar_arrive(my_empty + stage_b * a.pps * 8);
-                }
-                tokens_left -= 2 * a.pps * kPage;
-                stage = stage_b + 1 == a.stages ? 0 : stage_b + 1;
-                phase = stage == 0 ? phase_b ^ 1 : phase_b;
-            }
-            if (it + 1 < my_pages) it = my_pages; // a wait ran out: nothing more is consumed
-        }
-        for (; it < my_pages; ++it) {
+        for (int it = 0; it < my_pages; ++it) {
             const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) flags[1] = 1;
@@ -318,9 +296,14 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     if (timed_out) {
         // nothing is published; the copies already on their way are waited for (bounded), so
         // that none lands in shared memory after this CTA has gone
-        if (warp == kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps)
-            drain_issued_copies(full0 + (lane >> 1) * 8, a.pps * 8, a.stages, issued,
+        if (warp == kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps) {
+            // pages of my slot whose copies were issued: one per trip of the producer loop while
+            // the slot still had pages of the chunk
+            const int slot = lane >> 1;
+            const int mine = cnt > slot ? (cnt - slot + a.pps - 1) / a.pps : 0;
+            drain_issued_copies(full0 + slot * 8, a.pps * 8, a.stages, min(producer_trips, mine),
                                 a.wait_cycles);
+        }
         __syncthreads();
         if (tid == 0 && a.status) atomicExch(a.status, 1);
         if (!kCluster) return; // (a cluster's CTAs still meet at its barriers: a poisoned state)
@@ -556,7 +539,6 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     args.stages = launch.stages;
     args.scale_log2 = launch.scale_log2;
     args.workspace_numel = launch.workspace_numel;
-    args.pair = launch.pages_per_step == 2 ? 1 : 0;
     args.skip_page = launch.test_skip_page;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
     args.peer = launch.peer;

@@ -41,7 +41,6 @@ struct StreamArgs {
     int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, stages, workers;
     int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
-    int32_t pair; // 1: a consumer warp takes two pages of its range per step
     long long workspace_numel; // F32 elements bound as the workspace (checked builds)
     float scale_log2;
     long long wait_cycles; // limit of every bounded wait
@@ -65,8 +64,7 @@ __device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
 
 // kGather: the instantiation for plans that gather their output (the other one carries none of
 // its registers or shared memory).
-// kPair: the instantiation whose consumer warps take two pages per step.
-template <bool kGather, bool kPair>
+template <bool kGather>
 __global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
 balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
@@ -305,38 +303,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
             bool bad = false;
             const int tail = ptail[r];
             const int last_in_segment = num_pages - 1 - first_page; // p of the request's last page
-            int p = 0;
-            if (kPair) {
-                // two pages of the segment per step: consecutive stages of this worker's slot
-                for (; p + 1 < seg_pages; p += 2) {
-                    const int stage_b = stage + 1 == a.stages ? 0 : stage + 1;
-                    const uint32_t phase_b = stage_b == 0 ? phase ^ 1 : phase;
-                    const bool ok =
-                        mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles) &&
-                        mbar_wait(my_full + stage_b * a.pps * 8, phase_b, a.wait_cycles);
-                    if (__any_sync(0xffffffffu, !ok)) {
-                        if (lane == 0) *timeout_flag = 1;
-                        live = false;
-                        break;
-                    }
-                    bad |= bad_slot[stage * a.pps + my_slot] != 0 ||
-                           bad_slot[stage_b * a.pps + my_slot] != 0;
-                    uint8_t *tile_a = ring + stage * stage_bytes + tile_offset;
-                    uint8_t *tile_b = ring + stage_b * stage_bytes + tile_offset;
-                    const bool wrote = attend_page_pair(
-                        tile_a, tile_a + slot_bytes / 2, tile_b, tile_b + slot_bytes / 2,
-                        p + 1 == last_in_segment ? tail : kPage, qf, a.scale_log2, lane, st);
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (wrote) fence_proxy_async();
-                        mbar_arrive(my_empty + stage * a.pps * 8);
-                        mbar_arrive(my_empty + stage_b * a.pps * 8);
-                    }
-                    stage = stage_b + 1 == a.stages ? 0 : stage_b + 1;
-                    phase = stage == 0 ? phase_b ^ 1 : phase_b;
-                }
-            }
-            for (; live && p < seg_pages; ++p) {
+            for (int p = 0; live && p < seg_pages; ++p) {
                 const bool ok = mbar_wait(my_full + stage * a.pps * 8, phase, a.wait_cycles);
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) *timeout_flag = 1;
@@ -500,22 +467,20 @@ int balanced_state_rows(const DecodeLaunch &launch) {
 
 } // namespace
 
-template <bool kGather, bool kPair>
+template <bool kGather>
 static int configure_balanced(size_t max_dynamic_shared) {
     // the opt-in limit covers static and dynamic shared memory together
     cudaFuncAttributes attributes;
-    const int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<kGather, kPair>);
+    const int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<kGather>);
     if (rc) return rc;
-    return cudaFuncSetAttribute(balanced_decode_kernel<kGather, kPair>,
+    return cudaFuncSetAttribute(balanced_decode_kernel<kGather>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)(max_dynamic_shared - attributes.sharedSizeBytes));
 }
 
 int configure_stream_kernels(size_t max_dynamic_shared) {
-    int rc = configure_balanced<false, false>(max_dynamic_shared);
-    if (!rc) rc = configure_balanced<false, true>(max_dynamic_shared);
-    if (!rc) rc = configure_balanced<true, false>(max_dynamic_shared);
-    if (!rc) rc = configure_balanced<true, true>(max_dynamic_shared);
+    int rc = configure_balanced<false>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<true>(max_dynamic_shared);
     return rc;
 }
 
@@ -542,7 +507,6 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     args.stages = launch.stages;
     args.workers = (int32_t)launch.grid * launch.pages_per_stage;
     args.rows = balanced_state_rows(launch);
-    args.pair = launch.pages_per_step == 2 ? 1 : 0;
     args.workspace_numel = launch.workspace_numel;
     args.scale_log2 = launch.scale_log2;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
@@ -550,10 +514,7 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    const bool gather = launch.peer.world != 0, pair = args.pair != 0;
-    auto kernel = gather ? (pair ? balanced_decode_kernel<true, true> : balanced_decode_kernel<true, false>)
-                         : (pair ? balanced_decode_kernel<false, true>
-                                 : balanced_decode_kernel<false, false>);
+    auto kernel = launch.peer.world != 0 ? balanced_decode_kernel<true> : balanced_decode_kernel<false>;
     return launch_dependent(kernel, launch.grid, launch.block, launch.shared_bytes, stream, k_map,
                             v_map, args);
 }

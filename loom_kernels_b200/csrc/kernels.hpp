@@ -51,13 +51,12 @@ struct DecodeLaunch {
     int32_t indices_min; // page_indptr[batch] must lie in [indices_min, indices_len]
     int32_t heads_per_cta, pages_per_stage, q_tiles, q_blocks, partitions, stages;
     int32_t cluster;        // 1: the chunks of an item are one thread-block cluster (one command)
-    int32_t pages_per_step; // pages a consumer warp takes per step: 1, or 2 (one joint softmax update)
     float scale_log2;
     uint32_t grid, block, shared_bytes;
     long long wait_cycles;  // limit of every bounded wait of the kernel, in SM clock cycles
     long long workspace_numel; // F32 elements bound as the workspace (the checked build's bound)
     int32_t test_skip_page; // tests of the give-up path: 1 + the page of a CTA's chunk whose
-                            // loads the producer leaves out (0 = none)
+                            // bytes never all arrive (0 = none)
     PeerOut peer;           // zeroed unless the plan gathers its output
     PeerSignal signal;      // zeroed unless this launch is the last kernel of a gathering command
 };

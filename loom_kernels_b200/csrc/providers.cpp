@@ -113,8 +113,7 @@ void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
         c.algorithm == LB_DECODE_DIRECT || c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 2;
     info->workspace_numel = c.workspace_numel;
     info->workspace_bytes = c.workspace_numel * sizeof(float);
-    info->pages_per_step = c.pages_per_step;
-    info->reserved = 0;
+    info->reserved[0] = info->reserved[1] = 0;
 }
 
 } // namespace
@@ -363,7 +362,6 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     launch.q_blocks = (int32_t)c.q_blocks;
     launch.partitions = (int32_t)c.partitions;
     launch.stages = (int32_t)c.stages;
-    launch.pages_per_step = (int32_t)c.pages_per_step;
     launch.cluster = c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 0;
     launch.scale_log2 = spec.softmax_scale * kLog2E;
     launch.grid = c.grid;

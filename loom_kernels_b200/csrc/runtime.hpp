@@ -165,7 +165,6 @@ uint64_t fresh_id();
 struct DecodeChoice {
     uint32_t algorithm; // LB_DECODE_DIRECT / LB_DECODE_SPLIT_K / LB_DECODE_BALANCED
     uint32_t partitions, heads_per_cta, q_tiles, q_blocks, pages_per_stage, stages, warps;
-    uint32_t pages_per_step;
     uint32_t grid, block, shared_bytes, merge_grid, merge_block;
     size_t workspace_numel;
 };

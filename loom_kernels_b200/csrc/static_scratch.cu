@@ -165,7 +165,6 @@ lb_status lb_paged_decode_split_noalloc(const lb_paged_spec *spec, uint32_t part
     launch.q_blocks = (int32_t)c.q_blocks;
     launch.partitions = (int32_t)c.partitions;
     launch.stages = (int32_t)c.stages;
-    launch.pages_per_step = (int32_t)c.pages_per_step;
     launch.scale_log2 = checked.softmax_scale * 1.44269504088896340736f;
     launch.grid = c.grid;
     launch.block = c.block;

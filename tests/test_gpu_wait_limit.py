@@ -2,8 +2,9 @@
 
 Every wait of the decode kernels (a consumer for the bytes of a page, the producer for a free
 stage, the last CTA of a gathering command for the other ranks) has a limit.  A test plan lowers
-the limit to a millisecond and leaves the copies of one page out (`test_skip_page`), which is all
-a lost copy would look like: the consumers of that page wait for bytes that never arrive, give
+the limit to a millisecond and makes one page's barrier expect more bytes than its copies deliver
+(`test_skip_page`), which is all a lost copy would look like: the consumers of that page wait for
+bytes that never arrive, give
 up, the CTA writes nothing and sets the provider's status word, and the kernel returns by itself.
 The next call on the same provider, with a normal plan, must be correct.
 """
