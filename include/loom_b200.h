@@ -320,7 +320,17 @@ typedef struct lb_paged_decode_options {
                                 and split-K plans, a page of the ring's first round */
     uint32_t cluster;        /* with partitions 2..8: 1 = LB_DECODE_CLUSTER_SPLIT instead of the
                                 two-command split-K */
-    uint32_t reserved[4];    /* zero */
+    uint32_t merge_in_kernel; /* 1 = the kernel that computes the partial states also merges them
+                                 (whoever counts the last state of an item; one command; needs a
+                                 counting word of the queue per item), 2 = a second command merges
+                                 (the reference's two-command form), 0 = the plan decides, which
+                                 is the second command: merging in the kernel measured no faster
+                                 on any shape of the benchmark and slower on some */
+    uint32_t max_stages;     /* 0 = the plan decides; >= 2 caps the stages of the page ring (the
+                                bytes a CTA keeps in flight) */
+    uint32_t producer_warps; /* balanced plans: 0 = the plan decides, 1 = one warp issues the page
+                                copies of all page slots, pages_per_stage = one warp per slot */
+    uint32_t reserved;       /* zero */
 } lb_paged_decode_options;
 
 typedef struct lb_paged_decode_plan_info {
@@ -336,7 +346,9 @@ typedef struct lb_paged_decode_plan_info {
     uint32_t commands;       /* 1 direct or cluster split, 2 split or balanced (partials + merge) */
     size_t workspace_numel;  /* F32 elements the caller must bind (0 for direct) */
     size_t workspace_bytes;
-    uint32_t reserved[2];
+    uint32_t merged_in_kernel; /* 1: a split-K or balanced plan that merges its partial states in
+                                  the decode kernel (commands == 1, the workspace is still bound) */
+    uint32_t reserved;
 } lb_paged_decode_plan_info;
 
 /* Bf16PagedBatchDecodeArgs, decode.rs:1451-1487, plus the split-K workspace

@@ -53,7 +53,8 @@ class DecodeOptions(ctypes.Structure):
     _fields_ = [("partitions", c_uint32), ("heads_per_cta", c_uint32), ("balanced", c_uint32),
                 ("balanced_ctas", c_uint32), ("indices_capacity", c_uint32),
                 ("wait_limit_us", c_uint32), ("test_skip_page", c_uint32),
-                ("cluster", c_uint32), ("reserved", c_uint32 * 4)]
+                ("cluster", c_uint32), ("merge_in_kernel", c_uint32), ("max_stages", c_uint32),
+                ("producer_warps", c_uint32), ("reserved", c_uint32)]
 
 
 class AppendOptions(ctypes.Structure):
@@ -66,7 +67,7 @@ class DecodePlanInfo(ctypes.Structure):
                 ("stages", c_uint32), ("grid", c_uint32), ("block", c_uint32),
                 ("shared_bytes", c_uint32), ("merge_grid", c_uint32), ("merge_block", c_uint32),
                 ("commands", c_uint32), ("workspace_numel", c_size_t),
-                ("workspace_bytes", c_size_t), ("reserved", c_uint32 * 2)]
+                ("workspace_bytes", c_size_t), ("merged_in_kernel", c_uint32), ("reserved", c_uint32)]
 
 
 class DecodeArgs(ctypes.Structure):

@@ -11,6 +11,7 @@ Buffers are CUDA torch tensors (torch owns device memory; this layer only passes
 from __future__ import annotations
 
 import ctypes
+import gc
 from ctypes import byref, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 from dataclasses import dataclass
 from typing import Callable, Optional, Sequence
@@ -533,18 +534,25 @@ class DecodeProvider:
                               heads_per_cta: int = 0, balanced: int = 0,
                               balanced_ctas: int = 0, indices_capacity: bool = False,
                               wait_limit_us: int = 0, test_skip_page: int = 0,
-                              cluster: bool = False) -> "Bf16PagedBatchDecodePlan":
+                              cluster: bool = False,
+                              merge_in_kernel: int = 0,
+                              max_stages: int = 0,
+                              producer_warps: int = 0) -> "Bf16PagedBatchDecodePlan":
         """partitions: 0 heuristic, 1 direct, N split-K; balanced (with partitions 0): 0
         heuristic, 1 force the balanced algorithm, 2 never use it.  indices_capacity: the bound
         page_indices may be longer than the table in use (page_indptr[batch] <= len), which
         lets one fixed-address Graph serve steps with different total page counts.
         wait_limit_us: limit of the kernels' bounded waits (0 = about two seconds);
-        test_skip_page: tests of the give-up path only."""
+        test_skip_page: tests of the give-up path only.  merge_in_kernel (static split-K): 1 the
+        last CTA of an item merges it (one command), 0 or 2 a second command does.  max_stages:
+        cap on the stages of the page ring (0 = the plan decides)."""
         options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta,
                                      balanced=balanced, balanced_ctas=balanced_ctas,
                                      indices_capacity=1 if indices_capacity else 0,
                                      wait_limit_us=wait_limit_us, test_skip_page=test_skip_page,
-                                     cluster=1 if cluster else 0)
+                                     cluster=1 if cluster else 0,
+                                     merge_in_kernel=merge_in_kernel, max_stages=max_stages,
+                                     producer_warps=producer_warps)
         out = c_void_p()
         _check(_abi.load().lb_paged_decode_plan_create(self._ptr, byref(spec._raw),
                                                        byref(options), byref(out)))
@@ -552,10 +560,10 @@ class DecodeProvider:
 
 
 def choose_paged_decode(spec, sm_count: int, partitions: int = 0, heads_per_cta: int = 0,
-                        balanced: int = 0):
+                        balanced: int = 0, merge_in_kernel: int = 0):
     """The plan-time heuristic as a pure function (no device needed)."""
     options = _abi.DecodeOptions(partitions=partitions, heads_per_cta=heads_per_cta,
-                                 balanced=balanced)
+                                 balanced=balanced, merge_in_kernel=merge_in_kernel)
     info = _abi.DecodePlanInfo()
     _check(_abi.load().lb_paged_decode_choose(byref(spec._raw), sm_count, byref(options),
                                               byref(info)))
@@ -580,6 +588,7 @@ class Bf16PagedBatchDecodePlan:
     def partitions(self): return self._info.partitions
     def info(self): return self._info
     def commands(self): return self._info.commands
+    def merged_in_kernel(self): return bool(self._info.merged_in_kernel)
     def workspace_required_numel(self): return self._info.workspace_numel
     def workspace_required_bytes(self): return self._info.workspace_bytes
 
@@ -1001,8 +1010,17 @@ class GraphQueue:
         callback = _abi.RECORD_FN(trampoline)
         out = c_void_p()
         queue_ptr, self._ptr = self._ptr, None
-        status = _abi.load().lb_graph_capture(queue_ptr, bindings._release(), callback, None,
-                                              byref(out))
+        # no finaliser runs while the stream is capturing: one that frees device memory (an old
+        # provider, a tensor) in this thread would invalidate the capture
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            status = _abi.load().lb_graph_capture(queue_ptr, bindings._release(), callback, None,
+                                                  byref(out))
+        finally:
+            if collecting:
+                gc.enable()
         if raised:
             raise raised[0]
         _check(status)

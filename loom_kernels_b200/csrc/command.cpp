@@ -5,6 +5,11 @@
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include <cuda_runtime.h>
 
 #include "runtime.hpp"
 
@@ -165,6 +170,40 @@ lb_handle lb_handle_write(lb_handle h) {
     return h;
 }
 
+// The synchronisation words of queues come from a per-device list and go back to it: a queue
+// leaves its words zero, so the next queue takes them as they are, and destroying a queue calls
+// nothing that a stream capture running in the same thread would forbid (a garbage collector may
+// finalise an old queue at any moment, a cudaFree there invalidated the capture).  The blocks
+// live as long as the process.
+static std::mutex g_words_mutex;
+static std::map<int, std::vector<int32_t *>> g_free_words;
+
+static int acquire_sync_words(int device, int32_t **out) {
+    {
+        std::lock_guard<std::mutex> lock(g_words_mutex);
+        std::vector<int32_t *> &list = g_free_words[device];
+        if (!list.empty()) {
+            *out = list.back();
+            list.pop_back();
+            return 0;
+        }
+    }
+    int32_t *words = nullptr;
+    const int rc = driver().configure(device, [&]() -> int {
+        int e = cudaMalloc((void **)&words, kQueueSyncWords * sizeof(int32_t));
+        if (e) return e;
+        if ((e = cudaMemset(words, 0, kQueueSyncWords * sizeof(int32_t)))) return e;
+        return cudaDeviceSynchronize(); // the zeros are there before any stream uses them
+    });
+    *out = rc ? nullptr : words; // (the fake driver runs no set-up: no words, and no kernels)
+    return rc;
+}
+
+static void release_sync_words(int device, int32_t *words) {
+    std::lock_guard<std::mutex> lock(g_words_mutex);
+    g_free_words[device].push_back(words);
+}
+
 lb_status lb_queue_create(void *stream, size_t max_commands, lb_queue **out) {
     if (!out) return fail(LB_INVALID_ARGUMENT, "out");
     *out = nullptr;
@@ -174,7 +213,14 @@ lb_status lb_queue_create(void *stream, size_t max_commands, lb_queue **out) {
     if (rc) return fail(LB_DRIVER, "stream_device", rc);
     void *event = nullptr;
     if ((rc = driver().event_create(device, false, &event))) return fail(LB_DRIVER, "event", rc);
+    // (under the fake driver nothing is allocated: its launches run no kernel)
+    int32_t *words = nullptr;
+    if ((rc = acquire_sync_words(device, &words))) {
+        driver().event_destroy(device, event);
+        return fail(LB_DRIVER, "queue_words", rc);
+    }
     lb_queue *queue = new lb_queue();
+    queue->sync_words = words;
     queue->id = fresh_id();
     queue->stream = stream;
     queue->device = device;
@@ -210,6 +256,8 @@ void lb_queue_destroy(lb_queue *queue) {
                             "drop: CUDA error %d\n", error);
     }
     driver().event_destroy(queue->device, queue->completion_event);
+    // (a queue that met an error may leave counts behind: its words are not handed on)
+    if (queue->sync_words && !queue->poisoned) release_sync_words(queue->device, queue->sync_words);
     if (queue->owns_stream) driver().stream_destroy(queue->device, queue->stream);
     delete queue;
 }

@@ -98,6 +98,8 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         (spec.num_kv_heads / balanced_hc) * q_blocks <= 4096 &&
         2 * stage_bytes + 3072 + balanced_extra <= smem;
 
+    const uint32_t merge_option = options ? options->merge_in_kernel : 0;
+    if (merge_option > 2) return fail(LB_LAUNCH_CONTRACT, "merge_in_kernel", merge_option);
     const bool cluster_option = options && options->cluster == 1;
     if (options && options->cluster > 1) return fail(LB_LAUNCH_CONTRACT, "cluster", options->cluster);
     if (cluster_option && (partitions < 2 || partitions > 8))
@@ -190,6 +192,8 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     if (algorithm == LB_DECODE_BALANCED) extra += balanced_extra;
     uint32_t stages = (uint32_t)((smem - extra) / stage_bytes);
     if (stages > 6) stages = 6;
+    if (options && options->max_stages >= 2 && stages > options->max_stages)
+        stages = options->max_stages;
     // direct/split CTAs merge their warps' states in the ring: 8 warps x 68 x 32 floats
     if (stages < 2 || (algorithm != LB_DECODE_BALANCED && pps > 1 &&
                        (size_t)stages * stage_bytes < 8u * 68u * 32u * 4u))
@@ -222,10 +226,42 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
         }
     }
 
-    // Pages a consumer warp takes per step: two halve the dependent chain (maximum, shuffles,
-    // exponentials) per token and occupy two stages of the ring at once.  The plan does not choose
-    // it: on the wide-group shape it was written for (ragged MQA 32/1) the producer's copies, not
-    // the consumers, bound the kernel, and it measured 117.6 against 114.4 us; a caller may pin it.
+    // Balanced plans whose boxes are small (one KV head per CTA: 4 KB) give every page slot a
+    // producer warp of its own; the others keep one.
+    uint32_t producer_warps = 1;
+    const uint32_t producer_option = options ? options->producer_warps : 0;
+    if (producer_option > 1 && (algorithm != LB_DECODE_BALANCED || producer_option != pps))
+        return fail(LB_LAUNCH_CONTRACT, "producer_warps", producer_option);
+    if (algorithm == LB_DECODE_BALANCED && pps > 1 && pps <= 4 &&
+        (producer_option == pps || (producer_option == 0 && hc == 1)))
+        producer_warps = pps;
+    // On request a static split is merged inside its own kernel: every chunk counts itself on a
+    // word of the queue and the last one of an item merges it.  One command instead of two, at
+    // no gain in time -- the tail of the last CTAs is as long as a merge kernel that starts under
+    // programmatic dependent launch (C1 8.9 against 8.6 us per Graph node), and a large plan
+    // loses the parallel merge (C4 split 16: 179.9 against 163.8 us) -- so the plan never
+    // chooses it by itself.
+    uint32_t merged_in_kernel = 0;
+    if (algorithm == LB_DECODE_SPLIT_K) {
+        const bool fits = grid / partitions <= kQueueSyncWords;
+        if (merge_option == 1 && !fits)
+            return fail(LB_LAUNCH_CONTRACT, "merge_in_kernel", (int64_t)(grid / partitions));
+        merged_in_kernel = merge_option == 1 ? 1 : 0;
+    } else if (algorithm == LB_DECODE_BALANCED) {
+        // On request a balanced plan merges its cut items in the decode kernel: the warp that
+        // counts the last state of an item merges the rows of its tile and publishes them.  The
+        // plan does not choose it either: a warp that merges stalls its page slot, and on ragged
+        // MQA (32 rows per item) the kernel went from 110 to 143 us; C3 and ragged GQA4 were
+        // unchanged (172 / 527 us).  It needs a word of the queue per (item, KV head, row tile).
+        const size_t words =
+            spec.batch_size * (spec.num_kv_heads / hc) * q_blocks * (size_t)hc * q_tiles;
+        if (merge_option == 1 && words > kQueueSyncWords)
+            return fail(LB_LAUNCH_CONTRACT, "merge_in_kernel", (int64_t)words);
+        merged_in_kernel = merge_option == 1 ? 1 : 0;
+    } else if (merge_option == 1) {
+        return fail(LB_LAUNCH_CONTRACT, "merge_in_kernel", 1);
+    }
+    out->merged_in_kernel = merged_in_kernel;
     out->algorithm = algorithm;
     out->partitions = partitions;
     out->heads_per_cta = hc;
@@ -235,15 +271,22 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     out->stages = stages;
     out->warps = warps;
     out->grid = (uint32_t)grid;
-    out->block = (warps + 1) * 32;
+    out->producer_warps = producer_warps;
+    out->block = (warps + producer_warps) * 32;
     out->shared_bytes = (uint32_t)(stages * stage_bytes + extra);
     out->merge_block = 128;
-    // one warp per (request, query head); the balanced merge of a small batch -- where a long
-    // request is cut into many states -- gives every item a whole CTA of four warps
-    out->merge_grid = algorithm == LB_DECODE_DIRECT || algorithm == LB_DECODE_CLUSTER_SPLIT ? 0
-                      : algorithm == LB_DECODE_BALANCED && states <= 2048
-                          ? (uint32_t)states
-                          : ceil_div((uint32_t)states, 4);
+    // One warp per (request, query head), four items per CTA.  Where the balanced cut leaves many
+    // states per item -- few requests on many workers: eight or more workers per (request, head
+    // block) -- every item gets a whole CTA whose four warps share its states.  (With two or
+    // three states per item that form only multiplies CTAs: C3 merged in 19 us instead of 7.)
+    const bool many_states_per_item =
+        algorithm == LB_DECODE_BALANCED && states <= 2048 &&
+        (size_t)grid * pps >= 8 * spec.batch_size * (spec.num_kv_heads / hc) * q_blocks;
+    out->merge_grid = algorithm == LB_DECODE_DIRECT || algorithm == LB_DECODE_CLUSTER_SPLIT ||
+                              merged_in_kernel
+                          ? 0
+                      : many_states_per_item ? (uint32_t)states
+                                             : ceil_div((uint32_t)states, 4);
     out->workspace_numel = workspace;
     return LB_OK;
 }
@@ -503,12 +546,13 @@ lb_status lb_paged_decode_choose(const lb_paged_spec *spec, uint32_t sm_count,
     info->merge_grid = choice.merge_grid;
     info->merge_block = choice.merge_block;
     info->commands = choice.algorithm == LB_DECODE_DIRECT ||
-                             choice.algorithm == LB_DECODE_CLUSTER_SPLIT
+                             choice.algorithm == LB_DECODE_CLUSTER_SPLIT || choice.merged_in_kernel
                          ? 1
                          : 2;
     info->workspace_numel = choice.workspace_numel;
     info->workspace_bytes = choice.workspace_numel * sizeof(float);
-    info->reserved[0] = info->reserved[1] = 0;
+    info->merged_in_kernel = choice.merged_in_kernel;
+    info->reserved = 0;
     return LB_OK;
 }
 

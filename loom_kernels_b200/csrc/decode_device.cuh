@@ -23,6 +23,7 @@ constexpr int kHeadDim = 128;
 constexpr int kPage = 16;
 constexpr int kStateWidth = 130;
 constexpr int kComputeWarps = 8;
+constexpr int kMaxProducerWarps = 4; // the balanced kernel: up to one producer warp per page slot
 constexpr int kUnitBytes = 8192;  // K (16 x 256 B) + V (16 x 256 B) of one (page, KV head)
 constexpr int kBoxBytes = 2048;   // half a tile: 16 tokens x 64 dims x 2 B
 constexpr long long kWaitCycles = 4000000000ll; // ~2 s at 2 GHz; waits normally take microseconds
@@ -745,6 +746,56 @@ __device__ __forceinline__ void merge_states(StateOf state_of, int n, int lane, 
     if (!merge_partial<kBatch>(state_of, n, lane, top, norm, acc) || !publish) return;
     if (!(norm > 0.0f)) return; // every state was empty: nothing to publish
     publish_merged(top, norm, acc, lane, out_row, lse_slot);
+}
+
+// kRows rows of at most four states each, merged by one warp with the loads of all of them in
+// flight together (a warp that merges the sixteen rows of its tile one by one pays sixteen round
+// trips to the L2; this pays four).  state_of(row, i) is state i of row `row` (row < rows);
+// publish(row, top, norm, acc) receives every row that has a finite, unpoisoned result.  The
+// arithmetic is merge_partial's short path.
+template <int kRows, typename StateOf, typename Publish>
+__device__ __forceinline__ void merge_few_states_of_rows(StateOf state_of, int n, int rows,
+                                                         int lane, Publish publish) {
+    float part_max[kRows][4], part_norm[kRows][4];
+    float2 lo[kRows][4], hi[kRows][4];
+#pragma unroll
+    for (int row = 0; row < kRows; ++row)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            part_max[row][i] = part_norm[row][i] = 0.0f;
+            lo[row][i] = hi[row][i] = make_float2(0.f, 0.f);
+            if (row < rows && i < n) {
+                const float *s = state_of(row, i);
+                part_max[row][i] = __ldcg(s);
+                part_norm[row][i] = __ldcg(s + 1);
+                lo[row][i] = __ldcg(reinterpret_cast<const float2 *>(s + 2 + lane * 4));
+                hi[row][i] = __ldcg(reinterpret_cast<const float2 *>(s + 4 + lane * 4));
+            }
+        }
+#pragma unroll
+    for (int row = 0; row < kRows; ++row) {
+        if (row >= rows) break;
+        float top = -INFINITY;
+        bool poisoned = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            poisoned |= part_norm[row][i] < 0.0f;
+            if (part_norm[row][i] > 0.0f) top = fmaxf(top, part_max[row][i]);
+        }
+        float norm = 0.0f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float weight =
+                part_norm[row][i] > 0.0f ? exp2f(part_max[row][i] - top) : 0.0f;
+            norm += part_norm[row][i] * weight;
+            acc.x += lo[row][i].x * weight;
+            acc.y += lo[row][i].y * weight;
+            acc.z += hi[row][i].x * weight;
+            acc.w += hi[row][i].y * weight;
+        }
+        if (!poisoned && norm > 0.0f) publish(row, top, norm, acc);
+    }
 }
 
 // As merge_states, by the kWarps warps of a CTA for one item (every thread of the CTA calls).

@@ -49,6 +49,8 @@ struct DecodeArgs {
     long long workspace_numel; // F32 elements bound as the workspace (checked builds)
     int32_t skip_page;     // tests of the give-up path: 1 + the page whose bytes never all arrive
     long long wait_cycles; // limit of every bounded wait
+    int32_t *counters;     // split plans that merge in this kernel: one word per item, zero
+                           // between commands (a queue's synchronisation words)
     PeerOut peer;          // world == 0 unless the plan gathers its output
     PeerSignal signal;     // world == 0 unless this kernel is the last of a gathering command
 };
@@ -58,9 +60,16 @@ struct DecodeArgs {
 // kCluster: the `partitions` CTAs of one (request, head block, query block) form a thread-block
 // cluster (the chunk is the CTA's rank in it) and their states are merged through distributed
 // shared memory by the cluster's first CTA: split-K as one command, without a workspace.
+// What the merge at the end of a split plan's kernel (a.counters) needs to know about this CTA.
+struct CtaItem {
+    int request, qb, hb;
+    bool counted; // the CTA left a state (finished, empty or poisoned) for every row of its item
+};
+
 template <bool kGather, bool kCluster>
 __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const CUtensorMap &v_map,
-                                                 const DecodeArgs &a, PeerLocal &peer_local) {
+                                                 const DecodeArgs &a, PeerLocal &peer_local,
+                                                 CtaItem &item_out) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -94,6 +103,10 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         item /= a.partitions;
     }
     const int request = item;
+    item_out.request = request;
+    item_out.qb = qb;
+    item_out.hb = hb;
+    item_out.counted = false;
     // (a CTA past the batch leaves at once, unless the plan gathers: there every CTA of the grid
     // is counted at the kernel's end)
     if (!kGather && request >= a.batch) return;
@@ -152,6 +165,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
             if (in_bounds((long long)at, a.workspace_numel, a.status, kSiteWorkspace))
                 a.workspace[at] = 0.0f;
         }
+        item_out.counted = true;
         return;
     }
 
@@ -306,6 +320,21 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         }
         __syncthreads();
         if (tid == 0 && a.status) atomicExch(a.status, 1);
+        if (!kCluster && a.counters != nullptr) {
+            // the item's chunks are counted at the kernel's end: this one leaves poisoned states,
+            // so that the count stays whole and the rows keep their previous contents
+            const int row_lo = qb * rows_per_block;
+            const int rows = max(0, min(group, row_lo + rows_per_block) - row_lo);
+            for (int i = tid; i < a.hc * rows; i += blockDim.x) {
+                const int qhead = (hb * a.hc + i / rows) * group + row_lo + i % rows;
+                const size_t at =
+                    ((size_t)(request * a.qh + qhead) * a.partitions + part) * kStateWidth;
+                if (in_bounds((long long)at, a.workspace_numel, a.status, kSiteWorkspace,
+                              kStateWidth))
+                    a.workspace[at + 1] = -1.0f;
+            }
+            item_out.counted = true;
+        }
         if (!kCluster) return; // (a cluster's CTAs still meet at its barriers: a poisoned state)
     }
 
@@ -398,6 +427,7 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
         cluster_barrier(); // nobody leaves while the first CTA still reads its shared memory
         return;
     }
+    item_out.counted = true; // (every thread of the CTA passes here)
     if (warp >= kComputeWarps || page_slot0 != 0) return;
 
     // ---- epilogue ---------------------------------------------------------------------------------
@@ -429,6 +459,47 @@ __device__ __forceinline__ void paged_decode_cta(const CUtensorMap &k_map, const
     }
 }
 
+// Split-K as one command: every chunk's CTA has left its states in the workspace; each counts
+// itself on its item's word, and the one that finds the item complete merges the item's rows and
+// writes O and LSE.  The word wraps to zero on the last count (atomicInc), so it is ready for
+// the next command without anybody resetting it.  No CTA waits for another.
+template <bool kGather>
+__device__ __forceinline__ void merge_when_last(const DecodeArgs &a, const CtaItem &item) {
+    __shared__ int is_last;
+    const int head_blocks = a.kvh / a.hc;
+    __syncthreads(); // every state of this CTA has been written ...
+    if (threadIdx.x == 0) {
+        __threadfence(); // ... and is visible to the GPU before the count is
+        const unsigned word = ((unsigned)item.request * a.qb + item.qb) * head_blocks + item.hb;
+        const unsigned seen = atomicInc(reinterpret_cast<unsigned *>(a.counters) + word,
+                                        (unsigned)a.partitions - 1);
+        is_last = seen == (unsigned)a.partitions - 1;
+        if (is_last) __threadfence();
+    }
+    __syncthreads();
+    if (!is_last) return;
+    const int group = a.qh / a.kvh;
+    const int rows_per_block = 16 * a.mt;
+    const int row_lo = item.qb * rows_per_block;
+    const int rows = max(0, min(group, row_lo + rows_per_block) - row_lo);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < a.hc * rows; r += kComputeWarps + 1) {
+        const int qhead = (item.hb * a.hc + r / rows) * group + row_lo + r % rows;
+        const long long state = (long long)item.request * a.qh + qhead;
+        const float *first = a.workspace + (size_t)state * a.partitions * kStateWidth;
+        auto state_of = [&](int p) { return first + (size_t)p * kStateWidth; };
+        if (!in_bounds((state + 1) * a.partitions * kStateWidth - 1, a.workspace_numel, a.status,
+                       kSiteWorkspace) ||
+            !in_bounds(state, (long long)a.batch * a.qh, a.status, kSiteOutput))
+            continue;
+        if (kGather && a.peer.world != 0)
+            merge_states_to_peers(state_of, a.partitions, lane, true, a.peer, item.request, qhead);
+        else
+            merge_states<8>(state_of, a.partitions, lane, true, a.output + state * kHeadDim,
+                            a.lse + state);
+    }
+}
+
 // kGather: the instantiation for plans that gather their output (the other one carries none of
 // its registers or shared memory).
 template <bool kGather, bool kCluster>
@@ -437,7 +508,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const DecodeArgs a) {
     __shared__ PeerLocal peer_local;
     dependent_launch_release();
-    paged_decode_cta<kGather, kCluster>(k_map, v_map, a, peer_local);
+    CtaItem item;
+    paged_decode_cta<kGather, kCluster>(k_map, v_map, a, peer_local, item);
+    if (!kCluster && a.counters != nullptr && item.counted)
+        merge_when_last<kGather>(a, item);
     if (!kGather || a.signal.world == 0 || a.signal.defer) return;
     __syncthreads(); // every row of this CTA has been stored; peer_local is complete
     if (threadIdx.x >= 32) return;
@@ -541,6 +615,7 @@ int launch_paged_decode(const DecodeLaunch &launch, void *stream) {
     args.workspace_numel = launch.workspace_numel;
     args.skip_page = launch.test_skip_page;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
+    args.counters = launch.counters;
     args.peer = launch.peer;
     args.signal = launch.signal;
     CUtensorMap k_map, v_map;

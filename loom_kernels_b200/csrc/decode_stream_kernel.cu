@@ -40,11 +40,15 @@ struct StreamArgs {
     int32_t *status;
     int32_t batch, max_pages, qh, kvh, indices_len, indices_min;
     int32_t hc, pps, mt, qb, stages, workers;
+    int32_t pw;   // producer warps: 1, or one per page slot (pps)
     int32_t rows; // state rows per KV head in a slot: min(group, 16 * mt)
     long long workspace_numel; // F32 elements bound as the workspace (checked builds)
     float scale_log2;
     long long wait_cycles; // limit of every bounded wait
+    int32_t *counters;     // one zeroed word per (item, KV head of the CTA, row tile): cut items
+                           // are merged by the warp that counts the last of their states
     PeerOut peer;          // world == 0 unless the plan gathers its output
+    PeerSignal signal;     // world == 0 unless this kernel is the last of a gathering command
 };
 
 __device__ __forceinline__ size_t state_floats(int workers, int hc, int rows) {
@@ -65,12 +69,10 @@ __device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
 // kGather: the instantiation for plans that gather their output (the other one carries none of
 // its registers or shared memory).
 template <bool kGather>
-__global__ void __launch_bounds__((kComputeWarps + 1) * 32, 1)
-balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
-                       const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
+__device__ __forceinline__ void balanced_decode_cta(const CUtensorMap &k_map,
+                                                    const CUtensorMap &v_map, const StreamArgs &a,
+                                                    PeerLocal &peer_local) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ PeerLocal peer_local;
-    dependent_launch_release();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
@@ -108,11 +110,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     dependent_launch_wait();
     // a gathering plan: the peers' addresses, fetched now for the row stores (the barriers of the
     // prefix computation below come before any of them)
-    if (kGather && warp == kComputeWarps - 1) {
-        PeerSignal none;
-        none.world = 0;
-        peer_prefetch(a.peer, none, lane, peer_local);
-    }
+    if (kGather && warp == kComputeWarps - 1) peer_prefetch(a.peer, a.signal, lane, peer_local);
 
     // ---- per-request guards (decode.rs:234-248), then the page prefix over valid requests ------
     const int global_end = a.indptr[a.batch];
@@ -168,20 +166,27 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if ((int)blockIdx.x * a.pps >= cut.workers) return;
 
     const int rows_per_block = 16 * a.mt;
-    int issued = 0; // producer lanes: pages of my slot whose copies were issued
+    int issued = 0; // producer lanes, set when the page loop ends: pages of my slot whose copies
+                    // were issued
 
-    if (warp == kComputeWarps) {
-        // ================= producer warp ==========================================================
-        const int my_slot = lane >> 1;
+    if (warp >= kComputeWarps) {
+        // ================= producer warps =========================================================
+        // One warp serves all pps page slots of the CTA, or (a.pw == pps) every slot has a warp of
+        // its own: with 4 KB boxes (one KV head per CTA) a single warp's loop -- look up, wait for
+        // a free stage, arm, issue, for four slots in lock-step -- is what bounds the kernel, and
+        // four independent loops are not.
+        const int slots_here = a.pps / a.pw;                       // slots this warp serves
+        const int slot_base = (warp - kComputeWarps) * slots_here; // the first of them
+        const int my_slot = slot_base + (lane >> 1);
         const int which = lane & 1; // 0: K box, 1: V box
-        const bool lane_active = my_slot < a.pps;
+        const bool lane_active = (lane >> 1) < slots_here;
         const CUtensorMap *map = which == 0 ? &k_map : &v_map;
-        // Page lookup is spread over the lanes: the warp's 32 lanes hold a window of 32 / pps pages
-        // for each of the CTA's pps workers; lane l looks after page (l % window) of worker
-        // (l / window).  So the range of a worker (it starts at page y0 of item h0; one 64-bit
-        // division) and every window refill cost one lane's work, whatever pps is.
-        const int window = 32 / a.pps;
-        const int look_slot = lane / window, look_j = lane & (window - 1);
+        // Page lookup is spread over the lanes: the warp's 32 lanes hold a window of 32 /
+        // slots_here pages for each worker it serves; lane l looks after page (l % window) of
+        // worker (l / window).  So the range of a worker (it starts at page y0 of item h0; one
+        // 64-bit division) and every window refill cost one lane's work.
+        const int window = 32 / slots_here;
+        const int look_slot = slot_base + lane / window, look_j = lane & (window - 1);
         int h0 = 0, y0 = 0, count = 0;
         {
             const int w = blockIdx.x * a.pps + look_slot;
@@ -213,7 +218,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         };
         int win_id, win_hb, next_id = 0, next_hb = 0;
         look_up(0, win_id, win_hb);
-        const int my_source = (my_slot & (a.pps - 1)) * window; // first lane of my worker's window
+        const int my_source = ((lane >> 1) & (slots_here - 1)) * window; // first lane of my worker's window
         const int my_count = __shfl_sync(0xffffffffu, count, my_source);
         const uint32_t my_full = full0 + my_slot * 8, my_empty = empty0 + my_slot * 8;
         const uint32_t my_tile =
@@ -221,7 +226,8 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         int stage = 0;
         uint32_t phase = 0;    // parity of the ring round being filled
         bool recycled = false; // the ring has wrapped: a slot must be handed back before reuse
-        for (int j = 0; j < longest; ++j) {
+        int j = 0;
+        for (; j < longest; ++j) {
             if (j > 0 && (j & (window - 1)) == 0) {
                 win_id = next_id;
                 win_hb = next_hb;
@@ -244,11 +250,9 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 mbar_expect_tx(bar_full, slot_bytes);
             }
             __syncwarp();
-            if (has) {
+            if (has)
                 tma_load_3d(my_tile + stage * stage_bytes, map, 0, max(page_id, 0) * kPage,
                             hb * a.hc * 2, bar_full);
-                ++issued;
-            }
             if (j == 0) {
                 // the second window is fetched once the first pages are on their way
                 if (window < longest) look_up(window, next_id, next_hb);
@@ -259,6 +263,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                 recycled = true;
             }
         }
+        issued = lane_active ? min(j, my_count) : 0;
     } else {
         // ================= consumer warps: one (worker, KV head, 16-row tile) each ==================
         const int unit = warp / a.mt;
@@ -283,7 +288,7 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
         int stage = 0;
         uint32_t phase = 0;
         bool live = true;
-        while (live && remaining > 0) {
+        while (remaining > 0) {
             // ---- segment: the part of one (request, head block, query block) item in my range ---
             const int r = owner_of(prefix, a.batch, y);
             const int num_pages = prefix[r + 1] - prefix[r];
@@ -325,7 +330,9 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                     phase ^= 1;
                 }
             }
-            if (!live) break;
+            // (after a wait ran out the worker still walks its segments: each leaves a poisoned
+            // state, so that the items it shares with other workers are counted whole)
+            if (!live) bad = true;
             st.finish_rows();
             const bool complete = first_page == 0 && seg_pages == num_pages;
             const int which = first_segment ? 0 : 1;
@@ -358,6 +365,78 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                         write_state_row(slot, lane, half, st, bad);
                 }
             }
+            if (!complete && a.counters != nullptr) {
+                // The item is cut: its states are counted, and the warp that finds them all there
+                // merges the rows of its tile and publishes them.  Nobody waits; the word wraps to
+                // zero on the last count, ready for the next command.
+                const long long start = (long long)h * total + prefix[r];
+                const int w0 = cut.owner_fast(start), w1 = cut.owner_fast(start + num_pages - 1);
+                const int n = w1 - w0 + 1;
+                __syncwarp(); // every lane's part of the state has been written ...
+                int last = 0;
+                if (lane == 0) {
+                    __threadfence(); // ... and is visible to the GPU before the count is
+                    const unsigned word =
+                        ((((unsigned)h * a.batch + r) * a.hc + head_in_cta) * a.mt + mtile);
+                    last = atomicInc(reinterpret_cast<unsigned *>(a.counters) + word,
+                                     (unsigned)n - 1) == (unsigned)n - 1;
+                    if (last) __threadfence();
+                }
+                if (__shfl_sync(0xffffffffu, last, 0)) {
+                    // every worker in [w0, w1] holds pages of this item; all but the first begin
+                    // inside the item and used slot 0
+                    const int first_slot = cut.begin(w0) != start ? 1 : 0;
+                    const size_t slot_stride = slot_rows * kStateWidth;
+                    const int tile_row0 = mtile * 16;
+                    const int valid = max(0, min(16, group - qb * rows_per_block - tile_row0));
+                    const float *base = a.workspace + (size_t)w0 * 2 * slot_stride +
+                                        ((size_t)head_in_cta * a.rows + tile_row0) * kStateWidth;
+                    auto state_of = [&](int row, int i) -> const float * {
+                        return base + (size_t)row * kStateWidth +
+                               ((size_t)i * 2 + (i == 0 ? first_slot : 0)) * slot_stride;
+                    };
+                    const long long head_row0 =
+                        (long long)kv_head * group + qb * rows_per_block + tile_row0;
+                    auto publish = [&](int row, float top, float norm, float4 acc) {
+                        if (kGather && a.peer.world != 0) {
+                            const long long at = (long long)dest_request * a.peer.gathered_qh +
+                                                 a.peer.head_offset + head_row0 + row;
+                            for (int p = 0; p < a.peer.world; ++p)
+                                publish_merged(top, norm, acc, lane,
+                                               static_cast<__nv_bfloat16 *>(peer_local.out[p]) +
+                                                   at * kHeadDim,
+                                               peer_local.lse[p] + at);
+                        } else {
+                            const long long at = (long long)r * a.qh + head_row0 + row;
+                            if (in_bounds(at, (long long)a.batch * a.qh, a.status, kSiteOutput))
+                                publish_merged(top, norm, acc, lane, a.output + at * kHeadDim,
+                                               a.lse + at);
+                        }
+                    };
+                    const bool inside = in_bounds(
+                        (base - a.workspace) + (long long)((size_t)(w1 - w0) * 2 + 1) * slot_stride +
+                            (long long)(valid > 0 ? valid - 1 : 0) * kStateWidth,
+                        a.workspace_numel, a.status, kSiteWorkspace, kStateWidth);
+                    if (inside && n <= 4) {
+                        for (int row0 = 0; row0 < valid; row0 += 4)
+                            merge_few_states_of_rows<4>(
+                                [&](int row, int i) { return state_of(row0 + row, i); }, n,
+                                min(4, valid - row0), lane,
+                                [&](int row, float top, float norm, float4 acc) {
+                                    publish(row0 + row, top, norm, acc);
+                                });
+                    } else if (inside) {
+                        for (int row = 0; row < valid; ++row) {
+                            float top, norm;
+                            float4 acc;
+                            if (merge_partial<8>([&](int i) { return state_of(row, i); }, n, lane,
+                                                 top, norm, acc) &&
+                                norm > 0.0f)
+                                publish(row, top, norm, acc);
+                        }
+                    }
+                }
+            }
             first_segment = false;
             remaining -= seg_pages;
             y += seg_pages;
@@ -371,14 +450,31 @@ balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
     if (*timeout_flag != 0) {
         // a wait ran out: the copies already on their way are waited for (bounded), so that none
         // lands in shared memory after this CTA has gone
-        if (warp == kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps)
-            drain_issued_copies(full0 + (lane >> 1) * 8, a.pps * 8, a.stages, issued,
+        if (warp >= kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps / a.pw)
+            drain_issued_copies(full0 + ((warp - kComputeWarps) * (a.pps / a.pw) + (lane >> 1)) * 8,
+                                a.pps * 8, a.stages, issued,
                                 a.wait_cycles);
         __syncthreads();
     }
     // (rows this kernel stored into other GPUs' memory are ordered by the stream before the merge
     // kernel, whose last CTA fences at system scope before it publishes the epoch)
     if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);
+}
+
+template <bool kGather>
+__global__ void __launch_bounds__((kComputeWarps + kMaxProducerWarps) * 32, 1)
+balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
+                       const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
+    __shared__ PeerLocal peer_local;
+    dependent_launch_release();
+    balanced_decode_cta<kGather>(k_map, v_map, a, peer_local);
+    // a gathering plan that merges in this kernel: this is the command's last kernel
+    if (!kGather || a.signal.world == 0 || a.signal.defer) return;
+    __syncthreads(); // every row of this CTA has been stored; peer_local is complete
+    if (threadIdx.x >= 32) return;
+    peer_signal_and_wait(a.signal,
+                         (int)threadIdx.x < a.signal.world ? peer_local.flags[threadIdx.x] : nullptr,
+                         peer_local.flags[a.signal.rank], peer_local.epoch);
 }
 
 // One warp per (request, query head): finds the workers whose ranges cut this head's item and
@@ -434,17 +530,17 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
         return;
     }
     if (kWarps == 1)
-        merge_states<8>(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim,
+        merge_states(state_of, w1 - w0 + 1, lane, true, output + (size_t)state * kHeadDim,
                         lse + state);
     else
         merge_states_shared<kWarps>(state_of, w1 - w0 + 1, lane, part,
                                     output + (size_t)state * kHeadDim, lse + state);
 }
 
-// (one warp per item: the kernel is a few waves of latency-bound CTAs, so it is built for eight
-// CTAs per SM, 64 registers, rather than for the four that its long-request path would take)
+// (Capping the one-warp form at 64 registers for eight CTAs per SM spilled and measured slower:
+// 16.0 against 14.5 us on the 8192 rows of a ragged MQA batch.)
 template <int kWarps>
-__global__ void __launch_bounds__(128, kWarps == 1 ? 8 : 1)
+__global__ void __launch_bounds__(128)
 balanced_merge_kernel(const float *__restrict__ workspace, __nv_bfloat16 *output, float *lse,
                       int batch, int qh, int kvh, int hc, int mt, int qblocks, int workers,
                       int rows, const PeerOut peer, const PeerSignal signal,
@@ -505,12 +601,15 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     args.mt = launch.q_tiles;
     args.qb = launch.q_blocks;
     args.stages = launch.stages;
+    args.pw = launch.producer_warps > 0 ? launch.producer_warps : 1;
     args.workers = (int32_t)launch.grid * launch.pages_per_stage;
     args.rows = balanced_state_rows(launch);
     args.workspace_numel = launch.workspace_numel;
     args.scale_log2 = launch.scale_log2;
     args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
+    args.counters = launch.counters;
     args.peer = launch.peer;
+    args.signal = launch.signal;
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));

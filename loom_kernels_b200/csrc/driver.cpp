@@ -124,7 +124,15 @@ struct CudaDriver final : Driver {
     }
     int configure(int device, const std::function<int()> &fn) override {
         DeviceGuard guard(device);
-        return fn();
+        // Set-up calls (allocation, free, memset) are "potentially unsafe" to a stream capture
+        // running in this thread and would invalidate it; a destructor may well run there (a
+        // garbage collector finalising an old provider while a Graph is being recorded).  They
+        // touch nothing the capture records, so they run in relaxed mode.
+        cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+        cudaThreadExchangeStreamCaptureMode(&mode);
+        const int rc = fn();
+        cudaThreadExchangeStreamCaptureMode(&mode);
+        return rc;
     }
     int launch(int device, const std::function<int()> &fn) override {
         DeviceGuard guard(device);

@@ -57,6 +57,8 @@ struct DecodeLaunch {
     long long workspace_numel; // F32 elements bound as the workspace (the checked build's bound)
     int32_t test_skip_page; // tests of the give-up path: 1 + the page of a CTA's chunk whose
                             // bytes never all arrive (0 = none)
+    int32_t producer_warps; // balanced plans: 1, or one per page slot
+    int32_t *counters;      // one zeroed word per item when the split is merged in the kernel
     PeerOut peer;           // zeroed unless the plan gathers its output
     PeerSignal signal;      // zeroed unless this launch is the last kernel of a gathering command
 };

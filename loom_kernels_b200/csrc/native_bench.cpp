@@ -457,21 +457,25 @@ int main(int argc, char **argv) {
                            {1, 4, 16}, {128, 256, 512});
     PrefillCase p_gqa_long("gate prefill gqa4_b2_q32_64_kv256_1024 16/4", prefill, 16, 4, {32, 64},
                            {256, 1024});
-    // C1 with the plan's parameters pinned (heads per CTA, chunks, one- or two-command split): the
-    // measurements behind the plan-time rule for a single short request
+    // C1 with the plan's parameters pinned (heads per CTA, chunks, cluster / in-kernel merge /
+    // two-command split): the measurements behind the plan-time rule for a single short request
     std::vector<DecodeCase *> c1_variants;
     if (!opt.only.empty() && opt.only.find("C1") == 0) {
-        const uint32_t grid[][3] = {{4, 8, 1}, {2, 8, 1}, {1, 4, 1}, {4, 8, 0},
-                                    {4, 9, 0}, {2, 4, 1}, {4, 4, 1}};
+        // {heads per CTA, chunks, cluster, merge_in_kernel}
+        const uint32_t grid[][4] = {{4, 8, 1, 0}, {4, 8, 0, 1}, {4, 16, 0, 1}, {2, 8, 0, 1},
+                                    {4, 9, 0, 0}, {4, 18, 0, 0}, {1, 4, 1, 0}, {2, 8, 1, 0}};
         for (const auto &g : grid) {
             lb_paged_decode_options o{};
             o.heads_per_cta = g[0];
             o.partitions = g[1];
             o.cluster = g[2];
+            o.merge_in_kernel = g[3];
             char label[160];
             std::snprintf(label, sizeof(label),
                           "C1 variant hc%u x %u chunks, %s", g[0], g[1],
-                          g[2] ? "cluster (1 command)" : "workspace (2 commands)");
+                          g[2]        ? "cluster (1 command)"
+                          : g[3] == 1 ? "workspace, merged by the last CTA (1 command)"
+                                      : "workspace, merge command (2 commands)");
             c1_variants.push_back(new DecodeCase(label, decode, 1, 256, 32, 32, {0, 64}, c1_pages,
                                                  {16}, 0, &o));
         }

@@ -109,11 +109,14 @@ void fill_info(const DecodeChoice &c, lb_paged_decode_plan_info *info) {
     info->shared_bytes = c.shared_bytes;
     info->merge_grid = c.merge_grid;
     info->merge_block = c.merge_block;
-    info->commands =
-        c.algorithm == LB_DECODE_DIRECT || c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 2;
+    info->commands = c.algorithm == LB_DECODE_DIRECT || c.algorithm == LB_DECODE_CLUSTER_SPLIT ||
+                             c.merged_in_kernel
+                         ? 1
+                         : 2;
     info->workspace_numel = c.workspace_numel;
     info->workspace_bytes = c.workspace_numel * sizeof(float);
-    info->reserved[0] = info->reserved[1] = 0;
+    info->merged_in_kernel = c.merged_in_kernel;
+    info->reserved = 0;
 }
 
 } // namespace
@@ -266,11 +269,12 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     const lb_paged_spec &spec = plan->spec;
     const DecodeChoice &c = plan->choice;
     const bool balanced = c.algorithm == LB_DECODE_BALANCED;
-    const bool split = c.algorithm == LB_DECODE_SPLIT_K || balanced; // two commands, a workspace
+    const bool split = c.algorithm == LB_DECODE_SPLIT_K || balanced; // states in a workspace
+    const bool merge_command = split && !c.merged_in_kernel;          // ... merged by a second command
     if (scope->queue->device != plan->device)
         return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
     // both commands of a split plan must fit before anything is launched (decode.rs:1327)
-    lb_status rc = require_command_capacity(*scope, split ? 2 : 1);
+    lb_status rc = require_command_capacity(*scope, merge_command ? 2 : 1);
     if (rc) return rc;
 
     // operand 8 is the workspace of a split plan, else the row map of a gathering enqueue
@@ -363,6 +367,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     launch.partitions = (int32_t)c.partitions;
     launch.stages = (int32_t)c.stages;
     launch.cluster = c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 0;
+    launch.producer_warps = (int32_t)c.producer_warps;
     launch.scale_log2 = spec.softmax_scale * kLog2E;
     launch.grid = c.grid;
     launch.block = c.block;
@@ -387,15 +392,16 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
         signal.defer = gather->layout->defer_wait ? 1 : 0;
     }
     // rows leave from the kernel that finishes them; the command's last kernel signals
-    if (c.algorithm != LB_DECODE_SPLIT_K) launch.peer = peer;
-    if (!split) launch.signal = signal;
+    if (c.algorithm != LB_DECODE_SPLIT_K || c.merged_in_kernel) launch.peer = peer;
+    if (!merge_command) launch.signal = signal;
+    if (c.merged_in_kernel) launch.counters = scope->queue->sync_words;
     void *stream = scope->queue->stream;
     if ((rc = submit_launch(*scope, [&]() {
              return balanced ? launch_balanced_decode(launch, stream)
                              : launch_paged_decode(launch, stream);
          })))
         return rc;
-    if (!split) return LB_OK;
+    if (!merge_command) return LB_OK;
 
     // second command: workspace is now a read operand (decode.rs:1374-1388)
     OperandRequest merge_requests[3] = {

@@ -41,7 +41,12 @@ struct lb_queue { // CommandQueue
     bool busy = false; // a scope or completion borrowed from this queue is alive
     bool orphaned = false; // lb_queue_destroy came while busy: the borrower destroys the queue
     bool owns_stream = false;
+    // kQueueSyncWords device words, zero whenever no command of this queue is running: kernels
+    // that count their CTAs (a split merged by its last CTA) use them and leave them zero.  The
+    // queue's stream orders its commands, so no two kernels use the words at the same time.
+    int32_t *sync_words = nullptr;
 };
+constexpr size_t kQueueSyncWords = 16384;
 
 struct lb_scope { // CommandScope
     lb_queue *queue = nullptr;
@@ -167,6 +172,8 @@ struct DecodeChoice {
     uint32_t partitions, heads_per_cta, q_tiles, q_blocks, pages_per_stage, stages, warps;
     uint32_t grid, block, shared_bytes, merge_grid, merge_block;
     size_t workspace_numel;
+    uint32_t producer_warps;   // balanced plans: warps that issue the page copies
+    uint32_t merged_in_kernel; // split-K as one command: the last CTA of an item merges it
 };
 lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t smem_optin,
                         const lb_paged_decode_options *options, DecodeChoice *out);

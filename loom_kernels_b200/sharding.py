@@ -10,8 +10,12 @@ is partitioned
   * by KV head when batch < GPUs and the GPU count divides kv_heads: rank g owns a contiguous
     block of KV heads (and their query heads) of every request.
 
-Each rank builds its own spec, plan, queue and bindings; nothing is shared.  NCCL is used only by
-`gather_output_rows`, when the caller wants one contiguous result.  A ragged prefill batch is
+Each rank builds its own spec, plan, queue and bindings; nothing is shared.  When the caller wants
+one contiguous result on every rank there are three ways, in order of cost: a gathering decode
+command (`Bf16PagedBatchDecodePlan.enqueue_gathered_into` over an `api.PeerGroup`: the kernel that
+finishes a row stores it into every rank's result), the all-gather as a command of the same scope
+(`api.OutputGatherPlan`, NCCL on the queue's stream), or `gather_output_rows` here, a
+`torch.distributed` all-gather after the completion fence.  A ragged prefill batch is
 partitioned the same way, by request, with the causal pair count as the weight
 (`prefill_assignment`, `shard_prefill`).
 """

@@ -39,7 +39,8 @@ def main():
     g_out = [group.buffer(batch * qh * 128, lk.BF16) for _ in range(2)]
     g_lse = [group.buffer(batch * qh, lk.F32) for _ in range(2)]
     step = 0
-    for options in ({"partitions": 1}, {"partitions": 3}, {"balanced": 1}):
+    for options in ({"partitions": 1}, {"partitions": 3}, {"partitions": 3, "merge_in_kernel": 1},
+                    {"balanced": 1, "merge_in_kernel": 2}, {"balanced": 1, "merge_in_kernel": 1}):
         run = H.DecodeRun(spec, q, k, v, indptr, indices, last, device=device, provider=provider,
                           max_commands=4, **options)
         plain_out, plain_lse = run.run()

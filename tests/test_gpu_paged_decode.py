@@ -32,8 +32,10 @@ def fixture_case(oracle, case):
 
 
 @pytest.mark.parametrize("name", ["mha_b1_l1", "mqa_b3_mixed", "gqa4_b4_reuse"])
-@pytest.mark.parametrize("partitions", [1, 2, 3])
-def test_reference_gate_cases(oracle, provider, name, partitions):
+@pytest.mark.parametrize("partitions,merge_in_kernel", [(1, 0), (2, 0), (3, 0), (2, 1), (3, 1)])
+def test_reference_gate_cases(oracle, provider, name, partitions, merge_in_kernel):
+    # split plans in both forms: merged by a second command (the reference's form) and by the
+    # last CTA of an item (merge_in_kernel=1, one command)
     case = GOLDEN["paged_decode"]["cases"][name]
     batch, pages, qh, kvh = case["spec"]
     if partitions > pages:
@@ -41,9 +43,9 @@ def test_reference_gate_cases(oracle, provider, name, partitions):
     spec = lk.Bf16PagedBatchDecodeSpec.new(batch, pages, qh, kvh)
     q, k, v = fixture_case(oracle, case)
     run = H.DecodeRun(spec, q, k, v, case["indptr"], case["indices"], case["last"],
-                      partitions=partitions, provider=provider)
+                      partitions=partitions, provider=provider, merge_in_kernel=merge_in_kernel)
     out, lse = run.run()
-    assert run.submitted == (1 if partitions == 1 else 2)
+    assert run.submitted == (2 if partitions > 1 and merge_in_kernel != 1 else 1)
     if partitions == 1:  # and once more through the heuristic's choice for this shape
         auto = H.DecodeRun(spec, q, k, v, case["indptr"], case["indices"], case["last"],
                            provider=provider)
@@ -125,13 +127,23 @@ def test_random_ragged_batches(oracle, provider, batch, qh, kvh, hc, partitions)
     ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced=2)
 
 
+@pytest.mark.parametrize("batch,qh,kvh,hc,partitions", [s for s in SHAPES if s[4] > 1])
+def test_random_ragged_batches_split_merged_in_kernel(oracle, provider, batch, qh, kvh, hc,
+                                                      partitions):
+    ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced=2, merge_in_kernel=1)
+
+
+@pytest.mark.parametrize("merge_in_kernel", [1, 2])
 @pytest.mark.parametrize("batch,qh,kvh,hc,partitions", SHAPES)
-def test_random_ragged_batches_balanced(oracle, provider, batch, qh, kvh, hc, partitions):
-    # the same batches through the page-balanced algorithm (pages cut evenly over the SMs)
-    ragged_case(oracle, provider, batch, qh, kvh, hc, 0, balanced=1)
+def test_random_ragged_batches_balanced(oracle, provider, batch, qh, kvh, hc, partitions,
+                                        merge_in_kernel):
+    # the same batches through the page-balanced algorithm (pages cut evenly over the SMs), the
+    # cut items merged in the decode kernel (1) or by the merge kernel (2)
+    ragged_case(oracle, provider, batch, qh, kvh, hc, 0, balanced=1,
+                merge_in_kernel=merge_in_kernel)
 
 
-def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced):
+def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced, merge_in_kernel=0):
     rng = np.random.default_rng(batch * 1000 + qh * 10 + kvh + hc + partitions)
     pool = 96
     kv_lens = rng.integers(1, 16 * 18, size=batch)
@@ -150,11 +162,21 @@ def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced):
         vr[page, last[r]:] = 0x7FC0
     q = H.normal_bf16(rng, spec.query_numel())
     run = H.DecodeRun(spec, q, k, v, indptr, indices, last, partitions=partitions,
-                      heads_per_cta=hc, provider=provider, balanced=balanced)
+                      heads_per_cta=hc, provider=provider, balanced=balanced,
+                      merge_in_kernel=merge_in_kernel)
     if balanced == 1:
         assert run.plan.algorithm() == lk.Bf16PagedBatchDecodeAlgorithm.Balanced
+    if partitions > 1 or balanced == 1:
+        assert run.plan.merged_in_kernel() == (merge_in_kernel == 1)
+        assert run.plan.commands() == (1 if merge_in_kernel == 1 else 2)
     out, lse = run.run()
     assert run.submitted == run.plan.commands()
+    if run.plan.merged_in_kernel():
+        # the items' counting words are back at zero: the same queue serves the next call, with
+        # the output reset in between so that stale rows cannot pass
+        run.out.fill_(float("nan"))
+        again_out, again_lse = run.run()
+        assert np.array_equal(again_out, out) and np.array_equal(again_lse, lse)
     ospec = oracle.paged_spec(batch, pool, qh, kvh)
     eo, el = oracle.paged_decode(ospec, q, k, v, indptr, indices, last, threads=4)
     H.check_decode(out, lse, eo, el, lse_limit=H.SPLIT_LSE_MAX_ABS)
@@ -331,7 +353,11 @@ def test_plan_is_immutable_and_reports_its_shape(provider):
     assert plan.commands() == 1 and plan.workspace_required_numel() == 0
     plan = provider.plan_bf16_paged_batch(lk.Bf16PagedBatchDecodeSpec.new(8, 20000, 64, 8),
                                           partitions=16)
-    assert plan.commands() == 2 and plan.partitions() == 16
+    assert plan.commands() == 2 and not plan.merged_in_kernel() and plan.partitions() == 16
+    assert plan.workspace_required_bytes() == 8 * 64 * 16 * 130 * 4
+    plan = provider.plan_bf16_paged_batch(lk.Bf16PagedBatchDecodeSpec.new(8, 20000, 64, 8),
+                                          partitions=16, merge_in_kernel=1)
+    assert plan.commands() == 1 and plan.merged_in_kernel()
     assert plan.workspace_required_bytes() == 8 * 64 * 16 * 130 * 4
     with pytest.raises(lk.PlanError):
         provider.plan_bf16_paged_batch(spec, heads_per_cta=3)

@@ -31,6 +31,8 @@ def group():
 
 
 @pytest.mark.parametrize("options", [{"partitions": 1}, {"partitions": 3}, {"balanced": 1},
+                                     {"partitions": 3, "merge_in_kernel": 1},
+                                     {"balanced": 1, "merge_in_kernel": 1},
                                      {"partitions": 1, "heads_per_cta": 1}])
 @pytest.mark.parametrize("batch,qh,kvh", [(5, 32, 8), (3, 8, 1), (2, 40, 2), (4, 16, 16)])
 def test_gathered_rows_equal_the_plain_result(oracle, group, options, batch, qh, kvh):

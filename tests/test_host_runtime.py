@@ -138,13 +138,33 @@ def test_plan_heuristic_is_fixed_by_spec_and_device():
     # left to itself the plan cuts a batch smaller than the device by pages, one CTA per SM
     auto = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148)
     assert (auto.algorithm, auto.commands, auto.grid, auto.heads_per_cta) == (2, 2, 148, 8)
+    assert auto.merged_in_kernel == 0 and auto.merge_grid == 512
     assert auto.workspace_numel == 148 * 2 * 8 * 4 * 130 + 64 + 8
+    # on request the cut items are merged in the decode kernel: one command, the same workspace
+    one = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148,
+                                 merge_in_kernel=1)
+    assert (one.algorithm, one.commands, one.merged_in_kernel, one.merge_grid) == (2, 1, 1, 0)
+    assert one.workspace_numel == auto.workspace_numel
+    # few requests on many workers: dozens of states per item, a CTA of the merge kernel each
+    few = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(32, 65536, 32, 1), 148)
+    assert (few.algorithm, few.commands, few.merged_in_kernel, few.merge_grid) == (2, 2, 0, 1024)
     many = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(4096, 65536, 32, 8), 148)
     assert (many.algorithm, many.commands) == (0, 1)  # thousands of requests tile the device
     c4 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(8, 20000, 64, 8), 148,
                                 partitions=16)
-    assert (c4.partitions, c4.algorithm, c4.commands) == (16, 1, 2)
+    assert (c4.partitions, c4.algorithm, c4.commands, c4.merged_in_kernel) == (16, 1, 2, 0)
     assert c4.workspace_numel == 8 * 64 * 16 * 130 and c4.merge_grid == 8 * 64 // 4
+    # on request the last CTA of every item merges it: one command, the workspace stays
+    one = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(8, 20000, 64, 8), 148,
+                                 partitions=16, merge_in_kernel=1)
+    assert (one.commands, one.merged_in_kernel, one.merge_grid) == (1, 1, 0)
+    assert one.workspace_numel == c4.workspace_numel
+    with pytest.raises(lk.PlanError):  # more items than a queue has counting words
+        lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(40000, 2000000, 8, 8), 148,
+                               partitions=2, heads_per_cta=8, merge_in_kernel=1)
+    with pytest.raises(lk.PlanError):  # nothing to merge
+        lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(64, 20000, 32, 8), 148,
+                               partitions=1, merge_in_kernel=1)
     c1 = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(1, 256, 32, 32), 148, balanced=2)
     assert c1.partitions > 1 and c1.grid >= 64  # one request cannot fill 148 SMs unsplit
     mqa = lk.choose_paged_decode(lk.Bf16PagedBatchDecodeSpec.new(256, 65536, 32, 1), 148)
@@ -302,6 +322,19 @@ def test_split_plan_reserves_both_commands_and_checks_workspace(fake):
                                                          workspace=ws, **h))
     assert fake.lb_test_launch_count() - before == 2
     assert scope.finish().submitted() == 2
+    # merged by the last CTA of every item: one command, same workspace
+    fused = provider.plan_bf16_paged_batch(spec, partitions=3, merge_in_kernel=1)
+    assert fused.commands() == 1 and fused.merged_in_kernel()
+    assert fused.workspace_required_numel() == 4 * 16 * 3 * 130
+    queue = lk.CommandQueue(0x100, 1)
+    b, h, out, lse = decode_setup(queue, spec, capacity=9)
+    ws = b.bind_read_write(D(0x30000000, 4 * 16 * 3 * 130, _abi.F32))
+    scope = queue.begin(b)
+    before = fake.lb_test_launch_count()
+    fused.enqueue_into(scope, lk.Bf16PagedBatchDecodeArgs(output=out.write(), lse=lse.write(),
+                                                          workspace=ws, **h))
+    assert fake.lb_test_launch_count() - before == 1
+    assert scope.finish().submitted() == 1
 
 
 def test_launch_failure_poisons_scope_and_queue(fake):
@@ -679,7 +712,8 @@ def test_gathering_commands_under_the_fake_driver(fake):
               if plan.workspace_required_numel() else None)
         return reads, ws
 
-    for options, commands in (({"partitions": 1}, 1), ({"partitions": 4}, 2), ({"balanced": 1}, 2)):
+    for options, commands in (({"partitions": 1}, 1), ({"partitions": 4}, 2),
+                              ({"partitions": 4, "merge_in_kernel": 1}, 1), ({"balanced": 1}, 2)):
         plan = provider.plan_bf16_paged_batch(spec, **options)
         b = queue.bindings(12)
         reads, ws = bind(b, plan)
