@@ -537,7 +537,11 @@ lb_status lb_rope_provider_device_status(const lb_rope_provider *provider, int32
 /* Plan options of the append (NULL = all zero). */
 typedef struct lb_rope_append_options {
     uint32_t indices_capacity; /* as lb_paged_decode_options.indices_capacity */
-    uint32_t reserved[3];
+    uint32_t one_command;      /* extended (any-total) plans: 1 = validation and scatter in ONE
+                                  kernel whose token CTAs wait for the validators on words of
+                                  the queue (calls whose whole grid is resident at once: up to
+                                  2048 tokens); 0 = two commands, which measured faster */
+    uint32_t reserved[2];
 } lb_rope_append_options;
 /* RopeProvider::plan_bf16_paged_append, rope/mod.rs:628-654 */
 lb_status lb_rope_append_plan_create(const lb_rope_provider *provider, const lb_paged_spec *spec,

@@ -58,7 +58,8 @@ class DecodeOptions(ctypes.Structure):
 
 
 class AppendOptions(ctypes.Structure):
-    _fields_ = [("indices_capacity", c_uint32), ("reserved", c_uint32 * 3)]
+    _fields_ = [("indices_capacity", c_uint32), ("one_command", c_uint32),
+                ("reserved", c_uint32 * 2)]
 
 
 class DecodePlanInfo(ctypes.Structure):

@@ -917,9 +917,12 @@ class RopeProvider:
         return Bf16RopePagedKvAppendPlan(out.value, spec)
 
     def plan_bf16_paged_append_tokens(self, spec: Bf16RopePagedKvAppendTokensSpec,
-                                      indices_capacity: bool = False):
+                                      indices_capacity: bool = False, one_command: bool = False):
+        """one_command (extended specs of up to 2048 tokens): validation and scatter in one kernel
+        whose token CTAs wait for the validators, instead of two commands."""
         out = c_void_p()
-        options = _abi.AppendOptions(indices_capacity=1 if indices_capacity else 0)
+        options = _abi.AppendOptions(indices_capacity=1 if indices_capacity else 0,
+                                     one_command=1 if one_command else 0)
         _check(_abi.load().lb_rope_append_tokens_plan_create_with(
             self._ptr, byref(spec._raw), byref(options), byref(out)))
         return Bf16RopePagedKvAppendTokensPlan(out.value, spec)

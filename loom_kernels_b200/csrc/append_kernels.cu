@@ -359,63 +359,64 @@ constexpr int kVerdictSlots = 32;
 constexpr int kValidateThreads = 1024;
 constexpr int kScatterThreads = 256;
 
-__global__ void __launch_bounds__(kValidateThreads)
-append_validate_kernel(const AppendArgs a, int32_t *workspace) {
-    extern __shared__ int hash_table[];
-    dev::dependent_launch_wait();    // the inputs may come from the command before this one
-    dev::dependent_launch_release(); // from here on everything before this command is complete
+// The validation of one call by validator CTA `cta` of `ctas` (`threads` threads each): true when
+// this CTA found something invalid.  CTA 0 maps the tokens into the workspace.
+// kTokens: tokens whose dependent loads one thread keeps in flight per round of the mapping.
+template <int kTokens>
+__device__ __forceinline__ bool validate_call(const AppendArgs &a, int32_t *workspace, int cta,
+                                              int ctas, int threads, int *hash_table) {
     const int tid = threadIdx.x;
     bool invalid = false;
-    if (blockIdx.x > 0 || gridDim.x == 1) {
+    if (cta > 0 || ctas == 1) {
         // page-table and request checks, sliced over the scanning CTAs
-        const int scanners = gridDim.x == 1 ? 1 : (int)gridDim.x - 1;
-        const int me = gridDim.x == 1 ? 0 : (int)blockIdx.x - 1;
+        const int scanners = ctas == 1 ? 1 : ctas - 1;
+        const int me = ctas == 1 ? 0 : cta - 1;
         const int final_indptr = a.indptr[a.batch]; // must lie in [indices_min, indices_len]
         invalid = a.indptr[0] != 0 || final_indptr < a.indices_min || final_indptr > a.indices_len;
         int table_end = a.indices_len;
         if (a.indices_min != a.indices_len) table_end = min(max(final_indptr, 0), a.indices_len);
-        for (int request = me * kValidateThreads + tid; request < a.batch;
-             request += scanners * kValidateThreads) {
+        for (int request = me * threads + tid; request < a.batch;
+             request += scanners * threads) {
             const int begin = a.indptr[request], end = a.indptr[request + 1];
             const int tail = a.last[request];
             if (begin < 0 || end <= begin || end > table_end || tail < 1 || tail > kPage)
                 invalid = true;
         }
-        for (int base = me * 4 * kValidateThreads; base < table_end;
-             base += scanners * 4 * kValidateThreads) {
+        for (int base = me * 4 * threads; base < table_end;
+             base += scanners * 4 * threads) {
             int id[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int page = base + u * kValidateThreads + tid;
+                const int page = base + u * threads + tid;
                 id[u] = page < table_end ? a.indices[page] : 0;
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
         }
     }
-    if (blockIdx.x == 0) {
-        for (int i = tid; i < a.hash_slots; i += kValidateThreads) hash_table[i] = -1;
-        if (tid >= (int)gridDim.x && tid < kVerdictSlots) workspace[tid] = 0; // unused verdicts
+    if (cta == 0) {
+        for (int i = tid; i < a.hash_slots; i += threads) hash_table[i] = -1;
+        if (tid >= ctas && tid < kVerdictSlots) workspace[tid] = 0; // unused verdicts
         __syncthreads();
-        for (int base = 0; base < a.tokens; base += 4 * kValidateThreads) {
-            int position[4], start[4], slot[4];
-            bool ok[4];
+        for (int base = 0; base < a.tokens; base += kTokens * threads) {
+            int position[kTokens], start[kTokens], slot[kTokens];
+            bool ok[kTokens];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int token = base + u * kValidateThreads + tid;
+            for (int u = 0; u < kTokens; ++u) {
+                const int token = base + u * threads + tid;
                 position[u] = start[u] = 0;
                 ok[u] = token < a.tokens ? token_request(a, token, position[u], start[u]) : false;
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kTokens; ++u) {
                 // the table itself is being checked elsewhere: stay inside page_indices
                 const long long page = (long long)start[u] + position[u] / kPage;
                 ok[u] = ok[u] && page >= 0 && page < a.indices_len;
                 slot[u] = a.indices[ok[u] ? (int)page : 0] * kPage + position[u] % kPage;
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int token = base + u * kValidateThreads + tid;
+            for (int u = 0; u < kTokens; ++u) {
+                const int token = base + u * threads + tid;
                 if (token >= a.tokens) continue;
                 if (in_bounds(kVerdictSlots + 2 * token + 1, a.workspace_numel, a.status,
                               dev::kSiteAppendWorkspace)) {
@@ -439,8 +440,63 @@ append_validate_kernel(const AppendArgs a, int32_t *workspace) {
             }
         }
     }
+    return invalid;
+}
+
+__global__ void __launch_bounds__(kValidateThreads)
+append_validate_kernel(const AppendArgs a, int32_t *workspace) {
+    extern __shared__ int hash_table[];
+    dev::dependent_launch_wait();    // the inputs may come from the command before this one
+    dev::dependent_launch_release(); // from here on everything before this command is complete
+    const bool invalid = validate_call<4>(a, workspace, (int)blockIdx.x, (int)gridDim.x,
+                                          kValidateThreads, hash_table);
     const int verdict = __syncthreads_or(invalid);
-    if (tid == 0) workspace[blockIdx.x] = verdict;
+    if (threadIdx.x == 0) workspace[blockIdx.x] = verdict;
+}
+
+// One token of an any-total call, in two steps: fetch its rows, rotate-ready, into registers and
+// build its sin/cos table (from in-bounds loads only, before the verdict is known), then store.
+struct ScatterRows {
+    uint4 lo[2], hi[2], v;
+};
+
+__device__ __forceinline__ void scatter_fetch(const AppendArgs &a, int token, int tid,
+                                              ScatterRows &rows, float2 *table) {
+    const int row_tasks = (a.qh + a.kvh) * 8, copy_tasks = a.kvh * 16;
+    rows.v = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int task = tid + i * kScatterThreads;
+        rows.lo[i] = rows.hi[i] = make_uint4(0, 0, 0, 0);
+        if (task < row_tasks) {
+            const uint4 *src = row_source(a, token, task >> 3);
+            rows.lo[i] = src[task & 7];
+            rows.hi[i] = src[8 + (task & 7)];
+        }
+    }
+    if (tid < copy_tasks) rows.v = a.value[(size_t)token * copy_tasks + tid];
+    if (tid < kPairs) table[tid] = pair_sincos(speculative_position(a, token), tid);
+}
+
+__device__ __forceinline__ void scatter_store(const AppendArgs &a, int token, int slot, int tid,
+                                              const ScatterRows &rows, const float2 *table) {
+    const int row_tasks = (a.qh + a.kvh) * 8, copy_tasks = a.kvh * 16;
+    if (!in_bounds(slot, (long long)a.max_pages * kPage, a.status, dev::kSiteAppendPool)) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int task = tid + i * kScatterThreads;
+        if (task < row_tasks)
+            rotate_row(rows.lo[i], rows.hi[i], row_destination(a, token, slot, task >> 3), task & 7,
+                       table);
+    }
+    for (int task = tid + 2 * kScatterThreads; task < row_tasks; task += kScatterThreads) {
+        const uint4 *src = row_source(a, token, task >> 3);
+        rotate_row(src[task & 7], src[8 + (task & 7)], row_destination(a, token, slot, task >> 3),
+                   task & 7, table);
+    }
+    if (tid < copy_tasks) a.value_pages[(size_t)slot * copy_tasks + tid] = rows.v;
+    for (int task = tid + kScatterThreads; task < copy_tasks; task += kScatterThreads)
+        a.value_pages[(size_t)slot * copy_tasks + task] = a.value[(size_t)token * copy_tasks + task];
 }
 
 __global__ void __launch_bounds__(kScatterThreads, 8)
@@ -449,43 +505,108 @@ append_scatter_kernel(const AppendArgs a, const int32_t *workspace) {
     dev::dependent_launch_release();
     const int tid = threadIdx.x;
     const int token = blockIdx.x;
-    const int row_tasks = (a.qh + a.kvh) * 8, copy_tasks = a.kvh * 16;
     // The validation kernel released this one only after everything before the call had
     // completed, so the call's inputs are final: fetch, rotate and keep the result in registers.
-    uint4 lo[2], hi[2], v = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int task = tid + i * kScatterThreads;
-        lo[i] = hi[i] = make_uint4(0, 0, 0, 0);
-        if (task < row_tasks) {
-            const uint4 *src = row_source(a, token, task >> 3);
-            lo[i] = src[task & 7];
-            hi[i] = src[8 + (task & 7)];
-        }
-    }
-    if (tid < copy_tasks) v = a.value[(size_t)token * copy_tasks + tid];
-    if (tid < kPairs) table[tid] = pair_sincos(speculative_position(a, token), tid);
+    ScatterRows rows;
+    scatter_fetch(a, token, tid, rows, table);
     __syncthreads();
     dev::dependent_launch_wait(); // the verdicts and this token's slot are final
     // the slot travels with the verdicts (one round trip, not two); it is used only if they agree
     const int slot = __ldcg(workspace + kVerdictSlots + 2 * token + 1);
     const int verdict = __syncthreads_or(tid < kVerdictSlots ? __ldcg(workspace + tid) : 0);
     if (verdict != 0) return;
-    if (!in_bounds(slot, (long long)a.max_pages * kPage, a.status, dev::kSiteAppendPool)) return;
+    scatter_store(a, token, slot, tid, rows, table);
+}
+
+// ---- the any-total append as ONE command ---------------------------------------------------------
+//
+// The same two roles in one grid: the first `validators` CTAs validate (CTA 0 maps the tokens into
+// the workspace), every other CTA owns tokens.  A token CTA fetches and prepares its first token
+// while the validators work, then waits -- bounded -- for their verdicts on words of the queue
+// (0 = not yet, 1 = nothing wrong, 2 = invalid) instead of for the end of a kernel, and stores.
+// The plan sizes the grid so that every CTA is resident at once, so a waiting CTA never keeps a
+// validator off the GPU.  The last CTA of the grid to finish hands the words back as zeros; the
+// queue's stream orders the next command after that.
+constexpr long long kVerdictWaitCycles = 4000000000ll; // ~2 s of SM clock
+
+__device__ __forceinline__ int load_acquire_gpu(const int32_t *p) {
+    int value;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(value) : "l"(p) : "memory");
+    return value;
+}
+
+// (Four CTAs per SM: the validators' code shares the kernel's register budget and spills at the
+// 32 registers that eight CTAs would leave; a token CTA holds two tokens ahead of the verdict
+// instead, so a call of up to 2 x 4 x SMs tokens is still one round.)
+constexpr int kFusedTokensAhead = 2;
+
+__global__ void __launch_bounds__(kScatterThreads, 4)
+append_fused_kernel(const AppendArgs a, int32_t *workspace, int32_t *words, int validators) {
+    extern __shared__ int hash_table[];
+    __shared__ __align__(16) float2 table[kFusedTokensAhead][kPairs];
+    dev::dependent_launch_release();
+    dev::dependent_launch_wait(); // global memory (and the queue's words) from here on
+    const int tid = threadIdx.x;
+    if ((int)blockIdx.x < validators) {
+        // (eight tokens per thread: a quarter of the validation kernel's threads map a call of
+        // up to 2048 tokens in one round of dependent loads all the same)
+        const bool invalid = validate_call<8>(a, workspace, (int)blockIdx.x, validators,
+                                              kScatterThreads, hash_table);
+        // (the barrier orders every thread's workspace stores before the release below)
+        const int verdict = __syncthreads_or(invalid);
+        if (tid == 0) {
+            __threadfence();
+            atomicExch(words + blockIdx.x, verdict ? 2 : 1);
+        }
+    } else {
+        const int token_ctas = (int)gridDim.x - validators;
+        int token = (int)blockIdx.x - validators;
+        ScatterRows rows[kFusedTokensAhead];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int task = tid + i * kScatterThreads;
-        if (task < row_tasks)
-            rotate_row(lo[i], hi[i], row_destination(a, token, slot, task >> 3), task & 7, table);
+        for (int i = 0; i < kFusedTokensAhead; ++i)
+            if (token + i * token_ctas < a.tokens)
+                scatter_fetch(a, token + i * token_ctas, tid, rows[i], table[i]);
+        int seen = 1;
+        if (tid < validators) {
+            const long long start = clock64();
+            while ((seen = load_acquire_gpu(words + tid)) == 0) {
+                if (clock64() - start > kVerdictWaitCycles) break;
+                __nanosleep(64); // (hundreds of CTAs poll the same few words)
+            }
+        }
+        // (the barrier also publishes the sin/cos table and carries the acquire to every thread)
+        const int bad = __syncthreads_or(seen != 1);
+        if (bad) {
+            if (seen == 0 && a.status) atomicExch(a.status, 1); // a wait ran out
+        } else {
+            int slot[kFusedTokensAhead];
+#pragma unroll
+            for (int i = 0; i < kFusedTokensAhead; ++i)
+                slot[i] = token + i * token_ctas < a.tokens
+                              ? __ldcg(workspace + kVerdictSlots + 2 * (token + i * token_ctas) + 1)
+                              : 0;
+#pragma unroll
+            for (int i = 0; i < kFusedTokensAhead; ++i)
+                if (token + i * token_ctas < a.tokens)
+                    scatter_store(a, token + i * token_ctas, slot[i], tid, rows[i], table[i]);
+            // (a grid smaller than half the call: the rest one token at a time)
+            for (token += kFusedTokensAhead * token_ctas; token < a.tokens; token += token_ctas) {
+                __syncthreads(); // table[0] has been used by everybody
+                scatter_fetch(a, token, tid, rows[0], table[0]);
+                __syncthreads();
+                scatter_store(a, token, __ldcg(workspace + kVerdictSlots + 2 * token + 1), tid,
+                              rows[0], table[0]);
+            }
+        }
     }
-    for (int task = tid + 2 * kScatterThreads; task < row_tasks; task += kScatterThreads) {
-        const uint4 *src = row_source(a, token, task >> 3);
-        rotate_row(src[task & 7], src[8 + (task & 7)], row_destination(a, token, slot, task >> 3),
-                   task & 7, table);
+    // the last CTA to get here leaves the words as it found them: zero
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned done =
+            atomicInc(reinterpret_cast<unsigned *>(words) + kVerdictSlots, gridDim.x - 1);
+        if (done == gridDim.x - 1)
+            for (int v = 0; v < validators; ++v) words[v] = 0;
     }
-    if (tid < copy_tasks) a.value_pages[(size_t)slot * copy_tasks + tid] = v;
-    for (int task = tid + kScatterThreads; task < copy_tasks; task += kScatterThreads)
-        a.value_pages[(size_t)slot * copy_tasks + task] = a.value[(size_t)token * copy_tasks + task];
 }
 
 // Stand-alone NeoX RoPE over contiguous NHD Q and K (the reference's rope_pos_ids_bf16_neox_d128,
@@ -594,6 +715,17 @@ int append_workspace_numel(size_t tokens) { return (int)(kVerdictSlots + 2 * tok
 int launch_append_validate(const AppendLaunch &launch, void *stream) {
     return launch_dependent(append_validate_kernel, launch.validate_grid, kValidateThreads,
                             launch.shared_bytes, stream, append_args(launch), launch.workspace);
+}
+
+int append_fused_ctas_per_sm(int *ctas, size_t shared_bytes) {
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas, append_fused_kernel,
+                                                         kScatterThreads, shared_bytes);
+}
+
+int launch_append_fused(const AppendLaunch &launch, void *stream) {
+    return launch_dependent(append_fused_kernel, launch.grid, kScatterThreads, launch.shared_bytes,
+                            stream, append_args(launch), launch.workspace, launch.words,
+                            (int)launch.validate_grid);
 }
 
 int launch_append_scatter(const AppendLaunch &launch, void *stream) {

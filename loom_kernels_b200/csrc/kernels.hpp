@@ -91,7 +91,8 @@ struct AppendLaunch {
     int32_t *workspace;
     uint32_t validate_grid;
     int32_t workspace_numel; // I32 elements of `workspace` (the checked build's bound)
-    int32_t *status;         // optional device status word (written by the checked build only)
+    int32_t *status;         // optional device status word (the checked build; a wait that ran out)
+    int32_t *words;          // one-command extended plans: the queue's synchronisation words
 };
 
 // Each returns a CUDA error code (0 = success).
@@ -109,6 +110,9 @@ int launch_rope_append(const AppendLaunch &launch, void *stream);
 int append_workspace_numel(size_t tokens);
 int launch_append_validate(const AppendLaunch &launch, void *stream);
 int launch_append_scatter(const AppendLaunch &launch, void *stream);
+// One-command form: launch.grid = launch.validate_grid validators + token CTAs, all resident at once.
+int launch_append_fused(const AppendLaunch &launch, void *stream);
+int append_fused_ctas_per_sm(int *ctas, size_t shared_bytes); // occupancy of that kernel
 // One stand-alone RoPE launch over contiguous NHD Q and K.
 struct RopeLaunch {
     const void *query, *key;   // bf16 [tokens, heads, 128]

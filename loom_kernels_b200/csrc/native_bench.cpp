@@ -270,10 +270,10 @@ struct AppendCase : Case {
     size_t workspace_numel = 0;
 
     // request r appends new_tokens[r] tokens after prior[r] existing ones; pages in order.
-    // extended: no 64-token cap on the call (two commands: validate, then rotate and scatter)
+    // extended: no 64-token cap on the call (validate and scatter as two commands, or as one)
     AppendCase(const char *label, lb_rope_provider *provider, size_t pool_pages, size_t qh,
                size_t kvh, const std::vector<int> &new_tokens, const std::vector<int> &prior,
-               bool extended = false) {
+               bool extended = false, bool one_command = false) {
         name = label;
         const size_t batch = new_tokens.size();
         std::vector<int32_t> page_indptr{0}, page_indices, last_page_len, owner, position;
@@ -297,7 +297,9 @@ struct AppendCase : Case {
         else
             LB(lb_append_tokens_spec_new(tokens, batch, pool_pages, qh, kvh, 128, 16, &token_spec));
         LB(lb_paged_spec_new(batch, pool_pages, qh, kvh, 128, 16, &spec));
-        LB(lb_rope_append_tokens_plan_create(provider, &token_spec, &plan));
+        lb_rope_append_options options{};
+        options.one_command = one_command ? 1 : 0;
+        LB(lb_rope_append_tokens_plan_create_with(provider, &token_spec, &options, &plan));
         lb_rope_append_plan_info info{};
         LB(lb_rope_append_plan_info_get(plan, &info));
         commands = (int)info.commands;
@@ -443,6 +445,8 @@ int main(int argc, char **argv) {
     }
     AppendCase c2("C2 RoPE+append b32 32/8 tokens1081 pool8192 extended", rope, 8192, 32, 8, c2_new,
                   c2_prior, true);
+    AppendCase c2_one("C2 RoPE+append b32 32/8 tokens1081 pool8192 extended, as one command", rope,
+                      8192, 32, 8, c2_new, c2_prior, true, true);
     // C1 of the configuration list: MHA batch 1, 32/32 heads, context 1024, plan-chosen split
     std::vector<int32_t> c1_pages(64);
     for (int i = 0; i < 64; ++i) c1_pages[i] = (i * 37 + 11) % 256;
@@ -480,7 +484,7 @@ int main(int argc, char **argv) {
                                                  {16}, 0, &o));
         }
     }
-    std::vector<Case *> cases = {&mha, &mqa, &gqa, &one, &six, &c2, &c1, &p_mha, &p_mqa, &p_gqa,
+    std::vector<Case *> cases = {&mha, &mqa, &gqa, &one, &six, &c2, &c2_one, &c1, &p_mha, &p_mqa, &p_gqa,
                                  &p_mqa_long, &p_gqa_long};
     for (DecodeCase *c : c1_variants) cases.push_back(c);
     for (Case *c : cases)

@@ -34,10 +34,14 @@ struct lb_paged_decode_plan {
     int32_t test_skip_page = 0;
 };
 
+// The one-command extended append keeps its slot hash set within this many bytes per CTA.
+constexpr size_t kFusedHashBytes = 16384;
+
 struct lb_rope_provider {
     int device = 0, sm_count = 0;
     size_t smem_optin = 0;
-    int32_t *status = nullptr; // device word; only the checked (bounds) build ever writes it
+    int32_t *status = nullptr; // device word: the checked (bounds) build, a wait that ran out
+    int fused_ctas_per_sm = 8; // CTAs of the one-command extended append that fit one SM
 };
 
 struct lb_rope_append_plan {
@@ -50,6 +54,9 @@ struct lb_rope_append_plan {
     bool extended = false;
     uint32_t validate_grid = 0;
     size_t workspace_numel = 0;
+    // ... or as ONE command whose token CTAs wait for the validators on words of the queue
+    bool fused = false, fused_possible = false;
+    uint32_t fused_grid = 0, fused_validators = 0;
     bool indices_capacity = false; // page_indices may be bound longer than the table in use
     int32_t *status = nullptr;
 };
@@ -521,14 +528,17 @@ lb_status lb_rope_provider_load(int device, lb_rope_provider **out) {
     }
     const size_t hash_bytes = 2 * lb_append_extended_max_tokens() * sizeof(int);
     int32_t *status = nullptr;
+    int fused_ctas = 8; // (what the fake driver's provider assumes)
     const int error = driver().configure(device, [&]() -> int {
         int e = configure_append_kernels(hash_bytes, inverse_frequency);
         if (e) return e;
         if ((e = cudaMalloc((void **)&status, 64))) return e;
-        return cudaMemset(status, 0, 64);
+        if ((e = cudaMemset(status, 0, 64))) return e;
+        return append_fused_ctas_per_sm(&fused_ctas, kFusedHashBytes);
     });
     if (error) return fail(LB_DRIVER, "provider_load", error);
     lb_rope_provider *provider = new lb_rope_provider();
+    provider->fused_ctas_per_sm = fused_ctas > 0 ? fused_ctas : 1;
     provider->status = status;
     provider->device = device;
     provider->sm_count = sm_count;
@@ -597,6 +607,22 @@ static lb_status make_append_plan(const lb_rope_provider *provider, const lb_pag
         const size_t scanners = (spec.max_num_pages + 8191) / 8192;
         plan->validate_grid = (uint32_t)(1 + (scanners > 31 ? 31 : scanners));
         plan->workspace_numel = (size_t)append_workspace_numel(tokens);
+        // One command is possible when the call is small enough for every CTA of the grid to be
+        // resident at once (the token CTAs wait for the validators inside the kernel): a hash set of at most
+        // kFusedHashBytes, validators of a quarter of the threads (so four times as many
+        // scanners), one token CTA per token up to what the device holds.
+        const size_t validators = 1 + (4 * scanners > 31 ? 31 : 4 * scanners);
+        const size_t resident =
+            (size_t)provider->fused_ctas_per_sm * (size_t)(provider->sm_count ? provider->sm_count : 148);
+        if (plan->shared_bytes <= kFusedHashBytes && resident > validators + 1) {
+            // (a token CTA holds two tokens ahead of the verdict: half as many CTAs as tokens
+            // when the call is larger than the device holds)
+            const size_t room = resident - validators;
+            const size_t token_ctas = tokens <= room ? tokens : ((tokens + 1) / 2 <= room ? (tokens + 1) / 2 : room);
+            plan->fused_possible = true; // (chosen by the one_command option only)
+            plan->fused_validators = (uint32_t)validators;
+            plan->fused_grid = (uint32_t)(validators + token_ctas);
+        }
     }
     *out = plan;
     return LB_OK;
@@ -610,7 +636,13 @@ static lb_status apply_append_options(const lb_rope_append_options *options,
         *plan = nullptr;
         return fail(LB_LAUNCH_CONTRACT, "indices_capacity", options->indices_capacity);
     }
+    if (options->one_command > 1 || (options->one_command == 1 && !(*plan)->fused_possible)) {
+        delete *plan;
+        *plan = nullptr;
+        return fail(LB_LAUNCH_CONTRACT, "one_command", options->one_command);
+    }
     (*plan)->indices_capacity = options->indices_capacity == 1;
+    (*plan)->fused = options->one_command == 1;
     return LB_OK;
 }
 
@@ -675,7 +707,7 @@ lb_status lb_rope_append_plan_info_get(const lb_rope_append_plan *plan,
     info->grid = plan->grid;
     info->block = plan->block;
     info->shared_bytes = plan->shared_bytes;
-    info->commands = plan->extended ? 2 : 1;
+    info->commands = plan->extended && !plan->fused ? 2 : 1;
     info->workspace_numel = plan->workspace_numel;
     return LB_OK;
 }
@@ -687,7 +719,7 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     if (scope->queue->device != plan->device)
         return fail(LB_BUFFER_CONTEXT_MISMATCH, nullptr, plan->device, scope->queue->device);
     // both commands of an extended plan must fit before anything is launched
-    lb_status rc = require_command_capacity(*scope, plan->extended ? 2 : 1);
+    lb_status rc = require_command_capacity(*scope, plan->extended && !plan->fused ? 2 : 1);
     if (rc) return rc;
 
     Operand op[11];
@@ -781,6 +813,12 @@ lb_status lb_rope_append_enqueue(const lb_rope_append_plan *plan, lb_scope *scop
     launch.workspace = (int32_t *)ws[0].ptr;
     launch.workspace_numel = (int32_t)ws[0].numel;
     launch.validate_grid = plan->validate_grid;
+    if (plan->fused) {
+        launch.grid = plan->fused_grid;
+        launch.validate_grid = plan->fused_validators;
+        launch.words = scope->queue->sync_words;
+        return submit_launch(*scope, [&]() { return launch_append_fused(launch, stream); });
+    }
     if ((rc = submit_launch(*scope, [&]() { return launch_append_validate(launch, stream); })))
         return rc;
     if ((rc = require_command_capacity(*scope, 1))) return rc;

@@ -33,12 +33,12 @@ def ulp_distance(a_bits, b_bits):
 
 class AppendRun:
     def __init__(self, provider, spec, q, k, v, indptr, indices, last, k_pages, v_pages,
-                 batch_indices=None, positions=None, max_commands=1):
+                 batch_indices=None, positions=None, max_commands=1, one_command=False):
         self.spec = spec
         self.provider = provider
         self.explicit = batch_indices is not None
-        self.plan = (provider.plan_bf16_paged_append_tokens(spec) if self.explicit
-                     else provider.plan_bf16_paged_append(spec))
+        self.plan = (provider.plan_bf16_paged_append_tokens(spec, one_command=one_command)
+                     if self.explicit else provider.plan_bf16_paged_append(spec))
         self.stream = torch.cuda.Stream()
         self.queue = lk.CommandQueue(self.stream, max(max_commands, self.plan.commands()))
         numel = self.plan.workspace_required_numel()  # extended plans: validate, then scatter
@@ -200,7 +200,8 @@ def test_short_metadata_is_rejected_before_submission(oracle, provider):
     completion.wait()
 
 
-def guard_run(provider, spec, indptr, indices, last, batch_indices=None, positions=None):
+def guard_run(provider, spec, indptr, indices, last, batch_indices=None, positions=None,
+              one_command=False):
     tokens = spec.tokens() if batch_indices is not None else spec.batch_size()
     qh, kvh = spec.num_query_heads(), spec.num_kv_heads()
     ks, vs = H.bf16_bits(np.array([-7.0], np.float32))[0], H.bf16_bits(np.array([9.0], np.float32))[0]
@@ -208,7 +209,7 @@ def guard_run(provider, spec, indptr, indices, last, batch_indices=None, positio
     run = AppendRun(provider, spec, np.zeros(tokens * qh * 128, np.uint16),
                     np.zeros(tokens * kvh * 128, np.uint16), np.zeros(tokens * kvh * 128, np.uint16),
                     indptr, indices, last, np.full(pool, ks, np.uint16), np.full(pool, vs, np.uint16),
-                    batch_indices, positions)
+                    batch_indices, positions, one_command=one_command)
     q, kp, vp = run.run()
     assert np.all(np.isnan(H.bits_to_f32(q))), "Q output written despite invalid metadata"
     assert np.all(kp == ks) and np.all(vp == vs), "page pools written despite invalid metadata"
@@ -226,6 +227,16 @@ def test_device_guards_preserve_every_sentinel(provider):
     guard_run(provider, spec, *table, batch_indices=[0, 1], positions=[1, 20])   # position
     guard_run(provider, spec, [0, 2, 4], [4, 1, 3, 2], [4, 4], batch_indices=[0, 1],
               positions=[16, 16])                                                # page index
+    # the same through the any-total plan, as two commands and as one (the token CTAs wait for
+    # the validators' verdict inside the kernel)
+    spec = lk.Bf16RopePagedKvAppendTokensSpec.new_extended(2, 2, 4, 2, 1)
+    for one_command in (False, True):
+        guard_run(provider, spec, *table, batch_indices=[0, 1], positions=[2, 2],
+                  one_command=one_command)
+        guard_run(provider, spec, *table, batch_indices=[0, 2], positions=[1, 1],
+                  one_command=one_command)
+        guard_run(provider, spec, [0, 2, 4], [4, 1, 3, 2], [4, 4], batch_indices=[0, 1],
+                  positions=[16, 16], one_command=one_command)
 
 
 def draw_append_batch(rng, batch, pool_pages, max_new=64, max_prior=2048):
@@ -238,8 +249,9 @@ def draw_append_batch(rng, batch, pool_pages, max_new=64, max_prior=2048):
     return indptr, indices, last, batch_indices, positions
 
 
+@pytest.mark.parametrize("one_command", [False, True])
 @pytest.mark.parametrize("shuffle", [False, True])
-def test_extended_append_equals_chunked_reference(oracle, provider, shuffle):
+def test_extended_append_equals_chunked_reference(oracle, provider, shuffle, one_command):
     # 32 requests x 1-64 new tokens, 32 q / 8 kv heads, priors 0-2048, shuffled 8192-page pool:
     # one extended command == the reference applied in <=64-token chunks
     rng = np.random.default_rng(0xC2)
@@ -256,9 +268,15 @@ def test_extended_append_equals_chunked_reference(oracle, provider, shuffle):
     pool = spec.kv_pages_numel()
     kp0, vp0 = H.normal_bf16(rng, pool), H.normal_bf16(rng, pool)
     run = AppendRun(provider, spec, q, k, v, indptr, indices, last, kp0, vp0, batch_indices,
-                    positions)
+                    positions, one_command=one_command)
     actual = run.run()
-    assert run.submitted == run.plan.commands() == 2
+    assert run.submitted == run.plan.commands() == (1 if one_command else 2)
+    if one_command:
+        # the words of the queue the token CTAs waited on are zero again: the same queue serves
+        # the next call (outputs reset in between, so that stale rows cannot pass)
+        run.q_out.fill_(float("nan"))
+        again = run.run()
+        assert all(np.array_equal(x, y) for x, y in zip(again, actual))
     ospec = oracle.paged_spec(batch, pool_pages, qh, kvh)
     kc, vc, qc = kp0, vp0, []
     for start in range(0, tokens, 64):

@@ -641,6 +641,12 @@ def test_indices_capacity_option_is_a_plan_property(fake):
     tokens_spec = lk.Bf16RopePagedKvAppendTokensSpec.new_extended(100, 4, 96, 16, 4)
     extended = rope.plan_bf16_paged_append_tokens(tokens_spec, indices_capacity=True)
     assert (extended.commands(), extended.workspace_required_numel()) == (2, 32 + 200)
+    extended = rope.plan_bf16_paged_append_tokens(tokens_spec, indices_capacity=True,
+                                                  one_command=True)
+    assert (extended.commands(), extended.workspace_required_numel()) == (1, 32 + 200)
+    with pytest.raises(lk.LoomError):  # a call too large for its whole grid to be resident
+        rope.plan_bf16_paged_append_tokens(
+            lk.Bf16RopePagedKvAppendTokensSpec.new_extended(4000, 4, 4096, 16, 4), one_command=True)
     lib = _abi.load()
     options = _abi.DecodeOptions(indices_capacity=2)
     out = ctypes.c_void_p()
