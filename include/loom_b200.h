@@ -240,7 +240,13 @@ lb_handle lb_handle_read(lb_handle read_write);
 lb_handle lb_handle_write(lb_handle read_write);
 
 /* CommandQueue::new, submission.rs:31-46.  `stream` is a cudaStream_t / CUstream owned by
- * the caller; it must outlive the queue. */
+ * the caller; it must outlive the queue.
+ * Beyond the reference: a queue also owns 64 KB of device words that are zero whenever none of
+ * its commands is running.  Kernels that count their own CTAs (plans made with merge_in_kernel,
+ * one_command) use them and leave them zero; the queue's stream is what keeps two such kernels
+ * apart, so commands of one queue must not be made to overlap by any other means, and a Graph
+ * uses the words of the queue it was captured on.  A queue that was poisoned does not hand its
+ * words on. */
 lb_status lb_queue_create(void *stream, size_t max_commands, lb_queue **out);
 /* Drop for CommandQueue, submission.rs:102-117 (synchronises retained work first).  While a scope
  * or completion of the queue is alive the destruction is deferred until it has settled (in Rust the
