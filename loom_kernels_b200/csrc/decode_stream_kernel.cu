@@ -68,7 +68,10 @@ __device__ __forceinline__ int owner_of(const int *prefix, int n, int y) {
 
 // kGather: the instantiation for plans that gather their output (the other one carries none of
 // its registers or shared memory).
-template <bool kGather>
+// kMerge: the instantiation that merges cut items itself (a.counters); the plain one carries none
+// of its registers (with the merge compiled into the one kernel the page loop spilled, and the
+// ragged MQA family went from 110 to 123 us).
+template <bool kGather, bool kMerge>
 __device__ __forceinline__ void balanced_decode_cta(const CUtensorMap &k_map,
                                                     const CUtensorMap &v_map, const StreamArgs &a,
                                                     PeerLocal &peer_local) {
@@ -365,7 +368,7 @@ __device__ __forceinline__ void balanced_decode_cta(const CUtensorMap &k_map,
                         write_state_row(slot, lane, half, st, bad);
                 }
             }
-            if (!complete && a.counters != nullptr) {
+            if (kMerge && !complete && a.counters != nullptr) {
                 // The item is cut: its states are counted, and the warp that finds them all there
                 // merges the rows of its tile and publishes them.  Nobody waits; the word wraps to
                 // zero on the last count, ready for the next command.
@@ -461,13 +464,13 @@ __device__ __forceinline__ void balanced_decode_cta(const CUtensorMap &k_map,
     if (*timeout_flag != 0 && tid == 0 && a.status) atomicExch(a.status, 1);
 }
 
-template <bool kGather>
+template <bool kGather, bool kMerge>
 __global__ void __launch_bounds__((kComputeWarps + kMaxProducerWarps) * 32, 1)
 balanced_decode_kernel(const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const StreamArgs a) {
     __shared__ PeerLocal peer_local;
     dependent_launch_release();
-    balanced_decode_cta<kGather>(k_map, v_map, a, peer_local);
+    balanced_decode_cta<kGather, kMerge>(k_map, v_map, a, peer_local);
     // a gathering plan that merges in this kernel: this is the command's last kernel
     if (!kGather || a.signal.world == 0 || a.signal.defer) return;
     __syncthreads(); // every row of this CTA has been stored; peer_local is complete
@@ -563,20 +566,22 @@ int balanced_state_rows(const DecodeLaunch &launch) {
 
 } // namespace
 
-template <bool kGather>
+template <bool kGather, bool kMerge>
 static int configure_balanced(size_t max_dynamic_shared) {
     // the opt-in limit covers static and dynamic shared memory together
     cudaFuncAttributes attributes;
-    const int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<kGather>);
+    const int rc = cudaFuncGetAttributes(&attributes, balanced_decode_kernel<kGather, kMerge>);
     if (rc) return rc;
-    return cudaFuncSetAttribute(balanced_decode_kernel<kGather>,
+    return cudaFuncSetAttribute(balanced_decode_kernel<kGather, kMerge>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)(max_dynamic_shared - attributes.sharedSizeBytes));
 }
 
 int configure_stream_kernels(size_t max_dynamic_shared) {
-    int rc = configure_balanced<false>(max_dynamic_shared);
-    if (!rc) rc = configure_balanced<true>(max_dynamic_shared);
+    int rc = configure_balanced<false, false>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<true, false>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<false, true>(max_dynamic_shared);
+    if (!rc) rc = configure_balanced<true, true>(max_dynamic_shared);
     return rc;
 }
 
@@ -613,7 +618,10 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));
-    auto kernel = launch.peer.world != 0 ? balanced_decode_kernel<true> : balanced_decode_kernel<false>;
+    const bool gather = launch.peer.world != 0, merge = launch.counters != nullptr;
+    auto kernel = merge ? (gather ? balanced_decode_kernel<true, true> : balanced_decode_kernel<false, true>)
+                        : (gather ? balanced_decode_kernel<true, false>
+                                  : balanced_decode_kernel<false, false>);
     return launch_dependent(kernel, launch.grid, launch.block, launch.shared_bytes, stream, k_map,
                             v_map, args);
 }
