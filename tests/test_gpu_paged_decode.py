@@ -143,7 +143,24 @@ def test_random_ragged_batches_balanced(oracle, provider, batch, qh, kvh, hc, pa
                 merge_in_kernel=merge_in_kernel)
 
 
-def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced, merge_in_kernel=0):
+@pytest.mark.parametrize("options", [dict(producer_warps=1), dict(producer_warps=4),
+                                     dict(max_stages=3), dict(producer_warps=4, max_stages=2)])
+def test_balanced_producer_and_ring_options(oracle, provider, options):
+    # one KV head per CTA (4 KB boxes): one producer warp for all four page slots or one per slot,
+    # and a ring capped below what shared memory allows, give the same results
+    ragged_case(oracle, provider, 3, 32, 1, 0, 0, balanced=1, merge_in_kernel=2, **options)
+    info = provider.plan_bf16_paged_batch(lk.Bf16PagedBatchDecodeSpec.new(3, 96, 32, 1),
+                                          balanced=1, **options).info()
+    assert info.block == (8 + options.get("producer_warps", 4)) * 32
+    if "max_stages" in options:
+        assert info.stages == options["max_stages"]
+    with pytest.raises(lk.PlanError):  # neither 1 nor the plan's page slots per stage
+        provider.plan_bf16_paged_batch(lk.Bf16PagedBatchDecodeSpec.new(3, 96, 32, 1), balanced=1,
+                                       producer_warps=3)
+
+
+def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced, merge_in_kernel=0,
+                **plan_options):
     rng = np.random.default_rng(batch * 1000 + qh * 10 + kvh + hc + partitions)
     pool = 96
     kv_lens = rng.integers(1, 16 * 18, size=batch)
@@ -163,7 +180,7 @@ def ragged_case(oracle, provider, batch, qh, kvh, hc, partitions, balanced, merg
     q = H.normal_bf16(rng, spec.query_numel())
     run = H.DecodeRun(spec, q, k, v, indptr, indices, last, partitions=partitions,
                       heads_per_cta=hc, provider=provider, balanced=balanced,
-                      merge_in_kernel=merge_in_kernel)
+                      merge_in_kernel=merge_in_kernel, **plan_options)
     if balanced == 1:
         assert run.plan.algorithm() == lk.Bf16PagedBatchDecodeAlgorithm.Balanced
     if partitions > 1 or balanced == 1:
