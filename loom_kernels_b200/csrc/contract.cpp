@@ -282,6 +282,7 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     const bool many_states_per_item =
         algorithm == LB_DECODE_BALANCED && states <= 2048 &&
         (size_t)grid * pps >= 8 * spec.batch_size * (spec.num_kv_heads / hc) * q_blocks;
+    out->merge_four_warps = many_states_per_item ? 1 : 0;
     out->merge_grid = algorithm == LB_DECODE_DIRECT || algorithm == LB_DECODE_CLUSTER_SPLIT ||
                               merged_in_kernel
                           ? 0

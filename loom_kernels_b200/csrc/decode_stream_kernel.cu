@@ -540,6 +540,10 @@ __device__ __forceinline__ void balanced_merge_warp(const float *__restrict__ wo
                                     output + (size_t)state * kHeadDim, lse + state);
 }
 
+// (A form in which a warp takes four consecutive rows of one KV head -- one look-up of the cut
+// for the four, their loads in flight together, a quarter of the warps -- measured the same
+// 14.5 us on the 8192 rows of a ragged MQA batch and slower on small grids: the kernel's time is
+// the instruction chain of one warp, about ten cycles per instruction, not the number of warps.)
 // (Capping the one-warp form at 64 registers for eight CTAs per SM spilled and measured slower:
 // 16.0 against 14.5 us on the 8192 rows of a ragged MQA batch.)
 template <int kWarps>
@@ -628,8 +632,7 @@ int launch_balanced_decode(const DecodeLaunch &launch, void *stream) {
 
 int launch_balanced_merge(const DecodeLaunch &launch, uint32_t grid, uint32_t block,
                           void *stream) {
-    // a grid of one CTA per (request, query head) means four warps per item
-    if ((uint64_t)grid >= (uint64_t)launch.batch * (uint64_t)launch.qh)
+    if (launch.merge_four_warps)
         return launch_dependent(balanced_merge_kernel<4>, grid, block, 0, stream,
                                 (const float *)launch.workspace,
                                 static_cast<__nv_bfloat16 *>(launch.output), launch.lse,

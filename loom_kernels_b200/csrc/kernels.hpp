@@ -58,6 +58,7 @@ struct DecodeLaunch {
     int32_t test_skip_page; // tests of the give-up path: 1 + the page of a CTA's chunk whose
                             // bytes never all arrive (0 = none)
     int32_t producer_warps; // balanced plans: 1, or one per page slot
+    int32_t merge_four_warps; // balanced plans: the merge gives every row a CTA of four warps
     int32_t *counters;      // one zeroed word per item when the split is merged in the kernel
     PeerOut peer;           // zeroed unless the plan gathers its output
     PeerSignal signal;      // zeroed unless this launch is the last kernel of a gathering command

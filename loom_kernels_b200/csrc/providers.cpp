@@ -375,6 +375,7 @@ lb_status enqueue_decode(const lb_paged_decode_plan *plan, lb_scope *scope,
     launch.stages = (int32_t)c.stages;
     launch.cluster = c.algorithm == LB_DECODE_CLUSTER_SPLIT ? 1 : 0;
     launch.producer_warps = (int32_t)c.producer_warps;
+    launch.merge_four_warps = (int32_t)c.merge_four_warps;
     launch.scale_log2 = spec.softmax_scale * kLog2E;
     launch.grid = c.grid;
     launch.block = c.block;

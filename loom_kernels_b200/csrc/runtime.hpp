@@ -173,6 +173,7 @@ struct DecodeChoice {
     uint32_t grid, block, shared_bytes, merge_grid, merge_block;
     size_t workspace_numel;
     uint32_t producer_warps;   // balanced plans: warps that issue the page copies
+    uint32_t merge_four_warps; // balanced plans: the merge kernel's form (many states per item)
     uint32_t merged_in_kernel; // split-K as one command: the last CTA of an item merges it
 };
 lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t smem_optin,
