@@ -265,15 +265,17 @@ __global__ void __launch_bounds__(kThreads, 2) rope_append_kernel(const AppendAr
         if (begin < 0 || end <= begin || end > table_end || tail < 1 || tail > kPage)
             invalid = true;
     }
-    for (int base = 0; base < table_end; base += 4 * kThreads) {
-        int id[4];
+    // (eight loads per thread per round: a table of up to 4096 pages -- the C2 calls have 2100 --
+    // is one round trip, not two)
+    for (int base = 0; base < table_end; base += 8 * kThreads) {
+        int id[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
             const int page = base + u * kThreads + tid;
             id[u] = page < table_end ? a.indices[page] : 0;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
+        for (int u = 0; u < 8; ++u) invalid |= id[u] < 0 || id[u] >= a.max_pages;
     }
     if (__syncthreads_or(invalid)) return;
 
