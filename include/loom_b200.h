@@ -689,7 +689,13 @@ typedef struct lb_paged_prefill_options {
                                   (at most 64) = the 64-token KV blocks of every tile are shared
                                   out to up to N CTAs by the balanced rule of the split-K contract
                                   (single_decode/mod.rs:171-185); see min_chunk_blocks */
-    uint32_t reserved[4];
+    uint32_t wait_limit_us;    /* tiled only: limit of every bounded wait, in microseconds; 0 = about
+                                  two seconds.  When it runs out the CTA writes nothing, waits (bounded
+                                  again) for its copies and MMAs in flight, frees its TMEM, and the
+                                  provider's status word reads 1 */
+    uint32_t test_lost_copy;   /* tiled only, tests of that give-up path: 1 = the barrier of a CTA's
+                                  first K block expects 16 bytes more than its copies deliver */
+    uint32_t reserved[2];
 } lb_paged_prefill_options;
 
 typedef struct lb_paged_prefill_plan_info {

@@ -120,7 +120,8 @@ class PrefillSpec(ctypes.Structure):
 
 class PrefillOptions(ctypes.Structure):
     _fields_ = [("q_tiles", c_uint32), ("indices_capacity", c_uint32), ("algorithm", c_uint32),
-                ("partitions", c_uint32), ("reserved", c_uint32 * 4)]
+                ("partitions", c_uint32), ("wait_limit_us", c_uint32),
+                ("test_lost_copy", c_uint32), ("reserved", c_uint32 * 2)]
 
 
 class PrefillPlanInfo(ctypes.Structure):

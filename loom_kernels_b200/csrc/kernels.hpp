@@ -144,6 +144,8 @@ struct PrefillLaunch {
     float *workspace;
     int32_t partitions;
     int32_t min_chunk_blocks; // a tile uses min(partitions, its blocks / min_chunk_blocks) chunks
+    long long wait_cycles;    // tiled kernel: limit of its bounded waits (0 = the default)
+    int32_t test_lost_copy;   // tiled kernel, tests of the give-up path only
 };
 int configure_prefill_kernels(size_t max_dynamic_shared);
 int launch_paged_prefill(const PrefillLaunch &launch, void *stream);

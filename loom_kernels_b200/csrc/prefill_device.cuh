@@ -25,6 +25,9 @@ struct PrefillArgs {
     // plan-chosen count would come out below three): the count follows the KV length actually
     // met, which a plan cannot know
     int32_t min_chunk_blocks;
+    long long wait_cycles;  // limit of every bounded wait (tiled kernel)
+    int32_t test_lost_copy; // tests of the give-up path: the barrier of the first K block expects
+                            // 16 bytes more than its copies deliver
 };
 
 // Chunks a tile of `tile_blocks` 64-token blocks is cut into.  One chunk means the CTA writes O and

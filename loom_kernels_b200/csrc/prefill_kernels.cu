@@ -323,6 +323,8 @@ int launch_paged_prefill(const PrefillLaunch &launch, void *stream) {
     args.workspace = nullptr;
     args.partitions = 1;
     args.min_chunk_blocks = 1;
+    args.wait_cycles = 0; // (the tiled kernel's)
+    args.test_lost_copy = 0;
     CUtensorMap k_map, v_map;
     memcpy(&k_map, launch.k_map, sizeof(k_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));

@@ -28,6 +28,8 @@ struct lb_paged_prefill_plan {
     int device = 0;
     int32_t *status = nullptr;
     bool indices_capacity = false;
+    long long wait_cycles = 0; // tiled kernel: 0 = the default limit
+    int32_t test_lost_copy = 0;
 };
 
 namespace {
@@ -399,6 +401,12 @@ lb_status lb_paged_prefill_plan_create(const lb_prefill_provider *provider,
     plan->device = provider->device;
     plan->status = provider->status;
     plan->indices_capacity = options && options->indices_capacity == 1;
+    if (options && options->wait_limit_us) {
+        int khz = 0;
+        driver().device_clock_khz(provider->device, &khz);
+        plan->wait_cycles = (long long)options->wait_limit_us * (khz > 0 ? khz : 1965000) / 1000;
+    }
+    plan->test_lost_copy = options && options->test_lost_copy ? 1 : 0;
     *out = plan;
     return LB_OK;
 }
@@ -498,6 +506,8 @@ lb_status lb_paged_prefill_enqueue(const lb_paged_prefill_plan *plan, lb_scope *
     launch.workspace = split ? (float *)op[9].ptr : nullptr;
     launch.partitions = (int32_t)c.partitions;
     launch.min_chunk_blocks = (int32_t)c.min_chunk_blocks;
+    launch.wait_cycles = plan->wait_cycles;
+    launch.test_lost_copy = plan->test_lost_copy;
     void *stream = scope->queue->stream;
     if ((rc = submit_launch(*scope, [&]() {
              return tiled ? launch_paged_prefill_tiled(launch, stream)

@@ -32,9 +32,11 @@
 //                [max_log2, normaliser, weighted values] of its share into a workspace and
 //                prefill_merge_kernel, a second command, merges them per (query row, head).
 //
-// Device-resident metadata is never an error (prefill.rs:289-347).  Every mbarrier wait is bounded;
-// after a timeout every role leaves its loop, the CTA frees its TMEM, records a status word and
-// writes nothing.
+// Device-resident metadata is never an error (prefill.rs:289-347).  Every mbarrier wait is bounded
+// (the plan's wait limit); after a timeout every role leaves its loop -- the producer after a
+// bounded wait for the copies it has in flight, the MMA warp after a bounded wait for the MMAs it
+// has issued (a commit on a barrier of its own) -- and only then the CTA frees its TMEM, records a
+// status word and leaves without writing.
 #include <cstring>
 
 #include "kernels.hpp"
@@ -69,7 +71,7 @@ constexpr int kOffBars = kOffV + kStages * kVStageBytes;
 // q_full (the Q tile is in shared memory and TMEM is allocated)
 constexpr int kBarKFull = 0, kBarKEmpty = 2, kBarVFull = 4, kBarVEmpty = 6, kBarSFull = 8,
               kBarSFree = 9, kBarPFull = 10, kBarPFree = 12, kBarVerdict = 14, kBarQFull = 15,
-              kNumBars = 16;
+              kBarDrain = 16, kNumBars = 17;
 constexpr int kOffMisc = kOffBars + kNumBars * 8; // tmem base address, flags
 constexpr int kSharedBytes = kOffMisc + 24;
 static_assert(2 * (kSharedBytes + 1024) <= 233472, "two CTAs must fit one SM");
@@ -85,6 +87,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    auto wait_on = [&](uint32_t bar, uint32_t parity) { return mbar_wait(bar, parity, a.wait_cycles); };
     uint8_t *base = smem_raw;
     const uint32_t base_u32 = smem_u32(base);
     const uint32_t bars = base_u32 + kOffBars;
@@ -187,7 +190,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
     }
     bool q_ready = true;
     if (warp != 4) {
-        q_ready = __all_sync(0xffffffffu, mbar_wait(bars + kBarQFull * 8, 0));
+        q_ready = __all_sync(0xffffffffu, wait_on(bars + kBarQFull * 8, 0));
         tc_fence_after();
     }
     const uint32_t tmem_base = misc[0]; // not used by the producer warp
@@ -231,7 +234,9 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         auto pages_in = [&](int block) { return min(kBlockPages, cnt - block * kBlockPages); };
         auto load_k = [&](int block, int id) {
             const int stage = block & 1;
-            if (lane == 0) mbar_expect_tx(bars + (kBarKFull + stage) * 8, pages_in(block) * 4096);
+            if (lane == 0)
+                mbar_expect_tx(bars + (kBarKFull + stage) * 8,
+                               pages_in(block) * 4096 + (block == 0 && a.test_lost_copy ? 16 : 0));
             __syncwarp();
             if (is_k && block * kBlockPages + slot < cnt)
                 tma_load_3d(base_u32 + kOffK + stage * kKStageBytes + half * kKHalfBytes + slot * 2048,
@@ -252,23 +257,29 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         const int k_slot = lane >> 1, v_slot = lane - 8; // the page of a block this lane loads
         load_k(0, id_of_page(k_slot));
         if (blocks > 1) load_k(1, id_of_page(kBlockPages + k_slot));
+        int k_issued = blocks > 1 ? 1 : 0, v_issued = -1; // the last blocks whose copies were issued
+        bool gave_up = false;
         for (int j = 0; j < blocks; ++j) {
             const int stage = j & 1;
             const int v_id = id_of_page(j * kBlockPages + v_slot);
             const int k_id = id_of_page((j + 2) * kBlockPages + k_slot);
-            bool ok = j < kStages || mbar_wait(bars + (kBarVEmpty + stage) * 8, ((j >> 1) + 1) & 1);
+            bool ok = j < kStages || wait_on(bars + (kBarVEmpty + stage) * 8, ((j >> 1) + 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
+                gave_up = true;
                 break;
             }
             load_v(j, v_id);
+            v_issued = j;
             if (j + 2 < blocks) {
-                ok = mbar_wait(bars + (kBarKEmpty + stage) * 8, (j >> 1) & 1); // S(j) has completed
+                ok = wait_on(bars + (kBarKEmpty + stage) * 8, (j >> 1) & 1); // S(j) has completed
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) misc[2] = 1;
+                    gave_up = true;
                     break;
                 }
                 load_k(j + 2, k_id);
+                k_issued = j + 2;
             }
             if ((((j + 1) * kBlockPages) >> 5) != first_window) { // the values enter the next window
                 ++first_window;
@@ -276,6 +287,19 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 win1 = load_window(first_window + 1);
             }
         }
+        if (gave_up && lane < 4) {
+            // A wait ran out: before this CTA frees its TMEM and leaves, the copies already on
+            // their way are waited for (bounded again), so that none lands in shared memory the
+            // next CTA may own.  Lanes 0, 1: the K stages; lanes 2, 3: the V stages; each waits
+            // for the last block issued into its stage.
+            const int stage = lane & 1;
+            const int issued = lane < 2 ? k_issued : v_issued;
+            const int block = issued >= 0 && (issued & 1) != stage ? issued - 1 : issued;
+            if (block >= 0)
+                (void)wait_on(bars + ((lane < 2 ? kBarKFull : kBarVFull) + stage) * 8,
+                              (block >> 1) & 1);
+        }
+        __syncwarp();
         // the reference validates every page of the request, also those past the causal limit of
         // a row (prefill.rs:333-340): the pages this CTA does not stream are range-checked
         for (int j = cnt + lane; j < num_pages; j += 32) {
@@ -297,8 +321,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         const uint64_t v_desc0 = smem_desc(base_u32 + kOffV, 2048, 1024);
         auto issue_pv = [&](int i) -> bool {
             const int stage = i & 1, buffer = i & 1;
-            bool ok = mbar_wait(bars + (kBarPFull + buffer) * 8, (i >> 1) & 1);
-            ok = mbar_wait(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
+            bool ok = wait_on(bars + (kBarPFull + buffer) * 8, (i >> 1) & 1);
+            ok = wait_on(bars + (kBarVFull + stage) * 8, (i >> 1) & 1) && ok;
             if (!ok) return false;
             tc_fence_after();
             const int pages_here = min(kBlockPages, cnt - i * kBlockPages);
@@ -319,8 +343,8 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         bool ok = q_ready;
         for (int j = 0; j < blocks && ok; ++j) {
             const int stage = j & 1;
-            ok = mbar_wait(bars + (kBarKFull + stage) * 8, (j >> 1) & 1);
-            if (ok && j > 0) ok = mbar_wait(bars + kBarSFree * 8, (j - 1) & 1);
+            ok = wait_on(bars + (kBarKFull + stage) * 8, (j >> 1) & 1);
+            if (ok && j > 0) ok = wait_on(bars + kBarSFree * 8, (j - 1) & 1);
             if (!ok) break;
             tc_fence_after();
             if (elect_one()) {
@@ -338,7 +362,14 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (j > 0) ok = issue_pv(j - 1);
         }
         if (ok) ok = issue_pv(blocks - 1);
-        if (!ok && lane == 0) misc[2] = 1;
+        if (!ok) {
+            // a wait ran out: the MMAs already issued complete before the TMEM goes (the commit
+            // arrives on the barrier when every earlier tcgen05 operation of the thread has)
+            if (lane == 0) misc[2] = 1;
+            if (elect_one()) umma_commit(bars + kBarDrain * 8);
+            __syncwarp();
+            (void)wait_on(bars + kBarDrain * 8, 0);
+        }
     } else {
         // ================= softmax + epilogue: thread t owns packed row t ===========================
         // tokens of the share this row sees (none when negative)
@@ -349,7 +380,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
         float l = 0.0f;
         bool ok = q_ready;
         for (int j = 0; q_ready && j < blocks; ++j) {
-            ok = mbar_wait(bars + kBarSFull * 8, j & 1);
+            ok = wait_on(bars + kBarSFull * 8, j & 1);
             if (__any_sync(0xffffffffu, !ok)) break;
             tc_fence_after();
             float s[kBlockTokens]; // raw dot products
@@ -386,7 +417,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
                 m_used = m_new;
                 if (j > 0) {
                     // O holds blocks 0..j-1 once P V (j - 1) has completed
-                    ok = mbar_wait(bars + (kBarPFree + ((j - 1) & 1)) * 8, ((j - 1) >> 1) & 1);
+                    ok = wait_on(bars + (kBarPFree + ((j - 1) & 1)) * 8, ((j - 1) >> 1) & 1);
                     if (__any_sync(0xffffffffu, !ok)) break;
                     tc_fence_after();
 #pragma unroll
@@ -426,7 +457,7 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             const int last_page = num_pages - 1;
             const bool zero_tail = tail < kPage && last_page / kBlockPages == j && last_page < cnt;
             if (zero_tail) {
-                ok = mbar_wait(bars + (kBarVFull + (j & 1)) * 8, (j >> 1) & 1);
+                ok = wait_on(bars + (kBarVFull + (j & 1)) * 8, (j >> 1) & 1);
                 if (__any_sync(0xffffffffu, !ok)) break;
                 uint8_t *v_page =
                     base + kOffV + (j & 1) * kVStageBytes + (last_page % kBlockPages) * 4096;
@@ -445,12 +476,12 @@ paged_prefill_tiled_kernel(const __grid_constant__ CUtensorMap k_half_map,
             if (lane == 0) misc[2] = 1;
         } else {
             // every P V has completed once the last one has
-            ok = mbar_wait(bars + (kBarPFree + ((blocks - 1) & 1)) * 8, ((blocks - 1) >> 1) & 1);
+            ok = wait_on(bars + (kBarPFree + ((blocks - 1) & 1)) * 8, ((blocks - 1) >> 1) & 1);
             if (__any_sync(0xffffffffu, !ok)) {
                 if (lane == 0) misc[2] = 1;
             } else {
                 tc_fence_after();
-                const bool verdict = mbar_wait(bars + kBarVerdict * 8, 0); // the producer's page scan
+                const bool verdict = wait_on(bars + kBarVerdict * 8, 0); // the producer's page scan
                 const bool settled = verdict && row_valid && misc[2] == 0;
                 float *my_partial = chunks > 1 ? partial_state() : nullptr;
                 const bool publish = settled && misc[1] == 0 && my_partial == nullptr;
@@ -589,6 +620,8 @@ int launch_paged_prefill_tiled(const PrefillLaunch &launch, void *stream) {
     args.workspace = launch.workspace;
     args.partitions = launch.partitions > 1 ? launch.partitions : 1;
     args.min_chunk_blocks = launch.min_chunk_blocks > 1 ? launch.min_chunk_blocks : 1;
+    args.wait_cycles = launch.wait_cycles > 0 ? launch.wait_cycles : kWaitCycles;
+    args.test_lost_copy = launch.test_lost_copy;
     CUtensorMap k_half_map, v_map;
     memcpy(&k_half_map, launch.k_map, sizeof(k_half_map));
     memcpy(&v_map, launch.v_map, sizeof(v_map));

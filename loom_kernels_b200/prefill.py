@@ -160,14 +160,18 @@ class PrefillProvider:
 
     def plan_bf16_paged(self, spec: Bf16PagedPrefillSpec, q_tiles: int = 0,
                         indices_capacity: bool = False, algorithm: int = 0,
-                        partitions: int = 0) -> "Bf16PagedPrefillPlan":
+                        partitions: int = 0, wait_limit_us: int = 0,
+                        test_lost_copy: bool = False) -> "Bf16PagedPrefillPlan":
         """algorithm: 0 heuristic, 1 token-parallel, 2 tiled (tcgen05).  q_tiles (token-parallel):
         0 heuristic, else the 16-row tiles of packed query rows one CTA owns (1, 2, 4 or 8).
         partitions (tiled): 0 heuristic, 1 one CTA per tile, N > 1 the KV blocks of every tile
         shared out to N CTAs whose states a second command merges (needs the workspace).
-        indices_capacity as for the decode plan."""
+        indices_capacity as for the decode plan.  wait_limit_us (tiled): limit of the kernel's
+        bounded waits, 0 = about two seconds; test_lost_copy: tests of the give-up path only."""
         options = _abi.PrefillOptions(q_tiles=q_tiles, algorithm=algorithm, partitions=partitions,
-                                      indices_capacity=1 if indices_capacity else 0)
+                                      indices_capacity=1 if indices_capacity else 0,
+                                      wait_limit_us=wait_limit_us,
+                                      test_lost_copy=1 if test_lost_copy else 0)
         out = c_void_p()
         _check(_abi.load().lb_paged_prefill_plan_create(self._ptr, byref(spec._raw),
                                                         byref(options), byref(out)))

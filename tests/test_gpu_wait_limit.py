@@ -75,3 +75,48 @@ def test_wait_limit_option_leaves_results_unchanged():
     limited.plan = provider.plan_bf16_paged_batch(spec, partitions=1, wait_limit_us=50000)
     got = limited.run()
     assert np.array_equal(base[0], got[0]) and np.array_equal(base[1], got[1])
+
+
+def test_tiled_prefill_gives_up_without_a_hang(oracle):
+    """The tcgen05 prefill kernel: the barrier of every CTA's first K block expects more bytes
+    than arrive (`test_lost_copy`), the MMA warp's wait for it runs out after a millisecond, the
+    other roles' waits follow, the producer and the MMA warp wait -- bounded again -- for what they
+    have in flight, the CTA frees its TMEM and writes nothing; status 1, sentinels kept, and the
+    next plan on the same provider is correct."""
+    from tests.test_gpu_prefill import PrefillRun, check, ragged_case
+
+    rng = np.random.default_rng(33)
+    qh, kvh, pool = 8, 2, 64
+    qo_lens, kv_lens = [200, 131], [200, 300]
+    q, k, v, qo_indptr, indptr, indices, last = ragged_case(rng, qo_lens, kv_lens, qh, kvh, pool)
+    dims = (len(qo_lens), int(qo_indptr[-1]), pool, qh, kvh)
+    spec = lk.Bf16PagedPrefillSpec.new(*dims)
+    provider = lk.PrefillProvider.load(0)
+    assert provider.device_status() == 0
+
+    broken = PrefillRun(provider, spec, q, k, v, qo_indptr, indptr, indices, last, algorithm=2)
+    broken.plan = provider.plan_bf16_paged(spec, algorithm=2, partitions=1, wait_limit_us=1000,
+                                           test_lost_copy=True)
+    b = broken.queue.bindings(10)
+    reads = [b.bind_read(t) for t in broken.tensors]
+    h_out, h_lse = b.bind_read_write(broken.out), b.bind_read_write(broken.lse)
+    scope = broken.queue.begin(b)
+    broken.plan.enqueue_into(scope, lk.Bf16PagedPrefillArgs(*reads, h_out.write(), h_lse.write(),
+                                                            None))
+    b = scope.finish().wait()  # the kernel returns by itself
+    assert provider.device_status() == 1  # read and cleared
+    assert provider.device_status() == 0
+    out = H.bits_to_f32(H.host_bits(b.take_read_write(h_out)))
+    assert np.all(np.isnan(out)) and np.all(np.isnan(b.take_read_write(h_lse).cpu().numpy()))
+
+    # the provider and the device are as usable as before
+    good, good_lse = PrefillRun(provider, spec, q, k, v, qo_indptr, indptr, indices, last,
+                                algorithm=2).run()
+    expected, expected_lse = oracle.paged_prefill(oracle.prefill_spec(*dims), q, k, v, qo_indptr,
+                                                  indptr, indices, last)
+    check(good, good_lse, expected, expected_lse, gate=False)
+    # and a short limit with nothing lost changes no bit
+    limited = PrefillRun(provider, spec, q, k, v, qo_indptr, indptr, indices, last, algorithm=2)
+    limited.plan = provider.plan_bf16_paged(spec, algorithm=2, partitions=1, wait_limit_us=50000)
+    again, again_lse = limited.run()
+    assert np.array_equal(again, good) and np.array_equal(again_lse, good_lse)
