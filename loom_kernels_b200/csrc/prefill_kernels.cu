@@ -99,6 +99,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
     const int mtile = warp % a.mt; // consumer: which 16-row tile of the CTA
     const long long warp_row = row_lo + mtile * 16;
 
+    int producer_trips = 0; // producer lanes: iterations of the page loop that issued copies
     if (warp == kComputeWarps) {
         // ================= producer warp: page-table walk + TMA issue =========================
         const int my_slot = lane >> 1;
@@ -129,7 +130,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
         int stage = 0;
         uint32_t phase = 0;
         bool recycled = false;
-        for (int it = 0; it < n_iter; ++it) {
+        int it = 0;
+        for (; it < n_iter; ++it) {
             const int first = it * a.pps;
             if (it > 0 && (first & 31) == 0) {
                 window = window_next;
@@ -156,6 +158,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
                 recycled = true;
             }
         }
+        producer_trips = it;
         // the reference validates every page of the request, also those past the causal limit
         // of a row (prefill.rs:333-340): the pages this CTA does not stream are range-checked
         for (int j = cnt + lane; j < num_pages; j += 32) {
@@ -230,6 +233,15 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap k_map,
     // ---- join: every TMA write has been consumed or abandoned; the ring becomes scratch ---------
     __syncthreads();
     if (flags[1] != 0) {
+        // a wait ran out: nothing is published; the copies already on their way are waited for
+        // (bounded), so that none lands in shared memory after this CTA has gone
+        if (warp == kComputeWarps && (lane & 1) == 0 && (lane >> 1) < a.pps) {
+            const int slot = lane >> 1;
+            const int mine = cnt > slot ? (cnt - slot + a.pps - 1) / a.pps : 0;
+            drain_issued_copies(full0 + slot * 8, a.pps * 8, a.stages, min(producer_trips, mine),
+                                kWaitCycles);
+        }
+        __syncthreads();
         if (tid == 0 && a.status) atomicExch(a.status, 1);
         return;
     }
