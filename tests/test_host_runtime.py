@@ -439,6 +439,39 @@ def test_rope_append_enqueue_preflight(fake):
         provider.plan_bf16_paged_append_tokens(lk.Bf16RopePagedKvAppendTokensSpec.new(65, 1, 4, 1, 1))
 
 
+def test_extended_append_as_one_command_or_two(fake):
+    """The any-total append: two commands (validate, scatter) by default, one on request; both
+    need the workspace, and the one-command form fits a queue of one command."""
+    provider = lk.RopeProvider.load(0)
+    spec = lk.Bf16RopePagedKvAppendTokensSpec.new_extended(100, 4, 96, 16, 4)
+    sizes = [100 * 16 * 128, 100 * 4 * 128, 100 * 4 * 128, 100, 100, 5, 40, 4]
+    names = ["query", "key", "value", "batch_indices", "positions", "page_indptr", "page_indices",
+             "last_page_len"]
+    for one_command, commands in ((False, 2), (True, 1)):
+        plan = provider.plan_bf16_paged_append_tokens(spec, one_command=one_command)
+        assert plan.info().commands == commands and plan.workspace_required_numel() == 32 + 200
+        queue = lk.CommandQueue(0x100, commands)
+        b = queue.bindings(12)
+        h = {}
+        for i, (name, numel) in enumerate(zip(names, sizes)):
+            h[name] = b.bind_read(D(0x20000000 + i * 0x1000000, numel,
+                                    _abi.BF16 if i < 3 else _abi.I32))
+        q = b.bind_read_write(D(0x2a000000, 100 * 16 * 128, _abi.BF16))
+        k = b.bind_read_write(D(0x2b000000, spec.kv_pages_numel(), _abi.BF16))
+        v = b.bind_read_write(D(0x2c000000, spec.kv_pages_numel(), _abi.BF16))
+        ws = b.bind_read_write(D(0x2d000000, 32 + 200, _abi.I32))
+        args = lk.Bf16RopePagedKvAppendTokensArgs(query_output=q.write(), key_pages=k.write(),
+                                                  value_pages=v.write(), workspace=ws, **h)
+        scope = queue.begin(b)
+        before = fake.lb_test_launch_count()
+        plan.enqueue_into(scope, args)
+        assert fake.lb_test_launch_count() - before == commands
+        with pytest.raises(lk.CommandError) as e:  # the queue is full
+            plan.enqueue_into(scope, args)
+        assert e.value.variant == "CommandCapacityExceeded"
+        assert scope.finish().submitted() == commands
+
+
 def test_rope_pos_ids_contract_and_preflight(fake):
     """Bf16RopePosIdsSpec::new (crates/loom-infer/src/rope/mod.rs:21-62), plan_bf16_pos_ids
     (crates/loom-infer-cuda/src/rope/mod.rs:592-626) and the enqueue preflight (:698-742)."""
