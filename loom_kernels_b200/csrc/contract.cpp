@@ -192,6 +192,13 @@ lb_status choose_decode(const lb_paged_spec &spec, uint32_t sm_count, size_t sme
     if (algorithm == LB_DECODE_BALANCED) extra += balanced_extra;
     uint32_t stages = (uint32_t)((smem - extra) / stage_bytes);
     if (stages > 6) stages = 6;
+    // A balanced plan with one KV head per CTA (4 KB boxes, a producer warp per page slot) keeps
+    // four stages = 128 KB in flight per SM: scattered 4 KB reads stream best with about 100 KB
+    // in flight (a probe: 6.5 TB/s with 96 KB, 6.0 with 192 KB), and the kernel measured 108.3 us
+    // on the ragged MQA batch with four stages against 109.8 with six (111.2 with three).
+    if (algorithm == LB_DECODE_BALANCED && hc == 1 && pps > 1 && pps <= 4 && stages > 4 &&
+        !(options && (options->producer_warps == 1 || options->max_stages != 0)))
+        stages = 4;
     if (options && options->max_stages >= 2 && stages > options->max_stages)
         stages = options->max_stages;
     // direct/split CTAs merge their warps' states in the ring: 8 warps x 68 x 32 floats
